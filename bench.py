@@ -1,0 +1,438 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): int4 block-quantized GEMV at the Llama-7B
+MLP shapes, W 11008x4096 (K = 4096) and 4096x11008 (K = 11008), weights
+N(0, 0.02) from a seed, symmetric 4-bit with one f32 scale per 32-element
+block, x f32 N(0, 1), M = 1, through the arithmetic of the reference operator
+qlinear-i8 (activation quantized to int8 inside the op, integer block dots,
+per-block scale fold).  Inputs are synthetic and seeded; there is no dataset.
+
+One step = one pass of the operator over R distinct device copies of each
+weight matrix (R * bytes >= 4 x L2, so every launch streams its weights from
+HBM, not from the 126 MB L2), replayed as one CUDA graph.  `value` is
+weight-stream GB/s = (codes + scales bytes of every launch) / device time.
+
+Printed on one JSON line (rank 0): the contract keys plus
+  roofline      dominant kernel (the decode GEMV) timed alone on the same
+                rotation: algorithmic bytes per launch / average launch time,
+                against the measured HBM copy peak
+  e2e           the same metric through the host-array C-ABI operator
+                rstq_qlinear_i8 (x up, y down over PCIe every call)
+  cpu_baseline  the vectorised CPU port of the reference's production kernel on
+                the host cores of this box (rank 0, N = 1 only)
+  detail        other M / dtype / shape points of the same path
+
+With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank owns the
+column shard [rank*out, (rank+1)*out) of an N-times wider matrix per shape and
+streams it; the all-gather of the y slices is the fused peer-store epilogue
+when available.  Per-GPU work is fixed, so scaling is "weak".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [("gate_up", 11008, 4096), ("down", 4096, 11008)]   # (name, out, in)
+SEED_W, SEED_X = 1, 2
+SIGMA_W = 0.02
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def stream_bytes(out, in_, bits=4):
+    return out * in_ * bits // 8 + out * (in_ // 32) * 4
+
+
+def algorithmic_bytes(out, in_, M, bits=4, act_bytes=4, out_bytes=4):
+    return stream_bytes(out, in_, bits) + M * in_ * act_bytes + M * out * out_bytes
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0=None, t1=None):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.rows:
+            if t0 is not None and not (t0 - 0.05 <= ts <= t1 + 0.15):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_weights(rank=0):
+    """Quantized host weights of both shapes in the reference layouts."""
+    from raster_b200 import synth
+    from raster_b200.quant import cpu_quant as cq
+    ws = []
+    for i, (name, out, in_) in enumerate(SHAPES):
+        w = synth.normal(SEED_W + 10 * i + 1000 * rank, out * in_, SIGMA_W)
+        q = cq.quantize_weight(w, cq.q4_0)
+        r = cq.repack_stream(q["wq"], q["ws"], out, in_, cq.q4_0)
+        x = synth.normal(SEED_X + 10 * i, 8 * in_)
+        ws.append({"name": name, "out": out, "in": in_, "wq": q["wq"], "ws": q["ws"],
+                   "wqi": r["wqi"], "wsi": r["wsi"], "x": x})
+    return ws
+
+
+def time_graph(ctx, graph, steps, warmup):
+    for _ in range(warmup):
+        graph.replay()
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    ctx.sync()
+    ms = e0.elapsed_ms(e1)
+    e0.destroy(), e1.destroy()
+    return ms
+
+
+def run_ours(args):
+    from raster_b200 import Context
+    from raster_b200 import _lib as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    hbm_peak, peak_src = measured_peaks()
+    ctx = Context((f"cuda:{local_rank}",))
+    info = ctx.device_info()
+    weights = make_weights(rank)
+    per_pass = sum(stream_bytes(w["out"], w["in"]) for w in weights)
+    R = max(2, -(-4 * info["l2_bytes"] // per_pass))
+
+    # device state: R copies of each weight, activations, outputs
+    bound, xbuf, ybuf = [], [], []
+    for w in weights:
+        first = ctx.bind_weight(w["wqi"], w["wsi"], w["out"], w["in"], L.FMT_Q4_0, L.LAYOUT_STREAM8)
+        bound.append([first] + [first.clone() for _ in range(R - 1)])
+        xbuf.append(ctx.array_to_buffer(w["x"]))
+        ybuf.append(ctx.make_buffer(8 * w["out"], np.float32))
+
+    def capture(fn):
+        fn(False)                       # sizes scratch before capture
+        ctx.sync()
+        ctx.graph_begin()
+        fn(True)
+        return ctx.graph_end()
+
+    def op_pass(M, act=L.F32, mode=L.MODE_A8, xb=None):
+        def f(_):
+            for r in range(R):
+                for i in range(len(weights)):
+                    ctx.qmatmul(bound[i][r], (xb or xbuf)[i], ybuf[i], M, act, L.F32, mode)
+        return f
+
+    # ---- headline: the operator (quantize + GEMV), M = 1, f32 x ------------
+    g_op = capture(op_pass(1))
+    kernels_per_step = 2 * R * len(weights)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        ctx.sync()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    for _ in range(args.warmup):
+        g_op.replay()
+    barrier()
+    t0 = time.perf_counter()
+    e0, e1 = ctx.event(), ctx.event()
+    e0.record()
+    for _ in range(args.steps):
+        g_op.replay()
+    e1.record()
+    barrier()
+    t1 = time.perf_counter()
+    ms = e0.elapsed_ms(e1)
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    ms_per_step = ms / args.steps
+    total_stream = per_pass * R * world
+    value = total_stream / (ms_per_step * 1e-3) / 1e9
+
+    result = None
+    if rank == 0:
+        # ---- roofline: the GEMV alone on pre-quantized activations ---------
+        from raster_b200.quant import cpu_quant as cq
+        xq_b, xs_b, xsum_b = [], [], []
+        for w in weights:
+            a = cq.quantize_act_i8(w["x"][: w["in"]], 1, w["in"])
+            xq_b.append(ctx.array_to_buffer(a["xq"]))
+            xs_b.append(ctx.array_to_buffer(a["xs"]))
+            xsum_b.append(ctx.array_to_buffer(a["xsum"]))
+
+        def gemv_pass(_):
+            for r in range(R):
+                for i in range(len(weights)):
+                    ctx.qmatmul_prequant(bound[i][r], xq_b[i], xs_b[i], xsum_b[i], ybuf[i], 1)
+        g_gemv = capture(gemv_pass)
+        ms_gemv = time_graph(ctx, g_gemv, args.steps, args.warmup)
+        launches = R * len(weights) * args.steps
+        alg = sum(algorithmic_bytes(w["out"], w["in"], 1) for w in weights) / len(weights)
+        avg_launch_s = ms_gemv * 1e-3 / launches
+        achieved = alg / avg_launch_s / 1e9
+        roofline = {"bound": "hbm", "kernel": "gemv_a8_kernel<4,1,true>", "achieved": round(achieved, 1),
+                    "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s",
+                    "frac": round(achieved / hbm_peak, 4), "frac_of_nominal_8TBs": round(achieved / 8000.0, 4),
+                    "traffic": None, "avg_launch_us": round(avg_launch_s * 1e6, 3),
+                    "algorithmic_bytes_per_launch": alg}
+        g_gemv.destroy()
+
+        # ---- detail points: M in {1, 4, 8}, A8 / F, f32 / bf16 ----------------
+        detail = {}
+        from raster_b200 import synth
+        xb16 = [ctx.array_to_buffer(synth.to_bf16_bits(w["x"])) for w in weights]
+        for M in (1, 4, 8):
+            for tag, act, mode, xb in (("a8_f32", L.F32, L.MODE_A8, None),
+                                       ("f_f32", L.F32, L.MODE_F, None),
+                                       ("f_bf16", L.BF16, L.MODE_F, xb16)):
+                g = capture(op_pass(M, act, mode, xb))
+                msd = time_graph(ctx, g, max(3, args.steps // 2), 3) / max(3, args.steps // 2)
+                detail[f"M{M}_{tag}_GBs"] = round(per_pass * R / (msd * 1e-3) / 1e9, 1)
+                g.destroy()
+        # warm (single copy, L2-resident) figure, labelled as such
+        def warm_pass(_):
+            for _r in range(R):
+                for i in range(len(weights)):
+                    ctx.qmatmul(bound[i][0], xbuf[i], ybuf[i], 1)
+        g = capture(warm_pass)
+        msw = time_graph(ctx, g, max(3, args.steps // 2), 3) / max(3, args.steps // 2)
+        detail["M1_a8_f32_warm_L2_GBs"] = round(per_pass * R / (msw * 1e-3) / 1e9, 1)
+        g.destroy()
+
+        # ---- e2e: host arrays through the operator entry point ----------------
+        host_copies = []
+        for w in weights:
+            host_copies.append([(w["wqi"], w["wsi"])] +
+                               [(w["wqi"].copy(), w["wsi"].copy()) for _ in range(R - 1)])
+        from raster_b200.quant import op as qop
+        ys = [np.empty(w["out"], np.float32) for w in weights]
+
+        def e2e_pass():
+            for r in range(R):
+                for i, w in enumerate(weights):
+                    qop.qlinear_i8_into(w["x"][: w["in"]], host_copies[i][r][0], host_copies[i][r][1],
+                                        ys[i], w["in"], w["out"], ctx)
+        e2e_pass()                      # binds (uploads) every copy once
+        e2e_pass()
+        e2e_steps = max(3, args.steps // 2)
+        tt = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_pass()
+        e2e_s = (time.perf_counter() - tt) / e2e_steps
+        e2e = {"value": round(per_pass * R / e2e_s / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": int(R * sum(w["in"] * 4 for w in weights)),
+               "d2h_bytes_per_step": int(R * sum(w["out"] * 4 for w in weights)),
+               "ms_per_step": round(e2e_s * 1e3, 4), "calls_per_step": R * len(weights),
+               "api": "rstq_qlinear_i8 (host arrays, blocking)"}
+
+        cpu = cpu_baseline(weights) if world == 1 else None
+        result = {
+            "metric": "qmatmul weight-stream GB/s at M=1 (int4, per-32-block f32 scales)",
+            "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u4 x s8 -> s32, f32 fold",
+            "data": "synthetic",
+            "config": {"workload": "configs[1]: int4 GEMV, Llama-7B MLP shapes 4096->11008 and "
+                                   "11008->4096, M=1, f32 x, qlinear-i8 arithmetic",
+                       "launches_per_step": kernels_per_step, "weight_copies_rotated": R,
+                       "cache": "inputs larger than L2: %d MB of weights per step vs %d MB L2"
+                                % (per_pass * R >> 20, info["l2_bytes"] >> 20),
+                       "parallelism": "column-shard per GPU (tp%d)" % world,
+                       "frac_of_measured_hbm": round(value / world / hbm_peak, 4),
+                       "frac_of_nominal_8TBs": round(value / world / 8000.0, 4)},
+            "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu,
+            "gpu_launches": kernels_per_step * args.steps, "clocks": clocks, "detail": detail,
+        }
+    barrier()
+    if dist is not None:
+        dist.destroy_process_group()
+    ctx.close()
+    if rank == 0:
+        print(json.dumps(result))
+
+
+def cpu_baseline(weights, reps=60, warm=25, threads=None):
+    """Times the CPU port of the reference's production kernel (oracle/cpu_kernel.c) on the
+    host cores: 25 warm-up calls, median of 60 (bench/raster/quant_faithfulness.clj:77-101)."""
+    from oracle import oracle as orc
+    try:
+        orc.build(force=True, native_only=True)   # -march=native for THIS host
+    except Exception as e:  # keep the prebuilt library
+        print(f"[bench] cpu kernel rebuild failed, using prebuilt: {e}", file=sys.stderr)
+    threads = threads or (os.cpu_count() or 1)
+    k = orc.CpuKernel(threads)
+    tot_bytes, tot_s = 0, 0.0
+    per_shape = {}
+    for w in weights:
+        y = np.empty(w["out"], np.float32)
+        x = np.ascontiguousarray(w["x"][: w["in"]])
+        f = lambda: k.qlinear_i8(x, w["wqi"], w["wsi"], y, w["in"], w["out"], 4)
+        for _ in range(warm):
+            f()
+        ts = []
+        for _ in range(reps):
+            t = time.perf_counter()
+            f()
+            ts.append(time.perf_counter() - t)
+        med = statistics.median(ts)
+        per_shape[w["name"] + "_us"] = round(med * 1e6, 1)
+        tot_bytes += stream_bytes(w["out"], w["in"])
+        tot_s += med
+    isa = k.isa
+    k.close()
+    return {"value": round(tot_bytes / tot_s / 1e9, 2), "unit": "GB/s", "cores": threads,
+            "kind": "port", "isa": isa,
+            "sample": f"both shapes, M=1, median of {reps} calls after {warm} warm-ups each",
+            **per_shape}
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path on the host cores (its own code needs
+    a JVM and clang, absent here: the C port of its production kernel stands in)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    weights = make_weights(0)
+    per_pass = sum(stream_bytes(w["out"], w["in"]) for w in weights)
+    from oracle import oracle as orc
+    try:
+        orc.build(force=True, native_only=True)
+    except Exception:
+        pass
+    threads = os.cpu_count() or 1
+    k = orc.CpuKernel(threads)
+    ys = [np.empty(w["out"], np.float32) for w in weights]
+    xs = [np.ascontiguousarray(w["x"][: w["in"]]) for w in weights]
+    calls = 8   # one step = 8 passes over both shapes (bounded sample of the rotation)
+
+    def step():
+        for _ in range(calls):
+            for i, w in enumerate(weights):
+                k.qlinear_i8(xs[i], w["wqi"], w["wsi"], ys[i], w["in"], w["out"], 4)
+    for _ in range(args.warmup):
+        step()
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    s = (time.perf_counter() - t) / args.steps
+    val = round(per_pass * calls / s / 1e9, 2)
+    base = {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "isa": k.isa,
+            "sample": f"{calls} passes over both shapes per step"}
+    k.close()
+    print(json.dumps({
+        "impl": "reference",
+        "metric": "qmatmul weight-stream GB/s at M=1 (int4, per-32-block f32 scales)",
+        "value": val, "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(s * 1e3, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u4 x s8 -> s32, f32 fold", "data": "synthetic",
+        "config": {"workload": "configs[1]: int4 GEMV, Llama-7B MLP shapes 4096->11008 and "
+                               "11008->4096, M=1, f32 x, qlinear-i8 arithmetic",
+                   "note": "CPU port of the reference's production kernel; the reference's own "
+                           "JVM path is unavailable on this box (no JVM, no clang)"},
+        "cpu_baseline": base,
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,202 @@
+/*
+ * rstq -- Blackwell (sm_100a) quantized matmul for Raster: C ABI.
+ *
+ * This is the boundary Raster's Clojure host code binds through Panama FFM
+ * (java.lang.foreign), the way it already binds its generated CPU kernels
+ * (src/raster/compiler/backend/cpu/codegen.clj:100-125) and its OpenCL driver
+ * (src/raster/gpu/ocl_runtime.clj:59-76, :192-199).  Conventions kept from
+ * there:
+ *   - pointers first, then scalars, in every signature;
+ *   - only int32_t / int64_t / float / double / pointers cross the boundary;
+ *   - every function returns an int32_t status (0 = ok, < 0 = error code) and
+ *     hands results back through out-pointers; rstq_last_error() returns the
+ *     text of the calling thread's most recent failure;
+ *   - no C++ exception and no abort() crosses this boundary;
+ *   - every create has a destroy; destroying NULL is a no-op returning 0.
+ *
+ * Shapes use the reference's names: `in` = K (reduction length), `out` = N
+ * (rows of W; W is row-major [out, in]); a block is 32 consecutive K elements
+ * of one row; nb = in / 32.  Activations are row-major [M, in], results
+ * row-major [M, out].
+ *
+ * Threading: a context is thread-compatible -- calls on one context must be
+ * serialised by the caller.  Work on one device of a context runs in order on
+ * that device's stream and is asynchronous to the host unless stated.
+ */
+#ifndef RSTQ_H
+#define RSTQ_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RSTQ_API __attribute__((visibility("default")))
+
+typedef struct rstq_ctx rstq_ctx;
+typedef struct rstq_buf rstq_buf;
+typedef struct rstq_weight rstq_weight;
+typedef struct rstq_graph rstq_graph;
+typedef struct rstq_event rstq_event;
+
+/* status codes */
+#define RSTQ_OK 0
+#define RSTQ_E_INVALID (-1)  /* null pointer, bad enum, bad handle            */
+#define RSTQ_E_SHAPE (-2)    /* in % 32 != 0, out % 8 != 0 (stream layout), M < 1, size overflow */
+#define RSTQ_E_ALIGN (-3)    /* device pointer / offset not 16-byte aligned   */
+#define RSTQ_E_CUDA (-4)     /* a CUDA runtime call failed                    */
+#define RSTQ_E_OOM (-5)      /* device or pinned-host allocation failed       */
+#define RSTQ_E_NODEV (-6)    /* no CUDA device, or device index out of range  */
+#define RSTQ_E_ARCH (-7)     /* device is not compute capability 10.x         */
+#define RSTQ_E_DEVICE (-8)   /* handles live on different devices             */
+#define RSTQ_E_STATE (-9)    /* call not legal now (e.g. sync during capture) */
+#define RSTQ_E_LIMIT (-10)   /* problem exceeds a stated fixed limit          */
+#define RSTQ_E_RANGE (-11)   /* offset + bytes beyond the buffer              */
+
+/* weight formats (the `format` argument of rstq_weight_bind) */
+#define RSTQ_FMT_Q4_0 0 /* unsigned nibble, zero point 8, two per byte (lo = elem k, hi = elem k+16);
+                           src/raster/compiler/backend/cpu/quant.clj:27-31 */
+#define RSTQ_FMT_Q8_0 1 /* unsigned byte, zero point 128; src/raster/compiler/backend/cpu/quant.clj:33-39 */
+#define RSTQ_FMT_Q8_S 2 /* signed int8 codes, W = scale * code; src/raster/quant/train.clj:34-71,
+                           and, read as bytes, the int32-packed rows of src/raster/quant/pack.clj:55-81 */
+
+/* host layouts accepted at bind time */
+#define RSTQ_LAYOUT_ROWMAJOR 0 /* codes row-major by output row, scales [out, nb] */
+#define RSTQ_LAYOUT_STREAM8 1  /* 8-row interleaved stream layout (wqi / wsi);
+                                  src/raster/compiler/core/layout.clj:246-286; needs out % 8 == 0 */
+
+/* element types of activations / results */
+#define RSTQ_F32 0
+#define RSTQ_BF16 1 /* raw bits in uint16_t, as the reference carries f16 in short[] */
+
+/* arithmetic modes */
+#define RSTQ_MODE_F 0  /* y = dequant(W) . x on the float activations (f32 accumulate) */
+#define RSTQ_MODE_A8 1 /* activations quantized per 32-block to int8 inside the op, integer block
+                          dots, per-block scale fold: the arithmetic of qlinear-i8 */
+
+/* shard kinds (rstq_weight_bind_shard) */
+#define RSTQ_SPLIT_NONE 0
+#define RSTQ_SPLIT_COLUMN 1 /* rank owns output rows [rank*out/P, (rank+1)*out/P) */
+#define RSTQ_SPLIT_ROW 2    /* rank owns K range   [rank*in/P,  (rank+1)*in/P) of every row */
+
+/* tuning keys (rstq_tune) */
+#define RSTQ_TUNE_SPLITK 0      /* 0 = automatic, n > 0 = force n K-slices in the decode kernels */
+#define RSTQ_TUNE_GEMM_MIN_M 1  /* smallest M routed to the tensor-core GEMM (default 17) */
+
+/* ---- library / errors -------------------------------------------------- */
+RSTQ_API int32_t rstq_version(void);
+RSTQ_API const char* rstq_last_error(void);
+RSTQ_API int32_t rstq_device_count(int32_t* count);
+
+/* ---- context: replaces the session / runtime init of
+ *      src/raster/gpu/core.clj:243-293 and src/raster/gpu/ocl_runtime.clj:205-215.
+ * `devices` lists CUDA ordinals; later calls name a device by its index in
+ * that list (device index 0 = devices[0]). ------------------------------- */
+RSTQ_API int32_t rstq_init(const int32_t* devices, int32_t ndev, rstq_ctx** ctx);
+RSTQ_API int32_t rstq_shutdown(rstq_ctx* ctx);
+RSTQ_API int32_t rstq_sync(rstq_ctx* ctx, int32_t dev);
+RSTQ_API int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value);
+/* out[0] = SM count, out[1] = L2 bytes, out[2] = total device memory, out[3] = cc major*10+minor */
+RSTQ_API int32_t rstq_device_info(rstq_ctx* ctx, int32_t dev, int64_t* out4);
+
+/* ---- device buffers: make-buffer / array->buffer! / buffer->array /
+ *      free-buffer! of src/raster/gpu/ocl_runtime.clj:405-499. ----------- */
+RSTQ_API int32_t rstq_alloc(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, int64_t bytes);
+RSTQ_API int32_t rstq_free(rstq_buf* buf);
+RSTQ_API int32_t rstq_upload(rstq_buf* buf, const void* host, int64_t offset, int64_t bytes);
+RSTQ_API int32_t rstq_download(rstq_buf* buf, void* host, int64_t offset, int64_t bytes);
+RSTQ_API int32_t rstq_memset(rstq_buf* buf, int32_t byte_value, int64_t offset, int64_t bytes);
+RSTQ_API int32_t rstq_buf_ptr(rstq_buf* buf, void** device_ptr, int64_t* bytes);
+
+/* ---- weights: the one-time host->device bind.  Replaces repack-stream
+ *      (src/raster/compiler/backend/cpu/quant.clj:317-326) as the load-time
+ *      layout transform: the host arrays keep the reference's layouts, the
+ *      device copy is re-tiled for the sm_100a kernels. ------------------- */
+RSTQ_API int32_t rstq_weight_bind(rstq_ctx* ctx, rstq_weight** w, const void* codes,
+                                  const float* scales, int32_t dev, int64_t out, int64_t in,
+                                  int32_t format, int32_t layout);
+/* Bind rank `rank` of `nranks`'s shard of a full host matrix (column or row split). */
+RSTQ_API int32_t rstq_weight_bind_shard(rstq_ctx* ctx, rstq_weight** w, const void* codes,
+                                        const float* scales, int32_t dev, int64_t out, int64_t in,
+                                        int32_t format, int32_t layout, int32_t split,
+                                        int32_t rank, int32_t nranks);
+/* Second device copy of a bound weight at a distinct address (cold-cache measurement). */
+RSTQ_API int32_t rstq_weight_clone(rstq_weight* src, rstq_weight** w);
+RSTQ_API int32_t rstq_weight_free(rstq_weight* w);
+/* out[0]=out rows, out[1]=in, out[2]=bits, out[3]=device bytes (codes+scales as stored),
+ * out[4]=algorithmic stream bytes out*in*bits/8 + out*nb*4, out[5]=device index */
+RSTQ_API int32_t rstq_weight_info(rstq_weight* w, int64_t* out6);
+
+/* ---- activation quantizer on the device: quantize-act-i8 of
+ *      src/raster/compiler/backend/cpu/quant.clj:282-305 (xsum != NULL) and
+ *      quant-act-i8-rows-gpu! of src/raster/quant/kernels_k.clj:309-342
+ *      (xsum == NULL; xq read as int32 words is its `xp`).
+ *      x: f32 [M, in]; xq: int8 [M, in]; xs: f32 [M, nb]; xsum: int32 [M, nb].
+ *      Bit-exact with the reference (double-precision scale and rounding). */
+RSTQ_API int32_t rstq_quant_act_i8(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rstq_buf* xs,
+                                   rstq_buf* xsum, int64_t M, int64_t in);
+
+/* ---- the matmul on device-resident data.
+ * rstq_qmatmul: y[M, out] = W . x[M, in]; x is act_dtype, y is out_dtype.
+ *   MODE_A8 quantizes x inside the call (needs act_dtype F32) -- the arithmetic of
+ *   qlinear-i8! / qlinear-i8-q8! (src/raster/quant/op.clj:43-51, :81-90) for any M.
+ *   MODE_F multiplies the float activations directly -- qlinear-q8
+ *   (src/raster/quant/train.clj:77-108) and the prefill GEMM.
+ * rstq_qmatmul_prequant: the kernel-level call of the reference,
+ *   (xq xs xsum wqi wsi y in out ...) of qmatmul-q4-x8! / qmatmul-q8-x8!
+ *   (src/raster/quant/kernels.clj:216-247, :308-333), and with xsum == NULL and a
+ *   Q8_S weight the signed x signed qmatmul-i8-gemm!
+ *   (src/raster/quant/kernels_k.clj:344-370). y is f32. */
+RSTQ_API int32_t rstq_qmatmul(rstq_ctx* ctx, rstq_weight* w, rstq_buf* x, rstq_buf* y, int64_t M,
+                              int32_t act_dtype, int32_t out_dtype, int32_t mode);
+RSTQ_API int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_buf* xs,
+                                       rstq_buf* xsum, rstq_buf* y, int64_t M);
+
+/* ---- the operators on HOST arrays, same argument order as the reference's
+ *      CPU operators, so the Clojure method bodies change one call.  x and y
+ *      cross PCIe on every call; the weight is uploaded and re-tiled on first
+ *      sight of its (codes pointer, scales pointer, in, out) and kept resident
+ *      (weights are immutable after load); rstq_weight_cache_clear drops it.
+ *      These calls block until y is on the host.
+ *   rstq_qlinear_i8      qlinear-i8!       src/raster/quant/op.clj:43-51   (Q4_0 wqi/wsi)
+ *   rstq_qlinear_i8_q8   qlinear-i8-q8!    src/raster/quant/op.clj:81-90   (Q8_0 wqi/wsi)
+ *   rstq_qlinear_q8      qlinear-q8        src/raster/quant/train.clj:77-108
+ *   rstq_qmatmul_i8_gemm qmatmul-i8-gemm!  src/raster/quant/kernels_k.clj:344-370
+ *   rstq_i8gemv_dp4a     i8gemv-dp4a!      src/raster/quant/kernels_k.clj:141-150 */
+RSTQ_API int32_t rstq_qlinear_i8(rstq_ctx* ctx, const float* x, const void* wqi, const float* wsi,
+                                 float* y, int64_t in, int64_t out);
+RSTQ_API int32_t rstq_qlinear_i8_q8(rstq_ctx* ctx, const float* x, const void* wqi,
+                                    const float* wsi, float* y, int64_t in, int64_t out);
+RSTQ_API int32_t rstq_qlinear_q8(rstq_ctx* ctx, const float* x, const void* codes,
+                                 const float* scales, float* y, int64_t m, int64_t in,
+                                 int64_t out);
+RSTQ_API int32_t rstq_qmatmul_i8_gemm(rstq_ctx* ctx, const int32_t* xp, const float* xs,
+                                      const int32_t* wp, const float* ws, float* y, int64_t in,
+                                      int64_t out, int64_t nrows);
+RSTQ_API int32_t rstq_i8gemv_dp4a(rstq_ctx* ctx, const int32_t* wp, const int32_t* xp, float* y,
+                                  int64_t kw, int64_t out);
+/* Host x / y against an already bound weight (the resident path for callers whose
+ * arrays move, e.g. JVM heap arrays): x is act_dtype [M, in], y is f32 [M, out]. */
+RSTQ_API int32_t rstq_qmatmul_host(rstq_ctx* ctx, rstq_weight* w, const void* x, float* y,
+                                   int64_t M, int32_t act_dtype, int32_t mode);
+RSTQ_API int32_t rstq_weight_cache_clear(rstq_ctx* ctx);
+
+/* ---- graphs and events: record-graph! / replay-graph! / destroy-graph! of
+ *      src/raster/gpu/ocl_runtime.clj:1051-1084 and the per-kernel device
+ *      timestamps of src/raster/gpu/core.clj:1343-1388. -------------------- */
+RSTQ_API int32_t rstq_graph_begin(rstq_ctx* ctx, int32_t dev);
+RSTQ_API int32_t rstq_graph_end(rstq_ctx* ctx, rstq_graph** graph, int32_t dev);
+RSTQ_API int32_t rstq_graph_replay(rstq_graph* graph);
+RSTQ_API int32_t rstq_graph_destroy(rstq_graph* graph);
+RSTQ_API int32_t rstq_event_create(rstq_ctx* ctx, rstq_event** ev, int32_t dev);
+RSTQ_API int32_t rstq_event_record(rstq_event* ev);
+RSTQ_API int32_t rstq_event_elapsed_ms(rstq_event* start, rstq_event* stop, float* ms);
+RSTQ_API int32_t rstq_event_destroy(rstq_event* ev);
+/* Number of kernels this library has launched on the context since init. */
+RSTQ_API int32_t rstq_launch_count(rstq_ctx* ctx, int64_t* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RSTQ_H */

@@ -1,0 +1,65 @@
+// Per-32-block int8 activation quantizer on the device.
+//
+// Arithmetic of quantize-act-blocks! / quantize-act-i8
+// (src/raster/compiler/backend/cpu/quant.clj:282-305) and, without the block
+// sums, of quant-act-i8-rows-gpu! (src/raster/quant/kernels_k.clj:309-342):
+//   mx = max|x| over the block, d = mx / 127 (double), id = d == 0 ? 0 : 1 / d,
+//   q = clamp(round_half_up((double)x * id), -127, 127), xs = (float)d, xsum = sum q.
+// The scale and the rounding are carried in double so the codes are bit-exact
+// with the JVM's (Java Math.round = nearest, ties toward +infinity).
+#include "internal.h"
+
+namespace rstq {
+
+__device__ __forceinline__ int round_half_up(double v) {
+    double f = floor(v);
+    return (int)f + ((v - f) >= 0.5 ? 1 : 0);
+}
+
+// One warp per block; lane k owns element k.  Bytes are gathered so that each
+// of eight lanes stores one 32-bit word.
+__global__ void __launch_bounds__(256)
+quant_act_i8_kernel(const float* __restrict__ x, int8_t* __restrict__ xq, float* __restrict__ xs,
+                    int32_t* __restrict__ xsum, int64_t nblocks) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t blk = warp; blk < nblocks; blk += nwarps) {
+        const float v = x[blk * 32 + lane];
+        float mx = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const double d = (double)mx / 127.0;
+        const double id = d == 0.0 ? 0.0 : 1.0 / d;
+        int q = round_half_up((double)v * id);
+        q = max(-127, min(127, q));
+        int s = q;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        // pack four neighbouring codes into the word lane (lane & ~3) stores
+        uint32_t b = (uint32_t)(q & 0xFF);
+        uint32_t w = b << (8 * (lane & 3));
+        w |= __shfl_xor_sync(0xffffffffu, w, 1);
+        w |= __shfl_xor_sync(0xffffffffu, w, 2);
+        if ((lane & 3) == 0) reinterpret_cast<uint32_t*>(xq)[blk * 8 + (lane >> 2)] = w;
+        if (lane == 0) {
+            xs[blk] = (float)d;
+            if (xsum) xsum[blk] = s;
+        }
+    }
+}
+
+int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs,
+                            int32_t* xsum, int64_t M, int64_t in) {
+    const int64_t nblocks = M * (in / 32);
+    int64_t ctas = (nblocks + 7) / 8;  // 8 warps per CTA
+    const int64_t cap = (int64_t)ds.sm_count * 8;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    quant_act_i8_kernel<<<(int)ctas, 256, 0, ds.stream>>>(x, xq, xs, xsum, nblocks);
+    ctx->launches++;
+    RSTQ_CUDA(cudaGetLastError());
+    return RSTQ_OK;
+}
+
+}  // namespace rstq

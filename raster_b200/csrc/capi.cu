@@ -1,0 +1,940 @@
+// C ABI of librstq: contexts, buffers, weight binding, operator dispatch,
+// graphs and events.  See include/rstq.h for the contract of each entry point.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "internal.h"
+
+namespace rstq {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int32_t cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
+    const char* base = strrchr(file, '/');
+    set_error("CUDA error %d (%s) at %s:%d in %s", (int)e, cudaGetErrorString(e),
+              base ? base + 1 : file, line, what);
+    return e == cudaErrorMemoryAllocation ? RSTQ_E_OOM : RSTQ_E_CUDA;
+}
+
+static bool ok_ctx(const rstq_ctx* c) { return c && c->magic == kCtxMagic; }
+static bool ok_buf(const rstq_buf* b) { return b && b->magic == kBufMagic && ok_ctx(b->ctx); }
+static bool ok_w(const rstq_weight* w) { return w && w->magic == kWgtMagic && ok_ctx(w->ctx); }
+
+#define CHECK_CTX(c) RSTQ_REQUIRE(ok_ctx(c), RSTQ_E_INVALID, "invalid context handle")
+#define CHECK_DEV(c, d)                                                              \
+    RSTQ_REQUIRE((d) >= 0 && (d) < (int)(c)->devs.size(), RSTQ_E_NODEV,              \
+                 "device index %d out of range (context has %d)", (int)(d), (int)(c)->devs.size())
+
+static int32_t use_dev(rstq_ctx* ctx, int dev) {
+    RSTQ_CUDA(cudaSetDevice(ctx->devs[dev].ordinal));
+    return RSTQ_OK;
+}
+
+// grow-only scratch helpers (never called while capturing)
+static int32_t ensure_dev(DeviceState& ds, void** p, int64_t* have, int64_t need) {
+    if (need <= *have) return RSTQ_OK;
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE,
+                 "scratch must grow (%lld bytes) during graph capture; run the call once before "
+                 "capturing", (long long)need);
+    if (*p) {
+        RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+        RSTQ_CUDA(cudaFree(*p));
+        *p = nullptr;
+        *have = 0;
+    }
+    need = (need + 0xFFFFF) & ~0xFFFFFll;
+    RSTQ_CUDA(cudaMalloc(p, (size_t)need));
+    *have = need;
+    return RSTQ_OK;
+}
+
+static int32_t ensure_pinned(DeviceState& ds, int64_t need) {
+    if (need <= ds.pinned_bytes) return RSTQ_OK;
+    if (ds.pinned) {
+        RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+        RSTQ_CUDA(cudaFreeHost(ds.pinned));
+        ds.pinned = nullptr;
+        ds.pinned_bytes = 0;
+    }
+    need = (need + 0xFFFF) & ~0xFFFFll;
+    RSTQ_CUDA(cudaMallocHost(&ds.pinned, (size_t)need));
+    ds.pinned_bytes = need;
+    return RSTQ_OK;
+}
+
+__global__ void block_sum_kernel(const int8_t* __restrict__ xq, int32_t* __restrict__ xsum,
+                                 int64_t nblocks) {
+    const int64_t b = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (b >= nblocks) return;
+    const int4* p = reinterpret_cast<const int4*>(xq + b * 32);
+    int s = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int4 v = p[h];
+        s = __dp4a(v.x, 0x01010101, s);
+        s = __dp4a(v.y, 0x01010101, s);
+        s = __dp4a(v.z, 0x01010101, s);
+        s = __dp4a(v.w, 0x01010101, s);
+    }
+    xsum[b] = s;
+}
+
+// y[o] = (float) sum_w dp4a(wp[o*kw + w], xp[w]) : exact int32 dot, one warp per row.
+__global__ void i8gemv_dp4a_kernel(const int32_t* __restrict__ wp, const int32_t* __restrict__ xp,
+                                   float* __restrict__ y, int64_t kw, int64_t out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t o = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    if (o >= out) return;
+    int acc = 0;
+    for (int64_t k = lane; k < kw; k += 32) acc = __dp4a(wp[o * kw + k], xp[k], acc);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) y[o] = (float)acc;
+}
+
+// Activation scratch layout for MODE_A8: [xq: M*in int8][xs: M*nb f32][xsum: M*nb i32]
+struct ActScratch {
+    int8_t* xq;
+    float* xs;
+    int32_t* xsum;
+};
+static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* out) {
+    const int64_t nb = in / 32;
+    const int64_t xq_bytes = (M * in + 255) & ~255ll;
+    const int64_t sb = (M * nb * 4 + 255) & ~255ll;
+    int32_t rc = ensure_dev(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 2 * sb);
+    if (rc != RSTQ_OK) return rc;
+    char* base = (char*)ds.act_scratch;
+    out->xq = (int8_t*)base;
+    out->xs = (float*)(base + xq_bytes);
+    out->xsum = (int32_t*)(base + xq_bytes + sb);
+    return RSTQ_OK;
+}
+
+// One matmul over device pointers, M split into decode-kernel chunks.
+static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs,
+                      const int32_t* xsum, float* y, int64_t M) {
+    DeviceState& ds = ctx->devs[w->dev];
+    for (int64_t m0 = 0; m0 < M; m0 += kGemvMaxM) {
+        const int64_t mc = M - m0 < kGemvMaxM ? M - m0 : kGemvMaxM;
+        GemvA8Args a{w->data, xq + m0 * w->in, xs + m0 * w->nb, xsum + m0 * w->nb,
+                     y + m0 * w->out, mc, w->in, w->out, w->bits, w->zp};
+        int32_t rc = launch_gemv_a8(ctx, ds, a);
+        if (rc != RSTQ_OK) return rc;
+    }
+    return RSTQ_OK;
+}
+
+static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
+                     int act_dtype, int out_dtype) {
+    DeviceState& ds = ctx->devs[w->dev];
+    const int64_t xe = act_dtype == RSTQ_F32 ? 4 : 2, ye = out_dtype == RSTQ_F32 ? 4 : 2;
+    for (int64_t m0 = 0; m0 < M; m0 += kGemvMaxM) {
+        const int64_t mc = M - m0 < kGemvMaxM ? M - m0 : kGemvMaxM;
+        GemvFArgs a{w->data, (const char*)x + m0 * w->in * xe, (char*)y + m0 * w->out * ye,
+                    mc, w->in, w->out, w->bits, w->zp, act_dtype, out_dtype};
+        int32_t rc = launch_gemv_f(ctx, ds, a);
+        if (rc != RSTQ_OK) return rc;
+    }
+    return RSTQ_OK;
+}
+
+static int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
+                             int act_dtype, int out_dtype, int mode) {
+    DeviceState& ds = ctx->devs[w->dev];
+    if (mode == RSTQ_MODE_A8) {
+        RSTQ_REQUIRE(act_dtype == RSTQ_F32 && out_dtype == RSTQ_F32, RSTQ_E_INVALID,
+                     "MODE_A8 takes f32 activations and writes f32");
+        ActScratch s;
+        int32_t rc = act_scratch(ds, M, w->in, &s);
+        if (rc != RSTQ_OK) return rc;
+        rc = launch_quant_act_i8(ctx, ds, (const float*)x, s.xq, s.xs, s.xsum, M, w->in);
+        if (rc != RSTQ_OK) return rc;
+        return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M);
+    }
+    return run_f(ctx, w, x, y, M, act_dtype, out_dtype);
+}
+
+static int32_t bind_impl(rstq_ctx* ctx, rstq_weight** wout, const void* codes,
+                         const float* scales, int dev, int64_t out, int64_t in, int format,
+                         int layout, int split, int rank, int nranks) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(wout && codes && scales, RSTQ_E_INVALID, "null argument");
+    *wout = nullptr;
+    CHECK_DEV(ctx, dev);
+    RSTQ_REQUIRE(format >= RSTQ_FMT_Q4_0 && format <= RSTQ_FMT_Q8_S, RSTQ_E_INVALID,
+                 "unknown weight format %d", format);
+    RSTQ_REQUIRE(layout == RSTQ_LAYOUT_ROWMAJOR || layout == RSTQ_LAYOUT_STREAM8, RSTQ_E_INVALID,
+                 "unknown host layout %d", layout);
+    RSTQ_REQUIRE(out >= 1 && in >= 32 && in % 32 == 0, RSTQ_E_SHAPE,
+                 "in = %lld must be a positive multiple of 32 and out = %lld >= 1", (long long)in,
+                 (long long)out);
+    RSTQ_REQUIRE(layout != RSTQ_LAYOUT_STREAM8 || out % 8 == 0, RSTQ_E_SHAPE,
+                 "stream layout needs out %% 8 == 0 (out = %lld)", (long long)out);
+    RSTQ_REQUIRE(layout != RSTQ_LAYOUT_STREAM8 || format != RSTQ_FMT_Q8_S, RSTQ_E_INVALID,
+                 "signed codes have no stream layout in the reference");
+    RSTQ_REQUIRE(split >= RSTQ_SPLIT_NONE && split <= RSTQ_SPLIT_ROW, RSTQ_E_INVALID,
+                 "unknown split %d", split);
+    if (split == RSTQ_SPLIT_NONE) { rank = 0; nranks = 1; }
+    RSTQ_REQUIRE(nranks >= 1 && rank >= 0 && rank < nranks, RSTQ_E_INVALID,
+                 "rank %d of %d", rank, nranks);
+    const int bits = format == RSTQ_FMT_Q4_0 ? 4 : 8;
+    const int64_t nb_full = in / 32;
+    int64_t sh_out = out, sh_in = in, row0 = 0, kb0 = 0;
+    if (split == RSTQ_SPLIT_COLUMN) {
+        const int64_t q = layout == RSTQ_LAYOUT_STREAM8 ? 8 : 1;
+        RSTQ_REQUIRE(out % (nranks * q) == 0, RSTQ_E_SHAPE,
+                     "column split: out = %lld not divisible by %lld", (long long)out,
+                     (long long)(nranks * q));
+        sh_out = out / nranks;
+        row0 = rank * sh_out;
+    } else if (split == RSTQ_SPLIT_ROW) {
+        RSTQ_REQUIRE(nb_full % nranks == 0, RSTQ_E_SHAPE,
+                     "row split: in/32 = %lld not divisible by %d", (long long)nb_full, nranks);
+        sh_in = in / nranks;
+        kb0 = rank * (sh_in / 32);
+    }
+    DeviceState& ds = ctx->devs[dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "cannot bind a weight during graph capture");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+
+    // Host slab holding the rows of this shard (all K; a row split selects its
+    // K range inside the re-tiling kernel).
+    const int64_t code_row_bytes = (int64_t)in * bits / 8;
+    const uint8_t* hcodes = (const uint8_t*)codes + row0 * code_row_bytes;
+    const float* hscales = scales + row0 * nb_full;
+    const int64_t codes_bytes = sh_out * code_row_bytes;
+    const int64_t scales_bytes = sh_out * nb_full * 4;
+
+    rstq_weight* w = new (std::nothrow) rstq_weight();
+    RSTQ_REQUIRE(w, RSTQ_E_OOM, "out of host memory");
+    w->magic = kWgtMagic;
+    w->ctx = ctx;
+    w->dev = dev;
+    w->bits = bits;
+    w->zp = bits == 4 ? 8 : 128;
+    w->out = sh_out;
+    w->in = sh_in;
+    w->outp = (sh_out + 31) / 32 * 32;
+    w->nb = sh_in / 32;
+    w->data_bytes = (w->outp / 32) * w->nb * unit_bytes(bits);
+    w->data = nullptr;
+    uint8_t *stage_c = nullptr;
+    float* stage_s = nullptr;
+    cudaError_t e = cudaMalloc((void**)&w->data, (size_t)w->data_bytes);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&stage_c, (size_t)codes_bytes);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&stage_s, (size_t)scales_bytes);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(stage_c, hcodes, (size_t)codes_bytes, cudaMemcpyHostToDevice, ds.stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(stage_s, hscales, (size_t)scales_bytes, cudaMemcpyHostToDevice, ds.stream);
+    if (e == cudaSuccess) {
+        rc = launch_repack(ctx, ds, stage_c, stage_s, w->data, format, layout, sh_out, sh_in, in, kb0);
+        if (rc == RSTQ_OK) e = cudaStreamSynchronize(ds.stream);
+    }
+    if (stage_c) cudaFree(stage_c);
+    if (stage_s) cudaFree(stage_s);
+    if (e != cudaSuccess || rc != RSTQ_OK) {
+        if (w->data) cudaFree(w->data);
+        delete w;
+        if (e != cudaSuccess) return cuda_fail(e, "weight bind", __FILE__, __LINE__);
+        return rc;
+    }
+    *wout = w;
+    return RSTQ_OK;
+}
+
+}  // namespace rstq
+
+using namespace rstq;
+
+extern "C" {
+
+int32_t rstq_version(void) { return 100; }
+
+const char* rstq_last_error(void) { return g_err; }
+
+int32_t rstq_device_count(int32_t* count) {
+    RSTQ_REQUIRE(count, RSTQ_E_INVALID, "null argument");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        *count = 0;
+        cudaGetLastError();
+        set_error("no CUDA device: %s", cudaGetErrorString(e));
+        return RSTQ_E_NODEV;
+    }
+    *count = n;
+    return RSTQ_OK;
+}
+
+int32_t rstq_init(const int32_t* devices, int32_t ndev, rstq_ctx** ctxp) {
+    RSTQ_REQUIRE(ctxp, RSTQ_E_INVALID, "null argument");
+    *ctxp = nullptr;
+    RSTQ_REQUIRE(devices && ndev >= 1 && ndev <= 64, RSTQ_E_INVALID, "need 1..64 devices");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        set_error("no CUDA device visible (%s); this library has no CPU path",
+                  e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+        return RSTQ_E_NODEV;
+    }
+    rstq_ctx* ctx = new (std::nothrow) rstq_ctx();
+    RSTQ_REQUIRE(ctx, RSTQ_E_OOM, "out of host memory");
+    ctx->magic = kCtxMagic;
+    ctx->devs.resize(ndev);
+    int32_t rc = RSTQ_OK;
+    for (int i = 0; i < ndev && rc == RSTQ_OK; ++i) {
+        DeviceState& ds = ctx->devs[i];
+        if (devices[i] < 0 || devices[i] >= n) {
+            set_error("CUDA ordinal %d not present (%d devices)", devices[i], n);
+            rc = RSTQ_E_NODEV;
+            break;
+        }
+        ds.ordinal = devices[i];
+        auto step = [&]() -> int32_t {
+            cudaDeviceProp prop;
+            RSTQ_CUDA(cudaSetDevice(ds.ordinal));
+            RSTQ_CUDA(cudaGetDeviceProperties(&prop, ds.ordinal));
+            ds.cc = prop.major * 10 + prop.minor;
+            RSTQ_REQUIRE(prop.major == 10, RSTQ_E_ARCH,
+                         "device %d is sm_%d%d; this library holds sm_100a code only", ds.ordinal,
+                         prop.major, prop.minor);
+            ds.sm_count = prop.multiProcessorCount;
+            ds.l2_bytes = prop.l2CacheSize;
+            ds.total_mem = (int64_t)prop.totalGlobalMem;
+            RSTQ_CUDA(cudaStreamCreateWithFlags(&ds.stream, cudaStreamNonBlocking));
+            ds.partials_bytes = 32ll << 20;
+            RSTQ_CUDA(cudaMalloc((void**)&ds.partials, (size_t)ds.partials_bytes));
+            ds.counters_len = 1 << 18;
+            RSTQ_CUDA(cudaMalloc((void**)&ds.counters, (size_t)ds.counters_len * 4));
+            RSTQ_CUDA(cudaMemsetAsync(ds.counters, 0, (size_t)ds.counters_len * 4, ds.stream));
+            int32_t r = gemv_configure(ds);
+            if (r != RSTQ_OK) return r;
+            RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+            return RSTQ_OK;
+        };
+        rc = step();
+    }
+    if (rc != RSTQ_OK) {
+        char keep[512];
+        strncpy(keep, g_err, sizeof(keep));
+        keep[sizeof(keep) - 1] = 0;
+        rstq_shutdown(ctx);
+        set_error("%s", keep);
+        return rc;
+    }
+    *ctxp = ctx;
+    return RSTQ_OK;
+}
+
+int32_t rstq_shutdown(rstq_ctx* ctx) {
+    if (!ctx) return RSTQ_OK;
+    CHECK_CTX(ctx);
+    for (auto& kv : ctx->wcache) {
+        rstq_weight* w = kv.second;
+        if (w) {
+            cudaSetDevice(ctx->devs[w->dev].ordinal);
+            cudaFree(w->data);
+            w->magic = 0;
+            delete w;
+        }
+    }
+    ctx->wcache.clear();
+    for (auto& ds : ctx->devs) {
+        if (ds.ordinal < 0) continue;
+        cudaSetDevice(ds.ordinal);
+        if (ds.stream) cudaStreamSynchronize(ds.stream);
+        if (ds.act_scratch) cudaFree(ds.act_scratch);
+        if (ds.partials) cudaFree(ds.partials);
+        if (ds.counters) cudaFree(ds.counters);
+        if (ds.io_dev) cudaFree(ds.io_dev);
+        if (ds.pinned) cudaFreeHost(ds.pinned);
+        if (ds.stream) cudaStreamDestroy(ds.stream);
+    }
+    cudaGetLastError();
+    ctx->magic = 0;
+    delete ctx;
+    return RSTQ_OK;
+}
+
+int32_t rstq_sync(rstq_ctx* ctx, int32_t dev) {
+    CHECK_CTX(ctx);
+    CHECK_DEV(ctx, dev);
+    RSTQ_REQUIRE(!ctx->devs[dev].capturing, RSTQ_E_STATE, "cannot synchronise during capture");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaStreamSynchronize(ctx->devs[dev].stream));
+    return RSTQ_OK;
+}
+
+int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
+    CHECK_CTX(ctx);
+    switch (key) {
+        case RSTQ_TUNE_SPLITK:
+            RSTQ_REQUIRE(value >= 0 && value <= 4096, RSTQ_E_INVALID, "split-K out of range");
+            ctx->tune_splitk = value;
+            return RSTQ_OK;
+        case RSTQ_TUNE_GEMM_MIN_M:
+            RSTQ_REQUIRE(value >= 1, RSTQ_E_INVALID, "threshold must be >= 1");
+            ctx->tune_gemm_min_m = value;
+            return RSTQ_OK;
+        default:
+            set_error("unknown tuning key %d", key);
+            return RSTQ_E_INVALID;
+    }
+}
+
+int32_t rstq_device_info(rstq_ctx* ctx, int32_t dev, int64_t* out4) {
+    CHECK_CTX(ctx);
+    CHECK_DEV(ctx, dev);
+    RSTQ_REQUIRE(out4, RSTQ_E_INVALID, "null argument");
+    const DeviceState& ds = ctx->devs[dev];
+    out4[0] = ds.sm_count;
+    out4[1] = ds.l2_bytes;
+    out4[2] = ds.total_mem;
+    out4[3] = ds.cc;
+    return RSTQ_OK;
+}
+
+// ---- buffers ---------------------------------------------------------------
+int32_t rstq_alloc(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, int64_t bytes) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(buf, RSTQ_E_INVALID, "null argument");
+    *buf = nullptr;
+    CHECK_DEV(ctx, dev);
+    RSTQ_REQUIRE(bytes >= 1, RSTQ_E_SHAPE, "bytes = %lld", (long long)bytes);
+    RSTQ_REQUIRE(!ctx->devs[dev].capturing, RSTQ_E_STATE, "cannot allocate during graph capture");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    void* p = nullptr;
+    RSTQ_CUDA(cudaMalloc(&p, (size_t)bytes));
+    rstq_buf* b = new (std::nothrow) rstq_buf{kBufMagic, ctx, dev, p, bytes};
+    if (!b) {
+        cudaFree(p);
+        set_error("out of host memory");
+        return RSTQ_E_OOM;
+    }
+    *buf = b;
+    return RSTQ_OK;
+}
+
+int32_t rstq_free(rstq_buf* buf) {
+    if (!buf) return RSTQ_OK;
+    RSTQ_REQUIRE(ok_buf(buf), RSTQ_E_INVALID, "invalid buffer handle");
+    DeviceState& ds = buf->ctx->devs[buf->dev];
+    cudaSetDevice(ds.ordinal);
+    if (!ds.capturing) cudaStreamSynchronize(ds.stream);
+    cudaFree(buf->ptr);
+    cudaGetLastError();
+    buf->magic = 0;
+    delete buf;
+    return RSTQ_OK;
+}
+
+static int32_t check_range(rstq_buf* buf, const void* host, int64_t offset, int64_t bytes) {
+    RSTQ_REQUIRE(ok_buf(buf), RSTQ_E_INVALID, "invalid buffer handle");
+    RSTQ_REQUIRE(host || bytes == 0, RSTQ_E_INVALID, "null host pointer");
+    RSTQ_REQUIRE(offset >= 0 && bytes >= 0 && offset + bytes <= buf->bytes, RSTQ_E_RANGE,
+                 "range [%lld, %lld) outside buffer of %lld bytes", (long long)offset,
+                 (long long)(offset + bytes), (long long)buf->bytes);
+    return RSTQ_OK;
+}
+
+int32_t rstq_upload(rstq_buf* buf, const void* host, int64_t offset, int64_t bytes) {
+    int32_t rc = check_range(buf, host, offset, bytes);
+    if (rc != RSTQ_OK) return rc;
+    DeviceState& ds = buf->ctx->devs[buf->dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "upload during graph capture");
+    if ((rc = use_dev(buf->ctx, buf->dev)) != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaMemcpyAsync((char*)buf->ptr + offset, host, (size_t)bytes,
+                              cudaMemcpyHostToDevice, ds.stream));
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    return RSTQ_OK;
+}
+
+int32_t rstq_download(rstq_buf* buf, void* host, int64_t offset, int64_t bytes) {
+    int32_t rc = check_range(buf, host, offset, bytes);
+    if (rc != RSTQ_OK) return rc;
+    DeviceState& ds = buf->ctx->devs[buf->dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "download during graph capture");
+    if ((rc = use_dev(buf->ctx, buf->dev)) != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaMemcpyAsync(host, (const char*)buf->ptr + offset, (size_t)bytes,
+                              cudaMemcpyDeviceToHost, ds.stream));
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    return RSTQ_OK;
+}
+
+int32_t rstq_memset(rstq_buf* buf, int32_t byte_value, int64_t offset, int64_t bytes) {
+    int32_t rc = check_range(buf, buf, offset, bytes);
+    if (rc != RSTQ_OK) return rc;
+    DeviceState& ds = buf->ctx->devs[buf->dev];
+    if ((rc = use_dev(buf->ctx, buf->dev)) != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaMemsetAsync((char*)buf->ptr + offset, byte_value, (size_t)bytes, ds.stream));
+    return RSTQ_OK;
+}
+
+int32_t rstq_buf_ptr(rstq_buf* buf, void** device_ptr, int64_t* bytes) {
+    RSTQ_REQUIRE(ok_buf(buf), RSTQ_E_INVALID, "invalid buffer handle");
+    if (device_ptr) *device_ptr = buf->ptr;
+    if (bytes) *bytes = buf->bytes;
+    return RSTQ_OK;
+}
+
+// ---- weights ---------------------------------------------------------------
+int32_t rstq_weight_bind(rstq_ctx* ctx, rstq_weight** w, const void* codes, const float* scales,
+                         int32_t dev, int64_t out, int64_t in, int32_t format, int32_t layout) {
+    return bind_impl(ctx, w, codes, scales, dev, out, in, format, layout, RSTQ_SPLIT_NONE, 0, 1);
+}
+
+int32_t rstq_weight_bind_shard(rstq_ctx* ctx, rstq_weight** w, const void* codes,
+                               const float* scales, int32_t dev, int64_t out, int64_t in,
+                               int32_t format, int32_t layout, int32_t split, int32_t rank,
+                               int32_t nranks) {
+    return bind_impl(ctx, w, codes, scales, dev, out, in, format, layout, split, rank, nranks);
+}
+
+int32_t rstq_weight_clone(rstq_weight* src, rstq_weight** wout) {
+    RSTQ_REQUIRE(wout, RSTQ_E_INVALID, "null argument");
+    *wout = nullptr;
+    RSTQ_REQUIRE(ok_w(src), RSTQ_E_INVALID, "invalid weight handle");
+    rstq_ctx* ctx = src->ctx;
+    DeviceState& ds = ctx->devs[src->dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "cannot clone during graph capture");
+    int32_t rc = use_dev(ctx, src->dev);
+    if (rc != RSTQ_OK) return rc;
+    rstq_weight* w = new (std::nothrow) rstq_weight(*src);
+    RSTQ_REQUIRE(w, RSTQ_E_OOM, "out of host memory");
+    w->data = nullptr;
+    cudaError_t e = cudaMalloc((void**)&w->data, (size_t)w->data_bytes);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(w->data, src->data, (size_t)w->data_bytes, cudaMemcpyDeviceToDevice,
+                            ds.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ds.stream);
+    if (e != cudaSuccess) {
+        if (w->data) cudaFree(w->data);
+        delete w;
+        return cuda_fail(e, "weight clone", __FILE__, __LINE__);
+    }
+    *wout = w;
+    return RSTQ_OK;
+}
+
+int32_t rstq_weight_free(rstq_weight* w) {
+    if (!w) return RSTQ_OK;
+    RSTQ_REQUIRE(ok_w(w), RSTQ_E_INVALID, "invalid weight handle");
+    DeviceState& ds = w->ctx->devs[w->dev];
+    cudaSetDevice(ds.ordinal);
+    if (!ds.capturing) cudaStreamSynchronize(ds.stream);
+    cudaFree(w->data);
+    cudaGetLastError();
+    w->magic = 0;
+    delete w;
+    return RSTQ_OK;
+}
+
+int32_t rstq_weight_info(rstq_weight* w, int64_t* out6) {
+    RSTQ_REQUIRE(ok_w(w), RSTQ_E_INVALID, "invalid weight handle");
+    RSTQ_REQUIRE(out6, RSTQ_E_INVALID, "null argument");
+    out6[0] = w->out;
+    out6[1] = w->in;
+    out6[2] = w->bits;
+    out6[3] = w->data_bytes;
+    out6[4] = w->out * w->in * w->bits / 8 + w->out * w->nb * 4;
+    out6[5] = w->dev;
+    return RSTQ_OK;
+}
+
+// ---- device-resident ops ----------------------------------------------------
+static int32_t need_bytes(rstq_buf* b, int64_t bytes, const char* name) {
+    RSTQ_REQUIRE(ok_buf(b), RSTQ_E_INVALID, "invalid buffer handle for %s", name);
+    RSTQ_REQUIRE(b->bytes >= bytes, RSTQ_E_RANGE, "%s holds %lld bytes, call needs %lld", name,
+                 (long long)b->bytes, (long long)bytes);
+    RSTQ_REQUIRE(((uintptr_t)b->ptr & 15) == 0, RSTQ_E_ALIGN, "%s is not 16-byte aligned", name);
+    return RSTQ_OK;
+}
+
+int32_t rstq_quant_act_i8(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rstq_buf* xs, rstq_buf* xsum,
+                          int64_t M, int64_t in) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(M >= 1 && in >= 32 && in % 32 == 0, RSTQ_E_SHAPE,
+                 "M = %lld, in = %lld (in must be a multiple of 32)", (long long)M, (long long)in);
+    const int64_t nb = in / 32;
+    int32_t rc;
+    if ((rc = need_bytes(x, M * in * 4, "x")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(xq, M * in, "xq")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(xs, M * nb * 4, "xs")) != RSTQ_OK) return rc;
+    if (xsum && (rc = need_bytes(xsum, M * nb * 4, "xsum")) != RSTQ_OK) return rc;
+    RSTQ_REQUIRE(x->dev == xq->dev && x->dev == xs->dev && (!xsum || xsum->dev == x->dev),
+                 RSTQ_E_DEVICE, "buffers live on different devices");
+    if ((rc = use_dev(ctx, x->dev)) != RSTQ_OK) return rc;
+    return launch_quant_act_i8(ctx, ctx->devs[x->dev], (const float*)x->ptr, (int8_t*)xq->ptr,
+                               (float*)xs->ptr, xsum ? (int32_t*)xsum->ptr : nullptr, M, in);
+}
+
+int32_t rstq_qmatmul(rstq_ctx* ctx, rstq_weight* w, rstq_buf* x, rstq_buf* y, int64_t M,
+                     int32_t act_dtype, int32_t out_dtype, int32_t mode) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(ok_w(w) && w->ctx == ctx, RSTQ_E_INVALID, "invalid weight handle");
+    RSTQ_REQUIRE(M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)M);
+    RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "bad act dtype");
+    RSTQ_REQUIRE(out_dtype == RSTQ_F32 || out_dtype == RSTQ_BF16, RSTQ_E_INVALID, "bad out dtype");
+    RSTQ_REQUIRE(mode == RSTQ_MODE_F || mode == RSTQ_MODE_A8, RSTQ_E_INVALID, "bad mode");
+    int32_t rc;
+    if ((rc = need_bytes(x, M * w->in * (act_dtype == RSTQ_F32 ? 4 : 2), "x")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(y, M * w->out * (out_dtype == RSTQ_F32 ? 4 : 2), "y")) != RSTQ_OK) return rc;
+    RSTQ_REQUIRE(x->dev == w->dev && y->dev == w->dev, RSTQ_E_DEVICE,
+                 "weight and buffers live on different devices");
+    if ((rc = use_dev(ctx, w->dev)) != RSTQ_OK) return rc;
+    return matmul_device(ctx, w, x->ptr, y->ptr, M, act_dtype, out_dtype, mode);
+}
+
+int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_buf* xs,
+                              rstq_buf* xsum, rstq_buf* y, int64_t M) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(ok_w(w) && w->ctx == ctx, RSTQ_E_INVALID, "invalid weight handle");
+    RSTQ_REQUIRE(M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)M);
+    int32_t rc;
+    if ((rc = need_bytes(xq, M * w->in, "xq")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(xs, M * w->nb * 4, "xs")) != RSTQ_OK) return rc;
+    if (xsum && (rc = need_bytes(xsum, M * w->nb * 4, "xsum")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(y, M * w->out * 4, "y")) != RSTQ_OK) return rc;
+    RSTQ_REQUIRE(xq->dev == w->dev && xs->dev == w->dev && y->dev == w->dev &&
+                     (!xsum || xsum->dev == w->dev),
+                 RSTQ_E_DEVICE, "weight and buffers live on different devices");
+    if ((rc = use_dev(ctx, w->dev)) != RSTQ_OK) return rc;
+    DeviceState& ds = ctx->devs[w->dev];
+    const int32_t* sums = xsum ? (const int32_t*)xsum->ptr : nullptr;
+    if (!sums) {
+        // the stored codes carry a zero point, so the block sums are needed even
+        // when the caller's arithmetic (signed x signed) has none
+        ActScratch s;
+        if ((rc = act_scratch(ds, M, w->in, &s)) != RSTQ_OK) return rc;
+        const int64_t nblocks = M * w->nb;
+        block_sum_kernel<<<(unsigned)((nblocks + 127) / 128), 128, 0, ds.stream>>>(
+            (const int8_t*)xq->ptr, s.xsum, nblocks);
+        ctx->launches++;
+        RSTQ_CUDA(cudaGetLastError());
+        sums = s.xsum;
+    }
+    return run_a8(ctx, w, (const int8_t*)xq->ptr, (const float*)xs->ptr, sums, (float*)y->ptr, M);
+}
+
+// ---- host-array operators -----------------------------------------------------
+static int32_t cached_weight(rstq_ctx* ctx, const void* codes, const float* scales, int64_t in,
+                             int64_t out, int fmt, int layout, rstq_weight** w) {
+    rstq_ctx::CacheKey key{codes, scales, in, out, fmt, layout};
+    auto it = ctx->wcache.find(key);
+    if (it != ctx->wcache.end()) {
+        *w = it->second;
+        return RSTQ_OK;
+    }
+    int32_t rc = bind_impl(ctx, w, codes, scales, 0, out, in, fmt, layout, RSTQ_SPLIT_NONE, 0, 1);
+    if (rc != RSTQ_OK) return rc;
+    ctx->wcache.emplace(key, *w);
+    return RSTQ_OK;
+}
+
+// Stage x (x_bytes) to the device, run `body(dev_x, dev_y)`, bring y (y_bytes) back.
+extern "C++" {
+template <typename Body>
+int32_t host_roundtrip(rstq_ctx* ctx, int dev, const void* x, int64_t x_bytes, void* y,
+                              int64_t y_bytes, Body body) {
+    DeviceState& ds = ctx->devs[dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "host-array operators cannot be captured");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    const int64_t xa = (x_bytes + 255) & ~255ll, ya = (y_bytes + 255) & ~255ll;
+    if ((rc = ensure_pinned(ds, xa + ya)) != RSTQ_OK) return rc;
+    if ((rc = ensure_dev(ds, &ds.io_dev, &ds.io_dev_bytes, xa + ya)) != RSTQ_OK) return rc;
+    char* hp = (char*)ds.pinned;
+    char* dp = (char*)ds.io_dev;
+    memcpy(hp, x, (size_t)x_bytes);
+    RSTQ_CUDA(cudaMemcpyAsync(dp, hp, (size_t)x_bytes, cudaMemcpyHostToDevice, ds.stream));
+    if ((rc = body((void*)dp, (void*)(dp + xa))) != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaMemcpyAsync(hp + xa, dp + xa, (size_t)y_bytes, cudaMemcpyDeviceToHost, ds.stream));
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    memcpy(y, hp + xa, (size_t)y_bytes);
+    return RSTQ_OK;
+}
+}  // extern "C++"
+
+static int32_t qlinear_i8_impl(rstq_ctx* ctx, const float* x, const void* wqi, const float* wsi,
+                               float* y, int64_t in, int64_t out, int fmt) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(x && wqi && wsi && y, RSTQ_E_INVALID, "null argument");
+    RSTQ_REQUIRE(in >= 32 && in % 32 == 0 && out >= 8 && out % 8 == 0, RSTQ_E_SHAPE,
+                 "qlinear-i8 contract: in %% 32 == 0 and out %% 8 == 0 (in = %lld, out = %lld)",
+                 (long long)in, (long long)out);
+    rstq_weight* w = nullptr;
+    int32_t rc = cached_weight(ctx, wqi, wsi, in, out, fmt, RSTQ_LAYOUT_STREAM8, &w);
+    if (rc != RSTQ_OK) return rc;
+    return host_roundtrip(ctx, w->dev, x, in * 4, y, out * 4, [&](void* dx, void* dy) {
+        return matmul_device(ctx, w, dx, dy, 1, RSTQ_F32, RSTQ_F32, RSTQ_MODE_A8);
+    });
+}
+
+int32_t rstq_qlinear_i8(rstq_ctx* ctx, const float* x, const void* wqi, const float* wsi, float* y,
+                        int64_t in, int64_t out) {
+    return qlinear_i8_impl(ctx, x, wqi, wsi, y, in, out, RSTQ_FMT_Q4_0);
+}
+
+int32_t rstq_qlinear_i8_q8(rstq_ctx* ctx, const float* x, const void* wqi, const float* wsi,
+                           float* y, int64_t in, int64_t out) {
+    return qlinear_i8_impl(ctx, x, wqi, wsi, y, in, out, RSTQ_FMT_Q8_0);
+}
+
+int32_t rstq_qlinear_q8(rstq_ctx* ctx, const float* x, const void* codes, const float* scales,
+                        float* y, int64_t m, int64_t in, int64_t out) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(x && codes && scales && y, RSTQ_E_INVALID, "null argument");
+    RSTQ_REQUIRE(m >= 1 && out >= 1 && in >= 32 && in % 32 == 0, RSTQ_E_SHAPE,
+                 "in=%lld not a multiple of 32 (m = %lld, out = %lld)", (long long)in, (long long)m,
+                 (long long)out);
+    rstq_weight* w = nullptr;
+    int32_t rc = cached_weight(ctx, codes, scales, in, out, RSTQ_FMT_Q8_S, RSTQ_LAYOUT_ROWMAJOR, &w);
+    if (rc != RSTQ_OK) return rc;
+    return host_roundtrip(ctx, w->dev, x, m * in * 4, y, m * out * 4, [&](void* dx, void* dy) {
+        return matmul_device(ctx, w, dx, dy, m, RSTQ_F32, RSTQ_F32, RSTQ_MODE_F);
+    });
+}
+
+int32_t rstq_qmatmul_i8_gemm(rstq_ctx* ctx, const int32_t* xp, const float* xs, const int32_t* wp,
+                             const float* ws, float* y, int64_t in, int64_t out, int64_t nrows) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(xp && xs && wp && ws && y, RSTQ_E_INVALID, "null argument");
+    RSTQ_REQUIRE(nrows >= 1 && out >= 1 && in >= 32 && in % 32 == 0, RSTQ_E_SHAPE,
+                 "in = %lld must be a multiple of 32", (long long)in);
+    rstq_weight* w = nullptr;
+    int32_t rc = cached_weight(ctx, wp, ws, in, out, RSTQ_FMT_Q8_S, RSTQ_LAYOUT_ROWMAJOR, &w);
+    if (rc != RSTQ_OK) return rc;
+    DeviceState& ds = ctx->devs[w->dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "host-array operators cannot be captured");
+    if ((rc = use_dev(ctx, w->dev)) != RSTQ_OK) return rc;
+    const int64_t nb = in / 32;
+    const int64_t xq_b = (nrows * in + 255) & ~255ll, xs_b = (nrows * nb * 4 + 255) & ~255ll;
+    const int64_t y_b = (nrows * out * 4 + 255) & ~255ll;
+    if ((rc = ensure_pinned(ds, xq_b + xs_b + y_b)) != RSTQ_OK) return rc;
+    if ((rc = ensure_dev(ds, &ds.io_dev, &ds.io_dev_bytes, xq_b + xs_b + y_b)) != RSTQ_OK) return rc;
+    ActScratch s;
+    if ((rc = act_scratch(ds, nrows, in, &s)) != RSTQ_OK) return rc;
+    char* hp = (char*)ds.pinned;
+    char* dp = (char*)ds.io_dev;
+    memcpy(hp, xp, (size_t)(nrows * in));
+    memcpy(hp + xq_b, xs, (size_t)(nrows * nb * 4));
+    RSTQ_CUDA(cudaMemcpyAsync(dp, hp, (size_t)(xq_b + xs_b), cudaMemcpyHostToDevice, ds.stream));
+    const int64_t nblocks = nrows * nb;
+    block_sum_kernel<<<(unsigned)((nblocks + 127) / 128), 128, 0, ds.stream>>>((const int8_t*)dp,
+                                                                              s.xsum, nblocks);
+    ctx->launches++;
+    RSTQ_CUDA(cudaGetLastError());
+    rc = run_a8(ctx, w, (const int8_t*)dp, (const float*)(dp + xq_b), s.xsum,
+                (float*)(dp + xq_b + xs_b), nrows);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaMemcpyAsync(hp + xq_b + xs_b, dp + xq_b + xs_b, (size_t)(nrows * out * 4),
+                              cudaMemcpyDeviceToHost, ds.stream));
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    memcpy(y, hp + xq_b + xs_b, (size_t)(nrows * out * 4));
+    return RSTQ_OK;
+}
+
+int32_t rstq_i8gemv_dp4a(rstq_ctx* ctx, const int32_t* wp, const int32_t* xp, float* y, int64_t kw,
+                         int64_t out) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(wp && xp && y, RSTQ_E_INVALID, "null argument");
+    RSTQ_REQUIRE(kw >= 1 && out >= 1, RSTQ_E_SHAPE, "kw = %lld, out = %lld", (long long)kw,
+                 (long long)out);
+    DeviceState& ds = ctx->devs[0];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "host-array operators cannot be captured");
+    int32_t rc = use_dev(ctx, 0);
+    if (rc != RSTQ_OK) return rc;
+    const int64_t w_b = (out * kw * 4 + 255) & ~255ll, x_b = (kw * 4 + 255) & ~255ll;
+    const int64_t y_b = (out * 4 + 255) & ~255ll;
+    if ((rc = ensure_pinned(ds, x_b + y_b)) != RSTQ_OK) return rc;
+    if ((rc = ensure_dev(ds, &ds.io_dev, &ds.io_dev_bytes, w_b + x_b + y_b)) != RSTQ_OK) return rc;
+    char* hp = (char*)ds.pinned;
+    char* dp = (char*)ds.io_dev;
+    memcpy(hp, xp, (size_t)(kw * 4));
+    RSTQ_CUDA(cudaMemcpyAsync(dp, wp, (size_t)(out * kw * 4), cudaMemcpyHostToDevice, ds.stream));
+    RSTQ_CUDA(cudaMemcpyAsync(dp + w_b, hp, (size_t)(kw * 4), cudaMemcpyHostToDevice, ds.stream));
+    const int64_t threads = out * 32;
+    i8gemv_dp4a_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ds.stream>>>(
+        (const int32_t*)dp, (const int32_t*)(dp + w_b), (float*)(dp + w_b + x_b), kw, out);
+    ctx->launches++;
+    RSTQ_CUDA(cudaGetLastError());
+    RSTQ_CUDA(cudaMemcpyAsync(hp + x_b, dp + w_b + x_b, (size_t)(out * 4), cudaMemcpyDeviceToHost,
+                              ds.stream));
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    memcpy(y, hp + x_b, (size_t)(out * 4));
+    return RSTQ_OK;
+}
+
+int32_t rstq_qmatmul_host(rstq_ctx* ctx, rstq_weight* w, const void* x, float* y, int64_t M,
+                          int32_t act_dtype, int32_t mode) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(ok_w(w) && w->ctx == ctx, RSTQ_E_INVALID, "invalid weight handle");
+    RSTQ_REQUIRE(x && y, RSTQ_E_INVALID, "null argument");
+    RSTQ_REQUIRE(M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)M);
+    RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "bad act dtype");
+    RSTQ_REQUIRE(mode == RSTQ_MODE_F || mode == RSTQ_MODE_A8, RSTQ_E_INVALID, "bad mode");
+    const int64_t xe = act_dtype == RSTQ_F32 ? 4 : 2;
+    return host_roundtrip(ctx, w->dev, x, M * w->in * xe, y, M * w->out * 4,
+                          [&](void* dx, void* dy) {
+                              return matmul_device(ctx, w, dx, dy, M, act_dtype, RSTQ_F32, mode);
+                          });
+}
+
+int32_t rstq_weight_cache_clear(rstq_ctx* ctx) {
+    CHECK_CTX(ctx);
+    for (auto& kv : ctx->wcache) rstq_weight_free(kv.second);
+    ctx->wcache.clear();
+    return RSTQ_OK;
+}
+
+// ---- graphs / events ----------------------------------------------------------
+int32_t rstq_graph_begin(rstq_ctx* ctx, int32_t dev) {
+    CHECK_CTX(ctx);
+    CHECK_DEV(ctx, dev);
+    DeviceState& ds = ctx->devs[dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "capture already in progress");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaStreamBeginCapture(ds.stream, cudaStreamCaptureModeThreadLocal));
+    ds.capturing = true;
+    return RSTQ_OK;
+}
+
+int32_t rstq_graph_end(rstq_ctx* ctx, rstq_graph** graph, int32_t dev) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(graph, RSTQ_E_INVALID, "null argument");
+    *graph = nullptr;
+    CHECK_DEV(ctx, dev);
+    DeviceState& ds = ctx->devs[dev];
+    RSTQ_REQUIRE(ds.capturing, RSTQ_E_STATE, "no capture in progress");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    ds.capturing = false;
+    cudaGraph_t g = nullptr;
+    RSTQ_CUDA(cudaStreamEndCapture(ds.stream, &g));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        return cuda_fail(e, "cudaGraphInstantiate", __FILE__, __LINE__);
+    }
+    size_t nodes = 0;
+    cudaGraphGetNodes(g, nullptr, &nodes);
+    int64_t kernels = 0;
+    if (nodes) {
+        std::vector<cudaGraphNode_t> v(nodes);
+        cudaGraphGetNodes(g, v.data(), &nodes);
+        for (auto n : v) {
+            cudaGraphNodeType t;
+            if (cudaGraphNodeGetType(n, &t) == cudaSuccess && t == cudaGraphNodeTypeKernel) ++kernels;
+        }
+    }
+    ctx->launches -= kernels;  // recorded, not run: replays count them
+    rstq_graph* gr = new (std::nothrow) rstq_graph{kGrfMagic, ctx, dev, g, exec, kernels};
+    if (!gr) {
+        cudaGraphExecDestroy(exec);
+        cudaGraphDestroy(g);
+        set_error("out of host memory");
+        return RSTQ_E_OOM;
+    }
+    *graph = gr;
+    return RSTQ_OK;
+}
+
+int32_t rstq_graph_replay(rstq_graph* graph) {
+    RSTQ_REQUIRE(graph && graph->magic == kGrfMagic, RSTQ_E_INVALID, "invalid graph handle");
+    rstq_ctx* ctx = graph->ctx;
+    int32_t rc = use_dev(ctx, graph->dev);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaGraphLaunch(graph->exec, ctx->devs[graph->dev].stream));
+    ctx->launches += graph->kernels;
+    return RSTQ_OK;
+}
+
+int32_t rstq_graph_destroy(rstq_graph* graph) {
+    if (!graph) return RSTQ_OK;
+    RSTQ_REQUIRE(graph->magic == kGrfMagic, RSTQ_E_INVALID, "invalid graph handle");
+    DeviceState& ds = graph->ctx->devs[graph->dev];
+    cudaSetDevice(ds.ordinal);
+    cudaStreamSynchronize(ds.stream);
+    cudaGraphExecDestroy(graph->exec);
+    cudaGraphDestroy(graph->graph);
+    cudaGetLastError();
+    graph->magic = 0;
+    delete graph;
+    return RSTQ_OK;
+}
+
+int32_t rstq_event_create(rstq_ctx* ctx, rstq_event** ev, int32_t dev) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(ev, RSTQ_E_INVALID, "null argument");
+    *ev = nullptr;
+    CHECK_DEV(ctx, dev);
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    cudaEvent_t e;
+    RSTQ_CUDA(cudaEventCreate(&e));
+    rstq_event* r = new (std::nothrow) rstq_event{kEvtMagic, ctx, dev, e};
+    if (!r) {
+        cudaEventDestroy(e);
+        set_error("out of host memory");
+        return RSTQ_E_OOM;
+    }
+    *ev = r;
+    return RSTQ_OK;
+}
+
+int32_t rstq_event_record(rstq_event* ev) {
+    RSTQ_REQUIRE(ev && ev->magic == kEvtMagic, RSTQ_E_INVALID, "invalid event handle");
+    int32_t rc = use_dev(ev->ctx, ev->dev);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaEventRecord(ev->ev, ev->ctx->devs[ev->dev].stream));
+    return RSTQ_OK;
+}
+
+int32_t rstq_event_elapsed_ms(rstq_event* start, rstq_event* stop, float* ms) {
+    RSTQ_REQUIRE(start && start->magic == kEvtMagic && stop && stop->magic == kEvtMagic && ms,
+                 RSTQ_E_INVALID, "invalid event handle");
+    RSTQ_REQUIRE(start->dev == stop->dev, RSTQ_E_DEVICE, "events live on different devices");
+    int32_t rc = use_dev(start->ctx, start->dev);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaEventSynchronize(stop->ev));
+    RSTQ_CUDA(cudaEventElapsedTime(ms, start->ev, stop->ev));
+    return RSTQ_OK;
+}
+
+int32_t rstq_event_destroy(rstq_event* ev) {
+    if (!ev) return RSTQ_OK;
+    RSTQ_REQUIRE(ev->magic == kEvtMagic, RSTQ_E_INVALID, "invalid event handle");
+    cudaSetDevice(ev->ctx->devs[ev->dev].ordinal);
+    cudaEventDestroy(ev->ev);
+    cudaGetLastError();
+    ev->magic = 0;
+    delete ev;
+    return RSTQ_OK;
+}
+
+int32_t rstq_launch_count(rstq_ctx* ctx, int64_t* count) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(count, RSTQ_E_INVALID, "null argument");
+    *count = ctx->launches;
+    return RSTQ_OK;
+}
+
+}  // extern "C"

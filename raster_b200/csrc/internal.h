@@ -1,0 +1,181 @@
+// Internal declarations shared by the translation units of librstq.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/rstq.h"
+
+namespace rstq {
+
+// ---- error plumbing --------------------------------------------------------
+void set_error(const char* fmt, ...);
+int32_t cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+
+#define RSTQ_CUDA(call)                                                      \
+    do {                                                                     \
+        cudaError_t e__ = (call);                                            \
+        if (e__ != cudaSuccess) return ::rstq::cuda_fail(e__, #call, __FILE__, __LINE__); \
+    } while (0)
+
+#define RSTQ_REQUIRE(cond, code, ...)     \
+    do {                                  \
+        if (!(cond)) {                    \
+            ::rstq::set_error(__VA_ARGS__); \
+            return (code);                \
+        }                                 \
+    } while (0)
+
+// ---- device weight layout ("mma32") -----------------------------------------
+// Rows are padded to a multiple of 32.  A unit (g, b) holds block b (32 K
+// elements) of the 32 rows of group g.  Units are stored b-fastest, so the
+// K-slice of one group is one contiguous byte range.
+//
+//   4-bit unit, 640 B : [32 slots x 16 B codes][32 x f32 scales]
+//   8-bit unit, 1152 B: [plane 0: 32 slots x 16 B][plane 1: 32 x 16 B][32 x f32 scales]
+//
+// Slot `lane` = gid*4 + tig (gid = lane >> 2, tig = lane & 3) holds four 32-bit
+// words i = 0..3, one per row r_i = 32g + gid + 8i:
+//   4-bit: word `tig` of that row's 16-byte Q4_0 block (low nibbles = elements
+//          4tig..4tig+3, high nibbles = elements 16+4tig..16+4tig+3);
+//   8-bit: plane p holds word `tig + 4p` of the row's 32-byte block (elements
+//          4tig+16p .. 4tig+16p+3), unsigned with zero point 128.
+// Scale index gid*4 + i is the scale of row r_i.
+// This is exactly the A-fragment ownership of mma.sync m16n8k32 (int8) and, per
+// 16-element half, of m16n8k16 (bf16), so one 16-byte load per lane feeds two
+// 16-row tensor-core tiles with no shuffles.
+constexpr int kUnitBytesQ4 = 640;
+constexpr int kUnitBytesQ8 = 1152;
+constexpr int kUnitCodesQ4 = 512;
+constexpr int kUnitCodesQ8 = 1024;
+inline int unit_bytes(int bits) { return bits == 4 ? kUnitBytesQ4 : kUnitBytesQ8; }
+
+struct DeviceState {
+    int ordinal = -1;
+    int sm_count = 0;
+    int64_t l2_bytes = 0;
+    int64_t total_mem = 0;
+    int cc = 0;
+    cudaStream_t stream = nullptr;
+    bool capturing = false;
+    // scratch owned by the context
+    void* act_scratch = nullptr;   // quantized / converted activations
+    int64_t act_scratch_bytes = 0;
+    float* partials = nullptr;     // split-K partial sums
+    int64_t partials_bytes = 0;
+    int* counters = nullptr;       // split-K arrival counters (zero between calls)
+    int64_t counters_len = 0;
+    void* pinned = nullptr;        // host staging for the host-array entry points
+    int64_t pinned_bytes = 0;
+    void* io_dev = nullptr;        // device staging for the host-array entry points
+    int64_t io_dev_bytes = 0;
+    int gemv_ctas_per_sm = 3;
+};
+
+}  // namespace rstq
+
+struct rstq_ctx {
+    uint32_t magic;
+    std::vector<rstq::DeviceState> devs;
+    int64_t tune_splitk = 0;
+    int64_t tune_gemm_min_m = 17;
+    int64_t launches = 0;
+    struct CacheKey {
+        const void* codes;
+        const void* scales;
+        int64_t in, out;
+        int fmt, layout;
+        bool operator==(const CacheKey& o) const {
+            return codes == o.codes && scales == o.scales && in == o.in && out == o.out &&
+                   fmt == o.fmt && layout == o.layout;
+        }
+    };
+    struct CacheHash {
+        size_t operator()(const CacheKey& k) const {
+            size_t h = (size_t)k.codes * 1315423911u ^ (size_t)k.scales;
+            return h ^ (size_t)(k.in * 31 + k.out) ^ (size_t)(k.fmt * 7 + k.layout);
+        }
+    };
+    std::unordered_map<CacheKey, rstq_weight*, CacheHash> wcache;
+};
+
+struct rstq_buf {
+    uint32_t magic;
+    rstq_ctx* ctx;
+    int dev;
+    void* ptr;
+    int64_t bytes;
+};
+
+struct rstq_weight {
+    uint32_t magic;
+    rstq_ctx* ctx;
+    int dev;
+    int bits;          // 4 or 8
+    int zp;            // 8 or 128 (signed codes are stored offset by 128)
+    int64_t out, in;   // logical shape of this (possibly sharded) matrix
+    int64_t outp;      // rows padded to a multiple of 32
+    int64_t nb;        // in / 32
+    uint8_t* data;     // mma32 units, (outp/32) * nb of them
+    int64_t data_bytes;
+};
+
+struct rstq_graph {
+    uint32_t magic;
+    rstq_ctx* ctx;
+    int dev;
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    int64_t kernels;  // kernel nodes per replay
+};
+
+struct rstq_event {
+    uint32_t magic;
+    rstq_ctx* ctx;
+    int dev;
+    cudaEvent_t ev;
+};
+
+namespace rstq {
+
+constexpr uint32_t kCtxMagic = 0x52535143;   // 'RSQC'
+constexpr uint32_t kBufMagic = 0x52535142;
+constexpr uint32_t kWgtMagic = 0x52535157;
+constexpr uint32_t kGrfMagic = 0x52535147;
+constexpr uint32_t kEvtMagic = 0x52535145;
+
+// ---- kernel launchers (each returns a status; all launch on ds.stream) -------
+// layout.cu
+int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
+                      const float* src_scales, uint8_t* dst, int fmt, int layout, int64_t out,
+                      int64_t in, int64_t src_in, int64_t k_block0);
+// actquant.cu
+int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs,
+                            int32_t* xsum, int64_t M, int64_t in);
+// gemv.cu
+struct GemvA8Args {
+    const uint8_t* w;
+    const int8_t* xq;
+    const float* xs;
+    const int32_t* xsum;  // may be null (treated as zero-point-free: signed x signed)
+    float* y;
+    int64_t M, in, out;   // y is [M, out] f32
+    int bits, zp;
+};
+struct GemvFArgs {
+    const uint8_t* w;
+    const void* x;        // f32 or bf16 [M, in]
+    void* y;              // f32 or bf16 [M, out]
+    int64_t M, in, out;
+    int bits, zp;
+    int act_dtype, out_dtype;
+};
+int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a);
+int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a);
+int32_t gemv_configure(DeviceState& ds);  // occupancy / smem attributes, once per device
+constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels
+
+}  // namespace rstq

@@ -1,0 +1,125 @@
+// Load-time layout transform: reference host layouts -> the mma32 device layout.
+//
+// Takes the place of repack-stream (src/raster/compiler/backend/cpu/quant.clj:317-326,
+// src/raster/compiler/core/layout.clj:246-286) as the one-time weight re-tiling,
+// and accepts every host layout the reference's operators take:
+//   row-major Q4_0 / Q8_0  {wq, ws}         quant.clj:42-70
+//   8-row stream layout    {wqi, wsi}       layout.clj:246-286
+//   signed row-major codes {codes, scales}  src/raster/quant/train.clj:34-58
+//                          (= the int32-packed {wp, ws} of src/raster/quant/pack.clj:55-81
+//                           read as little-endian bytes)
+#include "internal.h"
+
+namespace rstq {
+
+// Source accessors return the *unsigned* stored code of (row, block b, element e).
+struct SrcView {
+    const uint8_t* codes;
+    const float* scales;
+    int64_t nb_src;   // blocks per source row
+    int64_t kb0;      // first source block of this shard
+    int layout;       // RSTQ_LAYOUT_*
+};
+
+__device__ __forceinline__ uint32_t src_nibble(const SrcView& s, int64_t row, int64_t b, int e) {
+    const int64_t sb = b + s.kb0;
+    if (s.layout == RSTQ_LAYOUT_ROWMAJOR) {
+        uint32_t bv = s.codes[(row * s.nb_src + sb) * 16 + (e & 15)];
+        return e < 16 ? (bv & 0xF) : (bv >> 4);
+    }
+    // 8-row interleave: byte ((g*nb + b)*8 + ig)*16 + j, j = (row%8 % 4)*4 + e%4,
+    // low nibble for rows 0..3 of the group, high nibble for rows 4..7.
+    const int64_t g = row >> 3;
+    const int rr = (int)(row & 7);
+    uint32_t bv = s.codes[((g * s.nb_src + sb) * 8 + (e >> 2)) * 16 + (rr & 3) * 4 + (e & 3)];
+    return rr < 4 ? (bv & 0xF) : (bv >> 4);
+}
+
+__device__ __forceinline__ uint32_t src_byte(const SrcView& s, int64_t row, int64_t b, int e) {
+    const int64_t sb = b + s.kb0;
+    if (s.layout == RSTQ_LAYOUT_ROWMAJOR) return s.codes[(row * s.nb_src + sb) * 32 + e];
+    const int64_t g = row >> 3;
+    const int rr = (int)(row & 7);
+    return s.codes[((g * s.nb_src + sb) * 8 + (e >> 2)) * 32 + rr * 4 + (e & 3)];
+}
+
+__device__ __forceinline__ float src_scale(const SrcView& s, int64_t row, int64_t b) {
+    const int64_t sb = b + s.kb0;
+    if (s.layout == RSTQ_LAYOUT_ROWMAJOR) return s.scales[row * s.nb_src + sb];
+    return s.scales[((row >> 3) * s.nb_src + sb) * 8 + (row & 7)];
+}
+
+// One thread per destination 32-bit word (codes) or scale.
+template <int BITS>
+__global__ void repack_kernel(SrcView s, uint8_t* __restrict__ dst, int64_t out, int64_t nb,
+                              int64_t groups, int flip_sign) {
+    constexpr int UNIT = BITS == 4 ? kUnitBytesQ4 : kUnitBytesQ8;
+    constexpr int WORDS = UNIT / 4;  // code words + 32 scale words
+    const int64_t total = groups * nb * WORDS;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t unit = idx / WORDS;
+        const int wi = (int)(idx % WORDS);
+        const int64_t g = unit / nb, b = unit % nb;
+        uint32_t* dword = reinterpret_cast<uint32_t*>(dst + unit * UNIT) + wi;
+        constexpr int CODE_WORDS = (UNIT - 128) / 4;
+        if (wi >= CODE_WORDS) {  // scale gid*4 + i -> row 32g + gid + 8i
+            const int si = wi - CODE_WORDS;
+            const int64_t row = g * 32 + (si >> 2) + 8 * (si & 3);
+            float v = row < out ? src_scale(s, row, b) : 0.0f;
+            *reinterpret_cast<float*>(dword) = v;
+            continue;
+        }
+        const int plane = wi >> 7;           // 0 for 4-bit; 0/1 for 8-bit
+        const int slot = (wi & 127) >> 2;    // lane slot
+        const int i = wi & 3;
+        const int gid = slot >> 2, tig = slot & 3;
+        const int64_t row = g * 32 + gid + 8 * i;
+        uint32_t word = 0;
+        if (BITS == 4) {
+            if (row < out) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t lo = src_nibble(s, row, b, 4 * tig + j);
+                    uint32_t hi = src_nibble(s, row, b, 16 + 4 * tig + j);
+                    word |= (lo | (hi << 4)) << (8 * j);
+                }
+            } else {
+                word = 0x88888888u;  // zero point: padded rows dequantize to 0
+            }
+        } else {
+            if (row < out) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t v = src_byte(s, row, b, 16 * plane + 4 * tig + j);
+                    if (flip_sign) v ^= 0x80u;  // signed code c -> c + 128
+                    word |= v << (8 * j);
+                }
+            } else {
+                word = 0x80808080u;
+            }
+        }
+        *dword = word;
+    }
+}
+
+int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
+                      const float* src_scales, uint8_t* dst, int fmt, int layout, int64_t out,
+                      int64_t in, int64_t src_in, int64_t k_block0) {
+    SrcView s{src_codes, src_scales, src_in / 32, k_block0, layout};
+    const int64_t nb = in / 32, groups = (out + 31) / 32;
+    const int bits = fmt == RSTQ_FMT_Q4_0 ? 4 : 8;
+    const int64_t total = groups * nb * (unit_bytes(bits) / 4);
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (blocks < 1) blocks = 1;
+    if (bits == 4)
+        repack_kernel<4><<<blocks, 256, 0, ds.stream>>>(s, dst, out, nb, groups, 0);
+    else
+        repack_kernel<8><<<blocks, 256, 0, ds.stream>>>(s, dst, out, nb, groups,
+                                                        fmt == RSTQ_FMT_Q8_S ? 1 : 0);
+    ctx->launches++;
+    RSTQ_CUDA(cudaGetLastError());
+    return RSTQ_OK;
+}
+
+}  // namespace rstq

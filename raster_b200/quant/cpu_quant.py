@@ -1,0 +1,81 @@
+"""Host-side codecs of the block-quantized formats (load-time code, numpy).
+
+Mirrors the reference namespace ``raster.compiler.backend.cpu.quant``
+(src/raster/compiler/backend/cpu/quant.clj): the format rows ``q4-0`` (:27-31)
+and ``q8-0`` (:33-39), ``quantize-weight`` (:42-70), ``quantize-weight-q4``
+(:72-76), ``quantize-act-i8`` (:298-305) and ``repack-stream`` (:317-326).  As
+in the reference these run once per weight on the host; the matmul itself is
+never computed here.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import layout as _layout
+
+q4_0 = {"name": "q4_0", "block": 32, "weight_bits": 4, "pack": "nibble-interleaved",
+        "zero_point": 8, "symmetric": True, "act_type": "i8"}
+q8_0 = {"name": "q8_0", "block": 32, "weight_bits": 8, "pack": "byte-direct",
+        "zero_point": 128, "symmetric": True, "act_type": "i8"}
+
+
+def jround(v: np.ndarray) -> np.ndarray:
+    """Java ``Math.round`` on doubles: nearest integer, ties toward +infinity."""
+    f = np.floor(v)
+    return (f + ((v - f) >= 0.5)).astype(np.int64)
+
+
+def quantize_weight(w, fmt=q4_0):
+    """Flat f32 array (len % 32 == 0) -> {"wq": uint8, "ws": float32}.
+
+    Per block: v = the signed element of largest magnitude (first on ties),
+    d = v / -zp, q = clamp(round(x / d) + zp, 0, 2^bits - 1); nibble formats put
+    element k in the low and element k+16 in the high nibble of byte k.
+    """
+    w = np.ascontiguousarray(w, dtype=np.float32).reshape(-1, 32)
+    zp, bits = fmt["zero_point"], fmt["weight_bits"]
+    qmax = (1 << bits) - 1
+    idx = np.argmax(np.abs(w), axis=1)  # first maximum, as the strict > scan finds
+    v = w[np.arange(w.shape[0]), idx].astype(np.float64)
+    d = v / float(-zp)
+    with np.errstate(divide="ignore"):
+        inv = np.where(d == 0.0, 0.0, 1.0 / d)
+    q = np.clip(jround(w.astype(np.float64) * inv[:, None]) + zp, 0, qmax).astype(np.uint8)
+    if fmt["pack"] == "nibble-interleaved":
+        wq = (q[:, :16] | (q[:, 16:] << 4)).astype(np.uint8).ravel()
+    else:
+        wq = q.ravel()
+    return {"wq": wq, "ws": d.astype(np.float32)}
+
+
+def quantize_weight_q4(w):
+    return quantize_weight(w, q4_0)
+
+
+def dequant_weight(wq, ws, fmt=q4_0):
+    """w ~= d * (q - zp); the rule the reference's codec test checks."""
+    zp = fmt["zero_point"]
+    if fmt["pack"] == "nibble-interleaved":
+        b = np.asarray(wq, dtype=np.uint8).reshape(-1, 16)
+        q = np.concatenate([b & 0xF, b >> 4], axis=1).astype(np.int32)
+    else:
+        q = np.asarray(wq, dtype=np.uint8).reshape(-1, 32).astype(np.int32)
+    return ((q - zp) * np.asarray(ws, dtype=np.float64)[:, None]).astype(np.float32).ravel()
+
+
+def quantize_act_i8(x, M, in_):
+    """f32 rows [M*in] -> {"xq": int8, "xs": float32 [M*nb], "xsum": int32 [M*nb]}."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, 32)
+    assert x.shape[0] == M * (in_ // 32)
+    d = np.abs(x).max(axis=1).astype(np.float64) / 127.0
+    with np.errstate(divide="ignore"):
+        inv = np.where(d == 0.0, 0.0, 1.0 / d)
+    q = np.clip(jround(x.astype(np.float64) * inv[:, None]), -127, 127)
+    return {"xq": q.astype(np.int8).ravel(), "xs": d.astype(np.float32),
+            "xsum": q.sum(axis=1).astype(np.int32)}
+
+
+def repack_stream(wq, ws, out, in_, fmt=q4_0):
+    """Row-major {wq, ws} -> the 8-row interleaved stream layout {"wqi", "wsi"}."""
+    lay = _layout.quant_stream_layout({"vector_bits": 256}, fmt)
+    return _layout.repack(lay, wq, ws, out, in_)

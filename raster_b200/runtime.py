@@ -1,0 +1,242 @@
+"""Object layer over the C ABI: context, device buffers, bound weights, graphs, events.
+
+Mirrors the slice of Raster's GPU runtime name table the quantized matmul
+needs (src/raster/gpu/ocl_runtime.clj:405-499 make-buffer / array->buffer! /
+buffer->array / free-buffer!, :1051-1084 record-graph! / replay-graph! /
+destroy-graph!; src/raster/gpu/core.clj:243-293 session lifetime).  Device ids
+follow the reference's keyword convention ``:cuda:N``
+(src/raster/compiler/passes/parallel/device.clj:9-29), written "cuda:N" here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+import numpy as np
+
+from . import _lib as L
+
+
+def _np_ptr(a: np.ndarray):
+    if not a.flags["C_CONTIGUOUS"]:
+        raise ValueError("array must be C-contiguous")
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def parse_device(dev) -> int:
+    """'cuda:N' / ':cuda:N' / N -> CUDA ordinal."""
+    if isinstance(dev, int):
+        return dev
+    s = str(dev).lstrip(":")
+    kind, _, idx = s.partition(":")
+    if kind != "cuda":
+        raise ValueError(f"unknown backend {dev!r}: only cuda:N devices exist here")
+    return int(idx or 0)
+
+
+class DeviceBuffer:
+    """make-buffer: {:segment :n-elements :byte-size :dtype} on a CUDA device."""
+
+    def __init__(self, ctx: "Context", n: int, dtype, dev: int = 0):
+        self.ctx, self.dtype, self.n_elements, self.dev = ctx, np.dtype(dtype), int(n), dev
+        self.byte_size = self.n_elements * self.dtype.itemsize
+        h = C.c_void_p()
+        L.check(ctx.lib.rstq_alloc(ctx.handle, C.byref(h), dev, max(self.byte_size, 1)))
+        self.handle = h
+
+    def upload(self, arr) -> "DeviceBuffer":
+        a = np.ascontiguousarray(arr)
+        if a.nbytes > self.byte_size:
+            raise ValueError("array larger than buffer")
+        L.check(self.ctx.lib.rstq_upload(self.handle, _np_ptr(a), 0, a.nbytes))
+        return self
+
+    def download(self, dtype=None, n=None) -> np.ndarray:
+        dt = np.dtype(dtype or self.dtype)
+        n = self.byte_size // dt.itemsize if n is None else n
+        out = np.empty(n, dtype=dt)
+        L.check(self.ctx.lib.rstq_download(self.handle, _np_ptr(out), 0, out.nbytes))
+        return out
+
+    def fill_bytes(self, value: int = 0) -> None:
+        L.check(self.ctx.lib.rstq_memset(self.handle, value, 0, self.byte_size))
+
+    @property
+    def device_ptr(self) -> int:
+        p, n = C.c_void_p(), C.c_int64()
+        L.check(self.ctx.lib.rstq_buf_ptr(self.handle, C.byref(p), C.byref(n)))
+        return p.value
+
+    def free(self) -> None:
+        if self.handle:
+            self.ctx.lib.rstq_free(self.handle)
+            self.handle = None
+
+
+class QWeight:
+    """A weight matrix bound to one device in the kernels' tiling."""
+
+    def __init__(self, ctx, handle, keep=()):
+        self.ctx, self.handle, self._keep = ctx, handle, keep
+        info = (C.c_int64 * 6)()
+        L.check(ctx.lib.rstq_weight_info(handle, info))
+        self.out, self.in_, self.bits, self.device_bytes, self.stream_bytes, self.dev = list(info)
+
+    def clone(self) -> "QWeight":
+        h = C.c_void_p()
+        L.check(self.ctx.lib.rstq_weight_clone(self.handle, C.byref(h)))
+        return QWeight(self.ctx, h)
+
+    def free(self) -> None:
+        if self.handle:
+            self.ctx.lib.rstq_weight_free(self.handle)
+            self.handle = None
+
+
+class Graph:
+    def __init__(self, ctx, handle):
+        self.ctx, self.handle = ctx, handle
+
+    def replay(self) -> None:
+        L.check(self.ctx.lib.rstq_graph_replay(self.handle))
+
+    def destroy(self) -> None:
+        if self.handle:
+            self.ctx.lib.rstq_graph_destroy(self.handle)
+            self.handle = None
+
+
+class Event:
+    def __init__(self, ctx, dev=0):
+        self.ctx = ctx
+        h = C.c_void_p()
+        L.check(ctx.lib.rstq_event_create(ctx.handle, C.byref(h), dev))
+        self.handle = h
+
+    def record(self) -> None:
+        L.check(self.ctx.lib.rstq_event_record(self.handle))
+
+    def elapsed_ms(self, stop: "Event") -> float:
+        ms = C.c_float()
+        L.check(self.ctx.lib.rstq_event_elapsed_ms(self.handle, stop.handle, C.byref(ms)))
+        return float(ms.value)
+
+    def destroy(self) -> None:
+        if self.handle:
+            self.ctx.lib.rstq_event_destroy(self.handle)
+            self.handle = None
+
+
+class Context:
+    """make-session for cuda:N devices; close() frees everything it still owns."""
+
+    def __init__(self, devices=("cuda:0",)):
+        self.lib = L.load()
+        if isinstance(devices, (str, int)):
+            devices = (devices,)
+        ords = [parse_device(d) for d in devices]
+        arr = (C.c_int32 * len(ords))(*ords)
+        h = C.c_void_p()
+        L.check(self.lib.rstq_init(arr, len(ords), C.byref(h)))
+        self.handle = h
+        self.devices = ords
+
+    # -- buffers ---------------------------------------------------------
+    def make_buffer(self, n, dtype, dev=0) -> DeviceBuffer:
+        return DeviceBuffer(self, n, dtype, dev)
+
+    def array_to_buffer(self, arr, dev=0) -> DeviceBuffer:
+        a = np.ascontiguousarray(arr)
+        return DeviceBuffer(self, a.size, a.dtype, dev).upload(a)
+
+    # -- weights ---------------------------------------------------------
+    def bind_weight(self, codes, scales, out, in_, fmt, layout, dev=0, split=L.SPLIT_NONE,
+                    rank=0, nranks=1) -> QWeight:
+        codes = np.ascontiguousarray(codes)
+        scales = np.ascontiguousarray(scales, dtype=np.float32)
+        h = C.c_void_p()
+        if split == L.SPLIT_NONE:
+            rc = self.lib.rstq_weight_bind(self.handle, C.byref(h), _np_ptr(codes), _np_ptr(scales),
+                                           dev, out, in_, fmt, layout)
+        else:
+            rc = self.lib.rstq_weight_bind_shard(self.handle, C.byref(h), _np_ptr(codes),
+                                                 _np_ptr(scales), dev, out, in_, fmt, layout,
+                                                 split, rank, nranks)
+        L.check(rc)
+        return QWeight(self, h)
+
+    # -- ops on device-resident data ----------------------------------------
+    def quant_act_i8(self, x: DeviceBuffer, xq, xs, xsum, M, in_) -> None:
+        L.check(self.lib.rstq_quant_act_i8(self.handle, x.handle, xq.handle, xs.handle,
+                                           xsum.handle if xsum is not None else None, M, in_))
+
+    def qmatmul(self, w: QWeight, x: DeviceBuffer, y: DeviceBuffer, M=1, act_dtype=L.F32,
+                out_dtype=L.F32, mode=L.MODE_A8) -> None:
+        L.check(self.lib.rstq_qmatmul(self.handle, w.handle, x.handle, y.handle, M, act_dtype,
+                                      out_dtype, mode))
+
+    def qmatmul_prequant(self, w: QWeight, xq, xs, xsum, y, M=1) -> None:
+        L.check(self.lib.rstq_qmatmul_prequant(self.handle, w.handle, xq.handle, xs.handle,
+                                               xsum.handle if xsum is not None else None,
+                                               y.handle, M))
+
+    def qmatmul_host(self, w: QWeight, x, M=1, act_dtype=L.F32, mode=L.MODE_A8) -> np.ndarray:
+        x = np.ascontiguousarray(x)
+        y = np.empty(M * w.out, dtype=np.float32)
+        L.check(self.lib.rstq_qmatmul_host(self.handle, w.handle, _np_ptr(x), _np_ptr(y), M,
+                                           act_dtype, mode))
+        return y.reshape(M, w.out)
+
+    # -- graphs / events / misc ------------------------------------------------
+    def graph_begin(self, dev=0) -> None:
+        L.check(self.lib.rstq_graph_begin(self.handle, dev))
+
+    def graph_end(self, dev=0) -> Graph:
+        h = C.c_void_p()
+        L.check(self.lib.rstq_graph_end(self.handle, C.byref(h), dev))
+        return Graph(self, h)
+
+    def event(self, dev=0) -> Event:
+        return Event(self, dev)
+
+    def sync(self, dev=0) -> None:
+        L.check(self.lib.rstq_sync(self.handle, dev))
+
+    def tune(self, key, value) -> None:
+        L.check(self.lib.rstq_tune(self.handle, key, value))
+
+    def device_info(self, dev=0) -> dict:
+        v = (C.c_int64 * 4)()
+        L.check(self.lib.rstq_device_info(self.handle, dev, v))
+        return {"sm_count": v[0], "l2_bytes": v[1], "total_mem": v[2], "cc": v[3]}
+
+    def launch_count(self) -> int:
+        n = C.c_int64()
+        L.check(self.lib.rstq_launch_count(self.handle, C.byref(n)))
+        return int(n.value)
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.rstq_shutdown(self.handle)
+            self.handle = None
+
+
+_default = None
+_default_lock = threading.Lock()
+
+
+def default_context() -> Context:
+    """The process-wide context the reference-named operators run on (cuda:0)."""
+    global _default
+    with _default_lock:
+        if _default is None:
+            _default = Context(("cuda:0",))
+        return _default
+
+
+def close_default_context() -> None:
+    global _default
+    with _default_lock:
+        if _default is not None:
+            _default.close()
+            _default = None

@@ -1,0 +1,62 @@
+"""The C-ABI library loads without a GPU and exports every symbol rstq.h declares."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from raster_b200 import _lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    for f in os.listdir(os.path.join(ROOT, "include")):
+        if f.endswith(".h"):
+            text = open(os.path.join(ROOT, "include", f)).read()
+            names |= set(re.findall(r"RSTQ_API\s+[\w\s\*]+?\b(rstq_\w+)\s*\(", text))
+    return names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = L.load()
+    names = declared_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/ but not exported"
+    assert names == set(L.SIGNATURES), names ^ set(L.SIGNATURES)
+
+
+def test_version_and_error_string():
+    lib = L.load()
+    assert lib.rstq_version() >= 100
+    assert isinstance(lib.rstq_last_error(), bytes)
+
+
+def test_null_and_bad_handles_are_status_codes_not_crashes():
+    lib = L.load()
+    assert lib.rstq_shutdown(None) == L.OK
+    assert lib.rstq_free(None) == L.OK
+    assert lib.rstq_weight_free(None) == L.OK
+    assert lib.rstq_graph_destroy(None) == L.OK
+    assert lib.rstq_event_destroy(None) == L.OK
+    assert lib.rstq_sync(None, 0) == L.E_INVALID
+    assert lib.rstq_init(None, 1, None) == L.E_INVALID
+    h = C.c_void_p()
+    assert lib.rstq_init(None, 0, C.byref(h)) == L.E_INVALID
+    assert lib.rstq_alloc(None, C.byref(h), 0, 16) == L.E_INVALID
+    assert b"context" in lib.rstq_last_error()
+
+
+@pytest.mark.skipif(os.path.exists("/dev/nvidia0"), reason="a GPU is present")
+def test_init_without_gpu_fails_loudly():
+    lib = L.load()
+    devs = (C.c_int32 * 1)(0)
+    h = C.c_void_p()
+    assert lib.rstq_init(devs, 1, C.byref(h)) == L.E_NODEV
+    assert not h.value
+    assert b"no CPU path" in lib.rstq_last_error()
+    from raster_b200 import Context
+    with pytest.raises(L.RstqError):
+        Context()

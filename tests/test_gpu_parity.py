@@ -1,0 +1,369 @@
+"""Parity of the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bar: bit-exact for the integer work (activation codes, scales, block sums, the
+pure int8 dot); for floating point the tolerances below, measured as
+max|y - y_ref| / max|y_ref| (the reference's own metric,
+test/raster/dl/decoder_layer_gpu_test.clj:17):
+  A8 mode (f32 fold of exact integer block dots)      <= 2e-6
+  F mode, f32 activations                              <= 1e-5 (M <= 2), 2e-5 otherwise
+  F mode, bf16 activations (exact products, f32 sums)  <= 2e-6
+  bf16 outputs: per element <= 2^-8 |y_ref| + 1e-3 max|y_ref|
+all far inside the 1e-3 the task allows for f32 accumulation.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from raster_b200 import _lib as L
+from raster_b200 import synth
+from raster_b200.quant import core as qcore
+from raster_b200.quant import cpu_quant as cq
+from raster_b200.quant import kernels_k, op, pack, train
+
+pytestmark = pytest.mark.gpu
+
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "qmatmul_small.npz"))
+TOL_A8 = 2e-6
+TOL_F = 2e-5
+FMT = {4: (cq.q4_0, L.FMT_Q4_0, 0), 8: (cq.q8_0, L.FMT_Q8_0, 1)}
+
+
+def relerr(y, ref):
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.abs(np.asarray(y, dtype=np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def make_weight(out, in_, bits, seed=1, sigma=0.02):
+    w = synth.normal(seed, out * in_, sigma)
+    wq, ws = orc.quantize_weight(w, bits)
+    return w, wq, ws
+
+
+# ---------------------------------------------------------------- activation quantizer
+@pytest.mark.parametrize("M,in_", [(1, 32), (1, 4096), (3, 160), (8, 11008), (64, 256)])
+def test_quant_act_i8_bit_exact(ctx, M, in_):
+    x = synth.normal(40 + M, M * in_)
+    if in_ >= 160:
+        x[:32] = 0.0
+        x[32:64] = np.float32(1e-30)
+        x[64] = np.float32(1e30)
+        x[100] = np.float32(-1e30)
+    bx = ctx.array_to_buffer(x)
+    bq, bs, bsum = (ctx.make_buffer(M * in_, np.int8), ctx.make_buffer(M * in_ // 32, np.float32),
+                    ctx.make_buffer(M * in_ // 32, np.int32))
+    ctx.quant_act_i8(bx, bq, bs, bsum, M, in_)
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    assert np.array_equal(bq.download(), xq)
+    assert np.array_equal(bs.download().view(np.uint32), xs.view(np.uint32))
+    assert np.array_equal(bsum.download(), xsum)
+    for b in (bx, bq, bs, bsum):
+        b.free()
+
+
+def test_quant_act_rounding_ties_go_up(ctx):
+    # block max 127 -> d = 1, id = 1: codes are round_half_up(x)
+    x = np.zeros(32, np.float32)
+    x[0] = 127.0
+    x[1:7] = [0.5, 1.5, 2.5, -0.5, -1.5, -2.5]
+    xp, xs = kernels_k.quant_act_i8_rows_gpu(x, 32, 1, ctx)
+    q = xp.view(np.int8)
+    assert list(q[:7]) == [127, 1, 2, 3, 0, -1, -2] and xs[0] == 1.0
+
+
+# ---------------------------------------------------------------- decode kernels, A8
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("out,in_,M", [
+    (8, 32, 1), (72, 160, 3), (40, 96, 1), (33, 64, 2), (4096, 4096, 1), (1000, 2048, 4),
+    (256, 11008, 8), (512, 1024, 9), (64, 512, 16), (96, 256, 19), (8192, 512, 1)])
+def test_gemv_a8_matches_oracle(ctx, bits, out, in_, M):
+    fmt_desc, fmt, ofmt = FMT[bits]
+    _, wq, ws = make_weight(out, in_, bits, seed=out + in_)
+    x = synth.normal(out + 2 * in_ + M, M * in_)
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    ref = orc.matmul_a8_f64(wq, ws, ofmt, xq, xs, xsum, M, in_, out)
+    assert relerr(y, ref) <= TOL_A8
+    w.free()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_prequant_entry_matches_reference_kernel_signature(ctx, bits):
+    """(xq xs xsum w y in out) of qmatmul-q4-x8! / qmatmul-q8-x8!, stream-layout weight."""
+    fmt_desc, fmt, ofmt = FMT[bits]
+    out, in_ = 264, 640
+    _, wq, ws = make_weight(out, in_, bits, seed=9)
+    wqi, wsi = orc.repack_stream(wq, ws, out, in_, bits, 8)
+    x = synth.normal(10, in_)
+    xq, xs, xsum = orc.quantize_act_i8(x, 1, in_)
+    w = ctx.bind_weight(wqi, wsi, out, in_, fmt, L.LAYOUT_STREAM8)
+    bq, bs, bsum = ctx.array_to_buffer(xq), ctx.array_to_buffer(xs), ctx.array_to_buffer(xsum)
+    by = ctx.make_buffer(out, np.float32)
+    ctx.qmatmul_prequant(w, bq, bs, bsum, by, 1)
+    y = by.download()
+    ref = orc.qmatmul_x8(xq, xs, xsum, wqi, wsi, in_, out, bits)
+    # the reference kernel itself rounds to f32 after every block: compare at its precision
+    assert relerr(y, ref) <= 4e-6
+    assert relerr(y, orc.matmul_a8_f64(wq, ws, ofmt, xq, xs, xsum, 1, in_, out)) <= TOL_A8
+    for b in (bq, bs, bsum, by):
+        b.free()
+    w.free()
+
+
+# ---------------------------------------------------------------- the operators (host arrays)
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("in_,out", [(256, 64), (512, 128), (4096, 512), (4096, 4096)])
+def test_qlinear_i8_operator(ctx, bits, in_, out):
+    """Shapes of test/raster/quant/x8_simd_test.clj:17-33 plus BASELINE config 1."""
+    _, wq, ws = make_weight(out, in_, bits, seed=in_ + out)
+    wqi, wsi = orc.repack_stream(wq, ws, out, in_, bits, 8)
+    x = synth.normal(77, in_)
+    fn = op.qlinear_i8 if bits == 4 else op.qlinear_i8_q8
+    y = fn(x, wqi, wsi, in_, out, ctx)
+    ref = orc.qlinear_i8(x, wqi, wsi, in_, out, bits)
+    assert np.abs(y - ref).max() < 1e-3                     # the reference's own gate
+    assert relerr(y, ref) <= 4e-6
+    # in-place form fully overwrites y
+    y2 = np.full(out, np.nan, dtype=np.float32)
+    into = op.qlinear_i8_into if bits == 4 else op.qlinear_i8_q8_into
+    assert into(x, wqi, wsi, y2, in_, out, ctx) is y2
+    assert np.array_equal(y2, y)
+
+
+def test_operators_reproduce_golden_vectors(ctx):
+    out, in_, m = (int(v) for v in G["shape"])
+    x = G["x"]
+    for bits, fn in ((4, op.qlinear_i8), (8, op.qlinear_i8_q8)):
+        y = fn(x[:in_], G[f"wqi{bits}"], G[f"wsi{bits}"], in_, out, ctx)
+        assert relerr(y, G[f"y_qlinear_i8_{bits}"]) <= 4e-6
+        assert relerr(y, G[f"y_a8_f64_{bits}"][0]) <= TOL_A8
+    y = train.qlinear_q8(x, G["codes"], G["scales"], m, in_, out, ctx)
+    assert relerr(y, G["y_qlinear_q8"]) <= TOL_F
+    y = kernels_k.qmatmul_i8_gemm(G["xp"], G["xs_rows"], G["wp"], G["scales"],
+                                  np.empty(m * out, np.float32), in_, out, m, ctx)
+    assert relerr(y, G["y_i8_gemm"]) <= TOL_A8
+
+
+def test_operator_contract_errors(ctx):
+    x = np.zeros(64, np.float32)
+    with pytest.raises(L.RstqError) as e:
+        op.qlinear_i8(x, np.zeros(64, np.uint8), np.zeros(8, np.float32), 30, 8, ctx)
+    assert e.value.code == L.E_SHAPE
+    with pytest.raises(L.RstqError) as e:
+        op.qlinear_i8(x, np.zeros(64, np.uint8), np.zeros(8, np.float32), 64, 4, ctx)
+    assert e.value.code == L.E_SHAPE
+    with pytest.raises(L.RstqError) as e:
+        ctx.bind_weight(np.zeros(16, np.uint8), np.zeros(1, np.float32), 1, 32, 9, L.LAYOUT_ROWMAJOR)
+    assert e.value.code == L.E_INVALID
+    with pytest.raises(L.RstqError) as e:
+        ctx.make_buffer(4, np.float32, dev=3)
+    assert e.value.code == L.E_NODEV
+    b = ctx.make_buffer(4, np.float32)
+    with pytest.raises(L.RstqError) as e:
+        L.check(ctx.lib.rstq_upload(b.handle, np.zeros(8, np.float32).ctypes.data, 0, 32))
+    assert e.value.code == L.E_RANGE
+    b.free()
+
+
+# ---------------------------------------------------------------- decode kernels, F
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("out,in_,M", [
+    (8, 32, 1), (72, 160, 3), (4096, 4096, 1), (1000, 2048, 2), (256, 11008, 4), (512, 1024, 8),
+    (64, 512, 16), (96, 256, 21)])
+def test_gemv_f_f32_activations(ctx, bits, out, in_, M):
+    fmt_desc, fmt, ofmt = FMT[bits]
+    _, wq, ws = make_weight(out, in_, bits, seed=out + in_ + 1)
+    x = synth.normal(3 * out + in_ + M, M * in_)
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_F)
+    ref = orc.matmul_dq_f64(wq, ws, ofmt, x, M, in_, out)
+    assert relerr(y, ref) <= (1e-5 if M <= 2 else TOL_F)
+    w.free()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("out,in_,M", [(72, 160, 1), (4096, 4096, 1), (11008, 4096, 4),
+                                       (4096, 11008, 8), (128, 512, 13)])
+def test_gemv_f_bf16_activations_and_outputs(ctx, bits, out, in_, M):
+    fmt_desc, fmt, ofmt = FMT[bits]
+    _, wq, ws = make_weight(out, in_, bits, seed=out + in_ + 2)
+    xb = synth.to_bf16_bits(synth.normal(5 * out + in_ + M, M * in_))
+    xr = synth.from_bf16_bits(xb)                      # the exact values the kernel sees
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    ref = orc.matmul_dq_f64(wq, ws, ofmt, xr, M, in_, out)
+    y = ctx.qmatmul_host(w, xb, M, L.BF16, L.MODE_F)
+    assert relerr(y, ref) <= TOL_A8
+    # bf16 output through the device-resident entry
+    bx, by = ctx.array_to_buffer(xb), ctx.make_buffer(M * out, np.uint16)
+    ctx.qmatmul(w, bx, by, M, L.BF16, L.BF16, L.MODE_F)
+    yb = synth.from_bf16_bits(by.download()).reshape(M, out)
+    bound = 2.0 ** -8 * np.abs(ref) + 1e-3 * np.abs(ref).max()
+    assert np.all(np.abs(yb - ref) <= bound)
+    bx.free(), by.free(), w.free()
+
+
+@pytest.mark.parametrize("m,in_,out", [(3, 64, 8), (1, 4096, 4096), (5, 256, 72), (16, 512, 96), (40, 128, 64)])
+def test_qlinear_q8_operator(ctx, m, in_, out):
+    """W8A32 with an M dimension (first shape is the reference's own test shape)."""
+    W = synth.normal(in_ + out, out * in_, 0.2)
+    x = synth.normal(in_ + out + 1, m * in_)
+    q = train.q8_quantize(W, out, in_)
+    y = train.qlinear_q8(x, q["codes"], q["scales"], m, in_, out, ctx)
+    ref = orc.qlinear_q8(x, q["codes"], q["scales"], m, in_, out)
+    assert relerr(y, ref) <= TOL_F
+    dense = x.reshape(m, in_).astype(np.float64) @ \
+        train.dequant_q8_dense(q["codes"], q["scales"], in_, out).reshape(out, in_).astype(np.float64).T
+    assert relerr(y.reshape(m, out), dense) <= TOL_F
+
+
+# ---------------------------------------------------------------- int32-packed kernels
+def test_i8gemv_dp4a_exact(ctx):
+    out, in_ = 16, 256
+    rng = np.random.default_rng(7)
+    W = rng.integers(-128, 128, out * in_, dtype=np.int8)
+    x = rng.integers(-128, 128, in_, dtype=np.int8)
+    y = kernels_k.i8gemv_dp4a(W.view(np.int32), x.view(np.int32), np.empty(out, np.float32),
+                              in_ // 4, out, ctx)
+    ref = W.reshape(out, in_).astype(np.int64) @ x.astype(np.int64)
+    assert np.array_equal(y.astype(np.int64), ref)
+
+
+@pytest.mark.parametrize("nrows,in_,out", [(5, 128, 24), (1, 32, 8), (16, 512, 200), (33, 256, 64)])
+def test_qmatmul_i8_gemm_operator(ctx, nrows, in_, out):
+    W = synth.normal(in_ + out + 3, out * in_, 0.05)
+    X = synth.normal(in_ + out + 4, nrows * in_)
+    p = pack.quantize_one_q8(W, in_, out)
+    xp, xs = kernels_k.quant_act_i8_rows_gpu(X, in_, nrows, ctx)
+    oxp, oxs = orc.quant_act_i8_rows(X, in_, nrows)
+    assert np.array_equal(xp, oxp) and np.array_equal(xs, oxs)
+    y = kernels_k.qmatmul_i8_gemm(xp, xs, p["wp"], p["ws"], np.empty(nrows * out, np.float32),
+                                  in_, out, nrows, ctx)
+    ref = orc.qmatmul_i8_gemm(oxp, oxs, p["wp"], p["ws"], in_, out, nrows)
+    assert relerr(y, ref) <= TOL_A8
+
+
+# ---------------------------------------------------------------- registry
+def test_format_registry(ctx):
+    rows, cols = 64, 256
+    W = synth.normal(12, rows * cols, 0.02)
+    x = synth.normal(13, cols)
+    assert {"q4_0", "q8_0"} <= set(qcore.registered_formats())
+    for name, bits in (("q4_0", 4), ("q8_0", 8)):
+        qm = qcore.qmatrix(name, W, rows, cols)
+        y = qcore.matmul(qm, x)
+        xq, xs, xsum = orc.quantize_act_i8(x, 1, cols)
+        ref = orc.qmatmul_composable(xq, xs, xsum, qm.data["wq"], qm.data["ws"], cols, rows, bits)
+        assert relerr(y, ref) <= 4e-6
+        qm.data["bound"].free()
+    with pytest.raises(KeyError):
+        qcore.qmatrix("q5_1", W, rows, cols)
+    qcore.register_quant("twice", {"descriptor": {}, "quantize": lambda W, r, c: {"W": W},
+                                   "apply": lambda qm, x: 2 * np.asarray(x)})
+    assert np.array_equal(qcore.matmul(qcore.qmatrix("twice", W, rows, cols), x), 2 * x)
+
+
+# ---------------------------------------------------------------- edge cases & properties
+@pytest.mark.parametrize("bits", [4, 8])
+def test_zero_inputs_give_exact_zeros(ctx, bits):
+    fmt_desc, fmt, _ = FMT[bits]
+    out, in_ = 40, 128
+    _, wq, ws = make_weight(out, in_, bits, seed=3)
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    for mode in (L.MODE_A8, L.MODE_F):
+        assert not ctx.qmatmul_host(w, np.zeros(in_, np.float32), 1, L.F32, mode).any()
+    w.free()
+    wq0, ws0 = orc.quantize_weight(np.zeros(out * in_, np.float32), bits)
+    w0 = ctx.bind_weight(wq0, ws0, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    assert not ctx.qmatmul_host(w0, synth.normal(4, in_), 1, L.F32, L.MODE_A8).any()
+    w0.free()
+
+
+def test_forced_split_k_values_agree(ctx):
+    out, in_ = 4096, 11008
+    _, wq, ws = make_weight(out, in_, 4, seed=21)
+    x = synth.normal(22, in_)
+    w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    xq, xs, xsum = orc.quantize_act_i8(x, 1, in_)
+    ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, 1, in_, out)
+    try:
+        for S in (1, 2, 5, 8, 11, 21):
+            ctx.tune(L.TUNE_SPLITK, S)
+            y1 = ctx.qmatmul_host(w, x, 1, L.F32, L.MODE_A8)
+            y2 = ctx.qmatmul_host(w, x, 1, L.F32, L.MODE_A8)
+            assert relerr(y1, ref) <= TOL_A8
+            assert np.array_equal(y1, y2)          # run-to-run bit-reproducible
+    finally:
+        ctx.tune(L.TUNE_SPLITK, 0)
+    w.free()
+
+
+def test_full_size_linearity_and_split_properties(ctx):
+    """BASELINE config 2 shape: size-independent properties instead of a full oracle pass."""
+    out, in_ = 11008, 4096
+    _, wq, ws = make_weight(out, in_, 4, seed=31)
+    w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    x1 = synth.from_bf16_bits(synth.to_bf16_bits(synth.normal(32, in_)))
+    x2 = synth.from_bf16_bits(synth.to_bf16_bits(synth.normal(33, in_)))
+    y1 = ctx.qmatmul_host(w, x1, 1, L.F32, L.MODE_F)[0].astype(np.float64)
+    y2 = ctx.qmatmul_host(w, x2, 1, L.F32, L.MODE_F)[0].astype(np.float64)
+    y12 = ctx.qmatmul_host(w, (x1 + x2).astype(np.float32), 1, L.F32, L.MODE_F)[0]
+    assert relerr(y12, y1 + y2) <= 1e-5                                   # linear in x (F mode)
+    ym = ctx.qmatmul_host(w, np.concatenate([x1, x2]), 2, L.F32, L.MODE_F)
+    assert relerr(ym[0], y1) <= 1e-5 and relerr(ym[1], y2) <= 1e-5         # rows independent
+    # oracle on a sample of rows
+    rows = np.arange(0, out, 97)
+    ref = orc.matmul_dq_f64(np.ascontiguousarray(wq.reshape(out, -1)[rows]).ravel(),
+                            np.ascontiguousarray(ws.reshape(out, -1)[rows]).ravel(), 0, x1, 1, in_, rows.size)
+    assert relerr(y1[rows], ref[0]) <= 1e-5
+    # column split: shards concatenate to the full result, bit for bit (A8)
+    ya = ctx.qmatmul_host(w, x1, 1, L.F32, L.MODE_A8)[0]
+    parts = []
+    for r in range(4):
+        ws_ = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR, 0, L.SPLIT_COLUMN, r, 4)
+        assert ws_.out == out // 4
+        parts.append(ctx.qmatmul_host(ws_, x1, 1, L.F32, L.MODE_A8)[0])
+        ws_.free()
+    assert relerr(np.concatenate(parts), ya) <= TOL_A8
+    # row split: partials sum to the full result
+    acc = np.zeros(out, np.float64)
+    for r in range(4):
+        ws_ = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR, 0, L.SPLIT_ROW, r, 4)
+        assert ws_.in_ == in_ // 4
+        acc += ctx.qmatmul_host(ws_, x1[r * in_ // 4:(r + 1) * in_ // 4], 1, L.F32, L.MODE_A8)[0]
+        ws_.free()
+    assert relerr(acc, ya) <= 4e-6
+    w.free()
+
+
+def test_graph_replay_is_idempotent_and_clone_is_equal(ctx):
+    out, in_ = 1024, 2048
+    _, wq, ws = make_weight(out, in_, 4, seed=41)
+    w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    w2 = w.clone()
+    x = synth.normal(42, in_)
+    bx = ctx.array_to_buffer(x)
+    by, by2 = ctx.make_buffer(out, np.float32), ctx.make_buffer(out, np.float32)
+    ctx.qmatmul(w, bx, by, 1)                     # warm (scratch sized before capture)
+    ctx.graph_begin()
+    ctx.qmatmul(w, bx, by, 1)
+    ctx.qmatmul(w2, bx, by2, 1)
+    g = ctx.graph_end()
+    n0 = ctx.launch_count()
+    by.fill_bytes(0xFF), by2.fill_bytes(0xFF)
+    g.replay()
+    ctx.sync()
+    first = by.download()
+    assert ctx.launch_count() - n0 == 4           # 2 x (quantize + gemv)
+    assert np.array_equal(first, by2.download())
+    g.replay(), g.replay()
+    ctx.sync()
+    assert np.array_equal(first, by.download())
+    assert relerr(first, ctx.qmatmul_host(w, x, 1)[0]) == 0.0
+    with pytest.raises(L.RstqError):
+        ctx.graph_end()                            # no capture in progress
+    g.destroy()
+    for b in (bx, by, by2):
+        b.free()
+    w.free(), w2.free()
