@@ -256,7 +256,7 @@ def run_ours(args):
         alg = sum(algorithmic_bytes(w["out"], w["in"], 1) for w in weights) / len(weights)
         avg_launch_s = ms_gemv * 1e-3 / launches
         achieved = alg / avg_launch_s / 1e9
-        roofline = {"bound": "hbm", "kernel": "gemv_a8_kernel<4,1,true>", "achieved": round(achieved, 1),
+        roofline = {"bound": "hbm", "kernel": "gemv_stream_kernel<4,1,A8,onecol>", "achieved": round(achieved, 1),
                     "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s",
                     "frac": round(achieved / hbm_peak, 4), "frac_of_nominal_8TBs": round(achieved / 8000.0, 4),
                     "traffic": None, "avg_launch_us": round(avg_launch_s * 1e6, 3),
@@ -420,13 +420,55 @@ def run_reference(args):
     }))
 
 
+def run_case(args):
+    """One small named case for profiler captures: a few launches of one decode kernel on
+    distinct weight copies (more than L2 in total), nothing else.
+    --case gemv:<bits>:<out>:<in>:<M>:<a8|f>"""
+    from raster_b200 import Context
+    from raster_b200 import _lib as L
+    from raster_b200.quant import cpu_quant as cq
+    _, bits, out, in_, M, mode = args.case.split(":")
+    bits, out, in_, M = int(bits), int(out), int(in_), int(M)
+    rng = np.random.default_rng(0)
+    ctx = Context(("cuda:0",))
+    nb = in_ // 32
+    codes = rng.integers(0, 256, out * in_ * bits // 8, dtype=np.uint8)
+    scales = (rng.standard_normal(out * nb) * 0.01).astype(np.float32)
+    w0 = ctx.bind_weight(codes, scales, out, in_, L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0,
+                         L.LAYOUT_ROWMAJOR)
+    R = max(2, -(-int(1.2 * ctx.device_info()["l2_bytes"]) // w0.stream_bytes))
+    ws = [w0] + [w0.clone() for _ in range(R - 1)]
+    x = rng.standard_normal(M * in_).astype(np.float32)
+    a = cq.quantize_act_i8(x, M, in_)
+    bq, bs, bsum = (ctx.array_to_buffer(a["xq"]), ctx.array_to_buffer(a["xs"]),
+                    ctx.array_to_buffer(a["xsum"]))
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    e0, e1 = ctx.event(), ctx.event()
+    for it in range(2):
+        e0.record()
+        for w in ws:
+            if mode == "a8":
+                ctx.qmatmul_prequant(w, bq, bs, bsum, by, M)
+            else:
+                ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_F)
+        e1.record()
+        ctx.sync()
+    us = e0.elapsed_ms(e1) * 1e3 / R
+    print(json.dumps({"case": args.case, "launches": 2 * R, "us_per_launch": round(us, 2),
+                      "GBs": round(w0.stream_bytes / us / 1e3, 1)}))
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default=None, help="small single-kernel case for profiler captures")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)

@@ -53,6 +53,8 @@ typedef struct rstq_event rstq_event;
 #define RSTQ_E_STATE (-9)    /* call not legal now (e.g. sync during capture) */
 #define RSTQ_E_LIMIT (-10)   /* problem exceeds a stated fixed limit          */
 #define RSTQ_E_RANGE (-11)   /* offset + bytes beyond the buffer              */
+#define RSTQ_E_WAIT (-12)    /* a time-bounded wait inside a kernel ran out; results of that
+                                launch are invalid (reported by rstq_sync)     */
 
 /* weight formats (the `format` argument of rstq_weight_bind) */
 #define RSTQ_FMT_Q4_0 0 /* unsigned nibble, zero point 8, two per byte (lo = elem k, hi = elem k+16);
@@ -81,8 +83,8 @@ typedef struct rstq_event rstq_event;
 #define RSTQ_SPLIT_ROW 2    /* rank owns K range   [rank*in/P,  (rank+1)*in/P) of every row */
 
 /* tuning keys (rstq_tune) */
-#define RSTQ_TUNE_SPLITK 0      /* 0 = automatic, n > 0 = force n K-slices in the decode kernels */
 #define RSTQ_TUNE_GEMM_MIN_M 1  /* smallest M routed to the tensor-core GEMM (default 17) */
+#define RSTQ_TUNE_TIMELINE 3      /* 1 = streaming kernel records per-CTA phase timestamps */
 
 /* ---- library / errors -------------------------------------------------- */
 RSTQ_API int32_t rstq_version(void);
@@ -99,6 +101,10 @@ RSTQ_API int32_t rstq_sync(rstq_ctx* ctx, int32_t dev);
 RSTQ_API int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value);
 /* out[0] = SM count, out[1] = L2 bytes, out[2] = total device memory, out[3] = cc major*10+minor */
 RSTQ_API int32_t rstq_device_info(rstq_ctx* ctx, int32_t dev, int64_t* out4);
+/* Phase timestamps (ns, device global timer) of the last streaming decode launch, 8 per CTA:
+ * [0] entry, [1] consumers start, [2] activations staged, [3] first weights landed,
+ * [4] main loop done, [5] exit.  Filled only while RSTQ_TUNE_TIMELINE is 1. */
+RSTQ_API int32_t rstq_timeline_read(rstq_ctx* ctx, int32_t dev, int64_t* out, int64_t n);
 
 /* ---- device buffers: make-buffer / array->buffer! / buffer->array /
  *      free-buffer! of src/raster/gpu/ocl_runtime.clj:405-499. ----------- */

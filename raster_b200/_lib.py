@@ -23,6 +23,7 @@ SIGNATURES = {
     "rstq_sync": [vp, i32],
     "rstq_tune": [vp, i32, i64],
     "rstq_device_info": [vp, i32, C.POINTER(i64)],
+    "rstq_timeline_read": [vp, i32, C.POINTER(i64), i64],
     "rstq_alloc": [vp, pp, i32, i64],
     "rstq_free": [vp],
     "rstq_upload": [vp, vp, i64, i64],
@@ -60,12 +61,13 @@ _RESTYPE = {"rstq_last_error": C.c_char_p}
 OK = 0
 E_INVALID, E_SHAPE, E_ALIGN, E_CUDA, E_OOM, E_NODEV, E_ARCH, E_DEVICE, E_STATE, E_LIMIT, E_RANGE = (
     -1, -2, -3, -4, -5, -6, -7, -8, -9, -10, -11)
+E_WAIT = -12
 FMT_Q4_0, FMT_Q8_0, FMT_Q8_S = 0, 1, 2
 LAYOUT_ROWMAJOR, LAYOUT_STREAM8 = 0, 1
 F32, BF16 = 0, 1
 MODE_F, MODE_A8 = 0, 1
 SPLIT_NONE, SPLIT_COLUMN, SPLIT_ROW = 0, 1, 2
-TUNE_SPLITK, TUNE_GEMM_MIN_M = 0, 1
+TUNE_GEMM_MIN_M, TUNE_TIMELINE = 1, 3
 
 
 class RstqError(RuntimeError):

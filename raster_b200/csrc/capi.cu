@@ -124,29 +124,14 @@ static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* o
 // One matmul over device pointers, M split into decode-kernel chunks.
 static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs,
                       const int32_t* xsum, float* y, int64_t M) {
-    DeviceState& ds = ctx->devs[w->dev];
-    for (int64_t m0 = 0; m0 < M; m0 += kGemvMaxM) {
-        const int64_t mc = M - m0 < kGemvMaxM ? M - m0 : kGemvMaxM;
-        GemvA8Args a{w->data, xq + m0 * w->in, xs + m0 * w->nb, xsum + m0 * w->nb,
-                     y + m0 * w->out, mc, w->in, w->out, w->bits, w->zp};
-        int32_t rc = launch_gemv_a8(ctx, ds, a);
-        if (rc != RSTQ_OK) return rc;
-    }
-    return RSTQ_OK;
+    GemvA8Args a{w->data, xq, xs, xsum, y, M, w->in, w->out, w->bits, w->zp};
+    return launch_gemv_a8(ctx, ctx->devs[w->dev], a);
 }
 
 static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
                      int act_dtype, int out_dtype) {
-    DeviceState& ds = ctx->devs[w->dev];
-    const int64_t xe = act_dtype == RSTQ_F32 ? 4 : 2, ye = out_dtype == RSTQ_F32 ? 4 : 2;
-    for (int64_t m0 = 0; m0 < M; m0 += kGemvMaxM) {
-        const int64_t mc = M - m0 < kGemvMaxM ? M - m0 : kGemvMaxM;
-        GemvFArgs a{w->data, (const char*)x + m0 * w->in * xe, (char*)y + m0 * w->out * ye,
-                    mc, w->in, w->out, w->bits, w->zp, act_dtype, out_dtype};
-        int32_t rc = launch_gemv_f(ctx, ds, a);
-        if (rc != RSTQ_OK) return rc;
-    }
-    return RSTQ_OK;
+    GemvFArgs a{w->data, x, y, M, w->in, w->out, w->bits, w->zp, act_dtype, out_dtype};
+    return launch_gemv_f(ctx, ctx->devs[w->dev], a);
 }
 
 static int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
@@ -321,6 +306,9 @@ int32_t rstq_init(const int32_t* devices, int32_t ndev, rstq_ctx** ctxp) {
             ds.counters_len = 1 << 18;
             RSTQ_CUDA(cudaMalloc((void**)&ds.counters, (size_t)ds.counters_len * 4));
             RSTQ_CUDA(cudaMemsetAsync(ds.counters, 0, (size_t)ds.counters_len * 4, ds.stream));
+            RSTQ_CUDA(cudaMalloc((void**)&ds.dbg_store, 1024 * 8 * 8));
+            RSTQ_CUDA(cudaMalloc((void**)&ds.status, 256));
+            RSTQ_CUDA(cudaMemsetAsync(ds.status, 0, 256, ds.stream));
             int32_t r = gemv_configure(ds);
             if (r != RSTQ_OK) return r;
             RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
@@ -360,6 +348,8 @@ int32_t rstq_shutdown(rstq_ctx* ctx) {
         if (ds.act_scratch) cudaFree(ds.act_scratch);
         if (ds.partials) cudaFree(ds.partials);
         if (ds.counters) cudaFree(ds.counters);
+        if (ds.status) cudaFree(ds.status);
+        if (ds.dbg_store) cudaFree(ds.dbg_store);
         if (ds.io_dev) cudaFree(ds.io_dev);
         if (ds.pinned) cudaFreeHost(ds.pinned);
         if (ds.stream) cudaStreamDestroy(ds.stream);
@@ -376,16 +366,26 @@ int32_t rstq_sync(rstq_ctx* ctx, int32_t dev) {
     RSTQ_REQUIRE(!ctx->devs[dev].capturing, RSTQ_E_STATE, "cannot synchronise during capture");
     int32_t rc = use_dev(ctx, dev);
     if (rc != RSTQ_OK) return rc;
-    RSTQ_CUDA(cudaStreamSynchronize(ctx->devs[dev].stream));
+    DeviceState& ds = ctx->devs[dev];
+    int st = 0;
+    RSTQ_CUDA(cudaMemcpyAsync(&st, ds.status, 4, cudaMemcpyDeviceToHost, ds.stream));
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    if (st != 0) {
+        // the flag is sticky until read: clear it so the context stays usable
+        RSTQ_CUDA(cudaMemsetAsync(ds.status, 0, 4, ds.stream));
+        RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+        set_error("a time-bounded wait inside a kernel ran out (status %d); results since the "
+                  "last rstq_sync are invalid", st);
+        return RSTQ_E_WAIT;
+    }
     return RSTQ_OK;
 }
 
 int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
     CHECK_CTX(ctx);
     switch (key) {
-        case RSTQ_TUNE_SPLITK:
-            RSTQ_REQUIRE(value >= 0 && value <= 4096, RSTQ_E_INVALID, "split-K out of range");
-            ctx->tune_splitk = value;
+        case RSTQ_TUNE_TIMELINE:
+            for (auto& ds : ctx->devs) ds.dbg = value ? ds.dbg_store : nullptr;
             return RSTQ_OK;
         case RSTQ_TUNE_GEMM_MIN_M:
             RSTQ_REQUIRE(value >= 1, RSTQ_E_INVALID, "threshold must be >= 1");
@@ -395,6 +395,18 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
             set_error("unknown tuning key %d", key);
             return RSTQ_E_INVALID;
     }
+}
+
+int32_t rstq_timeline_read(rstq_ctx* ctx, int32_t dev, int64_t* out, int64_t n) {
+    CHECK_CTX(ctx);
+    CHECK_DEV(ctx, dev);
+    RSTQ_REQUIRE(out && n >= 0 && n <= 1024 * 8, RSTQ_E_INVALID, "need 0 <= n <= 8192");
+    DeviceState& ds = ctx->devs[dev];
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaMemcpyAsync(out, ds.dbg_store, (size_t)n * 8, cudaMemcpyDeviceToHost, ds.stream));
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    return RSTQ_OK;
 }
 
 int32_t rstq_device_info(rstq_ctx* ctx, int32_t dev, int64_t* out4) {

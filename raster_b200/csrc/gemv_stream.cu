@@ -1,0 +1,772 @@
+// Streaming decode GEMV for sm_100a (M <= 16 per launch).
+//
+// Arithmetic: mode A8 = qmatmul-q4-x8! / qmatmul-q8-x8!
+// (src/raster/quant/kernels.clj:216-247, :308-333: integer block dots,
+// zero-point fold, per-block scale), mode F = qlinear-q8
+// (src/raster/quant/train.clj:77-108: y = dequant(W) . x).
+//
+// Work decomposition, built for HBM bandwidth:
+//  * The weight is a sequence of U = groups * nb units (mma32 layout) stored in
+//    exactly the order they are consumed.  G persistent CTAs (one per SM) each
+//    own ONE contiguous range of units, i.e. one contiguous byte range.
+//  * A producer warp copies that range into a shared-memory ring with bulk
+//    async copies (cp.async.bulk, up to 32 units per copy) that complete on
+//    mbarriers; 16 consumer warps each take up to two units of a chunk, read
+//    their 16-byte A-fragment slot from shared memory, run the tensor-core
+//    block dot (mma.sync) against activations staged once per CTA, and apply
+//    the per-block scale to the accumulator fragment in registers.  Bytes in
+//    flight per SM are set by the ring depth, not by registers or occupancy.
+//  * int4 unpacking is two AND masks per 32-bit word (no shifts): the layout
+//    pairs rows r / r+8 in the low / high nibble, the high-nibble rows come out
+//    of the tile multiplied by 16 and the factor is undone in the scale.  The
+//    zero-point term and the int->float bias ride in the accumulator input of
+//    the int8 tile, so the fold is one FADD + one FMUL + one FFMA per value.
+//  * Chunks never straddle a 32-row group, so all consumer warps reach a group
+//    boundary together: they reduce across warps and store y directly when the
+//    CTA covered the whole K range of the group; otherwise (at most the first
+//    and the last group of a CTA) the partial goes to scratch and the last CTA
+//    to arrive for that group adds the partials in CTA order.  Nothing spins on
+//    another CTA; every mbarrier wait is time-bounded and reports through a
+//    status word instead of hanging.
+#include "internal.h"
+#include "mma_helpers.cuh"
+
+namespace rstq {
+
+constexpr int kCW = 16;                          // consumer warps
+constexpr int kConsumers = kCW * 32;
+constexpr int kStreamThreads = kConsumers + 32;  // + producer warp
+constexpr int kChunkUnits = 2 * kCW;             // two units per consumer warp
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+constexpr int kMaxDynSmem = 232448 - 1024;       // 227 KB opt-in limit less the static part
+constexpr int kMagicInt = 0x4B400000;            // bits of 12582912.0f = 2^23 + 2^22
+constexpr float kMagicFlt = 12582912.0f;
+
+enum { MODE_F = 0, MODE_A8 = 1 };
+
+struct StreamParams {
+    const uint8_t* w;
+    const int8_t* xq;     // A8
+    const float* xs;
+    const int32_t* xsum;
+    const void* x;        // F
+    void* y;
+    float* partials;      // [G][2][M*32]
+    int* counters;        // [groups], zero between launches
+    int* status;          // device status word (0 = ok)
+    unsigned long long* dbg;  // optional per-CTA phase timestamps (8 per CTA), or null
+    int64_t in, out;
+    int64_t uq, ur;       // units per CTA: CTA c owns uq (+1 if c < ur) units
+    int M, nb, G, zp, NS, T, act_dtype, out_dtype;
+    uint32_t act_off, act2_off, red_off, bar_off;  // byte offsets into dynamic smem (ring at 0)
+};
+
+// ---- mbarrier / bulk-copy primitives -------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Slow path of a time-bounded wait.  Returns false when the limit ran out or
+// another warp already gave up (abort flag); the caller then skips its work but
+// keeps meeting every CTA barrier so nobody is left waiting.
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const unsigned long long t0 = gtime_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (gtime_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                              uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void consumer_bar() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+}
+
+// CTA c owns units [range_begin(c), range_begin(c + 1)): the first ur CTAs get uq + 1.
+__host__ __device__ __forceinline__ int64_t range_begin(int64_t c, int64_t uq, int64_t ur) {
+    return c * uq + (c < ur ? c : ur);
+}
+__device__ __forceinline__ int cta_of_unit(int64_t u, int64_t uq, int64_t ur) {
+    const int64_t big = ur * (uq + 1);
+    return u < big ? (int)(u / (uq + 1)) : (int)(ur + (u - big) / uq);
+}
+
+// D(16x8, s32) = A(16x32, u8) * B(32x8, s8) + C
+__device__ __forceinline__ void imma_acc(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                         int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2),
+          "r"(c3));
+}
+
+// ---- activation staging (once per CTA, all of K; loops free of divisions) -----------------
+// A8, M == 1: srec [nb][4 tig] uint4 {xq word tig, xq word 4+tig, xs bits, zp*xsum}.
+// A8, M > 1 : sB [nb][M][4 tig] uint2 {xq word tig, xq word 4+tig};
+//             sxz [nb][Mz] int2 {xs bits, zp*xsum}, Mz = M rounded up to even.
+template <bool ONECOL>
+__device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, int tid) {
+    const int nb = p.nb, M = p.M;
+    const uint32_t* xqw = reinterpret_cast<const uint32_t*>(p.xq);
+    if (ONECOL) {
+        uint4* srec = reinterpret_cast<uint4*>(smem + p.act_off);
+        for (int i = tid; i < nb * 4; i += kConsumers) {
+            const int b = i >> 2, tg = i & 3;
+            uint4 r;
+            r.x = xqw[b * 8 + tg];
+            r.y = xqw[b * 8 + 4 + tg];
+            r.z = __float_as_uint(p.xs[b]);
+            r.w = (uint32_t)(p.zp * p.xsum[b]);
+            srec[i] = r;
+        }
+        return;
+    }
+    uint2* sB = reinterpret_cast<uint2*>(smem + p.act_off);
+    int2* sxz = reinterpret_cast<int2*>(smem + p.act2_off);
+    const int Mz = (M + 1) & ~1;
+    const int64_t row_words = p.in >> 2;
+    for (int c = 0; c < Mz; ++c) {
+        const uint32_t* xr = xqw + c * row_words;
+        if (c < M) {
+            for (int i = tid; i < nb * 4; i += kConsumers) {
+                const int b = i >> 2, tg = i & 3;
+                sB[(b * M + c) * 4 + tg] = make_uint2(xr[b * 8 + tg], xr[b * 8 + 4 + tg]);
+            }
+        }
+        for (int b = tid; b < nb; b += kConsumers) {
+            int2 v = make_int2(0, 0);
+            if (c < M) {
+                v.x = __float_as_int(p.xs[(int64_t)c * nb + b]);
+                v.y = p.zp * p.xsum[(int64_t)c * nb + b];
+            }
+            sxz[b * Mz + c] = v;
+        }
+    }
+}
+
+// F: sx [nb][2 halves][C][4 tig] entries of 8 bytes = bf16 (e0, e2, e1, e3) of the four
+// elements 16h + 4tig + 0..3 of column c = m*T + t (term t of token m), C = M*T.
+__device__ __forceinline__ void stage_f(const StreamParams& p, uint8_t* smem, int tid) {
+    uint2* sx = reinterpret_cast<uint2*>(smem + p.act_off);
+    const int C = p.M * p.T, nb = p.nb;
+    int m = 0, t = 0;
+    for (int c = 0; c < C; ++c) {
+        for (int i = tid; i < nb * 8; i += kConsumers) {
+            const int tg = i & 3, h = (i >> 2) & 1, b = i >> 3;
+            const int64_t e = (int64_t)m * p.in + b * 32 + h * 16 + tg * 4;
+            __nv_bfloat16 q[4];
+            if (p.act_dtype == RSTQ_BF16) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(
+                    reinterpret_cast<const __nv_bfloat16*>(p.x) + e);
+                q[0] = __ushort_as_bfloat16((unsigned short)(raw.x & 0xFFFF));
+                q[1] = __ushort_as_bfloat16((unsigned short)(raw.x >> 16));
+                q[2] = __ushort_as_bfloat16((unsigned short)(raw.y & 0xFFFF));
+                q[3] = __ushort_as_bfloat16((unsigned short)(raw.y >> 16));
+            } else {
+                const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + e);
+                q[0] = bf16_term(f.x, t);
+                q[1] = bf16_term(f.y, t);
+                q[2] = bf16_term(f.z, t);
+                q[3] = bf16_term(f.w, t);
+            }
+            uint2 v;
+            v.x = (uint32_t)__bfloat16_as_ushort(q[0]) | ((uint32_t)__bfloat16_as_ushort(q[2]) << 16);
+            v.y = (uint32_t)__bfloat16_as_ushort(q[1]) | ((uint32_t)__bfloat16_as_ushort(q[3]) << 16);
+            sx[((b * 2 + h) * C + c) * 4 + tg] = v;
+        }
+        if (++t == p.T) { t = 0; ++m; }
+    }
+}
+
+// ---- one unit (32 rows x one 32-element block) from the ring ------------------------
+template <int BITS>
+struct SUnit {
+    uint4 c0, c1;
+    float4 sc;
+};
+template <int BITS>
+__device__ __forceinline__ void lds_unit(SUnit<BITS>& u, const uint8_t* unit, int lane) {
+    constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
+    u.c0 = *reinterpret_cast<const uint4*>(unit + lane * 16);
+    if (BITS == 8) u.c1 = *reinterpret_cast<const uint4*>(unit + 512 + lane * 16);
+    u.sc = *reinterpret_cast<const float4*>(unit + CODES + (lane >> 2) * 16);
+}
+
+// A-fragment registers of the two 16-row tiles (q = 0: rows gid, gid+8; q = 1: rows
+// gid+16, gid+24).  For 4-bit codes the rows gid+8 / gid+24 come out multiplied by 16.
+template <int BITS>
+__device__ __forceinline__ void a_frags(const SUnit<BITS>& u, uint32_t (&a)[2][4]) {
+    if (BITS == 4) {
+        const uint32_t lo = 0x0F0F0F0Fu, hi = 0xF0F0F0F0u;
+        a[0][0] = u.c0.x & lo;
+        a[0][1] = u.c0.x & hi;
+        a[0][2] = u.c0.y & lo;
+        a[0][3] = u.c0.y & hi;
+        a[1][0] = u.c0.z & lo;
+        a[1][1] = u.c0.z & hi;
+        a[1][2] = u.c0.w & lo;
+        a[1][3] = u.c0.w & hi;
+    } else {
+        a[0][0] = u.c0.x;
+        a[0][1] = u.c0.y;
+        a[0][2] = u.c1.x;
+        a[0][3] = u.c1.y;
+        a[1][0] = u.c0.z;
+        a[1][1] = u.c0.w;
+        a[1][2] = u.c1.z;
+        a[1][3] = u.c1.w;
+    }
+}
+
+template <int BITS, int NT, bool ONECOL>
+__device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* smem,
+                                        const StreamParams& p, int b, int gid, int tig,
+                                        float (&acc)[NT][4][2]) {
+    uint32_t a[2][4];
+    a_frags<BITS>(u, a);
+    const float sc[4] = {u.sc.x, u.sc.y, u.sc.z, u.sc.w};
+    // value of the high-nibble rows is 16x: scale by xs/16 and shift their zero-point term
+    constexpr float HI = BITS == 4 ? 0.0625f : 1.0f;
+    constexpr int ZSH = BITS == 4 ? 4 : 0;
+    if (ONECOL) {
+        const uint4 r = reinterpret_cast<const uint4*>(smem + p.act_off)[b * 4 + tig];
+        const float xs = __uint_as_float(r.z), xsh = xs * HI;
+        const int ca = kMagicInt - (int)r.w, cb = kMagicInt - ((int)r.w << ZSH);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            int d[4];
+            imma_acc(d, a[q], r.x, r.y, ca, ca, cb, cb);
+            acc[0][2 * q][0] = fmaf(sc[2 * q] * xs, __int_as_float(d[0]) - kMagicFlt, acc[0][2 * q][0]);
+            acc[0][2 * q + 1][0] =
+                fmaf(sc[2 * q + 1] * xsh, __int_as_float(d[2]) - kMagicFlt, acc[0][2 * q + 1][0]);
+        }
+        return;
+    }
+    const int M = p.M, Mz = (M + 1) & ~1;
+    const uint2* xB = reinterpret_cast<const uint2*>(smem + p.act_off) + b * M * 4;
+    const int2* xz = reinterpret_cast<const int2*>(smem + p.act2_off) + b * Mz;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        // columns beyond M are never stored, so any valid address will do for them
+        int col = nt * 8 + gid;
+        col = col < M ? col : M - 1;
+        const uint2 bb = xB[col * 4 + tig];
+        int c0 = nt * 8 + 2 * tig;
+        c0 = c0 < Mz ? c0 : 0;
+        const int4 z = *reinterpret_cast<const int4*>(xz + c0);
+        const float xs0 = __int_as_float(z.x), xs1 = __int_as_float(z.z);
+        const float xs0h = xs0 * HI, xs1h = xs1 * HI;
+        const int ca0 = kMagicInt - z.y, ca1 = kMagicInt - z.w;
+        const int cb0 = kMagicInt - (z.y << ZSH), cb1 = kMagicInt - (z.w << ZSH);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            int d[4];
+            imma_acc(d, a[q], bb.x, bb.y, ca0, ca1, cb0, cb1);
+            const float s0 = sc[2 * q], s1 = sc[2 * q + 1];
+            acc[nt][2 * q][0] = fmaf(s0 * xs0, __int_as_float(d[0]) - kMagicFlt, acc[nt][2 * q][0]);
+            acc[nt][2 * q][1] = fmaf(s0 * xs1, __int_as_float(d[1]) - kMagicFlt, acc[nt][2 * q][1]);
+            acc[nt][2 * q + 1][0] =
+                fmaf(s1 * xs0h, __int_as_float(d[2]) - kMagicFlt, acc[nt][2 * q + 1][0]);
+            acc[nt][2 * q + 1][1] =
+                fmaf(s1 * xs1h, __int_as_float(d[3]) - kMagicFlt, acc[nt][2 * q + 1][1]);
+        }
+    }
+}
+
+template <int BITS, int NT>
+__device__ __forceinline__ void unit_f(const SUnit<BITS>& u, const uint8_t* smem,
+                                       const StreamParams& p, int b, int gid, int tig,
+                                       float (&acc)[NT][4][2]) {
+    // fr[h][i][j]: half h, row gid + 8i, j = 0 -> elements (+0, +2), j = 1 -> (+1, +3)
+    uint32_t fr[2][4][2];
+    const uint32_t c0[4] = {u.c0.x, u.c0.y, u.c0.z, u.c0.w};
+    const uint32_t c1[4] = {u.c1.x, u.c1.y, u.c1.z, u.c1.w};
+    if (BITS == 4) {
+        // word 2q + h: low nibbles = row i = 2q, high nibbles = row i = 2q + 1.
+        // 0x4300 | n is bf16(128 + n); subtract 128 + zero point 8.
+        const uint32_t m4 = 0x000F000Fu, ex = 0x43004300u, off = 0x43084308u;
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t w = c0[2 * q + h];
+                fr[h][2 * q][0] = sub_bf16x2((w & m4) | ex, off);
+                fr[h][2 * q][1] = sub_bf16x2(((w >> 8) & m4) | ex, off);
+                fr[h][2 * q + 1][0] = sub_bf16x2(((w >> 4) & m4) | ex, off);
+                fr[h][2 * q + 1][1] = sub_bf16x2(((w >> 12) & m4) | ex, off);
+            }
+    } else {
+        // 0x4B000000 | b is f32(2^23 + b); subtract 2^23 + zero point 128
+        const float off = 8388736.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t w = h ? c1[i] : c0[i];
+                const float f0 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440)) - off;
+                const float f1 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7441)) - off;
+                const float f2 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7442)) - off;
+                const float f3 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7443)) - off;
+                fr[h][i][0] = pack_bf16x2(f2, f0);
+                fr[h][i][1] = pack_bf16x2(f3, f1);
+            }
+    }
+    const float sc[4] = {u.sc.x, u.sc.y, u.sc.z, u.sc.w};
+    const int C = p.M * p.T;
+    const uint2* xb = reinterpret_cast<const uint2*>(smem + p.act_off) + b * 2 * C * 4;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        int col = nt * 8 + gid;
+        col = col < C ? col : C - 1;
+        const uint2 bx0 = xb[col * 4 + tig];
+        const uint2 bx1 = xb[(C + col) * 4 + tig];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            const int r0 = 2 * mt, r1 = 2 * mt + 1;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t a_lo[4] = {fr[0][r0][0], fr[0][r1][0], fr[0][r0][1], fr[0][r1][1]};
+            const uint32_t a_hi[4] = {fr[1][r0][0], fr[1][r1][0], fr[1][r0][1], fr[1][r1][1]};
+            hmma_bf16(c, a_lo, bx0.x, bx0.y);
+            hmma_bf16(c, a_hi, bx1.x, bx1.y);
+            acc[nt][r0][0] = fmaf(sc[r0], c[0], acc[nt][r0][0]);
+            acc[nt][r0][1] = fmaf(sc[r0], c[1], acc[nt][r0][1]);
+            acc[nt][r1][0] = fmaf(sc[r1], c[2], acc[nt][r1][0]);
+            acc[nt][r1][1] = fmaf(sc[r1], c[3], acc[nt][r1][1]);
+        }
+    }
+}
+
+// Sum over the consumer warps of the fragment element holding (row, col); red is [warp][v][lane].
+template <int NT>
+__device__ __forceinline__ float stream_reduce_rc(const float* red, int row, int col) {
+    constexpr int NV = NT * 8;
+    const int gid = row & 7, i = row >> 3;
+    const int nt = col >> 3, within = col & 7;
+    const int lane = gid * 4 + (within >> 1);
+    const int v = (nt * 4 + i) * 2 + (within & 1);
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCW; ++w) s += red[(w * NV + v) * 32 + lane];
+    return s;
+}
+
+// ---- the kernel ---------------------------------------------------------------------
+template <int BITS, int NT, int MODE, bool ONECOL>
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
+    constexpr int UNIT = BITS == 4 ? kUnitBytesQ4 : kUnitBytesQ8;
+    constexpr int CHUNK_BYTES = kChunkUnits * UNIT;
+    constexpr int NV = NT * 8;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_abort;
+    __shared__ int s_last[2];
+    __shared__ long long s_g0;
+    __shared__ int s_bstart, s_total;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int NS = p.NS, nb = p.nb;
+    unsigned long long* dbg = p.dbg ? p.dbg + (size_t)blockIdx.x * 8 : nullptr;
+    if (dbg && tid == 0) dbg[0] = gtime_ns();
+    const uint32_t full0 = smem_u32(smem + p.bar_off), empty0 = full0 + NS * 8;
+    if (tid < NS) mbar_init(full0 + 8 * tid, 1);
+    else if (tid < 2 * NS) mbar_init(empty0 + 8 * (tid - NS), kCW);
+    if (tid == 2 * NS) {
+        // this CTA's unit range, as (first group, first block in it, unit count)
+        const int64_t u0 = range_begin(blockIdx.x, p.uq, p.ur);
+        const int64_t g0 = u0 / nb;
+        s_g0 = g0;
+        s_bstart = (int)(u0 - g0 * nb);
+        s_total = (int)(range_begin(blockIdx.x + 1, p.uq, p.ur) - u0);
+        s_abort = 0;
+    }
+    if (tid < 2 * NS) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+    volatile int* abort_flag = &s_abort;
+    const int64_t g0 = s_g0;
+    const int b_start = s_bstart, total = s_total;
+
+    // Both roles walk the same chunk schedule with incremental indices: g = group,
+    // b = block inside the group, left = units still to do, (s, ph) = ring slot and
+    // its phase.  A chunk is n = min(32, nb - b, left) units: it never straddles a group.
+    if (warp == kCW) {
+        // ---------------- producer: one lane streams the CTA's byte range ----------------
+        if (lane == 0) {
+            const uint8_t* src = p.w + (g0 * nb + b_start) * UNIT;
+            int b = b_start, left = total, s = 0, issued = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            while (left > 0) {
+                int n = nb - b < left ? nb - b : left;
+                n = n < kChunkUnits ? n : kChunkUnits;
+                ok = mbar_try(empty0 + 8 * s, ph ^ 1u) || mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag);
+                if (!ok) break;
+                const uint32_t bytes = (uint32_t)(n * UNIT);
+                mbar_expect_tx(full0 + 8 * s, bytes);
+                bulk_copy_g2s(smem_u32(smem) + (uint32_t)s * CHUNK_BYTES, src, bytes, full0 + 8 * s);
+                src += bytes;
+                b += n;
+                if (b == nb) b = 0;
+                left -= n;
+                ++issued;
+                if (++s == NS) { s = 0; ph ^= 1u; }
+            }
+            if (!ok) {
+                // gave up: still wait (bounded) for the copies already issued to land,
+                // so no copy is in flight into this CTA's shared memory when it exits
+                for (int k = issued > NS ? issued - NS : 0; k < issued; ++k) {
+                    const uint32_t bar = full0 + 8 * (k % NS), kph = (uint32_t)(k / NS) & 1u;
+                    const unsigned long long t0 = gtime_ns();
+                    while (!mbar_try(bar, kph) && gtime_ns() - t0 < kWaitLimitNs) {
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    if (dbg && tid == 0) dbg[1] = gtime_ns();
+    if (MODE == MODE_A8) stage_a8<ONECOL>(p, smem, tid);
+    else stage_f(p, smem, tid);
+    consumer_bar();
+    if (dbg && tid == 0) dbg[2] = gtime_ns();
+
+    float acc[NT][4][2];
+    float* red = reinterpret_cast<float*>(smem + p.red_off);
+    const int M = p.M, T = p.T;
+    int64_t part_g[2] = {0, 0};
+    int npart = 0;
+
+    auto zero_acc = [&]() {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[nt][i][0] = acc[nt][i][1] = 0.f;
+    };
+    // cross-warp reduction of the segment [b_from, b_to) of group g, then store
+    auto flush = [&](int64_t g, int b_from, int b_to) {
+        const bool whole = (b_from == 0) && (b_to == nb);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int c = 0; c < (ONECOL ? 1 : 2); ++c)
+                    red[(warp * NV + (nt * 4 + i) * 2 + c) * 32 + lane] = acc[nt][i][c];
+        consumer_bar();
+        const int64_t row0 = g * 32;
+        float* part = p.partials + ((int64_t)blockIdx.x * 2 + (g == g0 ? 0 : 1)) * M * 32;
+        for (int o = tid; o < M * 32; o += kConsumers) {
+            const int m = o >> 5, row = o & 31;
+            float sum = 0.f;
+            for (int t = 0; t < T; ++t) sum += stream_reduce_rc<NT>(red, row, m * T + t);
+            if (whole) {
+                if (row0 + row < p.out) store_out(p.y, p.out_dtype, (int64_t)m * p.out + row0 + row, sum);
+            } else {
+                part[o] = sum;
+            }
+        }
+        if (!whole) part_g[npart++] = g;
+        consumer_bar();  // red may be rewritten by the next flush
+    };
+
+    {
+        int64_t g = g0;
+        int b = b_start, seg_from = b_start, left = total, s = 0;
+        uint32_t ph = 0;
+        bool alive = true;
+        const uint8_t* ring_w = smem + warp * UNIT;
+        zero_acc();
+        while (left > 0) {
+            int n = nb - b < left ? nb - b : left;
+            n = n < kChunkUnits ? n : kChunkUnits;
+            if (alive && !mbar_try(full0 + 8 * s, ph)) alive = mbar_wait(full0 + 8 * s, ph, abort_flag);
+            if (dbg && tid == 0 && left == total) dbg[3] = gtime_ns();
+            if (alive && warp < n) {
+                const uint8_t* slot = ring_w + s * CHUNK_BYTES;
+                SUnit<BITS> ua, ub;
+                const bool two = warp + kCW < n;
+                lds_unit<BITS>(ua, slot, lane);
+                if (two) lds_unit<BITS>(ub, slot + kCW * UNIT, lane);
+                if (MODE == MODE_A8) {
+                    unit_a8<BITS, NT, ONECOL>(ua, smem, p, b + warp, gid, tig, acc);
+                    if (two) unit_a8<BITS, NT, ONECOL>(ub, smem, p, b + warp + kCW, gid, tig, acc);
+                } else {
+                    unit_f<BITS, NT>(ua, smem, p, b + warp, gid, tig, acc);
+                    if (two) unit_f<BITS, NT>(ub, smem, p, b + warp + kCW, gid, tig, acc);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);  // also when not alive: never block the producer
+            b += n;
+            left -= n;
+            if (++s == NS) { s = 0; ph ^= 1u; }
+            if (b == nb || left == 0) {
+                flush(g, seg_from, b);
+                ++g;
+                b = 0;
+                seg_from = 0;
+                zero_acc();
+            }
+        }
+    }
+
+    if (dbg && tid == 0) dbg[4] = gtime_ns();
+    // Groups this CTA shares with its neighbours: count in (one fence, both counters at
+    // once), and the last CTA to arrive adds the partials up in CTA order.
+    if (npart > 0) {
+        if (tid == 0) {
+            __threadfence();  // partial stores of the whole CTA (ordered by the flush barrier)
+            int prev[2] = {0, 0};
+            for (int i = 0; i < npart; ++i) prev[i] = atomicAdd(&p.counters[part_g[i]], 1);
+            for (int i = 0; i < npart; ++i) {
+                const int64_t g = part_g[i];
+                const int cf = cta_of_unit(g * nb, p.uq, p.ur);
+                const int cl = cta_of_unit((g + 1) * nb - 1, p.uq, p.ur);
+                s_last[i] = (prev[i] == cl - cf);
+            }
+            __threadfence();
+        }
+        consumer_bar();
+        for (int i = 0; i < npart; ++i) {
+            if (!s_last[i]) continue;
+            const int64_t g = part_g[i];
+            const int cf = cta_of_unit(g * nb, p.uq, p.ur);
+            const int cl = cta_of_unit((g + 1) * nb - 1, p.uq, p.ur);
+            const int64_t row0 = g * 32;
+            for (int o = tid; o < M * 32; o += kConsumers) {
+                const int m = o >> 5, row = o & 31;
+                float sum = 0.f;
+                for (int cc = cf; cc <= cl; ++cc) {
+                    const int slot = (range_begin(cc, p.uq, p.ur) / nb == g) ? 0 : 1;
+                    sum += __ldcg(p.partials + ((int64_t)cc * 2 + slot) * M * 32 + o);
+                }
+                if (row0 + row < p.out) store_out(p.y, p.out_dtype, (int64_t)m * p.out + row0 + row, sum);
+            }
+            if (tid == 0) p.counters[g] = 0;
+        }
+    }
+    if (tid == 0 && s_abort) atomicExch(p.status, 1);
+    if (dbg && tid == 0) dbg[5] = gtime_ns();
+}
+
+// ---- host side --------------------------------------------------------------------------
+struct StreamPlan {
+    bool fits;
+    int NS, G;
+    int64_t uq, ur;
+    uint32_t act_off, act2_off, red_off, bar_off;
+    size_t smem;
+};
+
+static StreamPlan plan_stream(const DeviceState& ds, int bits, int NT, int64_t groups, int64_t nb,
+                              int64_t act_bytes, int64_t act2_bytes) {
+    StreamPlan pl{};
+    const int chunk = kChunkUnits * unit_bytes(bits);
+    const int64_t red = (int64_t)kCW * NT * 8 * 32 * 4;
+    const int64_t a1 = (act_bytes + 127) & ~127ll, a2 = (act2_bytes + 127) & ~127ll;
+    const int64_t room = kMaxDynSmem - (a1 + a2 + red + 512);
+    int64_t ns = room / chunk;
+    if (ns > 8) ns = 8;
+    pl.fits = ns >= 2;
+    if (!pl.fits) return pl;
+    const int64_t U = groups * nb;
+    int64_t G = (U + kChunkUnits - 1) / kChunkUnits;  // at least one chunk of work per CTA
+    if (G > ds.sm_count) G = ds.sm_count;
+    if (G < 1) G = 1;
+    pl.G = (int)G;
+    pl.uq = U / G;
+    pl.ur = U % G;
+    pl.NS = (int)ns;
+    pl.act_off = (uint32_t)(ns * chunk);
+    pl.act2_off = pl.act_off + (uint32_t)a1;
+    pl.red_off = pl.act2_off + (uint32_t)a2;
+    pl.bar_off = pl.red_off + (uint32_t)red;
+    pl.smem = pl.bar_off + 2 * ns * 8;
+    return pl;
+}
+
+template <typename K>
+static int32_t set_stream_attr(K kernel) {
+    RSTQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+    return RSTQ_OK;
+}
+
+int32_t gemv_configure(DeviceState& ds) {
+    (void)ds;
+    int32_t rc;
+#define CFG(...) if ((rc = set_stream_attr(gemv_stream_kernel<__VA_ARGS__>)) != RSTQ_OK) return rc
+    CFG(4, 1, MODE_A8, true);
+    CFG(4, 1, MODE_A8, false);
+    CFG(4, 2, MODE_A8, false);
+    CFG(8, 1, MODE_A8, true);
+    CFG(8, 1, MODE_A8, false);
+    CFG(8, 2, MODE_A8, false);
+    CFG(4, 1, MODE_F, false);
+    CFG(4, 2, MODE_F, false);
+    CFG(4, 4, MODE_F, false);
+    CFG(8, 1, MODE_F, false);
+    CFG(8, 2, MODE_F, false);
+    CFG(8, 4, MODE_F, false);
+#undef CFG
+    return RSTQ_OK;
+}
+
+static int32_t stream_scratch_ok(const DeviceState& ds, int64_t groups, int G, int64_t M) {
+    RSTQ_REQUIRE(groups <= ds.counters_len, RSTQ_E_LIMIT, "out = %lld rows exceeds the %lld-group limit",
+                 (long long)groups * 32, (long long)ds.counters_len);
+    RSTQ_REQUIRE((int64_t)G * 2 * M * 32 * 4 <= ds.partials_bytes, RSTQ_E_LIMIT, "partials scratch too small");
+    return RSTQ_OK;
+}
+
+static void fill_common(StreamParams& p, const DeviceState& ds, const StreamPlan& pl, int64_t in,
+                        int64_t out, int M, int64_t nb, int zp) {
+    p.partials = ds.partials; p.counters = ds.counters; p.status = ds.status; p.dbg = ds.dbg;
+    p.in = in; p.out = out; p.uq = pl.uq; p.ur = pl.ur;
+    p.M = M; p.nb = (int)nb; p.G = pl.G; p.zp = zp; p.NS = pl.NS;
+    p.act_off = pl.act_off; p.act2_off = pl.act2_off; p.red_off = pl.red_off; p.bar_off = pl.bar_off;
+}
+
+// Largest token count <= want whose staged activations fit next to a ring of >= 2 chunks.
+template <typename BytesFn>
+static int fit_tokens(const DeviceState& ds, int bits, int64_t groups, int64_t nb, int want, BytesFn f,
+                      StreamPlan* out) {
+    for (int m = want; m >= 1; --m) {
+        int NT;
+        int64_t a1, a2;
+        f(m, &NT, &a1, &a2);
+        StreamPlan pl = plan_stream(ds, bits, NT, groups, nb, a1, a2);
+        if (pl.fits) {
+            *out = pl;
+            return m;
+        }
+    }
+    return 0;
+}
+
+int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
+    RSTQ_REQUIRE(a.M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)a.M);
+    const int64_t nb = a.in / 32, groups = (a.out + 31) / 32;
+    RSTQ_REQUIRE(nb < (1 << 24) && groups * nb < (1ll << 40), RSTQ_E_LIMIT, "matrix too large");
+    auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
+        *NT = m <= 8 ? 1 : 2;
+        if (m == 1) { *a1 = nb * 64; *a2 = 0; }
+        else { *a1 = nb * m * 32; *a2 = nb * ((m + 1) & ~1) * 8; }
+    };
+    for (int64_t m0 = 0; m0 < a.M;) {
+        const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
+        StreamPlan pl;
+        const int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
+        RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
+                     (long long)a.in);
+        int32_t rc = stream_scratch_ok(ds, groups, pl.G, M);
+        if (rc != RSTQ_OK) return rc;
+        const int NT = M <= 8 ? 1 : 2;
+        StreamParams p{};
+        fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp);
+        p.w = a.w;
+        p.xq = a.xq + m0 * a.in;
+        p.xs = a.xs + m0 * nb;
+        p.xsum = a.xsum + m0 * nb;
+        p.y = a.y + m0 * a.out;
+        p.T = 1; p.act_dtype = RSTQ_F32; p.out_dtype = RSTQ_F32;
+#define LAUNCH(...) gemv_stream_kernel<__VA_ARGS__><<<pl.G, kStreamThreads, pl.smem, ds.stream>>>(p)
+        if (a.bits == 4) {
+            if (NT == 2) LAUNCH(4, 2, MODE_A8, false);
+            else if (M == 1) LAUNCH(4, 1, MODE_A8, true);
+            else LAUNCH(4, 1, MODE_A8, false);
+        } else {
+            if (NT == 2) LAUNCH(8, 2, MODE_A8, false);
+            else if (M == 1) LAUNCH(8, 1, MODE_A8, true);
+            else LAUNCH(8, 1, MODE_A8, false);
+        }
+        ctx->launches++;
+        RSTQ_CUDA(cudaGetLastError());
+        m0 += M;
+    }
+    return RSTQ_OK;
+}
+
+int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
+    RSTQ_REQUIRE(a.M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)a.M);
+    const int64_t nb = a.in / 32, groups = (a.out + 31) / 32;
+    RSTQ_REQUIRE(nb < (1 << 24) && groups * nb < (1ll << 40), RSTQ_E_LIMIT, "matrix too large");
+    // f32 activations are expanded into exact bf16 terms: three while they fit one
+    // 8-column tile, else two (16 significant bits).
+    auto terms = [&](int m) { return a.act_dtype == RSTQ_F32 ? ((3 * m <= 8) ? 3 : 2) : 1; };
+    auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
+        const int C = m * terms(m);
+        *NT = C <= 8 ? 1 : (C <= 16 ? 2 : 4);
+        *a1 = nb * 2 * C * 32;
+        *a2 = 0;
+    };
+    const int64_t xe = a.act_dtype == RSTQ_F32 ? 4 : 2, ye = a.out_dtype == RSTQ_F32 ? 4 : 2;
+    for (int64_t m0 = 0; m0 < a.M;) {
+        const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
+        StreamPlan pl;
+        const int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
+        RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
+                     (long long)a.in);
+        int32_t rc = stream_scratch_ok(ds, groups, pl.G, M);
+        if (rc != RSTQ_OK) return rc;
+        const int T = terms(M), C = M * T;
+        const int NT = C <= 8 ? 1 : (C <= 16 ? 2 : 4);
+        StreamParams p{};
+        fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp);
+        p.w = a.w;
+        p.x = (const char*)a.x + m0 * a.in * xe;
+        p.y = (char*)a.y + m0 * a.out * ye;
+        p.T = T; p.act_dtype = a.act_dtype; p.out_dtype = a.out_dtype;
+        if (a.bits == 4) {
+            if (NT == 1) LAUNCH(4, 1, MODE_F, false);
+            else if (NT == 2) LAUNCH(4, 2, MODE_F, false);
+            else LAUNCH(4, 4, MODE_F, false);
+        } else {
+            if (NT == 1) LAUNCH(8, 1, MODE_F, false);
+            else if (NT == 2) LAUNCH(8, 2, MODE_F, false);
+            else LAUNCH(8, 4, MODE_F, false);
+        }
+#undef LAUNCH
+        ctx->launches++;
+        RSTQ_CUDA(cudaGetLastError());
+        m0 += M;
+    }
+    return RSTQ_OK;
+}
+
+}  // namespace rstq

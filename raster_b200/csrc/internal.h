@@ -38,15 +38,18 @@ int32_t cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 //   8-bit unit, 1152 B: [plane 0: 32 slots x 16 B][plane 1: 32 x 16 B][32 x f32 scales]
 //
 // Slot `lane` = gid*4 + tig (gid = lane >> 2, tig = lane & 3) holds four 32-bit
-// words i = 0..3, one per row r_i = 32g + gid + 8i:
-//   4-bit: word `tig` of that row's 16-byte Q4_0 block (low nibbles = elements
-//          4tig..4tig+3, high nibbles = elements 16+4tig..16+4tig+3);
-//   8-bit: plane p holds word `tig + 4p` of the row's 32-byte block (elements
-//          4tig+16p .. 4tig+16p+3), unsigned with zero point 128.
-// Scale index gid*4 + i is the scale of row r_i.
-// This is exactly the A-fragment ownership of mma.sync m16n8k32 (int8) and, per
-// 16-element half, of m16n8k16 (bf16), so one 16-byte load per lane feeds two
-// 16-row tensor-core tiles with no shuffles.
+// words.
+//   4-bit: word 2q + h (q = 0,1; h = 0,1), byte j: low nibble = code of row
+//          32g + gid + 16q, high nibble = code of row 32g + gid + 16q + 8, both at
+//          element 16h + 4tig + j of the block.  Masking a word with 0x0F0F0F0F /
+//          0xF0F0F0F0 therefore yields two int8 A-fragment registers of
+//          mma.sync m16n8k32 with no shift: the high-nibble rows come out
+//          multiplied by 16, which the kernels undo in the per-block scale.
+//   8-bit: plane p (p = 0,1), word i (i = 0..3) = elements 4tig + 16p .. +3 of
+//          row 32g + gid + 8i, unsigned with zero point 128.
+// Scale index gid*4 + i is the (true) scale of row 32g + gid + 8i.
+// One 16-byte load per lane thus feeds two 16-row tensor-core tiles with no
+// data movement between lanes.
 constexpr int kUnitBytesQ4 = 640;
 constexpr int kUnitBytesQ8 = 1152;
 constexpr int kUnitCodesQ4 = 512;
@@ -72,7 +75,9 @@ struct DeviceState {
     int64_t pinned_bytes = 0;
     void* io_dev = nullptr;        // device staging for the host-array entry points
     int64_t io_dev_bytes = 0;
-    int gemv_ctas_per_sm = 3;
+    int* status = nullptr;         // device status word: nonzero after a bounded wait ran out
+    unsigned long long* dbg = nullptr;      // phase timestamps of the last streaming launch, when enabled
+    unsigned long long* dbg_store = nullptr;
 };
 
 }  // namespace rstq
@@ -80,7 +85,6 @@ struct DeviceState {
 struct rstq_ctx {
     uint32_t magic;
     std::vector<rstq::DeviceState> devs;
-    int64_t tune_splitk = 0;
     int64_t tune_gemm_min_m = 17;
     int64_t launches = 0;
     struct CacheKey {
@@ -173,9 +177,10 @@ struct GemvFArgs {
     int bits, zp;
     int act_dtype, out_dtype;
 };
+// gemv_stream.cu.  Any M >= 1: the launchers cut M into pieces the kernel takes.
 int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a);
 int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a);
-int32_t gemv_configure(DeviceState& ds);  // occupancy / smem attributes, once per device
+int32_t gemv_configure(DeviceState& ds);  // shared-memory attributes, once per device
 constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels
 
 }  // namespace rstq

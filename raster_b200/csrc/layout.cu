@@ -70,24 +70,24 @@ __global__ void repack_kernel(SrcView s, uint8_t* __restrict__ dst, int64_t out,
             *reinterpret_cast<float*>(dword) = v;
             continue;
         }
-        const int plane = wi >> 7;           // 0 for 4-bit; 0/1 for 8-bit
         const int slot = (wi & 127) >> 2;    // lane slot
-        const int i = wi & 3;
         const int gid = slot >> 2, tig = slot & 3;
-        const int64_t row = g * 32 + gid + 8 * i;
         uint32_t word = 0;
         if (BITS == 4) {
-            if (row < out) {
+            // word 2q + h: low nibbles = row gid + 16q, high nibbles = row gid + 16q + 8,
+            // elements 16h + 4tig + j
+            const int q = (wi & 3) >> 1, h = wi & 1;
+            const int64_t r_lo = g * 32 + gid + 16 * q, r_hi = r_lo + 8;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t lo = src_nibble(s, row, b, 4 * tig + j);
-                    uint32_t hi = src_nibble(s, row, b, 16 + 4 * tig + j);
-                    word |= (lo | (hi << 4)) << (8 * j);
-                }
-            } else {
-                word = 0x88888888u;  // zero point: padded rows dequantize to 0
+            for (int j = 0; j < 4; ++j) {
+                const int e = 16 * h + 4 * tig + j;
+                const uint32_t lo = r_lo < out ? src_nibble(s, r_lo, b, e) : 8u;  // zero point:
+                const uint32_t hi = r_hi < out ? src_nibble(s, r_hi, b, e) : 8u;  // padding -> 0
+                word |= (lo | (hi << 4)) << (8 * j);
             }
         } else {
+            const int plane = wi >> 7, i = wi & 3;
+            const int64_t row = g * 32 + gid + 8 * i;
             if (row < out) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {

@@ -280,23 +280,20 @@ def test_zero_inputs_give_exact_zeros(ctx, bits):
     w0.free()
 
 
-def test_forced_split_k_values_agree(ctx):
-    out, in_ = 4096, 11008
-    _, wq, ws = make_weight(out, in_, 4, seed=21)
-    x = synth.normal(22, in_)
-    w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
-    xq, xs, xsum = orc.quantize_act_i8(x, 1, in_)
-    ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, 1, in_, out)
-    try:
-        for S in (1, 2, 5, 8, 11, 21):
-            ctx.tune(L.TUNE_SPLITK, S)
-            y1 = ctx.qmatmul_host(w, x, 1, L.F32, L.MODE_A8)
-            y2 = ctx.qmatmul_host(w, x, 1, L.F32, L.MODE_A8)
-            assert relerr(y1, ref) <= TOL_A8
-            assert np.array_equal(y1, y2)          # run-to-run bit-reproducible
-    finally:
-        ctx.tune(L.TUNE_SPLITK, 0)
-    w.free()
+def test_partial_groups_and_reproducibility(ctx):
+    """Shapes whose rows-per-CTA split leaves groups shared between CTAs; run-to-run identical."""
+    for out, in_, M in ((4096, 11008, 1), (11008, 4096, 1), (300, 22016, 2), (8192, 1024, 3)):
+        _, wq, ws = make_weight(out, in_, 4, seed=21 + out)
+        x = synth.normal(22 + in_, M * in_)
+        w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+        xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+        ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out)
+        y1 = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
+        y2 = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
+        assert relerr(y1, ref) <= TOL_A8
+        assert np.array_equal(y1, y2)
+        ctx.sync()                                   # no bounded wait ran out
+        w.free()
 
 
 def test_full_size_linearity_and_split_properties(ctx):
@@ -367,3 +364,19 @@ def test_graph_replay_is_idempotent_and_clone_is_equal(ctx):
     for b in (bx, by, by2):
         b.free()
     w.free(), w2.free()
+
+
+# ---------------------------------------------------------------- token splitting
+def test_tokens_are_split_when_activations_exceed_shared_memory(ctx):
+    out, in_, M = 64, 28672, 16          # 16 tokens x 28672 do not fit beside the weight ring
+    _, wq, ws = make_weight(out, in_, 4, seed=5)
+    x = synth.normal(6, M * in_)
+    w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    n0 = ctx.launch_count()
+    y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
+    assert ctx.launch_count() - n0 >= 3      # quantizer + at least two decode launches
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    assert relerr(y, orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out)) <= TOL_A8
+    yf = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_F)
+    assert relerr(yf, orc.matmul_dq_f64(wq, ws, 0, x, M, in_, out)) <= TOL_F
+    w.free()
