@@ -21,6 +21,10 @@ __device__ __forceinline__ int round_half_up(double v) {
 __global__ void __launch_bounds__(256)
 quant_act_i8_kernel(const float* __restrict__ x, int8_t* __restrict__ xq, float* __restrict__ xs,
                     int32_t* __restrict__ xsum, int64_t nblocks) {
+    // programmatic dependent launch: let the consumer kernel start its weight stream now;
+    // x may come from the kernel before this one, so wait for it
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -56,7 +60,16 @@ int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const float* x, int8
     const int64_t cap = (int64_t)ds.sm_count * 8;
     if (ctas > cap) ctas = cap;
     if (ctas < 1) ctas = 1;
-    quant_act_i8_kernel<<<(int)ctas, 256, 0, ds.stream>>>(x, xq, xs, xsum, nblocks);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ds.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ds.pdl ? 1 : 0;
+    RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel, x, xq, xs, xsum, nblocks));
     ctx->launches++;
     RSTQ_CUDA(cudaGetLastError());
     return RSTQ_OK;

@@ -384,6 +384,9 @@ int32_t rstq_sync(rstq_ctx* ctx, int32_t dev) {
 int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
     CHECK_CTX(ctx);
     switch (key) {
+        case RSTQ_TUNE_PDL:
+            for (auto& ds : ctx->devs) ds.pdl = value != 0;
+            return RSTQ_OK;
         case RSTQ_TUNE_TIMELINE:
             for (auto& ds : ctx->devs) ds.dbg = value ? ds.dbg_store : nullptr;
             return RSTQ_OK;

@@ -10,8 +10,8 @@
 //    exactly the order they are consumed.  G persistent CTAs (one per SM) each
 //    own ONE contiguous range of units, i.e. one contiguous byte range.
 //  * A producer warp copies that range into a shared-memory ring with bulk
-//    async copies (cp.async.bulk, up to 32 units per copy) that complete on
-//    mbarriers; 16 consumer warps each take up to two units of a chunk, read
+//    async copies (cp.async.bulk, up to 64 units per copy) that complete on
+//    mbarriers; 16 consumer warps each take up to four units of a chunk, read
 //    their 16-byte A-fragment slot from shared memory, run the tensor-core
 //    block dot (mma.sync) against activations staged once per CTA, and apply
 //    the per-block scale to the accumulator fragment in registers.  Bytes in
@@ -36,7 +36,9 @@ namespace rstq {
 constexpr int kCW = 16;                          // consumer warps
 constexpr int kConsumers = kCW * 32;
 constexpr int kStreamThreads = kConsumers + 32;  // + producer warp
-constexpr int kChunkUnits = 2 * kCW;             // two units per consumer warp
+// units per consumer warp per chunk: 4 (40 KB chunks) for 4-bit, 2 (36 KB chunks) for 8-bit
+__host__ __device__ constexpr int upw_of(int bits) { return bits == 4 ? 4 : 2; }
+__host__ __device__ constexpr int chunk_units_of(int bits) { return upw_of(bits) * kCW; }
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
 constexpr int kMaxDynSmem = 232448 - 1024;       // 227 KB opt-in limit less the static part
 constexpr int kMagicInt = 0x4B400000;            // bits of 12582912.0f = 2^23 + 2^22
@@ -137,23 +139,47 @@ __device__ __forceinline__ void imma_acc(int (&d)[4], const uint32_t (&a)[4], ui
 }
 
 // ---- activation staging (once per CTA, all of K; loops free of divisions) -----------------
-// A8, M == 1: srec [nb][4 tig] uint4 {xq word tig, xq word 4+tig, xs bits, zp*xsum}.
+// A8, M == 1: srec [nb][4 tig] uint4 {xq word tig, xq word 4+tig, xs_t bits, c_t}: lane tig
+//            folds row gid + 8*tig only (all eight tile columns are the same token), so the
+//            record carries that row's constants: for 4-bit codes the rows of odd tig sit in
+//            the high nibbles (tile value x16): xs_t = xs/16 and c_t = bias - 16*zp*xsum;
+//            otherwise xs_t = xs and c_t = bias - zp*xsum (bias = bits of 2^23 + 2^22).
 // A8, M > 1 : sB [nb][M][4 tig] uint2 {xq word tig, xq word 4+tig};
 //             sxz [nb][Mz] int2 {xs bits, zp*xsum}, Mz = M rounded up to even.
-template <bool ONECOL>
+template <bool ONECOL, int BITS>
 __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, int tid) {
     const int nb = p.nb, M = p.M;
     const uint32_t* xqw = reinterpret_cast<const uint32_t*>(p.xq);
     if (ONECOL) {
         uint4* srec = reinterpret_cast<uint4*>(smem + p.act_off);
-        for (int i = tid; i < nb * 4; i += kConsumers) {
-            const int b = i >> 2, tg = i & 3;
-            uint4 r;
-            r.x = xqw[b * 8 + tg];
-            r.y = xqw[b * 8 + 4 + tg];
-            r.z = __float_as_uint(p.xs[b]);
-            r.w = (uint32_t)(p.zp * p.xsum[b]);
-            srec[i] = r;
+        for (int i0 = tid; i0 < nb * 4; i0 += 4 * kConsumers) {
+            uint32_t wa[4], wb[4];
+            float xs[4];
+            int zs[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * kConsumers;
+                if (i < nb * 4) {
+                    const int b = i >> 2, tg = i & 3;
+                    wa[j] = xqw[b * 8 + tg];
+                    wb[j] = xqw[b * 8 + 4 + tg];
+                    xs[j] = p.xs[b];
+                    zs[j] = p.xsum[b];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * kConsumers;
+                if (i < nb * 4) {
+                    const bool hi = BITS == 4 && (i & 1);
+                    uint4 r;
+                    r.x = wa[j];
+                    r.y = wb[j];
+                    r.z = __float_as_uint(hi ? xs[j] * 0.0625f : xs[j]);
+                    r.w = (uint32_t)(kMagicInt - (p.zp * zs[j]) * (hi ? 16 : 1));
+                    srec[i] = r;
+                }
+            }
         }
         return;
     }
@@ -254,7 +280,28 @@ __device__ __forceinline__ void a_frags(const SUnit<BITS>& u, uint32_t (&a)[2][4
     }
 }
 
-template <int BITS, int NT, bool ONECOL>
+// M == 1: lane (gid, tig) owns output row gid + 8*tig of the group.  `codes` points at the
+// lane's 16-byte slot, `scale` at the f32 scale of its row, `rec` at its staged record.
+template <int BITS>
+__device__ __forceinline__ float unit_a8_row(const uint8_t* codes, const float* scale,
+                                             const uint4* rec, bool odd, bool upper, float acc) {
+    SUnit<BITS> u;
+    u.c0 = *reinterpret_cast<const uint4*>(codes);
+    if (BITS == 8) u.c1 = *reinterpret_cast<const uint4*>(codes + 512);
+    const float sc = *scale;
+    const uint4 r = *rec;
+    uint32_t a[2][4];
+    a_frags<BITS>(u, a);
+    int d0[4], d1[4];
+    imma_u8s8(d0, a[0], r.x, r.y);
+    imma_u8s8(d1, a[1], r.x, r.y);
+    // tig 0 -> d0[0] (row gid), 1 -> d0[2] (gid+8), 2 -> d1[0] (gid+16), 3 -> d1[2] (gid+24)
+    const int lo = upper ? d1[0] : d0[0], hi = upper ? d1[2] : d0[2];
+    const float f = __int_as_float((odd ? hi : lo) + (int)r.w) - kMagicFlt;
+    return fmaf(sc * __uint_as_float(r.z), f, acc);
+}
+
+template <int BITS, int NT>
 __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* smem,
                                         const StreamParams& p, int b, int gid, int tig,
                                         float (&acc)[NT][4][2]) {
@@ -264,20 +311,6 @@ __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* sme
     // value of the high-nibble rows is 16x: scale by xs/16 and shift their zero-point term
     constexpr float HI = BITS == 4 ? 0.0625f : 1.0f;
     constexpr int ZSH = BITS == 4 ? 4 : 0;
-    if (ONECOL) {
-        const uint4 r = reinterpret_cast<const uint4*>(smem + p.act_off)[b * 4 + tig];
-        const float xs = __uint_as_float(r.z), xsh = xs * HI;
-        const int ca = kMagicInt - (int)r.w, cb = kMagicInt - ((int)r.w << ZSH);
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            int d[4];
-            imma_acc(d, a[q], r.x, r.y, ca, ca, cb, cb);
-            acc[0][2 * q][0] = fmaf(sc[2 * q] * xs, __int_as_float(d[0]) - kMagicFlt, acc[0][2 * q][0]);
-            acc[0][2 * q + 1][0] =
-                fmaf(sc[2 * q + 1] * xsh, __int_as_float(d[2]) - kMagicFlt, acc[0][2 * q + 1][0]);
-        }
-        return;
-    }
     const int M = p.M, Mz = (M + 1) & ~1;
     const uint2* xB = reinterpret_cast<const uint2*>(smem + p.act_off) + b * M * 4;
     const int2* xz = reinterpret_cast<const int2*>(smem + p.act2_off) + b * Mz;
@@ -390,11 +423,12 @@ __device__ __forceinline__ float stream_reduce_rc(const float* red, int row, int
 template <int BITS, int NT, int MODE, bool ONECOL>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
     constexpr int UNIT = BITS == 4 ? kUnitBytesQ4 : kUnitBytesQ8;
+    constexpr int kUPW = upw_of(BITS), kChunkUnits = chunk_units_of(BITS);
     constexpr int CHUNK_BYTES = kChunkUnits * UNIT;
     constexpr int NV = NT * 8;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_abort;
-    __shared__ int s_last[2];
+    __shared__ int s_last[2], s_cf[2], s_cn[2], s_slot0[2];
     __shared__ long long s_g0;
     __shared__ int s_bstart, s_total;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -415,6 +449,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         s_abort = 0;
     }
     if (tid < 2 * NS) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // Programmatic dependent launch: the next kernel in the stream may be scheduled onto
+    // SMs as this grid's CTAs retire (a no-op for a plain launch).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __syncthreads();
     volatile int* abort_flag = &s_abort;
     const int64_t g0 = s_g0;
@@ -460,8 +497,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     }
 
     // ---------------- consumers ----------------
+    // Everything above (barriers, the weight stream) is independent of earlier kernels;
+    // activations, y and the scratch are not: wait for the preceding grid to finish.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (dbg && tid == 0) dbg[1] = gtime_ns();
-    if (MODE == MODE_A8) stage_a8<ONECOL>(p, smem, tid);
+    if (MODE == MODE_A8) stage_a8<ONECOL, BITS>(p, smem, tid);
     else stage_f(p, smem, tid);
     consumer_bar();
     if (dbg && tid == 0) dbg[2] = gtime_ns();
@@ -478,67 +518,110 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[nt][i][0] = acc[nt][i][1] = 0.f;
     };
-    // cross-warp reduction of the segment [b_from, b_to) of group g, then store
+    // Cross-warp reduction of the segment [b_from, b_to) of group g, then store.  Two
+    // reduction buffers alternate, so one barrier per flush is enough.
+    int flush_no = 0;
     auto flush = [&](int64_t g, int b_from, int b_to) {
         const bool whole = (b_from == 0) && (b_to == nb);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int c = 0; c < (ONECOL ? 1 : 2); ++c)
-                    red[(warp * NV + (nt * 4 + i) * 2 + c) * 32 + lane] = acc[nt][i][c];
-        consumer_bar();
         const int64_t row0 = g * 32;
         float* part = p.partials + ((int64_t)blockIdx.x * 2 + (g == g0 ? 0 : 1)) * M * 32;
-        for (int o = tid; o < M * 32; o += kConsumers) {
-            const int m = o >> 5, row = o & 31;
-            float sum = 0.f;
-            for (int t = 0; t < T; ++t) sum += stream_reduce_rc<NT>(red, row, m * T + t);
-            if (whole) {
-                if (row0 + row < p.out) store_out(p.y, p.out_dtype, (int64_t)m * p.out + row0 + row, sum);
-            } else {
-                part[o] = sum;
+        float* rbuf = red + (flush_no & 1) * (ONECOL ? kCW * 32 : kCW * NV * 32);
+        ++flush_no;
+        if (ONECOL) {
+            rbuf[warp * 32 + lane] = acc[0][0][0];  // row gid + 8*tig of this lane
+            consumer_bar();
+            // thread t: row t >> 4, warp t & 15; 16 neighbouring lanes add up one row
+            const int row = tid >> 4;
+            float sum = rbuf[(tid & 15) * 32 + (row & 7) * 4 + (row >> 3)];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if ((tid & 15) == 0) {
+                if (!whole) part[row] = sum;
+                else if (row0 + row < p.out) store_out(p.y, p.out_dtype, row0 + row, sum);
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+                        rbuf[(warp * NV + (nt * 4 + i) * 2 + c) * 32 + lane] = acc[nt][i][c];
+            consumer_bar();
+            for (int o = tid; o < M * 32; o += kConsumers) {
+                const int m = o >> 5, row = o & 31;
+                float sum = 0.f;
+                for (int t = 0; t < T; ++t) sum += stream_reduce_rc<NT>(rbuf, row, m * T + t);
+                if (!whole) part[o] = sum;
+                else if (row0 + row < p.out)
+                    store_out(p.y, p.out_dtype, (int64_t)m * p.out + row0 + row, sum);
             }
         }
         if (!whole) part_g[npart++] = g;
-        consumer_bar();  // red may be rewritten by the next flush
     };
 
     {
+        constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
         int64_t g = g0;
         int b = b_start, seg_from = b_start, left = total, s = 0;
         uint32_t ph = 0;
         bool alive = true;
-        const uint8_t* ring_w = smem + warp * UNIT;
+        // running pointers: this warp's first unit in ring slot s, and (M == 1) its record
+        const uint8_t* unit0 = smem + warp * UNIT;
+        const uint4* rec = reinterpret_cast<const uint4*>(smem + p.act_off) + (b_start + warp) * 4 + tig;
+        const bool odd = tig & 1, upper = tig & 2;
         zero_acc();
+        if (dbg) {  // timestamp of the first weights; the loop's own wait then passes at once
+            if (!mbar_try(full0, 0)) alive = mbar_wait(full0, 0, abort_flag);
+            if (tid == 0) dbg[3] = gtime_ns();
+        }
         while (left > 0) {
             int n = nb - b < left ? nb - b : left;
             n = n < kChunkUnits ? n : kChunkUnits;
             if (alive && !mbar_try(full0 + 8 * s, ph)) alive = mbar_wait(full0 + 8 * s, ph, abort_flag);
-            if (dbg && tid == 0 && left == total) dbg[3] = gtime_ns();
-            if (alive && warp < n) {
-                const uint8_t* slot = ring_w + s * CHUNK_BYTES;
-                SUnit<BITS> ua, ub;
-                const bool two = warp + kCW < n;
-                lds_unit<BITS>(ua, slot, lane);
-                if (two) lds_unit<BITS>(ub, slot + kCW * UNIT, lane);
-                if (MODE == MODE_A8) {
-                    unit_a8<BITS, NT, ONECOL>(ua, smem, p, b + warp, gid, tig, acc);
-                    if (two) unit_a8<BITS, NT, ONECOL>(ub, smem, p, b + warp + kCW, gid, tig, acc);
+            if (alive) {
+                if (ONECOL) {
+                    float v = acc[0][0][0];
+                    if (n == kChunkUnits) {
+#pragma unroll
+                        for (int j = 0; j < kUPW; ++j) {
+                            const uint8_t* un = unit0 + j * kCW * UNIT;
+                            v = unit_a8_row<BITS>(un + lane * 16, reinterpret_cast<const float*>(un + CODES) + lane,
+                                                  rec + j * kCW * 4, odd, upper, v);
+                        }
+                    } else {
+                        for (int j = 0; warp + j * kCW < n; ++j) {
+                            const uint8_t* un = unit0 + j * kCW * UNIT;
+                            v = unit_a8_row<BITS>(un + lane * 16, reinterpret_cast<const float*>(un + CODES) + lane,
+                                                  rec + j * kCW * 4, odd, upper, v);
+                        }
+                    }
+                    acc[0][0][0] = v;
                 } else {
-                    unit_f<BITS, NT>(ua, smem, p, b + warp, gid, tig, acc);
-                    if (two) unit_f<BITS, NT>(ub, smem, p, b + warp + kCW, gid, tig, acc);
+                    for (int j = 0; warp + j * kCW < n; ++j) {
+                        SUnit<BITS> un;
+                        lds_unit<BITS>(un, unit0 + j * kCW * UNIT, lane);
+                        const int blk = b + warp + j * kCW;
+                        if (MODE == MODE_A8) unit_a8<BITS, NT>(un, smem, p, blk, gid, tig, acc);
+                        else unit_f<BITS, NT>(un, smem, p, blk, gid, tig, acc);
+                    }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);  // also when not alive: never block the producer
             b += n;
             left -= n;
-            if (++s == NS) { s = 0; ph ^= 1u; }
+            rec += n * 4;
+            unit0 += CHUNK_BYTES;
+            if (++s == NS) {
+                s = 0;
+                ph ^= 1u;
+                unit0 -= (size_t)NS * CHUNK_BYTES;
+            }
             if (b == nb || left == 0) {
                 flush(g, seg_from, b);
                 ++g;
+                rec -= b * 4;  // back to block 0 of the next group
                 b = 0;
                 seg_from = 0;
                 zero_acc();
@@ -548,10 +631,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 
     if (dbg && tid == 0) dbg[4] = gtime_ns();
     // Groups this CTA shares with its neighbours: count in (one fence, both counters at
-    // once), and the last CTA to arrive adds the partials up in CTA order.
+    // once); the last CTA to arrive adds the partials up in CTA order.  Thread 0 works out
+    // who shares the group and which of their two partial slots holds it.
     if (npart > 0) {
+        consumer_bar();  // every partial store of this CTA is done
         if (tid == 0) {
-            __threadfence();  // partial stores of the whole CTA (ordered by the flush barrier)
+            __threadfence();  // ... and ordered before the counter updates
             int prev[2] = {0, 0};
             for (int i = 0; i < npart; ++i) prev[i] = atomicAdd(&p.counters[part_g[i]], 1);
             for (int i = 0; i < npart; ++i) {
@@ -559,23 +644,25 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 const int cf = cta_of_unit(g * nb, p.uq, p.ur);
                 const int cl = cta_of_unit((g + 1) * nb - 1, p.uq, p.ur);
                 s_last[i] = (prev[i] == cl - cf);
+                s_cf[i] = cf;
+                s_cn[i] = cl - cf + 1;
+                // CTA cf holds the group as its last segment unless the group starts its range;
+                // every later sharer holds it as its first segment
+                s_slot0[i] = (range_begin(cf, p.uq, p.ur) >= g * nb) ? 0 : 1;
             }
-            __threadfence();
         }
         consumer_bar();
         for (int i = 0; i < npart; ++i) {
             if (!s_last[i]) continue;
             const int64_t g = part_g[i];
-            const int cf = cta_of_unit(g * nb, p.uq, p.ur);
-            const int cl = cta_of_unit((g + 1) * nb - 1, p.uq, p.ur);
+            const int cf = s_cf[i], cn = s_cn[i];
             const int64_t row0 = g * 32;
             for (int o = tid; o < M * 32; o += kConsumers) {
                 const int m = o >> 5, row = o & 31;
-                float sum = 0.f;
-                for (int cc = cf; cc <= cl; ++cc) {
-                    const int slot = (range_begin(cc, p.uq, p.ur) / nb == g) ? 0 : 1;
-                    sum += __ldcg(p.partials + ((int64_t)cc * 2 + slot) * M * 32 + o);
-                }
+                // partials are read from L2 (ld.cg): the writers fenced before counting in
+                float sum = __ldcg(p.partials + ((int64_t)cf * 2 + s_slot0[i]) * M * 32 + o);
+                for (int k = 1; k < cn; ++k)
+                    sum += __ldcg(p.partials + ((int64_t)(cf + k) * 2) * M * 32 + o);
                 if (row0 + row < p.out) store_out(p.y, p.out_dtype, (int64_t)m * p.out + row0 + row, sum);
             }
             if (tid == 0) p.counters[g] = 0;
@@ -597,12 +684,13 @@ struct StreamPlan {
 static StreamPlan plan_stream(const DeviceState& ds, int bits, int NT, int64_t groups, int64_t nb,
                               int64_t act_bytes, int64_t act2_bytes) {
     StreamPlan pl{};
+    const int kChunkUnits = chunk_units_of(bits);
     const int chunk = kChunkUnits * unit_bytes(bits);
-    const int64_t red = (int64_t)kCW * NT * 8 * 32 * 4;
+    const int64_t red = 2 * (int64_t)kCW * NT * 8 * 32 * 4;  // two alternating reduction buffers
     const int64_t a1 = (act_bytes + 127) & ~127ll, a2 = (act2_bytes + 127) & ~127ll;
     const int64_t room = kMaxDynSmem - (a1 + a2 + red + 512);
     int64_t ns = room / chunk;
-    if (ns > 8) ns = 8;
+    if (ns > 6) ns = 6;
     pl.fits = ns >= 2;
     if (!pl.fits) return pl;
     const int64_t U = groups * nb;
@@ -662,6 +750,22 @@ static void fill_common(StreamParams& p, const DeviceState& ds, const StreamPlan
     p.act_off = pl.act_off; p.act2_off = pl.act2_off; p.red_off = pl.red_off; p.bar_off = pl.bar_off;
 }
 
+template <typename K>
+static cudaError_t launch_stream(K kernel, const DeviceState& ds, const StreamPlan& pl,
+                                 const StreamParams& p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl.G);
+    cfg.blockDim = dim3(kStreamThreads);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = ds.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ds.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // Largest token count <= want whose staged activations fit next to a ring of >= 2 chunks.
 template <typename BytesFn>
 static int fit_tokens(const DeviceState& ds, int bits, int64_t groups, int64_t nb, int want, BytesFn f,
@@ -705,7 +809,8 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         p.xsum = a.xsum + m0 * nb;
         p.y = a.y + m0 * a.out;
         p.T = 1; p.act_dtype = RSTQ_F32; p.out_dtype = RSTQ_F32;
-#define LAUNCH(...) gemv_stream_kernel<__VA_ARGS__><<<pl.G, kStreamThreads, pl.smem, ds.stream>>>(p)
+        cudaError_t le = cudaSuccess;
+#define LAUNCH(...) le = launch_stream(gemv_stream_kernel<__VA_ARGS__>, ds, pl, p)
         if (a.bits == 4) {
             if (NT == 2) LAUNCH(4, 2, MODE_A8, false);
             else if (M == 1) LAUNCH(4, 1, MODE_A8, true);
@@ -716,6 +821,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
             else LAUNCH(8, 1, MODE_A8, false);
         }
         ctx->launches++;
+        RSTQ_CUDA(le);
         RSTQ_CUDA(cudaGetLastError());
         m0 += M;
     }
@@ -728,7 +834,10 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
     RSTQ_REQUIRE(nb < (1 << 24) && groups * nb < (1ll << 40), RSTQ_E_LIMIT, "matrix too large");
     // f32 activations are expanded into exact bf16 terms: three while they fit one
     // 8-column tile, else two (16 significant bits).
-    auto terms = [&](int m) { return a.act_dtype == RSTQ_F32 ? ((3 * m <= 8) ? 3 : 2) : 1; };
+    int max_terms = 3;
+    auto terms = [&](int m) {
+        return a.act_dtype == RSTQ_F32 ? ((3 * m <= 8 && max_terms == 3) ? 3 : 2) : 1;
+    };
     auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
         const int C = m * terms(m);
         *NT = C <= 8 ? 1 : (C <= 16 ? 2 : 4);
@@ -739,7 +848,11 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
     for (int64_t m0 = 0; m0 < a.M;) {
         const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
         StreamPlan pl;
-        const int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
+        int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
+        if (M < 1 && max_terms == 3) {
+            max_terms = 2;  // a very long row: two bf16 terms (16 significant bits) per element
+            M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
+        }
         RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
                      (long long)a.in);
         int32_t rc = stream_scratch_ok(ds, groups, pl.G, M);
@@ -752,6 +865,7 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
         p.x = (const char*)a.x + m0 * a.in * xe;
         p.y = (char*)a.y + m0 * a.out * ye;
         p.T = T; p.act_dtype = a.act_dtype; p.out_dtype = a.out_dtype;
+        cudaError_t le = cudaSuccess;
         if (a.bits == 4) {
             if (NT == 1) LAUNCH(4, 1, MODE_F, false);
             else if (NT == 2) LAUNCH(4, 2, MODE_F, false);
@@ -763,6 +877,7 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
         }
 #undef LAUNCH
         ctx->launches++;
+        RSTQ_CUDA(le);
         RSTQ_CUDA(cudaGetLastError());
         m0 += M;
     }

@@ -64,6 +64,7 @@ struct DeviceState {
     int cc = 0;
     cudaStream_t stream = nullptr;
     bool capturing = false;
+    bool pdl = true;               // launch the hot kernels with programmatic stream serialization
     // scratch owned by the context
     void* act_scratch = nullptr;   // quantized / converted activations
     int64_t act_scratch_bytes = 0;
