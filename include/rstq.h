@@ -161,6 +161,21 @@ RSTQ_API int32_t rstq_qmatmul(rstq_ctx* ctx, rstq_weight* w, rstq_buf* x, rstq_b
 RSTQ_API int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_buf* xs,
                                        rstq_buf* xsum, rstq_buf* y, int64_t M);
 
+/* Allocation-free form of rstq_qmatmul_prequant: same arithmetic and the same kernel, for
+ * hosts that may not allocate device memory when they call -- a runtime that owns all
+ * device memory through its own arena, a caller inside a stream capture, a decode loop that
+ * must stay clear of the driver's allocator.  Has no counterpart in the reference.
+ * xq / xs / xsum / y are plain 16-byte-aligned device pointers (int8 [M, in], f32 [M, nb],
+ * int32 [M, nb], f32 [M, out]) on the weight's device; `stream` is a cudaStream_t, or NULL for
+ * the context's own stream.  The split-group scratch lives in fixed arrays inside the
+ * library's device image (about 1.3 MB held by every GPU that loads the library, until
+ * exit), hence the limits: out <= 2 097 152 rows (RSTQ_E_LIMIT beyond), M cut into launches of
+ * <= 16.  The first call on a device resolves the arrays' addresses and clears the counters:
+ * make that call before any stream capture.  Every call shares the arrays: calls that could
+ * overlap on the GPU must be serialised by the caller.  No cudaMalloc / cudaFree is reached. */
+RSTQ_API int32_t rstq_qmatmul_prequant_noalloc(rstq_weight* w, const void* xq, const void* xs,
+                                               const void* xsum, void* y, void* stream, int64_t M);
+
 /* ---- the operators on HOST arrays, same argument order as the reference's
  *      CPU operators, so the Clojure method bodies change one call.  x and y
  *      cross PCIe on every call; the weight is uploaded and re-tiled on first

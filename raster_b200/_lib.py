@@ -38,6 +38,7 @@ SIGNATURES = {
     "rstq_quant_act_i8": [vp, vp, vp, vp, vp, i64, i64],
     "rstq_qmatmul": [vp, vp, vp, vp, i64, i32, i32, i32],
     "rstq_qmatmul_prequant": [vp, vp, vp, vp, vp, vp, i64],
+    "rstq_qmatmul_prequant_noalloc": [vp, vp, vp, vp, vp, vp, i64],
     "rstq_qlinear_i8": [vp, vp, vp, vp, vp, i64, i64],
     "rstq_qlinear_i8_q8": [vp, vp, vp, vp, vp, i64, i64],
     "rstq_qlinear_q8": [vp, vp, vp, vp, vp, i64, i64, i64],

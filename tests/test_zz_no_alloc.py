@@ -1,0 +1,65 @@
+"""The allocation-free decode entry point against the regular one.
+
+Some hosts cannot allocate device memory at call time: a runtime that took all device memory
+into its own arena up front, code running inside a stream capture, a decode loop that must not
+touch the driver's allocator.  For them `rstq_qmatmul_prequant_noalloc` keeps its scratch in
+fixed arrays of the library's device image.  It must give what `rstq_qmatmul_prequant` gives,
+also on a second call (the arrays keep the first call's contents), whether this file runs
+alone in a fresh process or last after every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from raster_b200 import _lib as L
+from raster_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("bits,fmt", [(4, L.FMT_Q4_0), (8, L.FMT_Q8_0)])
+@pytest.mark.parametrize("out,in_,M", [(4096, 11008, 1), (1000, 2048, 3), (11008, 4096, 8)])
+def test_noalloc_matches_regular_entry_twice(ctx, bits, fmt, out, in_, M):
+    w = synth.normal(out + in_, out * in_, 0.02)
+    wq, ws = orc.quantize_weight(w, bits)
+    x = synth.normal(out + in_ + 1, M * in_)
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    bw = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    bq, bs, bsum = ctx.array_to_buffer(xq), ctx.array_to_buffer(xs), ctx.array_to_buffer(xsum)
+    y_ref, y_na = ctx.make_buffer(M * out, np.float32), ctx.make_buffer(M * out, np.float32)
+    ctx.qmatmul_prequant(bw, bq, bs, bsum, y_ref, M)
+    ctx.sync()
+    ref = y_ref.download()
+    oracle = orc.matmul_a8_f64(wq, ws, 0 if bits == 4 else 1, xq, xs, xsum, M, in_, out).ravel()
+    scale = np.abs(oracle).max()
+    assert np.abs(ref - oracle).max() <= 2e-6 * scale
+    for call in range(2):
+        y_na.fill_bytes(0xFF)
+        L.check(ctx.lib.rstq_qmatmul_prequant_noalloc(
+            bw.handle, C.c_void_p(bq.device_ptr), C.c_void_p(bs.device_ptr),
+            C.c_void_p(bsum.device_ptr), C.c_void_p(y_na.device_ptr), None, M))
+        ctx.sync()
+        got = y_na.download()
+        assert np.abs(got - ref).max() <= 2e-6 * scale, f"call {call}"
+        assert np.abs(got - oracle).max() <= 2e-6 * scale, f"call {call}"
+    for b in (bq, bs, bsum, y_ref, y_na):
+        b.free()
+    bw.free()
+
+
+def test_noalloc_rejects_what_exceeds_its_fixed_scratch(ctx):
+    # a weight handle with more rows than the fixed counters cover cannot be built cheaply;
+    # check the argument validation that guards the kernel instead
+    rc = ctx.lib.rstq_qmatmul_prequant_noalloc(None, None, None, None, None, None, 1)
+    assert rc == L.E_INVALID
+    bw = ctx.bind_weight(np.full(16 * 8, 0x88, np.uint8), np.ones(8, np.float32), 8, 32,
+                         L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    buf = ctx.make_buffer(64, np.float32)
+    p = C.c_void_p(buf.device_ptr)
+    assert ctx.lib.rstq_qmatmul_prequant_noalloc(bw.handle, p, p, p, p, None, 0) == L.E_SHAPE
+    mis = C.c_void_p(buf.device_ptr + 4)
+    assert ctx.lib.rstq_qmatmul_prequant_noalloc(bw.handle, mis, p, p, p, None, 1) == L.E_ALIGN
+    buf.free()
+    bw.free()
