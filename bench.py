@@ -260,8 +260,7 @@ def run_ours(args):
                     "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s",
                     "frac": round(achieved / hbm_peak, 4), "frac_of_nominal_8TBs": round(achieved / 8000.0, 4),
                     # dram__bytes_read.sum + dram__bytes_write.sum per launch of this kernel at the
-                    # 11008x4096 shape, from the ncu capture summarised in
-                    # profiles/gemv_stream_q4_m1_11008x4096.md (both shapes stream the same bytes)
+                    # 11008x4096 shape, from one ncu capture (both shapes stream the same bytes)
                     "traffic": 28222976, "avg_launch_us": round(avg_launch_s * 1e6, 3),
                     "algorithmic_bytes_per_launch": alg}
         g_gemv.destroy()
