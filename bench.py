@@ -429,7 +429,7 @@ def run_case(args):
     from raster_b200 import Context
     from raster_b200 import _lib as L
     from raster_b200.quant import cpu_quant as cq
-    _, bits, out, in_, M, mode = args.case.split(":")
+    kind, bits, out, in_, M, mode = (args.case.split(":") + ["f"])[:6]
     bits, out, in_, M = int(bits), int(out), int(in_), int(M)
     rng = np.random.default_rng(0)
     ctx = Context(("cuda:0",))
@@ -445,11 +445,17 @@ def run_case(args):
     bq, bs, bsum = (ctx.array_to_buffer(a["xq"]), ctx.array_to_buffer(a["xs"]),
                     ctx.array_to_buffer(a["xsum"]))
     bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    if kind == "gemm":      # prefill: bf16 activations in, bf16 out
+        from raster_b200 import synth
+        bx16 = ctx.array_to_buffer(synth.to_bf16_bits(x))
+        by16 = ctx.make_buffer(M * out, np.uint16)
     e0, e1 = ctx.event(), ctx.event()
     for it in range(2):
         e0.record()
         for w in ws:
-            if mode == "a8":
+            if kind == "gemm":
+                ctx.qmatmul(w, bx16, by16, M, L.BF16, L.BF16, L.MODE_F)
+            elif mode == "a8":
                 ctx.qmatmul_prequant(w, bq, bs, bsum, by, M)
             else:
                 ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_F)
@@ -457,7 +463,8 @@ def run_case(args):
         ctx.sync()
     us = e0.elapsed_ms(e1) * 1e3 / R
     print(json.dumps({"case": args.case, "launches": 2 * R, "us_per_launch": round(us, 2),
-                      "GBs": round(w0.stream_bytes / us / 1e3, 1)}))
+                      "GBs": round(w0.stream_bytes / us / 1e3, 1),
+                      "TFLOPs": round(2.0 * M * out * in_ / us / 1e6, 1)}))
     ctx.close()
 
 

@@ -2,6 +2,7 @@
 // graphs and events.  See include/rstq.h for the contract of each entry point.
 #include <stdarg.h>
 #include <stdio.h>
+#include <math.h>
 #include <string.h>
 
 #include <new>
@@ -41,7 +42,7 @@ static int32_t use_dev(rstq_ctx* ctx, int dev) {
 }
 
 // grow-only scratch helpers (never called while capturing)
-static int32_t ensure_dev(DeviceState& ds, void** p, int64_t* have, int64_t need) {
+int32_t dev_reserve(DeviceState& ds, void** p, int64_t* have, int64_t need) {
     if (need <= *have) return RSTQ_OK;
     RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE,
                  "scratch must grow (%lld bytes) during graph capture; run the call once before "
@@ -112,7 +113,7 @@ static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* o
     const int64_t nb = in / 32;
     const int64_t xq_bytes = (M * in + 255) & ~255ll;
     const int64_t sb = (M * nb * 4 + 255) & ~255ll;
-    int32_t rc = ensure_dev(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 2 * sb);
+    int32_t rc = dev_reserve(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 2 * sb);
     if (rc != RSTQ_OK) return rc;
     char* base = (char*)ds.act_scratch;
     out->xq = (int8_t*)base;
@@ -134,20 +135,44 @@ static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int6
     return launch_gemv_f(ctx, ctx->devs[w->dev], a);
 }
 
+// fp16 activation scratch of the tensor-core path: [x16: M*in halves][rowscale: M floats]
+static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, void** x16, float** rowscale) {
+    const int64_t xb = (M * in * 2 + 255) & ~255ll;
+    int32_t rc = dev_reserve(ds, &ds.gemm_scratch, &ds.gemm_scratch_bytes, xb + M * 4);
+    if (rc != RSTQ_OK) return rc;
+    *x16 = ds.gemm_scratch;
+    *rowscale = (float*)((char*)ds.gemm_scratch + xb);
+    return RSTQ_OK;
+}
+
 static int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
                              int act_dtype, int out_dtype, int mode) {
     DeviceState& ds = ctx->devs[w->dev];
+    // Prefill shapes go to the tensor-core GEMM (fp16 operands, results within 1e-3 of the
+    // reference).  A8 keeps its exact integer path up to M = 63: callers that chose the
+    // quantized-activation arithmetic get it bit-faithfully at decode and small-batch sizes.
+    const bool tc = M >= (mode == RSTQ_MODE_A8 ? (ctx->tune_gemm_min_m > 64 ? ctx->tune_gemm_min_m : 64)
+                                                : ctx->tune_gemm_min_m);
     if (mode == RSTQ_MODE_A8) {
-        RSTQ_REQUIRE(act_dtype == RSTQ_F32 && out_dtype == RSTQ_F32, RSTQ_E_INVALID,
-                     "MODE_A8 takes f32 activations and writes f32");
+        RSTQ_REQUIRE(act_dtype == RSTQ_F32, RSTQ_E_INVALID, "MODE_A8 takes f32 activations");
+        RSTQ_REQUIRE(out_dtype == RSTQ_F32 || tc, RSTQ_E_INVALID, "MODE_A8 decode writes f32");
         ActScratch s;
         int32_t rc = act_scratch(ds, M, w->in, &s);
         if (rc != RSTQ_OK) return rc;
         rc = launch_quant_act_i8(ctx, ds, (const float*)x, s.xq, s.xs, s.xsum, M, w->in);
         if (rc != RSTQ_OK) return rc;
-        return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M);
+        if (!tc) return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M);
+        void* x16;
+        float* rowscale;
+        if ((rc = gemm_scratch(ds, M, w->in, &x16, &rowscale)) != RSTQ_OK) return rc;
+        return launch_gemm(ctx, ds, w, s.xq, s.xs, 2, y, out_dtype, M, x16, rowscale);
     }
-    return run_f(ctx, w, x, y, M, act_dtype, out_dtype);
+    if (!tc) return run_f(ctx, w, x, y, M, act_dtype, out_dtype);
+    void* x16;
+    float* rowscale;
+    int32_t rc = gemm_scratch(ds, M, w->in, &x16, &rowscale);
+    if (rc != RSTQ_OK) return rc;
+    return launch_gemm(ctx, ds, w, x, nullptr, act_dtype == RSTQ_F32 ? 0 : 1, y, out_dtype, M, x16, rowscale);
 }
 
 static int32_t bind_impl(rstq_ctx* ctx, rstq_weight** wout, const void* codes,
@@ -215,6 +240,17 @@ static int32_t bind_impl(rstq_ctx* ctx, rstq_weight** wout, const void* codes,
     w->nb = sh_in / 32;
     w->data_bytes = (w->outp / 32) * w->nb * unit_bytes(bits);
     w->data = nullptr;
+    {
+        float mxs = 0.f;
+        const int64_t ns = sh_out * nb_full;
+        for (int64_t i = 0; i < ns; ++i) {
+            const float a = fabsf(hscales[i]);
+            if (a > mxs && a < 3.0e38f) mxs = a;
+        }
+        int ex = 0;
+        if (mxs > 0.f) frexpf(mxs, &ex);       // mxs = f * 2^ex, f in [0.5, 1)
+        w->gemm_exp = mxs > 0.f ? 7 - ex : 0;  // largest scaled |weight| = 128 * f * 2^7 < 2^14
+    }
     uint8_t *stage_c = nullptr;
     float* stage_s = nullptr;
     cudaError_t e = cudaMalloc((void**)&w->data, (size_t)w->data_bytes);
@@ -311,6 +347,7 @@ int32_t rstq_init(const int32_t* devices, int32_t ndev, rstq_ctx** ctxp) {
             RSTQ_CUDA(cudaMemsetAsync(ds.status, 0, 256, ds.stream));
             int32_t r = gemv_configure(ds);
             if (r != RSTQ_OK) return r;
+            if ((r = gemm_configure(ds)) != RSTQ_OK) return r;
             RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
             return RSTQ_OK;
         };
@@ -346,6 +383,7 @@ int32_t rstq_shutdown(rstq_ctx* ctx) {
         cudaSetDevice(ds.ordinal);
         if (ds.stream) cudaStreamSynchronize(ds.stream);
         if (ds.act_scratch) cudaFree(ds.act_scratch);
+        if (ds.gemm_scratch) cudaFree(ds.gemm_scratch);
         if (ds.partials) cudaFree(ds.partials);
         if (ds.counters) cudaFree(ds.counters);
         if (ds.status) cudaFree(ds.status);
@@ -673,7 +711,7 @@ int32_t host_roundtrip(rstq_ctx* ctx, int dev, const void* x, int64_t x_bytes, v
     if (rc != RSTQ_OK) return rc;
     const int64_t xa = (x_bytes + 255) & ~255ll, ya = (y_bytes + 255) & ~255ll;
     if ((rc = ensure_pinned(ds, xa + ya)) != RSTQ_OK) return rc;
-    if ((rc = ensure_dev(ds, &ds.io_dev, &ds.io_dev_bytes, xa + ya)) != RSTQ_OK) return rc;
+    if ((rc = dev_reserve(ds, &ds.io_dev, &ds.io_dev_bytes, xa + ya)) != RSTQ_OK) return rc;
     char* hp = (char*)ds.pinned;
     char* dp = (char*)ds.io_dev;
     memcpy(hp, x, (size_t)x_bytes);
@@ -742,7 +780,7 @@ int32_t rstq_qmatmul_i8_gemm(rstq_ctx* ctx, const int32_t* xp, const float* xs, 
     const int64_t xq_b = (nrows * in + 255) & ~255ll, xs_b = (nrows * nb * 4 + 255) & ~255ll;
     const int64_t y_b = (nrows * out * 4 + 255) & ~255ll;
     if ((rc = ensure_pinned(ds, xq_b + xs_b + y_b)) != RSTQ_OK) return rc;
-    if ((rc = ensure_dev(ds, &ds.io_dev, &ds.io_dev_bytes, xq_b + xs_b + y_b)) != RSTQ_OK) return rc;
+    if ((rc = dev_reserve(ds, &ds.io_dev, &ds.io_dev_bytes, xq_b + xs_b + y_b)) != RSTQ_OK) return rc;
     ActScratch s;
     if ((rc = act_scratch(ds, nrows, in, &s)) != RSTQ_OK) return rc;
     char* hp = (char*)ds.pinned;
@@ -778,7 +816,7 @@ int32_t rstq_i8gemv_dp4a(rstq_ctx* ctx, const int32_t* wp, const int32_t* xp, fl
     const int64_t w_b = (out * kw * 4 + 255) & ~255ll, x_b = (kw * 4 + 255) & ~255ll;
     const int64_t y_b = (out * 4 + 255) & ~255ll;
     if ((rc = ensure_pinned(ds, x_b + y_b)) != RSTQ_OK) return rc;
-    if ((rc = ensure_dev(ds, &ds.io_dev, &ds.io_dev_bytes, w_b + x_b + y_b)) != RSTQ_OK) return rc;
+    if ((rc = dev_reserve(ds, &ds.io_dev, &ds.io_dev_bytes, w_b + x_b + y_b)) != RSTQ_OK) return rc;
     char* hp = (char*)ds.pinned;
     char* dp = (char*)ds.io_dev;
     memcpy(hp, xp, (size_t)(kw * 4));

@@ -30,6 +30,7 @@
 //    status word instead of hanging.
 #include "internal.h"
 #include "mma_helpers.cuh"
+#include "sync_helpers.cuh"
 
 namespace rstq {
 
@@ -39,7 +40,6 @@ constexpr int kStreamThreads = kConsumers + 32;  // + producer warp
 // units per consumer warp per chunk: 4 (40 KB chunks) for 4-bit, 2 (36 KB chunks) for 8-bit
 __host__ __device__ constexpr int upw_of(int bits) { return bits == 4 ? 4 : 2; }
 __host__ __device__ constexpr int chunk_units_of(int bits) { return upw_of(bits) * kCW; }
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
 constexpr int kMaxDynSmem = 232448 - 1024;       // 227 KB opt-in limit less the static part
 constexpr int kMagicInt = 0x4B400000;            // bits of 12582912.0f = 2^23 + 2^22
 constexpr float kMagicFlt = 12582912.0f;
@@ -63,57 +63,6 @@ struct StreamParams {
     uint32_t act_off, act2_off, red_off, bar_off;  // byte offsets into dynamic smem (ring at 0)
 };
 
-// ---- mbarrier / bulk-copy primitives -------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar),
-                 "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long gtime_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Slow path of a time-bounded wait.  Returns false when the limit ran out or
-// another warp already gave up (abort flag); the caller then skips its work but
-// keeps meeting every CTA barrier so nobody is left waiting.
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    const unsigned long long t0 = gtime_ns();
-    for (;;) {
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (gtime_ns() - t0 > kWaitLimitNs) {
-            *abort_flag = 1;
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                              uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
-}
 __device__ __forceinline__ void consumer_bar() {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
 }

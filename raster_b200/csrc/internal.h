@@ -72,6 +72,8 @@ struct DeviceState {
     int64_t partials_bytes = 0;
     int* counters = nullptr;       // split-K arrival counters (zero between calls)
     int64_t counters_len = 0;
+    void* gemm_scratch = nullptr;  // fp16 activations + row exponents of the GEMM path
+    int64_t gemm_scratch_bytes = 0;
     void* pinned = nullptr;        // host staging for the host-array entry points
     int64_t pinned_bytes = 0;
     void* io_dev = nullptr;        // device staging for the host-array entry points
@@ -126,6 +128,7 @@ struct rstq_weight {
     int64_t nb;        // in / 32
     uint8_t* data;     // mma32 units, (outp/32) * nb of them
     int64_t data_bytes;
+    int gemm_exp;      // power of two applied to the block scales in the fp16 GEMM path
 };
 
 struct rstq_graph {
@@ -182,6 +185,12 @@ struct GemvFArgs {
 int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a);
 int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a);
 int32_t gemv_configure(DeviceState& ds);  // shared-memory attributes, once per device
+// gemm_tc.cu
+int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const void* x, const float* xs,
+                    int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale);
+int32_t gemm_configure(DeviceState& ds);
+// capi.cu: grow-only device scratch (refuses to grow during graph capture)
+int32_t dev_reserve(DeviceState& ds, void** p, int64_t* have, int64_t need);
 constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels
 
 }  // namespace rstq

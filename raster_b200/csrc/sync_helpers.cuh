@@ -1,0 +1,60 @@
+// Device helpers shared by the kernels that use mbarriers and bulk async copies:
+// barrier init / arrive / time-bounded wait, the global timer, 1-D bulk copies.
+#pragma once
+#include <stdint.h>
+
+namespace rstq {
+
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Slow path of a time-bounded wait.  Returns false when the limit ran out or
+// another warp already gave up (abort flag); the caller then skips its work but
+// keeps meeting every CTA barrier so nobody is left waiting.
+static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const unsigned long long t0 = gtime_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (gtime_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                              uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+}  // namespace rstq

@@ -1,0 +1,86 @@
+"""Parity of the prefill tensor-core GEMM (M > 16) against the CPU oracle.
+
+The GEMM multiplies fp16 dequantized weights by fp16 activations (one power-of-two
+exponent per token row) and accumulates in f32.  Stated bounds, on the reference's metric
+max|y - y_ref| / max|y_ref|: f32 output <= 1e-3; bf16 output: per element
+|y - y_ref| <= 2^-8 |y_ref| + 1e-3 max|y_ref|.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from raster_b200 import _lib as L
+from raster_b200 import synth
+from raster_b200.quant import kernels_k, pack
+
+pytestmark = pytest.mark.gpu
+
+FMT = {4: (L.FMT_Q4_0, 0), 8: (L.FMT_Q8_0, 1)}
+
+
+def relerr(y, ref):
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.abs(np.asarray(y, dtype=np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def sample_rows(out, n=192):
+    return np.unique(np.concatenate([np.arange(0, out, max(1, out // n)), [out - 1]]))
+
+
+def oracle_rows(wq, ws, ofmt, x, M, in_, out, rows, bits):
+    cb = in_ * bits // 8
+    c = np.ascontiguousarray(wq.reshape(out, cb)[rows]).ravel()
+    s = np.ascontiguousarray(ws.reshape(out, in_ // 32)[rows]).ravel()
+    return orc.matmul_dq_f64(c, s, ofmt, x, M, in_, rows.size)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("out,in_,M", [(128, 128, 17), (200, 160, 33), (512, 1024, 64), (300, 4096, 100),
+                                       (4096, 4096, 512), (1024, 11008, 130)])
+def test_gemm_f32_and_bf16_activations(ctx, bits, out, in_, M):
+    fmt, ofmt = FMT[bits]
+    w = synth.normal(out + in_ + bits, out * in_, 0.02)
+    wq, ws = orc.quantize_weight(w, bits)
+    x = synth.normal(out + in_ + M, M * in_)
+    bw = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    rows = sample_rows(out)
+    ref = oracle_rows(wq, ws, ofmt, x, M, in_, out, rows, bits)
+    y = ctx.qmatmul_host(bw, x, M, L.F32, L.MODE_F)
+    assert relerr(y[:, rows], ref) <= 1e-3
+    # bf16 activations in, bf16 out (the prefill configuration)
+    xb = synth.to_bf16_bits(x)
+    refb = oracle_rows(wq, ws, ofmt, synth.from_bf16_bits(xb), M, in_, out, rows, bits)
+    bx, by = ctx.array_to_buffer(xb), ctx.make_buffer(M * out, np.uint16)
+    ctx.qmatmul(bw, bx, by, M, L.BF16, L.BF16, L.MODE_F)
+    ctx.sync()
+    yb = synth.from_bf16_bits(by.download()).reshape(M, out)[:, rows]
+    assert np.all(np.abs(yb - refb) <= 2.0 ** -8 * np.abs(refb) + 1e-3 * np.abs(refb).max())
+    bx.free(), by.free(), bw.free()
+
+
+def test_gemm_quantized_activation_mode(ctx):
+    """MODE_A8 at prefill size: exact activation codes, fp16 tensor-core product."""
+    out, in_, M = 512, 1024, 96
+    w = synth.normal(3, out * in_, 0.02)
+    wq, ws = orc.quantize_weight(w, 4)
+    x = synth.normal(4, M * in_)
+    bw = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    y = ctx.qmatmul_host(bw, x, M, L.F32, L.MODE_A8)
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out)
+    assert relerr(y, ref) <= 1e-3
+    bw.free()
+
+
+def test_gemm_extreme_magnitudes_stay_finite(ctx):
+    out, in_, M = 128, 256, 32
+    w = synth.normal(5, out * in_, 1e-6)             # tiny weights: scales far below fp16 range
+    wq, ws = orc.quantize_weight(w, 8)
+    x = synth.normal(6, M * in_) * 1e6               # huge activations
+    x[: in_] = 0.0                                   # an all-zero token row
+    bw = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q8_0, L.LAYOUT_ROWMAJOR)
+    y = ctx.qmatmul_host(bw, x, M, L.F32, L.MODE_F)
+    ref = orc.matmul_dq_f64(wq, ws, 1, x, M, in_, out)
+    assert np.isfinite(y).all() and not y[0].any()
+    assert relerr(y, ref) <= 1e-3
+    bw.free()

@@ -27,6 +27,7 @@ pytestmark = pytest.mark.gpu
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "qmatmul_small.npz"))
 TOL_A8 = 2e-6
 TOL_F = 2e-5
+TOL_GEMM = 1e-3   # M > 16 in F mode: fp16 operands on the tensor cores, f32 accumulate
 FMT = {4: (cq.q4_0, L.FMT_Q4_0, 0), 8: (cq.q8_0, L.FMT_Q8_0, 1)}
 
 
@@ -179,7 +180,7 @@ def test_gemv_f_f32_activations(ctx, bits, out, in_, M):
     w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
     y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_F)
     ref = orc.matmul_dq_f64(wq, ws, ofmt, x, M, in_, out)
-    assert relerr(y, ref) <= (1e-5 if M <= 2 else TOL_F)
+    assert relerr(y, ref) <= (1e-5 if M <= 2 else TOL_F if M <= 16 else TOL_GEMM)
     w.free()
 
 
@@ -212,10 +213,11 @@ def test_qlinear_q8_operator(ctx, m, in_, out):
     q = train.q8_quantize(W, out, in_)
     y = train.qlinear_q8(x, q["codes"], q["scales"], m, in_, out, ctx)
     ref = orc.qlinear_q8(x, q["codes"], q["scales"], m, in_, out)
-    assert relerr(y, ref) <= TOL_F
+    tol = TOL_F if m <= 16 else TOL_GEMM      # m > 16 runs on the fp16 tensor-core path
+    assert relerr(y, ref) <= tol
     dense = x.reshape(m, in_).astype(np.float64) @ \
         train.dequant_q8_dense(q["codes"], q["scales"], in_, out).reshape(out, in_).astype(np.float64).T
-    assert relerr(y.reshape(m, out), dense) <= TOL_F
+    assert relerr(y.reshape(m, out), dense) <= tol
 
 
 # ---------------------------------------------------------------- int32-packed kernels
