@@ -84,6 +84,8 @@ typedef struct rstq_event rstq_event;
 
 /* tuning keys (rstq_tune) */
 #define RSTQ_TUNE_GEMM_MIN_M 1  /* smallest M routed to the tensor-core GEMM (default 17) */
+#define RSTQ_TUNE_GEMM_KERNEL 0  /* prefill GEMM: 0 (default) = dequantized weights kept in tensor
+                                     memory, 1 = staged through shared memory */
 #define RSTQ_TUNE_PDL 2           /* 1 (default) = launch the decode kernels with programmatic
                                      dependent launch so consecutive launches overlap; 0 = plain */
 #define RSTQ_TUNE_TIMELINE 3      /* 1 = streaming kernel records per-CTA phase timestamps */

@@ -422,6 +422,10 @@ int32_t rstq_sync(rstq_ctx* ctx, int32_t dev) {
 int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
     CHECK_CTX(ctx);
     switch (key) {
+        case RSTQ_TUNE_GEMM_KERNEL:
+            RSTQ_REQUIRE(value == 0 || value == 1, RSTQ_E_INVALID, "GEMM kernel selector 0..1");
+            ctx->tune_gemm_kernel = value;
+            return RSTQ_OK;
         case RSTQ_TUNE_PDL:
             for (auto& ds : ctx->devs) ds.pdl = value != 0;
             return RSTQ_OK;

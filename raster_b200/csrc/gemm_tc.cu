@@ -38,7 +38,7 @@ constexpr int kDqWarps = 16;
 constexpr int kGemmThreads = (2 + kDqWarps) * 32;  // TMA warp, MMA warp, 16 dequant/epilogue warps
 constexpr int kKStep = 128;                        // K elements per pipeline stage (4 blocks)
 constexpr int kAStage = 128 * kKStep * 2;          // 32 KB of fp16 weights per stage
-constexpr int kPrefetch = 3;                       // K-steps of packed weights held in registers
+constexpr int kPrefetch = 4;                       // K-steps of packed weights held in registers
 
 // ---- tcgen05 / TMA wrappers -------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -88,6 +88,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ void fence_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -117,13 +120,35 @@ act_to_f16_kernel(const void* __restrict__ x, const float* __restrict__ xs, __ha
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t m = blockIdx.x;
-    auto value = [&](int64_t k) -> float {
-        if (SRC == 0) return reinterpret_cast<const float*>(x)[m * in + k];
-        if (SRC == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[m * in + k]);
-        return (float)reinterpret_cast<const int8_t*>(x)[m * in + k] * xs[m * (in >> 5) + (k >> 5)];
+    // eight consecutive elements (one 16-byte fp16 store) per thread and step
+    auto load8 = [&](int64_t k, float (&v)[8]) {
+        if (SRC == 0) {
+            const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + m * in + k);
+            const float4 a = __ldg(q), b = __ldg(q + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else if (SRC == 1) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + m * in + k));
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[2 * j] = __uint_as_float(w[j] << 16);
+                v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+            }
+        } else {
+            const uint2 a = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(x) + m * in + k));
+            const float sc = __ldg(xs + m * (in >> 5) + (k >> 5));
+            const uint32_t w[2] = {a.x, a.y};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (float)(int8_t)(w[j >> 2] >> (8 * (j & 3))) * sc;
+        }
     };
     float mx = 0.f;
-    for (int64_t k = threadIdx.x; k < in; k += 256) mx = fmaxf(mx, fabsf(value(k)));
+    for (int64_t k = threadIdx.x * 8; k < in; k += 256 * 8) {
+        float v[8];
+        load8(k, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(v[j]));
+    }
     __shared__ float s_mx[8];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -139,7 +164,17 @@ act_to_f16_kernel(const void* __restrict__ x, const float* __restrict__ xs, __ha
         e = ex - 14;
     }
     const float down = ldexpf(1.0f, -e);
-    for (int64_t k = threadIdx.x; k < in; k += 256) x16[m * in + k] = __float2half_rn(value(k) * down);
+    for (int64_t k = threadIdx.x * 8; k < in; k += 256 * 8) {
+        float v[8];
+        load8(k, v);
+        uint32_t h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half2 t = __floats2half2_rn(v[2 * j] * down, v[2 * j + 1] * down);
+            h[j] = *reinterpret_cast<const uint32_t*>(&t);
+        }
+        *reinterpret_cast<uint4*>(x16 + m * in + k) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
     if (threadIdx.x == 0) rowscale[m] = ldexpf(1.0f, e);
 }
 
@@ -156,6 +191,7 @@ struct GemmParams {
     int M, ksteps, ttiles;
     float wmul, wdiv;       // 2^ew applied to the block scales, 2^-ew applied to the result
     int out_dtype;
+    unsigned long long* dbg;  // optional timeline of CTA 0 (see RSTQ_TUNE_TIMELINE), or null
 };
 
 // packed weights of one dequant task, as loaded from global memory
@@ -240,7 +276,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             uint32_t ph = 0;
             bool ok = true;
             for (int ks = 0; ks < ksteps; ++ks) {
-                ok = mbar_try(empty + 8 * s, ph ^ 1u) || mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag);
+                ok = mbar_spin(empty + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
                 const uint32_t dst = sbase + s * STAGE + kAStage;
                 mbar_expect_tx(full_b + 8 * s, BSTAGE);
@@ -266,8 +302,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             uint32_t ph = 0;
             bool ok = true, any = false;
             for (int ks = 0; ks < ksteps; ++ks) {
-                ok = mbar_try(full_a + 8 * s, ph) || mbar_wait(full_a + 8 * s, ph, abort_flag);
-                if (ok) ok = mbar_try(full_b + 8 * s, ph) || mbar_wait(full_b + 8 * s, ph, abort_flag);
+                ok = mbar_spin(full_a + 8 * s, ph, abort_flag) && mbar_spin(full_b + 8 * s, ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a0 = sbase + s * STAGE, b0 = a0 + kAStage;
@@ -297,70 +332,76 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
         const int tp = (lane >> 3) & 1, gid = lane & 7;
         const int64_t g_glob = (int64_t)ft * 4 + grp;
         const bool g_valid = g_glob < p.ngroups;
-        const uint8_t* wg = p.w + g_glob * p.nb * UNIT;
-        const int slot_off = (gid * 4 + 2 * tp) * 16;
+        // running pointer to this task's unit of the current prefetch K-step
+        const uint8_t* wptr = p.w + (g_glob * p.nb + sub) * UNIT + (gid * 4 + 2 * tp) * 16 +
+                              (BITS == 4 ? sel * 8 : sel * 512);
+        const uint8_t* sptr = p.w + (g_glob * p.nb + sub) * UNIT + CODES + gid * 16 + (BITS == 4 ? sel * 8 : 0);
+        int bk_next = sub;  // block index the next load refers to
 
-        auto load = [&](RawW<BITS>& r, int ks) {
-            const int bk = ks * 4 + sub;
-            if (g_valid && bk < p.nb && ks < ksteps) {
-                const uint8_t* u = wg + (int64_t)bk * UNIT;
+        auto load = [&](RawW<BITS>& r) {
+            if (g_valid && bk_next < p.nb) {
                 if constexpr (BITS == 4) {
-                    RawW<4>& q = r;
-                    q.a = __ldg(reinterpret_cast<const uint2*>(u + slot_off + sel * 8));
-                    q.b = __ldg(reinterpret_cast<const uint2*>(u + slot_off + 16 + sel * 8));
-                    q.s = __ldg(reinterpret_cast<const float2*>(u + CODES + gid * 16 + sel * 8));
+                    r.a = __ldg(reinterpret_cast<const uint2*>(wptr));
+                    r.b = __ldg(reinterpret_cast<const uint2*>(wptr + 16));
+                    r.s = __ldg(reinterpret_cast<const float2*>(sptr));
                 } else {
-                    RawW<8>& q = r;
-                    q.a = __ldg(reinterpret_cast<const uint4*>(u + sel * 512 + slot_off));
-                    q.b = __ldg(reinterpret_cast<const uint4*>(u + sel * 512 + slot_off + 16));
-                    q.s = __ldg(reinterpret_cast<const float4*>(u + CODES + gid * 16));
+                    r.a = __ldg(reinterpret_cast<const uint4*>(wptr));
+                    r.b = __ldg(reinterpret_cast<const uint4*>(wptr + 16));
+                    r.s = __ldg(reinterpret_cast<const float4*>(sptr));
                 }
             } else {
                 r = RawW<BITS>{};  // zero scale: rows / blocks beyond the matrix contribute 0
             }
+            wptr += 4 * UNIT;
+            sptr += 4 * UNIT;
+            bk_next += 4;
         };
-        // address of chunk c (16 bytes = 8 fp16) of tile row r inside a stage's A region
+        // Shared-memory byte offsets of this task's 16-byte chunks inside a stage (K-major,
+        // 128-byte swizzle: chunk c of row r sits at (r/8)*1024 + (r%8)*128 + ((c ^ r%8) * 16)).
+        // Rows of one task differ by multiples of 8, so they share the xor and sit 1024 B apart.
         const uint32_t katom_off = (sub >> 1) * (128 * 128);
-        auto chunk_addr = [&](uint8_t* stage, int row, int c) -> uint4* {
-            return reinterpret_cast<uint4*>(stage + katom_off + (row >> 3) * 1024 + (row & 7) * 128 +
-                                            ((c ^ (row & 7)) << 4));
-        };
-        auto convert = [&](const RawW<BITS>& r, uint8_t* stage) {
+        uint32_t soff0, soff1;
+        if (BITS == 4) {
+            const uint32_t rbase = katom_off + (grp * 4 + 2 * sel) * 1024 + gid * 128;
+            soff0 = rbase + (((4 * (sub & 1) + tp) ^ gid) << 4);      // h = 0
+            soff1 = rbase + (((4 * (sub & 1) + 2 + tp) ^ gid) << 4);  // h = 1
+        } else {
+            soff0 = katom_off + (grp * 4) * 1024 + gid * 128 + (((4 * (sub & 1) + 2 * sel + tp) ^ gid) << 4);
+            soff1 = 0;
+        }
+        const float wmul = p.wmul;
+        auto convert = [&](const RawW<BITS>& r, uint32_t stage) {
             if constexpr (BITS == 4) {
-                const RawW<4>& q = r;
                 const uint32_t off = 0x64086408u;  // 1024 + zero point 8
-                const uint32_t s_lo = scale_h2(q.s.x * p.wmul), s_hi = scale_h2(q.s.y * p.wmul);
-                const int row_lo = grp * 32 + gid + 16 * sel, row_hi = row_lo + 8;
-                const uint32_t wa[2] = {q.a.x, q.a.y}, wb[2] = {q.b.x, q.b.y};
+                const uint32_t s_lo = scale_h2(r.s.x * wmul), s_hi = scale_h2(r.s.y * wmul);
+                const uint32_t wa[2] = {r.a.x, r.a.y}, wb[2] = {r.b.x, r.b.y};
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int c = 4 * (sub & 1) + 2 * h + tp;
+                    const uint32_t dst = stage + (h ? soff1 : soff0);
                     const uint2 l0 = bytes_to_h4(wa[h] & 0x0F0F0F0Fu, off, s_lo);
                     const uint2 l1 = bytes_to_h4(wb[h] & 0x0F0F0F0Fu, off, s_lo);
-                    *chunk_addr(stage, row_lo, c) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+                    sts128(dst, l0.x, l0.y, l1.x, l1.y);            // row gid + 16q
                     const uint2 h0 = bytes_to_h4((wa[h] >> 4) & 0x0F0F0F0Fu, off, s_hi);
                     const uint2 h1 = bytes_to_h4((wb[h] >> 4) & 0x0F0F0F0Fu, off, s_hi);
-                    *chunk_addr(stage, row_hi, c) = make_uint4(h0.x, h0.y, h1.x, h1.y);
+                    sts128(dst + 1024, h0.x, h0.y, h1.x, h1.y);     // row gid + 16q + 8
                 }
             } else {
-                const RawW<8>& q = r;
                 const uint32_t off = 0x64806480u;  // 1024 + zero point 128
-                const uint32_t wa[4] = {q.a.x, q.a.y, q.a.z, q.a.w}, wb[4] = {q.b.x, q.b.y, q.b.z, q.b.w};
-                const float sc[4] = {q.s.x, q.s.y, q.s.z, q.s.w};
-                const int c = 4 * (sub & 1) + 2 * sel + tp;
+                const uint32_t wa[4] = {r.a.x, r.a.y, r.a.z, r.a.w}, wb[4] = {r.b.x, r.b.y, r.b.z, r.b.w};
+                const float sc[4] = {r.s.x, r.s.y, r.s.z, r.s.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint32_t s2 = scale_h2(sc[i] * p.wmul);
+                    const uint32_t s2 = scale_h2(sc[i] * wmul);
                     const uint2 l0 = bytes_to_h4(wa[i], off, s2);
                     const uint2 l1 = bytes_to_h4(wb[i], off, s2);
-                    *chunk_addr(stage, grp * 32 + gid + 8 * i, c) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+                    sts128(stage + soff0 + i * 1024, l0.x, l0.y, l1.x, l1.y);  // row gid + 8i
                 }
             }
         };
 
         RawW<BITS> raw[kPrefetch];
 #pragma unroll
-        for (int j = 0; j < kPrefetch; ++j) load(raw[j], j);
+        for (int j = 0; j < kPrefetch; ++j) load(raw[j]);
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
@@ -369,14 +410,14 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             for (int j = 0; j < kPrefetch; ++j) {
                 const int ks = ks0 + j;
                 if (ks < ksteps && ok) {
-                    bool got = mbar_try(empty + 8 * s, ph ^ 1u) || mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag);
+                    const bool got = mbar_spin(empty + 8 * s, ph ^ 1u, abort_flag);
                     ok = __all_sync(0xffffffffu, got);
                     if (ok) {
-                        convert(raw[j], smem + s * STAGE);
+                        convert(raw[j], sbase + s * STAGE);
                         fence_async_smem();  // generic-proxy stores -> visible to the tensor core
                         __syncwarp();
                         if (lane == 0) mbar_arrive(full_a + 8 * s);
-                        load(raw[j], ks + kPrefetch);
+                        load(raw[j]);
                         if (++s == kNST) { s = 0; ph ^= 1u; }
                     }
                 }
@@ -385,7 +426,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
 
         // ---------------- epilogue: tensor memory -> y ----------------
         if (ok) {
-            bool got = mbar_try(acc_full, 0) || mbar_wait(acc_full, 0, abort_flag);
+            const bool got = mbar_spin(acc_full, 0, abort_flag);
             ok = __all_sync(0xffffffffu, got);
         }
         if (ok) {
@@ -418,6 +459,363 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     if (tid == 0 && s_abort) atomicExch(p.status, 2);
 }
 
+// ---- GEMM with the dequantized weights kept in tensor memory ------------------------------------
+// Same tile and pipeline as gemm_tc_kernel, but A never touches shared memory: the
+// tcgen05.st.16x256b fragment layout (lane = 4*gid + tig writes rows gid and gid + 8,
+// 32-bit columns 2*tig and 2*tig + 1) is exactly how the mma32 layout hands a lane its 16-byte
+// slot, so every lane converts its slot in registers and stores it to the A ring in tensor
+// memory (64 columns per 128-element K-step); tcgen05.mma reads A from tensor memory and only B
+// from shared memory, which halves the shared-memory traffic of the K loop.
+// Warp roles: 0 = TMA (activations), 1 = MMA, 2..17 = dequant: warp & 3 = 32-row group (= its
+// tensor-memory sub-partition), (warp - 2) >> 2 = block of the K-step.
+constexpr int kNSTT = 6;                  // pipeline stages: B in shared memory, A in tensor memory
+constexpr int kAColsPerStage = kKStep / 2;
+
+__device__ __forceinline__ void tmem_st_16x256b_x2(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc], issued by the lanes whose `leader` is non-zero (one lane).
+// The descriptor comes as two words so that stepping through a stage is one 32-bit add.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t bdesc_lo, uint32_t bdesc_hi,
+                                            uint32_t idesc, uint32_t accumulate, uint32_t leader) {
+    asm volatile(
+        "{ .reg .pred p, q; .reg .b64 bd; setp.ne.b32 p, %5, 0; setp.ne.b32 q, %6, 0; mov.b64 bd, {%2, %3}; "
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p; }" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(bdesc_lo), "r"(bdesc_hi), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+// One 128-element K-step as a single block of instructions, so that nothing but a branch sits
+// between the last MMA of a step and the first of the next: eight MMAs (A columns a0 + 8 kk, B
+// descriptor b_lo + 2 (kk & 3) + BHALF (kk >> 2) in 16-byte units, BHALF = second 64-element half
+// of the stage), with the two barrier operations of the pipeline tucked in between them where the
+// issuing lane is waiting for the tensor core anyway: the commit that frees the PREVIOUS stage
+// (it then also covers the first MMAs of this one, so that stage is released a little later,
+// which the ring absorbs) and a non-blocking test of the NEXT stage's barrier, whose answer is
+// read at the end.  first = 0 makes MMA 0 overwrite the accumulator; lanes with leader = 0
+// issue no tensor-core instruction.
+template <int BHALF>
+__device__ __forceinline__ uint32_t umma_f16_ts_step(uint32_t d_tmem, uint32_t a0, uint32_t b_lo, uint32_t b_hi,
+                                                     uint32_t idesc, uint32_t first, uint32_t leader,
+                                                     uint32_t prev_empty, uint32_t commit_prev,
+                                                     uint32_t next_full, uint32_t next_parity) {
+    uint32_t next_ready;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q, t, r, c;\n"
+        ".reg .b64 bd0, bd1, bd2, bd3, bd4, bd5, bd6, bd7;\n"
+        ".reg .b32 a1, a2, a3, a4, a5, a6, a7, b;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "setp.ne.b32 q, %7, 0;\n"
+        "setp.ne.b32 c, %13, 0;\n"
+        "and.pred c, c, q;\n"
+        "setp.eq.b32 t, 0, 0;\n"
+        "mov.b64 bd0, {%3, %4};\n"
+        "add.u32 a1, %2, 8;  add.u32 b, %3, 2;   mov.b64 bd1, {b, %4};\n"
+        "add.u32 a2, %2, 16; add.u32 b, %3, 4;   mov.b64 bd2, {b, %4};\n"
+        "add.u32 a3, %2, 24; add.u32 b, %3, 6;   mov.b64 bd3, {b, %4};\n"
+        "add.u32 a4, %2, 32; add.u32 b, %3, %8;  mov.b64 bd4, {b, %4};\n"
+        "add.u32 a5, %2, 40; add.u32 b, %3, %9;  mov.b64 bd5, {b, %4};\n"
+        "add.u32 a6, %2, 48; add.u32 b, %3, %10; mov.b64 bd6, {b, %4};\n"
+        "add.u32 a7, %2, 56; add.u32 b, %3, %11; mov.b64 bd7, {b, %4};\n"
+        "tcgen05.fence::after_thread_sync;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], bd0, %5, p;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], bd1, %5, t;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 r, [%14], %15;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], bd2, %5, t;\n"
+        "@c tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%12];\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], bd3, %5, t;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a4], bd4, %5, t;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a5], bd5, %5, t;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a6], bd6, %5, t;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a7], bd7, %5, t;\n"
+        "selp.u32 %0, 1, 0, r;\n"
+        "}"
+        : "=r"(next_ready)
+        : "r"(d_tmem), "r"(a0), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first), "r"(leader), "n"(BHALF),
+          "n"(BHALF + 2), "n"(BHALF + 4), "n"(BHALF + 6), "r"(prev_empty), "r"(commit_prev), "r"(next_full),
+          "r"(next_parity)
+        : "memory");
+    return next_ready;
+}
+__device__ __forceinline__ void umma_commit_if(uint32_t bar, uint32_t leader) {
+    asm volatile(
+        "{ .reg .pred q; setp.ne.b32 q, %1, 0; "
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0]; }" ::"r"(bar),
+        "r"(leader)
+        : "memory");
+}
+
+template <int BITS>
+struct RawT;
+template <>
+struct RawT<4> {
+    uint4 c;    // the lane's slot: words 2q + h
+    float4 s;   // scales of rows gid + 8i
+};
+template <>
+struct RawT<8> {
+    uint4 c0, c1;  // plane 0 / 1 slot: word i = row gid + 8i
+    float4 s;
+};
+
+template <int BITS, int NTOK>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
+    constexpr int UNIT = BITS == 4 ? kUnitBytesQ4 : kUnitBytesQ8;
+    constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
+    constexpr int BSTAGE = NTOK * kKStep * 2;
+    constexpr uint32_t TMEM_COLS = 512;                       // D (NTOK) + A ring (6 x 64), power of two
+    constexpr uint32_t A_COL0 = NTOK;                         // A ring starts after the accumulator
+    static_assert(NTOK + kNSTT * kAColsPerStage <= 512, "tensor memory holds D and the A ring");
+    extern __shared__ uint8_t smem_raw[];
+    if (p.dbg && blockIdx.x == 0 && threadIdx.x == 64) { p.dbg[300] = (unsigned long long)clock64(); p.dbg[304] = gtime_ns(); }
+    __shared__ int s_abort;
+    __shared__ uint32_t s_tmem;
+    __shared__ __align__(8) uint64_t s_bar[2 * kNSTT + 1];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = smem_u32(s_bar);
+    // full[s]: 16 dequant warps have stored A of the stage and the TMA bytes of B have landed;
+    // empty[s]: the MMAs that read the stage have completed (tcgen05.commit)
+    const uint32_t full = bar0, empty = bar0 + 8 * kNSTT, acc_full = bar0 + 16 * kNSTT;
+    const int ft = blockIdx.x / p.ttiles, tt = blockIdx.x - ft * p.ttiles;
+    const int tok0 = tt * NTOK;
+    volatile int* abort_flag = &s_abort;
+
+    if (tid < kNSTT) {
+        mbar_init(full + 8 * tid, kDqWarps + 1);
+        mbar_init(empty + 8 * tid, 1);
+    } else if (tid == kNSTT) {
+        mbar_init(acc_full, 1);
+        s_abort = 0;
+    }
+    if (tid <= kNSTT) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&s_tmem), TMEM_COLS);
+        tmem_relinquish();
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const int ksteps = p.ksteps;
+    unsigned long long* dbg = (p.dbg && blockIdx.x == 0) ? p.dbg : nullptr;
+    if (dbg && tid == 64) dbg[301] = (unsigned long long)clock64();
+    unsigned long long* fine = dbg;
+
+    if (warp == 0) {
+        // ---------------- TMA producer of the activation tiles ----------------
+        if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // activations come from the pre-pass
+            int s = 0, issued = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int ks = 0; ks < ksteps; ++ks) {
+                ok = mbar_spin(empty + 8 * s, ph ^ 1u, abort_flag);
+                if (!ok) break;
+                if (fine && ks < 40) dbg[ks * 8 + 0] = (unsigned long long)clock64();  // TMA: slot free, issuing
+                const uint32_t dst = sbase + s * BSTAGE;
+                mbar_expect_tx(full + 8 * s, BSTAGE);
+                tma_load_2d(dst, &tmap, ks * kKStep, tok0, full + 8 * s);
+                tma_load_2d(dst + NTOK * 128, &tmap, ks * kKStep + 64, tok0, full + 8 * s);
+                ++issued;
+                if (++s == kNSTT) { s = 0; ph ^= 1u; }
+            }
+            if (!ok) {  // let the copies already issued land before this CTA's shared memory goes away
+                for (int k = issued > kNSTT ? issued - kNSTT : 0; k < issued; ++k) {
+                    const unsigned long long t0 = gtime_ns();
+                    while (!mbar_try(full + 8 * (k % kNSTT), (uint32_t)(k / kNSTT) & 1u) &&
+                           gtime_ns() - t0 < kWaitLimitNs) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        // The whole warp runs the loop with identical values (so the address arithmetic stays
+        // warp-uniform) and lane 0 alone issues the tensor-core instructions.  The loop must cost
+        // fewer issue cycles than the 8 MMAs of a step take to execute (8 x 64 cycles), or the
+        // tensor core starves: the descriptor of a stage is one multiply-add, each MMA adds a
+        // constant to it, and the barrier of step ks + 1 is tested before the MMAs of step ks so
+        // that its answer is back by the time they have been issued.
+        constexpr uint32_t idesc = idesc_f16(NTOK);
+        const uint32_t leader = lane == 0;
+        const uint64_t d0 = smem_desc_sw128(sbase);
+        const uint32_t d_lo = (uint32_t)d0, d_hi = (uint32_t)(d0 >> 32);
+        int s = 0;
+        uint32_t ph = 0;
+        bool any = false;
+        bool ok = mbar_spin(full, 0, abort_flag);
+        if (dbg && lane == 0) dbg[306] = (unsigned long long)clock64();
+        // The tensor core's queue is only an MMA or two deep: whenever this warp is late with the
+        // next MMA the pipe runs dry and pays a restart on top, so a step is one block of
+        // instructions (see umma_f16_ts_step) and the loop around it only rotates registers.
+        static_assert(kKStep == 128, "eight MMAs per step");
+        uint32_t a0 = tmem + A_COL0, b_lo = d_lo, prev_empty = empty;
+        for (int ks = 0; ks < ksteps && ok; ++ks) {
+            int s1 = s + 1;
+            uint32_t ph1 = ph;
+            if (s1 == kNSTT) { s1 = 0; ph1 ^= 1u; }
+            const uint32_t a0n = tmem + A_COL0 + s1 * kAColsPerStage, b_lon = d_lo + (uint32_t)s1 * (BSTAGE >> 4);
+            const uint32_t n1 = umma_f16_ts_step<NTOK * 8>(tmem, a0, b_lo, d_hi, idesc, ks != 0, leader, prev_empty,
+                                                           ks != 0, full + 8 * s1, ph1);
+            any = true;
+            prev_empty = empty + 8 * s;
+            if (ks + 1 < ksteps && !n1) ok = mbar_spin(full + 8 * s1, ph1, abort_flag);
+            a0 = a0n;
+            b_lo = b_lon;
+            s = s1;
+            ph = ph1;
+        }
+        if (any) umma_commit_if(prev_empty, leader);  // the last stage (nobody waits for it; keeps the ring uniform)
+        if (dbg && lane == 0) dbg[307] = (unsigned long long)clock64();
+        if (ok || any) {
+            umma_commit_if(acc_full, leader);
+            if (!ok) {  // gave up: tensor core must be idle before tensor memory is freed
+                const unsigned long long t0 = gtime_ns();
+                while (!mbar_try(acc_full, 0) && gtime_ns() - t0 < kWaitLimitNs) {
+                }
+            }
+        }
+    } else {
+        // ---------------- dequant warps ----------------
+        const int dq = warp - 2, grp = warp & 3, sub = dq >> 2;
+        const int gid = lane >> 2;
+        const int64_t g_glob = (int64_t)ft * 4 + grp;
+        const bool g_valid = g_glob < p.ngroups;
+        const uint8_t* wptr = p.w + (g_glob * p.nb + sub) * UNIT + lane * 16;
+        const uint8_t* sptr = p.w + (g_glob * p.nb + sub) * UNIT + CODES + gid * 16;
+        int bk_next = sub;
+        auto load = [&](RawT<BITS>& r) {
+            if (g_valid && bk_next < p.nb) {
+                if constexpr (BITS == 4) {
+                    r.c = __ldg(reinterpret_cast<const uint4*>(wptr));
+                } else {
+                    r.c0 = __ldg(reinterpret_cast<const uint4*>(wptr));
+                    r.c1 = __ldg(reinterpret_cast<const uint4*>(wptr + 512));
+                }
+                r.s = __ldg(reinterpret_cast<const float4*>(sptr));
+            } else {
+                r = RawT<BITS>{};  // zero scale: rows / blocks beyond the matrix contribute 0
+            }
+            wptr += 4 * UNIT;
+            sptr += 4 * UNIT;
+            bk_next += 4;
+        };
+        const float wmul = p.wmul;
+        // this warp's rows are tensor-memory lanes 32*grp .. 32*grp + 31; its block is 16 columns wide
+        const uint32_t t_lane = (uint32_t)(grp * 32) << 16;
+        auto convert_store = [&](const RawT<BITS>& r, uint32_t a_stage) {
+            const uint32_t dst = a_stage + t_lane + sub * 16;
+            const float sc[4] = {r.s.x, r.s.y, r.s.z, r.s.w};
+            if constexpr (BITS == 4) {
+                const uint32_t off = 0x64086408u;  // 1024 + zero point 8
+                const uint32_t w[4] = {r.c.x, r.c.y, r.c.z, r.c.w};
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {  // rows gid + 16q (low nibbles) and gid + 16q + 8 (high)
+                    const uint32_t s_lo = scale_h2(sc[2 * q] * wmul), s_hi = scale_h2(sc[2 * q + 1] * wmul);
+                    uint32_t v[8];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {  // columns 8h .. 8h + 7: elements 16h + 4tig ..
+                        const uint2 lo = bytes_to_h4(w[2 * q + h] & 0x0F0F0F0Fu, off, s_lo);
+                        const uint2 hi = bytes_to_h4((w[2 * q + h] >> 4) & 0x0F0F0F0Fu, off, s_hi);
+                        v[4 * h + 0] = lo.x;
+                        v[4 * h + 1] = lo.y;
+                        v[4 * h + 2] = hi.x;
+                        v[4 * h + 3] = hi.y;
+                    }
+                    tmem_st_16x256b_x2(dst + ((uint32_t)(16 * q) << 16), v);
+                }
+            } else {
+                const uint32_t off = 0x64806480u;  // 1024 + zero point 128
+                const uint32_t w0[4] = {r.c0.x, r.c0.y, r.c0.z, r.c0.w}, w1[4] = {r.c1.x, r.c1.y, r.c1.z, r.c1.w};
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {  // rows gid + 16q (i = 2q) and gid + 16q + 8 (i = 2q + 1)
+                    const uint32_t s_a = scale_h2(sc[2 * q] * wmul), s_b = scale_h2(sc[2 * q + 1] * wmul);
+                    uint32_t v[8];
+                    const uint2 a0 = bytes_to_h4(w0[2 * q], off, s_a), b0 = bytes_to_h4(w0[2 * q + 1], off, s_b);
+                    const uint2 a1 = bytes_to_h4(w1[2 * q], off, s_a), b1 = bytes_to_h4(w1[2 * q + 1], off, s_b);
+                    v[0] = a0.x; v[1] = a0.y; v[2] = b0.x; v[3] = b0.y;   // plane 0: columns 0..7
+                    v[4] = a1.x; v[5] = a1.y; v[6] = b1.x; v[7] = b1.y;   // plane 1: columns 8..15
+                    tmem_st_16x256b_x2(dst + ((uint32_t)(16 * q) << 16), v);
+                }
+            }
+        };
+
+        RawT<BITS> raw[kPrefetch];
+#pragma unroll
+        for (int j = 0; j < kPrefetch; ++j) load(raw[j]);
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int ks0 = 0; ks0 < ksteps && ok; ks0 += kPrefetch) {
+#pragma unroll
+            for (int j = 0; j < kPrefetch; ++j) {
+                const int ks = ks0 + j;
+                if (ks < ksteps && ok) {
+                    ok = mbar_wait_warp(empty + 8 * s, ph ^ 1u, abort_flag);
+                    if (ok) {
+                        if (fine && lane == 0 && ks == 10) dbg[336 + dq] = (unsigned long long)clock64();  // A slot seen free, per warp
+                        tc_fence_after();
+                        convert_store(raw[j], tmem + A_COL0 + s * kAColsPerStage);
+                        if (fine && warp == 2 && lane == 0 && ks < 40) dbg[ks * 8 + 4] = (unsigned long long)clock64();  // converted
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(full + 8 * s);
+                        if (fine && warp == 2 && lane == 0 && ks < 40) dbg[ks * 8 + 5] = (unsigned long long)clock64();  // signalled
+                        if (fine && lane == 0 && ks == 10) dbg[320 + dq] = (unsigned long long)clock64();  // signalled, per warp
+                        load(raw[j]);
+                        if (++s == kNSTT) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        }
+
+        // ---------------- epilogue: tensor memory -> y ----------------
+        if (ok) {
+            const bool got = mbar_spin(acc_full, 0, abort_flag);
+            ok = __all_sync(0xffffffffu, got);
+        }
+        if (dbg && tid == 64) dbg[302] = (unsigned long long)clock64();
+        if (ok) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // y may still be read by the grid before us
+            tc_fence_after();
+            const int sp = warp & 3;          // tensor-memory lanes 32*sp .. 32*sp + 31
+            const int cq = dq >> 2;           // column quarter
+            const int64_t f = (int64_t)ft * 128 + sp * 32 + lane;
+            constexpr int CPW = NTOK / 4;     // columns per warp
+#pragma unroll
+            for (int c0 = 0; c0 < CPW; c0 += 8) {
+                uint32_t v[8];
+                const int col = cq * CPW + c0;
+                tmem_ld8(tmem + ((uint32_t)(sp * 32) << 16) + (uint32_t)col, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int tok = tok0 + col + j;
+                    if (tok < p.M && f < p.out) {
+                        const float val = __uint_as_float(v[j]) * p.wdiv * __ldg(p.rowscale + tok);
+                        store_out(p.y, p.out_dtype, (int64_t)tok * p.out + f, val);
+                    }
+                }
+            }
+        }
+    }
+    if (dbg && tid == 64) { dbg[303] = (unsigned long long)clock64(); dbg[305] = gtime_ns(); }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+    if (tid == 0 && s_abort) atomicExch(p.status, 2);
+}
+
 // ---- host side --------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -440,6 +838,8 @@ template <int BITS, int NTOK>
 static int32_t gemm_attr() {
     RSTQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BITS, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    kNST * (kAStage + NTOK * kKStep * 2) + 1024));
+    RSTQ_CUDA(cudaFuncSetAttribute(gemm_tmem_kernel<BITS, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kNSTT * (NTOK * kKStep * 2) + 1024));
     return RSTQ_OK;
 }
 
@@ -481,7 +881,9 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
                  "activation scratch must be 16-byte aligned");
     EncodeTiledFn enc = encode_tiled_fn();
     RSTQ_REQUIRE(enc, RSTQ_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    // pre-pass: activations -> fp16 with one exponent per token row
+    // pre-pass: activations -> fp16 with one exponent per token row (kind::f16 wants A and B of
+    // one type, and fp16 keeps three more mantissa bits of the weights than bf16 would)
+    const bool a_in_tmem = ctx->tune_gemm_kernel != 1;
     cudaError_t le;
     if (src == 0)
         le = launch_pdl(act_to_f16_kernel<0>, dim3((unsigned)M), dim3(256), 0, ds, x, xs, (__half*)x16,
@@ -520,11 +922,15 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     p.wmul = ldexpf(1.0f, w->gemm_exp);
     p.wdiv = ldexpf(1.0f, -w->gemm_exp);
     p.out_dtype = out_dtype;
+    p.dbg = ds.dbg;
     const int64_t ftiles = (w->out + 127) / 128;
     RSTQ_REQUIRE(ftiles * p.ttiles < (1ll << 31), RSTQ_E_LIMIT, "grid too large");
     const dim3 grid((unsigned)(ftiles * p.ttiles));
-    const size_t smem = kNST * (kAStage + (size_t)ntok * kKStep * 2) + 1024;
-#define GL(B, N) le = launch_pdl(gemm_tc_kernel<B, N>, grid, dim3(kGemmThreads), smem, ds, p, tmap)
+    const size_t smem = a_in_tmem ? kNSTT * ((size_t)ntok * kKStep * 2) + 1024
+                                  : kNST * (kAStage + (size_t)ntok * kKStep * 2) + 1024;
+#define GL(B, N)                                                                                     \
+    le = a_in_tmem ? launch_pdl(gemm_tmem_kernel<B, N>, grid, dim3(kGemmThreads), smem, ds, p, tmap) \
+                   : launch_pdl(gemm_tc_kernel<B, N>, grid, dim3(kGemmThreads), smem, ds, p, tmap)
     if (w->bits == 4) {
         if (ntok == 32) GL(4, 32);
         else if (ntok == 64) GL(4, 64);

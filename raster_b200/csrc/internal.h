@@ -89,6 +89,7 @@ struct rstq_ctx {
     uint32_t magic;
     std::vector<rstq::DeviceState> devs;
     int64_t tune_gemm_min_m = 17;
+    int64_t tune_gemm_kernel = 0;   // 0 = weights in tensor memory, 1 = weights through shared memory
     int64_t launches = 0;
     struct CacheKey {
         const void* codes;

@@ -30,6 +30,16 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// non-blocking test of a phase
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long gtime_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -49,6 +59,30 @@ static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, vol
             return false;
         }
     }
+}
+// Wait with a short inline spin first (the common case: the other side is a few hundred
+// cycles away), then the timed slow path.
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 1024; ++i)
+        if (mbar_test(bar, parity)) return true;
+    return mbar_wait(bar, parity, abort_flag);
+}
+// Warp-wide wait that polls from lane 0 only, sleeping between polls: a producer warp that is
+// a long way ahead of its consumer then leaves the barrier unit and the issue slots to the
+// warps that are on the critical path.  All 32 lanes must call it; all get the same answer.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    int got = 1;
+    if ((threadIdx.x & 31) == 0) {
+        got = 0;
+#pragma unroll 1
+        for (int i = 0; i < 4096 && !got; ++i) {
+            got = mbar_test(bar, parity);
+            if (!got) __nanosleep(32);
+        }
+        if (!got) got = mbar_wait(bar, parity, abort_flag);
+    }
+    return __shfl_sync(0xffffffffu, got, 0) != 0;
 }
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
                                               uint32_t bar) {
