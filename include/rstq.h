@@ -118,6 +118,16 @@ RSTQ_API int32_t rstq_upload(rstq_buf* buf, const void* host, int64_t offset, in
 RSTQ_API int32_t rstq_download(rstq_buf* buf, void* host, int64_t offset, int64_t bytes);
 RSTQ_API int32_t rstq_memset(rstq_buf* buf, int32_t byte_value, int64_t offset, int64_t bytes);
 RSTQ_API int32_t rstq_buf_ptr(rstq_buf* buf, void** device_ptr, int64_t* bytes);
+/* A buffer handle over device memory the caller allocated (a runtime's own arena, a tensor of
+ * another library); rstq_free releases the handle only.  The reference's counterpart is
+ * buffer-of-array (src/raster/gpu/ocl_runtime.clj:452-499), which wraps an existing segment. */
+RSTQ_API int32_t rstq_buf_wrap(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, void* device_ptr,
+                               int64_t bytes);
+/* Launch on a CUDA stream of the caller (cudaStream_t) instead of the context's own, so that the
+ * operators order with the caller's other work without events; NULL returns to the own stream.
+ * Plays the part of *current-arena* (src/raster/gpu/ocl_runtime.clj:222-224): the queue every
+ * launch of the session goes to. */
+RSTQ_API int32_t rstq_stream_set(rstq_ctx* ctx, int32_t dev, void* stream);
 
 /* ---- weights: the one-time host->device bind.  Replaces repack-stream
  *      (src/raster/compiler/backend/cpu/quant.clj:317-326) as the load-time
@@ -220,6 +230,35 @@ RSTQ_API int32_t rstq_event_elapsed_ms(rstq_event* start, rstq_event* stop, floa
 RSTQ_API int32_t rstq_event_destroy(rstq_event* ev);
 /* Number of kernels this library has launched on the context since init. */
 RSTQ_API int32_t rstq_launch_count(rstq_ctx* ctx, int64_t* count);
+
+/* ---- tensor-parallel exchange of the sharded operator.  No counterpart in the reference: it
+ *      extends the placement / plan vocabulary (src/raster/compiler/passes/placement.clj:21-89)
+ *      with a weight split over the GPUs of one box.  One endpoint per rank.  Every rank owns a
+ *      zero-filled "region" of rstq_tp_region_bytes() bytes that all ranks can address: peer
+ *      access inside one process (rstq_tp_create_local sets that up), or a symmetric / IPC
+ *      mapping between processes (rstq_tp_attach takes the addresses as this device sees them).
+ *      The exchange is one kernel per rank over that memory (peer stores, a flag per rank,
+ *      time-bounded waits: a rank that never arrives yields RSTQ_E_WAIT from rstq_sync, not a
+ *      hang); all ranks must issue the same sequence of exchanges. ------------------------- */
+typedef struct rstq_tp rstq_tp;
+#define RSTQ_TP_MAX_RANKS 8
+RSTQ_API int64_t rstq_tp_region_bytes(int32_t nranks, int64_t max_payload_bytes); /* 0 = bad arguments */
+RSTQ_API int32_t rstq_tp_attach(rstq_ctx* ctx, int32_t dev, int32_t rank, int32_t nranks,
+                                void* const* regions, int64_t region_bytes, rstq_tp** tp);
+/* one process, nranks devices of ctx (devs = device indexes of the context): tps[nranks] */
+RSTQ_API int32_t rstq_tp_create_local(rstq_ctx* ctx, int32_t nranks, const int32_t* devs,
+                                      int64_t max_payload_bytes, rstq_tp** tps);
+/* dst[row][rank][row_bytes] = src of rank `rank` [row][row_bytes]; row_bytes % 16 == 0 */
+RSTQ_API int32_t rstq_tp_allgather(rstq_tp* tp, rstq_buf* src, rstq_buf* dst, int64_t rows,
+                                   int64_t row_bytes);
+/* dst[i] = sum over ranks (in rank order, the same on every rank) of src[i]; count % 4 == 0 */
+RSTQ_API int32_t rstq_tp_allreduce_f32(rstq_tp* tp, rstq_buf* src, rstq_buf* dst, int64_t count);
+/* The sharded operator: w is this rank's shard (rstq_weight_bind_shard).  Column split: x is
+ * the full activation, y [M, nranks * w.out] f32 gathers every rank's columns.  Row split: x is
+ * this rank's K slice [M, w.in], y [M, w.out] f32 is the sum of the partial products. */
+RSTQ_API int32_t rstq_tp_qmatmul(rstq_tp* tp, rstq_weight* w, rstq_buf* x, rstq_buf* y, int64_t M,
+                                 int32_t act_dtype, int32_t mode, int32_t split);
+RSTQ_API int32_t rstq_tp_free(rstq_tp* tp);
 
 #ifdef __cplusplus
 }

@@ -30,6 +30,8 @@ SIGNATURES = {
     "rstq_download": [vp, vp, i64, i64],
     "rstq_memset": [vp, i32, i64, i64],
     "rstq_buf_ptr": [vp, pp, C.POINTER(i64)],
+    "rstq_buf_wrap": [vp, pp, i32, vp, i64],
+    "rstq_stream_set": [vp, i32, vp],
     "rstq_weight_bind": [vp, pp, vp, vp, i32, i64, i64, i32, i32],
     "rstq_weight_bind_shard": [vp, pp, vp, vp, i32, i64, i64, i32, i32, i32, i32, i32],
     "rstq_weight_clone": [vp, pp],
@@ -55,8 +57,15 @@ SIGNATURES = {
     "rstq_event_elapsed_ms": [vp, vp, C.POINTER(C.c_float)],
     "rstq_event_destroy": [vp],
     "rstq_launch_count": [vp, C.POINTER(i64)],
+    "rstq_tp_region_bytes": [i32, i64],
+    "rstq_tp_attach": [vp, i32, i32, i32, pp, i64, pp],
+    "rstq_tp_create_local": [vp, i32, C.POINTER(i32), i64, pp],
+    "rstq_tp_allgather": [vp, vp, vp, i64, i64],
+    "rstq_tp_allreduce_f32": [vp, vp, vp, i64],
+    "rstq_tp_qmatmul": [vp, vp, vp, vp, i64, i32, i32, i32],
+    "rstq_tp_free": [vp],
 }
-_RESTYPE = {"rstq_last_error": C.c_char_p}
+_RESTYPE = {"rstq_last_error": C.c_char_p, "rstq_tp_region_bytes": i64}
 
 # constants of include/rstq.h
 OK = 0

@@ -36,7 +36,7 @@ static bool ok_w(const rstq_weight* w) { return w && w->magic == kWgtMagic && ok
     RSTQ_REQUIRE((d) >= 0 && (d) < (int)(c)->devs.size(), RSTQ_E_NODEV,              \
                  "device index %d out of range (context has %d)", (int)(d), (int)(c)->devs.size())
 
-static int32_t use_dev(rstq_ctx* ctx, int dev) {
+int32_t use_dev(rstq_ctx* ctx, int dev) {
     RSTQ_CUDA(cudaSetDevice(ctx->devs[dev].ordinal));
     return RSTQ_OK;
 }
@@ -145,8 +145,8 @@ static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, void** x16, 
     return RSTQ_OK;
 }
 
-static int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
-                             int act_dtype, int out_dtype, int mode) {
+int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M, int act_dtype,
+                      int out_dtype, int mode) {
     DeviceState& ds = ctx->devs[w->dev];
     // Prefill shapes go to the tensor-core GEMM (fp16 operands, results within 1e-3 of the
     // reference).  A8 keeps its exact integer path up to M = 63: callers that chose the
@@ -336,7 +336,8 @@ int32_t rstq_init(const int32_t* devices, int32_t ndev, rstq_ctx** ctxp) {
             ds.sm_count = prop.multiProcessorCount;
             ds.l2_bytes = prop.l2CacheSize;
             ds.total_mem = (int64_t)prop.totalGlobalMem;
-            RSTQ_CUDA(cudaStreamCreateWithFlags(&ds.stream, cudaStreamNonBlocking));
+            RSTQ_CUDA(cudaStreamCreateWithFlags(&ds.own_stream, cudaStreamNonBlocking));
+            ds.stream = ds.own_stream;
             ds.partials_bytes = 32ll << 20;
             RSTQ_CUDA(cudaMalloc((void**)&ds.partials, (size_t)ds.partials_bytes));
             ds.counters_len = 1 << 18;
@@ -390,7 +391,7 @@ int32_t rstq_shutdown(rstq_ctx* ctx) {
         if (ds.dbg_store) cudaFree(ds.dbg_store);
         if (ds.io_dev) cudaFree(ds.io_dev);
         if (ds.pinned) cudaFreeHost(ds.pinned);
-        if (ds.stream) cudaStreamDestroy(ds.stream);
+        if (ds.own_stream) cudaStreamDestroy(ds.own_stream);
     }
     cudaGetLastError();
     ctx->magic = 0;
@@ -478,7 +479,7 @@ int32_t rstq_alloc(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, int64_t bytes) {
     if (rc != RSTQ_OK) return rc;
     void* p = nullptr;
     RSTQ_CUDA(cudaMalloc(&p, (size_t)bytes));
-    rstq_buf* b = new (std::nothrow) rstq_buf{kBufMagic, ctx, dev, p, bytes};
+    rstq_buf* b = new (std::nothrow) rstq_buf{kBufMagic, ctx, dev, p, bytes, true};
     if (!b) {
         cudaFree(p);
         set_error("out of host memory");
@@ -488,13 +489,42 @@ int32_t rstq_alloc(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, int64_t bytes) {
     return RSTQ_OK;
 }
 
+int32_t rstq_buf_wrap(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, void* device_ptr, int64_t bytes) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(buf, RSTQ_E_INVALID, "null argument");
+    *buf = nullptr;
+    CHECK_DEV(ctx, dev);
+    RSTQ_REQUIRE(device_ptr && bytes > 0, RSTQ_E_INVALID, "need a device address and a positive size");
+    RSTQ_REQUIRE(((uintptr_t)device_ptr & 15) == 0, RSTQ_E_ALIGN, "device address must be 16-byte aligned");
+    rstq_buf* b = new (std::nothrow) rstq_buf{kBufMagic, ctx, dev, device_ptr, bytes, false};
+    RSTQ_REQUIRE(b, RSTQ_E_OOM, "out of host memory");
+    *buf = b;
+    return RSTQ_OK;
+}
+
+int32_t rstq_stream_set(rstq_ctx* ctx, int32_t dev, void* stream) {
+    CHECK_CTX(ctx);
+    CHECK_DEV(ctx, dev);
+    DeviceState& ds = ctx->devs[dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "cannot change the stream during graph capture");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    if (stream) {
+        ds.stream = (cudaStream_t)stream;
+    } else {
+        ds.stream = ds.own_stream;
+    }
+    return RSTQ_OK;
+}
+
 int32_t rstq_free(rstq_buf* buf) {
     if (!buf) return RSTQ_OK;
     RSTQ_REQUIRE(ok_buf(buf), RSTQ_E_INVALID, "invalid buffer handle");
     DeviceState& ds = buf->ctx->devs[buf->dev];
     cudaSetDevice(ds.ordinal);
     if (!ds.capturing) cudaStreamSynchronize(ds.stream);
-    cudaFree(buf->ptr);
+    if (buf->owned) cudaFree(buf->ptr);
     cudaGetLastError();
     buf->magic = 0;
     delete buf;

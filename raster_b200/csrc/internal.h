@@ -62,7 +62,8 @@ struct DeviceState {
     int64_t l2_bytes = 0;
     int64_t total_mem = 0;
     int cc = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;      // where everything launches: own_stream or one the caller lent
+    cudaStream_t own_stream = nullptr;
     bool capturing = false;
     bool pdl = true;               // launch the hot kernels with programmatic stream serialization
     // scratch owned by the context
@@ -116,6 +117,7 @@ struct rstq_buf {
     int dev;
     void* ptr;
     int64_t bytes;
+    bool owned;  // false: wraps memory the caller allocated (rstq_buf_wrap)
 };
 
 struct rstq_weight {
@@ -190,6 +192,10 @@ int32_t gemv_configure(DeviceState& ds);  // shared-memory attributes, once per 
 int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const void* x, const float* xs,
                     int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale);
 int32_t gemm_configure(DeviceState& ds);
+// capi.cu
+int32_t use_dev(rstq_ctx* ctx, int dev);
+int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M, int act_dtype,
+                      int out_dtype, int mode);
 // capi.cu: grow-only device scratch (refuses to grow during graph capture)
 int32_t dev_reserve(DeviceState& ds, void** p, int64_t* have, int64_t need);
 constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels

@@ -37,11 +37,15 @@ def parse_device(dev) -> int:
 class DeviceBuffer:
     """make-buffer: {:segment :n-elements :byte-size :dtype} on a CUDA device."""
 
-    def __init__(self, ctx: "Context", n: int, dtype, dev: int = 0):
+    def __init__(self, ctx: "Context", n: int, dtype, dev: int = 0, wrap_ptr=None):
         self.ctx, self.dtype, self.n_elements, self.dev = ctx, np.dtype(dtype), int(n), dev
         self.byte_size = self.n_elements * self.dtype.itemsize
         h = C.c_void_p()
-        L.check(ctx.lib.rstq_alloc(ctx.handle, C.byref(h), dev, max(self.byte_size, 1)))
+        if wrap_ptr is None:
+            L.check(ctx.lib.rstq_alloc(ctx.handle, C.byref(h), dev, max(self.byte_size, 1)))
+        else:   # buffer-of-array: memory somebody else owns
+            L.check(ctx.lib.rstq_buf_wrap(ctx.handle, C.byref(h), dev, C.c_void_p(int(wrap_ptr)),
+                                          self.byte_size))
         self.handle = h
 
     def upload(self, arr) -> "DeviceBuffer":
@@ -127,6 +131,29 @@ class Event:
             self.handle = None
 
 
+class TpEndpoint:
+    """One rank of a tensor-parallel group: the sharded operator and its exchanges."""
+
+    def __init__(self, ctx, handle, rank, nranks, dev):
+        self.ctx, self.handle, self.rank, self.nranks, self.dev = ctx, handle, rank, nranks, dev
+
+    def allgather(self, src: DeviceBuffer, dst: DeviceBuffer, rows: int, row_bytes: int) -> None:
+        L.check(self.ctx.lib.rstq_tp_allgather(self.handle, src.handle, dst.handle, rows, row_bytes))
+
+    def allreduce_f32(self, src: DeviceBuffer, dst: DeviceBuffer, count: int) -> None:
+        L.check(self.ctx.lib.rstq_tp_allreduce_f32(self.handle, src.handle, dst.handle, count))
+
+    def qmatmul(self, w: QWeight, x: DeviceBuffer, y: DeviceBuffer, M=1, act_dtype=L.F32,
+                mode=L.MODE_A8, split=L.SPLIT_COLUMN) -> None:
+        L.check(self.ctx.lib.rstq_tp_qmatmul(self.handle, w.handle, x.handle, y.handle, M, act_dtype,
+                                             mode, split))
+
+    def free(self) -> None:
+        if self.handle:
+            self.ctx.lib.rstq_tp_free(self.handle)
+            self.handle = None
+
+
 class Context:
     """make-session for cuda:N devices; close() frees everything it still owns."""
 
@@ -148,6 +175,33 @@ class Context:
     def array_to_buffer(self, arr, dev=0) -> DeviceBuffer:
         a = np.ascontiguousarray(arr)
         return DeviceBuffer(self, a.size, a.dtype, dev).upload(a)
+
+    def wrap_buffer(self, device_ptr: int, n, dtype, dev=0) -> DeviceBuffer:
+        return DeviceBuffer(self, n, dtype, dev, wrap_ptr=device_ptr)
+
+    def set_stream(self, cuda_stream: int | None, dev=0) -> None:
+        """Launch on the caller's cudaStream_t (an integer handle); None = the context's own."""
+        L.check(self.lib.rstq_stream_set(self.handle, dev, C.c_void_p(cuda_stream or 0)))
+
+    # -- tensor-parallel groups ------------------------------------------------
+    def tp_region_bytes(self, nranks: int, max_payload_bytes: int) -> int:
+        return int(self.lib.rstq_tp_region_bytes(nranks, max_payload_bytes))
+
+    def tp_create_local(self, devs, max_payload_bytes: int) -> list:
+        """One endpoint per device index of this context (one process driving all GPUs)."""
+        n = len(devs)
+        arr = (C.c_int32 * n)(*devs)
+        hs = (C.c_void_p * n)()
+        L.check(self.lib.rstq_tp_create_local(self.handle, n, arr, max_payload_bytes, hs))
+        return [TpEndpoint(self, C.c_void_p(hs[r]), r, n, devs[r]) for r in range(n)]
+
+    def tp_attach(self, rank: int, nranks: int, region_ptrs, region_bytes: int, dev=0) -> TpEndpoint:
+        """This process's endpoint; region_ptrs[r] = rank r's zero-filled region as this device
+        addresses it (symmetric memory or an IPC mapping)."""
+        arr = (C.c_void_p * nranks)(*[int(p) for p in region_ptrs])
+        h = C.c_void_p()
+        L.check(self.lib.rstq_tp_attach(self.handle, dev, rank, nranks, arr, region_bytes, C.byref(h)))
+        return TpEndpoint(self, h, rank, nranks, dev)
 
     # -- weights ---------------------------------------------------------
     def bind_weight(self, codes, scales, out, in_, fmt, layout, dev=0, split=L.SPLIT_NONE,
