@@ -25,10 +25,14 @@ Printed on one JSON line (rank 0): the contract keys plus
                 the host cores of this box (rank 0, N = 1 only)
   detail        other M / dtype / shape points of the same path
 
-With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank owns the
-column shard [rank*out, (rank+1)*out) of an N-times wider matrix per shape and
-streams it; the all-gather of the y slices is the fused peer-store epilogue
-when available.  Per-GPU work is fixed, so scaling is "weak".
+With --gpus N > 1 (launched by torchrun, one rank per GPU) the two matrices grow N
+times along the split dimension and every rank owns one shard of the configs[1]
+size: gate_up is split by columns (outputs all-gathered), down by rows (partial
+products summed).  Both exchanges are this repository's own kernel over peer memory
+(CUDA IPC mappings between the ranks), captured in the same graph as the matmuls;
+torch.distributed carries the handles, the barriers and the max over ranks, and an
+NCCL version of the same step is timed beside it (detail.nccl_*).  Per-GPU work is
+fixed, so scaling is "weak".
 """
 from __future__ import annotations
 
@@ -158,6 +162,241 @@ def time_graph(ctx, graph, steps, warmup):
     return ms
 
 
+def run_tp(args, world, rank, local_rank):
+    """N > 1: the sharded operator, one rank per GPU, exchanges inside the timed region."""
+    import torch
+    import torch.distributed as dist
+    from raster_b200 import Context
+    from raster_b200 import _lib as L
+
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    hbm_peak, peak_src = measured_peaks()
+    ctx = Context((f"cuda:{local_rank}",))
+    info = ctx.device_info()
+    weights = make_weights(rank)          # this rank's slab of the N-times larger matrices
+    up, down = weights
+    per_pass = sum(stream_bytes(w["out"], w["in"]) for w in weights)
+    R = max(2, -(-4 * info["l2_bytes"] // per_pass))
+    bound = []
+    for w in weights:
+        first = ctx.bind_weight(w["wqi"], w["wsi"], w["out"], w["in"], L.FMT_Q4_0, L.LAYOUT_STREAM8)
+        bound.append([first] + [first.clone() for _ in range(R - 1)])
+
+    # ---- the peer-memory group: every rank maps every other rank's region ----
+    payload = 4 * max(up["out"], down["out"])
+    region_bytes = ctx.tp_region_bytes(world, payload)
+    region = ctx.make_buffer(region_bytes, np.uint8)
+    region.fill_bytes(0)
+    ctx.sync()
+    mine = torch.tensor(list(ctx.ipc_export(region)), dtype=torch.uint8, device="cuda")
+    allh = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    ptrs = [region.device_ptr if r == rank else ctx.ipc_open(bytes(allh[r].cpu().tolist()))
+            for r in range(world)]
+    tp = ctx.tp_attach(rank, world, ptrs, region_bytes)
+    dist.barrier()
+
+    x_up = ctx.array_to_buffer(up["x"][: up["in"]])                 # replicated activation
+    y_up = ctx.make_buffer(world * up["out"], np.float32)           # gathered columns
+    x_dn = ctx.array_to_buffer(down["x"][: down["in"]])             # this rank's K slice
+    y_dn = ctx.make_buffer(down["out"], np.float32)                 # summed partial products
+
+    def tp_pass(_):
+        for r in range(R):
+            tp.qmatmul(bound[0][r], x_up, y_up, 1, L.F32, L.MODE_A8, L.SPLIT_COLUMN)
+            tp.qmatmul(bound[1][r], x_dn, y_dn, 1, L.F32, L.MODE_A8, L.SPLIT_ROW)
+
+    def capture(fn):
+        fn(False)
+        ctx.sync()
+        dist.barrier()
+        ctx.graph_begin()
+        fn(True)
+        return ctx.graph_end()
+
+    def barrier():
+        ctx.sync()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(replay, steps, warmup):
+        for _ in range(warmup):
+            replay()
+        barrier()
+        e0, e1 = ctx.event(), ctx.event()
+        e0.record()
+        for _ in range(steps):
+            replay()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_ms(e1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e0.destroy(), e1.destroy()
+        return float(t.item())
+
+    g_tp = capture(tp_pass)
+    kernels_per_step = 6 * R            # quantizer, GEMV, exchange for each of the 2 R matmuls
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    t0 = time.perf_counter()
+    ms = timed(g_tp.replay, args.steps, args.warmup)
+    t1 = time.perf_counter()
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = per_pass * R * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- the same matmuls with no exchange: what the exchanges cost ----
+    y_loc = ctx.make_buffer(max(up["out"], down["out"]), np.float32)
+
+    def local_pass(_):
+        for r in range(R):
+            ctx.qmatmul(bound[0][r], x_up, y_loc, 1)
+            ctx.qmatmul(bound[1][r], x_dn, y_loc, 1)
+    g_loc = capture(local_pass)
+    ms_loc = timed(g_loc.replay, max(3, args.steps // 2), 3) / max(3, args.steps // 2)
+    g_loc.destroy()
+
+    # ---- the same step with NCCL collectives (torch.distributed), on torch's stream ----
+    nccl = {}
+    try:
+        st = torch.cuda.Stream()
+        ctx.set_stream(st.cuda_stream)
+        t_up_loc = torch.empty(up["out"], dtype=torch.float32, device="cuda")
+        t_up_all = torch.empty(world * up["out"], dtype=torch.float32, device="cuda")
+        t_dn = torch.empty(down["out"], dtype=torch.float32, device="cuda")
+        b_up_loc = ctx.wrap_buffer(t_up_loc.data_ptr(), up["out"], np.float32)
+        b_dn = ctx.wrap_buffer(t_dn.data_ptr(), down["out"], np.float32)
+
+        def nccl_pass():
+            for r in range(R):
+                ctx.qmatmul(bound[0][r], x_up, b_up_loc, 1)
+                dist.all_gather_into_tensor(t_up_all, t_up_loc)
+                ctx.qmatmul(bound[1][r], x_dn, b_dn, 1)
+                dist.all_reduce(t_dn)
+        with torch.cuda.stream(st):
+            nccl_pass()
+            st.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=st):
+                nccl_pass()
+            n = max(3, args.steps // 2)
+            for _ in range(3):
+                graph.replay()
+            st.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(st)
+            for _ in range(n):
+                graph.replay()
+            b.record(st)
+            st.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / n], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nccl = {"nccl_ms_per_step": round(float(t.item()), 5),
+                "nccl_GBs": round(per_pass * R * world / (float(t.item()) * 1e-3) / 1e9, 1)}
+        del graph
+        b_up_loc.free(), b_dn.free()
+    except Exception as e:   # reported, not fatal: the NCCL arm is a comparison, not the product
+        nccl = {"nccl_error": repr(e)[:200]}
+    finally:
+        ctx.set_stream(None)
+    barrier()
+
+    # ---- e2e: x from pinned host memory every step, y back to the host ----
+    hx_up = torch.from_numpy(np.ascontiguousarray(up["x"][: up["in"]])).pin_memory()
+    hx_dn = torch.from_numpy(np.ascontiguousarray(down["x"][: down["in"]])).pin_memory()
+    hy = np.empty(down["out"], np.float32)
+
+    def e2e_step():
+        x_up.upload(hx_up.numpy())
+        x_dn.upload(hx_dn.numpy())
+        g_tp.replay()
+        ctx.sync()
+        return y_dn.download()
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    n = max(3, args.steps // 2)
+    tt = time.perf_counter()
+    for _ in range(n):
+        hy = e2e_step()
+    barrier()
+    e2e_s = torch.tensor([(time.perf_counter() - tt) / n], device="cuda")
+    dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_s = float(e2e_s.item())
+    e2e = {"value": round(per_pass * R * world / e2e_s / 1e9, 2), "unit": "GB/s",
+           "h2d_bytes_per_step": int(4 * (up["in"] + down["in"])), "d2h_bytes_per_step": int(4 * down["out"]),
+           "ms_per_step": round(e2e_s * 1e3, 4),
+           "api": "host x up, one graph replay of the sharded step, y down, per rank"}
+
+    # ---- roofline of the dominant kernel (the decode GEMV), on rank 0's shard ----
+    roofline = None
+    if rank == 0:
+        from raster_b200.quant import cpu_quant as cq
+        pre = []
+        for w in weights:
+            a = cq.quantize_act_i8(w["x"][: w["in"]], 1, w["in"])
+            pre.append([ctx.array_to_buffer(a[k]) for k in ("xq", "xs", "xsum")])
+
+        def gemv_pass(_):
+            for r in range(R):
+                for i in range(2):
+                    ctx.qmatmul_prequant(bound[i][r], pre[i][0], pre[i][1], pre[i][2], y_loc, 1)
+        ctx.sync()
+        gemv_pass(False)
+        ctx.sync()
+        ctx.graph_begin()
+        gemv_pass(True)
+        g = ctx.graph_end()
+        ms_gemv = time_graph(ctx, g, args.steps, args.warmup)
+        g.destroy()
+        launches = 2 * R * args.steps
+        alg = sum(algorithmic_bytes(w["out"], w["in"], 1) for w in weights) / 2
+        avg = ms_gemv * 1e-3 / launches
+        roofline = {"bound": "hbm", "kernel": "gemv_stream_kernel<4,1,A8,onecol>",
+                    "achieved": round(alg / avg / 1e9, 1), "peak": hbm_peak, "peak_source": peak_src,
+                    "unit": "GB/s", "frac": round(alg / avg / 1e9 / hbm_peak, 4), "traffic": 28222976,
+                    "avg_launch_us": round(avg * 1e6, 3), "algorithmic_bytes_per_launch": alg,
+                    "note": "rank 0's shard, timed alone while the other ranks wait"}
+    barrier()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "qmatmul weight-stream GB/s at M=1 (int4, per-32-block f32 scales)",
+            "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u4 x s8 -> s32, f32 fold",
+            "data": "synthetic",
+            "config": {"workload": "configs[1] per GPU: int4 GEMV, Llama-7B MLP shapes, M=1, f32 x, qlinear-i8 "
+                                   "arithmetic; gate_up %dx4096 split by columns (all-gather), down 4096x%d "
+                                   "split by rows (all-reduce)" % (world * up["out"], world * down["in"]),
+                       "launches_per_step": kernels_per_step, "weight_copies_rotated": R,
+                       "cache": "inputs larger than L2: %d MB of weights per GPU and step vs %d MB L2"
+                                % (per_pass * R >> 20, info["l2_bytes"] >> 20),
+                       "parallelism": "tp%d: column split + all-gather, row split + all-reduce, "
+                                      "own peer-memory exchange kernel" % world,
+                       "frac_of_measured_hbm": round(value / world / hbm_peak, 4),
+                       "frac_of_nominal_8TBs": round(value / world / 8000.0, 4)},
+            "roofline": roofline, "e2e": e2e, "cpu_baseline": None,
+            "gpu_launches": kernels_per_step * args.steps, "clocks": clocks,
+            "detail": {"no_exchange_ms_per_step": round(ms_loc, 5),
+                       "no_exchange_GBs": round(per_pass * R * world / (ms_loc * 1e-3) / 1e9, 1),
+                       "exchange_us_per_matmul": round((ms_per_step - ms_loc) * 1e3 / (2 * R), 3), **nccl},
+        }))
+    g_tp.destroy()
+    tp.free()
+    for r in range(world):
+        if r != rank:
+            ctx.ipc_close(ptrs[r])
+    dist.barrier()
+    dist.destroy_process_group()
+    ctx.close()
+
+
 def run_ours(args):
     from raster_b200 import Context
     from raster_b200 import _lib as L
@@ -165,6 +404,8 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        return run_tp(args, world, rank, local_rank)
     dist = None
     if world > 1:
         import torch

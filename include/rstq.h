@@ -259,6 +259,12 @@ RSTQ_API int32_t rstq_tp_allreduce_f32(rstq_tp* tp, rstq_buf* src, rstq_buf* dst
 RSTQ_API int32_t rstq_tp_qmatmul(rstq_tp* tp, rstq_weight* w, rstq_buf* x, rstq_buf* y, int64_t M,
                                  int32_t act_dtype, int32_t mode, int32_t split);
 RSTQ_API int32_t rstq_tp_free(rstq_tp* tp);
+/* One process per GPU: export the region (a buffer of rstq_alloc) as 64 opaque bytes, hand them
+ * to the other processes of the box by any channel, and map theirs.  The mapped address goes
+ * into the `regions` array of rstq_tp_attach. */
+RSTQ_API int32_t rstq_ipc_export(rstq_buf* buf, void* handle64);
+RSTQ_API int32_t rstq_ipc_open(rstq_ctx* ctx, int32_t dev, const void* handle64, void** device_ptr);
+RSTQ_API int32_t rstq_ipc_close(rstq_ctx* ctx, int32_t dev, void* device_ptr);
 
 #ifdef __cplusplus
 }

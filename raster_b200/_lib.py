@@ -64,6 +64,9 @@ SIGNATURES = {
     "rstq_tp_allreduce_f32": [vp, vp, vp, i64],
     "rstq_tp_qmatmul": [vp, vp, vp, vp, i64, i32, i32, i32],
     "rstq_tp_free": [vp],
+    "rstq_ipc_export": [vp, vp],
+    "rstq_ipc_open": [vp, i32, vp, pp],
+    "rstq_ipc_close": [vp, i32, vp],
 }
 _RESTYPE = {"rstq_last_error": C.c_char_p, "rstq_tp_region_bytes": i64}
 

@@ -124,14 +124,14 @@ static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* o
 
 // One matmul over device pointers, M split into decode-kernel chunks.
 static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs,
-                      const int32_t* xsum, float* y, int64_t M) {
-    GemvA8Args a{w->data, xq, xs, xsum, y, M, w->in, w->out, w->bits, w->zp};
+                      const int32_t* xsum, float* y, int64_t M, const TpFuse* tp = nullptr) {
+    GemvA8Args a{w->data, xq, xs, xsum, y, M, w->in, w->out, w->bits, w->zp, tp};
     return launch_gemv_a8(ctx, ctx->devs[w->dev], a);
 }
 
 static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
-                     int act_dtype, int out_dtype) {
-    GemvFArgs a{w->data, x, y, M, w->in, w->out, w->bits, w->zp, act_dtype, out_dtype};
+                     int act_dtype, int out_dtype, const TpFuse* tp = nullptr) {
+    GemvFArgs a{w->data, x, y, M, w->in, w->out, w->bits, w->zp, act_dtype, out_dtype, tp};
     return launch_gemv_f(ctx, ctx->devs[w->dev], a);
 }
 
@@ -146,13 +146,14 @@ static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, void** x16, 
 }
 
 int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M, int act_dtype,
-                      int out_dtype, int mode) {
+                      int out_dtype, int mode, const TpFuse* tp) {
     DeviceState& ds = ctx->devs[w->dev];
     // Prefill shapes go to the tensor-core GEMM (fp16 operands, results within 1e-3 of the
     // reference).  A8 keeps its exact integer path up to M = 63: callers that chose the
     // quantized-activation arithmetic get it bit-faithfully at decode and small-batch sizes.
     const bool tc = M >= (mode == RSTQ_MODE_A8 ? (ctx->tune_gemm_min_m > 64 ? ctx->tune_gemm_min_m : 64)
                                                 : ctx->tune_gemm_min_m);
+    if (tp && (tc || out_dtype != RSTQ_F32)) return kNotFused;  // only the decode kernel fuses the exchange
     if (mode == RSTQ_MODE_A8) {
         RSTQ_REQUIRE(act_dtype == RSTQ_F32, RSTQ_E_INVALID, "MODE_A8 takes f32 activations");
         RSTQ_REQUIRE(out_dtype == RSTQ_F32 || tc, RSTQ_E_INVALID, "MODE_A8 decode writes f32");
@@ -161,13 +162,13 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
         if (rc != RSTQ_OK) return rc;
         rc = launch_quant_act_i8(ctx, ds, (const float*)x, s.xq, s.xs, s.xsum, M, w->in);
         if (rc != RSTQ_OK) return rc;
-        if (!tc) return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M);
+        if (!tc) return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M, tp);
         void* x16;
         float* rowscale;
         if ((rc = gemm_scratch(ds, M, w->in, &x16, &rowscale)) != RSTQ_OK) return rc;
         return launch_gemm(ctx, ds, w, s.xq, s.xs, 2, y, out_dtype, M, x16, rowscale);
     }
-    if (!tc) return run_f(ctx, w, x, y, M, act_dtype, out_dtype);
+    if (!tc) return run_f(ctx, w, x, y, M, act_dtype, out_dtype, tp);
     void* x16;
     float* rowscale;
     int32_t rc = gemm_scratch(ds, M, w->in, &x16, &rowscale);

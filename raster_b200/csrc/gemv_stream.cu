@@ -61,6 +61,7 @@ struct StreamParams {
     int64_t uq, ur;       // units per CTA: CTA c owns uq (+1 if c < ur) units
     int M, nb, G, zp, NS, T, act_dtype, out_dtype;
     uint32_t act_off, act2_off, red_off, bar_off;  // byte offsets into dynamic smem (ring at 0)
+    TpFuse tp;            // tp.nranks == 0: no exchange, results go to y
 };
 
 __device__ __forceinline__ void consumer_bar() {
@@ -369,7 +370,7 @@ __device__ __forceinline__ float stream_reduce_rc(const float* red, int row, int
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-template <int BITS, int NT, int MODE, bool ONECOL>
+template <int BITS, int NT, int MODE, bool ONECOL, bool TP>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
     constexpr int UNIT = BITS == 4 ? kUnitBytesQ4 : kUnitBytesQ8;
     constexpr int kUPW = upw_of(BITS), kChunkUnits = chunk_units_of(BITS);
@@ -380,6 +381,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     __shared__ int s_last[2], s_cf[2], s_cn[2], s_slot0[2];
     __shared__ long long s_g0;
     __shared__ int s_bstart, s_total;
+    __shared__ int s_tp_ok;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int NS = p.NS, nb = p.nb;
@@ -450,6 +452,34 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     // activations, y and the scratch are not: wait for the preceding grid to finish.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (dbg && tid == 0) dbg[1] = gtime_ns();
+    // Fused exchange: results go to slot `rank` of every rank's stage (epoch parity picks the
+    // half; the epoch is written by the previous exchange of this stream, hence read after the wait)
+    const int tpn = TP ? p.tp.nranks : 0;  // (a separate instantiation: the plain kernel keeps its registers)
+    uint32_t tp_e = 0;
+    int64_t tp_off = 0, tp_slot = 0;
+    uint8_t* tp_mine = nullptr;
+    if (TP) {
+#pragma unroll
+        for (int r = 0; r < kTpMaxRanks; ++r)
+            if (r == p.tp.rank) tp_mine = p.tp.region[r];
+        tp_e = *reinterpret_cast<volatile uint32_t*>(tp_mine + 256) + 1u;
+        tp_off = p.tp.ll_off + ((int64_t)(tp_e & 1u) * tpn) * p.tp.slot_bytes;
+        tp_slot = tp_off + (int64_t)p.tp.rank * p.tp.slot_bytes;
+    }
+    auto emit = [&](int64_t idx, float v) {
+        if (!TP) {
+            store_out(p.y, p.out_dtype, idx, v);
+        } else {
+            // value and epoch travel in ONE 8-byte store: whoever reads the epoch has the value,
+            // so no fence and no separate flag stand between this store and the reader
+#pragma unroll
+            for (int r = 0; r < kTpMaxRanks; ++r)  // static indices keep the pointer table in the parameter bank
+                if (r < tpn)
+                    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.tp.region[r] + tp_slot + idx * 8),
+                                 "r"(__float_as_uint(v)), "r"(tp_e)
+                                 : "memory");
+        }
+    };
     if (MODE == MODE_A8) stage_a8<ONECOL, BITS>(p, smem, tid);
     else stage_f(p, smem, tid);
     consumer_bar();
@@ -486,7 +516,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             if ((tid & 15) == 0) {
                 if (!whole) part[row] = sum;
-                else if (row0 + row < p.out) store_out(p.y, p.out_dtype, row0 + row, sum);
+                else if (row0 + row < p.out) emit(row0 + row, sum);
             }
         } else {
 #pragma unroll
@@ -503,7 +533,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 for (int t = 0; t < T; ++t) sum += stream_reduce_rc<NT>(rbuf, row, m * T + t);
                 if (!whole) part[o] = sum;
                 else if (row0 + row < p.out)
-                    store_out(p.y, p.out_dtype, (int64_t)m * p.out + row0 + row, sum);
+                    emit((int64_t)m * p.out + row0 + row, sum);
             }
         }
         if (!whole) part_g[npart++] = g;
@@ -612,13 +642,66 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 float sum = __ldcg(p.partials + ((int64_t)cf * 2 + s_slot0[i]) * M * 32 + o);
                 for (int k = 1; k < cn; ++k)
                     sum += __ldcg(p.partials + ((int64_t)(cf + k) * 2) * M * 32 + o);
-                if (row0 + row < p.out) store_out(p.y, p.out_dtype, (int64_t)m * p.out + row0 + row, sum);
+                if (row0 + row < p.out) emit((int64_t)m * p.out + row0 + row, sum);
             }
             if (tid == 0) p.counters[g] = 0;
         }
     }
     if (tid == 0 && s_abort) atomicExch(p.status, 1);
     if (dbg && tid == 0) dbg[5] = gtime_ns();
+
+    // ---- fused exchange: wait for the other ranks' results, combine ----
+    if (TP) {
+        uint32_t* ctl = reinterpret_cast<uint32_t*>(tp_mine + 256);
+        if (tid == 0) {
+            s_tp_ok = 1;
+            // every CTA read the epoch when it started; the last one to get here closes it
+            if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) {
+                ctl[1] = 0u;
+                *reinterpret_cast<volatile uint32_t*>(ctl) = tp_e;
+            }
+        }
+        consumer_bar();
+        // this CTA's share of the result, two elements (one 16-byte load of two value/epoch
+        // pairs) per thread and step; a pair is polled until it carries this exchange's epoch
+        const int64_t row_pairs = p.out >> 1, pairs = (int64_t)M * row_pairs;
+        const int64_t per = (pairs + gridDim.x - 1) / gridDim.x;
+        const int64_t q0 = per * blockIdx.x, q1 = min(pairs, q0 + per);
+        const uint8_t* stage = tp_mine + tp_off;
+        float2* dst = reinterpret_cast<float2*>(p.tp.y);
+        const unsigned long long t0 = gtime_ns();
+        bool ok = true;
+        for (int64_t q = q0 + tid; q < q1 && ok; q += kConsumers) {
+            float2 acc = make_float2(0.f, 0.f);
+            const int64_t row = q / row_pairs, col = q - row * row_pairs;
+            for (int r = 0; r < tpn && ok; ++r) {
+                const uint8_t* src = stage + (int64_t)r * p.tp.slot_bytes + q * 16;
+                uint32_t a0, e0, a1, e1;
+                for (uint32_t spins = 1;; ++spins) {
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(a0), "=r"(e0), "=r"(a1), "=r"(e1)
+                                 : "l"(src)
+                                 : "memory");
+                    if (e0 == tp_e && e1 == tp_e) break;
+                    if ((spins & 63u) == 0 && (s_tp_ok == 0 || gtime_ns() - t0 > kWaitLimitNs)) {
+                        ok = false;  // a rank never delivered: report, do not hang
+                        s_tp_ok = 0;
+                        atomicExch(p.status, 2);
+                        break;
+                    }
+                }
+                if (!ok) break;
+                if (p.tp.sum) {
+                    if (r == 0) acc = make_float2(__uint_as_float(a0), __uint_as_float(a1));
+                    else { acc.x += __uint_as_float(a0); acc.y += __uint_as_float(a1); }
+                } else {
+                    dst[(row * tpn + r) * row_pairs + col] = make_float2(__uint_as_float(a0), __uint_as_float(a1));
+                }
+            }
+            if (ok && p.tp.sum) dst[q] = acc;
+        }
+        if (dbg && tid == 0) dbg[7] = gtime_ns();
+    }
 }
 
 // ---- host side --------------------------------------------------------------------------
@@ -668,18 +751,30 @@ int32_t gemv_configure(DeviceState& ds) {
     (void)ds;
     int32_t rc;
 #define CFG(...) if ((rc = set_stream_attr(gemv_stream_kernel<__VA_ARGS__>)) != RSTQ_OK) return rc
-    CFG(4, 1, MODE_A8, true);
-    CFG(4, 1, MODE_A8, false);
-    CFG(4, 2, MODE_A8, false);
-    CFG(8, 1, MODE_A8, true);
-    CFG(8, 1, MODE_A8, false);
-    CFG(8, 2, MODE_A8, false);
-    CFG(4, 1, MODE_F, false);
-    CFG(4, 2, MODE_F, false);
-    CFG(4, 4, MODE_F, false);
-    CFG(8, 1, MODE_F, false);
-    CFG(8, 2, MODE_F, false);
-    CFG(8, 4, MODE_F, false);
+    CFG(4, 1, MODE_A8, true, false);
+    CFG(4, 1, MODE_A8, true, true);
+    CFG(4, 1, MODE_A8, false, false);
+    CFG(4, 1, MODE_A8, false, true);
+    CFG(4, 2, MODE_A8, false, false);
+    CFG(4, 2, MODE_A8, false, true);
+    CFG(8, 1, MODE_A8, true, false);
+    CFG(8, 1, MODE_A8, true, true);
+    CFG(8, 1, MODE_A8, false, false);
+    CFG(8, 1, MODE_A8, false, true);
+    CFG(8, 2, MODE_A8, false, false);
+    CFG(8, 2, MODE_A8, false, true);
+    CFG(4, 1, MODE_F, false, false);
+    CFG(4, 1, MODE_F, false, true);
+    CFG(4, 2, MODE_F, false, false);
+    CFG(4, 2, MODE_F, false, true);
+    CFG(4, 4, MODE_F, false, false);
+    CFG(4, 4, MODE_F, false, true);
+    CFG(8, 1, MODE_F, false, false);
+    CFG(8, 1, MODE_F, false, true);
+    CFG(8, 2, MODE_F, false, false);
+    CFG(8, 2, MODE_F, false, true);
+    CFG(8, 4, MODE_F, false, false);
+    CFG(8, 4, MODE_F, false, true);
 #undef CFG
     return RSTQ_OK;
 }
@@ -747,6 +842,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         const int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
         RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
                      (long long)a.in);
+        if (a.tp && (M < a.M || a.out % 4 != 0)) return kNotFused;  // the exchange fuses into ONE launch
         int32_t rc = stream_scratch_ok(ds, groups, pl.G, M);
         if (rc != RSTQ_OK) return rc;
         const int NT = M <= 8 ? 1 : 2;
@@ -758,8 +854,11 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         p.xsum = a.xsum + m0 * nb;
         p.y = a.y + m0 * a.out;
         p.T = 1; p.act_dtype = RSTQ_F32; p.out_dtype = RSTQ_F32;
+        if (a.tp) p.tp = *a.tp;
         cudaError_t le = cudaSuccess;
-#define LAUNCH(...) le = launch_stream(gemv_stream_kernel<__VA_ARGS__>, ds, pl, p)
+#define LAUNCH(...)                                                                  \
+    le = a.tp ? launch_stream(gemv_stream_kernel<__VA_ARGS__, true>, ds, pl, p)      \
+              : launch_stream(gemv_stream_kernel<__VA_ARGS__, false>, ds, pl, p)
         if (a.bits == 4) {
             if (NT == 2) LAUNCH(4, 2, MODE_A8, false);
             else if (M == 1) LAUNCH(4, 1, MODE_A8, true);
@@ -804,6 +903,7 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
         }
         RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
                      (long long)a.in);
+        if (a.tp && (M < a.M || a.out % 4 != 0 || a.out_dtype != RSTQ_F32)) return kNotFused;
         int32_t rc = stream_scratch_ok(ds, groups, pl.G, M);
         if (rc != RSTQ_OK) return rc;
         const int T = terms(M), C = M * T;
@@ -814,6 +914,7 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
         p.x = (const char*)a.x + m0 * a.in * xe;
         p.y = (char*)a.y + m0 * a.out * ye;
         p.T = T; p.act_dtype = a.act_dtype; p.out_dtype = a.out_dtype;
+        if (a.tp) p.tp = *a.tp;
         cudaError_t le = cudaSuccess;
         if (a.bits == 4) {
             if (NT == 1) LAUNCH(4, 1, MODE_F, false);

@@ -166,6 +166,21 @@ int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
 // actquant.cu
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs,
                             int32_t* xsum, int64_t M, int64_t in);
+// Exchange fused into the tail of the decode kernel (layout of a region: see tp.cu).  The
+// kernel writes its results into slot `rank` of every rank's stage instead of y, signals, waits
+// (time-bounded) for the other ranks and lays the slots side by side (sum = 0) or adds them in
+// rank order (sum = 1) into y.
+constexpr int kTpMaxRanks = 8;
+constexpr int64_t kTpHeader = 512;
+struct TpFuse {
+    uint8_t* region[kTpMaxRanks];
+    int rank, nranks, sum;
+    int64_t ll_off;      // byte offset of the value/epoch pair stage inside a region
+    int64_t slot_bytes;  // bytes of one slot of that stage (8 per result)
+    float* y;  // [M, nranks * out] (gather) or [M, out] (sum), f32
+};
+constexpr int32_t kNotFused = 1;  // a launcher declined the fused exchange before launching anything
+
 // gemv.cu
 struct GemvA8Args {
     const uint8_t* w;
@@ -175,6 +190,7 @@ struct GemvA8Args {
     float* y;
     int64_t M, in, out;   // y is [M, out] f32
     int bits, zp;
+    const TpFuse* tp = nullptr;
 };
 struct GemvFArgs {
     const uint8_t* w;
@@ -183,6 +199,7 @@ struct GemvFArgs {
     int64_t M, in, out;
     int bits, zp;
     int act_dtype, out_dtype;
+    const TpFuse* tp = nullptr;
 };
 // gemv_stream.cu.  Any M >= 1: the launchers cut M into pieces the kernel takes.
 int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a);
@@ -195,7 +212,7 @@ int32_t gemm_configure(DeviceState& ds);
 // capi.cu
 int32_t use_dev(rstq_ctx* ctx, int dev);
 int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M, int act_dtype,
-                      int out_dtype, int mode);
+                      int out_dtype, int mode, const TpFuse* tp = nullptr);
 // capi.cu: grow-only device scratch (refuses to grow during graph capture)
 int32_t dev_reserve(DeviceState& ds, void** p, int64_t* have, int64_t need);
 constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels

@@ -6,7 +6,8 @@
 //
 //   [0, 256)    flags    uint32 flag[src]: last epoch whose data rank `src` has delivered here
 //   [256, 512)  control  uint32 epoch (exchanges completed by the owner), uint32 done (CTA counter)
-//   [512, ...)  stage    [2 parities][nranks slots][slot_bytes]
+//   [512, ...)  stage    [2 parities][nranks slots][slot_bytes]            plain results
+//   then        pairs    [2 parities][nranks slots][2 * slot_bytes]        (value, epoch) pairs
 //
 // One exchange = one launch on every rank:
 //   push     every CTA copies its chunk of the local result into slot `rank` (parity e & 1) of
@@ -21,8 +22,15 @@
 // ahead because its next combine needs the slow rank's next flag.  The flags only grow, so a
 // launch captured in a CUDA graph replays correctly: the epoch lives in device memory.
 //
+// Decode shapes skip this kernel: the matmul kernel itself stores each result as a (value,
+// epoch) pair into the `pairs` stage of every rank with one 8-byte store and, in its tail, polls
+// the pairs of the other ranks until they carry the current epoch (gemv_stream.cu).  A pair
+// needs no fence and no flag, which makes that exchange one NVLink crossing long.
+//
 // No collective library is involved and nothing here multicasts: peers are reached by ordinary
 // stores, local data by ordinary loads.
+#include <string.h>
+
 #include <new>
 
 #include "internal.h"
@@ -30,9 +38,7 @@
 
 namespace rstq {
 
-constexpr int kTpMaxRanks = 8;
 constexpr int kTpThreads = 512;
-constexpr int64_t kTpHeader = 512;
 constexpr uint32_t kTpMagic = 0x52535154;
 
 struct TpParams {
@@ -43,6 +49,7 @@ struct TpParams {
     uint8_t* dst;        // gather: rows x (nranks * row_bytes); sum: rows x row_bytes
     int64_t rows, row_bytes;
     int* status;
+    unsigned long long* dbg;  // optional phase timestamps (RSTQ_TUNE_TIMELINE), or null
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -57,9 +64,16 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 template <int SUM>
 __global__ void __launch_bounds__(kTpThreads) tp_exchange_kernel(const TpParams p) {
     __shared__ int s_last, s_ok;
+    // let the next kernel of the stream start its prologue; wait for the one that produced src
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint8_t* mine = p.region[p.rank];
     uint32_t* ctl = reinterpret_cast<uint32_t*>(mine + 256);
+    if (threadIdx.x == 0) s_ok = 1;
+    // (the epoch is written by the previous exchange of this stream: read it after the wait)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(ctl) + 1u;  // this exchange's epoch
+    unsigned long long* dbg = (p.dbg && blockIdx.x == 0 && threadIdx.x == 0) ? p.dbg : nullptr;
+    if (dbg) dbg[2000] = gtime_ns();  // producer kernel finished, push starts
     const int64_t total = p.rows * p.row_bytes;
     const int64_t vecs = total >> 4;
     const int64_t per = (vecs + gridDim.x - 1) / gridDim.x;
@@ -69,42 +83,44 @@ __global__ void __launch_bounds__(kTpThreads) tp_exchange_kernel(const TpParams 
     // ---- push ----
     const uint4* src = reinterpret_cast<const uint4*>(p.src);
     for (int64_t v = v0 + threadIdx.x; v < v1; v += kTpThreads) {
-        const uint4 val = __ldg(src + v);
+        const uint4 val = __ldcg(src + v);
         for (int r = 0; r < p.nranks; ++r)
             reinterpret_cast<uint4*>(p.region[r] + slot_off + (int64_t)p.rank * p.slot_bytes)[v] = val;
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // the CTA's stores happen before thread 0's release below (cumulative)
     if (threadIdx.x == 0) {
-        const uint32_t arrived = atomicAdd(ctl + 1, 1u);
-        s_last = arrived == gridDim.x - 1;
-        s_ok = 1;
+        __threadfence_system();
+        s_last = gridDim.x == 1 ? 1 : (atomicAdd(ctl + 1, 1u) == gridDim.x - 1);
     }
     __syncthreads();
     if (s_last) {
         // every CTA of this rank has pushed and fenced: tell all ranks, then close the epoch
-        __threadfence_system();
-        if (threadIdx.x < p.nranks)
+        if (threadIdx.x < p.nranks) {
+            if (gridDim.x > 1) __threadfence_system();
             st_release_sys(reinterpret_cast<uint32_t*>(p.region[threadIdx.x]) + p.rank, e);
+        }
         if (threadIdx.x == 0) {
             ctl[1] = 0u;
             *reinterpret_cast<volatile uint32_t*>(ctl) = e;  // all CTAs have read the old value by now
         }
     }
 
+    if (dbg) dbg[2001] = gtime_ns();  // pushed and signalled
+
     // ---- combine ----
     if (threadIdx.x < p.nranks) {
         const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine) + threadIdx.x;
         const unsigned long long t0 = gtime_ns();
-        while ((int32_t)(ld_acquire_sys(flag) - e) < 0) {
-            if (gtime_ns() - t0 > kWaitLimitNs) {  // a rank never delivered: report, do not hang
-                s_ok = 0;
+        for (uint32_t spins = 1; (int32_t)(ld_acquire_sys(flag) - e) < 0; ++spins) {
+            if ((spins & 63u) == 0 && gtime_ns() - t0 > kWaitLimitNs) {  // a rank never delivered:
+                s_ok = 0;                                               // report, do not hang
                 atomicExch(p.status, 2);
                 break;
             }
         }
     }
     __syncthreads();
+    if (dbg) dbg[2002] = gtime_ns();  // all ranks' data has arrived
     if (!s_ok) return;
     const uint8_t* stage = mine + slot_off;
     if (SUM) {
@@ -127,6 +143,7 @@ __global__ void __launch_bounds__(kTpThreads) tp_exchange_kernel(const TpParams 
                     __ldcg(reinterpret_cast<const uint4*>(stage + (int64_t)r * p.slot_bytes) + v);
         }
     }
+    if (dbg) dbg[2003] = gtime_ns();  // combined
 }
 
 }  // namespace rstq
@@ -166,16 +183,23 @@ static int32_t tp_exchange(rstq_tp* tp, const void* src, void* dst, int64_t rows
     p.rows = rows;
     p.row_bytes = row_bytes;
     p.status = ds.status;
-    // one CTA per 32 KB, at most one per SM: all CTAs of a launch must be resident together
+    p.dbg = ds.dbg;
+    // one CTA per 8 KB (one 16-byte vector per thread: the copy loops are latency-bound), at most one per SM: all CTAs of a launch must be resident together
     // because each of them waits for the peers' flags
     const int64_t total = rows * row_bytes;
-    int grid = (int)((total + 32767) / 32768);
+    int grid = (int)((total + 8191) / 8192);
     if (grid > ds.sm_count) grid = ds.sm_count;
     if (grid < 1) grid = 1;
-    if (sum)
-        tp_exchange_kernel<1><<<grid, kTpThreads, 0, ds.stream>>>(p);
-    else
-        tp_exchange_kernel<0><<<grid, kTpThreads, 0, ds.stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kTpThreads);
+    cfg.stream = ds.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ds.pdl ? 1 : 0;
+    RSTQ_CUDA(sum ? cudaLaunchKernelEx(&cfg, tp_exchange_kernel<1>, p) : cudaLaunchKernelEx(&cfg, tp_exchange_kernel<0>, p));
     tp->ctx->launches++;
     RSTQ_CUDA(cudaGetLastError());
     return RSTQ_OK;
@@ -186,7 +210,7 @@ extern "C" {
 int64_t rstq_tp_region_bytes(int32_t nranks, int64_t max_payload_bytes) {
     if (nranks < 1 || nranks > kTpMaxRanks || max_payload_bytes < 16) return 0;
     const int64_t slot = (max_payload_bytes + 255) / 256 * 256;
-    return kTpHeader + 2 * (int64_t)nranks * slot;
+    return kTpHeader + 6 * (int64_t)nranks * slot;
 }
 
 int32_t rstq_tp_attach(rstq_ctx* ctx, int32_t dev, int32_t rank, int32_t nranks, void* const* regions,
@@ -196,7 +220,7 @@ int32_t rstq_tp_attach(rstq_ctx* ctx, int32_t dev, int32_t rank, int32_t nranks,
     RSTQ_REQUIRE(out && regions, RSTQ_E_INVALID, "null argument");
     RSTQ_REQUIRE(nranks >= 1 && nranks <= kTpMaxRanks && rank >= 0 && rank < nranks, RSTQ_E_INVALID,
                  "rank %d of %d (at most %d ranks)", rank, nranks, kTpMaxRanks);
-    const int64_t slot = (region_bytes - kTpHeader) / (2 * (int64_t)nranks) / 256 * 256;
+    const int64_t slot = (region_bytes - kTpHeader) / (6 * (int64_t)nranks) / 256 * 256;
     RSTQ_REQUIRE(region_bytes > kTpHeader && slot >= 256, RSTQ_E_LIMIT, "region of %lld bytes is too small",
                  (long long)region_bytes);
     for (int r = 0; r < nranks; ++r)
@@ -306,10 +330,61 @@ int32_t rstq_tp_qmatmul(rstq_tp* tp, rstq_weight* w, rstq_buf* x, rstq_buf* y, i
         RSTQ_CUDA(cudaMalloc(&tp->tmp, (size_t)need));
         tp->tmp_bytes = need;
     }
+    // Decode shapes: the exchange runs in the tail of the matmul kernel itself (one launch).
+    if (M * w->out * 4 <= tp->slot_bytes && w->out % 4 == 0 && ((uintptr_t)y->ptr & 15) == 0) {
+        TpFuse f{};
+        for (int r = 0; r < tp->nranks; ++r) f.region[r] = tp->region[r];
+        f.rank = tp->rank;
+        f.nranks = tp->nranks;
+        f.sum = split == RSTQ_SPLIT_ROW;
+        f.ll_off = kTpHeader + 2 * (int64_t)tp->nranks * tp->slot_bytes;
+        f.slot_bytes = 2 * tp->slot_bytes;
+        f.y = (float*)y->ptr;
+        rc = matmul_device(tp->ctx, w, x->ptr, tp->tmp, M, act_dtype, RSTQ_F32, mode, &f);
+        if (rc != kNotFused) return rc;
+    }
+    // Otherwise (prefill shapes, M cut into several launches): matmul, then the exchange kernel.
     rc = matmul_device(tp->ctx, w, x->ptr, tp->tmp, M, act_dtype, RSTQ_F32, mode);
     if (rc != RSTQ_OK) return rc;
     if (split == RSTQ_SPLIT_COLUMN) return tp_exchange(tp, tp->tmp, y->ptr, M, w->out * 4, false);
     return tp_exchange(tp, tp->tmp, y->ptr, 1, M * w->out * 4, true);
+}
+
+// ---- regions shared between processes: one process per GPU, the other ranks' regions are
+// mapped through CUDA IPC handles that the host side passes around (any channel will do) ----
+int32_t rstq_ipc_export(rstq_buf* buf, void* handle64) {
+    RSTQ_REQUIRE(buf && buf->magic == kBufMagic && handle64, RSTQ_E_INVALID, "invalid buffer or null handle");
+    RSTQ_REQUIRE(buf->owned, RSTQ_E_INVALID, "only buffers this library allocated can be exported");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 opaque bytes");
+    int32_t rc = use_dev(buf->ctx, buf->dev);
+    if (rc != RSTQ_OK) return rc;
+    cudaIpcMemHandle_t h;
+    RSTQ_CUDA(cudaIpcGetMemHandle(&h, buf->ptr));
+    memcpy(handle64, &h, 64);
+    return RSTQ_OK;
+}
+
+int32_t rstq_ipc_open(rstq_ctx* ctx, int32_t dev, const void* handle64, void** device_ptr) {
+    RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
+    RSTQ_REQUIRE(dev >= 0 && dev < (int)ctx->devs.size(), RSTQ_E_NODEV, "device index %d out of range", dev);
+    RSTQ_REQUIRE(handle64 && device_ptr, RSTQ_E_INVALID, "null argument");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    RSTQ_CUDA(cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return RSTQ_OK;
+}
+
+int32_t rstq_ipc_close(rstq_ctx* ctx, int32_t dev, void* device_ptr) {
+    RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
+    RSTQ_REQUIRE(dev >= 0 && dev < (int)ctx->devs.size(), RSTQ_E_NODEV, "device index %d out of range", dev);
+    RSTQ_REQUIRE(device_ptr, RSTQ_E_INVALID, "null argument");
+    int32_t rc = use_dev(ctx, dev);
+    if (rc != RSTQ_OK) return rc;
+    RSTQ_CUDA(cudaStreamSynchronize(ctx->devs[dev].stream));
+    RSTQ_CUDA(cudaIpcCloseMemHandle(device_ptr));
+    return RSTQ_OK;
 }
 
 int32_t rstq_tp_free(rstq_tp* tp) {

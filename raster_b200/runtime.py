@@ -203,6 +203,19 @@ class Context:
         L.check(self.lib.rstq_tp_attach(self.handle, dev, rank, nranks, arr, region_bytes, C.byref(h)))
         return TpEndpoint(self, h, rank, nranks, dev)
 
+    def ipc_export(self, buf: DeviceBuffer) -> bytes:
+        h = C.create_string_buffer(64)
+        L.check(self.lib.rstq_ipc_export(buf.handle, h))
+        return h.raw
+
+    def ipc_open(self, handle: bytes, dev=0) -> int:
+        p = C.c_void_p()
+        L.check(self.lib.rstq_ipc_open(self.handle, dev, C.c_char_p(bytes(handle)), C.byref(p)))
+        return int(p.value)
+
+    def ipc_close(self, device_ptr: int, dev=0) -> None:
+        L.check(self.lib.rstq_ipc_close(self.handle, dev, C.c_void_p(device_ptr)))
+
     # -- weights ---------------------------------------------------------
     def bind_weight(self, codes, scales, out, in_, fmt, layout, dev=0, split=L.SPLIT_NONE,
                     rank=0, nranks=1) -> QWeight:
