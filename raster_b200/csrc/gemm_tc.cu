@@ -608,7 +608,6 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     const int ksteps = p.ksteps;
     unsigned long long* dbg = (p.dbg && blockIdx.x == 0) ? p.dbg : nullptr;
     if (dbg && tid == 64) dbg[301] = (unsigned long long)clock64();
-    unsigned long long* fine = dbg;
 
     if (warp == 0) {
         // ---------------- TMA producer of the activation tiles ----------------
@@ -618,9 +617,8 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             uint32_t ph = 0;
             bool ok = true;
             for (int ks = 0; ks < ksteps; ++ks) {
-                ok = mbar_spin(empty + 8 * s, ph ^ 1u, abort_flag);
+                ok = mbar_block(empty + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
-                if (fine && ks < 40) dbg[ks * 8 + 0] = (unsigned long long)clock64();  // TMA: slot free, issuing
                 const uint32_t dst = sbase + s * BSTAGE;
                 mbar_expect_tx(full + 8 * s, BSTAGE);
                 tma_load_2d(dst, &tmap, ks * kKStep, tok0, full + 8 * s);
@@ -760,18 +758,14 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             for (int j = 0; j < kPrefetch; ++j) {
                 const int ks = ks0 + j;
                 if (ks < ksteps && ok) {
-                    ok = mbar_wait_warp(empty + 8 * s, ph ^ 1u, abort_flag);
+                    ok = __all_sync(0xffffffffu, mbar_block(empty + 8 * s, ph ^ 1u, abort_flag));
                     if (ok) {
-                        if (fine && lane == 0 && ks == 10) dbg[336 + dq] = (unsigned long long)clock64();  // A slot seen free, per warp
                         tc_fence_after();
                         convert_store(raw[j], tmem + A_COL0 + s * kAColsPerStage);
-                        if (fine && warp == 2 && lane == 0 && ks < 40) dbg[ks * 8 + 4] = (unsigned long long)clock64();  // converted
                         tmem_st_wait();
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(full + 8 * s);
-                        if (fine && warp == 2 && lane == 0 && ks < 40) dbg[ks * 8 + 5] = (unsigned long long)clock64();  // signalled
-                        if (fine && lane == 0 && ks == 10) dbg[320 + dq] = (unsigned long long)clock64();  // signalled, per warp
                         load(raw[j]);
                         if (++s == kNSTT) { s = 0; ph ^= 1u; }
                     }
@@ -781,7 +775,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
 
         // ---------------- epilogue: tensor memory -> y ----------------
         if (ok) {
-            const bool got = mbar_spin(acc_full, 0, abort_flag);
+            const bool got = mbar_block(acc_full, 0, abort_flag);
             ok = __all_sync(0xffffffffu, got);
         }
         if (dbg && tid == 64) dbg[302] = (unsigned long long)clock64();

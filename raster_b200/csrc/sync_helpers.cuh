@@ -68,6 +68,16 @@ __device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, volatil
         if (mbar_test(bar, parity)) return true;
     return mbar_wait(bar, parity, abort_flag);
 }
+// Wait of a warp that is not on the critical path: mbarrier.try_wait suspends the thread in
+// hardware until the phase completes or a system time limit passes, so a waiting warp issues a
+// handful of instructions per microsecond instead of a polling loop that competes for issue
+// slots with the warps doing the work.
+__device__ __forceinline__ bool mbar_block(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)  // each try may suspend for a while: no timer reads on this path
+        if (mbar_try(bar, parity)) return true;
+    return mbar_wait(bar, parity, abort_flag);
+}
 // Warp-wide wait that polls from lane 0 only, sleeping between polls: a producer warp that is
 // a long way ahead of its consumer then leaves the barrier unit and the issue slots to the
 // warps that are on the critical path.  All 32 lanes must call it; all get the same answer.
