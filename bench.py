@@ -674,6 +674,7 @@ def run_case(args):
     bits, out, in_, M = int(bits), int(out), int(in_), int(M)
     rng = np.random.default_rng(0)
     ctx = Context(("cuda:0",))
+    ctx.tune(L.TUNE_GEMV_PLAN, args.plan)
     nb = in_ // 32
     codes = rng.integers(0, 256, out * in_ * bits // 8, dtype=np.uint8)
     scales = (rng.standard_normal(out * nb) * 0.01).astype(np.float32)
@@ -716,6 +717,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, help="small single-kernel case for profiler captures")
+    ap.add_argument("--plan", type=int, default=0, help="with --case: decode work split (rstq_tune key 4)")
     args = ap.parse_args()
     if args.case:
         return run_case(args)

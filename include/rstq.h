@@ -89,6 +89,9 @@ typedef struct rstq_event rstq_event;
 #define RSTQ_TUNE_PDL 2           /* 1 (default) = launch the decode kernels with programmatic
                                      dependent launch so consecutive launches overlap; 0 = plain */
 #define RSTQ_TUNE_TIMELINE 3      /* 1 = streaming kernel records per-CTA phase timestamps */
+#define RSTQ_TUNE_GEMV_PLAN 4     /* decode kernel work split: 0 (default) = choose per shape, 1 = equal
+                                     unit ranges (32-row groups may be shared by neighbouring thread
+                                     blocks), 2 = whole 32-row groups per thread block */
 
 /* ---- library / errors -------------------------------------------------- */
 RSTQ_API int32_t rstq_version(void);

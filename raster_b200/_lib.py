@@ -80,7 +80,7 @@ LAYOUT_ROWMAJOR, LAYOUT_STREAM8 = 0, 1
 F32, BF16 = 0, 1
 MODE_F, MODE_A8 = 0, 1
 SPLIT_NONE, SPLIT_COLUMN, SPLIT_ROW = 0, 1, 2
-TUNE_GEMM_KERNEL, TUNE_GEMM_MIN_M, TUNE_PDL, TUNE_TIMELINE = 0, 1, 2, 3
+TUNE_GEMM_KERNEL, TUNE_GEMM_MIN_M, TUNE_PDL, TUNE_TIMELINE, TUNE_GEMV_PLAN = 0, 1, 2, 3, 4
 
 
 class RstqError(RuntimeError):

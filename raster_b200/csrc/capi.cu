@@ -434,6 +434,10 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
         case RSTQ_TUNE_TIMELINE:
             for (auto& ds : ctx->devs) ds.dbg = value ? ds.dbg_store : nullptr;
             return RSTQ_OK;
+        case RSTQ_TUNE_GEMV_PLAN:
+            RSTQ_REQUIRE(value >= 0 && value <= 2, RSTQ_E_INVALID, "decode plan selector 0..2");
+            for (auto& ds : ctx->devs) ds.gemv_plan = (int)value;
+            return RSTQ_OK;
         case RSTQ_TUNE_GEMM_MIN_M:
             RSTQ_REQUIRE(value >= 1, RSTQ_E_INVALID, "threshold must be >= 1");
             ctx->tune_gemm_min_m = value;

@@ -66,6 +66,7 @@ struct DeviceState {
     cudaStream_t own_stream = nullptr;
     bool capturing = false;
     bool pdl = true;               // launch the hot kernels with programmatic stream serialization
+    int gemv_plan = 0;             // decode work split: 0 = per shape, 1 = equal unit ranges, 2 = whole groups
     // scratch owned by the context
     void* act_scratch = nullptr;   // quantized / converted activations
     int64_t act_scratch_bytes = 0;

@@ -283,19 +283,26 @@ def test_zero_inputs_give_exact_zeros(ctx, bits):
 
 
 def test_partial_groups_and_reproducibility(ctx):
-    """Shapes whose rows-per-CTA split leaves groups shared between CTAs; run-to-run identical."""
-    for out, in_, M in ((4096, 11008, 1), (11008, 4096, 1), (300, 22016, 2), (8192, 1024, 3)):
-        _, wq, ws = make_weight(out, in_, 4, seed=21 + out)
-        x = synth.normal(22 + in_, M * in_)
-        w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
-        xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
-        ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out)
-        y1 = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
-        y2 = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
-        assert relerr(y1, ref) <= TOL_A8
-        assert np.array_equal(y1, y2)
-        ctx.sync()                                   # no bounded wait ran out
-        w.free()
+    """Both work splits of the decode kernel: whole 32-row groups per thread block (the default) and
+    equal unit ranges, where neighbouring blocks share a group and hand partial sums over;
+    run-to-run identical either way."""
+    try:
+        for plan in (2, 1, 0):
+            ctx.tune(L.TUNE_GEMV_PLAN, plan)
+            for out, in_, M in ((4096, 11008, 1), (11008, 4096, 1), (300, 22016, 2), (8192, 1024, 3), (40, 32768, 1)):
+                _, wq, ws = make_weight(out, in_, 4, seed=21 + out)
+                x = synth.normal(22 + in_, M * in_)
+                w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+                xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+                ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out)
+                y1 = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
+                y2 = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
+                assert relerr(y1, ref) <= TOL_A8, (plan, out, in_, M)
+                assert np.array_equal(y1, y2)
+                ctx.sync()                                   # no bounded wait ran out
+                w.free()
+    finally:
+        ctx.tune(L.TUNE_GEMV_PLAN, 0)
 
 
 def test_full_size_linearity_and_split_properties(ctx):
