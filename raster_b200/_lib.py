@@ -8,7 +8,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "librstq.so")
+LIB_PATH = os.environ.get("RSTQ_LIB") or os.path.join(_HERE, "lib", "librstq.so")
 
 i32, i64, vp = C.c_int32, C.c_int64, C.c_void_p
 pp = C.POINTER(vp)

@@ -142,12 +142,29 @@ act_to_f16_kernel(const void* __restrict__ x, const float* __restrict__ xs, __ha
             for (int j = 0; j < 8; ++j) v[j] = (float)(int8_t)(w[j >> 2] >> (8 * (j & 3))) * sc;
         }
     };
+    // Rows of up to 8192 elements stay in registers between the two passes (max, convert);
+    // longer rows are read twice.
+    constexpr int kKeep = 4;  // x 256 threads x 8 elements
+    const bool keep = in <= (int64_t)kKeep * 256 * 8;
+    float held[kKeep][8];
     float mx = 0.f;
-    for (int64_t k = threadIdx.x * 8; k < in; k += 256 * 8) {
-        float v[8];
-        load8(k, v);
+    if (keep) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(v[j]));
+        for (int i = 0; i < kKeep; ++i) {
+            const int64_t k = (int64_t)(i * 256 + threadIdx.x) * 8;
+            if (k < in) {
+                load8(k, held[i]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(held[i][j]));
+            }
+        }
+    } else {
+        for (int64_t k = threadIdx.x * 8; k < in; k += 256 * 8) {
+            float v[8];
+            load8(k, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(v[j]));
+        }
     }
     __shared__ float s_mx[8];
 #pragma unroll
@@ -164,9 +181,7 @@ act_to_f16_kernel(const void* __restrict__ x, const float* __restrict__ xs, __ha
         e = ex - 14;
     }
     const float down = ldexpf(1.0f, -e);
-    for (int64_t k = threadIdx.x * 8; k < in; k += 256 * 8) {
-        float v[8];
-        load8(k, v);
+    auto store8 = [&](int64_t k, const float (&v)[8]) {
         uint32_t h[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -174,6 +189,19 @@ act_to_f16_kernel(const void* __restrict__ x, const float* __restrict__ xs, __ha
             h[j] = *reinterpret_cast<const uint32_t*>(&t);
         }
         *reinterpret_cast<uint4*>(x16 + m * in + k) = make_uint4(h[0], h[1], h[2], h[3]);
+    };
+    if (keep) {
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const int64_t k = (int64_t)(i * 256 + threadIdx.x) * 8;
+            if (k < in) store8(k, held[i]);
+        }
+    } else {
+        for (int64_t k = threadIdx.x * 8; k < in; k += 256 * 8) {
+            float v[8];
+            load8(k, v);
+            store8(k, v);
+        }
     }
     if (threadIdx.x == 0) rowscale[m] = ldexpf(1.0f, e);
 }
@@ -786,19 +814,30 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             const int cq = dq >> 2;           // column quarter
             const int64_t f = (int64_t)ft * 128 + sp * 32 + lane;
             constexpr int CPW = NTOK / 4;     // columns per warp
+            // all loads of this warp's columns first, one wait, then the stores with the output
+            // type decided once (a lane owns one feature: consecutive lanes write consecutive
+            // elements of a token's row)
+            uint32_t v[CPW];
+            const uint32_t t0 = tmem + ((uint32_t)(sp * 32) << 16) + (uint32_t)(cq * CPW);
 #pragma unroll
-            for (int c0 = 0; c0 < CPW; c0 += 8) {
-                uint32_t v[8];
-                const int col = cq * CPW + c0;
-                tmem_ld8(tmem + ((uint32_t)(sp * 32) << 16) + (uint32_t)col, v);
-                tmem_ld_wait();
+            for (int c0 = 0; c0 < CPW; c0 += 8) tmem_ld8(t0 + c0, *reinterpret_cast<uint32_t(*)[8]>(&v[c0]));
+            tmem_ld_wait();
+            const float wdiv = p.wdiv;
+            const int tokb = tok0 + cq * CPW;
+            if (f < p.out) {
+                if (p.out_dtype == RSTQ_BF16) {
+                    __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) + f;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int tok = tok0 + col + j;
-                    if (tok < p.M && f < p.out) {
-                        const float val = __uint_as_float(v[j]) * p.wdiv * __ldg(p.rowscale + tok);
-                        store_out(p.y, p.out_dtype, (int64_t)tok * p.out + f, val);
-                    }
+                    for (int j = 0; j < CPW; ++j)
+                        if (tokb + j < p.M)
+                            y[(int64_t)(tokb + j) * p.out] =
+                                __float2bfloat16_rn(__uint_as_float(v[j]) * wdiv * __ldg(p.rowscale + tokb + j));
+                } else {
+                    float* y = reinterpret_cast<float*>(p.y) + f;
+#pragma unroll
+                    for (int j = 0; j < CPW; ++j)
+                        if (tokb + j < p.M)
+                            y[(int64_t)(tokb + j) * p.out] = __uint_as_float(v[j]) * wdiv * __ldg(p.rowscale + tokb + j);
                 }
             }
         }
