@@ -528,6 +528,12 @@ def run_ours(args):
         detail["M1_a8_f32_warm_L2_GBs"] = round(per_pass * R / (msw * 1e-3) / 1e9, 1)
         g.destroy()
 
+        # ---- prefill point (configs[2]): int8 weights, M = 512, K = N = 4096, bf16 in / out ----
+        try:
+            detail.update(gemm_detail(ctx, info))
+        except Exception as e:  # a detail point must not take the headline down
+            detail["gemm_error"] = repr(e)[:200]
+
         # ---- e2e: host arrays through the operator entry point ----------------
         host_copies = []
         for w in weights:
@@ -578,6 +584,45 @@ def run_ours(args):
     ctx.close()
     if rank == 0:
         print(json.dumps(result))
+
+
+def gemm_detail(ctx, info, M=512, K=4096, N=4096):
+    """Tensor-core GEMM of the prefill config on rotated weight copies (> L2 in total): TFLOP/s of
+    the whole call (activation pre-pass + GEMM), against the measured cuBLAS bf16 peak."""
+    from raster_b200 import _lib as L
+    from raster_b200 import synth
+    from raster_b200.quant import cpu_quant as cq
+    w = synth.normal(77, N * K, SIGMA_W)
+    q = cq.quantize_weight(w, cq.q8_0)
+    first = ctx.bind_weight(q["wq"], q["ws"], N, K, L.FMT_Q8_0, L.LAYOUT_ROWMAJOR)
+    R = max(2, -(-int(1.2 * info["l2_bytes"]) // first.stream_bytes))
+    ws = [first] + [first.clone() for _ in range(R - 1)]
+    x = ctx.array_to_buffer(synth.to_bf16_bits(synth.normal(78, M * K)))
+    y = ctx.make_buffer(M * N, np.uint16)
+    for wq in ws:
+        ctx.qmatmul(wq, x, y, M, L.BF16, L.BF16, L.MODE_F)
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    e0.record()
+    for _ in range(3):
+        for wq in ws:
+            ctx.qmatmul(wq, x, y, M, L.BF16, L.BF16, L.MODE_F)
+    e1.record()
+    ctx.sync()
+    us = e0.elapsed_ms(e1) * 1e3 / (3 * R)
+    e0.destroy(), e1.destroy()
+    for o in ws + [x, y]:
+        o.free()
+    tf = 2.0 * M * N * K / us / 1e6
+    peak = None
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    out = {"gemm_int8_M512_K4096_N4096_bf16_us": round(us, 2), "gemm_int8_M512_K4096_N4096_bf16_TFLOPs": round(tf, 1)}
+    if peak:
+        out["gemm_frac_of_measured_bf16_peak"] = round(tf / peak, 4)
+    return out
 
 
 def cpu_baseline(weights, reps=60, warm=25, threads=None):
