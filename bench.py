@@ -162,6 +162,118 @@ def time_graph(ctx, graph, steps, warmup):
     return ms
 
 
+def tp_group(ctx, dist, world, rank, payload_bytes):
+    """The peer-memory group of this box: every rank allocates a zeroed region, exports it as a CUDA
+    IPC handle, maps the other ranks' regions and attaches its endpoint."""
+    import torch
+    region_bytes = ctx.tp_region_bytes(world, payload_bytes)
+    region = ctx.make_buffer(region_bytes, np.uint8)
+    region.fill_bytes(0)
+    ctx.sync()
+    mine = torch.tensor(list(ctx.ipc_export(region)), dtype=torch.uint8, device="cuda")
+    allh = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    ptrs = [region.device_ptr if r == rank else ctx.ipc_open(bytes(allh[r].cpu().tolist()))
+            for r in range(world)]
+    tp = ctx.tp_attach(rank, world, ptrs, region_bytes)
+    dist.barrier()
+    return tp, region, ptrs
+
+
+def run_layer(args):
+    """--case layer:<bits>: the seven projections of a Llama-7B-style decoder layer at M = 1 (q, k, v,
+    o 4096x4096; gate, up 11008x4096; down 4096x11008), tensor-parallel over the ranks of the launch:
+    q, k, v, gate, up split by columns, o and down by rows (strong scaling: the layer is fixed).
+    Prints one JSON line with microseconds per layer and weight-stream GB/s."""
+    from raster_b200 import Context
+    from raster_b200 import _lib as L
+    from raster_b200 import synth
+    bits = int(args.case.split(":")[1]) if ":" in args.case else 4
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = Context((f"cuda:{local_rank}",))
+    fmt = L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0
+    H, F = 4096, 11008
+    projs = [("q", H, H, "column"), ("k", H, H, "column"), ("v", H, H, "column"), ("o", H, H, "row"),
+             ("gate", F, H, "column"), ("up", F, H, "column"), ("down", H, F, "row")]
+    rng = np.random.default_rng(1)
+    L2 = ctx.device_info()["l2_bytes"]
+    per_layer = sum(stream_bytes(o, i, bits) for _, o, i, _ in projs)
+    layers = max(2, -(-4 * L2 // (per_layer // world)))      # distinct layers so weights come from HBM
+    tp = None
+    if world > 1:
+        tp, region, ptrs = tp_group(ctx, dist, world, rank, 4 * F)
+    stack = []
+    for _ in range(layers):
+        lay = []
+        for name, out, in_, split in projs:
+            so, si = (out // world, in_) if split == "column" else (out, in_ // world)
+            codes = rng.integers(0, 256, so * si * bits // 8, dtype=np.uint8)
+            scales = (rng.standard_normal(so * (si // 32)) * 0.01).astype(np.float32)
+            lay.append((ctx.bind_weight(codes, scales, so, si, fmt, L.LAYOUT_ROWMAJOR), split, out, si))
+        stack.append(lay)
+    xs = {si: ctx.array_to_buffer(synth.normal(5, si)) for si in {p[3] for p in stack[0]}}
+    ys = {out: ctx.make_buffer(out, np.float32) for out in {p[2] for p in stack[0]}}
+
+    def one_pass(_):
+        for lay in stack:
+            for w, split, out, si in lay:
+                if tp is None:
+                    ctx.qmatmul(w, xs[si], ys[out], 1)
+                else:
+                    tp.qmatmul(w, xs[si], ys[out], 1, L.F32, L.MODE_A8,
+                               L.SPLIT_COLUMN if split == "column" else L.SPLIT_ROW)
+    one_pass(False)
+    ctx.sync()
+    if dist is not None:
+        dist.barrier()
+    ctx.graph_begin()
+    one_pass(True)
+    g = ctx.graph_end()
+    for _ in range(3):
+        g.replay()
+    ctx.sync()
+    if dist is not None:
+        dist.barrier()
+    e0, e1 = ctx.event(), ctx.event()
+    n = max(3, args.steps)
+    e0.record()
+    for _ in range(n):
+        g.replay()
+    e1.record()
+    ctx.sync()
+    ms = e0.elapsed_ms(e1) / n
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    if rank == 0:
+        us_layer = ms * 1e3 / layers
+        print(json.dumps({"case": args.case, "n_gpus": world, "layers_per_step": layers,
+                          "us_per_layer": round(us_layer, 2),
+                          "GBs_total": round(per_layer / us_layer / 1e3, 1),
+                          "GBs_per_gpu": round(per_layer / world / us_layer / 1e3, 1),
+                          "weight_bytes_per_layer": per_layer, "scaling": "strong"}))
+    g.destroy()
+    if tp is not None:
+        tp.free()
+        for r in range(world):
+            if r != rank:
+                ctx.ipc_close(ptrs[r])
+        dist.barrier()
+        dist.destroy_process_group()
+    ctx.close()
+
+
 def run_tp(args, world, rank, local_rank):
     """N > 1: the sharded operator, one rank per GPU, exchanges inside the timed region."""
     import torch
@@ -183,19 +295,7 @@ def run_tp(args, world, rank, local_rank):
         first = ctx.bind_weight(w["wqi"], w["wsi"], w["out"], w["in"], L.FMT_Q4_0, L.LAYOUT_STREAM8)
         bound.append([first] + [first.clone() for _ in range(R - 1)])
 
-    # ---- the peer-memory group: every rank maps every other rank's region ----
-    payload = 4 * max(up["out"], down["out"])
-    region_bytes = ctx.tp_region_bytes(world, payload)
-    region = ctx.make_buffer(region_bytes, np.uint8)
-    region.fill_bytes(0)
-    ctx.sync()
-    mine = torch.tensor(list(ctx.ipc_export(region)), dtype=torch.uint8, device="cuda")
-    allh = [torch.empty_like(mine) for _ in range(world)]
-    dist.all_gather(allh, mine)
-    ptrs = [region.device_ptr if r == rank else ctx.ipc_open(bytes(allh[r].cpu().tolist()))
-            for r in range(world)]
-    tp = ctx.tp_attach(rank, world, ptrs, region_bytes)
-    dist.barrier()
+    tp, region, ptrs = tp_group(ctx, dist, world, rank, 4 * max(up["out"], down["out"]))
 
     x_up = ctx.array_to_buffer(up["x"][: up["in"]])                 # replicated activation
     y_up = ctx.make_buffer(world * up["out"], np.float32)           # gathered columns
@@ -392,6 +492,7 @@ def run_tp(args, world, rank, local_rank):
     for r in range(world):
         if r != rank:
             ctx.ipc_close(ptrs[r])
+    region.free()
     dist.barrier()
     dist.destroy_process_group()
     ctx.close()
@@ -764,6 +865,8 @@ def main():
     ap.add_argument("--case", default=None, help="small single-kernel case for profiler captures")
     ap.add_argument("--plan", type=int, default=0, help="with --case: decode work split (rstq_tune key 4)")
     args = ap.parse_args()
+    if args.case and args.case.startswith("layer"):
+        return run_layer(args)
     if args.case:
         return run_case(args)
     args.warmup = max(args.warmup, 3)

@@ -234,6 +234,22 @@ RSTQ_API int32_t rstq_event_destroy(rstq_event* ev);
 /* Number of kernels this library has launched on the context since init. */
 RSTQ_API int32_t rstq_launch_count(rstq_ctx* ctx, int64_t* count);
 
+/* ---- decode-chain neighbours of the matmul (f32, device buffers), so a decoder layer's chain
+ *      rms-norm -> quantize -> matmul -> SwiGLU / GeGLU -> residual stays on the device and in one
+ *      graph.  rms-norm!  src/raster/dl/nn.clj:497-513 (per row: x / sqrt(mean x^2 + eps) *
+ *      (gain_offset + weight)); silu-mul! :200-203; gelu-mul! :208-214 (tanh form); residual-add!
+ *      :217-219.  rstq_rms_norm_quant_act = rms-norm! followed by quantize-act-i8 in one kernel:
+ *      the codes, scales and block sums are bit-identical to rstq_quant_act_i8 run on
+ *      rstq_rms_norm's output (features % 32 == 0; xsum may be NULL). ----------------------- */
+RSTQ_API int32_t rstq_rms_norm(rstq_ctx* ctx, rstq_buf* x, rstq_buf* weight, rstq_buf* out,
+                               int64_t rows, int64_t features, double eps, double gain_offset);
+RSTQ_API int32_t rstq_rms_norm_quant_act(rstq_ctx* ctx, rstq_buf* x, rstq_buf* weight, rstq_buf* xq,
+                                         rstq_buf* xs, rstq_buf* xsum, int64_t rows,
+                                         int64_t features, double eps, double gain_offset);
+RSTQ_API int32_t rstq_silu_mul(rstq_ctx* ctx, rstq_buf* gate, rstq_buf* up, rstq_buf* out, int64_t n);
+RSTQ_API int32_t rstq_gelu_mul(rstq_ctx* ctx, rstq_buf* gate, rstq_buf* up, rstq_buf* out, int64_t n);
+RSTQ_API int32_t rstq_residual_add(rstq_ctx* ctx, rstq_buf* a, rstq_buf* b, rstq_buf* out, int64_t n);
+
 /* ---- tensor-parallel exchange of the sharded operator.  No counterpart in the reference: it
  *      extends the placement / plan vocabulary (src/raster/compiler/passes/placement.clj:21-89)
  *      with a weight split over the GPUs of one box.  One endpoint per rank.  Every rank owns a

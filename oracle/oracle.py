@@ -260,6 +260,33 @@ def matmul_a8_f64(codes, scales, fmt, xq, xs, xsum, m, in_, out):
 
 # ---- vectorised + threaded CPU kernel (timed CPU baseline) -------------------
 
+def rms_norm(x, weight, rows: int, features: int, eps: float = 1e-6, gain_offset: float = 0.0):
+    x, weight = _f32(x), _f32(weight)
+    out = np.empty(rows * features, np.float32)
+    lib().orc_rms_norm(_ptr(x), _ptr(weight), _ptr(out), C.c_int64(rows), C.c_int64(features), C.c_double(eps),
+                       C.c_double(gain_offset))
+    return out
+
+
+def _map2(name, a, b):
+    a, b = _f32(a), _f32(b)
+    out = np.empty(a.size, np.float32)
+    getattr(lib(), name)(_ptr(a), _ptr(b), _ptr(out), C.c_int64(a.size))
+    return out
+
+
+def silu_mul(gate, up):
+    return _map2("orc_silu_mul", gate, up)
+
+
+def gelu_mul(gate, up):
+    return _map2("orc_gelu_mul", gate, up)
+
+
+def residual_add(a, b):
+    return _map2("orc_residual_add", a, b)
+
+
 def cpk() -> C.CDLL:
     global _cpk
     if _cpk is None:

@@ -544,3 +544,45 @@ ORC_API void orc_matmul_a8_f64(const uint8_t* codes, const float* scales, int fm
             y[mi * out + o] = acc;
         }
 }
+
+/* ---- decode-chain neighbours of the matmul (src/raster/dl/nn.clj) ------------------------------
+ * The reference writes these as generic par/map-void! bodies whose literals (0.0, 1.0, 0.5, ...) are
+ * doubles, so the element arithmetic is carried in double and stored as float.  Parity for these is
+ * unpinned against reference outputs (its tests compare variants of the same op with one another,
+ * test/raster/dl/nn_test.clj:659-680, and report ~5e-7 between its own CPU and GPU lowerings). */
+
+/* rms-norm!  nn.clj:497-513: ms = (sum x^2) / features (double accumulator), inv = 1 / sqrt(ms + eps),
+ * out = x * inv * (gain_offset + weight). */
+ORC_API void orc_rms_norm(const float* x, const float* weight, float* out, int64_t rows, int64_t features,
+                          double eps, double gain_offset) {
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* xr = x + r * features;
+        double s = 0.0;
+        for (int64_t i = 0; i < features; ++i) s += (double)xr[i] * (double)xr[i];
+        const double ms = s / (double)features;
+        const double inv = 1.0 / sqrt(ms + eps);
+        for (int64_t i = 0; i < features; ++i)
+            out[r * features + i] = (float)((double)xr[i] * inv * (gain_offset + (double)weight[i]));
+    }
+}
+
+/* silu-mul!  nn.clj:200-203: out = g * (1 / (1 + exp(-g))) * up */
+ORC_API void orc_silu_mul(const float* gate, const float* up, float* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) {
+        const double g = gate[i];
+        out[i] = (float)(g * (1.0 / (1.0 + exp(-g))) * (double)up[i]);
+    }
+}
+
+/* gelu-mul!  nn.clj:208-214: out = 0.5 g (1 + tanh(0.7978845608028654 (g + 0.044715 g g g))) * up */
+ORC_API void orc_gelu_mul(const float* gate, const float* up, float* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) {
+        const double g = gate[i];
+        out[i] = (float)(0.5 * g * (1.0 + tanh(0.7978845608028654 * (g + 0.044715 * g * g * g))) * (double)up[i]);
+    }
+}
+
+/* residual-add!  nn.clj:217-219: out = a + b (float + float) */
+ORC_API void orc_residual_add(const float* a, const float* b, float* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = a[i] + b[i];
+}

@@ -57,6 +57,11 @@ SIGNATURES = {
     "rstq_event_elapsed_ms": [vp, vp, C.POINTER(C.c_float)],
     "rstq_event_destroy": [vp],
     "rstq_launch_count": [vp, C.POINTER(i64)],
+    "rstq_rms_norm": [vp, vp, vp, vp, i64, i64, C.c_double, C.c_double],
+    "rstq_rms_norm_quant_act": [vp, vp, vp, vp, vp, vp, i64, i64, C.c_double, C.c_double],
+    "rstq_silu_mul": [vp, vp, vp, vp, i64],
+    "rstq_gelu_mul": [vp, vp, vp, vp, i64],
+    "rstq_residual_add": [vp, vp, vp, vp, i64],
     "rstq_tp_region_bytes": [i32, i64],
     "rstq_tp_attach": [vp, i32, i32, i32, pp, i64, pp],
     "rstq_tp_create_local": [vp, i32, C.POINTER(i32), i64, pp],

@@ -254,6 +254,25 @@ class Context:
                                            act_dtype, mode))
         return y.reshape(M, w.out)
 
+    # -- decode-chain neighbours (raster.dl.nn) -----------------------------------
+    def rms_norm(self, x, weight, out, rows, features, eps=1e-6, gain_offset=0.0) -> None:
+        L.check(self.lib.rstq_rms_norm(self.handle, x.handle, weight.handle, out.handle, rows, features,
+                                       eps, gain_offset))
+
+    def rms_norm_quant_act(self, x, weight, xq, xs, xsum, rows, features, eps=1e-6, gain_offset=0.0) -> None:
+        L.check(self.lib.rstq_rms_norm_quant_act(self.handle, x.handle, weight.handle, xq.handle, xs.handle,
+                                                 xsum.handle if xsum is not None else None, rows, features,
+                                                 eps, gain_offset))
+
+    def silu_mul(self, gate, up, out, n) -> None:
+        L.check(self.lib.rstq_silu_mul(self.handle, gate.handle, up.handle, out.handle, n))
+
+    def gelu_mul(self, gate, up, out, n) -> None:
+        L.check(self.lib.rstq_gelu_mul(self.handle, gate.handle, up.handle, out.handle, n))
+
+    def residual_add(self, a, b, out, n) -> None:
+        L.check(self.lib.rstq_residual_add(self.handle, a.handle, b.handle, out.handle, n))
+
     # -- graphs / events / misc ------------------------------------------------
     def graph_begin(self, dev=0) -> None:
         L.check(self.lib.rstq_graph_begin(self.handle, dev))

@@ -209,3 +209,33 @@ def test_a_rank_that_never_arrives_is_reported_not_waited_for_forever():
     for t in tps:
         t.free()
     ctx.close()
+
+
+def test_decoder_layer_projections_sharded(group):
+    """The seven projections of a Llama-7B-style decoder layer at M = 1, int4: q, k, v, gate, up split
+    by columns (outputs gathered), o and down split by rows (partial products summed), each against
+    the unsharded oracle on the same seeded weights."""
+    ctx, tps, P = group
+    shapes = [("q", 4096, 4096, "column"), ("o", 4096, 4096, "row"), ("gate", 11008, 4096, "column"),
+              ("down", 4096, 11008, "row")]          # k, v = q's shape; up = gate's
+    for name, out, in_, split in shapes:
+        w = synth.normal(100 + out % 97 + in_ % 89 + len(name), out * in_, 0.02)
+        wq, ws = orc.quantize_weight(w, 4)
+        x = synth.normal(3 + out, in_)
+        plan = shard.ShardPlan(split, P)
+        shard.check(plan, out, in_)
+        sh = [ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR, dev=r, split=plan.split_code, rank=r,
+                              nranks=P) for r in range(P)]
+        bx = [ctx.array_to_buffer(shard.slice_activations(plan, r, x, 1, in_), dev=r) for r in range(P)]
+        by = [ctx.make_buffer(out, np.float32, dev=r) for r in range(P)]
+        for r in range(P):
+            tps[r].qmatmul(sh[r], bx[r], by[r], 1, L.F32, L.MODE_A8, plan.split_code)
+        _sync_all(ctx, P)
+        xq, xs, xsum = orc.quantize_act_i8(x, 1, in_)
+        ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, 1, in_, out)
+        got = [b.download() for b in by]
+        for r in range(P):
+            assert relerr(got[r], ref) <= 2e-6, (name, r)
+            assert np.array_equal(got[r].view(np.uint32), got[0].view(np.uint32)), (name, r)
+        for o in sh + bx + by:
+            o.free()
