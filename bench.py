@@ -613,6 +613,7 @@ def run_ours(args):
         xb16 = [ctx.array_to_buffer(synth.to_bf16_bits(w["x"])) for w in weights]
         for M in (1, 4, 8):
             for tag, act, mode, xb in (("a8_f32", L.F32, L.MODE_A8, None),
+                                       ("a8_bf16", L.BF16, L.MODE_A8, xb16),
                                        ("f_f32", L.F32, L.MODE_F, None),
                                        ("f_bf16", L.BF16, L.MODE_F, xb16)):
                 g = capture(op_pass(M, act, mode, xb))

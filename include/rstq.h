@@ -162,8 +162,9 @@ RSTQ_API int32_t rstq_quant_act_i8(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rst
 
 /* ---- the matmul on device-resident data.
  * rstq_qmatmul: y[M, out] = W . x[M, in]; x is act_dtype, y is out_dtype.
- *   MODE_A8 quantizes x inside the call (needs act_dtype F32) -- the arithmetic of
- *   qlinear-i8! / qlinear-i8-q8! (src/raster/quant/op.clj:43-51, :81-90) for any M.
+ *   MODE_A8 quantizes x inside the call -- the arithmetic of qlinear-i8! / qlinear-i8-q8!
+ *   (src/raster/quant/op.clj:43-51, :81-90) for any M; bf16 activations are widened exactly
+ *   first, so they give the result of the same values passed as f32.
  *   MODE_F multiplies the float activations directly -- qlinear-q8
  *   (src/raster/quant/train.clj:77-108) and the prefill GEMM.
  * rstq_qmatmul_prequant: the kernel-level call of the reference,

@@ -18,8 +18,11 @@ __device__ __forceinline__ int round_half_up(double v) {
 
 // One warp per block; lane k owns element k.  Bytes are gathered so that each
 // of eight lanes stores one 32-bit word.
+// BF16IN: x holds bf16 bit patterns (uint16_t); they are widened exactly, so the codes are those
+// the f32 quantizer gives for the widened values.
+template <bool BF16IN>
 __global__ void __launch_bounds__(256)
-quant_act_i8_kernel(const float* __restrict__ x, int8_t* __restrict__ xq, float* __restrict__ xs,
+quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float* __restrict__ xs,
                     int32_t* __restrict__ xsum, int64_t nblocks) {
     // programmatic dependent launch: let the consumer kernel start its weight stream now;
     // x may come from the kernel before this one, so wait for it
@@ -29,7 +32,8 @@ quant_act_i8_kernel(const float* __restrict__ x, int8_t* __restrict__ xq, float*
     const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t blk = warp; blk < nblocks; blk += nwarps) {
-        const float v = x[blk * 32 + lane];
+        const float v = BF16IN ? __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(xv)[blk * 32 + lane] << 16)
+                               : reinterpret_cast<const float*>(xv)[blk * 32 + lane];
         float mx = fabsf(v);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -53,8 +57,8 @@ quant_act_i8_kernel(const float* __restrict__ x, int8_t* __restrict__ xq, float*
     }
 }
 
-int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs,
-                            int32_t* xsum, int64_t M, int64_t in) {
+int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
+                            int32_t* xsum, int64_t M, int64_t in, int act_dtype) {
     const int64_t nblocks = M * (in / 32);
     int64_t ctas = (nblocks + 7) / 8;  // 8 warps per CTA
     const int64_t cap = (int64_t)ds.sm_count * 8;
@@ -69,7 +73,10 @@ int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const float* x, int8
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ds.pdl ? 1 : 0;
-    RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel, x, xq, xs, xsum, nblocks));
+    if (act_dtype == RSTQ_BF16)
+        RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel<true>, x, xq, xs, xsum, nblocks));
+    else
+        RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel<false>, x, xq, xs, xsum, nblocks));
     ctx->launches++;
     RSTQ_CUDA(cudaGetLastError());
     return RSTQ_OK;

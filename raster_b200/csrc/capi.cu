@@ -155,12 +155,12 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
                                                 : ctx->tune_gemm_min_m);
     if (tp && (tc || out_dtype != RSTQ_F32)) return kNotFused;  // only the decode kernel fuses the exchange
     if (mode == RSTQ_MODE_A8) {
-        RSTQ_REQUIRE(act_dtype == RSTQ_F32, RSTQ_E_INVALID, "MODE_A8 takes f32 activations");
+        RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "unknown activation type");
         RSTQ_REQUIRE(out_dtype == RSTQ_F32 || tc, RSTQ_E_INVALID, "MODE_A8 decode writes f32");
         ActScratch s;
         int32_t rc = act_scratch(ds, M, w->in, &s);
         if (rc != RSTQ_OK) return rc;
-        rc = launch_quant_act_i8(ctx, ds, (const float*)x, s.xq, s.xs, s.xsum, M, w->in);
+        rc = launch_quant_act_i8(ctx, ds, x, s.xq, s.xs, s.xsum, M, w->in, act_dtype);
         if (rc != RSTQ_OK) return rc;
         if (!tc) return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M, tp);
         void* x16;

@@ -89,7 +89,7 @@ __device__ __forceinline__ void imma_acc(int (&d)[4], const uint32_t (&a)[4], ui
           "r"(c3));
 }
 
-// ---- activation staging (once per CTA, all of K; loops free of divisions) -----------------
+// ---- activation staging (once per CTA, all of K) ---------------------------------------------
 // A8, M == 1: srec [nb][4 tig] uint4 {xq word tig, xq word 4+tig, xs_t bits, c_t}: lane tig
 //            folds row gid + 8*tig only (all eight tile columns are the same token), so the
 //            record carries that row's constants: for 4-bit codes the rows of odd tig sit in
@@ -138,21 +138,48 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
     int2* sxz = reinterpret_cast<int2*>(smem + p.act2_off);
     const int Mz = (M + 1) & ~1;
     const int64_t row_words = p.in >> 2;
-    for (int c = 0; c < Mz; ++c) {
-        const uint32_t* xr = xqw + c * row_words;
-        if (c < M) {
-            for (int i = tid; i < nb * 4; i += kConsumers) {
-                const int b = i >> 2, tg = i & 3;
-                sB[(b * M + c) * 4 + tg] = make_uint2(xr[b * 8 + tg], xr[b * 8 + 4 + tg]);
+    // The (token, word pair) space is walked flat, four global loads in flight per thread before
+    // the first store: the loads of different tokens do not wait for one another.
+    constexpr int U = 4;
+    const int per = nb * 4, tot = M * per;
+    for (int o0 = tid; o0 < tot; o0 += U * kConsumers) {
+        uint32_t wa[U], wb[U];
+        int dst[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int o = o0 + j * kConsumers;
+            dst[j] = -1;
+            if (o < tot) {
+                const int c = o / per, i = o - c * per, b = i >> 2, tg = i & 3;
+                const uint32_t* xr = xqw + c * row_words;
+                wa[j] = xr[b * 8 + tg];
+                wb[j] = xr[b * 8 + 4 + tg];
+                dst[j] = (b * M + c) * 4 + tg;
             }
         }
-        for (int b = tid; b < nb; b += kConsumers) {
-            int2 v = make_int2(0, 0);
-            if (c < M) {
-                v.x = __float_as_int(p.xs[(int64_t)c * nb + b]);
-                v.y = p.zp * p.xsum[(int64_t)c * nb + b];
+#pragma unroll
+        for (int j = 0; j < U; ++j)
+            if (dst[j] >= 0) sB[dst[j]] = make_uint2(wa[j], wb[j]);
+    }
+    const int tot2 = nb * Mz;
+    for (int o0 = tid; o0 < tot2; o0 += U * kConsumers) {
+        int2 v[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int o = o0 + j * kConsumers;
+            v[j] = make_int2(0, 0);
+            if (o < tot2) {
+                const int b = o / Mz, c = o - b * Mz;
+                if (c < M) {
+                    v[j].x = __float_as_int(p.xs[(int64_t)c * nb + b]);
+                    v[j].y = p.zp * p.xsum[(int64_t)c * nb + b];
+                }
             }
-            sxz[b * Mz + c] = v;
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int o = o0 + j * kConsumers;
+            if (o < tot2) sxz[o] = v[j];
         }
     }
 }

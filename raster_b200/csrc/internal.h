@@ -165,8 +165,8 @@ int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
                       const float* src_scales, uint8_t* dst, int fmt, int layout, int64_t out,
                       int64_t in, int64_t src_in, int64_t k_block0);
 // actquant.cu
-int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs,
-                            int32_t* xsum, int64_t M, int64_t in);
+int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
+                            int32_t* xsum, int64_t M, int64_t in, int act_dtype = RSTQ_F32);
 // Exchange fused into the tail of the decode kernel (layout of a region: see tp.cu).  The
 // kernel writes its results into slot `rank` of every rank's stage instead of y, signals, waits
 // (time-bounded) for the other ranks and lays the slots side by side (sum = 0) or adds them in

@@ -32,8 +32,8 @@ FMT = {4: (cq.q4_0, L.FMT_Q4_0, 0), 8: (cq.q8_0, L.FMT_Q8_0, 1)}
 
 
 def relerr(y, ref):
-    ref = np.asarray(ref, dtype=np.float64)
-    return float(np.abs(np.asarray(y, dtype=np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+    ref = np.asarray(ref, dtype=np.float64).ravel()
+    return float(np.abs(np.asarray(y, dtype=np.float64).ravel() - ref).max() / max(np.abs(ref).max(), 1e-30))
 
 
 def make_weight(out, in_, bits, seed=1, sigma=0.02):
@@ -280,6 +280,25 @@ def test_zero_inputs_give_exact_zeros(ctx, bits):
     w0 = ctx.bind_weight(wq0, ws0, out, in_, fmt, L.LAYOUT_ROWMAJOR)
     assert not ctx.qmatmul_host(w0, synth.normal(4, in_), 1, L.F32, L.MODE_A8).any()
     w0.free()
+
+
+@pytest.mark.parametrize("M", [1, 4, 9])
+def test_a8_takes_bf16_activations_like_their_f32_values(ctx, M):
+    out, in_ = 1000, 4096
+    _, wq, ws = make_weight(out, in_, 4, seed=33)
+    xb = synth.to_bf16_bits(synth.normal(34, M * in_))
+    xf = synth.from_bf16_bits(xb)                       # the same values, widened
+    w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    b16, b32 = ctx.array_to_buffer(xb), ctx.array_to_buffer(xf)
+    y16, y32 = ctx.make_buffer(M * out, np.float32), ctx.make_buffer(M * out, np.float32)
+    ctx.qmatmul(w, b16, y16, M, L.BF16, L.F32, L.MODE_A8)
+    ctx.qmatmul(w, b32, y32, M, L.F32, L.F32, L.MODE_A8)
+    ctx.sync()
+    assert np.array_equal(y16.download().view(np.uint32), y32.download().view(np.uint32))
+    xq, xs, xsum = orc.quantize_act_i8(xf, M, in_)
+    assert relerr(y16.download(), orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out)) <= TOL_A8
+    for o in (w, b16, b32, y16, y32):
+        o.free()
 
 
 def test_partial_groups_and_reproducibility(ctx):
