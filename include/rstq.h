@@ -83,7 +83,9 @@ typedef struct rstq_event rstq_event;
 #define RSTQ_SPLIT_ROW 2    /* rank owns K range   [rank*in/P,  (rank+1)*in/P) of every row */
 
 /* tuning keys (rstq_tune) */
-#define RSTQ_TUNE_GEMM_MIN_M 1  /* smallest M routed to the tensor-core GEMM (default 17) */
+#define RSTQ_TUNE_GEMM_MIN_M 1  /* smallest M routed to the tensor-core GEMM (default 17; at the
+                                   default, MODE_F also takes it from M = 9 when the rows are too long
+                                   for the decode kernel to hold M tokens in shared memory) */
 #define RSTQ_TUNE_GEMM_KERNEL 0  /* prefill GEMM: 0 (default) = dequantized weights kept in tensor
                                      memory, 1 = staged through shared memory */
 #define RSTQ_TUNE_PDL 2           /* 1 (default) = launch the decode kernels with programmatic

@@ -151,8 +151,14 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
     // Prefill shapes go to the tensor-core GEMM (fp16 operands, results within 1e-3 of the
     // reference).  A8 keeps its exact integer path up to M = 63: callers that chose the
     // quantized-activation arithmetic get it bit-faithfully at decode and small-batch sizes.
-    const bool tc = M >= (mode == RSTQ_MODE_A8 ? (ctx->tune_gemm_min_m > 64 ? ctx->tune_gemm_min_m : 64)
-                                                : ctx->tune_gemm_min_m);
+    bool tc = M >= (mode == RSTQ_MODE_A8 ? (ctx->tune_gemm_min_m > 64 ? ctx->tune_gemm_min_m : 64)
+                                          : ctx->tune_gemm_min_m);
+    // MODE_F, 9 .. 16 tokens of long rows: the decode kernel keeps every token's activations in
+    // shared memory and would have to cut M into several launches, each streaming all the
+    // weights again (3 - 5 x slower than the tensor-core path, measured at K = 8192 and 28672).
+    if (mode == RSTQ_MODE_F && !tc && M >= 9 && ctx->tune_gemm_min_m == 17 &&
+        w->in * 2 * M * (act_dtype == RSTQ_F32 ? 2 : 1) > 96 * 1024)
+        tc = true;
     if (tp && (tc || out_dtype != RSTQ_F32)) return kNotFused;  // only the decode kernel fuses the exchange
     if (mode == RSTQ_MODE_A8) {
         RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "unknown activation type");

@@ -405,6 +405,8 @@ def test_tokens_are_split_when_activations_exceed_shared_memory(ctx):
     assert ctx.launch_count() - n0 >= 3      # quantizer + at least two decode launches
     xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
     assert relerr(y, orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out)) <= TOL_A8
-    yf = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_F)
-    assert relerr(yf, orc.matmul_dq_f64(wq, ws, 0, x, M, in_, out)) <= TOL_F
+    yf = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_F)      # long rows, M >= 9: the tensor-core path
+    assert relerr(yf, orc.matmul_dq_f64(wq, ws, 0, x, M, in_, out)) <= TOL_GEMM
+    y8 = ctx.qmatmul_host(w, x[: 8 * in_], 8, L.F32, L.MODE_F)   # 8 tokens stay on the decode kernel, split
+    assert relerr(y8, orc.matmul_dq_f64(wq, ws, 0, x[: 8 * in_], 8, in_, out)) <= TOL_F
     w.free()
