@@ -135,13 +135,17 @@ static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int6
     return launch_gemv_f(ctx, ctx->devs[w->dev], a);
 }
 
-// fp16 activation scratch of the tensor-core path: [x16: M*in halves][rowscale: M floats]
-static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, void** x16, float** rowscale) {
-    const int64_t xb = (M * in * 2 + 255) & ~255ll;
-    int32_t rc = dev_reserve(ds, &ds.gemm_scratch, &ds.gemm_scratch_bytes, xb + M * 4);
+// scratch of the tensor-core path: [x16: M*in halves][rowscale: M floats][acc: M*out f32, only for
+// calls small enough to be split along K]
+static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, int64_t out, void** x16, float** rowscale,
+                            float** acc) {
+    const int64_t xb = (M * in * 2 + 255) & ~255ll, rb = (M * 4 + 255) & ~255ll;
+    const int64_t ab = M <= 256 ? M * out * 4 : 0;
+    int32_t rc = dev_reserve(ds, &ds.gemm_scratch, &ds.gemm_scratch_bytes, xb + rb + ab);
     if (rc != RSTQ_OK) return rc;
     *x16 = ds.gemm_scratch;
     *rowscale = (float*)((char*)ds.gemm_scratch + xb);
+    *acc = ab ? (float*)((char*)ds.gemm_scratch + xb + rb) : nullptr;
     return RSTQ_OK;
 }
 
@@ -159,6 +163,9 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
     if (mode == RSTQ_MODE_F && !tc && M >= 9 && ctx->tune_gemm_min_m == 17 &&
         w->in * 2 * M * (act_dtype == RSTQ_F32 ? 2 : 1) > 96 * 1024)
         tc = true;
+    // The same for MODE_A8 when not even 8 tokens of codes fit (K > 16 K): the codes and scales the
+    // quantizer produced feed the tensor-core path instead (<= 1e-3, no longer the exact integer dots).
+    if (mode == RSTQ_MODE_A8 && !tc && M >= 9 && ctx->tune_gemm_min_m == 17 && w->in * 8 > 128 * 1024) tc = true;
     if (tp && (tc || out_dtype != RSTQ_F32)) return kNotFused;  // only the decode kernel fuses the exchange
     if (mode == RSTQ_MODE_A8) {
         RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "unknown activation type");
@@ -171,15 +178,17 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
         if (!tc) return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M, tp);
         void* x16;
         float* rowscale;
-        if ((rc = gemm_scratch(ds, M, w->in, &x16, &rowscale)) != RSTQ_OK) return rc;
-        return launch_gemm(ctx, ds, w, s.xq, s.xs, 2, y, out_dtype, M, x16, rowscale);
+        float* acc;
+        if ((rc = gemm_scratch(ds, M, w->in, w->out, &x16, &rowscale, &acc)) != RSTQ_OK) return rc;
+        return launch_gemm(ctx, ds, w, s.xq, s.xs, 2, y, out_dtype, M, x16, rowscale, acc);
     }
     if (!tc) return run_f(ctx, w, x, y, M, act_dtype, out_dtype, tp);
     void* x16;
     float* rowscale;
-    int32_t rc = gemm_scratch(ds, M, w->in, &x16, &rowscale);
+    float* acc;
+    int32_t rc = gemm_scratch(ds, M, w->in, w->out, &x16, &rowscale, &acc);
     if (rc != RSTQ_OK) return rc;
-    return launch_gemm(ctx, ds, w, x, nullptr, act_dtype == RSTQ_F32 ? 0 : 1, y, out_dtype, M, x16, rowscale);
+    return launch_gemm(ctx, ds, w, x, nullptr, act_dtype == RSTQ_F32 ? 0 : 1, y, out_dtype, M, x16, rowscale, acc);
 }
 
 static int32_t bind_impl(rstq_ctx* ctx, rstq_weight** wout, const void* codes,

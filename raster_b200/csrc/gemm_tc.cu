@@ -217,6 +217,9 @@ struct GemmParams {
     int64_t out;            // output features
     int nb, ngroups;        // K blocks per row, 32-row groups stored
     int M, ksteps, ttiles;
+    int tiles, ksplit;      // feature x token tiles; K is cut into ksplit ranges of ksteps steps (last may be shorter)
+    int ksteps_total;
+    float* acc32;           // ksplit > 1: partial results are added into this zeroed [M, out] f32 array
     float wmul, wdiv;       // 2^ew applied to the block scales, 2^-ew applied to the result
     int out_dtype;
     unsigned long long* dbg;  // optional timeline of CTA 0 (see RSTQ_TUNE_TIMELINE), or null
@@ -612,7 +615,9 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     // full[s]: 16 dequant warps have stored A of the stage and the TMA bytes of B have landed;
     // empty[s]: the MMAs that read the stage have completed (tcgen05.commit)
     const uint32_t full = bar0, empty = bar0 + 8 * kNSTT, acc_full = bar0 + 16 * kNSTT;
-    const int ft = blockIdx.x / p.ttiles, tt = blockIdx.x - ft * p.ttiles;
+    const int kz = blockIdx.x / p.tiles, tile = blockIdx.x - kz * p.tiles;  // K range, output tile
+    const int ft = tile / p.ttiles, tt = tile - ft * p.ttiles;
+    const int ks_begin = kz * p.ksteps;
     const int tok0 = tt * NTOK;
     volatile int* abort_flag = &s_abort;
 
@@ -633,7 +638,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const int ksteps = p.ksteps;
+    const int ksteps = min(p.ksteps, p.ksteps_total - ks_begin);
     unsigned long long* dbg = (p.dbg && blockIdx.x == 0) ? p.dbg : nullptr;
     if (dbg && tid == 64) dbg[301] = (unsigned long long)clock64();
 
@@ -649,8 +654,8 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                 if (!ok) break;
                 const uint32_t dst = sbase + s * BSTAGE;
                 mbar_expect_tx(full + 8 * s, BSTAGE);
-                tma_load_2d(dst, &tmap, ks * kKStep, tok0, full + 8 * s);
-                tma_load_2d(dst + NTOK * 128, &tmap, ks * kKStep + 64, tok0, full + 8 * s);
+                tma_load_2d(dst, &tmap, (ks_begin + ks) * kKStep, tok0, full + 8 * s);
+                tma_load_2d(dst + NTOK * 128, &tmap, (ks_begin + ks) * kKStep + 64, tok0, full + 8 * s);
                 ++issued;
                 if (++s == kNSTT) { s = 0; ph ^= 1u; }
             }
@@ -716,9 +721,9 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
         const int gid = lane >> 2;
         const int64_t g_glob = (int64_t)ft * 4 + grp;
         const bool g_valid = g_glob < p.ngroups;
-        const uint8_t* wptr = p.w + (g_glob * p.nb + sub) * UNIT + lane * 16;
-        const uint8_t* sptr = p.w + (g_glob * p.nb + sub) * UNIT + CODES + gid * 16;
-        int bk_next = sub;
+        const uint8_t* wptr = p.w + (g_glob * p.nb + sub + 4 * ks_begin) * UNIT + lane * 16;
+        const uint8_t* sptr = p.w + (g_glob * p.nb + sub + 4 * ks_begin) * UNIT + CODES + gid * 16;
+        int bk_next = sub + 4 * ks_begin;
         auto load = [&](RawT<BITS>& r) {
             if (g_valid && bk_next < p.nb) {
                 if constexpr (BITS == 4) {
@@ -824,7 +829,15 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             tmem_ld_wait();
             const float wdiv = p.wdiv;
             const int tokb = tok0 + cq * CPW;
-            if (f < p.out) {
+            if (f < p.out && p.ksplit > 1) {
+                // two K ranges add their halves into a zeroed f32 array: a + b in either order
+                float* y = p.acc32 + f;
+#pragma unroll
+                for (int j = 0; j < CPW; ++j)
+                    if (tokb + j < p.M)
+                        atomicAdd(y + (int64_t)(tokb + j) * p.out,
+                                  __uint_as_float(v[j]) * wdiv * __ldg(p.rowscale + tokb + j));
+            } else if (f < p.out) {
                 if (p.out_dtype == RSTQ_BF16) {
                     __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) + f;
 #pragma unroll
@@ -907,8 +920,16 @@ static cudaError_t launch_pdl(K kernel, dim3 grid, dim3 block, size_t smem, cons
 // y[M, out] = x[M, in] . dequant(W)^T on the tensor cores.  src: 0 = f32 x, 1 = bf16 x,
 // 2 = int8 codes x with per-block scales xs.  x16 / rowscale are caller-provided scratch
 // (M*in fp16, M floats).
+// f32 -> output type after a split-K accumulation
+__global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restrict__ acc, void* __restrict__ y,
+                                                          int out_dtype, int64_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) store_out(y, out_dtype, i, acc[i]);
+}
+
 int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const void* x, const float* xs,
-                    int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale) {
+                    int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale, float* acc32) {
     RSTQ_REQUIRE(M >= 1 && M < (1ll << 30), RSTQ_E_SHAPE, "M = %lld", (long long)M);
     RSTQ_REQUIRE(((uintptr_t)x16 & 15) == 0 && (w->in * 2) % 16 == 0, RSTQ_E_ALIGN,
                  "activation scratch must be 16-byte aligned");
@@ -950,15 +971,27 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     p.nb = (int)w->nb;
     p.ngroups = (int)(w->outp / 32);
     p.M = (int)M;
-    p.ksteps = (int)((w->nb + 3) / 4);
+    p.ksteps_total = (int)((w->nb + 3) / 4);
     p.ttiles = (int)((M + ntok - 1) / ntok);
     p.wmul = ldexpf(1.0f, w->gemm_exp);
     p.wdiv = ldexpf(1.0f, -w->gemm_exp);
     p.out_dtype = out_dtype;
     p.dbg = ds.dbg;
     const int64_t ftiles = (w->out + 127) / 128;
-    RSTQ_REQUIRE(ftiles * p.ttiles < (1ll << 31), RSTQ_E_LIMIT, "grid too large");
-    const dim3 grid((unsigned)(ftiles * p.ttiles));
+    RSTQ_REQUIRE(ftiles * p.ttiles < (1ll << 30), RSTQ_E_LIMIT, "grid too large");
+    p.tiles = (int)(ftiles * p.ttiles);
+    // Few output tiles and a long K (small M, short matrices): two CTAs share a tile, each takes half
+    // of K, so twice as many SMs stream weights.  The halves meet in a zeroed f32 array (a + b is the
+    // same in either order, so the result stays reproducible); a bf16 result is converted afterwards.
+    const bool a_tmem = ctx->tune_gemm_kernel != 1;
+    p.ksplit = (a_tmem && acc32 && p.tiles * 2 <= ds.sm_count && p.ksteps_total >= 16) ? 2 : 1;
+    p.ksteps = (p.ksteps_total + p.ksplit - 1) / p.ksplit;
+    p.acc32 = nullptr;
+    if (p.ksplit > 1) {
+        p.acc32 = out_dtype == RSTQ_F32 ? (float*)y : acc32;
+        RSTQ_CUDA(cudaMemsetAsync(p.acc32, 0, (size_t)M * w->out * 4, ds.stream));
+    }
+    const dim3 grid((unsigned)(p.tiles * p.ksplit));
     const size_t smem = a_in_tmem ? kNSTT * ((size_t)ntok * kKStep * 2) + 1024
                                   : kNST * (kAStage + (size_t)ntok * kKStep * 2) + 1024;
 #define GL(B, N)                                                                                     \
@@ -977,6 +1010,14 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     ctx->launches++;
     RSTQ_CUDA(le);
     RSTQ_CUDA(cudaGetLastError());
+    if (p.ksplit > 1 && out_dtype != RSTQ_F32) {
+        const int64_t n = M * w->out;
+        int64_t ctas = (n + 255) / 256;
+        if (ctas > (int64_t)ds.sm_count * 8) ctas = (int64_t)ds.sm_count * 8;
+        RSTQ_CUDA(launch_pdl(gemm_finish_kernel, dim3((unsigned)ctas), dim3(256), 0, ds, (const float*)p.acc32, y,
+                             out_dtype, n));
+        ctx->launches++;
+    }
     return RSTQ_OK;
 }
 

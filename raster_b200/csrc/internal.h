@@ -208,7 +208,8 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a);
 int32_t gemv_configure(DeviceState& ds);  // shared-memory attributes, once per device
 // gemm_tc.cu
 int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const void* x, const float* xs,
-                    int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale);
+                    int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale,
+                    float* acc32 = nullptr);
 int32_t gemm_configure(DeviceState& ds);
 // capi.cu
 int32_t use_dev(rstq_ctx* ctx, int dev);

@@ -58,6 +58,29 @@ def test_gemm_f32_and_bf16_activations(ctx, bits, out, in_, M):
     bx.free(), by.free(), bw.free()
 
 
+def test_gemm_split_along_k_is_reproducible(ctx):
+    """Few output tiles and a long K: two CTAs share a tile and add their halves into a zeroed f32
+    array.  a + b does not depend on the order, so two runs agree bit for bit; K = 4128 gives an odd
+    number of 128-element steps (17 + 16) and a last step of a single block."""
+    out, in_, M = 256, 4128, 40
+    w = synth.normal(11, out * in_, 0.02)
+    wq, ws = orc.quantize_weight(w, 8)
+    x = synth.normal(12, M * in_)
+    bw = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q8_0, L.LAYOUT_ROWMAJOR)
+    y1 = ctx.qmatmul_host(bw, x, M, L.F32, L.MODE_F)
+    y2 = ctx.qmatmul_host(bw, x, M, L.F32, L.MODE_F)
+    assert np.array_equal(y1.view(np.uint32), y2.view(np.uint32))
+    assert relerr(y1, orc.matmul_dq_f64(wq, ws, 1, x, M, in_, out).reshape(M, out)) <= 1e-3
+    xb = synth.to_bf16_bits(x)
+    bx, by = ctx.array_to_buffer(xb), ctx.make_buffer(M * out, np.uint16)
+    ctx.qmatmul(bw, bx, by, M, L.BF16, L.BF16, L.MODE_F)
+    ctx.sync()
+    refb = orc.matmul_dq_f64(wq, ws, 1, synth.from_bf16_bits(xb), M, in_, out).reshape(M, out)
+    yb = synth.from_bf16_bits(by.download()).reshape(M, out)
+    assert np.all(np.abs(yb - refb) <= 2.0 ** -8 * np.abs(refb) + 1e-3 * np.abs(refb).max())
+    bx.free(), by.free(), bw.free()
+
+
 def test_gemm_quantized_activation_mode(ctx):
     """MODE_A8 at prefill size: exact activation codes, fp16 tensor-core product."""
     out, in_, M = 512, 1024, 96

@@ -400,11 +400,14 @@ def test_tokens_are_split_when_activations_exceed_shared_memory(ctx):
     _, wq, ws = make_weight(out, in_, 4, seed=5)
     x = synth.normal(6, M * in_)
     w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
-    n0 = ctx.launch_count()
-    y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)
-    assert ctx.launch_count() - n0 >= 3      # quantizer + at least two decode launches
     xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
-    assert relerr(y, orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out)) <= TOL_A8
+    ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out).reshape(M, out)
+    y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)      # 16 tokens of rows this long: tensor-core path
+    assert relerr(y, ref) <= TOL_GEMM
+    n0 = ctx.launch_count()
+    y = ctx.qmatmul_host(w, x[: 8 * in_], 8, L.F32, L.MODE_A8)   # 8 tokens: decode kernel, M cut in pieces
+    assert ctx.launch_count() - n0 >= 3      # quantizer + at least two decode launches
+    assert relerr(y, ref[:8]) <= TOL_A8
     yf = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_F)      # long rows, M >= 9: the tensor-core path
     assert relerr(yf, orc.matmul_dq_f64(wq, ws, 0, x, M, in_, out)) <= TOL_GEMM
     y8 = ctx.qmatmul_host(w, x[: 8 * in_], 8, L.F32, L.MODE_F)   # 8 tokens stay on the decode kernel, split
