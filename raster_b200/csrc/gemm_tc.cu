@@ -499,7 +499,10 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
 // from shared memory, which halves the shared-memory traffic of the K loop.
 // Warp roles: 0 = TMA (activations), 1 = MMA, 2..17 = dequant: warp & 3 = 32-row group (= its
 // tensor-memory sub-partition), (warp - 2) >> 2 = block of the K-step.
-constexpr int kNSTT = 6;                  // pipeline stages: B in shared memory, A in tensor memory
+constexpr int kGemmThreadsT = (3 + kDqWarps) * 32;  // TMA warp, MMA warp (even K-steps), 16 dequant / epilogue warps, MMA warp (odd K-steps)
+// pipeline stages (B in shared memory, A in tensor memory): what is left of the 512 columns after two
+// accumulators, at most 6
+__host__ __device__ constexpr int gemm_stages(int ntok) { return (512 - 2 * ntok) / 64 > 6 ? 6 : (512 - 2 * ntok) / 64; }
 constexpr int kAColsPerStage = kKStep / 2;
 
 __device__ __forceinline__ void tmem_st_16x256b_x2(uint32_t taddr, const uint32_t (&r)[8]) {
@@ -595,19 +598,21 @@ struct RawT<8> {
 };
 
 template <int BITS, int NTOK>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreadsT, 1)
 gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     constexpr int UNIT = BITS == 4 ? kUnitBytesQ4 : kUnitBytesQ8;
     constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
     constexpr int BSTAGE = NTOK * kKStep * 2;
-    constexpr uint32_t TMEM_COLS = 512;                       // D (NTOK) + A ring (6 x 64), power of two
-    constexpr uint32_t A_COL0 = NTOK;                         // A ring starts after the accumulator
-    static_assert(NTOK + kNSTT * kAColsPerStage <= 512, "tensor memory holds D and the A ring");
+    constexpr int kNSTT = gemm_stages(NTOK);
+    constexpr uint32_t TMEM_COLS = 512;                       // two accumulators (2 x NTOK) + A ring, power of two
+    constexpr uint32_t A_COL0 = 2 * NTOK;                     // A ring starts after the accumulators
+    static_assert(2 * NTOK + kNSTT * kAColsPerStage <= 512 && kNSTT >= 2 && kNSTT % 2 == 0,
+                  "tensor memory holds both accumulators and the A ring");
     extern __shared__ uint8_t smem_raw[];
     if (p.dbg && blockIdx.x == 0 && threadIdx.x == 64) { p.dbg[300] = (unsigned long long)clock64(); p.dbg[304] = gtime_ns(); }
     __shared__ int s_abort;
     __shared__ uint32_t s_tmem;
-    __shared__ __align__(8) uint64_t s_bar[2 * kNSTT + 1];
+    __shared__ __align__(8) uint64_t s_bar[2 * 6 + 1];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -620,12 +625,13 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     const int ks_begin = kz * p.ksteps;
     const int tok0 = tt * NTOK;
     volatile int* abort_flag = &s_abort;
+    const int ksteps = min(p.ksteps, p.ksteps_total - ks_begin);
 
     if (tid < kNSTT) {
         mbar_init(full + 8 * tid, kDqWarps + 1);
         mbar_init(empty + 8 * tid, 1);
     } else if (tid == kNSTT) {
-        mbar_init(acc_full, 1);
+        mbar_init(acc_full, ksteps >= 2 ? 2 : 1);  // one arrival per MMA issuer that has steps
         s_abort = 0;
     }
     if (tid <= kNSTT) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -638,7 +644,6 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const int ksteps = min(p.ksteps, p.ksteps_total - ks_begin);
     unsigned long long* dbg = (p.dbg && blockIdx.x == 0) ? p.dbg : nullptr;
     if (dbg && tid == 64) dbg[301] = (unsigned long long)clock64();
 
@@ -668,50 +673,50 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        // The whole warp runs the loop with identical values (so the address arithmetic stays
-        // warp-uniform) and lane 0 alone issues the tensor-core instructions.  The loop must cost
-        // fewer issue cycles than the 8 MMAs of a step take to execute (8 x 64 cycles), or the
-        // tensor core starves: the descriptor of a stage is one multiply-add, each MMA adds a
-        // constant to it, and the barrier of step ks + 1 is tested before the MMAs of step ks so
-        // that its answer is back by the time they have been issued.
+    } else if (warp == 1 || warp == 2 + kDqWarps) {
+        // ---------------- MMA issuers ----------------
+        // Issuing is what limits the tensor core here: a tcgen05 instruction costs the issuing
+        // thread 50 - 60 cycles (measured: an MMA, a commit and a barrier test alike, whatever N
+        // is), so the eight MMAs of a step plus its barrier work take one thread about 900 cycles
+        // while the tensor core needs 512 for them.  Two warps on different schedulers therefore
+        // take alternate K-steps, each into an accumulator of its own (the epilogue adds them);
+        // each commits its own stages, so the rest of the pipeline does not notice.
+        // The whole warp runs the loop with identical values (the address arithmetic stays
+        // warp-uniform) and lane 0 alone issues the tensor-core instructions.
+        const int m = warp == 1 ? 0 : 1;
         constexpr uint32_t idesc = idesc_f16(NTOK);
         const uint32_t leader = lane == 0;
         const uint64_t d0 = smem_desc_sw128(sbase);
         const uint32_t d_lo = (uint32_t)d0, d_hi = (uint32_t)(d0 >> 32);
-        int s = 0;
-        uint32_t ph = 0;
-        bool any = false;
-        bool ok = mbar_spin(full, 0, abort_flag);
-        if (dbg && lane == 0) dbg[306] = (unsigned long long)clock64();
-        // The tensor core's queue is only an MMA or two deep: whenever this warp is late with the
-        // next MMA the pipe runs dry and pays a restart on top, so a step is one block of
-        // instructions (see umma_f16_ts_step) and the loop around it only rotates registers.
+        const uint32_t dcol = tmem + (uint32_t)(m * NTOK);
         static_assert(kKStep == 128, "eight MMAs per step");
-        uint32_t a0 = tmem + A_COL0, b_lo = d_lo, prev_empty = empty;
-        for (int ks = 0; ks < ksteps && ok; ++ks) {
-            int s1 = s + 1;
-            uint32_t ph1 = ph;
-            if (s1 == kNSTT) { s1 = 0; ph1 ^= 1u; }
-            const uint32_t a0n = tmem + A_COL0 + s1 * kAColsPerStage, b_lon = d_lo + (uint32_t)s1 * (BSTAGE >> 4);
-            const uint32_t n1 = umma_f16_ts_step<NTOK * 8>(tmem, a0, b_lo, d_hi, idesc, ks != 0, leader, prev_empty,
-                                                           ks != 0, full + 8 * s1, ph1);
-            any = true;
-            prev_empty = empty + 8 * s;
-            if (ks + 1 < ksteps && !n1) ok = mbar_spin(full + 8 * s1, ph1, abort_flag);
-            a0 = a0n;
-            b_lo = b_lon;
-            s = s1;
-            ph = ph1;
-        }
-        if (any) umma_commit_if(prev_empty, leader);  // the last stage (nobody waits for it; keeps the ring uniform)
-        if (dbg && lane == 0) dbg[307] = (unsigned long long)clock64();
-        if (ok || any) {
-            umma_commit_if(acc_full, leader);
-            if (!ok) {  // gave up: tensor core must be idle before tensor memory is freed
-                const unsigned long long t0 = gtime_ns();
-                while (!mbar_try(acc_full, 0) && gtime_ns() - t0 < kWaitLimitNs) {
+        if (m < ksteps) {
+            int s = m;
+            uint32_t ph = 0;
+            bool any = false;
+            bool ok = mbar_spin(full + 8 * s, 0, abort_flag);
+            if (dbg && lane == 0) dbg[306 + 2 * m] = (unsigned long long)clock64();
+            for (int ks = m; ks < ksteps && ok; ks += 2) {
+                int s2 = s + 2;
+                uint32_t ph2 = ph;
+                if (s2 >= kNSTT) { s2 -= kNSTT; ph2 ^= 1u; }
+                const uint32_t a0 = tmem + A_COL0 + s * kAColsPerStage, b_lo = d_lo + (uint32_t)s * (BSTAGE >> 4);
+                // the block also tests the barrier of this issuer's next step (ks + 2) early
+                const uint32_t n2 = umma_f16_ts_step<NTOK * 8>(dcol, a0, b_lo, d_hi, idesc, ks != m, leader, empty, 0u,
+                                                               full + 8 * s2, ph2);
+                umma_commit_if(empty + 8 * s, leader);  // the stage is free once these MMAs have read it
+                any = true;
+                if (ks + 2 < ksteps && !n2) ok = mbar_spin(full + 8 * s2, ph2, abort_flag);
+                s = s2;
+                ph = ph2;
+            }
+            if (dbg && lane == 0) dbg[307 + 2 * m] = (unsigned long long)clock64();
+            if (any) {
+                umma_commit_if(acc_full, leader);
+                if (!ok) {  // gave up: the tensor core must be idle before tensor memory is freed
+                    const unsigned long long t0 = gtime_ns();
+                    while (!mbar_try(acc_full, 0) && gtime_ns() - t0 < kWaitLimitNs) {
+                    }
                 }
             }
         }
@@ -827,6 +832,14 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
 #pragma unroll
             for (int c0 = 0; c0 < CPW; c0 += 8) tmem_ld8(t0 + c0, *reinterpret_cast<uint32_t(*)[8]>(&v[c0]));
             tmem_ld_wait();
+            if (ksteps >= 2) {  // the odd K-steps went into the second accumulator
+                uint32_t v2[CPW];
+#pragma unroll
+                for (int c0 = 0; c0 < CPW; c0 += 8) tmem_ld8(t0 + NTOK + c0, *reinterpret_cast<uint32_t(*)[8]>(&v2[c0]));
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < CPW; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+            }
             const float wdiv = p.wdiv;
             const int tokb = tok0 + cq * CPW;
             if (f < p.out && p.ksplit > 1) {
@@ -885,7 +898,7 @@ static int32_t gemm_attr() {
     RSTQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BITS, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    kNST * (kAStage + NTOK * kKStep * 2) + 1024));
     RSTQ_CUDA(cudaFuncSetAttribute(gemm_tmem_kernel<BITS, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kNSTT * (NTOK * kKStep * 2) + 1024));
+                                   gemm_stages(NTOK) * (NTOK * kKStep * 2) + 1024));
     return RSTQ_OK;
 }
 
@@ -992,10 +1005,10 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
         RSTQ_CUDA(cudaMemsetAsync(p.acc32, 0, (size_t)M * w->out * 4, ds.stream));
     }
     const dim3 grid((unsigned)(p.tiles * p.ksplit));
-    const size_t smem = a_in_tmem ? kNSTT * ((size_t)ntok * kKStep * 2) + 1024
+    const size_t smem = a_in_tmem ? gemm_stages(ntok) * ((size_t)ntok * kKStep * 2) + 1024
                                   : kNST * (kAStage + (size_t)ntok * kKStep * 2) + 1024;
 #define GL(B, N)                                                                                     \
-    le = a_in_tmem ? launch_pdl(gemm_tmem_kernel<B, N>, grid, dim3(kGemmThreads), smem, ds, p, tmap) \
+    le = a_in_tmem ? launch_pdl(gemm_tmem_kernel<B, N>, grid, dim3(kGemmThreadsT), smem, ds, p, tmap) \
                    : launch_pdl(gemm_tc_kernel<B, N>, grid, dim3(kGemmThreads), smem, ds, p, tmap)
     if (w->bits == 4) {
         if (ntok == 32) GL(4, 32);
