@@ -73,6 +73,7 @@ __device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, volatil
 // handful of instructions per microsecond instead of a polling loop that competes for issue
 // slots with the warps doing the work.
 __device__ __forceinline__ bool mbar_block(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_test(bar, parity)) return true;  // one instruction when the phase is already complete
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)  // each try may suspend for a while: no timer reads on this path
         if (mbar_try(bar, parity)) return true;
