@@ -212,6 +212,11 @@ RSTQ_API int32_t rstq_qlinear_i8_q8(rstq_ctx* ctx, const float* x, const void* w
 RSTQ_API int32_t rstq_qlinear_q8(rstq_ctx* ctx, const float* x, const void* codes,
                                  const float* scales, float* y, int64_t m, int64_t in,
                                  int64_t out);
+/* qlinear-q8-dx (src/raster/quant/train.clj:110-142), the backward-data of qlinear-q8:
+ * dx[m, in] = dy[m, out] . dequant(codes, scales), W frozen.  Host arrays, same argument order. */
+RSTQ_API int32_t rstq_qlinear_q8_dx(rstq_ctx* ctx, const float* dy, const void* codes,
+                                    const float* scales, float* dx, int64_t m, int64_t in,
+                                    int64_t out);
 RSTQ_API int32_t rstq_qmatmul_i8_gemm(rstq_ctx* ctx, const int32_t* xp, const float* xs,
                                       const int32_t* wp, const float* ws, float* y, int64_t in,
                                       int64_t out, int64_t nrows);

@@ -44,6 +44,7 @@ SIGNATURES = {
     "rstq_qlinear_i8": [vp, vp, vp, vp, vp, i64, i64],
     "rstq_qlinear_i8_q8": [vp, vp, vp, vp, vp, i64, i64],
     "rstq_qlinear_q8": [vp, vp, vp, vp, vp, i64, i64, i64],
+    "rstq_qlinear_q8_dx": [vp, vp, vp, vp, vp, i64, i64, i64],
     "rstq_qmatmul_i8_gemm": [vp, vp, vp, vp, vp, vp, i64, i64, i64],
     "rstq_i8gemv_dp4a": [vp, vp, vp, vp, i64, i64],
     "rstq_qmatmul_host": [vp, vp, vp, vp, i64, i32, i32],

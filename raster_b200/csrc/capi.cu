@@ -646,6 +646,8 @@ int32_t rstq_weight_free(rstq_weight* w) {
     cudaSetDevice(ds.ordinal);
     if (!ds.capturing) cudaStreamSynchronize(ds.stream);
     cudaFree(w->data);
+    if (w->raw_codes) cudaFree(w->raw_codes);
+    if (w->raw_scales) cudaFree(w->raw_scales);
     cudaGetLastError();
     w->magic = 0;
     delete w;
@@ -740,16 +742,44 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
 }
 
 // ---- host-array operators -----------------------------------------------------
+// A fingerprint of the host arrays (64 samples of 8 bytes spread over the codes, 64 over the
+// scales): the cache is keyed by address, and a caller may free a matrix and get the same address
+// back for another one of the same shape.  A hit whose fingerprint differs is bound again.
+static uint64_t host_fingerprint(const void* codes, int64_t code_bytes, const float* scales, int64_t nscales) {
+    uint64_t h = 0x9E3779B97F4A7C15ull;
+    auto mix = [&](uint64_t v) { h = (h ^ v) * 0xBF58476D1CE4E5B9ull; h ^= h >> 29; };
+    const uint8_t* c = (const uint8_t*)codes;
+    const int64_t cw = code_bytes / 8;
+    for (int i = 0; i < 64 && cw > 0; ++i) {
+        uint64_t v;
+        memcpy(&v, c + (cw - 1) * i / 63 * 8, 8);
+        mix(v);
+    }
+    for (int i = 0; i < 64 && nscales > 0; ++i) {
+        uint32_t v;
+        memcpy(&v, scales + (nscales - 1) * i / 63, 4);
+        mix(v);
+    }
+    return h;
+}
+
 static int32_t cached_weight(rstq_ctx* ctx, const void* codes, const float* scales, int64_t in,
                              int64_t out, int fmt, int layout, rstq_weight** w) {
     rstq_ctx::CacheKey key{codes, scales, in, out, fmt, layout};
+    const int bits = fmt == RSTQ_FMT_Q4_0 ? 4 : 8;
+    const uint64_t fp = host_fingerprint(codes, out * in * bits / 8, scales, out * (in / 32));
     auto it = ctx->wcache.find(key);
     if (it != ctx->wcache.end()) {
-        *w = it->second;
-        return RSTQ_OK;
+        if (it->second->host_fp == fp) {
+            *w = it->second;
+            return RSTQ_OK;
+        }
+        rstq_weight_free(it->second);  // same address, other contents: the old matrix is gone
+        ctx->wcache.erase(it);
     }
     int32_t rc = bind_impl(ctx, w, codes, scales, 0, out, in, fmt, layout, RSTQ_SPLIT_NONE, 0, 1);
     if (rc != RSTQ_OK) return rc;
+    (*w)->host_fp = fp;
     ctx->wcache.emplace(key, *w);
     return RSTQ_OK;
 }
@@ -815,6 +845,32 @@ int32_t rstq_qlinear_q8(rstq_ctx* ctx, const float* x, const void* codes, const 
     if (rc != RSTQ_OK) return rc;
     return host_roundtrip(ctx, w->dev, x, m * in * 4, y, m * out * 4, [&](void* dx, void* dy) {
         return matmul_device(ctx, w, dx, dy, m, RSTQ_F32, RSTQ_F32, RSTQ_MODE_F);
+    });
+}
+
+int32_t rstq_qlinear_q8_dx(rstq_ctx* ctx, const float* dy, const void* codes, const float* scales, float* dx,
+                           int64_t m, int64_t in, int64_t out) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(dy && codes && scales && dx, RSTQ_E_INVALID, "null argument");
+    RSTQ_REQUIRE(m >= 1 && out >= 1 && in >= 32 && in % 32 == 0, RSTQ_E_SHAPE,
+                 "in=%lld not a multiple of 32 (m = %lld, out = %lld)", (long long)in, (long long)m,
+                 (long long)out);
+    rstq_weight* w = nullptr;
+    int32_t rc = cached_weight(ctx, codes, scales, in, out, RSTQ_FMT_Q8_S, RSTQ_LAYOUT_ROWMAJOR, &w);
+    if (rc != RSTQ_OK) return rc;
+    DeviceState& ds = ctx->devs[w->dev];
+    RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "host-array operators cannot be captured");
+    if ((rc = use_dev(ctx, w->dev)) != RSTQ_OK) return rc;
+    if (!w->raw_codes) {  // the transposed product reads W as the reference stores it
+        const int64_t cb = out * in, sb = out * (in / 32) * 4;
+        RSTQ_CUDA(cudaMalloc((void**)&w->raw_codes, (size_t)cb));
+        RSTQ_CUDA(cudaMalloc((void**)&w->raw_scales, (size_t)sb));
+        RSTQ_CUDA(cudaMemcpyAsync(w->raw_codes, codes, (size_t)cb, cudaMemcpyHostToDevice, ds.stream));
+        RSTQ_CUDA(cudaMemcpyAsync(w->raw_scales, scales, (size_t)sb, cudaMemcpyHostToDevice, ds.stream));
+        RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    }
+    return host_roundtrip(ctx, w->dev, dy, m * out * 4, dx, m * in * 4, [&](void* d_dy, void* d_dx) {
+        return launch_qlinear_q8_dx(ctx, ds, (const float*)d_dy, w->raw_codes, w->raw_scales, (float*)d_dx, m, in, out);
     });
 }
 

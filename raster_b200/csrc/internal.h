@@ -133,6 +133,9 @@ struct rstq_weight {
     uint8_t* data;     // mma32 units, (outp/32) * nb of them
     int64_t data_bytes;
     int gemm_exp;      // power of two applied to the block scales in the fp16 GEMM path
+    uint64_t host_fp = 0;          // fingerprint of the host arrays (host-array operators' cache)
+    int8_t* raw_codes = nullptr;   // row-major signed codes / scales as the reference holds them:
+    float* raw_scales = nullptr;   // made on first use by the backward-data operator
 };
 
 struct rstq_graph {
@@ -211,6 +214,9 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
                     int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale,
                     float* acc32 = nullptr);
 int32_t gemm_configure(DeviceState& ds);
+// dx.cu
+int32_t launch_qlinear_q8_dx(rstq_ctx* ctx, DeviceState& ds, const float* dy, const int8_t* codes,
+                             const float* scales, float* dx, int64_t m, int64_t in, int64_t out);
 // capi.cu
 int32_t use_dev(rstq_ctx* ctx, int dev);
 int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M, int act_dtype,

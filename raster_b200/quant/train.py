@@ -43,3 +43,17 @@ def qlinear_q8(x, codes, scales, m, in_, out, ctx=None):
     L.check(ctx.lib.rstq_qlinear_q8(ctx.handle, _np_ptr(x), _np_ptr(codes), _np_ptr(scales),
                                     _np_ptr(y), m, in_, out))
     return y
+
+
+def qlinear_q8_dx(dy, codes, scales, m, in_, out, ctx=None):
+    """Backward-data (src/raster/quant/train.clj:110-142): dx[m*in] = dy[m, out] . dequant(W)."""
+    ctx = ctx or default_context()
+    dy = np.ascontiguousarray(dy, dtype=np.float32)
+    codes = np.ascontiguousarray(codes)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    if codes.dtype not in (np.int8, np.uint8):
+        raise TypeError("codes must be a byte array")
+    dx = np.empty(m * in_, dtype=np.float32)
+    L.check(ctx.lib.rstq_qlinear_q8_dx(ctx.handle, _np_ptr(dy), _np_ptr(codes), _np_ptr(scales),
+                                       _np_ptr(dx), m, in_, out))
+    return dx

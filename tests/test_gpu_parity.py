@@ -413,3 +413,43 @@ def test_tokens_are_split_when_activations_exceed_shared_memory(ctx):
     y8 = ctx.qmatmul_host(w, x[: 8 * in_], 8, L.F32, L.MODE_F)   # 8 tokens stay on the decode kernel, split
     assert relerr(y8, orc.matmul_dq_f64(wq, ws, 0, x[: 8 * in_], 8, in_, out)) <= TOL_F
     w.free()
+
+
+# ---------------------------------------------------------------- backward-data of qlinear-q8
+@pytest.mark.parametrize("m,in_,out", [(3, 64, 8), (1, 4096, 4096), (5, 256, 72), (33, 512, 100), (64, 11008, 256)])
+def test_qlinear_q8_dx_operator(ctx, m, in_, out):
+    """dx = dy . dequant(W) (first shape is the reference's own test shape); also the identity its
+    gradient check rests on: <dy, forward(x)> == <dx, x> for the frozen weight."""
+    W = synth.normal(in_ + out + 7, out * in_, 0.2)
+    q = train.q8_quantize(W, out, in_)
+    dy = synth.normal(in_ + out + 8, m * out)
+    dx = train.qlinear_q8_dx(dy, q["codes"], q["scales"], m, in_, out, ctx)
+    ref = orc.qlinear_q8_dx(dy, q["codes"], q["scales"], m, in_, out)
+    assert relerr(dx, ref) <= TOL_F
+    dense = train.dequant_q8_dense(q["codes"], q["scales"], in_, out).reshape(out, in_).astype(np.float64)
+    assert relerr(dx.reshape(m, in_), dy.reshape(m, out).astype(np.float64) @ dense) <= TOL_F
+    if m <= 16:      # the forward below runs on the decode kernel (2e-5); adjoint identity to 1e-4
+        x = synth.normal(in_ + out + 9, m * in_)
+        y = train.qlinear_q8(x, q["codes"], q["scales"], m, in_, out, ctx)
+        lhs = float(np.dot(dy.astype(np.float64), y.astype(np.float64)))
+        rhs = float(np.dot(dx.astype(np.float64), x.astype(np.float64)))
+        assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), abs(rhs), 1.0)
+
+
+def test_host_array_cache_notices_new_contents_at_an_old_address(ctx):
+    """The host-array operators keep bound weights by address; a matrix rewritten in place (or
+    another one allocated where a freed one lived) must not be served from the stale copy."""
+    m, in_, out = 2, 256, 64
+    x = synth.normal(1, m * in_)
+    q = train.q8_quantize(synth.normal(2, out * in_, 0.2), out, in_)
+    codes, scales = q["codes"].copy(), q["scales"].copy()
+    y1 = train.qlinear_q8(x, codes, scales, m, in_, out, ctx)
+    assert relerr(y1, orc.qlinear_q8(x, codes, scales, m, in_, out)) <= TOL_F
+    q2 = train.q8_quantize(synth.normal(3, out * in_, 0.3), out, in_)
+    codes[:] = q2["codes"]                      # same arrays, same addresses, new matrix
+    scales[:] = q2["scales"]
+    y2 = train.qlinear_q8(x, codes, scales, m, in_, out, ctx)
+    assert relerr(y2, orc.qlinear_q8(x, codes, scales, m, in_, out)) <= TOL_F
+    dy = synth.normal(4, m * out)
+    dx = train.qlinear_q8_dx(dy, codes, scales, m, in_, out, ctx)
+    assert relerr(dx, orc.qlinear_q8_dx(dy, codes, scales, m, in_, out)) <= TOL_F
