@@ -810,6 +810,31 @@ def run_reference(args):
     }))
 
 
+def run_dx(args):
+    """--case dx:<out>:<in>:<M>: the backward-data operator qlinear-q8-dx through its host-array entry
+    (dy up, dx down over PCIe inside the timed call)."""
+    from raster_b200 import Context
+    from raster_b200.quant import train
+    _, out, in_, M = args.case.split(":")
+    out, in_, M = int(out), int(in_), int(M)
+    rng = np.random.default_rng(0)
+    ctx = Context(("cuda:0",))
+    codes = rng.integers(-127, 128, out * in_, dtype=np.int8)
+    scales = (rng.standard_normal(out * (in_ // 32)) * 0.01).astype(np.float32)
+    dy = rng.standard_normal(M * out).astype(np.float32)
+    for _ in range(2):
+        train.qlinear_q8_dx(dy, codes, scales, M, in_, out, ctx)
+    n = 5
+    t = time.perf_counter()
+    for _ in range(n):
+        train.qlinear_q8_dx(dy, codes, scales, M, in_, out, ctx)
+    s = (time.perf_counter() - t) / n
+    print(json.dumps({"case": args.case, "ms_per_call": round(s * 1e3, 3),
+                      "TFLOPs": round(2.0 * M * out * in_ / s / 1e12, 2),
+                      "h2d_bytes": M * out * 4, "d2h_bytes": M * in_ * 4}))
+    ctx.close()
+
+
 def run_case(args):
     """One small named case for profiler captures: a few launches of one decode kernel on
     distinct weight copies (more than L2 in total), nothing else.
@@ -868,6 +893,8 @@ def main():
     args = ap.parse_args()
     if args.case and args.case.startswith("layer"):
         return run_layer(args)
+    if args.case and args.case.startswith("dx"):
+        return run_dx(args)
     if args.case:
         return run_case(args)
     args.warmup = max(args.warmup, 3)
