@@ -799,8 +799,11 @@ int32_t host_roundtrip(rstq_ctx* ctx, int dev, const void* x, int64_t x_bytes, v
     char* hp = (char*)ds.pinned;
     char* dp = (char*)ds.io_dev;
     memcpy(hp, x, (size_t)x_bytes);
-    RSTQ_CUDA(cudaMemcpyAsync(dp, hp, (size_t)x_bytes, cudaMemcpyHostToDevice, ds.stream));
-    if ((rc = body((void*)dp, (void*)(dp + xa))) != RSTQ_OK) return rc;
+    // Small activations are read by the first kernel straight from the pinned host copy (unified
+    // addressing makes it device-visible): one PCIe round trip instead of a copy engine launch.
+    const bool direct = x_bytes <= 256 * 1024;
+    if (!direct) RSTQ_CUDA(cudaMemcpyAsync(dp, hp, (size_t)x_bytes, cudaMemcpyHostToDevice, ds.stream));
+    if ((rc = body(direct ? (void*)hp : (void*)dp, (void*)(dp + xa))) != RSTQ_OK) return rc;
     RSTQ_CUDA(cudaMemcpyAsync(hp + xa, dp + xa, (size_t)y_bytes, cudaMemcpyDeviceToHost, ds.stream));
     RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
     memcpy(y, hp + xa, (size_t)y_bytes);
