@@ -181,7 +181,8 @@ def tp_group(ctx, dist, world, rank, payload_bytes):
 
 
 def run_layer(args):
-    """--case layer:<bits>: the seven projections of a Llama-7B-style decoder layer at M = 1 (q, k, v,
+    """--case layer70:<bits>: the three MLP projections at the 70B-class shapes (8192 <-> 28672).
+    --case layer:<bits>: the seven projections of a Llama-7B-style decoder layer at M = 1 (q, k, v,
     o 4096x4096; gate, up 11008x4096; down 4096x11008), tensor-parallel over the ranks of the launch:
     q, k, v, gate, up split by columns, o and down by rows (strong scaling: the layer is fixed).
     Prints one JSON line with microseconds per layer and weight-stream GB/s."""
@@ -200,9 +201,13 @@ def run_layer(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = Context((f"cuda:{local_rank}",))
     fmt = L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0
-    H, F = 4096, 11008
-    projs = [("q", H, H, "column"), ("k", H, H, "column"), ("v", H, H, "column"), ("o", H, H, "row"),
-             ("gate", F, H, "column"), ("up", F, H, "column"), ("down", H, F, "row")]
+    if args.case.startswith("layer70"):     # the 70B-class MLP shapes of BASELINE configs[4]
+        H, F = 8192, 28672
+        projs = [("gate", F, H, "column"), ("up", F, H, "column"), ("down", H, F, "row")]
+    else:
+        H, F = 4096, 11008
+        projs = [("q", H, H, "column"), ("k", H, H, "column"), ("v", H, H, "column"), ("o", H, H, "row"),
+                 ("gate", F, H, "column"), ("up", F, H, "column"), ("down", H, F, "row")]
     rng = np.random.default_rng(1)
     L2 = ctx.device_info()["l2_bytes"]
     per_layer = sum(stream_bytes(o, i, bits) for _, o, i, _ in projs)
