@@ -444,6 +444,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         // ---------------- producer: one lane streams the CTA's byte range ----------------
         if (lane == 0) {
             const uint8_t* src = p.w + (g0 * nb + b_start) * UNIT;
+            const uint64_t pol = l2_evict_first_policy();  // the weights pass through L2 once
             int b = b_start, left = total, s = 0, issued = 0;
             uint32_t ph = 0;
             bool ok = true;
@@ -454,7 +455,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 if (!ok) break;
                 const uint32_t bytes = (uint32_t)(n * UNIT);
                 mbar_expect_tx(full0 + 8 * s, bytes);
-                bulk_copy_g2s(smem_u32(smem) + (uint32_t)s * CHUNK_BYTES, src, bytes, full0 + 8 * s);
+                bulk_copy_g2s_hint(smem_u32(smem) + (uint32_t)s * CHUNK_BYTES, src, bytes, full0 + 8 * s, pol);
                 src += bytes;
                 b += n;
                 if (b == nb) b = 0;

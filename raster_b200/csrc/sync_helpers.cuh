@@ -102,4 +102,19 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
+// The same copy with an L2 eviction hint: data that is read once (a weight stream) is marked
+// evict-first so that it does not push the small, reused buffers (activations, scratch) out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_copy_g2s_hint(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
+                                                   uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            dst),
+        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
 }  // namespace rstq
