@@ -349,6 +349,18 @@ def run_tp(args, world, rank, local_rank):
     t0 = time.perf_counter()
     ms = timed(g_tp.replay, args.steps, args.warmup)
     t1 = time.perf_counter()
+    # same step for another 0.6 s, untimed, on every rank (the exchange needs them all): the timed
+    # steps are shorter than one period of the clock sampler
+    extra = torch.tensor([0], device="cuda")
+    while True:
+        for _ in range(50):
+            g_tp.replay()
+        ctx.sync()
+        extra.fill_(1 if (rank == 0 and time.perf_counter() - t1 >= 0.6) else 0)
+        dist.broadcast(extra, 0)
+        if int(extra.item()):
+            break
+    t1 = time.perf_counter()
     clocks = sampler.stop(t0, t1) if rank == 0 else None
     ms_per_step = ms / args.steps
     value = per_pass * R * world / (ms_per_step * 1e-3) / 1e9
@@ -572,6 +584,14 @@ def run_ours(args):
     barrier()
     t1 = time.perf_counter()
     ms = e0.elapsed_ms(e1)
+    # the timed steps last a few milliseconds, less than one period of the clock sampler: keep the
+    # same step running for another 0.6 s (untimed) so the clock record is of this load
+    if rank == 0:
+        while time.perf_counter() - t1 < 0.6:
+            for _ in range(50):
+                g_op.replay()
+            ctx.sync()
+        t1 = time.perf_counter()
     if dist is not None:
         import torch
         t = torch.tensor([ms], device="cuda")
@@ -681,7 +701,8 @@ def run_ours(args):
                                 % (per_pass * R >> 20, info["l2_bytes"] >> 20),
                        "parallelism": "column-shard per GPU (tp%d)" % world,
                        "frac_of_measured_hbm": round(value / world / hbm_peak, 4),
-                       "frac_of_nominal_8TBs": round(value / world / 8000.0, 4)},
+                       "frac_of_nominal_8TBs": round(value / world / 8000.0, 4),
+                       "clocks_window": "the timed steps plus 0.6 s more of the same step"},
             "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu,
             "gpu_launches": kernels_per_step * args.steps, "clocks": clocks, "detail": detail,
         }
