@@ -107,3 +107,22 @@ def test_gemm_extreme_magnitudes_stay_finite(ctx):
     assert np.isfinite(y).all() and not y[0].any()
     assert relerr(y, ref) <= 1e-3
     bw.free()
+
+
+def test_gemm_shared_memory_variant_still_agrees(ctx):
+    """RSTQ_TUNE_GEMM_KERNEL = 1 selects the first version of the kernel (weights dequantized into
+    swizzled shared memory, one MMA issuer); it stays as the comparison point and must stay right."""
+    out, in_, M = 512, 1024, 96
+    w = synth.normal(21, out * in_, 0.02)
+    wq, ws = orc.quantize_weight(w, 8)
+    x = synth.normal(22, M * in_)
+    bw = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q8_0, L.LAYOUT_ROWMAJOR)
+    ref = orc.matmul_dq_f64(wq, ws, 1, x, M, in_, out).reshape(M, out)
+    try:
+        ctx.tune(L.TUNE_GEMM_KERNEL, 1)
+        y1 = ctx.qmatmul_host(bw, x, M, L.F32, L.MODE_F)
+    finally:
+        ctx.tune(L.TUNE_GEMM_KERNEL, 0)
+    y0 = ctx.qmatmul_host(bw, x, M, L.F32, L.MODE_F)
+    assert relerr(y1, ref) <= 1e-3 and relerr(y0, ref) <= 1e-3
+    bw.free()
