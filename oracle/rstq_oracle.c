@@ -586,3 +586,185 @@ ORC_API void orc_gelu_mul(const float* gate, const float* up, float* out, int64_
 ORC_API void orc_residual_add(const float* a, const float* b, float* out, int64_t n) {
     for (int64_t i = 0; i < n; ++i) out[i] = a[i] + b[i];
 }
+
+/* ------------------------------------------------------------------------
+ * K-quant super-block formats (the reference's own layout, not GGUF bytes).
+ *
+ * Q4_K weight codec: src/raster/compiler/backend/cpu/quant.clj:85-150.
+ * Super-block = 256 elements = 8 sub-blocks of 32.  Per sub-block a = (max-min)/15
+ * and b = min; per super-block dav = max(a)/63, dbv = max|b|/31 (doubles; the stored
+ * da, db are their float roundings); aq = clamp(jround(a/dav), 0, 63),
+ * bq = clamp(jround(b/dbv), -32, 31); weights are quantized against the QUANTIZED
+ * sub scale a' = dav*aq and min b' = dbv*bq: q = clamp(jround((w - b')/a'), 0, 15);
+ * byte k of a sub-block = q(w[k]) | q(w[k+16]) << 4.
+ * ---------------------------------------------------------------------- */
+ORC_API void orc_quantize_weight_q4k(const float* w, int64_t len, uint8_t* wq, float* da, float* db,
+                                     int8_t* aq, int8_t* bq) {
+    const int64_t nsb = len / 256;
+    for (int64_t sb = 0; sb < nsb; ++sb) {
+        const float* s = w + sb * 256;
+        double as[8], bs[8];
+        for (int j = 0; j < 8; ++j) {
+            double lo = (double)s[j * 32], hi = lo;
+            for (int i = 1; i < 32; ++i) {
+                double v = (double)s[j * 32 + i];
+                if (v < lo) lo = v;
+                if (v > hi) hi = v;
+            }
+            as[j] = (hi - lo) / 15.0;
+            bs[j] = lo;
+        }
+        double amax = 0.0, bmax = 0.0;
+        for (int j = 0; j < 8; ++j) {
+            if (as[j] > amax) amax = as[j];
+            if (fabs(bs[j]) > bmax) bmax = fabs(bs[j]);
+        }
+        const double dav = amax / 63.0, dbv = bmax / 31.0;
+        const double ida = dav == 0.0 ? 0.0 : 1.0 / dav, idb = dbv == 0.0 ? 0.0 : 1.0 / dbv;
+        da[sb] = (float)dav;
+        db[sb] = (float)dbv;
+        for (int j = 0; j < 8; ++j) {
+            const int64_t aqj = clampi(orc_jround(as[j] * ida), 0, 63);
+            const int64_t bqj = clampi(orc_jround(bs[j] * idb), -32, 31);
+            const double a1 = dav * (double)aqj, b1 = dbv * (double)bqj;
+            const double ia1 = a1 == 0.0 ? 0.0 : 1.0 / a1;
+            aq[sb * 8 + j] = (int8_t)aqj;
+            bq[sb * 8 + j] = (int8_t)bqj;
+            for (int k = 0; k < 16; ++k) {
+                const int64_t q0 = clampi(orc_jround(((double)s[j * 32 + k] - b1) * ia1), 0, 15);
+                const int64_t q1 = clampi(orc_jround(((double)s[j * 32 + k + 16] - b1) * ia1), 0, 15);
+                wq[(sb * 256 + j * 32) / 2 + k] = (uint8_t)(q0 | (q1 << 4));
+            }
+        }
+    }
+}
+
+/* dequant-q4k, quant.clj:152-170: x = (da*aq)*q + (db*bq), products and sum in double from the
+ * stored floats, rounded to float once. */
+ORC_API void orc_dequant_q4k(const uint8_t* wq, const float* da, const float* db, const int8_t* aq,
+                             const int8_t* bq, int64_t len, float* out) {
+    for (int64_t sub = 0; sub < len / 32; ++sub) {
+        const double a1 = (double)da[sub / 8] * (double)aq[sub], b1 = (double)db[sub / 8] * (double)bq[sub];
+        for (int k = 0; k < 16; ++k) {
+            const uint8_t bv = wq[sub * 16 + k];
+            out[sub * 32 + k] = (float)(a1 * (double)(bv & 0xF) + b1);
+            out[sub * 32 + k + 16] = (float)(a1 * (double)(bv >> 4) + b1);
+        }
+    }
+}
+
+/* quantize-act-q8k, quant.clj:172-193 (and its two-phase device form quant-act-q8k-gpu!,
+ * src/raster/quant/kernels_k.clj:93-134, which yields the same codes): one row of `in` floats,
+ * per 256 super-block d = max|x|/127, xq = clamp(jround(x/d), -127, 127), xs = (float)d, and
+ * bsums = the sum of the codes per sub-block of `sub` elements (32 for Q4_K, 16 for Q6_K). */
+ORC_API void orc_quantize_act_q8k(const float* x, int64_t in, int sub, int8_t* xq, float* xs, int32_t* bsums) {
+    const int per = 256 / sub;
+    for (int64_t sb = 0; sb < in / 256; ++sb) {
+        const float* s = x + sb * 256;
+        double mx = 0.0;
+        for (int i = 0; i < 256; ++i) {
+            const double a = (double)fabsf(s[i]);
+            if (a > mx) mx = a;
+        }
+        const double d = mx / 127.0, id = d == 0.0 ? 0.0 : 1.0 / d;
+        xs[sb] = (float)d;
+        for (int j = 0; j < per; ++j) {
+            int32_t t = 0;
+            for (int k = 0; k < sub; ++k) {
+                const int64_t q = clampi(orc_jround((double)s[j * sub + k] * id), -127, 127);
+                xq[sb * 256 + j * sub + k] = (int8_t)q;
+                t += (int32_t)q;
+            }
+            bsums[sb * per + j] = t;
+        }
+    }
+}
+
+/* qmatmul-q4k-composable!, src/raster/quant/kernels_k.clj:15-48 (row dot = q4k-q8k-dot,
+ * quant.clj:195-220): y[o] = sum_sb dact[sb] * sum_j ((da*aq_j) * dp_j + (db*bq_j) * bsum_j), dp_j the
+ * nibble x int8 dot of one 32-element sub-block, everything after the integer dot in double;
+ * y rounded to float once.  y64 (may be null) receives the unrounded sums. */
+ORC_API void orc_qmatmul_q4k(const int8_t* xq, const float* xs, const int32_t* bsums, const uint8_t* wq,
+                             const float* da, const float* db, const int8_t* aq, const int8_t* bq, float* y,
+                             double* y64, int64_t in, int64_t out, int64_t o_start, int64_t o_count) {
+    (void)out;
+    const int64_t nsb = in / 256, nsub = in / 32, wrow = in / 2;
+    for (int64_t oi = 0; oi < o_count; ++oi) {
+        const int64_t o = o_start + oi;
+        double acc = 0.0;
+        for (int64_t sb = 0; sb < nsb; ++sb) {
+            const double dav = (double)da[o * nsb + sb], dbv = (double)db[o * nsb + sb], dact = (double)xs[sb];
+            double ssum = 0.0;
+            for (int j = 0; j < 8; ++j) {
+                const int64_t sidx = sb * 8 + j, base = sb * 256 + j * 32;
+                const double aj = dav * (double)aq[o * nsub + sidx], bj = dbv * (double)bq[o * nsub + sidx];
+                const int64_t dp = orc_wi8_dot_q4(wq, o * wrow + base / 2, xq, base);
+                ssum = ssum + aj * (double)dp + bj * (double)bsums[sidx];
+            }
+            acc += dact * ssum;
+        }
+        if (y) y[o] = (float)acc;
+        if (y64) y64[o] = acc;
+    }
+}
+
+/* Q6_K weight codec: quant.clj:222-262.  256 = 16 sub-blocks of 16; per sub-block a = max|w|/32,
+ * per super-block dv = max(a)/127 (stored as float), sc = clamp(jround(a/dv), 0, 127),
+ * q = clamp(jround(w/(dv*sc)) + 32, 0, 63), one unsigned 6-bit code per byte. */
+ORC_API void orc_quantize_weight_q6k(const float* w, int64_t len, uint8_t* wq, int8_t* sc, float* ds) {
+    for (int64_t sb = 0; sb < len / 256; ++sb) {
+        const float* s = w + sb * 256;
+        double as[16], amax = 0.0;
+        for (int j = 0; j < 16; ++j) {
+            double mx = 0.0;
+            for (int i = 0; i < 16; ++i) {
+                const double a = (double)fabsf(s[j * 16 + i]);
+                if (a > mx) mx = a;
+            }
+            as[j] = mx / 32.0;
+            if (as[j] > amax) amax = as[j];
+        }
+        const double dv = amax / 127.0, idv = dv == 0.0 ? 0.0 : 1.0 / dv;
+        ds[sb] = (float)dv;
+        for (int j = 0; j < 16; ++j) {
+            const int64_t scj = clampi(orc_jround(as[j] * idv), 0, 127);
+            const double a1 = dv * (double)scj, ia1 = a1 == 0.0 ? 0.0 : 1.0 / a1;
+            sc[sb * 16 + j] = (int8_t)scj;
+            for (int k = 0; k < 16; ++k)
+                wq[sb * 256 + j * 16 + k] = (uint8_t)clampi(orc_jround((double)s[j * 16 + k] * ia1) + 32, 0, 63);
+        }
+    }
+}
+
+/* dequant-q6k, quant.clj:264-278: x = (ds*sc)*(q - 32). */
+ORC_API void orc_dequant_q6k(const uint8_t* wq, const int8_t* sc, const float* ds, int64_t len, float* out) {
+    for (int64_t sub = 0; sub < len / 16; ++sub) {
+        const double a1 = (double)ds[sub / 16] * (double)sc[sub];
+        for (int k = 0; k < 16; ++k) out[sub * 16 + k] = (float)(a1 * (double)((int)wq[sub * 16 + k] - 32));
+    }
+}
+
+/* qmatmul-q6k-composable!, kernels_k.clj:50-79 (row dot = q6k-q8k-dot, quant.clj:280-304):
+ * y[o] = sum_sb ds*dact * sum_j sc_j * (dp_j - 32*bsum_j), 16-element sub-blocks. */
+ORC_API void orc_qmatmul_q6k(const int8_t* xq, const float* xs, const int32_t* bsums, const uint8_t* wq,
+                             const int8_t* sc, const float* ds, float* y, double* y64, int64_t in, int64_t out,
+                             int64_t o_start, int64_t o_count) {
+    (void)out;
+    const int64_t nsb = in / 256, nsub = in / 16;
+    for (int64_t oi = 0; oi < o_count; ++oi) {
+        const int64_t o = o_start + oi;
+        double acc = 0.0;
+        for (int64_t sb = 0; sb < nsb; ++sb) {
+            const double dv = (double)ds[o * nsb + sb], dact = (double)xs[sb];
+            double ssum = 0.0;
+            for (int j = 0; j < 16; ++j) {
+                const int64_t sidx = sb * 16 + j, base = sb * 256 + j * 16;
+                const int64_t dp = orc_wi8_dot(wq, o * in + base, xq, base, 16);
+                ssum += (double)sc[o * nsub + sidx] * (double)(dp - 32 * (int64_t)bsums[sidx]);
+            }
+            acc += dv * dact * ssum;
+        }
+        if (y) y[o] = (float)acc;
+        if (y64) y64[o] = acc;
+    }
+}

@@ -842,7 +842,40 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             }
             const float wdiv = p.wdiv;
             const int tokb = tok0 + cq * CPW;
-            if (f < p.out && p.ksplit > 1) {
+            if (p.ksplit == 1 && (p.out & 7) == 0) {
+                // Fast path: transpose the warp's 32-feature x CPW-token tile through shared memory
+                // (the B ring is idle: every MMA has completed) so that a lane stores eight
+                // consecutive features of one token with one 16-byte (bf16) or two (f32) stores,
+                // instead of one element per store.
+                constexpr int LD = 36;  // floats per token row of the staging tile (16-byte aligned rows)
+                float* tile = reinterpret_cast<float*>(smem) + dq * (CPW * LD);
+#pragma unroll
+                for (int j = 0; j < CPW; ++j) tile[j * LD + lane] = __uint_as_float(v[j]);
+                __syncwarp();
+                const int fg = (lane & 3) * 8;
+                const int64_t f0 = (int64_t)ft * 128 + sp * 32 + fg;
+#pragma unroll
+                for (int t0 = 0; t0 < CPW; t0 += 8) {
+                    const int t = t0 + (lane >> 2), tok = tokb + t;
+                    if (tok < p.M && f0 < p.out) {
+                        const float sc = wdiv * __ldg(p.rowscale + tok);
+                        const float4 a = *reinterpret_cast<const float4*>(tile + t * LD + fg);
+                        const float4 c = *reinterpret_cast<const float4*>(tile + t * LD + fg + 4);
+                        if (p.out_dtype == RSTQ_BF16) {
+                            uint4 o;
+                            o.x = pack_bf16x2(a.y * sc, a.x * sc);
+                            o.y = pack_bf16x2(a.w * sc, a.z * sc);
+                            o.z = pack_bf16x2(c.y * sc, c.x * sc);
+                            o.w = pack_bf16x2(c.w * sc, c.z * sc);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)tok * p.out + f0) = o;
+                        } else {
+                            float* y = reinterpret_cast<float*>(p.y) + (int64_t)tok * p.out + f0;
+                            *reinterpret_cast<float4*>(y) = make_float4(a.x * sc, a.y * sc, a.z * sc, a.w * sc);
+                            *reinterpret_cast<float4*>(y + 4) = make_float4(c.x * sc, c.y * sc, c.z * sc, c.w * sc);
+                        }
+                    }
+                }
+            } else if (f < p.out && p.ksplit > 1) {
                 // two K ranges add their halves into a zeroed f32 array: a + b in either order
                 float* y = p.acc32 + f;
 #pragma unroll
