@@ -861,6 +861,39 @@ def run_dx(args):
     ctx.close()
 
 
+def run_q4k(args):
+    """--case q4k:<out>:<in>:<M>: the Q4_K operator (q8_K quantizer + decode kernel + min-term GEMV) on
+    distinct weight copies (more than L2 in total), timed with CUDA events per call."""
+    from raster_b200 import Context
+    from raster_b200 import _lib as L
+    _, out, in_, M = args.case.split(":")
+    out, in_, M = int(out), int(in_), int(M)
+    rng = np.random.default_rng(0)
+    ctx = Context(("cuda:0",))
+    enc = {"wq": rng.integers(0, 256, out * in_ // 2, dtype=np.uint8),
+           "da": (np.abs(rng.standard_normal(out * in_ // 256)) * 1e-3).astype(np.float32),
+           "db": (np.abs(rng.standard_normal(out * in_ // 256)) * 1e-3).astype(np.float32),
+           "aq": rng.integers(0, 64, out * in_ // 32, dtype=np.int8),
+           "bq": rng.integers(-32, 32, out * in_ // 32, dtype=np.int8)}
+    w0 = ctx.bind_weight_q4k(enc, out, in_)
+    R = max(2, -(-int(1.2 * ctx.device_info()["l2_bytes"]) // w0.device_bytes))
+    ws = [w0] + [w0.clone() for _ in range(R - 1)]
+    bx, by = ctx.array_to_buffer(rng.standard_normal(M * in_).astype(np.float32)), ctx.make_buffer(M * out, np.float32)
+    e0, e1 = ctx.event(), ctx.event()
+    n0 = ctx.launch_count()
+    for it in range(3):
+        e0.record()
+        for w in ws:
+            ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+        e1.record()
+        ctx.sync()
+    us = e0.elapsed_ms(e1) * 1e3 / R
+    print(json.dumps({"case": args.case, "calls": 3 * R, "kernels_per_call": (ctx.launch_count() - n0) // (3 * R),
+                      "us_per_call": round(us, 2), "device_GBs": round(w0.device_bytes / us / 1e3, 1),
+                      "reference_format_GBs": round(w0.stream_bytes / us / 1e3, 1)}))
+    ctx.close()
+
+
 def run_case(args):
     """One small named case for profiler captures: a few launches of one decode kernel on
     distinct weight copies (more than L2 in total), nothing else.
@@ -921,6 +954,8 @@ def main():
         return run_layer(args)
     if args.case and args.case.startswith("dx"):
         return run_dx(args)
+    if args.case and args.case.startswith("q4k"):
+        return run_q4k(args)
     if args.case:
         return run_case(args)
     args.warmup = max(args.warmup, 3)

@@ -146,6 +146,18 @@ RSTQ_API int32_t rstq_weight_bind_shard(rstq_ctx* ctx, rstq_weight** w, const vo
                                         const float* scales, int32_t dev, int64_t out, int64_t in,
                                         int32_t format, int32_t layout, int32_t split,
                                         int32_t rank, int32_t nranks);
+/* Q4_K, the reference's asymmetric 4-bit super-block format, from the arrays quantize-weight-q4k
+ * makes (src/raster/compiler/backend/cpu/quant.clj:85-150): wq nibbles [out, in/2] (element k low,
+ * k+16 high per 32-element sub-block), da / db f32 [out, in/256], aq (0..63) / bq (-32..31) int8
+ * [out, in/32]; in % 256 == 0.  On the device the sub-block scales da*aq ride the 4-bit units of
+ * the decode kernel and the minima db*bq are a separate f32 [out, in/32] array.  Such a weight is
+ * used with rstq_qmatmul (f32 activations, MODE_A8: q8_K quantizer + qmatmul-q4k, the `:apply` of
+ * the registered :q4_K format, src/raster/quant/core.clj:57-66) and rstq_qmatmul_prequant (xs per
+ * super-block [M, in/256], xsum = bsums [M, in/32]: qmatmul-q4k-dp4a!,
+ * src/raster/quant/kernels_k.clj:195-237).  Not sharded, no tensor-core route, no MODE_F. */
+RSTQ_API int32_t rstq_weight_bind_q4k(rstq_ctx* ctx, rstq_weight** w, const void* wq, const float* da,
+                                      const float* db, const int8_t* aq, const int8_t* bq, int32_t dev,
+                                      int64_t out, int64_t in);
 /* Second device copy of a bound weight at a distinct address (cold-cache measurement). */
 RSTQ_API int32_t rstq_weight_clone(rstq_weight* src, rstq_weight** w);
 RSTQ_API int32_t rstq_weight_free(rstq_weight* w);
@@ -161,6 +173,15 @@ RSTQ_API int32_t rstq_weight_info(rstq_weight* w, int64_t* out6);
  *      Bit-exact with the reference (double-precision scale and rounding). */
 RSTQ_API int32_t rstq_quant_act_i8(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rstq_buf* xs,
                                    rstq_buf* xsum, int64_t M, int64_t in);
+
+/* q8_K activation quantizer, quant-act-q8k-gpu! (src/raster/quant/kernels_k.clj:93-134; CPU form
+ * quantize-act-q8k, src/raster/compiler/backend/cpu/quant.clj:172-193): per 256-element
+ * super-block d = max|x|/127, codes = round-half-up(x/d); x f32 [rows, in], xq int8 [rows, in]
+ * (read as int32 words it is the reference's `xp`), xs f32 [rows, in/256], bsums int32
+ * [rows, in/sub] = code sums per sub-block of `sub` = 32 (Q4_K) or 16 (Q6_K) elements.
+ * Bit-exact with the reference.  One launch, no `submax` scratch. */
+RSTQ_API int32_t rstq_quant_act_q8k(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rstq_buf* xs, rstq_buf* bsums,
+                                    int64_t rows, int64_t in, int32_t sub);
 
 /* ---- the matmul on device-resident data.
  * rstq_qmatmul: y[M, out] = W . x[M, in]; x is act_dtype, y is out_dtype.

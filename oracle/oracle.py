@@ -287,6 +287,83 @@ def residual_add(a, b):
     return _map2("orc_residual_add", a, b)
 
 
+# ---- K-quant super-block formats (the reference's registered built-ins) ---------------------
+def quantize_weight_q4k(w):
+    """`quantize-weight-q4k` over a flat f32 array (len % 256 == 0) -> dict(wq, da, db, aq, bq)."""
+    w = _f32(w).ravel()
+    assert w.size % 256 == 0
+    e = dict(wq=np.empty(w.size // 2, np.uint8), da=np.empty(w.size // 256, np.float32),
+             db=np.empty(w.size // 256, np.float32), aq=np.empty(w.size // 32, np.int8),
+             bq=np.empty(w.size // 32, np.int8))
+    lib().orc_quantize_weight_q4k(_ptr(w), _i64(w.size), _ptr(e["wq"]), _ptr(e["da"]), _ptr(e["db"]),
+                                  _ptr(e["aq"]), _ptr(e["bq"]))
+    return e
+
+
+def dequant_q4k(e):
+    n = e["aq"].size * 32
+    out = np.empty(n, np.float32)
+    lib().orc_dequant_q4k(_ptr(e["wq"]), _ptr(e["da"]), _ptr(e["db"]), _ptr(e["aq"]), _ptr(e["bq"]), _i64(n),
+                          _ptr(out))
+    return out
+
+
+def quantize_act_q8k(x, in_: int, sub: int = 32):
+    """`quantize-act-q8k` of one row: (xq int8[in], xs f32[in/256], bsums i32[in/sub])."""
+    x = _f32(x).ravel()
+    assert x.size == in_ and in_ % 256 == 0 and sub in (16, 32)
+    xq = np.empty(in_, np.int8)
+    xs = np.empty(in_ // 256, np.float32)
+    bsums = np.empty(in_ // sub, np.int32)
+    lib().orc_quantize_act_q8k(_ptr(x), _i64(in_), sub, _ptr(xq), _ptr(xs), _ptr(bsums))
+    return xq, xs, bsums
+
+
+def qmatmul_q4k(xq, xs, bsums, e, in_: int, out: int, o_start: int = 0, o_count=None):
+    """`qmatmul-q4k-composable!` for one activation row -> (y f32[out], y f64[out])."""
+    o_count = out - o_start if o_count is None else o_count
+    y = np.zeros(out, np.float32)
+    y64 = np.zeros(out, np.float64)
+    lib().orc_qmatmul_q4k(_ptr(xq), _ptr(xs), _ptr(bsums), _ptr(e["wq"]), _ptr(e["da"]), _ptr(e["db"]),
+                          _ptr(e["aq"]), _ptr(e["bq"]), _ptr(y), _ptr(y64), _i64(in_), _i64(out), _i64(o_start),
+                          _i64(o_count))
+    return y, y64
+
+
+def quantize_weight_q6k(w):
+    w = _f32(w).ravel()
+    assert w.size % 256 == 0
+    e = dict(wq=np.empty(w.size, np.uint8), sc=np.empty(w.size // 16, np.int8), ds=np.empty(w.size // 256, np.float32))
+    lib().orc_quantize_weight_q6k(_ptr(w), _i64(w.size), _ptr(e["wq"]), _ptr(e["sc"]), _ptr(e["ds"]))
+    return e
+
+
+def dequant_q6k(e):
+    n = e["wq"].size
+    out = np.empty(n, np.float32)
+    lib().orc_dequant_q6k(_ptr(e["wq"]), _ptr(e["sc"]), _ptr(e["ds"]), _i64(n), _ptr(out))
+    return out
+
+
+def qmatmul_q6k(xq, xs, bsums, e, in_: int, out: int, o_start: int = 0, o_count=None):
+    o_count = out - o_start if o_count is None else o_count
+    y = np.zeros(out, np.float32)
+    y64 = np.zeros(out, np.float64)
+    lib().orc_qmatmul_q6k(_ptr(xq), _ptr(xs), _ptr(bsums), _ptr(e["wq"]), _ptr(e["sc"]), _ptr(e["ds"]), _ptr(y),
+                          _ptr(y64), _i64(in_), _i64(out), _i64(o_start), _i64(o_count))
+    return y, y64
+
+
+def qmatrix_matmul(fmt: str, e, x, rows: int, cols: int):
+    """`raster.quant.core/matmul` for a registered format (src/raster/quant/core.clj:49-75):
+    quantize the activation row to q8_K, then the format's GEMV."""
+    if fmt == "q4_K":
+        return qmatmul_q4k(*quantize_act_q8k(x, cols, 32), e, cols, rows)[0]
+    if fmt == "q6_K":
+        return qmatmul_q6k(*quantize_act_q8k(x, cols, 16), e, cols, rows)[0]
+    raise KeyError(f"unknown quant format {fmt}")
+
+
 def cpk() -> C.CDLL:
     global _cpk
     if _cpk is None:

@@ -34,10 +34,12 @@ SIGNATURES = {
     "rstq_stream_set": [vp, i32, vp],
     "rstq_weight_bind": [vp, pp, vp, vp, i32, i64, i64, i32, i32],
     "rstq_weight_bind_shard": [vp, pp, vp, vp, i32, i64, i64, i32, i32, i32, i32, i32],
+    "rstq_weight_bind_q4k": [vp, pp, vp, vp, vp, vp, vp, i32, i64, i64],
     "rstq_weight_clone": [vp, pp],
     "rstq_weight_free": [vp],
     "rstq_weight_info": [vp, C.POINTER(i64)],
     "rstq_quant_act_i8": [vp, vp, vp, vp, vp, i64, i64],
+    "rstq_quant_act_q8k": [vp, vp, vp, vp, vp, i64, i64, i32],
     "rstq_qmatmul": [vp, vp, vp, vp, i64, i32, i32, i32],
     "rstq_qmatmul_prequant": [vp, vp, vp, vp, vp, vp, i64],
     "rstq_qmatmul_prequant_noalloc": [vp, vp, vp, vp, vp, vp, i64],

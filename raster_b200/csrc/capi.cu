@@ -6,6 +6,7 @@
 #include <string.h>
 
 #include <new>
+#include <vector>
 
 #include "internal.h"
 
@@ -135,6 +136,14 @@ static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int6
     return launch_gemv_f(ctx, ctx->devs[w->dev], a);
 }
 
+// Q4_K: decode kernel over the sub-block scales (zero point 0), then the min term added to y.
+static int32_t run_q4k(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs32, const int32_t* bsums,
+                       float* y, int64_t M) {
+    int32_t rc = run_a8(ctx, w, xq, xs32, bsums, y, M);
+    if (rc != RSTQ_OK) return rc;
+    return launch_q4k_min(ctx, ctx->devs[w->dev], w->mins, xs32, bsums, y, M, w->nb, w->out);
+}
+
 // scratch of the tensor-core path: [x16: M*in halves][rowscale: M floats][acc: M*out f32, only for
 // calls small enough to be split along K]
 static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, int64_t out, void** x16, float** rowscale,
@@ -152,6 +161,19 @@ static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, int64_t out,
 int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M, int act_dtype,
                       int out_dtype, int mode, const TpFuse* tp) {
     DeviceState& ds = ctx->devs[w->dev];
+    if (w->mins) {
+        // Q4_K: the one arithmetic the reference has for it -- q8_K activations, integer sub-block
+        // dots, scale / min fold (src/raster/quant/core.clj:57-66) -- at any M, on the decode kernel.
+        RSTQ_REQUIRE(mode == RSTQ_MODE_A8 && act_dtype == RSTQ_F32 && out_dtype == RSTQ_F32, RSTQ_E_INVALID,
+                     "a Q4_K weight takes f32 activations in MODE_A8 and writes f32");
+        RSTQ_REQUIRE(!tp, RSTQ_E_INVALID, "Q4_K weights are not sharded");
+        ActScratch s;
+        int32_t rc = act_scratch(ds, M, w->in, &s);
+        if (rc != RSTQ_OK) return rc;
+        rc = launch_quant_act_q8k(ctx, ds, (const float*)x, s.xq, nullptr, s.xs, s.xsum, M, w->in, 32);
+        if (rc != RSTQ_OK) return rc;
+        return run_q4k(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M);
+    }
     // Prefill shapes go to the tensor-core GEMM (fp16 operands, results within 1e-3 of the
     // reference).  A8 keeps its exact integer path up to M = 63: callers that chose the
     // quantized-activation arithmetic get it bit-faithfully at decode and small-batch sizes.
@@ -613,6 +635,39 @@ int32_t rstq_weight_bind_shard(rstq_ctx* ctx, rstq_weight** w, const void* codes
     return bind_impl(ctx, w, codes, scales, dev, out, in, format, layout, split, rank, nranks);
 }
 
+int32_t rstq_weight_bind_q4k(rstq_ctx* ctx, rstq_weight** wout, const void* wq, const float* da, const float* db,
+                             const int8_t* aq, const int8_t* bq, int32_t dev, int64_t out, int64_t in) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(wout && wq && da && db && aq && bq, RSTQ_E_INVALID, "null argument");
+    *wout = nullptr;
+    RSTQ_REQUIRE(out >= 1 && in >= 256 && in % 256 == 0, RSTQ_E_SHAPE,
+                 "in = %lld must be a positive multiple of 256 and out = %lld >= 1", (long long)in, (long long)out);
+    const int64_t nb = in / 32, n = out * nb;
+    // per-sub-block scale da*aq and min db*bq: the products the reference forms (in double) before
+    // it multiplies by the integer dot and the sub-block sum, rounded to f32 once
+    std::vector<float> a((size_t)n), b((size_t)n);
+    for (int64_t i = 0; i < n; ++i) {
+        a[(size_t)i] = (float)((double)da[i >> 3] * (double)aq[i]);
+        b[(size_t)i] = (float)((double)db[i >> 3] * (double)bq[i]);
+    }
+    rstq_weight* w = nullptr;
+    int32_t rc = bind_impl(ctx, &w, wq, a.data(), dev, out, in, RSTQ_FMT_Q4_0, RSTQ_LAYOUT_ROWMAJOR,
+                           RSTQ_SPLIT_NONE, 0, 1);
+    if (rc != RSTQ_OK) return rc;
+    w->zp = 0;  // codes are 0 .. 15 as they stand; the offset is the min term
+    DeviceState& ds = ctx->devs[dev];
+    cudaError_t e = cudaMalloc((void**)&w->mins, (size_t)n * 4);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->mins, b.data(), (size_t)n * 4, cudaMemcpyHostToDevice, ds.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ds.stream);
+    if (e != cudaSuccess) {
+        w->mins = nullptr;
+        rstq_weight_free(w);
+        return cuda_fail(e, "Q4_K bind", __FILE__, __LINE__);
+    }
+    *wout = w;
+    return RSTQ_OK;
+}
+
 int32_t rstq_weight_clone(rstq_weight* src, rstq_weight** wout) {
     RSTQ_REQUIRE(wout, RSTQ_E_INVALID, "null argument");
     *wout = nullptr;
@@ -625,13 +680,21 @@ int32_t rstq_weight_clone(rstq_weight* src, rstq_weight** wout) {
     rstq_weight* w = new (std::nothrow) rstq_weight(*src);
     RSTQ_REQUIRE(w, RSTQ_E_OOM, "out of host memory");
     w->data = nullptr;
+    w->raw_codes = nullptr;
+    w->raw_scales = nullptr;
+    w->mins = nullptr;
+    const size_t min_bytes = (size_t)(src->out * src->nb * 4);
     cudaError_t e = cudaMalloc((void**)&w->data, (size_t)w->data_bytes);
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(w->data, src->data, (size_t)w->data_bytes, cudaMemcpyDeviceToDevice,
                             ds.stream);
+    if (e == cudaSuccess && src->mins) e = cudaMalloc((void**)&w->mins, min_bytes);
+    if (e == cudaSuccess && src->mins)
+        e = cudaMemcpyAsync(w->mins, src->mins, min_bytes, cudaMemcpyDeviceToDevice, ds.stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ds.stream);
     if (e != cudaSuccess) {
         if (w->data) cudaFree(w->data);
+        if (w->mins) cudaFree(w->mins);
         delete w;
         return cuda_fail(e, "weight clone", __FILE__, __LINE__);
     }
@@ -648,6 +711,7 @@ int32_t rstq_weight_free(rstq_weight* w) {
     cudaFree(w->data);
     if (w->raw_codes) cudaFree(w->raw_codes);
     if (w->raw_scales) cudaFree(w->raw_scales);
+    if (w->mins) cudaFree(w->mins);
     cudaGetLastError();
     w->magic = 0;
     delete w;
@@ -660,8 +724,10 @@ int32_t rstq_weight_info(rstq_weight* w, int64_t* out6) {
     out6[0] = w->out;
     out6[1] = w->in;
     out6[2] = w->bits;
-    out6[3] = w->data_bytes;
-    out6[4] = w->out * w->in * w->bits / 8 + w->out * w->nb * 4;
+    out6[3] = w->data_bytes + (w->mins ? w->out * w->nb * 4 : 0);
+    // Q4_K as the reference stores it: nibbles, da + db per super-block, aq + bq per sub-block
+    out6[4] = w->mins ? w->out * w->in / 2 + w->out * (w->in / 256) * 8 + w->out * w->nb * 2
+                      : w->out * w->in * w->bits / 8 + w->out * w->nb * 4;
     out6[5] = w->dev;
     return RSTQ_OK;
 }
@@ -693,6 +759,24 @@ int32_t rstq_quant_act_i8(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rstq_buf* xs
                                (float*)xs->ptr, xsum ? (int32_t*)xsum->ptr : nullptr, M, in);
 }
 
+int32_t rstq_quant_act_q8k(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rstq_buf* xs, rstq_buf* bsums, int64_t rows,
+                           int64_t in, int32_t sub) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(rows >= 1 && in >= 256 && in % 256 == 0, RSTQ_E_SHAPE,
+                 "rows = %lld, in = %lld (in must be a multiple of 256)", (long long)rows, (long long)in);
+    RSTQ_REQUIRE(sub == 16 || sub == 32, RSTQ_E_INVALID, "sub-block of %d elements (16 or 32)", sub);
+    int32_t rc;
+    if ((rc = need_bytes(x, rows * in * 4, "x")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(xq, rows * in, "xq")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(xs, rows * (in / 256) * 4, "xs")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(bsums, rows * (in / sub) * 4, "bsums")) != RSTQ_OK) return rc;
+    RSTQ_REQUIRE(x->dev == xq->dev && x->dev == xs->dev && x->dev == bsums->dev, RSTQ_E_DEVICE,
+                 "buffers live on different devices");
+    if ((rc = use_dev(ctx, x->dev)) != RSTQ_OK) return rc;
+    return launch_quant_act_q8k(ctx, ctx->devs[x->dev], (const float*)x->ptr, (int8_t*)xq->ptr, (float*)xs->ptr,
+                                nullptr, (int32_t*)bsums->ptr, rows, in, sub);
+}
+
 int32_t rstq_qmatmul(rstq_ctx* ctx, rstq_weight* w, rstq_buf* x, rstq_buf* y, int64_t M,
                      int32_t act_dtype, int32_t out_dtype, int32_t mode) {
     CHECK_CTX(ctx);
@@ -716,6 +800,24 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
     RSTQ_REQUIRE(ok_w(w) && w->ctx == ctx, RSTQ_E_INVALID, "invalid weight handle");
     RSTQ_REQUIRE(M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)M);
     int32_t rc;
+    if (w->mins) {
+        // qmatmul-q4k-dp4a! (src/raster/quant/kernels_k.clj:195-237): q8_K activations, xs per
+        // super-block, bsums per 32-element sub-block
+        const int64_t nsb = w->in / 256;
+        RSTQ_REQUIRE(xsum, RSTQ_E_INVALID, "a Q4_K weight needs the sub-block sums");
+        if ((rc = need_bytes(xq, M * w->in, "xq")) != RSTQ_OK) return rc;
+        if ((rc = need_bytes(xs, M * nsb * 4, "xs")) != RSTQ_OK) return rc;
+        if ((rc = need_bytes(xsum, M * w->nb * 4, "bsums")) != RSTQ_OK) return rc;
+        if ((rc = need_bytes(y, M * w->out * 4, "y")) != RSTQ_OK) return rc;
+        RSTQ_REQUIRE(xq->dev == w->dev && xs->dev == w->dev && y->dev == w->dev && xsum->dev == w->dev,
+                     RSTQ_E_DEVICE, "weight and buffers live on different devices");
+        if ((rc = use_dev(ctx, w->dev)) != RSTQ_OK) return rc;
+        DeviceState& dsk = ctx->devs[w->dev];
+        ActScratch s;
+        if ((rc = act_scratch(dsk, M, w->in, &s)) != RSTQ_OK) return rc;
+        if ((rc = launch_expand_scales(ctx, dsk, (const float*)xs->ptr, s.xs, M * w->nb)) != RSTQ_OK) return rc;
+        return run_q4k(ctx, w, (const int8_t*)xq->ptr, s.xs, (const int32_t*)xsum->ptr, (float*)y->ptr, M);
+    }
     if ((rc = need_bytes(xq, M * w->in, "xq")) != RSTQ_OK) return rc;
     if ((rc = need_bytes(xs, M * w->nb * 4, "xs")) != RSTQ_OK) return rc;
     if (xsum && (rc = need_bytes(xsum, M * w->nb * 4, "xsum")) != RSTQ_OK) return rc;

@@ -136,6 +136,7 @@ struct rstq_weight {
     uint64_t host_fp = 0;          // fingerprint of the host arrays (host-array operators' cache)
     int8_t* raw_codes = nullptr;   // row-major signed codes / scales as the reference holds them:
     float* raw_scales = nullptr;   // made on first use by the backward-data operator
+    float* mins = nullptr;         // Q4_K only: per-sub-block minima db*bq, [out, nb]; zp is 0 then
 };
 
 struct rstq_graph {
@@ -167,6 +168,12 @@ constexpr uint32_t kEvtMagic = 0x52535145;
 int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
                       const float* src_scales, uint8_t* dst, int fmt, int layout, int64_t out,
                       int64_t in, int64_t src_in, int64_t k_block0);
+// kquant.cu (Q4_K: q8_K activation quantizer, scale expansion, the min-term GEMV)
+int32_t launch_quant_act_q8k(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs, float* xs32,
+                             int32_t* bsums, int64_t rows, int64_t in, int sub);
+int32_t launch_expand_scales(rstq_ctx* ctx, DeviceState& ds, const float* xs, float* xs32, int64_t n32);
+int32_t launch_q4k_min(rstq_ctx* ctx, DeviceState& ds, const float* mins, const float* xs32, const int32_t* bsums,
+                       float* y, int64_t M, int64_t nb, int64_t out);
 // actquant.cu
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
                             int32_t* xsum, int64_t M, int64_t in, int act_dtype = RSTQ_F32);

@@ -65,3 +65,21 @@ def _builtin(fmt_desc, fmt_code):
 
 register_quant("q4_0", _builtin(cq.q4_0, L.FMT_Q4_0))
 register_quant("q8_0", _builtin(cq.q8_0, L.FMT_Q8_0))
+
+
+def _q4k():
+    """:q4_K as the reference registers it (src/raster/quant/core.clj:57-66): quantize-weight-q4k on
+    the host once, then q8_K activations x Q4_K sub-block dots with the scale / min fold on the device."""
+    def quantize(W, rows, cols):
+        q = cq.quantize_weight_q4k(np.asarray(W, dtype=np.float32).ravel(), cq.q4_K)
+        q["bound"] = default_context().bind_weight_q4k(q, rows, cols)
+        return q
+
+    def apply(qm, x):
+        return default_context().qmatmul_host(qm.data["bound"], np.asarray(x, dtype=np.float32), 1, L.F32,
+                                              L.MODE_A8)[0]
+
+    return {"descriptor": cq.q4_K, "quantize": quantize, "apply": apply}
+
+
+register_quant("q4_K", _q4k())

@@ -79,3 +79,42 @@ def repack_stream(wq, ws, out, in_, fmt=q4_0):
     """Row-major {wq, ws} -> the 8-row interleaved stream layout {"wqi", "wsi"}."""
     lay = _layout.quant_stream_layout({"vector_bits": 256}, fmt)
     return _layout.repack(lay, wq, ws, out, in_)
+
+
+# ---- Q4_K: asymmetric 4-bit super-blocks (quant.clj:85-170) ------------------------------------
+q4_K = {"name": "q4_K", "super_block": 256, "subblock": 32, "n_subblocks": 8, "weight_bits": 4,
+        "scale_bits": 6, "has_dmin": True, "pack": "nibble-interleaved", "act_type": "i8-K"}
+
+
+def quantize_weight_q4k(w, fmt=q4_K):
+    """Flat f32 array (len % 256 == 0) -> {"wq", "da", "db", "aq", "bq"} (`quantize-weight-q4k`,
+    quant.clj:95-150).  Per 32-element sub-block a = (max - min) / 15 and b = min; per 256-element
+    super-block da = max(a) / 63 and db = max|b| / 31; aq = clamp(round(a / da), 0, 63),
+    bq = clamp(round(b / db), -32, 31); the codes are taken against the quantized pair:
+    q = clamp(round((w - db*bq) / (da*aq)), 0, 15), element k low / k+16 high nibble."""
+    w = np.ascontiguousarray(w, dtype=np.float32).reshape(-1, 8, 32).astype(np.float64)
+    lo, hi = w.min(axis=2), w.max(axis=2)
+    a, b = (hi - lo) / 15.0, lo
+    dav = np.maximum(a.max(axis=1), 0.0) / 63.0
+    dbv = np.abs(b).max(axis=1) / 31.0
+    with np.errstate(divide="ignore"):
+        ida = np.where(dav == 0.0, 0.0, 1.0 / dav)
+        idb = np.where(dbv == 0.0, 0.0, 1.0 / dbv)
+    aq = np.clip(jround(a * ida[:, None]), 0, 63)
+    bq = np.clip(jround(b * idb[:, None]), -32, 31)
+    a1, b1 = dav[:, None] * aq, dbv[:, None] * bq
+    with np.errstate(divide="ignore"):
+        ia1 = np.where(a1 == 0.0, 0.0, 1.0 / a1)
+    q = np.clip(jround((w - b1[:, :, None]) * ia1[:, :, None]), 0, 15).astype(np.uint8)
+    wq = (q[:, :, :16] | (q[:, :, 16:] << 4)).astype(np.uint8).ravel()
+    return {"wq": wq, "da": dav.astype(np.float32), "db": dbv.astype(np.float32),
+            "aq": aq.astype(np.int8).ravel(), "bq": bq.astype(np.int8).ravel()}
+
+
+def dequant_q4k(enc):
+    """x = (da*aq)*q + (db*bq) (`dequant-q4k`, quant.clj:152-170)."""
+    b = np.asarray(enc["wq"], dtype=np.uint8).reshape(-1, 16)
+    q = np.concatenate([b & 0xF, b >> 4], axis=1).astype(np.float64)
+    a1 = np.repeat(np.asarray(enc["da"], np.float64), 8) * np.asarray(enc["aq"], np.float64)
+    b1 = np.repeat(np.asarray(enc["db"], np.float64), 8) * np.asarray(enc["bq"], np.float64)
+    return (a1[:, None] * q + b1[:, None]).astype(np.float32).ravel()

@@ -232,10 +232,29 @@ class Context:
         L.check(rc)
         return QWeight(self, h)
 
+    def bind_weight_q4k(self, enc, out, in_, dev=0) -> QWeight:
+        """Bind a Q4_K matrix from the arrays of `quantize-weight-q4k` (keys wq, da, db, aq, bq;
+        src/raster/compiler/backend/cpu/quant.clj:95-150), all rows of one matrix [out, in]."""
+        wq = np.ascontiguousarray(enc["wq"]).view(np.uint8)
+        da = np.ascontiguousarray(enc["da"], dtype=np.float32)
+        db = np.ascontiguousarray(enc["db"], dtype=np.float32)
+        aq = np.ascontiguousarray(enc["aq"]).view(np.int8)
+        bq = np.ascontiguousarray(enc["bq"]).view(np.int8)
+        if wq.size != out * in_ // 2 or da.size != out * in_ // 256 or db.size != da.size \
+                or aq.size != out * in_ // 32 or bq.size != aq.size:
+            raise ValueError("Q4_K arrays do not match out x in")
+        h = C.c_void_p()
+        L.check(self.lib.rstq_weight_bind_q4k(self.handle, C.byref(h), _np_ptr(wq), _np_ptr(da), _np_ptr(db),
+                                              _np_ptr(aq), _np_ptr(bq), dev, out, in_))
+        return QWeight(self, h)
+
     # -- ops on device-resident data ----------------------------------------
     def quant_act_i8(self, x: DeviceBuffer, xq, xs, xsum, M, in_) -> None:
         L.check(self.lib.rstq_quant_act_i8(self.handle, x.handle, xq.handle, xs.handle,
                                            xsum.handle if xsum is not None else None, M, in_))
+
+    def quant_act_q8k(self, x: DeviceBuffer, xq, xs, bsums, rows, in_, sub=32) -> None:
+        L.check(self.lib.rstq_quant_act_q8k(self.handle, x.handle, xq.handle, xs.handle, bsums.handle, rows, in_, sub))
 
     def qmatmul(self, w: QWeight, x: DeviceBuffer, y: DeviceBuffer, M=1, act_dtype=L.F32,
                 out_dtype=L.F32, mode=L.MODE_A8) -> None:

@@ -1,0 +1,134 @@
+"""Q4_K on the device against the oracle, through the C ABI.
+
+The q8_K activation quantizer must give the oracle's codes, scales and sub-block sums bit for bit.
+The matmul (integer sub-block dots exact, scale / min fold in f32) is compared with the oracle's
+unrounded f64 sums: max|y - ref| <= 1e-5 of max|ref| and, as the reference's own device test asks
+(test/raster/quant/kernels_k_gpu_test.clj:157-178), <= 1e-3 absolute on its 32 x 256 case."""
+import numpy as np
+import pytest
+
+from javarandom import JavaRandom
+from oracle import oracle as orc
+from raster_b200 import _lib as L
+from raster_b200 import synth
+from raster_b200.quant import cpu_quant as cq
+
+pytestmark = pytest.mark.gpu
+
+
+def gen_centered(n, seed):
+    r = JavaRandom(seed)
+    return np.array([np.float32(r.next_double() - 0.5) for _ in range(n)], dtype=np.float32)
+
+
+def relerr(y, ref):
+    ref = np.asarray(ref, dtype=np.float64).ravel()
+    return float(np.abs(np.asarray(y, dtype=np.float64).ravel() - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def oracle_rows(e, x, M, in_, out):
+    ys = []
+    for m in range(M):
+        xq, xs, bsums = orc.quantize_act_q8k(x[m * in_:(m + 1) * in_], in_, 32)
+        ys.append(orc.qmatmul_q4k(xq, xs, bsums, e, in_, out)[1])
+    return np.stack(ys)
+
+
+@pytest.mark.parametrize("rows,in_,sub", [(1, 256, 32), (3, 1024, 32), (2, 4096, 16), (5, 768, 16)])
+def test_q8k_quantizer_is_bit_exact(ctx, rows, in_, sub):
+    x = synth.normal(31 + in_, rows * in_)
+    x[:256] = 0.0                                       # an all-zero super-block
+    x[in_ - 256] = np.float32(3.5)                      # a lone peak: most codes round to 0 or +-1
+    bx = ctx.array_to_buffer(x)
+    bq, bs, bb = ctx.make_buffer(rows * in_, np.int8), ctx.make_buffer(rows * in_ // 256, np.float32), \
+        ctx.make_buffer(rows * in_ // sub, np.int32)
+    ctx.quant_act_q8k(bx, bq, bs, bb, rows, in_, sub)
+    ctx.sync()
+    gq, gs, gb = bq.download(), bs.download(), bb.download()
+    for r in range(rows):
+        xq, xs, bsums = orc.quantize_act_q8k(x[r * in_:(r + 1) * in_], in_, sub)
+        assert np.array_equal(gq[r * in_:(r + 1) * in_], xq)
+        assert np.array_equal(gs[r * (in_ // 256):(r + 1) * (in_ // 256)].view(np.uint32), xs.view(np.uint32))
+        assert np.array_equal(gb[r * (in_ // sub):(r + 1) * (in_ // sub)], bsums)
+    for o in (bx, bq, bs, bb):
+        o.free()
+
+
+def test_reference_device_case_32x256(ctx):
+    out, in_ = 32, 256
+    W, x = gen_centered(out * in_, 11), gen_centered(in_, 22)
+    e = orc.quantize_weight_q4k(W)
+    w = ctx.bind_weight_q4k(e, out, in_)
+    y = ctx.qmatmul_host(w, x, 1, L.F32, L.MODE_A8)[0]
+    xq, xs, bsums = orc.quantize_act_q8k(x, in_, 32)
+    ycpu, y64 = orc.qmatmul_q4k(xq, xs, bsums, e, in_, out)
+    assert np.abs(y - ycpu).max() < 1e-3
+    assert relerr(y, y64) <= 1e-5
+    w.free()
+
+
+@pytest.mark.parametrize("out,in_,M", [(96, 1024, 1), (100, 512, 3), (4096, 4096, 1), (2048, 2048, 8), (512, 1024, 20),
+                                       (64, 11008 // 256 * 256, 2)])
+def test_q4k_matmul_matches_the_oracle(ctx, out, in_, M):
+    W = synth.normal(5 + out, out * in_, 0.02) + np.float32(0.01)      # off-centre: the min term matters
+    x = synth.normal(6 + in_, M * in_)
+    e = orc.quantize_weight_q4k(W)
+    w = ctx.bind_weight_q4k(e, out, in_)
+    assert (w.out, w.in_, w.bits) == (out, in_, 4)
+    assert w.stream_bytes == out * in_ // 2 + out * (in_ // 256) * 8 + out * (in_ // 32) * 2
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+    ctx.sync()
+    ref = oracle_rows(e, x, M, in_, out)
+    assert relerr(by.download(), ref) <= 1e-5
+    # a second copy at another address gives the same bits
+    w2 = w.clone()
+    by2 = ctx.make_buffer(M * out, np.float32)
+    ctx.qmatmul(w2, bx, by2, M, L.F32, L.F32, L.MODE_A8)
+    ctx.sync()
+    assert np.array_equal(by.download().view(np.uint32), by2.download().view(np.uint32))
+    for o in (w, w2, bx, by, by2):
+        o.free()
+
+
+def test_kernel_level_call_and_registry(ctx):
+    from raster_b200.quant import core as qcore
+    from raster_b200.quant import kernels_k as qk
+    out, in_ = 64, 512
+    W, x = gen_centered(out * in_, 1), gen_centered(in_, 2)
+    e = cq.quantize_weight_q4k(W)
+    xp, xs, bsums = qk.quant_act_q8k_gpu(x, in_ // 256)
+    oq, os_, ob = orc.quantize_act_q8k(x, in_, 32)
+    assert np.array_equal(xp.view(np.int8), oq) and np.array_equal(xs, os_) and np.array_equal(bsums, ob)
+    y = qk.qmatmul_q4k_dp4a(xp, xs, bsums, e["wq"].view(np.int32), e["da"], e["db"], e["aq"], e["bq"],
+                            np.zeros(out, np.float32), in_, out)
+    ref = orc.qmatmul_q4k(oq, os_, ob, e, in_, out)[1]
+    assert relerr(y, ref) <= 1e-5
+    assert "q4_K" in qcore.registered_formats()
+    qm = qcore.qmatrix("q4_K", W, out, in_)
+    y4k = qcore.matmul(qm, x)
+    assert relerr(y4k, ref) <= 1e-5
+    y40 = qcore.matmul(qcore.qmatrix("q4_0", W, out, in_), x)
+    assert not np.array_equal(y4k, y40)                       # the formats take different paths
+    qm.data["bound"].free()
+
+
+def test_q4k_contract_errors(ctx):
+    out, in_ = 32, 256
+    e = orc.quantize_weight_q4k(gen_centered(out * in_, 3))
+    w = ctx.bind_weight_q4k(e, out, in_)
+    bx, by = ctx.make_buffer(in_, np.float32), ctx.make_buffer(out, np.float32)
+    with pytest.raises(L.RstqError) as err:
+        ctx.qmatmul(w, bx, by, 1, L.F32, L.F32, L.MODE_F)      # no float-activation arithmetic for Q4_K
+    assert err.value.code == L.E_INVALID
+    with pytest.raises(L.RstqError) as err:
+        ctx.qmatmul(w, bx, by, 1, L.BF16, L.F32, L.MODE_A8)
+    assert err.value.code == L.E_INVALID
+    with pytest.raises(ValueError):
+        ctx.bind_weight_q4k(e, out, in_ * 2)
+    h = __import__("ctypes").c_void_p()
+    rc = ctx.lib.rstq_weight_bind_q4k(ctx.handle, __import__("ctypes").byref(h), e["wq"].ctypes.data, e["da"].ctypes.data,
+                                      e["db"].ctypes.data, e["aq"].ctypes.data, e["bq"].ctypes.data, 0, 64, 128)
+    assert rc == L.E_SHAPE
+    for o in (w, bx, by):
+        o.free()
