@@ -888,9 +888,21 @@ def run_q4k(args):
         e1.record()
         ctx.sync()
     us = e0.elapsed_ms(e1) * 1e3 / R
-    print(json.dumps({"case": args.case, "calls": 3 * R, "kernels_per_call": (ctx.launch_count() - n0) // (3 * R),
-                      "us_per_call": round(us, 2), "device_GBs": round(w0.device_bytes / us / 1e3, 1),
-                      "reference_format_GBs": round(w0.stream_bytes / us / 1e3, 1)}))
+    kernels = (ctx.launch_count() - n0) // (3 * R)
+    ctx.graph_begin()                       # the same R calls replayed from one CUDA graph
+    for w in ws:
+        ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+    g = ctx.graph_end()
+    for it in range(3):
+        e0.record()
+        g.replay()
+        e1.record()
+        ctx.sync()
+    us_g = e0.elapsed_ms(e1) * 1e3 / R
+    print(json.dumps({"case": args.case, "calls": 3 * R, "kernels_per_call": kernels,
+                      "us_per_call": round(us, 2), "us_per_call_graph": round(us_g, 2),
+                      "device_GBs": round(w0.device_bytes / us_g / 1e3, 1),
+                      "reference_format_GBs": round(w0.stream_bytes / us_g / 1e3, 1)}))
     ctx.close()
 
 

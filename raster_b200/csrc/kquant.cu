@@ -73,31 +73,50 @@ expand_scales_kernel(const float* __restrict__ xs, float* __restrict__ xs32, int
         xs32[i] = xs[i >> 3];
 }
 
-// y[m, o] += sum over b of mins[o, b] * (xs32[m, b] * bsums[m, b]); one warp per output row,
-// eight tokens at a time in registers.  mins is read once per eight tokens (coalesced rows).
+// y[m, o] += sum over b of mins[o, b] * (xs32[m, b] * bsums[m, b]).  The products t[m, b] of up to
+// TT tokens are staged in shared memory once per CTA; a warp owns an output row at a time and reads
+// it with 16-byte loads (nb % 8 == 0), so mins crosses the memory system once per TT tokens.
+// Launched with programmatic serialization: the CTAs are resident while the decode kernel
+// finishes and start adding as soon as its results are visible.
+constexpr int kMinTok = 8;
 __global__ void __launch_bounds__(256)
 q4k_min_kernel(const float* __restrict__ mins, const float* __restrict__ xs32, const int32_t* __restrict__ bsums,
-               float* __restrict__ y, int64_t M, int64_t nb, int64_t out) {
+               float* __restrict__ y, int64_t M, int64_t nb, int64_t out, int TT) {
+    extern __shared__ float s_t[];  // [TT][nb]
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
-    const int64_t o = blockIdx.x * 8ll + (threadIdx.x >> 5);
-    if (o >= out) return;
-    const float* mrow = mins + o * nb;
-    for (int64_t m0 = 0; m0 < M; m0 += 8) {
-        float acc[8];
+    const int64_t warp0 = blockIdx.x * 8ll + (threadIdx.x >> 5), nwarps = gridDim.x * 8ll;
+    const int64_t nb4 = nb >> 2;
+    for (int64_t m0 = 0; m0 < M; m0 += TT) {
+        const int tt = (int)min((int64_t)TT, M - m0);
+        if (m0) __syncthreads();
+        for (int64_t i = threadIdx.x; i < tt * nb; i += 256) s_t[i] = xs32[m0 * nb + i] * (float)bsums[m0 * nb + i];
+        __syncthreads();
+        for (int64_t o = warp0; o < out; o += nwarps) {
+            const float4* mrow = reinterpret_cast<const float4*>(mins + o * nb);
+            float acc[kMinTok];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int64_t b = lane; b < nb; b += 32) {
-            const float mn = __ldg(mrow + b);
+            for (int j = 0; j < kMinTok; ++j) acc[j] = 0.f;
+            for (int64_t b = lane; b < nb4; b += 32) {
+                const float4 mn = __ldg(mrow + b);
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (m0 + j < M) acc[j] = fmaf(mn, xs32[(m0 + j) * nb + b] * (float)bsums[(m0 + j) * nb + b], acc[j]);
-        }
+                for (int j = 0; j < kMinTok; ++j) {
+                    if (j < tt) {
+                        const float4 t = *reinterpret_cast<const float4*>(s_t + j * nb + b * 4);
+                        acc[j] = fmaf(mn.x, t.x, fmaf(mn.y, t.y, fmaf(mn.z, t.z, fmaf(mn.w, t.w, acc[j]))));
+                    }
+                }
+            }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float a = acc[j];
+            for (int j = 0; j < kMinTok; ++j) {
+                if (j < tt) {
+                    float a = acc[j];
 #pragma unroll
-            for (int s = 16; s > 0; s >>= 1) a += __shfl_xor_sync(0xffffffffu, a, s);
-            if (lane == 0 && m0 + j < M) y[(m0 + j) * out + o] += a;
+                    for (int s = 16; s > 0; s >>= 1) a += __shfl_xor_sync(0xffffffffu, a, s);
+                    if (lane == 0) y[(m0 + j) * out + o] += a;
+                }
+            }
         }
     }
 }
@@ -138,12 +157,24 @@ int32_t launch_expand_scales(rstq_ctx* ctx, DeviceState& ds, const float* xs, fl
 
 int32_t launch_q4k_min(rstq_ctx* ctx, DeviceState& ds, const float* mins, const float* xs32, const int32_t* bsums,
                        float* y, int64_t M, int64_t nb, int64_t out) {
-    const int64_t ctas = (out + 7) / 8;
-    RSTQ_REQUIRE(ctas < (1ll << 31), RSTQ_E_LIMIT, "out = %lld", (long long)out);
-    // plain launch: it adds to what the decode kernel wrote, so it starts when that has finished
-    q4k_min_kernel<<<(unsigned)ctas, 256, 0, ds.stream>>>(mins, xs32, bsums, y, M, nb, out);
+    int64_t TT = 48 * 1024 / (nb * 4);  // tokens whose products fit the default shared-memory window
+    RSTQ_REQUIRE(TT >= 1, RSTQ_E_LIMIT, "in = %lld too long for the Q4_K min term", (long long)(nb * 32));
+    if (TT > kMinTok) TT = kMinTok;
+    if (TT > M) TT = M;
+    int64_t ctas = (out + 7) / 8;
+    if (ctas > (int64_t)ds.sm_count * 4) ctas = (int64_t)ds.sm_count * 4;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = (size_t)(TT * nb * 4);
+    cfg.stream = ds.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ds.pdl ? 1 : 0;
+    RSTQ_CUDA(cudaLaunchKernelEx(&cfg, q4k_min_kernel, mins, xs32, bsums, y, M, nb, out, (int)TT));
     ctx->launches++;
-    RSTQ_CUDA(cudaGetLastError());
     return RSTQ_OK;
 }
 
