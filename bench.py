@@ -906,6 +906,126 @@ def run_q4k(args):
     ctx.close()
 
 
+def run_attn(args):
+    """--case attn:<n_q>:<n_kv>:<head_dim>:<cache_len>: the decode attention kernel over f32 K / V caches,
+    distinct cache copies (more than L2 in total) replayed from one CUDA graph; bytes = K + V rows read."""
+    from raster_b200 import Context
+    _, n_q, n_kv, hd, clen = args.case.split(":")
+    n_q, n_kv, hd, clen = int(n_q), int(n_kv), int(hd), int(clen)
+    rng = np.random.default_rng(0)
+    ctx = Context(("cuda:0",))
+    kv_bytes = 2 * clen * n_kv * hd * 4
+    R = max(2, -(-int(1.2 * ctx.device_info()["l2_bytes"]) // kv_bytes))
+    ks = [ctx.array_to_buffer(rng.standard_normal(clen * n_kv * hd).astype(np.float32)) for _ in range(R)]
+    vs = [ctx.array_to_buffer(rng.standard_normal(clen * n_kv * hd).astype(np.float32)) for _ in range(R)]
+    bq, bo = ctx.array_to_buffer(rng.standard_normal(n_q * hd).astype(np.float32)), ctx.make_buffer(n_q * hd, np.float32)
+    scale = 1.0 / float(np.sqrt(hd))
+    ctx.gqa_decode_attention(bq, ks[0], vs[0], bo, clen, n_q, n_q // n_kv, n_kv, hd, clen, scale)
+    ctx.sync()
+    ctx.graph_begin()
+    for k, v in zip(ks, vs):
+        ctx.gqa_decode_attention(bq, k, v, bo, clen, n_q, n_q // n_kv, n_kv, hd, clen, scale)
+    g = ctx.graph_end()
+    e0, e1 = ctx.event(), ctx.event()
+    for it in range(3):
+        e0.record()
+        g.replay()
+        e1.record()
+        ctx.sync()
+    us = e0.elapsed_ms(e1) * 1e3 / R
+    print(json.dumps({"case": args.case, "launches": 3 * R, "us_per_launch": round(us, 2),
+                      "GBs": round(kv_bytes / us / 1e3, 1)}))
+    ctx.close()
+
+
+def run_decoder(args):
+    """--case decoder:<bits>:<cache_len>: one token through whole Llama-7B-style decoder layers on one GPU --
+    the reference's decode chain (test/raster/dl/decoder_layer_gpu_test.clj:59-77): rms-norm + quantize,
+    q / k / v, rope, cache append, GQA attention over f32 caches, o, residual, rms-norm + quantize,
+    gate / up, SwiGLU, down, residual -- 19 kernels per layer, distinct layers (weights and caches well
+    over L2), replayed from one CUDA graph with the position in a device buffer."""
+    from raster_b200 import Context
+    from raster_b200 import _lib as L
+    from raster_b200 import synth
+    parts = args.case.split(":")
+    bits = int(parts[1]) if len(parts) > 1 else 4
+    clen = int(parts[2]) if len(parts) > 2 else 1024
+    H, F, NQ, NKV, HD = 4096, 11008, 32, 32, 128
+    kvrow, maxpos = NKV * HD, clen
+    ctx = Context(("cuda:0",))
+    fmt = L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0
+    rng = np.random.default_rng(1)
+    shapes = {"q": (H, H), "k": (kvrow, H), "v": (kvrow, H), "o": (H, H), "gate": (F, H), "up": (F, H), "down": (H, F)}
+    per_layer_w = sum(stream_bytes(o, i, bits) for o, i in shapes.values())
+    per_layer_kv = 2 * clen * kvrow * 4
+    layers = max(2, -(-3 * ctx.device_info()["l2_bytes"] // (per_layer_w + per_layer_kv)))
+    stack = []
+    for _ in range(layers):
+        lay = {}
+        for name, (o, i) in shapes.items():
+            codes = rng.integers(0, 256, o * i * bits // 8, dtype=np.uint8)
+            scales = (rng.standard_normal(o * (i // 32)) * 0.01).astype(np.float32)
+            lay[name] = ctx.bind_weight(codes, scales, o, i, fmt, L.LAYOUT_ROWMAJOR)
+        lay["kc"] = ctx.array_to_buffer(synth.normal(7, maxpos * kvrow))
+        lay["vc"] = ctx.array_to_buffer(synth.normal(8, maxpos * kvrow))
+        lay["n1"] = ctx.array_to_buffer(np.ones(H, np.float32))
+        lay["n2"] = ctx.array_to_buffer(np.ones(H, np.float32))
+        stack.append(lay)
+    f32 = np.float32
+    x = ctx.array_to_buffer(synth.normal(5, H))
+    h, o_, q, k, v, att = (ctx.make_buffer(n, f32) for n in (H, H, H, kvrow, kvrow, H))
+    gate, up, act, down = (ctx.make_buffer(n, f32) for n in (F, F, F, H))
+    xq, xs, xsum = ctx.make_buffer(H, np.int8), ctx.make_buffer(H // 32, f32), ctx.make_buffer(H // 32, np.int32)
+    bpos = ctx.array_to_buffer(np.array([clen - 1], np.int64))
+    blen = ctx.array_to_buffer(np.array([clen], np.int64))
+    scale = 1.0 / float(np.sqrt(HD))
+
+    def one_pass():
+        for lay in stack:
+            ctx.rms_norm_quant_act(x, lay["n1"], xq, xs, xsum, 1, H)
+            ctx.qmatmul_prequant(lay["q"], xq, xs, xsum, q, 1)
+            ctx.qmatmul_prequant(lay["k"], xq, xs, xsum, k, 1)
+            ctx.qmatmul_prequant(lay["v"], xq, xs, xsum, v, 1)
+            ctx.rope_pos(q, q, NQ, HD, 10000.0, posbuf=bpos)
+            ctx.rope_pos(k, k, NKV, HD, 10000.0, posbuf=bpos)
+            ctx.kv_append(k, lay["kc"], kvrow, maxpos=maxpos, posbuf=bpos)
+            ctx.kv_append(v, lay["vc"], kvrow, maxpos=maxpos, posbuf=bpos)
+            ctx.gqa_decode_attention(q, lay["kc"], lay["vc"], att, 0, NQ, NQ // NKV, NKV, HD, maxpos, scale, clenbuf=blen)
+            ctx.qmatmul(lay["o"], att, o_, 1)
+            ctx.residual_add(x, o_, h, H)
+            ctx.rms_norm_quant_act(h, lay["n2"], xq, xs, xsum, 1, H)
+            ctx.qmatmul_prequant(lay["gate"], xq, xs, xsum, gate, 1)
+            ctx.qmatmul_prequant(lay["up"], xq, xs, xsum, up, 1)
+            ctx.silu_mul(gate, up, act, F)
+            ctx.qmatmul(lay["down"], act, down, 1)
+            ctx.residual_add(h, down, x, H)
+
+    n0 = ctx.launch_count()
+    one_pass()
+    ctx.sync()
+    kernels = (ctx.launch_count() - n0) // layers
+    ctx.graph_begin()
+    one_pass()
+    g = ctx.graph_end()
+    for _ in range(3):
+        g.replay()
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    n = max(3, args.steps)
+    e0.record()
+    for _ in range(n):
+        g.replay()
+    e1.record()
+    ctx.sync()
+    us_layer = e0.elapsed_ms(e1) * 1e3 / n / layers
+    print(json.dumps({"case": args.case, "layers_per_step": layers, "kernels_per_layer": kernels,
+                      "cache_len": clen, "us_per_layer": round(us_layer, 2),
+                      "weight_bytes_per_layer": per_layer_w, "kv_bytes_per_layer": per_layer_kv,
+                      "GBs": round((per_layer_w + per_layer_kv) / us_layer / 1e3, 1),
+                      "tokens_per_s_32_layers": round(1e6 / (32 * us_layer), 1)}))
+    ctx.close()
+
+
 def run_case(args):
     """One small named case for profiler captures: a few launches of one decode kernel on
     distinct weight copies (more than L2 in total), nothing else.
@@ -962,12 +1082,16 @@ def main():
     ap.add_argument("--case", default=None, help="small single-kernel case for profiler captures")
     ap.add_argument("--plan", type=int, default=0, help="with --case: decode work split (rstq_tune key 4)")
     args = ap.parse_args()
+    if args.case and args.case.startswith("decoder"):
+        return run_decoder(args)
     if args.case and args.case.startswith("layer"):
         return run_layer(args)
     if args.case and args.case.startswith("dx"):
         return run_dx(args)
     if args.case and args.case.startswith("q4k"):
         return run_q4k(args)
+    if args.case and args.case.startswith("attn"):
+        return run_attn(args)
     if args.case:
         return run_case(args)
     args.warmup = max(args.warmup, 3)

@@ -279,6 +279,25 @@ RSTQ_API int32_t rstq_silu_mul(rstq_ctx* ctx, rstq_buf* gate, rstq_buf* up, rstq
 RSTQ_API int32_t rstq_gelu_mul(rstq_ctx* ctx, rstq_buf* gate, rstq_buf* up, rstq_buf* out, int64_t n);
 RSTQ_API int32_t rstq_residual_add(rstq_ctx* ctx, rstq_buf* a, rstq_buf* b, rstq_buf* out, int64_t n);
 
+/* The attention steps of the same chain, one token (src/raster/dl/attention.clj):
+ *   rstq_rope_pos      rope-pos-gpu! :386-408 / rope-pos-buf! :482-499 -- NeoX rotate-half of x
+ *                      [heads, head_dim] at absolute position pos (out may be x);
+ *   rstq_kv_append     kv-append! :413-416 / kv-append-buf! :501-504 -- cache[pos*kvrow + i] = src[i];
+ *                      the cache buffer holds maxpos rows (checked against pos when it is a host scalar);
+ *   rstq_gqa_decode_attention  gqa-decode-attention-gpu! :423-471 / -buf! :514-575 -- per query head
+ *                      softmax(scale * q.K^T) V over cache positions [0, cache_len), K / V caches
+ *                      [maxpos][n_kv][head_dim], n_q = group * n_kv, head_dim % 4 == 0 and <= 256.
+ * posbuf / clenbuf: NULL, or a device buffer holding one int64 that the kernel reads (the -buf
+ * variants: a captured graph then serves every token; call once before capturing).  The
+ * reference's score scratch `sc` has no counterpart (scores stay in registers).  All f32. */
+RSTQ_API int32_t rstq_rope_pos(rstq_ctx* ctx, rstq_buf* x, rstq_buf* out, int64_t heads, int64_t head_dim,
+                               double theta, int64_t pos, rstq_buf* posbuf);
+RSTQ_API int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, int64_t kvrow, int64_t pos,
+                                int64_t maxpos, rstq_buf* posbuf);
+RSTQ_API int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
+                                           int64_t cache_len, rstq_buf* clenbuf, int64_t n_q, int64_t group,
+                                           int64_t n_kv, int64_t head_dim, int64_t maxpos, double scale);
+
 /* ---- tensor-parallel exchange of the sharded operator.  No counterpart in the reference: it
  *      extends the placement / plan vocabulary (src/raster/compiler/passes/placement.clj:21-89)
  *      with a weight split over the GPUs of one box.  One endpoint per rank.  Every rank owns a

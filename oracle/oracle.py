@@ -364,6 +364,28 @@ def qmatrix_matmul(fmt: str, e, x, rows: int, cols: int):
     raise KeyError(f"unknown quant format {fmt}")
 
 
+# ---- attention steps of the decode chain (src/raster/dl/attention.clj:386-575) ---------------
+def rope_pos(x, heads: int, head_dim: int, theta: float, pos: int):
+    x = _f32(x).ravel()
+    out = np.empty_like(x)
+    lib().orc_rope_pos(_ptr(x), _ptr(out), _i64(heads), _i64(head_dim), C.c_double(theta), _i64(pos))
+    return out
+
+
+def kv_append(src, cache, kvrow: int, pos: int):
+    src = _f32(src).ravel()
+    lib().orc_kv_append(_ptr(src), _ptr(cache), _i64(kvrow), _i64(pos))
+    return cache
+
+
+def gqa_decode_attention(q, k, v, cache_len: int, n_q: int, group: int, n_kv: int, head_dim: int, scale: float):
+    q, k, v = _f32(q).ravel(), _f32(k).ravel(), _f32(v).ravel()
+    out = np.empty(n_q * head_dim, np.float32)
+    lib().orc_gqa_decode_attention(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _i64(cache_len), _i64(n_q), _i64(group),
+                                   _i64(n_kv), _i64(head_dim), C.c_double(scale))
+    return out
+
+
 def cpk() -> C.CDLL:
     global _cpk
     if _cpk is None:

@@ -768,3 +768,59 @@ ORC_API void orc_qmatmul_q6k(const int8_t* xq, const float* xs, const int32_t* b
         if (y64) y64[o] = acc;
     }
 }
+
+/* ------------------------------------------------------------------------
+ * The attention steps of the decoder layer's decode chain (one token), carried in double and
+ * rounded to float once per stored value.
+ *
+ * rope-pos-gpu! / rope-pos-buf!, src/raster/dl/attention.clj:386-408, :482-499: NeoX rotate-half at
+ * absolute position pos; pair (i, i + head_dim/2) of every head turns by pos * exp(-2i/head_dim * ln theta).
+ * ---------------------------------------------------------------------- */
+ORC_API void orc_rope_pos(const float* x, float* out, int64_t heads, int64_t head_dim, double theta, int64_t pos) {
+    const int64_t h2 = head_dim / 2;
+    const double ln_theta = log(theta);
+    for (int64_t h = 0; h < heads; ++h)
+        for (int64_t i = 0; i < h2; ++i) {
+            const double freq = exp((-2.0 * (double)i) / (double)head_dim * ln_theta);
+            const double ang = (double)pos * freq, c = cos(ang), s = sin(ang);
+            const double x0 = (double)x[h * head_dim + i], x1 = (double)x[h * head_dim + i + h2];
+            out[h * head_dim + i] = (float)(x0 * c - x1 * s);
+            out[h * head_dim + i + h2] = (float)(x1 * c + x0 * s);
+        }
+}
+
+/* kv-append! / kv-append-buf!, attention.clj:413-416, :501-504: cache[pos*kvrow + i] = src[i]. */
+ORC_API void orc_kv_append(const float* src, float* cache, int64_t kvrow, int64_t pos) {
+    memcpy(cache + pos * kvrow, src, (size_t)kvrow * sizeof(float));
+}
+
+/* gqa-decode-attention-gpu! / -buf!, attention.clj:423-471, :514-575: per query head hq (kv head
+ * hq / group): scores = scale * q.k_j over the cache positions, max-subtracted softmax, out = sum_j
+ * p_j * v_j.  K / V cache layout [pos][n_kv][head_dim]. */
+ORC_API void orc_gqa_decode_attention(const float* q, const float* k, const float* v, float* out, int64_t cache_len,
+                                      int64_t n_q, int64_t group, int64_t n_kv, int64_t head_dim, double scale) {
+    const int64_t kvstride = n_kv * head_dim;
+    double* sc = (double*)malloc((size_t)cache_len * sizeof(double));
+    for (int64_t hq = 0; hq < n_q; ++hq) {
+        const int64_t hkvb = (hq / group) * head_dim;
+        double mx = -1.0e38;
+        for (int64_t j = 0; j < cache_len; ++j) {
+            double dot = 0.0;
+            for (int64_t d = 0; d < head_dim; ++d) dot += (double)q[hq * head_dim + d] * (double)k[j * kvstride + hkvb + d];
+            sc[j] = dot * scale;
+            if (sc[j] > mx) mx = sc[j];
+        }
+        double sum = 0.0;
+        for (int64_t j = 0; j < cache_len; ++j) {
+            sc[j] = exp(sc[j] - mx);
+            sum += sc[j];
+        }
+        const double inv = 1.0 / sum;
+        for (int64_t d = 0; d < head_dim; ++d) {
+            double a = 0.0;
+            for (int64_t j = 0; j < cache_len; ++j) a += sc[j] * inv * (double)v[j * kvstride + hkvb + d];
+            out[hq * head_dim + d] = (float)a;
+        }
+    }
+    free(sc);
+}

@@ -65,6 +65,9 @@ SIGNATURES = {
     "rstq_silu_mul": [vp, vp, vp, vp, i64],
     "rstq_gelu_mul": [vp, vp, vp, vp, i64],
     "rstq_residual_add": [vp, vp, vp, vp, i64],
+    "rstq_rope_pos": [vp, vp, vp, i64, i64, C.c_double, i64, vp],
+    "rstq_kv_append": [vp, vp, vp, i64, i64, i64, vp],
+    "rstq_gqa_decode_attention": [vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, C.c_double],
     "rstq_tp_region_bytes": [i32, i64],
     "rstq_tp_attach": [vp, i32, i32, i32, pp, i64, pp],
     "rstq_tp_create_local": [vp, i32, C.POINTER(i32), i64, pp],

@@ -423,6 +423,7 @@ int32_t rstq_shutdown(rstq_ctx* ctx) {
         if (ds.stream) cudaStreamSynchronize(ds.stream);
         if (ds.act_scratch) cudaFree(ds.act_scratch);
         if (ds.gemm_scratch) cudaFree(ds.gemm_scratch);
+        if (ds.attn_scratch) cudaFree(ds.attn_scratch);
         if (ds.partials) cudaFree(ds.partials);
         if (ds.counters) cudaFree(ds.counters);
         if (ds.status) cudaFree(ds.status);

@@ -76,6 +76,8 @@ struct DeviceState {
     int64_t counters_len = 0;
     void* gemm_scratch = nullptr;  // fp16 activations + row exponents of the GEMM path
     int64_t gemm_scratch_bytes = 0;
+    void* attn_scratch = nullptr;  // decode attention: arrival counters + per-slice softmax states
+    int64_t attn_scratch_bytes = 0;
     void* pinned = nullptr;        // host staging for the host-array entry points
     int64_t pinned_bytes = 0;
     void* io_dev = nullptr;        // device staging for the host-array entry points

@@ -1,0 +1,282 @@
+"""`raster.gpu.cuda-runtime`: the runtime function table the reference's session layer resolves by
+name (src/raster/gpu/core.clj:39-84; the OpenCL instance it mirrors is
+src/raster/gpu/ocl_runtime.clj:405-1097), for `:cuda:N` devices, over the C ABI of this library.
+
+What the table holds here: buffers, an arena, a registry of NAMED kernels with bound launches,
+graphs, synchronisation.  What it does not hold: kernels compiled from generated source
+(`register-kernel!` of the reference takes OpenCL C text; here a registered kernel is one of the
+hand-written operators of this library, looked up by the reference's own operator name, and a
+caller-supplied entry is a Python callable over device buffers).
+
+Calling convention of a registered kernel, as in `invoke-registered-map-void-kernel
+[name arrays scalars n]` (ocl_runtime.clj:708-799): `arrays` = the array arguments in the deftm's
+order (buffer records from make_buffer / array_to_buffer, or QWeight handles for weights),
+`scalars` = the scalar arguments in the deftm's order, `n` = the work-item count of the
+reference's `par/map-void!` (accepted and checked where the operator defines it, otherwise
+unused: the grid is the library's own).
+"""
+from __future__ import annotations
+
+import contextlib
+import threading
+
+import numpy as np
+
+from . import _lib as L
+from .runtime import Context, DeviceBuffer, QWeight
+
+_state = {"ctx": None, "devices": ()}
+_lock = threading.RLock()
+_registry: dict = {}
+_tls = threading.local()
+
+_DTYPES = {"float": np.float32, "int": np.int32, "byte": np.int8, "int8": np.int8, "long": np.int64,
+           "half": np.uint16, "bf16": np.uint16}
+
+
+# ---- init / devices -------------------------------------------------------------------------
+def query_devices():
+    """[{:id "cuda:N" :ordinal N}] for every CUDA device the driver shows ([] without a GPU)."""
+    import ctypes as C
+    n = C.c_int32()
+    if L.load().rstq_device_count(C.byref(n)) != 0:
+        return []
+    return [{"id": f"cuda:{i}", "ordinal": i} for i in range(n.value)]
+
+
+def init(devices=("cuda:0",)) -> Context:
+    with _lock:
+        if _state["ctx"] is None:
+            _state["ctx"] = Context(tuple(devices))
+            _state["devices"] = tuple(devices)
+        return _state["ctx"]
+
+
+def shutdown() -> None:
+    with _lock:
+        if _state["ctx"] is not None:
+            _state["ctx"].close()
+            _state["ctx"] = None
+
+
+def _ctx() -> Context:
+    if _state["ctx"] is None:
+        raise RuntimeError("raster.gpu.cuda-runtime: init! has not been called")
+    return _state["ctx"]
+
+
+# ---- arena + buffers -------------------------------------------------------------------------
+class KernelArena:
+    """Owns every buffer made while it is the current arena; close frees them (idempotent)."""
+
+    def __init__(self):
+        self.buffers, self.closed = [], False
+
+
+def make_kernel_arena() -> KernelArena:
+    return KernelArena()
+
+
+def close_kernel_arena(arena: KernelArena) -> None:
+    if arena.closed:
+        return
+    arena.closed = True
+    for rec in arena.buffers:
+        free_buffer(rec)
+    arena.buffers.clear()
+
+
+def current_arena():
+    return getattr(_tls, "arena", None)
+
+
+@contextlib.contextmanager
+def with_arena(arena: KernelArena):
+    """(binding [*current-arena* arena] ...), ocl_runtime.clj:222-224."""
+    prev = current_arena()
+    _tls.arena = arena
+    try:
+        yield arena
+    finally:
+        _tls.arena = prev
+
+
+def make_buffer(n: int, dtype="float", dev=0) -> dict:
+    """-> {:segment :n-elements :byte-size :dtype} (ocl_runtime.clj:405-430)."""
+    if dtype not in _DTYPES:
+        raise ValueError(f"make-buffer: unknown dtype {dtype!r}; known: {sorted(_DTYPES)}")
+    seg = _ctx().make_buffer(int(n), _DTYPES[dtype], dev)
+    rec = {"segment": seg, "n_elements": int(n), "byte_size": seg.byte_size, "dtype": dtype}
+    a = current_arena()
+    if a is not None:
+        if a.closed:
+            raise RuntimeError("make-buffer: the current arena is closed")
+        a.buffers.append(rec)
+    return rec
+
+
+def free_buffer(rec: dict) -> None:
+    seg = rec.get("segment")
+    if seg is not None:
+        seg.free()
+        rec["segment"] = None
+
+
+def _np_dtype_name(a: np.ndarray) -> str:
+    for name in ("float", "int", "byte", "long"):
+        if a.dtype == _DTYPES[name]:
+            return name
+    if a.dtype == np.uint8:
+        return "byte"
+    if a.dtype in (np.uint16, np.int16):
+        return "half"
+    raise ValueError(f"array->buffer!: no device dtype for {a.dtype}")
+
+
+def array_to_buffer(arr, dev=0) -> dict:
+    a = np.ascontiguousarray(arr)
+    rec = make_buffer(a.size, _np_dtype_name(a), dev)
+    rec["segment"].upload(a.view(_DTYPES[rec["dtype"]]))
+    return rec
+
+
+buffer_of_array = array_to_buffer
+
+
+def buffer_to_array(rec: dict) -> np.ndarray:
+    if rec.get("segment") is None:
+        raise RuntimeError("buffer->array: the buffer has been freed")
+    return rec["segment"].download()
+
+
+def buffer_as_float_buffer(rec: dict) -> np.ndarray:
+    return rec["segment"].download(np.float32)
+
+
+def buffer_as_int_buffer(rec: dict) -> np.ndarray:
+    return rec["segment"].download(np.int32)
+
+
+# ---- kernel registry --------------------------------------------------------------------------
+def register_kernel(name: str, fn, n_arrays=None, n_scalars=None) -> None:
+    """fn(ctx, arrays, scalars) launches asynchronously on the context's stream."""
+    if not callable(fn):
+        raise TypeError("register-kernel!: the entry must be callable")
+    _registry[name] = {"kernel_name": name, "fn": fn, "n_arrays": n_arrays, "n_scalars": n_scalars}
+
+
+def kernel_registry_entry(name: str) -> dict:
+    if name not in _registry:
+        raise KeyError(f"no kernel registered under {name!r}; registered: {sorted(_registry)}")
+    return _registry[name]
+
+
+def _seg(x):
+    if isinstance(x, dict):
+        if x.get("segment") is None:
+            raise RuntimeError("a freed buffer was passed to a kernel")
+        return x["segment"]
+    if x is None or isinstance(x, (DeviceBuffer, QWeight)):
+        return x
+    raise TypeError(f"kernel array argument must be a buffer record, a weight or None, got {type(x).__name__}")
+
+
+def _check(entry, arrays, scalars):
+    for key, got in (("n_arrays", len(arrays)), ("n_scalars", len(scalars))):
+        want = entry[key]
+        if want is not None and got != want:
+            raise ValueError(f"{entry['kernel_name']}: {key[2:]} expected {want}, got {got}")
+
+
+def invoke_registered_map_void_kernel(name: str, arrays, scalars, n=None) -> None:
+    """Launch and wait (the reference's synchronous invoke)."""
+    entry = kernel_registry_entry(name)
+    _check(entry, arrays, scalars)
+    entry["fn"](_ctx(), [_seg(a) for a in arrays], list(scalars))
+    _ctx().sync()
+
+
+def bind_registered_map_void_kernel(name: str, arrays, scalars, n=None, async_=False) -> dict:
+    """-> {:bound :group-count :kernel-name :async?} (ocl_runtime.clj:1003-1029): arguments are
+    resolved once; launch_registered_bound replays the call."""
+    entry = kernel_registry_entry(name)
+    _check(entry, arrays, scalars)
+    segs, sc = [_seg(a) for a in arrays], list(scalars)
+    return {"bound": (entry["fn"], segs, sc), "group_count": None if n is None else -(-int(n) // 256),
+            "kernel_name": name, "async?": bool(async_), "destroyed": False}
+
+
+def launch_registered_bound(bound: dict) -> None:
+    if bound.get("destroyed"):
+        raise RuntimeError(f"{bound['kernel_name']}: the bound kernel has been destroyed")
+    fn, segs, sc = bound["bound"]
+    fn(_ctx(), segs, sc)
+    if not bound["async?"]:
+        _ctx().sync()
+
+
+def synchronize_async() -> None:
+    _ctx().sync()
+
+
+def destroy_prepared(bound: dict) -> None:
+    bound["destroyed"] = True
+    bound["bound"] = None
+
+
+def record_graph(bounds, dev=0):
+    """Capture the bound launches, in order, into one CUDA graph (ocl_runtime.clj:1051-1058).  Every
+    bound kernel must have run once before (scratch is sized outside a capture)."""
+    ctx = _ctx()
+    for b in bounds:
+        if b.get("destroyed"):
+            raise RuntimeError(f"{b['kernel_name']}: the bound kernel has been destroyed")
+    ctx.graph_begin(dev)
+    try:
+        for b in bounds:
+            fn, segs, sc = b["bound"]
+            fn(ctx, segs, sc)
+    except Exception:
+        try:
+            ctx.graph_end(dev).destroy()
+        except Exception:
+            pass
+        raise
+    return ctx.graph_end(dev)
+
+
+def replay_graph(graph, sync=True) -> None:
+    graph.replay()
+    if sync:
+        _ctx().sync()
+
+
+def destroy_graph(graph) -> None:
+    graph.destroy()
+
+
+# ---- the hand-written operators under the reference's names -----------------------------------
+def _builtin():
+    r = register_kernel
+    # raster.quant.kernels: (xq xs xsum wqi wsi y in out g-start g-count) -> arrays (xq xs xsum w y), scalars (M)
+    r("qmatmul-q4-x8!", lambda c, a, s: c.qmatmul_prequant(a[3], a[0], a[1], a[2], a[4], *(s[:1] or [1])), 5)
+    r("qmatmul-q8-x8!", lambda c, a, s: c.qmatmul_prequant(a[3], a[0], a[1], a[2], a[4], *(s[:1] or [1])), 5)
+    r("qmatmul-q4k-dp4a!", lambda c, a, s: c.qmatmul_prequant(a[3], a[0], a[1], a[2], a[4], 1), 5)
+    # raster.compiler.backend.cpu.quant / kernels-k activation quantizers
+    r("quantize-act-i8", lambda c, a, s: c.quant_act_i8(a[0], a[1], a[2], a[3], s[0], s[1]), 4, 2)
+    r("quant-act-q8k-gpu!", lambda c, a, s: c.quant_act_q8k(a[0], a[1], a[2], a[3], 1, s[0] * 256, 32), 4, 1)
+    # raster.dl.nn
+    r("rms-norm!", lambda c, a, s: c.rms_norm(a[0], a[1], a[2], s[0], s[1], s[2], s[3]), 3, 4)
+    r("silu-mul!", lambda c, a, s: c.silu_mul(a[0], a[1], a[2], s[0]), 3, 1)
+    r("gelu-mul!", lambda c, a, s: c.gelu_mul(a[0], a[1], a[2], s[0]), 3, 1)
+    r("residual-add!", lambda c, a, s: c.residual_add(a[0], a[1], a[2], s[0]), 3, 1)
+    # raster.dl.attention, device-side position forms: (x out heads head-dim theta posbuf) etc.
+    r("rope-pos-buf!", lambda c, a, s: c.rope_pos(a[0], a[1], s[0], s[1], s[2], posbuf=a[2]), 3, 3)
+    r("kv-append-buf!", lambda c, a, s: c.kv_append(a[0], a[1], s[0], maxpos=s[1], posbuf=a[2]), 3, 2)
+    # (q k v out sc clenbuf) (n-q group n-kv head-dim maxpos scale); sc may be None: it is not used
+    r("gqa-decode-attention-buf!",
+      lambda c, a, s: c.gqa_decode_attention(a[0], a[1], a[2], a[3], 0, s[0], s[1], s[2], s[3], s[4], s[5], clenbuf=a[5]),
+      6, 6)
+
+
+_builtin()

@@ -292,6 +292,21 @@ class Context:
     def residual_add(self, a, b, out, n) -> None:
         L.check(self.lib.rstq_residual_add(self.handle, a.handle, b.handle, out.handle, n))
 
+    # -- attention steps of the decode chain (raster.dl.attention) -----------------
+    def rope_pos(self, x, out, heads, head_dim, theta, pos=0, posbuf=None) -> None:
+        L.check(self.lib.rstq_rope_pos(self.handle, x.handle, out.handle, heads, head_dim, theta, pos,
+                                       posbuf.handle if posbuf is not None else None))
+
+    def kv_append(self, src, cache, kvrow, pos=0, maxpos=1, posbuf=None) -> None:
+        L.check(self.lib.rstq_kv_append(self.handle, src.handle, cache.handle, kvrow, pos, maxpos,
+                                        posbuf.handle if posbuf is not None else None))
+
+    def gqa_decode_attention(self, q, k, v, out, cache_len, n_q, group, n_kv, head_dim, maxpos, scale,
+                             clenbuf=None) -> None:
+        L.check(self.lib.rstq_gqa_decode_attention(self.handle, q.handle, k.handle, v.handle, out.handle, cache_len,
+                                                   clenbuf.handle if clenbuf is not None else None, n_q, group,
+                                                   n_kv, head_dim, maxpos, scale))
+
     # -- graphs / events / misc ------------------------------------------------
     def graph_begin(self, dev=0) -> None:
         L.check(self.lib.rstq_graph_begin(self.handle, dev))
