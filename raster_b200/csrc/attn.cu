@@ -13,6 +13,9 @@
 // softmax (running max, sum and weighted V in registers), the warps of a CTA are merged through
 // shared memory and the slices through a small scratch in device memory, where the last CTA to
 // arrive for a KV head writes out = sum_j p_j v_j.  The reference's score scratch `sc` is not used.
+// head_dim 64 and 128 take gqa_decode_fast_kernel (eight lanes per position, four positions per
+// warp step); every other head_dim % 4 == 0 up to 256 takes the general gqa_decode_kernel (a
+// warp per position).
 #include "internal.h"
 
 namespace rstq {
@@ -62,19 +65,89 @@ struct AttnParams {
     float scale;
 };
 
-// merge `n` partial states (max m, sum l, weighted V o[d]) of one query head for one d
-__device__ __forceinline__ void attn_merge(const float* base, int n, int stride, int hd, int d, float* o_out,
-                                           float* l_out) {
-    float M = kNegInf;
-    for (int w = 0; w < n; ++w) M = fmaxf(M, __ldcg(base + w * stride + hd));
-    float L = 0.f, O = 0.f;
-    for (int w = 0; w < n; ++w) {
-        const float e = expf(__ldcg(base + w * stride + hd) - M);
-        L = fmaf(__ldcg(base + w * stride + hd + 1), e, L);
-        O = fmaf(__ldcg(base + w * stride + d), e, O);
+// Second half of both attention kernels: the per-warp states in shared memory ([warps][gc][row]:
+// weighted V, max, sum) are merged per CTA, then per KV head across the slices of the cache.
+// GS = query heads per CTA (the stride of the scratch).
+template <int GS>
+__device__ __forceinline__ void attn_finish(const AttnParams& p, float* s_part, int* s_last_p, int gc, int g0, int hkv,
+                                            int split, int gz, int hd, int row) {
+    __syncthreads();
+    // CTA state per (g, d): straight to out when there is one slice, else to the scratch
+    float* mine = p.part + ((((int64_t)hkv * gridDim.z + gz) * p.S + split) * GS) * row;
+    for (int i = threadIdx.x; i < gc * row; i += blockDim.x) {
+        const int g = i / row, d = i - g * row;
+        if (d >= hd + 2) continue;   // padding
+        const float* base = s_part + g * row;
+        float M = kNegInf;
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, base[w * gc * row + hd]);
+        float val;
+        if (d == hd) {
+            val = M;
+        } else {
+            float acc1 = 0.f;
+            const int src = d == hd + 1 ? hd + 1 : d;
+            for (int w = 0; w < kAttnWarps; ++w)
+                acc1 = fmaf(base[w * gc * row + src], expf(base[w * gc * row + hd] - M), acc1);
+            val = acc1;
+        }
+        if (p.S == 1) {
+            if (d < hd) {
+                float L = 0.f;
+                for (int w = 0; w < kAttnWarps; ++w)
+                    L = fmaf(base[w * gc * row + hd + 1], expf(base[w * gc * row + hd] - M), L);
+                p.out[(int64_t)(hkv * p.group + g0 + g) * hd + d] = val * (1.0f / L);
+            }
+        } else {
+            mine[g * row + d] = val;
+        }
     }
-    *o_out = O;
-    *l_out = L;
+    if (p.S == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(p.counters + hkv * gridDim.z + gz, 1);
+        *s_last_p = prev == p.S - 1;
+        if (*s_last_p) p.counters[hkv * gridDim.z + gz] = 0;   // ready for the next launch / graph replay
+    }
+    __syncthreads();
+    if (!*s_last_p) return;
+    __threadfence();
+    // The last CTA of this KV head merges the S slices.  Slice weights exp(m_s - M) and the sums L go
+    // through shared memory (the per-warp states are dead by now; the host keeps S + 1 <= 8 * row),
+    // so that the loop over the slices below is independent loads the compiler can batch.
+    const float* all = p.part + (((int64_t)hkv * gridDim.z + gz) * p.S * GS) * row;
+    const int S = p.S, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* s_w = s_part;            // [gc][S] maxima, then weights
+    float* s_L = s_part + gc * S;   // [gc]
+    for (int i = threadIdx.x; i < gc * S; i += blockDim.x) {
+        const int g = i / S, sl = i - g * S;
+        s_w[i] = __ldcg(all + ((int64_t)sl * GS + g) * row + hd);
+    }
+    __syncthreads();
+    if (warp < gc) {
+        float M = kNegInf;
+        for (int sl = lane; sl < S; sl += 32) M = fmaxf(M, s_w[warp * S + sl]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float Lsum = 0.f;
+        for (int sl = lane; sl < S; sl += 32) {
+            const float e = expf(s_w[warp * S + sl] - M);
+            Lsum = fmaf(__ldcg(all + ((int64_t)sl * GS + warp) * row + hd + 1), e, Lsum);
+            s_w[warp * S + sl] = e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, o);
+        if (lane == 0) s_L[warp] = Lsum;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < gc * hd; i += blockDim.x) {
+        const int g = i / hd, d = i - g * hd;
+        const float* col = all + (int64_t)g * row + d;
+        float O = 0.f;
+#pragma unroll 8
+        for (int sl = 0; sl < S; ++sl) O = fmaf(__ldcg(col + (int64_t)sl * GS * row), s_w[g * S + sl], O);
+        p.out[(int64_t)(hkv * p.group + g0 + g) * hd + d] = O * (1.0f / s_L[g]);
+    }
 }
 
 __global__ void __launch_bounds__(kAttnWarps * 32)
@@ -164,54 +237,111 @@ gqa_decode_kernel(const AttnParams p) {
             }
         }
     }
+    attn_finish<kAttnGroup>(p, s_part, &s_last, gc, g0, hkv, split, gz, hd, row);
+}
+
+// head_dim = 32 * VEC (64, 128): eight lanes share a cache position, so a warp works on four
+// positions at once and a dot needs three shuffles; a lane owns float4 columns sub, sub + 8, ... of
+// the head.  Query heads (pre-scaled) sit in shared memory; a CTA serves up to kFastGroup of them.
+constexpr int kFastGroup = 4;
+template <int VEC>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+gqa_decode_fast_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) float s_part[];   // [kAttnWarps][gc][hd + 4], then q [gc][hd]
+    __shared__ int s_last;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    constexpr int hd = 32 * VEC, hd4 = hd / 4, row = hd + 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = lane >> 3, sub = lane & 7;
+    const int hkv = blockIdx.x, split = blockIdx.y, gz = blockIdx.z;
+    const int g0 = gz * kFastGroup;
+    const int gc = min(kFastGroup, p.group - g0);
+    float4* s_q = reinterpret_cast<float4*>(s_part + kAttnWarps * gc * row);
+    for (int i = threadIdx.x; i < gc * hd4; i += blockDim.x) {
+        const float4 t = reinterpret_cast<const float4*>(p.q + (int64_t)(hkv * p.group + g0) * hd)[i];
+        s_q[i] = make_float4(t.x * p.scale, t.y * p.scale, t.z * p.scale, t.w * p.scale);
+    }
     __syncthreads();
-    // CTA state per (g, d): straight to out when there is one slice, else to the scratch
-    float* mine = p.part + ((((int64_t)hkv * gridDim.z + gz) * p.S + split) * kAttnGroup) * row;
-    for (int i = threadIdx.x; i < gc * row; i += blockDim.x) {
-        const int g = i / row, d = i - g * row;
-        if (d >= hd + 2) continue;   // padding
-        const float* base = s_part + g * row;
-        float M = kNegInf;
-        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, base[w * gc * row + hd]);
-        float val;
-        if (d == hd) {
-            val = M;
-        } else {
-            float acc1 = 0.f;
-            const int src = d == hd + 1 ? hd + 1 : d;
-            for (int w = 0; w < kAttnWarps; ++w)
-                acc1 = fmaf(base[w * gc * row + src], expf(base[w * gc * row + hd] - M), acc1);
-            val = acc1;
-        }
-        if (p.S == 1) {
-            if (d < hd) {
-                float L = 0.f;
-                for (int w = 0; w < kAttnWarps; ++w)
-                    L = fmaf(base[w * gc * row + hd + 1], expf(base[w * gc * row + hd] - M), L);
-                p.out[(int64_t)(hkv * p.group + g0 + g) * hd + d] = val * (1.0f / L);
+    const int64_t clen = p.clenbuf ? p.clenbuf[0] : p.cache_len;
+    const int64_t chunk = (clen + p.S - 1) / p.S;
+    const int64_t j0 = split * chunk, j1 = min(clen, j0 + chunk);
+    const int64_t kv4 = ((int64_t)p.n_kv * hd) >> 2;
+    const float4* kb = reinterpret_cast<const float4*>(p.k + (int64_t)hkv * hd) + sub;
+    const float4* vb = reinterpret_cast<const float4*>(p.v + (int64_t)hkv * hd) + sub;
+    const unsigned gmask = 0xFFu << (grp * 8);
+    float4 acc[kFastGroup][VEC];
+    float m[kFastGroup], l[kFastGroup];
+#pragma unroll
+    for (int g = 0; g < kFastGroup; ++g) {
+        m[g] = kNegInf;
+        l[g] = 0.f;
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) acc[g][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int64_t j = j0 + warp * 4 + grp; j < j1; j += kAttnWarps * 4) {
+        float4 kk[VEC], vv[VEC];
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) kk[u] = __ldg(kb + j * kv4 + 8 * u);
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) vv[u] = __ldg(vb + j * kv4 + 8 * u);
+#pragma unroll
+        for (int g = 0; g < kFastGroup; ++g) {
+            if (g < gc) {
+                float s = 0.f;
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) {
+                    const float4 qq = s_q[g * hd4 + sub + 8 * u];
+                    s = fmaf(qq.x, kk[u].x, fmaf(qq.y, kk[u].y, fmaf(qq.z, kk[u].z, fmaf(qq.w, kk[u].w, s))));
+                }
+                s += __shfl_xor_sync(gmask, s, 1);   // the eight lanes of this position only: the other
+                s += __shfl_xor_sync(gmask, s, 2);   // groups of the warp may have left the loop already
+                s += __shfl_xor_sync(gmask, s, 4);
+                const float mn = fmaxf(m[g], s);
+                const float corr = expf(m[g] - mn), pj = expf(s - mn);
+                m[g] = mn;
+                l[g] = fmaf(l[g], corr, pj);
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) {
+                    acc[g][u].x = fmaf(acc[g][u].x, corr, pj * vv[u].x);
+                    acc[g][u].y = fmaf(acc[g][u].y, corr, pj * vv[u].y);
+                    acc[g][u].z = fmaf(acc[g][u].z, corr, pj * vv[u].z);
+                    acc[g][u].w = fmaf(acc[g][u].w, corr, pj * vv[u].w);
+                }
             }
-        } else {
-            mine[g * row + d] = val;
         }
     }
-    if (p.S == 1) return;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int prev = atomicAdd(p.counters + hkv * gridDim.z + gz, 1);
-        s_last = prev == p.S - 1;
-        if (s_last) p.counters[hkv * gridDim.z + gz] = 0;   // ready for the next launch / graph replay
+    // the four position groups of the warp -> one state (every lane ends with the merged values)
+#pragma unroll
+    for (int g = 0; g < kFastGroup; ++g) {
+        if (g < gc) {
+#pragma unroll
+            for (int o = 8; o <= 16; o <<= 1) {
+                const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
+                const float lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+                const float mn = fmaxf(m[g], mo);
+                const float es = expf(m[g] - mn), eo = expf(mo - mn);
+                m[g] = mn;
+                l[g] = fmaf(l[g], es, lo * eo);
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) {
+                    acc[g][u].x = fmaf(acc[g][u].x, es, __shfl_xor_sync(0xffffffffu, acc[g][u].x, o) * eo);
+                    acc[g][u].y = fmaf(acc[g][u].y, es, __shfl_xor_sync(0xffffffffu, acc[g][u].y, o) * eo);
+                    acc[g][u].z = fmaf(acc[g][u].z, es, __shfl_xor_sync(0xffffffffu, acc[g][u].z, o) * eo);
+                    acc[g][u].w = fmaf(acc[g][u].w, es, __shfl_xor_sync(0xffffffffu, acc[g][u].w, o) * eo);
+                }
+            }
+            if (grp == 0) {
+                float* dst = s_part + (warp * gc + g) * row;
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) reinterpret_cast<float4*>(dst)[sub + 8 * u] = acc[g][u];
+                if (sub == 0) {
+                    dst[hd] = m[g];
+                    dst[hd + 1] = l[g];
+                }
+            }
+        }
     }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    const float* all = p.part + (((int64_t)hkv * gridDim.z + gz) * p.S * kAttnGroup) * row;
-    for (int i = threadIdx.x; i < gc * hd; i += blockDim.x) {
-        const int g = i / hd, d = i - g * hd;
-        float O, L;
-        attn_merge(all + g * row, p.S, kAttnGroup * row, hd, d, &O, &L);
-        p.out[(int64_t)(hkv * p.group + g0 + g) * hd + d] = O * (1.0f / L);
-    }
+    attn_finish<kFastGroup>(p, s_part, &s_last, gc, g0, hkv, split, gz, hd, row);
 }
 
 template <typename K, typename... Args>
@@ -301,18 +431,21 @@ int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_
     DeviceState& ds = ctx->devs[q->dev];
     int32_t rc = use_dev(ctx, q->dev);
     if (rc != RSTQ_OK) return rc;
-    const int64_t gz = (group + kAttnGroup - 1) / kAttnGroup;
-    RSTQ_REQUIRE(n_kv * gz <= kAttnCounters, RSTQ_E_LIMIT, "n_kv x ceil(group / %d) = %lld exceeds %d", kAttnGroup,
+    const bool fast = head_dim == 64 || head_dim == 128;
+    const int64_t gs = fast ? kFastGroup : kAttnGroup;                 // query heads per CTA
+    const int64_t gz = (group + gs - 1) / gs;
+    RSTQ_REQUIRE(n_kv * gz <= kAttnCounters, RSTQ_E_LIMIT, "n_kv x ceil(group / %d) = %lld exceeds %d", (int)gs,
                  (long long)(n_kv * gz), kAttnCounters);
-    // slices of the cache: enough CTAs for two per SM, at least 64 positions each; sized from the
+    // slices of the cache: enough CTAs for three per SM, at least 64 positions each; sized from the
     // capacity when the length lives on the device, so that one captured launch serves every length
     const int64_t span = clenbuf ? maxpos : cache_len;
-    int64_t S = (2 * (int64_t)ds.sm_count + n_kv * gz - 1) / (n_kv * gz);
+    int64_t S = (3 * (int64_t)ds.sm_count + n_kv * gz - 1) / (n_kv * gz);
     if (S > (span + 63) / 64) S = (span + 63) / 64;
-    if (S < 1) S = 1;
-    if (S > 65535) S = 65535;
     const int64_t row = head_dim + 4;
-    const int64_t part_bytes = n_kv * gz * S * kAttnGroup * row * 4;
+    if (S > 8 * row - 1) S = 8 * row - 1;   // the final merge keeps S weights + 1 sum per head in shared memory
+    if (S > 512) S = 512;
+    if (S < 1) S = 1;
+    const int64_t part_bytes = n_kv * gz * S * gs * row * 4;
     const bool fresh = ds.attn_scratch_bytes < kAttnCounters * 4 + part_bytes;
     rc = dev_reserve(ds, &ds.attn_scratch, &ds.attn_scratch_bytes, kAttnCounters * 4 + part_bytes);
     if (rc != RSTQ_OK) return rc;
@@ -332,12 +465,20 @@ int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_
     p.head_dim = (int)head_dim;
     p.S = (int)S;
     p.scale = (float)scale;
-    const int64_t gc = group < kAttnGroup ? group : kAttnGroup;
-    const size_t smem = (size_t)(kAttnWarps * gc * row * 4);
-    if (smem > 48 * 1024)
-        RSTQ_CUDA(cudaFuncSetAttribute(gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    RSTQ_CUDA(launch_attn(gqa_decode_kernel, dim3((unsigned)n_kv, (unsigned)S, (unsigned)gz), dim3(kAttnWarps * 32), smem,
-                          ds, p));
+    const int64_t gc = group < gs ? group : gs;
+    const dim3 grid((unsigned)n_kv, (unsigned)S, (unsigned)gz), block(kAttnWarps * 32);
+    if (fast) {
+        const size_t smem = (size_t)((kAttnWarps * gc * row + gc * head_dim) * 4);   // <= 17.5 KB
+        if (head_dim == 64)
+            RSTQ_CUDA(launch_attn(gqa_decode_fast_kernel<2>, grid, block, smem, ds, p));
+        else
+            RSTQ_CUDA(launch_attn(gqa_decode_fast_kernel<4>, grid, block, smem, ds, p));
+    } else {
+        const size_t smem = (size_t)(kAttnWarps * gc * row * 4);
+        if (smem > 48 * 1024)
+            RSTQ_CUDA(cudaFuncSetAttribute(gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        RSTQ_CUDA(launch_attn(gqa_decode_kernel, grid, block, smem, ds, p));
+    }
     ctx->launches++;
     return RSTQ_OK;
 }
