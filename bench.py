@@ -942,20 +942,25 @@ def run_decoder(args):
     """--case decoder:<bits>:<cache_len>: one token through whole Llama-7B-style decoder layers on one GPU --
     the reference's decode chain (test/raster/dl/decoder_layer_gpu_test.clj:59-77): rms-norm + quantize,
     q / k / v, rope, cache append, GQA attention over f32 caches, o, residual, rms-norm + quantize,
-    gate / up, SwiGLU, down, residual -- 19 kernels per layer, distinct layers (weights and caches well
-    over L2), replayed from one CUDA graph with the position in a device buffer."""
+    gate / up, SwiGLU, down, residual -- distinct layers (weights and caches well over L2), replayed from
+    one CUDA graph with the position in a device buffer.  Default: the fused steps and merged q|k|v and
+    gate|up matrices, 10 kernels per layer; `decoder:<bits>:<cache_len>:unfused` runs the reference's
+    chain step by step, 19 kernels per layer."""
     from raster_b200 import Context
     from raster_b200 import _lib as L
     from raster_b200 import synth
     parts = args.case.split(":")
     bits = int(parts[1]) if len(parts) > 1 else 4
     clen = int(parts[2]) if len(parts) > 2 else 1024
+    fused = not (len(parts) > 3 and parts[3] == "unfused")
     H, F, NQ, NKV, HD = 4096, 11008, 32, 32, 128
     kvrow, maxpos = NKV * HD, clen
     ctx = Context(("cuda:0",))
     fmt = L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0
     rng = np.random.default_rng(1)
     shapes = {"q": (H, H), "k": (kvrow, H), "v": (kvrow, H), "o": (H, H), "gate": (F, H), "up": (F, H), "down": (H, F)}
+    if fused:
+        shapes = {"qkv": (H + 2 * kvrow, H), "o": (H, H), "gate_up": (2 * F, H), "down": (H, F)}
     per_layer_w = sum(stream_bytes(o, i, bits) for o, i in shapes.values())
     per_layer_kv = 2 * clen * kvrow * 4
     layers = max(2, -(-3 * ctx.device_info()["l2_bytes"] // (per_layer_w + per_layer_kv)))
@@ -980,7 +985,34 @@ def run_decoder(args):
     blen = ctx.array_to_buffer(np.array([clen], np.int64))
     scale = 1.0 / float(np.sqrt(HD))
 
+    aq, as_, asum = ctx.make_buffer(F, np.int8), ctx.make_buffer(F // 32, f32), ctx.make_buffer(F // 32, np.int32)
+
+    # q | k | v and gate | up as one matrix each (rows concatenated at bind time): one launch writes
+    # one buffer, the next steps read its slices
+    qkv = ctx.make_buffer(H + 2 * kvrow, f32)
+    q_s, k_s, v_s = (ctx.wrap_buffer(qkv.device_ptr + 4 * off, n, f32) for off, n in ((0, H), (H, kvrow), (H + kvrow, kvrow)))
+    gu = ctx.make_buffer(2 * F, f32)
+    g_s, u_s = ctx.wrap_buffer(gu.device_ptr, F, f32), ctx.wrap_buffer(gu.device_ptr + 4 * F, F, f32)
+
+    def fused_pass():
+        # 10 kernels per layer: the residual adds ride the next norm + quantizer, q / k / v are one
+        # matrix and gate / up another, rope and both cache appends are one launch, SwiGLU writes the
+        # down projection's int8 input directly.  x holds the residual stream, `down` the last
+        # layer's MLP output still to be added to it.
+        for lay in stack:
+            ctx.residual_rms_norm_quant_act(x, down, h, lay["n1"], xq, xs, xsum, 1, H)
+            ctx.qmatmul_prequant(lay["qkv"], xq, xs, xsum, qkv, 1)
+            ctx.rope_append(q_s, k_s, v_s, lay["kc"], lay["vc"], NQ, NKV, HD, 10000.0, maxpos=maxpos, posbuf=bpos)
+            ctx.gqa_decode_attention(q_s, lay["kc"], lay["vc"], att, 0, NQ, NQ // NKV, NKV, HD, maxpos, scale, clenbuf=blen)
+            ctx.qmatmul(lay["o"], att, o_, 1)
+            ctx.residual_rms_norm_quant_act(h, o_, x, lay["n2"], xq, xs, xsum, 1, H)
+            ctx.qmatmul_prequant(lay["gate_up"], xq, xs, xsum, gu, 1)
+            ctx.silu_mul_quant_act(g_s, u_s, aq, as_, asum, F)
+            ctx.qmatmul_prequant(lay["down"], aq, as_, asum, down, 1)
+
     def one_pass():
+        if fused:
+            return fused_pass()
         for lay in stack:
             ctx.rms_norm_quant_act(x, lay["n1"], xq, xs, xsum, 1, H)
             ctx.qmatmul_prequant(lay["q"], xq, xs, xsum, q, 1)
@@ -1000,6 +1032,7 @@ def run_decoder(args):
             ctx.qmatmul(lay["down"], act, down, 1)
             ctx.residual_add(h, down, x, H)
 
+    down.fill_bytes(0)
     n0 = ctx.launch_count()
     one_pass()
     ctx.sync()

@@ -294,6 +294,24 @@ RSTQ_API int32_t rstq_rope_pos(rstq_ctx* ctx, rstq_buf* x, rstq_buf* out, int64_
                                double theta, int64_t pos, rstq_buf* posbuf);
 RSTQ_API int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, int64_t kvrow, int64_t pos,
                                 int64_t maxpos, rstq_buf* posbuf);
+/* Fusions the chain invites (no counterpart in the reference; each equals its steps run one by one,
+ * bit for bit):
+ *   rstq_rope_append                  rope of q and k in place + append of the turned k and of v to
+ *                                     their caches: four steps, one launch;
+ *   rstq_residual_rms_norm_quant_act  sum = a + b (stored: the residual stream), then rms-norm of
+ *                                     sum quantized to int8 blocks; sum may not alias a or b;
+ *   rstq_silu_mul_quant_act / rstq_gelu_mul_quant_act   the gated activation quantized to int8
+ *                                     blocks (the input of the down projection), n % 32 == 0. */
+RSTQ_API int32_t rstq_rope_append(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* kcache,
+                                  rstq_buf* vcache, int64_t n_q, int64_t n_kv, int64_t head_dim, double theta,
+                                  int64_t pos, int64_t maxpos, rstq_buf* posbuf);
+RSTQ_API int32_t rstq_residual_rms_norm_quant_act(rstq_ctx* ctx, rstq_buf* a, rstq_buf* b, rstq_buf* sum,
+                                                  rstq_buf* weight, rstq_buf* xq, rstq_buf* xs, rstq_buf* xsum,
+                                                  int64_t rows, int64_t features, double eps, double gain_offset);
+RSTQ_API int32_t rstq_silu_mul_quant_act(rstq_ctx* ctx, rstq_buf* gate, rstq_buf* up, rstq_buf* xq, rstq_buf* xs,
+                                         rstq_buf* xsum, int64_t n);
+RSTQ_API int32_t rstq_gelu_mul_quant_act(rstq_ctx* ctx, rstq_buf* gate, rstq_buf* up, rstq_buf* xq, rstq_buf* xs,
+                                         rstq_buf* xsum, int64_t n);
 RSTQ_API int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
                                            int64_t cache_len, rstq_buf* clenbuf, int64_t n_q, int64_t group,
                                            int64_t n_kv, int64_t head_dim, int64_t maxpos, double scale);

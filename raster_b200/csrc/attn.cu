@@ -54,6 +54,40 @@ kv_append_kernel(const float* __restrict__ src, float* __restrict__ cache, int64
         cache[p * kvrow + i] = src[i];
 }
 
+// rope(q), rope(k), append k, append v of one token in ONE launch (four steps of the reference's
+// chain): q is turned in place; k is turned, stored back and written to its cache row; v is copied
+// to its cache row.  One thread per rotation pair of q and k, and per pair of v elements.
+__global__ void __launch_bounds__(256)
+rope_append_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
+                   float* __restrict__ kcache, float* __restrict__ vcache, int64_t n_q, int64_t n_kv, int64_t head_dim,
+                   double ln_theta, int64_t pos, const int64_t* __restrict__ posbuf) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int64_t h2 = head_dim >> 1, kvrow = n_kv * head_dim;
+    const int64_t nrot = (n_q + n_kv) * h2, idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const int64_t p = posbuf ? posbuf[0] : pos;
+    if (idx < nrot) {
+        const int64_t h = idx / h2, i = idx - h * h2;
+        const bool isk = h >= n_q;
+        float* x = isk ? k + (h - n_q) * head_dim : q + h * head_dim;
+        const double freq = exp((-2.0 * (double)i) / (double)head_dim * ln_theta);
+        double s, c;
+        sincos((double)p * freq, &s, &c);
+        const double x0 = (double)x[i], x1 = (double)x[i + h2];
+        const float y0 = (float)(x0 * c - x1 * s), y1 = (float)(x1 * c + x0 * s);
+        x[i] = y0;
+        x[i + h2] = y1;
+        if (isk) {
+            float* dst = kcache + p * kvrow + (h - n_q) * head_dim;
+            dst[i] = y0;
+            dst[i + h2] = y1;
+        }
+    } else if (idx < nrot + n_kv * h2) {
+        const int64_t e = (idx - nrot) * 2;
+        *reinterpret_cast<float2*>(vcache + p * kvrow + e) = *reinterpret_cast<const float2*>(v + e);
+    }
+}
+
 struct AttnParams {
     const float *q, *k, *v;
     float* out;
@@ -408,6 +442,33 @@ int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, int64_t kv
     if (ctas > ds.sm_count * 4) ctas = ds.sm_count * 4;
     RSTQ_CUDA(launch_attn(kv_append_kernel, dim3((unsigned)ctas), dim3(256), 0, ds, (const float*)src->ptr,
                           (float*)cache->ptr, kvrow, pos, posbuf ? (const int64_t*)posbuf->ptr : (const int64_t*)nullptr));
+    ctx->launches++;
+    return RSTQ_OK;
+}
+
+int32_t rstq_rope_append(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* kcache, rstq_buf* vcache,
+                         int64_t n_q, int64_t n_kv, int64_t head_dim, double theta, int64_t pos, int64_t maxpos,
+                         rstq_buf* posbuf) {
+    RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
+    RSTQ_REQUIRE(n_q >= 1 && n_kv >= 1 && head_dim >= 2 && head_dim % 2 == 0 && theta > 0.0 && maxpos >= 1 &&
+                     (posbuf || (pos >= 0 && pos < maxpos)),
+                 RSTQ_E_SHAPE, "n_q = %lld, n_kv = %lld, head_dim = %lld (even), pos = %lld of %lld", (long long)n_q,
+                 (long long)n_kv, (long long)head_dim, (long long)pos, (long long)maxpos);
+    const int64_t kvrow = n_kv * head_dim;
+    RSTQ_REQUIRE(attn_buf(q, ctx, n_q * head_dim * 4) && attn_buf(k, ctx, kvrow * 4) && attn_buf(v, ctx, kvrow * 4) &&
+                     attn_buf(kcache, ctx, maxpos * kvrow * 4) && attn_buf(vcache, ctx, maxpos * kvrow * 4) &&
+                     (!posbuf || attn_buf(posbuf, ctx, 8)),
+                 RSTQ_E_INVALID, "invalid, unaligned or too small buffer (the caches hold maxpos rows)");
+    RSTQ_REQUIRE(q->dev == k->dev && q->dev == v->dev && q->dev == kcache->dev && q->dev == vcache->dev &&
+                     (!posbuf || posbuf->dev == q->dev),
+                 RSTQ_E_DEVICE, "buffers live on different devices");
+    DeviceState& ds = ctx->devs[q->dev];
+    int32_t rc = use_dev(ctx, q->dev);
+    if (rc != RSTQ_OK) return rc;
+    const int64_t items = (n_q + 2 * n_kv) * (head_dim / 2);
+    RSTQ_CUDA(launch_attn(rope_append_kernel, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, ds, (float*)q->ptr,
+                          (float*)k->ptr, (const float*)v->ptr, (float*)kcache->ptr, (float*)vcache->ptr, n_q, n_kv,
+                          head_dim, log(theta), pos, posbuf ? (const int64_t*)posbuf->ptr : (const int64_t*)nullptr));
     ctx->launches++;
     return RSTQ_OK;
 }

@@ -301,6 +301,26 @@ class Context:
         L.check(self.lib.rstq_kv_append(self.handle, src.handle, cache.handle, kvrow, pos, maxpos,
                                         posbuf.handle if posbuf is not None else None))
 
+    def rope_append(self, q, k, v, kcache, vcache, n_q, n_kv, head_dim, theta, pos=0, maxpos=1, posbuf=None) -> None:
+        L.check(self.lib.rstq_rope_append(self.handle, q.handle, k.handle, v.handle, kcache.handle, vcache.handle,
+                                          n_q, n_kv, head_dim, theta, pos, maxpos,
+                                          posbuf.handle if posbuf is not None else None))
+
+    def residual_rms_norm_quant_act(self, a, b, total, weight, xq, xs, xsum, rows, features, eps=1e-6,
+                                    gain_offset=0.0) -> None:
+        L.check(self.lib.rstq_residual_rms_norm_quant_act(self.handle, a.handle, b.handle, total.handle, weight.handle,
+                                                          xq.handle, xs.handle,
+                                                          xsum.handle if xsum is not None else None, rows, features,
+                                                          eps, gain_offset))
+
+    def silu_mul_quant_act(self, gate, up, xq, xs, xsum, n) -> None:
+        L.check(self.lib.rstq_silu_mul_quant_act(self.handle, gate.handle, up.handle, xq.handle, xs.handle,
+                                                 xsum.handle if xsum is not None else None, n))
+
+    def gelu_mul_quant_act(self, gate, up, xq, xs, xsum, n) -> None:
+        L.check(self.lib.rstq_gelu_mul_quant_act(self.handle, gate.handle, up.handle, xq.handle, xs.handle,
+                                                 xsum.handle if xsum is not None else None, n))
+
     def gqa_decode_attention(self, q, k, v, out, cache_len, n_q, group, n_kv, head_dim, maxpos, scale,
                              clenbuf=None) -> None:
         L.check(self.lib.rstq_gqa_decode_attention(self.handle, q.handle, k.handle, v.handle, out.handle, cache_len,

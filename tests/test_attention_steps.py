@@ -177,3 +177,35 @@ def test_attention_contract_errors(ctx):
         ctx.rope_pos(b, b, 4, 7, 10000.0, 0)                                # odd head_dim
     assert e.value.code == L.E_SHAPE
     b.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_q,n_kv,hd", [(32, 8, 128), (8, 8, 64), (3, 1, 6)])
+def test_rope_append_equals_its_four_steps(ctx, n_q, n_kv, hd):
+    kvrow, maxpos, pos, theta = n_kv * hd, 9, 6, 10000.0
+    q, k, v = synth.normal(51, n_q * hd), synth.normal(52, kvrow), synth.normal(53, kvrow)
+    cache0 = synth.normal(54, maxpos * kvrow)
+    # the steps one by one
+    bq, bk, bv = ctx.array_to_buffer(q), ctx.array_to_buffer(k), ctx.array_to_buffer(v)
+    bkc, bvc = ctx.array_to_buffer(cache0), ctx.array_to_buffer(cache0)
+    ctx.rope_pos(bq, bq, n_q, hd, theta, pos)
+    ctx.rope_pos(bk, bk, n_kv, hd, theta, pos)
+    ctx.kv_append(bk, bkc, kvrow, pos, maxpos)
+    ctx.kv_append(bv, bvc, kvrow, pos, maxpos)
+    ctx.sync()
+    want = [b.download() for b in (bq, bk, bkc, bvc)]
+    # one launch, position from the device
+    fq, fk, fv = ctx.array_to_buffer(q), ctx.array_to_buffer(k), ctx.array_to_buffer(v)
+    fkc, fvc = ctx.array_to_buffer(cache0), ctx.array_to_buffer(cache0)
+    bp = ctx.array_to_buffer(np.array([pos], np.int64))
+    ctx.rope_append(fq, fk, fv, fkc, fvc, n_q, n_kv, hd, theta, maxpos=maxpos, posbuf=bp)
+    ctx.sync()
+    got = [b.download() for b in (fq, fk, fkc, fvc)]
+    for g, w in zip(got, want):
+        assert np.array_equal(g.view(np.uint32), w.view(np.uint32))
+    assert relerr(got[0], orc.rope_pos(q, n_q, hd, theta, pos)) <= 1e-6
+    with pytest.raises(L.RstqError) as e:
+        ctx.rope_append(fq, fk, fv, fkc, fvc, n_q, n_kv, hd, theta, 9, maxpos)
+    assert e.value.code == L.E_SHAPE
+    for o in (bq, bk, bv, bkc, bvc, fq, fk, fv, fkc, fvc, bp):
+        o.free()

@@ -94,6 +94,56 @@ def test_fused_norm_quantizer_equals_norm_then_quantizer(ctx, rows, features):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("rows,features", [(1, 4096), (3, 11008), (2, 32)])
+def test_fused_residual_norm_quantizer_equals_its_steps(ctx, rows, features):
+    a, b = synth.normal(81, rows * features), synth.normal(82, rows * features)
+    w = synth.normal(83, features, 0.1) + np.float32(1.0)
+    nb = features // 32
+    ba, bb, bw = ctx.array_to_buffer(a), ctx.array_to_buffer(b), ctx.array_to_buffer(w)
+    bsum1, bsum2 = ctx.make_buffer(rows * features, np.float32), ctx.make_buffer(rows * features, np.float32)
+    q1, s1, z1 = (ctx.make_buffer(rows * features, np.int8), ctx.make_buffer(rows * nb, np.float32),
+                  ctx.make_buffer(rows * nb, np.int32))
+    q2, s2, z2 = (ctx.make_buffer(rows * features, np.int8), ctx.make_buffer(rows * nb, np.float32),
+                  ctx.make_buffer(rows * nb, np.int32))
+    ctx.residual_add(ba, bb, bsum1, rows * features)
+    ctx.rms_norm_quant_act(bsum1, bw, q1, s1, z1, rows, features, 1e-6, 0.0)
+    ctx.residual_rms_norm_quant_act(ba, bb, bsum2, bw, q2, s2, z2, rows, features, 1e-6, 0.0)
+    ctx.sync()
+    assert np.array_equal(bsum2.download(), orc.residual_add(a, b))
+    assert np.array_equal(bsum1.download().view(np.uint32), bsum2.download().view(np.uint32))
+    assert np.array_equal(q1.download(), q2.download())
+    assert np.array_equal(s1.download().view(np.uint32), s2.download().view(np.uint32))
+    assert np.array_equal(z1.download(), z2.download())
+    from raster_b200 import _lib as L
+    with pytest.raises(L.RstqError) as e:
+        ctx.residual_rms_norm_quant_act(ba, bb, ba, bw, q2, s2, z2, rows, features)    # sum aliases an input
+    assert e.value.code == L.E_INVALID
+    for o in (ba, bb, bw, bsum1, bsum2, q1, s1, z1, q2, s2, z2):
+        o.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [32, 11008, 28672])
+def test_fused_gated_quantizer_equals_its_steps(ctx, n):
+    g, u = synth.normal(85, n) * np.float32(3.0), synth.normal(86, n)
+    bg, bu, bact = ctx.array_to_buffer(g), ctx.array_to_buffer(u), ctx.make_buffer(n, np.float32)
+    for fused, plain in ((ctx.silu_mul_quant_act, ctx.silu_mul), (ctx.gelu_mul_quant_act, ctx.gelu_mul)):
+        q1, s1, z1 = ctx.make_buffer(n, np.int8), ctx.make_buffer(n // 32, np.float32), ctx.make_buffer(n // 32, np.int32)
+        q2, s2, z2 = ctx.make_buffer(n, np.int8), ctx.make_buffer(n // 32, np.float32), ctx.make_buffer(n // 32, np.int32)
+        plain(bg, bu, bact, n)
+        ctx.quant_act_i8(bact, q1, s1, z1, 1, n)
+        fused(bg, bu, q2, s2, z2, n)
+        ctx.sync()
+        assert np.array_equal(q1.download(), q2.download())
+        assert np.array_equal(s1.download().view(np.uint32), s2.download().view(np.uint32))
+        assert np.array_equal(z1.download(), z2.download())
+        for o in (q1, s1, z1, q2, s2, z2):
+            o.free()
+    for o in (bg, bu, bact):
+        o.free()
+
+
+@pytest.mark.gpu
 def test_host_mirror_of_the_neighbours(ctx):
     from raster_b200 import nn
     g, u = synth.normal(91, 300), synth.normal(92, 300)
