@@ -891,7 +891,7 @@ static int32_t cached_weight(rstq_ctx* ctx, const void* codes, const float* scal
 extern "C++" {
 template <typename Body>
 int32_t host_roundtrip(rstq_ctx* ctx, int dev, const void* x, int64_t x_bytes, void* y,
-                              int64_t y_bytes, Body body) {
+                              int64_t y_bytes, Body body, bool y_write_only = false) {
     DeviceState& ds = ctx->devs[dev];
     RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "host-array operators cannot be captured");
     int32_t rc = use_dev(ctx, dev);
@@ -906,8 +906,12 @@ int32_t host_roundtrip(rstq_ctx* ctx, int dev, const void* x, int64_t x_bytes, v
     // addressing makes it device-visible): one PCIe round trip instead of a copy engine launch.
     const bool direct = x_bytes <= 256 * 1024;
     if (!direct) RSTQ_CUDA(cudaMemcpyAsync(dp, hp, (size_t)x_bytes, cudaMemcpyHostToDevice, ds.stream));
-    if ((rc = body(direct ? (void*)hp : (void*)dp, (void*)(dp + xa))) != RSTQ_OK) return rc;
-    RSTQ_CUDA(cudaMemcpyAsync(hp + xa, dp + xa, (size_t)y_bytes, cudaMemcpyDeviceToHost, ds.stream));
+    // A small result the kernels only write goes straight to the pinned host copy too (posted
+    // PCIe writes during the kernel instead of a copy-engine launch after it).
+    const bool y_direct = y_write_only && y_bytes <= 64 * 1024;
+    if ((rc = body(direct ? (void*)hp : (void*)dp, y_direct ? (void*)(hp + xa) : (void*)(dp + xa))) != RSTQ_OK) return rc;
+    if (!y_direct)
+        RSTQ_CUDA(cudaMemcpyAsync(hp + xa, dp + xa, (size_t)y_bytes, cudaMemcpyDeviceToHost, ds.stream));
     RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
     memcpy(y, hp + xa, (size_t)y_bytes);
     return RSTQ_OK;
@@ -926,7 +930,7 @@ static int32_t qlinear_i8_impl(rstq_ctx* ctx, const float* x, const void* wqi, c
     if (rc != RSTQ_OK) return rc;
     return host_roundtrip(ctx, w->dev, x, in * 4, y, out * 4, [&](void* dx, void* dy) {
         return matmul_device(ctx, w, dx, dy, 1, RSTQ_F32, RSTQ_F32, RSTQ_MODE_A8);
-    });
+    }, true);  // M = 1: the decode kernel stores each result once and never reads y
 }
 
 int32_t rstq_qlinear_i8(rstq_ctx* ctx, const float* x, const void* wqi, const float* wsi, float* y,
