@@ -862,20 +862,23 @@ def run_dx(args):
 
 
 def run_q4k(args):
-    """--case q4k:<out>:<in>:<M>: the Q4_K operator (q8_K quantizer + decode kernel + min-term GEMV) on
+    """--case q4k:<out>:<in>:<M> / q6k:<out>:<in>:<M>: the Q4_K operator (q8_K quantizer + decode kernel +
+    min-term GEMV) or the Q6_K operator (q8_K quantizer + decode kernel over twin rows + pair sum) on
     distinct weight copies (more than L2 in total), timed with CUDA events per call."""
     from raster_b200 import Context
     from raster_b200 import _lib as L
-    _, out, in_, M = args.case.split(":")
+    kind, out, in_, M = args.case.split(":")
     out, in_, M = int(out), int(in_), int(M)
     rng = np.random.default_rng(0)
     ctx = Context(("cuda:0",))
+    enc6 = {"wq": rng.integers(0, 64, out * in_, dtype=np.uint8), "sc": rng.integers(0, 128, out * in_ // 16, dtype=np.int8),
+            "ds": (np.abs(rng.standard_normal(out * in_ // 256)) * 1e-4).astype(np.float32)} if kind == "q6k" else None
     enc = {"wq": rng.integers(0, 256, out * in_ // 2, dtype=np.uint8),
            "da": (np.abs(rng.standard_normal(out * in_ // 256)) * 1e-3).astype(np.float32),
            "db": (np.abs(rng.standard_normal(out * in_ // 256)) * 1e-3).astype(np.float32),
            "aq": rng.integers(0, 64, out * in_ // 32, dtype=np.int8),
            "bq": rng.integers(-32, 32, out * in_ // 32, dtype=np.int8)}
-    w0 = ctx.bind_weight_q4k(enc, out, in_)
+    w0 = ctx.bind_weight_q6k(enc6, out, in_) if kind == "q6k" else ctx.bind_weight_q4k(enc, out, in_)
     R = max(2, -(-int(1.2 * ctx.device_info()["l2_bytes"]) // w0.device_bytes))
     ws = [w0] + [w0.clone() for _ in range(R - 1)]
     bx, by = ctx.array_to_buffer(rng.standard_normal(M * in_).astype(np.float32)), ctx.make_buffer(M * out, np.float32)
@@ -1121,7 +1124,7 @@ def main():
         return run_layer(args)
     if args.case and args.case.startswith("dx"):
         return run_dx(args)
-    if args.case and args.case.startswith("q4k"):
+    if args.case and args.case.startswith(("q4k", "q6k")):
         return run_q4k(args)
     if args.case and args.case.startswith("attn"):
         return run_attn(args)

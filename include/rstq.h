@@ -158,6 +158,13 @@ RSTQ_API int32_t rstq_weight_bind_shard(rstq_ctx* ctx, rstq_weight** w, const vo
 RSTQ_API int32_t rstq_weight_bind_q4k(rstq_ctx* ctx, rstq_weight** w, const void* wq, const float* da,
                                       const float* db, const int8_t* aq, const int8_t* bq, int32_t dev,
                                       int64_t out, int64_t in);
+/* Q6_K from the arrays quantize-weight-q6k makes (src/raster/compiler/backend/cpu/quant.clj:222-262):
+ * wq one unsigned 6-bit code per byte [out, in] (zero point 32), sc int8 [out, in/16], ds f32
+ * [out, in/256]; in % 256 == 0.  Used with rstq_qmatmul / rstq_qmatmul_host (f32 activations,
+ * MODE_A8: q8_K quantizer + qmatmul-q6k, the `:apply` of :q6_K, src/raster/quant/core.clj:68-75).
+ * Held on the device as two 8-bit rows per matrix row (twice the reference's code bytes). */
+RSTQ_API int32_t rstq_weight_bind_q6k(rstq_ctx* ctx, rstq_weight** w, const void* wq, const int8_t* sc,
+                                      const float* ds, int32_t dev, int64_t out, int64_t in);
 /* Second device copy of a bound weight at a distinct address (cold-cache measurement). */
 RSTQ_API int32_t rstq_weight_clone(rstq_weight* src, rstq_weight** w);
 RSTQ_API int32_t rstq_weight_free(rstq_weight* w);

@@ -35,6 +35,7 @@ SIGNATURES = {
     "rstq_weight_bind": [vp, pp, vp, vp, i32, i64, i64, i32, i32],
     "rstq_weight_bind_shard": [vp, pp, vp, vp, i32, i64, i64, i32, i32, i32, i32, i32],
     "rstq_weight_bind_q4k": [vp, pp, vp, vp, vp, vp, vp, i32, i64, i64],
+    "rstq_weight_bind_q6k": [vp, pp, vp, vp, vp, i32, i64, i64],
     "rstq_weight_clone": [vp, pp],
     "rstq_weight_free": [vp],
     "rstq_weight_info": [vp, C.POINTER(i64)],

@@ -161,6 +161,21 @@ static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, int64_t out,
 int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M, int act_dtype,
                       int out_dtype, int mode, const TpFuse* tp) {
     DeviceState& ds = ctx->devs[w->dev];
+    if (w->pair_out) {
+        // Q6_K: q8_K activations (the decode kernel wants the code sums per 32 elements), the twin
+        // rows through the decode kernel, then the pairs added (src/raster/quant/core.clj:68-75).
+        RSTQ_REQUIRE(mode == RSTQ_MODE_A8 && act_dtype == RSTQ_F32 && out_dtype == RSTQ_F32, RSTQ_E_INVALID,
+                     "a Q6_K weight takes f32 activations in MODE_A8 and writes f32");
+        RSTQ_REQUIRE(!tp, RSTQ_E_INVALID, "Q6_K weights are not sharded");
+        ActScratch s;
+        int32_t rc = act_scratch(ds, M, w->in, &s);
+        if (rc != RSTQ_OK) return rc;
+        if ((rc = dev_reserve(ds, &ds.kq_scratch, &ds.kq_scratch_bytes, M * w->out * 4)) != RSTQ_OK) return rc;
+        rc = launch_quant_act_q8k(ctx, ds, (const float*)x, s.xq, nullptr, s.xs, s.xsum, M, w->in, 32);
+        if (rc != RSTQ_OK) return rc;
+        if ((rc = run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)ds.kq_scratch, M)) != RSTQ_OK) return rc;
+        return launch_pair_sum(ctx, ds, (const float*)ds.kq_scratch, (float*)y, M, w->pair_out);
+    }
     if (w->mins) {
         // Q4_K: the one arithmetic the reference has for it -- q8_K activations, integer sub-block
         // dots, scale / min fold (src/raster/quant/core.clj:57-66) -- at any M, on the decode kernel.
@@ -424,6 +439,7 @@ int32_t rstq_shutdown(rstq_ctx* ctx) {
         if (ds.act_scratch) cudaFree(ds.act_scratch);
         if (ds.gemm_scratch) cudaFree(ds.gemm_scratch);
         if (ds.attn_scratch) cudaFree(ds.attn_scratch);
+        if (ds.kq_scratch) cudaFree(ds.kq_scratch);
         if (ds.partials) cudaFree(ds.partials);
         if (ds.counters) cudaFree(ds.counters);
         if (ds.status) cudaFree(ds.status);
@@ -669,6 +685,41 @@ int32_t rstq_weight_bind_q4k(rstq_ctx* ctx, rstq_weight** wout, const void* wq, 
     return RSTQ_OK;
 }
 
+int32_t rstq_weight_bind_q6k(rstq_ctx* ctx, rstq_weight** wout, const void* wq, const int8_t* sc, const float* dsup,
+                             int32_t dev, int64_t out, int64_t in) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(wout && wq && sc && dsup, RSTQ_E_INVALID, "null argument");
+    *wout = nullptr;
+    RSTQ_REQUIRE(out >= 1 && in >= 256 && in % 256 == 0, RSTQ_E_SHAPE,
+                 "in = %lld must be a positive multiple of 256 and out = %lld >= 1", (long long)in, (long long)out);
+    const int64_t nb = in / 32, nsb = in / 256;
+    const uint8_t* q = (const uint8_t*)wq;
+    std::vector<uint8_t> codes((size_t)(2 * out * in));
+    std::vector<float> scales((size_t)(2 * out * nb));
+    for (int64_t o = 0; o < out; ++o) {
+        uint8_t* ra = codes.data() + (2 * o) * in;
+        uint8_t* rb = ra + in;
+        for (int64_t b = 0; b < nb; ++b) {
+            const uint8_t* src = q + o * in + b * 32;
+            memcpy(ra + b * 32, src, 16);            // twin A: even sub-block, zero point elsewhere
+            memset(ra + b * 32 + 16, 32, 16);
+            memset(rb + b * 32, 32, 16);             // twin B: odd sub-block
+            memcpy(rb + b * 32 + 16, src + 16, 16);
+            const double d = (double)dsup[o * nsb + b / 8];
+            scales[(size_t)((2 * o) * nb + b)] = (float)(d * (double)sc[o * (in / 16) + 2 * b]);
+            scales[(size_t)((2 * o + 1) * nb + b)] = (float)(d * (double)sc[o * (in / 16) + 2 * b + 1]);
+        }
+    }
+    rstq_weight* w = nullptr;
+    int32_t rc = bind_impl(ctx, &w, codes.data(), scales.data(), dev, 2 * out, in, RSTQ_FMT_Q8_0, RSTQ_LAYOUT_ROWMAJOR,
+                           RSTQ_SPLIT_NONE, 0, 1);
+    if (rc != RSTQ_OK) return rc;
+    w->zp = 32;
+    w->pair_out = out;
+    *wout = w;
+    return RSTQ_OK;
+}
+
 int32_t rstq_weight_clone(rstq_weight* src, rstq_weight** wout) {
     RSTQ_REQUIRE(wout, RSTQ_E_INVALID, "null argument");
     *wout = nullptr;
@@ -722,13 +773,15 @@ int32_t rstq_weight_free(rstq_weight* w) {
 int32_t rstq_weight_info(rstq_weight* w, int64_t* out6) {
     RSTQ_REQUIRE(ok_w(w), RSTQ_E_INVALID, "invalid weight handle");
     RSTQ_REQUIRE(out6, RSTQ_E_INVALID, "null argument");
-    out6[0] = w->out;
+    out6[0] = w->pair_out ? w->pair_out : w->out;
     out6[1] = w->in;
-    out6[2] = w->bits;
+    out6[2] = w->pair_out ? 6 : w->bits;
     out6[3] = w->data_bytes + (w->mins ? w->out * w->nb * 4 : 0);
     // Q4_K as the reference stores it: nibbles, da + db per super-block, aq + bq per sub-block
     out6[4] = w->mins ? w->out * w->in / 2 + w->out * (w->in / 256) * 8 + w->out * w->nb * 2
                       : w->out * w->in * w->bits / 8 + w->out * w->nb * 4;
+    // Q6_K as the reference stores it: a byte per code, an int8 scale per 16, an f32 per 256
+    if (w->pair_out) out6[4] = w->pair_out * (w->in + w->in / 16 + (w->in / 256) * 4);
     out6[5] = w->dev;
     return RSTQ_OK;
 }
@@ -788,7 +841,8 @@ int32_t rstq_qmatmul(rstq_ctx* ctx, rstq_weight* w, rstq_buf* x, rstq_buf* y, in
     RSTQ_REQUIRE(mode == RSTQ_MODE_F || mode == RSTQ_MODE_A8, RSTQ_E_INVALID, "bad mode");
     int32_t rc;
     if ((rc = need_bytes(x, M * w->in * (act_dtype == RSTQ_F32 ? 4 : 2), "x")) != RSTQ_OK) return rc;
-    if ((rc = need_bytes(y, M * w->out * (out_dtype == RSTQ_F32 ? 4 : 2), "y")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(y, M * (w->pair_out ? w->pair_out : w->out) * (out_dtype == RSTQ_F32 ? 4 : 2), "y")) != RSTQ_OK)
+        return rc;
     RSTQ_REQUIRE(x->dev == w->dev && y->dev == w->dev, RSTQ_E_DEVICE,
                  "weight and buffers live on different devices");
     if ((rc = use_dev(ctx, w->dev)) != RSTQ_OK) return rc;
@@ -800,6 +854,7 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
     CHECK_CTX(ctx);
     RSTQ_REQUIRE(ok_w(w) && w->ctx == ctx, RSTQ_E_INVALID, "invalid weight handle");
     RSTQ_REQUIRE(M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)M);
+    RSTQ_REQUIRE(!w->pair_out, RSTQ_E_INVALID, "Q6_K weights go through rstq_qmatmul");
     int32_t rc;
     if (w->mins) {
         // qmatmul-q4k-dp4a! (src/raster/quant/kernels_k.clj:195-237): q8_K activations, xs per
@@ -1063,7 +1118,7 @@ int32_t rstq_qmatmul_host(rstq_ctx* ctx, rstq_weight* w, const void* x, float* y
     RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "bad act dtype");
     RSTQ_REQUIRE(mode == RSTQ_MODE_F || mode == RSTQ_MODE_A8, RSTQ_E_INVALID, "bad mode");
     const int64_t xe = act_dtype == RSTQ_F32 ? 4 : 2;
-    return host_roundtrip(ctx, w->dev, x, M * w->in * xe, y, M * w->out * 4,
+    return host_roundtrip(ctx, w->dev, x, M * w->in * xe, y, M * (w->pair_out ? w->pair_out : w->out) * 4,
                           [&](void* dx, void* dy) {
                               return matmul_device(ctx, w, dx, dy, M, act_dtype, RSTQ_F32, mode);
                           });

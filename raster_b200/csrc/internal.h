@@ -76,6 +76,8 @@ struct DeviceState {
     int64_t counters_len = 0;
     void* gemm_scratch = nullptr;  // fp16 activations + row exponents of the GEMM path
     int64_t gemm_scratch_bytes = 0;
+    void* kq_scratch = nullptr;    // Q6_K: the twin-row results before they are added in pairs
+    int64_t kq_scratch_bytes = 0;
     void* attn_scratch = nullptr;  // decode attention: arrival counters + per-slice softmax states
     int64_t attn_scratch_bytes = 0;
     void* pinned = nullptr;        // host staging for the host-array entry points
@@ -139,6 +141,7 @@ struct rstq_weight {
     int8_t* raw_codes = nullptr;   // row-major signed codes / scales as the reference holds them:
     float* raw_scales = nullptr;   // made on first use by the backward-data operator
     float* mins = nullptr;         // Q4_K only: per-sub-block minima db*bq, [out, nb]; zp is 0 then
+    int64_t pair_out = 0;          // Q6_K only: logical rows; `out` = 2 * pair_out twin rows, y[o] = t[2o] + t[2o+1]
 };
 
 struct rstq_graph {
@@ -174,6 +177,7 @@ int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
 int32_t launch_quant_act_q8k(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs, float* xs32,
                              int32_t* bsums, int64_t rows, int64_t in, int sub);
 int32_t launch_expand_scales(rstq_ctx* ctx, DeviceState& ds, const float* xs, float* xs32, int64_t n32);
+int32_t launch_pair_sum(rstq_ctx* ctx, DeviceState& ds, const float* t, float* y, int64_t M, int64_t out);
 int32_t launch_q4k_min(rstq_ctx* ctx, DeviceState& ds, const float* mins, const float* xs32, const int32_t* bsums,
                        float* y, int64_t M, int64_t nb, int64_t out);
 // actquant.cu

@@ -1,5 +1,15 @@
-// Q4_K, the reference's asymmetric 4-bit super-block format, on the decode kernel.
+// Q4_K and Q6_K, the reference's super-block formats, on the decode kernel.
 //
+// Q6_K (symmetric, 16 sub-blocks of 16 with an integer scale each, codes 0..63 with zero point 32;
+// qmatmul-q6k-composable!, src/raster/quant/kernels_k.clj:50-79): a 16-element sub-block has no
+// place in a 32-element block with one scale, so a row is bound as TWO rows of 8-bit units -- twin A
+// keeps the codes of the even sub-blocks and holds the zero point (32) in the odd ones, twin B the
+// converse; block scales ds*sc_even and ds*sc_odd.  A zero-point code contributes (32 - 32) * x = 0,
+// so each twin's integer dots are exactly dp_j - 32 * bsum_j of its own sub-blocks and
+// y[o] = t[2o] + t[2o+1] (pair_sum_kernel).  Twice the code bytes of the reference's layout: a first
+// correct path, not the final layout.
+//
+// Q4_K:
 // The reference's Q4_K GEMV (qmatmul-q4k-composable! / qmatmul-q4k-gpu! / qmatmul-q4k-dp4a!,
 // src/raster/quant/kernels_k.clj:15-48, :156-186, :195-237) computes, per output row o,
 //   y[o] = sum over super-blocks sb of dact[sb] * sum over j < 8 of
@@ -121,6 +131,17 @@ q4k_min_kernel(const float* __restrict__ mins, const float* __restrict__ xs32, c
     }
 }
 
+// y[m, o] = t[m, 2o] + t[m, 2o + 1]: the two twin rows of a Q6_K row (see rstq_weight_bind_q6k)
+__global__ void __launch_bounds__(256)
+pair_sum_kernel(const float2* __restrict__ t, float* __restrict__ y, int64_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float2 v = t[i];
+        y[i] = v.x + v.y;
+    }
+}
+
 template <typename K, typename... Args>
 static cudaError_t launch_pdl(K kernel, dim3 grid, const DeviceState& ds, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -174,6 +195,15 @@ int32_t launch_q4k_min(rstq_ctx* ctx, DeviceState& ds, const float* mins, const 
     cfg.attrs = attr;
     cfg.numAttrs = ds.pdl ? 1 : 0;
     RSTQ_CUDA(cudaLaunchKernelEx(&cfg, q4k_min_kernel, mins, xs32, bsums, y, M, nb, out, (int)TT));
+    ctx->launches++;
+    return RSTQ_OK;
+}
+
+int32_t launch_pair_sum(rstq_ctx* ctx, DeviceState& ds, const float* t, float* y, int64_t M, int64_t out) {
+    const int64_t n = M * out;   // twin rows are neighbours, so token m's pairs start at t + m * 2 * out
+    int64_t ctas = (n + 255) / 256;
+    if (ctas > (int64_t)ds.sm_count * 8) ctas = (int64_t)ds.sm_count * 8;
+    RSTQ_CUDA(launch_pdl(pair_sum_kernel, dim3((unsigned)ctas), ds, reinterpret_cast<const float2*>(t), y, n));
     ctx->launches++;
     return RSTQ_OK;
 }

@@ -65,7 +65,7 @@ extern "C" int32_t rstq_qmatmul_prequant_noalloc(rstq_weight* w, const void* xq,
     RSTQ_REQUIRE(w && w->magic == kWgtMagic && w->ctx && w->ctx->magic == kCtxMagic, RSTQ_E_INVALID,
                  "invalid weight handle");
     RSTQ_REQUIRE(xq && xs && xsum && y, RSTQ_E_INVALID, "null argument");
-    RSTQ_REQUIRE(!w->mins, RSTQ_E_INVALID, "Q4_K weights go through rstq_qmatmul / rstq_qmatmul_prequant");
+    RSTQ_REQUIRE(!w->mins && !w->pair_out, RSTQ_E_INVALID, "K-quant weights go through rstq_qmatmul / rstq_qmatmul_prequant");
     RSTQ_REQUIRE(M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)M);
     RSTQ_REQUIRE((((uintptr_t)xq | (uintptr_t)xs | (uintptr_t)xsum | (uintptr_t)y) & 15) == 0,
                  RSTQ_E_ALIGN, "device pointers must be 16-byte aligned");

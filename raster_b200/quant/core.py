@@ -83,3 +83,21 @@ def _q4k():
 
 
 register_quant("q4_K", _q4k())
+
+
+def _q6k():
+    """:q6_K (src/raster/quant/core.clj:68-75): quantize-weight-q6k on the host once, q8_K activations
+    x Q6_K sub-block dots on the device."""
+    def quantize(W, rows, cols):
+        q = cq.quantize_weight_q6k(np.asarray(W, dtype=np.float32).ravel(), cq.q6_K)
+        q["bound"] = default_context().bind_weight_q6k(q, rows, cols)
+        return q
+
+    def apply(qm, x):
+        return default_context().qmatmul_host(qm.data["bound"], np.asarray(x, dtype=np.float32), 1, L.F32,
+                                              L.MODE_A8)[0]
+
+    return {"descriptor": cq.q6_K, "quantize": quantize, "apply": apply}
+
+
+register_quant("q6_K", _q6k())

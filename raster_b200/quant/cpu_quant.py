@@ -118,3 +118,32 @@ def dequant_q4k(enc):
     a1 = np.repeat(np.asarray(enc["da"], np.float64), 8) * np.asarray(enc["aq"], np.float64)
     b1 = np.repeat(np.asarray(enc["db"], np.float64), 8) * np.asarray(enc["bq"], np.float64)
     return (a1[:, None] * q + b1[:, None]).astype(np.float32).ravel()
+
+
+# ---- Q6_K: symmetric 6-bit super-blocks (quant.clj:206-278) -------------------------------------
+q6_K = {"name": "q6_K", "super_block": 256, "subblock": 16, "n_subblocks": 16, "weight_bits": 6,
+        "scale_bits": 8, "has_dmin": False, "zero_point": 32, "pack": "byte-direct", "act_type": "i8-K"}
+
+
+def quantize_weight_q6k(w, fmt=q6_K):
+    """Flat f32 array (len % 256 == 0) -> {"wq", "sc", "ds"} (`quantize-weight-q6k`, quant.clj:222-262):
+    per 16-element sub-block a = max|w| / 32, per super-block ds = max(a) / 127,
+    sc = clamp(round(a / ds), 0, 127), q = clamp(round(w / (ds*sc)) + 32, 0, 63), a byte per code."""
+    w = np.ascontiguousarray(w, dtype=np.float32).reshape(-1, 16, 16).astype(np.float64)
+    a = np.abs(w).max(axis=2) / 32.0
+    dv = a.max(axis=1) / 127.0
+    with np.errstate(divide="ignore"):
+        idv = np.where(dv == 0.0, 0.0, 1.0 / dv)
+    sc = np.clip(jround(a * idv[:, None]), 0, 127)
+    a1 = dv[:, None] * sc
+    with np.errstate(divide="ignore"):
+        ia1 = np.where(a1 == 0.0, 0.0, 1.0 / a1)
+    q = np.clip(jround(w * ia1[:, :, None]) + 32, 0, 63).astype(np.uint8)
+    return {"wq": q.ravel(), "sc": sc.astype(np.int8).ravel(), "ds": dv.astype(np.float32)}
+
+
+def dequant_q6k(enc):
+    """x = (ds*sc)*(q - 32) (`dequant-q6k`, quant.clj:264-278)."""
+    q = np.asarray(enc["wq"], dtype=np.uint8).reshape(-1, 16).astype(np.float64) - 32.0
+    a1 = np.repeat(np.asarray(enc["ds"], np.float64), 16) * np.asarray(enc["sc"], np.float64)
+    return (a1[:, None] * q).astype(np.float32).ravel()

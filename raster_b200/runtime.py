@@ -248,6 +248,19 @@ class Context:
                                               _np_ptr(aq), _np_ptr(bq), dev, out, in_))
         return QWeight(self, h)
 
+    def bind_weight_q6k(self, enc, out, in_, dev=0) -> QWeight:
+        """Bind a Q6_K matrix from the arrays of `quantize-weight-q6k` (keys wq, sc, ds;
+        src/raster/compiler/backend/cpu/quant.clj:222-262), all rows of one matrix [out, in]."""
+        wq = np.ascontiguousarray(enc["wq"]).view(np.uint8)
+        sc = np.ascontiguousarray(enc["sc"]).view(np.int8)
+        ds = np.ascontiguousarray(enc["ds"], dtype=np.float32)
+        if wq.size != out * in_ or sc.size != out * in_ // 16 or ds.size != out * in_ // 256:
+            raise ValueError("Q6_K arrays do not match out x in")
+        h = C.c_void_p()
+        L.check(self.lib.rstq_weight_bind_q6k(self.handle, C.byref(h), _np_ptr(wq), _np_ptr(sc), _np_ptr(ds), dev,
+                                              out, in_))
+        return QWeight(self, h)
+
     # -- ops on device-resident data ----------------------------------------
     def quant_act_i8(self, x: DeviceBuffer, xq, xs, xsum, M, in_) -> None:
         L.check(self.lib.rstq_quant_act_i8(self.handle, x.handle, xq.handle, xs.handle,

@@ -132,3 +132,46 @@ def test_q4k_contract_errors(ctx):
     assert rc == L.E_SHAPE
     for o in (w, bx, by):
         o.free()
+
+
+def oracle_rows_q6k(e, x, M, in_, out):
+    ys = []
+    for m in range(M):
+        xq, xs, bsums = orc.quantize_act_q8k(x[m * in_:(m + 1) * in_], in_, 16)
+        ys.append(orc.qmatmul_q6k(xq, xs, bsums, e, in_, out)[1])
+    return np.stack(ys)
+
+
+@pytest.mark.parametrize("out,in_,M", [(8, 256, 1), (100, 512, 3), (4096, 4096, 1), (1024, 2048, 8), (512, 1024, 20)])
+def test_q6k_matmul_matches_the_oracle(ctx, out, in_, M):
+    W = synth.normal(15 + out, out * in_, 0.02)
+    x = synth.normal(16 + in_, M * in_)
+    e = orc.quantize_weight_q6k(W)
+    w = ctx.bind_weight_q6k(e, out, in_)
+    assert (w.out, w.in_, w.bits) == (out, in_, 6)
+    assert w.stream_bytes == out * (in_ + in_ // 16 + in_ // 256 * 4)
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+    ctx.sync()
+    assert relerr(by.download(), oracle_rows_q6k(e, x, M, in_, out)) <= 1e-5
+    with pytest.raises(L.RstqError) as err:
+        ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_F)
+    assert err.value.code == L.E_INVALID
+    for o in (w, bx, by):
+        o.free()
+
+
+def test_q6k_reference_case_and_registry(ctx):
+    from raster_b200.quant import core as qcore
+    out, in_ = 8, 256                                   # kernels_k_test.clj:52-66, seeds 3 and 4
+    W, x = gen_centered(out * in_, 3), gen_centered(in_, 4)
+    e = orc.quantize_weight_q6k(W)
+    xq, xs, bsums = orc.quantize_act_q8k(x, in_, 16)
+    ycpu, y64 = orc.qmatmul_q6k(xq, xs, bsums, e, in_, out)
+    qm = qcore.qmatrix("q6_K", W, out, in_)
+    y = qcore.matmul(qm, x)
+    assert np.abs(y - ycpu).max() < 1e-3 and relerr(y, y64) <= 1e-5
+    y4 = qcore.matmul(qcore.qmatrix("q4_K", W, out, in_), x)
+    assert not np.array_equal(y, y4)                    # core_test.clj:39-46: different code paths
+    assert {"q4_0", "q8_0", "q4_K", "q6_K"} <= set(qcore.registered_formats())
+    qm.data["bound"].free()

@@ -134,3 +134,20 @@ def test_host_codec_matches_oracle(case):
     for k in ("da", "db"):
         assert np.array_equal(a[k].view(np.uint32), b[k].view(np.uint32)), k
     assert np.array_equal(cq.dequant_q4k(a).view(np.uint32), orc.dequant_q4k(b).view(np.uint32))
+
+
+@pytest.mark.parametrize("case", ["uniform", "zeros", "normal"])
+def test_host_q6k_codec_matches_oracle(case):
+    n = 2048
+    if case == "uniform":
+        w = gen_centered(n, 15)
+    elif case == "zeros":
+        w = gen_centered(n, 16)
+        w[256:512] = 0.0
+        w[1024:1040] = 0.0
+    else:
+        w = (np.random.default_rng(4).standard_normal(n) * 0.02).astype(np.float32)
+    a, b = cq.quantize_weight_q6k(w), orc.quantize_weight_q6k(w)
+    assert np.array_equal(a["wq"], b["wq"]) and np.array_equal(a["sc"], b["sc"])
+    assert np.array_equal(a["ds"].view(np.uint32), b["ds"].view(np.uint32))
+    assert np.array_equal(cq.dequant_q6k(a).view(np.uint32), orc.dequant_q6k(b).view(np.uint32))
