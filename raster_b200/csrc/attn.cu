@@ -277,8 +277,10 @@ gqa_decode_kernel(const AttnParams p) {
 // head_dim = 32 * VEC (64, 128): eight lanes share a cache position, so a warp works on four
 // positions at once and a dot needs three shuffles; a lane owns float4 columns sub, sub + 8, ... of
 // the head.  Query heads (pre-scaled) sit in shared memory; a CTA serves up to kFastGroup of them.
+// GC = query heads a CTA serves at most (1, 2 or 4): the accumulators of unused heads would only cost
+// registers, and with one head per CTA three CTAs fit an SM instead of two.
 constexpr int kFastGroup = 4;
-template <int VEC>
+template <int VEC, int GC>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 gqa_decode_fast_kernel(const AttnParams p) {
     extern __shared__ __align__(16) float s_part[];   // [kAttnWarps][gc][hd + 4], then q [gc][hd]
@@ -288,8 +290,8 @@ gqa_decode_fast_kernel(const AttnParams p) {
     constexpr int hd = 32 * VEC, hd4 = hd / 4, row = hd + 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = lane >> 3, sub = lane & 7;
     const int hkv = blockIdx.x, split = blockIdx.y, gz = blockIdx.z;
-    const int g0 = gz * kFastGroup;
-    const int gc = min(kFastGroup, p.group - g0);
+    const int g0 = gz * GC;
+    const int gc = min(GC, p.group - g0);
     float4* s_q = reinterpret_cast<float4*>(s_part + kAttnWarps * gc * row);
     for (int i = threadIdx.x; i < gc * hd4; i += blockDim.x) {
         const float4 t = reinterpret_cast<const float4*>(p.q + (int64_t)(hkv * p.group + g0) * hd)[i];
@@ -303,10 +305,10 @@ gqa_decode_fast_kernel(const AttnParams p) {
     const float4* kb = reinterpret_cast<const float4*>(p.k + (int64_t)hkv * hd) + sub;
     const float4* vb = reinterpret_cast<const float4*>(p.v + (int64_t)hkv * hd) + sub;
     const unsigned gmask = 0xFFu << (grp * 8);
-    float4 acc[kFastGroup][VEC];
-    float m[kFastGroup], l[kFastGroup];
+    float4 acc[GC][VEC];
+    float m[GC], l[GC];
 #pragma unroll
-    for (int g = 0; g < kFastGroup; ++g) {
+    for (int g = 0; g < GC; ++g) {
         m[g] = kNegInf;
         l[g] = 0.f;
 #pragma unroll
@@ -319,7 +321,7 @@ gqa_decode_fast_kernel(const AttnParams p) {
 #pragma unroll
         for (int u = 0; u < VEC; ++u) vv[u] = __ldg(vb + j * kv4 + 8 * u);
 #pragma unroll
-        for (int g = 0; g < kFastGroup; ++g) {
+        for (int g = 0; g < GC; ++g) {
             if (g < gc) {
                 float s = 0.f;
 #pragma unroll
@@ -346,7 +348,7 @@ gqa_decode_fast_kernel(const AttnParams p) {
     }
     // the four position groups of the warp -> one state (every lane ends with the merged values)
 #pragma unroll
-    for (int g = 0; g < kFastGroup; ++g) {
+    for (int g = 0; g < GC; ++g) {
         if (g < gc) {
 #pragma unroll
             for (int o = 8; o <= 16; o <<= 1) {
@@ -375,7 +377,7 @@ gqa_decode_fast_kernel(const AttnParams p) {
             }
         }
     }
-    attn_finish<kFastGroup>(p, s_part, &s_last, gc, g0, hkv, split, gz, hd, row);
+    attn_finish<GC>(p, s_part, &s_last, gc, g0, hkv, split, gz, hd, row);
 }
 
 template <typename K, typename... Args>
@@ -493,14 +495,16 @@ int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_
     int32_t rc = use_dev(ctx, q->dev);
     if (rc != RSTQ_OK) return rc;
     const bool fast = head_dim == 64 || head_dim == 128;
-    const int64_t gs = fast ? kFastGroup : kAttnGroup;                 // query heads per CTA
+    const int64_t fg = group >= kFastGroup ? kFastGroup : (group >= 2 ? 2 : 1);   // heads per CTA of the fast kernel
+    const int64_t gs = fast ? fg : kAttnGroup;                         // query heads per CTA
     const int64_t gz = (group + gs - 1) / gs;
     RSTQ_REQUIRE(n_kv * gz <= kAttnCounters, RSTQ_E_LIMIT, "n_kv x ceil(group / %d) = %lld exceeds %d", (int)gs,
                  (long long)(n_kv * gz), kAttnCounters);
     // slices of the cache: enough CTAs for three per SM, at least 64 positions each; sized from the
     // capacity when the length lives on the device, so that one captured launch serves every length
     const int64_t span = clenbuf ? maxpos : cache_len;
-    int64_t S = (3 * (int64_t)ds.sm_count + n_kv * gz - 1) / (n_kv * gz);
+    const int64_t resident = fast && fg == 1 ? 4 : 2;   // CTAs an SM holds (registers): aim at one wave
+    int64_t S = resident * (int64_t)ds.sm_count / (n_kv * gz);
     if (S > (span + 63) / 64) S = (span + 63) / 64;
     const int64_t row = head_dim + 4;
     if (S > 8 * row - 1) S = 8 * row - 1;   // the final merge keeps S weights + 1 sum per head in shared memory
@@ -530,10 +534,16 @@ int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_
     const dim3 grid((unsigned)n_kv, (unsigned)S, (unsigned)gz), block(kAttnWarps * 32);
     if (fast) {
         const size_t smem = (size_t)((kAttnWarps * gc * row + gc * head_dim) * 4);   // <= 17.5 KB
+        cudaError_t e;
         if (head_dim == 64)
-            RSTQ_CUDA(launch_attn(gqa_decode_fast_kernel<2>, grid, block, smem, ds, p));
+            e = fg == 1 ? launch_attn(gqa_decode_fast_kernel<2, 1>, grid, block, smem, ds, p)
+                : fg == 2 ? launch_attn(gqa_decode_fast_kernel<2, 2>, grid, block, smem, ds, p)
+                          : launch_attn(gqa_decode_fast_kernel<2, 4>, grid, block, smem, ds, p);
         else
-            RSTQ_CUDA(launch_attn(gqa_decode_fast_kernel<4>, grid, block, smem, ds, p));
+            e = fg == 1 ? launch_attn(gqa_decode_fast_kernel<4, 1>, grid, block, smem, ds, p)
+                : fg == 2 ? launch_attn(gqa_decode_fast_kernel<4, 2>, grid, block, smem, ds, p)
+                          : launch_attn(gqa_decode_fast_kernel<4, 4>, grid, block, smem, ds, p);
+        RSTQ_CUDA(e);
     } else {
         const size_t smem = (size_t)(kAttnWarps * gc * row * 4);
         if (smem > 48 * 1024)
