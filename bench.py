@@ -855,9 +855,21 @@ def run_dx(args):
     for _ in range(n):
         train.qlinear_q8_dx(dy, codes, scales, M, in_, out, ctx)
     s = (time.perf_counter() - t) / n
+    # the kernel alone, on device-resident arrays (CUDA events over 10 launches)
+    bdy, bc, bs = ctx.array_to_buffer(dy), ctx.array_to_buffer(codes), ctx.array_to_buffer(scales)
+    bdx = ctx.make_buffer(M * in_, np.float32)
+    e0, e1 = ctx.event(), ctx.event()
+    for it in range(2):
+        e0.record()
+        for _ in range(10):
+            ctx.qlinear_q8_dx_device(bdy, bc, bs, bdx, M, in_, out)
+        e1.record()
+        ctx.sync()
+    us = e0.elapsed_ms(e1) * 1e3 / 10
     print(json.dumps({"case": args.case, "ms_per_call": round(s * 1e3, 3),
                       "TFLOPs": round(2.0 * M * out * in_ / s / 1e12, 2),
-                      "h2d_bytes": M * out * 4, "d2h_bytes": M * in_ * 4}))
+                      "h2d_bytes": M * out * 4, "d2h_bytes": M * in_ * 4,
+                      "kernel_us": round(us, 1), "kernel_TFLOPs": round(2.0 * M * out * in_ / us / 1e6, 1)}))
     ctx.close()
 
 

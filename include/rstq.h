@@ -245,6 +245,10 @@ RSTQ_API int32_t rstq_qlinear_q8(rstq_ctx* ctx, const float* x, const void* code
 RSTQ_API int32_t rstq_qlinear_q8_dx(rstq_ctx* ctx, const float* dy, const void* codes,
                                     const float* scales, float* dx, int64_t m, int64_t in,
                                     int64_t out);
+/* qlinear-q8-dx on device-resident arrays: dy f32 [m, out], codes int8 [out, in] and scales f32
+ * [out, in/32] row-major as the reference holds them, dx f32 [m, in]. */
+RSTQ_API int32_t rstq_qlinear_q8_dx_device(rstq_ctx* ctx, rstq_buf* dy, rstq_buf* codes, rstq_buf* scales,
+                                           rstq_buf* dx, int64_t m, int64_t in, int64_t out);
 RSTQ_API int32_t rstq_qmatmul_i8_gemm(rstq_ctx* ctx, const int32_t* xp, const float* xs,
                                       const int32_t* wp, const float* ws, float* y, int64_t in,
                                       int64_t out, int64_t nrows);

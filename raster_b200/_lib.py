@@ -43,6 +43,7 @@ SIGNATURES = {
     "rstq_quant_act_q8k": [vp, vp, vp, vp, vp, i64, i64, i32],
     "rstq_qmatmul": [vp, vp, vp, vp, i64, i32, i32, i32],
     "rstq_qmatmul_prequant": [vp, vp, vp, vp, vp, vp, i64],
+    "rstq_qlinear_q8_dx_device": [vp, vp, vp, vp, vp, i64, i64, i64],
     "rstq_qmatmul_prequant_noalloc": [vp, vp, vp, vp, vp, vp, i64],
     "rstq_qlinear_i8": [vp, vp, vp, vp, vp, i64, i64],
     "rstq_qlinear_i8_q8": [vp, vp, vp, vp, vp, i64, i64],

@@ -1039,6 +1039,23 @@ int32_t rstq_qlinear_q8_dx(rstq_ctx* ctx, const float* dy, const void* codes, co
     });
 }
 
+int32_t rstq_qlinear_q8_dx_device(rstq_ctx* ctx, rstq_buf* dy, rstq_buf* codes, rstq_buf* scales, rstq_buf* dx,
+                                  int64_t m, int64_t in, int64_t out) {
+    CHECK_CTX(ctx);
+    RSTQ_REQUIRE(m >= 1 && out >= 1 && in >= 32 && in % 32 == 0, RSTQ_E_SHAPE,
+                 "in=%lld not a multiple of 32 (m = %lld, out = %lld)", (long long)in, (long long)m, (long long)out);
+    int32_t rc;
+    if ((rc = need_bytes(dy, m * out * 4, "dy")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(codes, out * in, "codes")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(scales, out * (in / 32) * 4, "scales")) != RSTQ_OK) return rc;
+    if ((rc = need_bytes(dx, m * in * 4, "dx")) != RSTQ_OK) return rc;
+    RSTQ_REQUIRE(dy->dev == codes->dev && dy->dev == scales->dev && dy->dev == dx->dev, RSTQ_E_DEVICE,
+                 "buffers live on different devices");
+    if ((rc = use_dev(ctx, dy->dev)) != RSTQ_OK) return rc;
+    return launch_qlinear_q8_dx(ctx, ctx->devs[dy->dev], (const float*)dy->ptr, (const int8_t*)codes->ptr,
+                                (const float*)scales->ptr, (float*)dx->ptr, m, in, out);
+}
+
 int32_t rstq_qmatmul_i8_gemm(rstq_ctx* ctx, const int32_t* xp, const float* xs, const int32_t* wp,
                              const float* ws, float* y, int64_t in, int64_t out, int64_t nrows) {
     CHECK_CTX(ctx);

@@ -3,12 +3,14 @@
 // the dequant-transpose GEMM dX = dY . dequant(W), W = [out, in] signed 8-bit codes in the
 // reference's row-major layout with one f32 scale per 32 columns.
 //
-// First correct path: a tiled f32 kernel on the CUDA cores (no tensor cores yet).  A CTA owns a
+// Two kernels: the tensor-core one below (m >= 16 and out % 8 == 0) and a tiled f32 kernel on the
+// CUDA cores for everything else.  In the f32 kernel a CTA owns a
 // 32-token x 128-column tile of dx and walks `out` in chunks of 32 rows: the chunk of W is
 // dequantized once into shared memory (code * scale in f32, the product the reference forms
 // first), the chunk of dy is stored transposed, and every thread keeps a 4 x 4 micro-tile in
 // registers.  Products are f32, sums are f32 in o order per thread.
 #include "internal.h"
+#include "mma_helpers.cuh"
 
 namespace rstq {
 
@@ -76,8 +78,131 @@ qlinear_q8_dx_kernel(const float* __restrict__ dy, const int8_t* __restrict__ co
     }
 }
 
+// ---- the same product on the tensor cores (m >= 16, out % 8 == 0) --------------------------------
+// mma roles: M = 16 tokens, N = 8 columns i, K = 16 rows o of W.  For the 32 columns of one scale
+// block b,  dx[m, i] = sum_o (dy[m, o] * s[o, b]) * c[o, i]:  the codes c are exact in bf16, the f32
+// factor dy * s is split into three bf16 terms (each step of the expansion exact in f32), so three
+// bf16 m16n8k16 MMAs per tile give the f32 product to about 2^-24 -- the arithmetic of the decode
+// kernel's float-activation mode.  A CTA owns 64 tokens x 128 columns and walks `out` in chunks of 32
+// rows: dy chunk (f32), the four scale columns and the codes (transposed to bf16 [column][o], so a B
+// fragment is one 32-bit load) are staged in shared memory; warp w holds tokens 16 * (w & 3) and the
+// two column blocks 2 * (w >> 2), 2 * (w >> 2) + 1 (eight accumulator tiles).
+constexpr int kMmaTok = 64, kMmaCols = 128, kMmaChunk = 32;
+constexpr int kDyStride = 40;   // floats per token row of the dy chunk: conflict-free 8-byte fragment loads
+constexpr int kBStride = 20;    // 32-bit words per column row of the bf16 codes: conflict-free fragment loads
+
+__device__ __forceinline__ void split3_bf16x2(float hi, float lo, uint32_t (&t)[3]) {
+    // terms of hi (upper half) and lo (lower half) side by side; bf16 -> f32 is a 16-bit shift
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        t[k] = pack_bf16x2(hi, lo);
+        hi -= __uint_as_float(t[k] & 0xFFFF0000u);
+        lo -= __uint_as_float(t[k] << 16);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+qlinear_q8_dx_mma_kernel(const float* __restrict__ dy, const int8_t* __restrict__ codes,
+                         const float* __restrict__ scales, float* __restrict__ dx, int64_t m, int64_t in, int64_t out) {
+    __shared__ __align__(16) float s_dy[kMmaTok][kDyStride];
+    __shared__ __align__(16) uint32_t s_b[kMmaCols][kBStride];
+    __shared__ float s_s[kMmaChunk][4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int64_t col0 = (int64_t)blockIdx.x * kMmaCols, tok0 = (int64_t)blockIdx.y * kMmaTok;
+    const int64_t nb = in >> 5;
+    const int wm = warp & 3, wb = (warp >> 2) * 2;
+    float acc[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    const int f_tok = tid >> 2, f_o = (tid & 3) * 8;   // dy loader: a token, eight consecutive o
+    const int c_i = tid & 127, c_p = tid >> 7;         // code loader: a column, o pairs c_p, c_p + 2, ...
+    for (int64_t o0 = 0; o0 < out; o0 += kMmaChunk) {
+        {
+            const int64_t tk = tok0 + f_tok, o = o0 + f_o;
+            float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+            if (tk < m && o < out) {   // out % 8 == 0: the eight are in range together
+                v0 = *reinterpret_cast<const float4*>(dy + tk * out + o);
+                v1 = *reinterpret_cast<const float4*>(dy + tk * out + o + 4);
+            }
+            *reinterpret_cast<float4*>(&s_dy[f_tok][f_o]) = v0;
+            *reinterpret_cast<float4*>(&s_dy[f_tok][f_o + 4]) = v1;
+        }
+        if (tid < 128) {
+            const int64_t o = o0 + (tid >> 2), b = (col0 >> 5) + (tid & 3);
+            s_s[tid >> 2][tid & 3] = (o < out && b < nb) ? scales[o * nb + b] : 0.f;
+        }
+        {
+            const int64_t i = col0 + c_i;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int op = c_p + 2 * q;              // pair of rows 2 op, 2 op + 1 of the chunk
+                const int64_t o = o0 + 2 * op;
+                float lo = 0.f, hi = 0.f;
+                if (i < in && o < out) {                 // out % 2 == 0
+                    lo = (float)codes[o * in + i];
+                    hi = (float)codes[(o + 1) * in + i];
+                }
+                s_b[c_i][op] = pack_bf16x2(hi, lo);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            const int kb = ks * 16;
+            const float2 d00 = *reinterpret_cast<const float2*>(&s_dy[wm * 16 + g][kb + 2 * t]);
+            const float2 d10 = *reinterpret_cast<const float2*>(&s_dy[wm * 16 + g + 8][kb + 2 * t]);
+            const float2 d01 = *reinterpret_cast<const float2*>(&s_dy[wm * 16 + g][kb + 2 * t + 8]);
+            const float2 d11 = *reinterpret_cast<const float2*>(&s_dy[wm * 16 + g + 8][kb + 2 * t + 8]);
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                const int bc = wb + blk;
+                const float s0 = s_s[kb + 2 * t][bc], s1 = s_s[kb + 2 * t + 1][bc];
+                const float s8 = s_s[kb + 2 * t + 8][bc], s9 = s_s[kb + 2 * t + 9][bc];
+                uint32_t a0[3], a1[3], a2[3], a3[3];
+                split3_bf16x2(d00.y * s1, d00.x * s0, a0);   // row g,     k 2t, 2t+1
+                split3_bf16x2(d10.y * s1, d10.x * s0, a1);   // row g + 8, k 2t, 2t+1
+                split3_bf16x2(d01.y * s9, d01.x * s8, a2);   // row g,     k 2t+8, 2t+9
+                split3_bf16x2(d11.y * s9, d11.x * s8, a3);   // row g + 8, k 2t+8, 2t+9
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int ci = bc * 32 + nt * 8 + g;
+                    const uint32_t b0 = s_b[ci][ks * 8 + t], b1 = s_b[ci][ks * 8 + t + 4];
+#pragma unroll
+                    for (int k = 0; k < 3; ++k) {
+                        const uint32_t af[4] = {a0[k], a1[k], a2[k], a3[k]};
+                        hmma_bf16(acc[blk * 4 + nt], af, b0, b1);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int64_t c = col0 + (wb + blk) * 32 + nt * 8 + 2 * t;
+            const int64_t r0 = tok0 + wm * 16 + g;
+            if (c < in) {   // in % 2 == 0: the pair is in range together
+                if (r0 < m) *reinterpret_cast<float2*>(dx + r0 * in + c) = make_float2(acc[blk * 4 + nt][0], acc[blk * 4 + nt][1]);
+                if (r0 + 8 < m)
+                    *reinterpret_cast<float2*>(dx + (r0 + 8) * in + c) = make_float2(acc[blk * 4 + nt][2], acc[blk * 4 + nt][3]);
+            }
+        }
+}
+
 int32_t launch_qlinear_q8_dx(rstq_ctx* ctx, DeviceState& ds, const float* dy, const int8_t* codes,
                              const float* scales, float* dx, int64_t m, int64_t in, int64_t out) {
+    if (m >= 16 && out % 8 == 0) {
+        const dim3 gm((unsigned)((in + kMmaCols - 1) / kMmaCols), (unsigned)((m + kMmaTok - 1) / kMmaTok));
+        RSTQ_REQUIRE(gm.y < 65536, RSTQ_E_LIMIT, "m = %lld too large for one launch", (long long)m);
+        qlinear_q8_dx_mma_kernel<<<gm, 256, 0, ds.stream>>>(dy, codes, scales, dx, m, in, out);
+        ctx->launches++;
+        RSTQ_CUDA(cudaGetLastError());
+        return RSTQ_OK;
+    }
     const dim3 grid((unsigned)((in + kDxCols - 1) / kDxCols), (unsigned)((m + kDxTok - 1) / kDxTok));
     RSTQ_REQUIRE(grid.y < 65536, RSTQ_E_LIMIT, "m = %lld too large for one launch", (long long)m);
     qlinear_q8_dx_kernel<<<grid, kDxThreads, 0, ds.stream>>>(dy, codes, scales, dx, m, in, out);

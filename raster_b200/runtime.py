@@ -279,6 +279,10 @@ class Context:
                                                xsum.handle if xsum is not None else None,
                                                y.handle, M))
 
+    def qlinear_q8_dx_device(self, dy, codes, scales, dx, m, in_, out) -> None:
+        L.check(self.lib.rstq_qlinear_q8_dx_device(self.handle, dy.handle, codes.handle, scales.handle, dx.handle,
+                                                   m, in_, out))
+
     def qmatmul_host(self, w: QWeight, x, M=1, act_dtype=L.F32, mode=L.MODE_A8) -> np.ndarray:
         x = np.ascontiguousarray(x)
         y = np.empty(M * w.out, dtype=np.float32)

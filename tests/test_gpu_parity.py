@@ -416,7 +416,8 @@ def test_tokens_are_split_when_activations_exceed_shared_memory(ctx):
 
 
 # ---------------------------------------------------------------- backward-data of qlinear-q8
-@pytest.mark.parametrize("m,in_,out", [(3, 64, 8), (1, 4096, 4096), (5, 256, 72), (33, 512, 100), (64, 11008, 256)])
+@pytest.mark.parametrize("m,in_,out", [(3, 64, 8), (1, 4096, 4096), (5, 256, 72), (33, 512, 100), (64, 11008, 256),
+                                       (16, 96, 8), (40, 160, 72), (100, 2048, 1024)])
 def test_qlinear_q8_dx_operator(ctx, m, in_, out):
     """dx = dy . dequant(W) (first shape is the reference's own test shape); also the identity its
     gradient check rests on: <dy, forward(x)> == <dx, x> for the frozen weight."""
@@ -434,6 +435,25 @@ def test_qlinear_q8_dx_operator(ctx, m, in_, out):
         lhs = float(np.dot(dy.astype(np.float64), y.astype(np.float64)))
         rhs = float(np.dot(dx.astype(np.float64), x.astype(np.float64)))
         assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), abs(rhs), 1.0)
+
+
+def test_qlinear_q8_dx_on_device_buffers(ctx):
+    """The device-resident entry: both kernels (tensor cores for m >= 16 and out % 8 == 0, f32 otherwise)
+    against the oracle, and the two against each other on a shape both accept."""
+    in_, out = 384, 200
+    q = train.q8_quantize(synth.normal(91, out * in_, 0.2), out, in_)
+    bc, bs = ctx.array_to_buffer(q["codes"]), ctx.array_to_buffer(q["scales"])
+    got = {}
+    for m in (15, 48):                                   # 15 tokens: f32 kernel; 48: tensor cores
+        dy = synth.normal(92, m * out)
+        bdy, bdx = ctx.array_to_buffer(dy), ctx.make_buffer(m * in_, np.float32)
+        ctx.qlinear_q8_dx_device(bdy, bc, bs, bdx, m, in_, out)
+        ctx.sync()
+        got[m] = bdx.download()
+        assert relerr(got[m], orc.qlinear_q8_dx(dy, q["codes"], q["scales"], m, in_, out)) <= TOL_F
+        bdy.free(), bdx.free()
+    assert relerr(got[48][:15 * in_], got[15]) <= TOL_F   # same dy rows (same seed prefix), other kernel
+    bc.free(), bs.free()
 
 
 def test_host_array_cache_notices_new_contents_at_an_old_address(ctx):
