@@ -84,8 +84,8 @@ qlinear_q8_dx_kernel(const float* __restrict__ dy, const int8_t* __restrict__ co
 // factor dy * s is split into three bf16 terms (each step of the expansion exact in f32), so three
 // bf16 m16n8k16 MMAs per tile give the f32 product to about 2^-24 -- the arithmetic of the decode
 // kernel's float-activation mode.  A CTA owns 64 tokens x 128 columns and walks `out` in chunks of 32
-// rows: dy chunk (f32), the four scale columns and the codes (transposed to bf16 [column][o], so a B
-// fragment is one 32-bit load) are staged in shared memory; warp w holds tokens 16 * (w & 3) and the
+// rows: dy chunk (f32), the four scale columns and the codes come in by asynchronous copies, two
+// chunks in flight; the codes are then transposed to bf16 [column][o] so a B fragment is one 32-bit load; warp w holds tokens 16 * (w & 3) and the
 // two column blocks 2 * (w >> 2), 2 * (w >> 2) + 1 (eight accumulator tiles).
 constexpr int kMmaTok = 64, kMmaCols = 128, kMmaChunk = 32;
 constexpr int kDyStride = 40;   // floats per token row of the dy chunk: conflict-free 8-byte fragment loads
@@ -101,12 +101,29 @@ __device__ __forceinline__ void split3_bf16x2(float hi, float lo, uint32_t (&t)[
     }
 }
 
+// 16-byte / 4-byte asynchronous copies global -> shared; `ok` false copies nothing and fills zeros
+// (the source address is then only required to be a valid one).
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool ok) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(ok ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src, bool ok) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(ok ? 4 : 0) : "memory");
+}
+
+struct DxStage {   // one chunk of 32 rows o as it comes from memory
+    float dy[kMmaTok][kDyStride];
+    int8_t codes[kMmaChunk][kMmaCols];
+    float s[kMmaChunk][4];
+};
+
 __global__ void __launch_bounds__(256)
 qlinear_q8_dx_mma_kernel(const float* __restrict__ dy, const int8_t* __restrict__ codes,
                          const float* __restrict__ scales, float* __restrict__ dx, int64_t m, int64_t in, int64_t out) {
-    __shared__ __align__(16) float s_dy[kMmaTok][kDyStride];
+    // two stages in flight: while the MMAs of chunk c run, the copies of chunk c + 1 land
+    __shared__ __align__(16) DxStage stage[2];
     __shared__ __align__(16) uint32_t s_b[kMmaCols][kBStride];
-    __shared__ float s_s[kMmaChunk][4];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int64_t col0 = (int64_t)blockIdx.x * kMmaCols, tok0 = (int64_t)blockIdx.y * kMmaTok;
     const int64_t nb = in >> 5;
@@ -116,68 +133,78 @@ qlinear_q8_dx_mma_kernel(const float* __restrict__ dy, const int8_t* __restrict_
     for (int a = 0; a < 8; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
-    const int f_tok = tid >> 2, f_o = (tid & 3) * 8;   // dy loader: a token, eight consecutive o
-    const int c_i = tid & 127, c_p = tid >> 7;         // code loader: a column, o pairs c_p, c_p + 2, ...
-    for (int64_t o0 = 0; o0 < out; o0 += kMmaChunk) {
+    const int f_tok = tid >> 2, f_o = (tid & 3) * 8;   // dy copies: a token, eight consecutive o (two 16-byte copies)
+    const int k_o = tid >> 3, k_i = (tid & 7) * 16;    // code copies: a row o, 16 consecutive columns
+    const int c_i = tid & 127, c_p = tid >> 7;         // conversion: a column, o pairs c_p, c_p + 2, ...
+
+    auto issue = [&](int64_t o0, DxStage& st) {
         {
             const int64_t tk = tok0 + f_tok, o = o0 + f_o;
-            float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
-            if (tk < m && o < out) {   // out % 8 == 0: the eight are in range together
-                v0 = *reinterpret_cast<const float4*>(dy + tk * out + o);
-                v1 = *reinterpret_cast<const float4*>(dy + tk * out + o + 4);
-            }
-            *reinterpret_cast<float4*>(&s_dy[f_tok][f_o]) = v0;
-            *reinterpret_cast<float4*>(&s_dy[f_tok][f_o + 4]) = v1;
+            const bool ok = tk < m && o < out;           // out % 8 == 0: the eight are in range together
+            const float* src = ok ? dy + tk * out + o : dy;
+            cp_async16(&st.dy[f_tok][f_o], src, ok);
+            cp_async16(&st.dy[f_tok][f_o + 4], src + (ok ? 4 : 0), ok);
+        }
+        {
+            const int64_t o = o0 + k_o, i = col0 + k_i;
+            const bool ok = o < out && i < in;           // in % 32 == 0: the sixteen are in range together
+            cp_async16(&st.codes[k_o][k_i], ok ? codes + o * in + i : codes, ok);
         }
         if (tid < 128) {
             const int64_t o = o0 + (tid >> 2), b = (col0 >> 5) + (tid & 3);
-            s_s[tid >> 2][tid & 3] = (o < out && b < nb) ? scales[o * nb + b] : 0.f;
+            const bool ok = o < out && b < nb;
+            cp_async4(&st.s[tid >> 2][tid & 3], ok ? scales + o * nb + b : scales, ok);
         }
-        {
-            const int64_t i = col0 + c_i;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    issue(0, stage[0]);
+    int cur = 0;
+    for (int64_t o0 = 0; o0 < out; o0 += kMmaChunk, cur ^= 1) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();   // chunk `cur` has landed for everyone; the MMAs of the chunk before are done
+        if (o0 + kMmaChunk < out) issue(o0 + kMmaChunk, stage[cur ^ 1]);
+        const DxStage& st = stage[cur];
+        // codes -> bf16, transposed to [column][o] so that a B fragment is one 32-bit load
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int op = c_p + 2 * q;              // pair of rows 2 op, 2 op + 1 of the chunk
-                const int64_t o = o0 + 2 * op;
-                float lo = 0.f, hi = 0.f;
-                if (i < in && o < out) {                 // out % 2 == 0
-                    lo = (float)codes[o * in + i];
-                    hi = (float)codes[(o + 1) * in + i];
-                }
-                s_b[c_i][op] = pack_bf16x2(hi, lo);
-            }
+        for (int q = 0; q < 8; ++q) {
+            const int op = c_p + 2 * q;                  // rows 2 op, 2 op + 1 of the chunk
+            s_b[c_i][op] = pack_bf16x2((float)st.codes[2 * op + 1][c_i], (float)st.codes[2 * op][c_i]);
         }
         __syncthreads();
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
             const int kb = ks * 16;
-            const float2 d00 = *reinterpret_cast<const float2*>(&s_dy[wm * 16 + g][kb + 2 * t]);
-            const float2 d10 = *reinterpret_cast<const float2*>(&s_dy[wm * 16 + g + 8][kb + 2 * t]);
-            const float2 d01 = *reinterpret_cast<const float2*>(&s_dy[wm * 16 + g][kb + 2 * t + 8]);
-            const float2 d11 = *reinterpret_cast<const float2*>(&s_dy[wm * 16 + g + 8][kb + 2 * t + 8]);
+            const float2 d00 = *reinterpret_cast<const float2*>(&st.dy[wm * 16 + g][kb + 2 * t]);
+            const float2 d10 = *reinterpret_cast<const float2*>(&st.dy[wm * 16 + g + 8][kb + 2 * t]);
+            const float2 d01 = *reinterpret_cast<const float2*>(&st.dy[wm * 16 + g][kb + 2 * t + 8]);
+            const float2 d11 = *reinterpret_cast<const float2*>(&st.dy[wm * 16 + g + 8][kb + 2 * t + 8]);
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
                 const int bc = wb + blk;
-                const float s0 = s_s[kb + 2 * t][bc], s1 = s_s[kb + 2 * t + 1][bc];
-                const float s8 = s_s[kb + 2 * t + 8][bc], s9 = s_s[kb + 2 * t + 9][bc];
+                const float s0 = st.s[kb + 2 * t][bc], s1 = st.s[kb + 2 * t + 1][bc];
+                const float s8 = st.s[kb + 2 * t + 8][bc], s9 = st.s[kb + 2 * t + 9][bc];
                 uint32_t a0[3], a1[3], a2[3], a3[3];
                 split3_bf16x2(d00.y * s1, d00.x * s0, a0);   // row g,     k 2t, 2t+1
                 split3_bf16x2(d10.y * s1, d10.x * s0, a1);   // row g + 8, k 2t, 2t+1
                 split3_bf16x2(d01.y * s9, d01.x * s8, a2);   // row g,     k 2t+8, 2t+9
                 split3_bf16x2(d11.y * s9, d11.x * s8, a3);   // row g + 8, k 2t+8, 2t+9
+                uint32_t b0[4], b1[4];
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
                     const int ci = bc * 32 + nt * 8 + g;
-                    const uint32_t b0 = s_b[ci][ks * 8 + t], b1 = s_b[ci][ks * 8 + t + 4];
+                    b0[nt] = s_b[ci][ks * 8 + t];
+                    b1[nt] = s_b[ci][ks * 8 + t + 4];
+                }
+                // smallest term first; the four column tiles of a term are independent MMAs
 #pragma unroll
-                    for (int k = 0; k < 3; ++k) {
-                        const uint32_t af[4] = {a0[k], a1[k], a2[k], a3[k]};
-                        hmma_bf16(acc[blk * 4 + nt], af, b0, b1);
-                    }
+                for (int k = 2; k >= 0; --k) {
+                    const uint32_t af[4] = {a0[k], a1[k], a2[k], a3[k]};
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) hmma_bf16(acc[blk * 4 + nt], af, b0[nt], b1[nt]);
                 }
             }
         }
-        __syncthreads();
     }
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk)
