@@ -20,7 +20,7 @@ from . import _lib as L
 def _np_ptr(a: np.ndarray):
     if not a.flags["C_CONTIGUOUS"]:
         raise ValueError("array must be C-contiguous")
-    return a.ctypes.data_as(C.c_void_p)
+    return a.ctypes.data   # the address as an int: half the cost of data_as(), and c_void_p parameters take it
 
 
 def parse_device(dev) -> int:
