@@ -11,16 +11,33 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
+import weakref
 
 import numpy as np
 
 from . import _lib as L
 
 
+_ptr_cache: dict = {}   # id(array) -> (weak reference to it, its address): hot callers pass the same arrays
+
+
 def _np_ptr(a: np.ndarray):
-    if not a.flags["C_CONTIGUOUS"]:
+    """Address of a C-contiguous array as an int (c_void_p parameters take it).  `ndarray.ctypes` costs
+    about a microsecond per use, a quarter of a small operator call with four arrays, so addresses of
+    live arrays are remembered; the weak reference tells a new array at a recycled id() apart."""
+    e = _ptr_cache.get(id(a))
+    if e is not None and e[0]() is a and e[2] == a.nbytes:   # nbytes: an in-place resize moves the data
+        return e[1]
+    if not a.flags.c_contiguous:
         raise ValueError("array must be C-contiguous")
-    return a.ctypes.data   # the address as an int: half the cost of data_as(), and c_void_p parameters take it
+    p = a.ctypes.data
+    if len(_ptr_cache) > 1024:
+        _ptr_cache.clear()
+    try:
+        _ptr_cache[id(a)] = (weakref.ref(a), p, a.nbytes)
+    except TypeError:        # an array subclass without weak references
+        pass
+    return p
 
 
 def parse_device(dev) -> int:
