@@ -959,7 +959,7 @@ def run_decoder(args):
     q / k / v, rope, cache append, GQA attention over f32 caches, o, residual, rms-norm + quantize,
     gate / up, SwiGLU, down, residual -- distinct layers (weights and caches well over L2), replayed from
     one CUDA graph with the position in a device buffer.  Default: the fused steps and merged q|k|v and
-    gate|up matrices, 10 kernels per layer; `decoder:<bits>:<cache_len>:unfused` runs the reference's
+    gate|up matrices, 9 kernels per layer; `decoder:<bits>:<cache_len>:unfused` runs the reference's
     chain step by step, 19 kernels per layer."""
     from raster_b200 import Context
     from raster_b200 import _lib as L
@@ -1010,16 +1010,17 @@ def run_decoder(args):
     g_s, u_s = ctx.wrap_buffer(gu.device_ptr, F, f32), ctx.wrap_buffer(gu.device_ptr + 4 * F, F, f32)
 
     def fused_pass():
-        # 10 kernels per layer: the residual adds ride the next norm + quantizer, q / k / v are one
-        # matrix and gate / up another, rope and both cache appends are one launch, SwiGLU writes the
-        # down projection's int8 input directly.  x holds the residual stream, `down` the last
+        # 9 kernels per layer: the residual adds ride the next norm + quantizer, q / k / v are one
+        # matrix and gate / up another, rope and both cache appends are one launch, attention and SwiGLU
+        # write the int8 input of the projection that follows them directly.  x holds the residual stream, `down` the last
         # layer's MLP output still to be added to it.
         for lay in stack:
             ctx.residual_rms_norm_quant_act(x, down, h, lay["n1"], xq, xs, xsum, 1, H)
             ctx.qmatmul_prequant(lay["qkv"], xq, xs, xsum, qkv, 1)
             ctx.rope_append(q_s, k_s, v_s, lay["kc"], lay["vc"], NQ, NKV, HD, 10000.0, maxpos=maxpos, posbuf=bpos)
-            ctx.gqa_decode_attention(q_s, lay["kc"], lay["vc"], att, 0, NQ, NQ // NKV, NKV, HD, maxpos, scale, clenbuf=blen)
-            ctx.qmatmul(lay["o"], att, o_, 1)
+            ctx.gqa_decode_attention_quant_act(q_s, lay["kc"], lay["vc"], att, xq, xs, xsum, 0, NQ, NQ // NKV, NKV, HD,
+                                               maxpos, scale, clenbuf=blen)
+            ctx.qmatmul_prequant(lay["o"], xq, xs, xsum, o_, 1)
             ctx.residual_rms_norm_quant_act(h, o_, x, lay["n2"], xq, xs, xsum, 1, H)
             ctx.qmatmul_prequant(lay["gate_up"], xq, xs, xsum, gu, 1)
             ctx.silu_mul_quant_act(g_s, u_s, aq, as_, asum, F)

@@ -313,6 +313,14 @@ RSTQ_API int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, i
  *                                     sum quantized to int8 blocks; sum may not alias a or b;
  *   rstq_silu_mul_quant_act / rstq_gelu_mul_quant_act   the gated activation quantized to int8
  *                                     blocks (the input of the down projection), n % 32 == 0. */
+/* rstq_gqa_decode_attention whose output is also quantized to int8 blocks of 32 (codes, scales, sums as
+ * rstq_quant_act_i8 gives them for `out`) by the CTA that writes it: the o projection then starts from
+ * rstq_qmatmul_prequant.  head_dim 64 or 128; xsum may be NULL. */
+RSTQ_API int32_t rstq_gqa_decode_attention_quant_act(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v,
+                                                     rstq_buf* out, rstq_buf* xq, rstq_buf* xs, rstq_buf* xsum,
+                                                     int64_t cache_len, rstq_buf* clenbuf, int64_t n_q,
+                                                     int64_t group, int64_t n_kv, int64_t head_dim, int64_t maxpos,
+                                                     double scale);
 RSTQ_API int32_t rstq_rope_append(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* kcache,
                                   rstq_buf* vcache, int64_t n_q, int64_t n_kv, int64_t head_dim, double theta,
                                   int64_t pos, int64_t maxpos, rstq_buf* posbuf);

@@ -68,6 +68,7 @@ SIGNATURES = {
     "rstq_gelu_mul": [vp, vp, vp, vp, i64],
     "rstq_residual_add": [vp, vp, vp, vp, i64],
     "rstq_rope_pos": [vp, vp, vp, i64, i64, C.c_double, i64, vp],
+    "rstq_gqa_decode_attention_quant_act": [vp, vp, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, C.c_double],
     "rstq_rope_append": [vp, vp, vp, vp, vp, vp, i64, i64, i64, C.c_double, i64, i64, vp],
     "rstq_residual_rms_norm_quant_act": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, C.c_double, C.c_double],
     "rstq_silu_mul_quant_act": [vp, vp, vp, vp, vp, vp, i64],

@@ -97,7 +97,17 @@ struct AttnParams {
     int64_t cache_len;
     int n_q, group, n_kv, head_dim, S;
     float scale;
+    // optional: the output quantized to int8 blocks of 32 as well (the o projection's input), by the
+    // CTA that writes it; only with S >= 2 and head_dim % 32 == 0 (a warp then owns whole blocks)
+    int8_t* xq;
+    float* xs;
+    int32_t* xsum;
 };
+
+__device__ __forceinline__ int attn_round_half_up(double v) {
+    const double f = floor(v);
+    return (int)f + ((v - f) >= 0.5 ? 1 : 0);
+}
 
 // Second half of both attention kernels: the per-warp states in shared memory ([warps][gc][row]:
 // weighted V, max, sum) are merged per CTA, then per KV head across the slices of the cache.
@@ -180,7 +190,30 @@ __device__ __forceinline__ void attn_finish(const AttnParams& p, float* s_part, 
         float O = 0.f;
 #pragma unroll 8
         for (int sl = 0; sl < S; ++sl) O = fmaf(__ldcg(col + (int64_t)sl * GS * row), s_w[g * S + sl], O);
-        p.out[(int64_t)(hkv * p.group + g0 + g) * hd + d] = O * (1.0f / s_L[g]);
+        const float v = O * (1.0f / s_L[g]);
+        const int64_t e = (int64_t)(hkv * p.group + g0 + g) * hd + d;
+        p.out[e] = v;
+        if (p.xq) {   // lanes hold 32 consecutive elements of one head: one quantizer block
+            float mx = fabsf(v);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const double dq = (double)mx / 127.0;
+            const double id = dq == 0.0 ? 0.0 : 1.0 / dq;
+            int q = attn_round_half_up((double)v * id);
+            q = max(-127, min(127, q));
+            int sm = q;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+            uint32_t word = (uint32_t)(q & 0xFF) << (8 * (lane & 3));
+            word |= __shfl_xor_sync(0xffffffffu, word, 1);
+            word |= __shfl_xor_sync(0xffffffffu, word, 2);
+            const int64_t blk = e >> 5;
+            if ((lane & 3) == 0) reinterpret_cast<uint32_t*>(p.xq)[blk * 8 + (lane >> 2)] = word;
+            if (lane == 0) {
+                p.xs[blk] = (float)dq;
+                if (p.xsum) p.xsum[blk] = sm;
+            }
+        }
     }
 }
 
@@ -475,9 +508,10 @@ int32_t rstq_rope_append(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, r
     return RSTQ_OK;
 }
 
-int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
-                                  int64_t cache_len, rstq_buf* clenbuf, int64_t n_q, int64_t group, int64_t n_kv,
-                                  int64_t head_dim, int64_t maxpos, double scale) {
+static int32_t attention_impl(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
+                              int64_t cache_len, rstq_buf* clenbuf, int64_t n_q, int64_t group, int64_t n_kv,
+                              int64_t head_dim, int64_t maxpos, double scale, rstq_buf* xq, rstq_buf* xs,
+                              rstq_buf* xsum) {
     RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
     RSTQ_REQUIRE(n_q >= 1 && group >= 1 && n_kv >= 1 && n_q == group * n_kv, RSTQ_E_SHAPE,
                  "n_q = %lld must be group (%lld) x n_kv (%lld)", (long long)n_q, (long long)group, (long long)n_kv);
@@ -510,6 +544,15 @@ int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_
     if (S > 8 * row - 1) S = 8 * row - 1;   // the final merge keeps S weights + 1 sum per head in shared memory
     if (S > 512) S = 512;
     if (S < 1) S = 1;
+    if (xq) {
+        RSTQ_REQUIRE(fast, RSTQ_E_SHAPE, "the quantized output needs head_dim 64 or 128, got %lld", (long long)head_dim);
+        const int64_t n = n_q * head_dim;
+        RSTQ_REQUIRE(attn_buf(xq, ctx, n) && attn_buf(xs, ctx, n / 32 * 4) && (!xsum || attn_buf(xsum, ctx, n / 32 * 4)),
+                     RSTQ_E_INVALID, "invalid, unaligned or too small quantizer buffer");
+        RSTQ_REQUIRE(xq->dev == q->dev && xs->dev == q->dev && (!xsum || xsum->dev == q->dev), RSTQ_E_DEVICE,
+                     "buffers live on different devices");
+        if (S < 2) S = 2;   // the quantizer rides the merge of the slices
+    }
     const int64_t part_bytes = n_kv * gz * S * gs * row * 4;
     const bool fresh = ds.attn_scratch_bytes < kAttnCounters * 4 + part_bytes;
     rc = dev_reserve(ds, &ds.attn_scratch, &ds.attn_scratch_bytes, kAttnCounters * 4 + part_bytes);
@@ -530,6 +573,9 @@ int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_
     p.head_dim = (int)head_dim;
     p.S = (int)S;
     p.scale = (float)scale;
+    p.xq = xq ? (int8_t*)xq->ptr : nullptr;
+    p.xs = xq ? (float*)xs->ptr : nullptr;
+    p.xsum = xq && xsum ? (int32_t*)xsum->ptr : nullptr;
     const int64_t gc = group < gs ? group : gs;
     const dim3 grid((unsigned)n_kv, (unsigned)S, (unsigned)gz), block(kAttnWarps * 32);
     if (fast) {
@@ -552,6 +598,21 @@ int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_
     }
     ctx->launches++;
     return RSTQ_OK;
+}
+
+int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
+                                  int64_t cache_len, rstq_buf* clenbuf, int64_t n_q, int64_t group, int64_t n_kv,
+                                  int64_t head_dim, int64_t maxpos, double scale) {
+    return attention_impl(ctx, q, k, v, out, cache_len, clenbuf, n_q, group, n_kv, head_dim, maxpos, scale, nullptr,
+                          nullptr, nullptr);
+}
+
+int32_t rstq_gqa_decode_attention_quant_act(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
+                                            rstq_buf* xq, rstq_buf* xs, rstq_buf* xsum, int64_t cache_len,
+                                            rstq_buf* clenbuf, int64_t n_q, int64_t group, int64_t n_kv,
+                                            int64_t head_dim, int64_t maxpos, double scale) {
+    RSTQ_REQUIRE(xq && xs, RSTQ_E_INVALID, "null quantizer buffer");
+    return attention_impl(ctx, q, k, v, out, cache_len, clenbuf, n_q, group, n_kv, head_dim, maxpos, scale, xq, xs, xsum);
 }
 
 }  // extern "C"

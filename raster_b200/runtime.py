@@ -335,6 +335,13 @@ class Context:
         L.check(self.lib.rstq_kv_append(self.handle, src.handle, cache.handle, kvrow, pos, maxpos,
                                         posbuf.handle if posbuf is not None else None))
 
+    def gqa_decode_attention_quant_act(self, q, k, v, out, xq, xs, xsum, cache_len, n_q, group, n_kv, head_dim,
+                                       maxpos, scale, clenbuf=None) -> None:
+        L.check(self.lib.rstq_gqa_decode_attention_quant_act(
+            self.handle, q.handle, k.handle, v.handle, out.handle, xq.handle, xs.handle,
+            xsum.handle if xsum is not None else None, cache_len,
+            clenbuf.handle if clenbuf is not None else None, n_q, group, n_kv, head_dim, maxpos, scale))
+
     def rope_append(self, q, k, v, kcache, vcache, n_q, n_kv, head_dim, theta, pos=0, maxpos=1, posbuf=None) -> None:
         L.check(self.lib.rstq_rope_append(self.handle, q.handle, k.handle, v.handle, kcache.handle, vcache.handle,
                                           n_q, n_kv, head_dim, theta, pos, maxpos,

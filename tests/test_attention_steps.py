@@ -209,3 +209,27 @@ def test_rope_append_equals_its_four_steps(ctx, n_q, n_kv, hd):
     assert e.value.code == L.E_SHAPE
     for o in (bq, bk, bv, bkc, bvc, fq, fk, fv, fkc, fvc, bp):
         o.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_q,n_kv,hd,clen,maxpos", [(32, 32, 128, 1, 8), (32, 8, 128, 700, 1024), (8, 4, 64, 40, 64)])
+def test_attention_with_quantized_output_equals_attention_then_quantizer(ctx, n_q, n_kv, hd, clen, maxpos):
+    group, n = n_q // n_kv, n_q * hd
+    q, k, v = synth.normal(61, n), synth.normal(62, maxpos * n_kv * hd), synth.normal(63, maxpos * n_kv * hd)
+    scale = 1.0 / math.sqrt(hd)
+    bq, bk, bv = ctx.array_to_buffer(q), ctx.array_to_buffer(k), ctx.array_to_buffer(v)
+    bo = ctx.make_buffer(n, np.float32)
+    q1, s1, z1 = ctx.make_buffer(n, np.int8), ctx.make_buffer(n // 32, np.float32), ctx.make_buffer(n // 32, np.int32)
+    q2, s2, z2 = ctx.make_buffer(n, np.int8), ctx.make_buffer(n // 32, np.float32), ctx.make_buffer(n // 32, np.int32)
+    ctx.gqa_decode_attention_quant_act(bq, bk, bv, bo, q2, s2, z2, clen, n_q, group, n_kv, hd, maxpos, scale)
+    ctx.quant_act_i8(bo, q1, s1, z1, 1, n)          # the quantizer on the output the fused call also wrote
+    ctx.sync()
+    assert relerr(bo.download(), orc.gqa_decode_attention(q, k, v, clen, n_q, group, n_kv, hd, scale)) <= 1e-5
+    assert np.array_equal(q1.download(), q2.download())
+    assert np.array_equal(s1.download().view(np.uint32), s2.download().view(np.uint32))
+    assert np.array_equal(z1.download(), z2.download())
+    with pytest.raises(L.RstqError) as e:
+        ctx.gqa_decode_attention_quant_act(bq, bk, bv, bo, q2, s2, z2, 1, n // 32, 1, n // 32, 32, 1, scale)
+    assert e.value.code == L.E_SHAPE                  # head_dim 32: no fused quantizer
+    for o in (bq, bk, bv, bo, q1, s1, z1, q2, s2, z2):
+        o.free()
