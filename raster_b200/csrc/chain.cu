@@ -12,7 +12,7 @@
 
 namespace rstq {
 
-constexpr int kRowThreads = 256;
+constexpr int kRowThreads = 1024;
 
 __device__ __forceinline__ int chain_round_half_up(double v) {
     const double f = floor(v);
@@ -35,7 +35,36 @@ __device__ __forceinline__ float cta_sum(float v, float* s_red) {
 // One CTA per row.  QUANT = false: out f32.  QUANT = true: int8 codes + per-32-block scale and sum
 // (features % 32 == 0; each warp owns whole blocks so the block reductions are warp shuffles).
 // RES: the row normalized is x + res (residual-add! feeding rms-norm!); the sum is stored to
-// `sum` first (the residual stream the layer carries on), by the thread that reads it back below.
+// `sum` first (the residual stream the layer carries on).
+// 1024 threads per row and the row kept in registers (up to kRowKeep elements per thread = 8192
+// features; longer rows read the rest back): a decode step has ONE row, so the kernel's time is its
+// dependent chain -- loads, a block reduction, the double-precision quantizer -- and not its bytes.
+// With 256 threads and two passes over memory it took 15 us per launch on a 4096-feature row, a third
+// of a whole decoder layer.
+constexpr int kRowKeep = 8;
+
+__device__ __forceinline__ void quant_block_store(float v, int lane, int64_t blk, int8_t* __restrict__ xq,
+                                                  float* __restrict__ xs, int32_t* __restrict__ xsum) {
+    float mx = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const double d = (double)mx / 127.0;
+    const double id = d == 0.0 ? 0.0 : 1.0 / d;
+    int q = chain_round_half_up((double)v * id);
+    q = max(-127, min(127, q));
+    int s = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    uint32_t word = (uint32_t)(q & 0xFF) << (8 * (lane & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if ((lane & 3) == 0) reinterpret_cast<uint32_t*>(xq)[blk * 8 + (lane >> 2)] = word;
+    if (lane == 0) {
+        xs[blk] = (float)d;
+        if (xsum) xsum[blk] = s;
+    }
+}
+
 template <bool QUANT, bool RES = false>
 __global__ void __launch_bounds__(kRowThreads)
 rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
@@ -45,13 +74,29 @@ rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t r = blockIdx.x;
-    const float* xr = RES ? sum + r * features : x + r * features;
+    const float* xr = RES ? sum + r * features : x + r * features;   // where the row is read back from
+    float keep[kRowKeep];
     float ss = 0.f;
-    for (int64_t i = threadIdx.x; i < features; i += kRowThreads) {
+#pragma unroll
+    for (int k = 0; k < kRowKeep; ++k) {
+        const int64_t i = threadIdx.x + (int64_t)k * kRowThreads;
+        float v = 0.f;
+        if (i < features) {
+            if (RES) {
+                v = x[r * features + i] + res[r * features + i];
+                sum[r * features + i] = v;
+            } else {
+                v = xr[i];
+            }
+        }
+        keep[k] = v;
+        ss = fmaf(v, v, ss);
+    }
+    for (int64_t i = threadIdx.x + (int64_t)kRowKeep * kRowThreads; i < features; i += kRowThreads) {
         float v;
         if (RES) {
             v = x[r * features + i] + res[r * features + i];
-            sum[r * features + i] = v;
+            sum[r * features + i] = v;   // read back below by this same thread
         } else {
             v = xr[i];
         }
@@ -59,34 +104,23 @@ rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
     }
     const float ms = cta_sum(ss, s_red) / (float)features;
     const float inv = 1.0f / sqrtf(ms + eps);
-    if (!QUANT) {
-        for (int64_t i = threadIdx.x; i < features; i += kRowThreads)
-            out[r * features + i] = xr[i] * inv * (gain_offset + w[i]);
-        return;
-    }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
     const int64_t nb = features >> 5;
-    for (int64_t b = warp; b < nb; b += kRowThreads / 32) {
-        const int64_t i = b * 32 + lane;
-        const float v = xr[i] * inv * (gain_offset + w[i]);
-        float mx = fabsf(v);
+    // element i = threadIdx.x + k * 1024: a warp holds the 32 elements of block i / 32 (features % 32 == 0
+    // when QUANT), so the block reductions are warp shuffles and a whole warp is in or out of range
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        const double d = (double)mx / 127.0;
-        const double id = d == 0.0 ? 0.0 : 1.0 / d;
-        int q = chain_round_half_up((double)v * id);
-        q = max(-127, min(127, q));
-        int s = q;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        uint32_t word = (uint32_t)(q & 0xFF) << (8 * (lane & 3));
-        word |= __shfl_xor_sync(0xffffffffu, word, 1);
-        word |= __shfl_xor_sync(0xffffffffu, word, 2);
-        if ((lane & 3) == 0) reinterpret_cast<uint32_t*>(xq)[(r * nb + b) * 8 + (lane >> 2)] = word;
-        if (lane == 0) {
-            xs[r * nb + b] = (float)d;
-            if (xsum) xsum[r * nb + b] = s;
+    for (int k = 0; k < kRowKeep; ++k) {
+        const int64_t i = threadIdx.x + (int64_t)k * kRowThreads;
+        if (i < features) {
+            const float v = keep[k] * inv * (gain_offset + w[i]);
+            if (QUANT) quant_block_store(v, lane, r * nb + (i >> 5), xq, xs, xsum);
+            else out[r * features + i] = v;
         }
+    }
+    for (int64_t i = threadIdx.x + (int64_t)kRowKeep * kRowThreads; i < features; i += kRowThreads) {
+        const float v = xr[i] * inv * (gain_offset + w[i]);
+        if (QUANT) quant_block_store(v, lane, r * nb + (i >> 5), xq, xs, xsum);
+        else out[r * features + i] = v;
     }
 }
 
