@@ -98,7 +98,7 @@ struct AttnParams {
     int n_q, group, n_kv, head_dim, S;
     float scale;
     // optional: the output quantized to int8 blocks of 32 as well (the o projection's input), by the
-    // CTA that writes it; only with S >= 2 and head_dim % 32 == 0 (a warp then owns whole blocks)
+    // CTA that writes it; only with head_dim % 32 == 0 (a warp then owns whole blocks)
     int8_t* xq;
     float* xs;
     int32_t* xsum;
@@ -112,38 +112,71 @@ __device__ __forceinline__ int attn_round_half_up(double v) {
 // Second half of both attention kernels: the per-warp states in shared memory ([warps][gc][row]:
 // weighted V, max, sum) are merged per CTA, then per KV head across the slices of the cache.
 // GS = query heads per CTA (the stride of the scratch).
+// one value of the output, and with it -- when asked for -- its 32-element quantizer block (the 32
+// lanes of the warp hold 32 consecutive elements of one head)
+__device__ __forceinline__ void attn_store(const AttnParams& p, int64_t e, float v, int lane) {
+    p.out[e] = v;
+    if (p.xq) {
+        float mx = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const double dq = (double)mx / 127.0;
+        const double id = dq == 0.0 ? 0.0 : 1.0 / dq;
+        int q = attn_round_half_up((double)v * id);
+        q = max(-127, min(127, q));
+        int sm = q;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+        uint32_t word = (uint32_t)(q & 0xFF) << (8 * (lane & 3));
+        word |= __shfl_xor_sync(0xffffffffu, word, 1);
+        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+        const int64_t blk = e >> 5;
+        if ((lane & 3) == 0) reinterpret_cast<uint32_t*>(p.xq)[blk * 8 + (lane >> 2)] = word;
+        if (lane == 0) {
+            p.xs[blk] = (float)dq;
+            if (p.xsum) p.xsum[blk] = sm;
+        }
+    }
+}
+
 template <int GS>
 __device__ __forceinline__ void attn_finish(const AttnParams& p, float* s_part, int* s_last_p, int gc, int g0, int hkv,
                                             int split, int gz, int hd, int row) {
+    __shared__ float s_cw[kAttnGroup][kAttnWarps];   // weight of each warp's state in the CTA's state
+    __shared__ float s_cM[kAttnGroup], s_cL[kAttnGroup];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (warp < gc && lane < kAttnWarps) {            // warp g merges the eight (max, sum) pairs of head g
+        const float* st = s_part + (lane * gc + warp) * row + hd;
+        const float mw = st[0], lw = st[1];
+        float M = mw;
+#pragma unroll
+        for (int o = kAttnWarps / 2; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFu, M, o));
+        const float e = expf(mw - M);
+        float L = lw * e;
+#pragma unroll
+        for (int o = kAttnWarps / 2; o > 0; o >>= 1) L += __shfl_xor_sync(0xFFu, L, o);
+        s_cw[warp][lane] = e;
+        if (lane == 0) {
+            s_cM[warp] = M;
+            s_cL[warp] = L;
+        }
+    }
     __syncthreads();
     // CTA state per (g, d): straight to out when there is one slice, else to the scratch
     float* mine = p.part + ((((int64_t)hkv * gridDim.z + gz) * p.S + split) * GS) * row;
-    for (int i = threadIdx.x; i < gc * row; i += blockDim.x) {
-        const int g = i / row, d = i - g * row;
-        if (d >= hd + 2) continue;   // padding
-        const float* base = s_part + g * row;
-        float M = kNegInf;
-        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, base[w * gc * row + hd]);
-        float val;
-        if (d == hd) {
-            val = M;
-        } else {
-            float acc1 = 0.f;
-            const int src = d == hd + 1 ? hd + 1 : d;
-            for (int w = 0; w < kAttnWarps; ++w)
-                acc1 = fmaf(base[w * gc * row + src], expf(base[w * gc * row + hd] - M), acc1);
-            val = acc1;
-        }
-        if (p.S == 1) {
-            if (d < hd) {
-                float L = 0.f;
-                for (int w = 0; w < kAttnWarps; ++w)
-                    L = fmaf(base[w * gc * row + hd + 1], expf(base[w * gc * row + hd] - M), L);
-                p.out[(int64_t)(hkv * p.group + g0 + g) * hd + d] = val * (1.0f / L);
-            }
-        } else {
-            mine[g * row + d] = val;
-        }
+    for (int i = threadIdx.x; i < gc * hd; i += blockDim.x) {
+        const int g = i / hd, d = i - g * hd;
+        const float* base = s_part + g * row + d;
+        float O = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) O = fmaf(base[w * gc * row], s_cw[g][w], O);
+        if (p.S == 1) attn_store(p, (int64_t)(hkv * p.group + g0 + g) * hd + d, O * (1.0f / s_cL[g]), lane);
+        else mine[g * row + d] = O;
+    }
+    if (p.S > 1 && threadIdx.x < gc) {
+        mine[threadIdx.x * row + hd] = s_cM[threadIdx.x];
+        mine[threadIdx.x * row + hd + 1] = s_cL[threadIdx.x];
     }
     if (p.S == 1) return;
     __threadfence();
@@ -160,7 +193,7 @@ __device__ __forceinline__ void attn_finish(const AttnParams& p, float* s_part, 
     // through shared memory (the per-warp states are dead by now; the host keeps S + 1 <= 8 * row),
     // so that the loop over the slices below is independent loads the compiler can batch.
     const float* all = p.part + (((int64_t)hkv * gridDim.z + gz) * p.S * GS) * row;
-    const int S = p.S, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int S = p.S;
     float* s_w = s_part;            // [gc][S] maxima, then weights
     float* s_L = s_part + gc * S;   // [gc]
     for (int i = threadIdx.x; i < gc * S; i += blockDim.x) {
@@ -190,30 +223,7 @@ __device__ __forceinline__ void attn_finish(const AttnParams& p, float* s_part, 
         float O = 0.f;
 #pragma unroll 8
         for (int sl = 0; sl < S; ++sl) O = fmaf(__ldcg(col + (int64_t)sl * GS * row), s_w[g * S + sl], O);
-        const float v = O * (1.0f / s_L[g]);
-        const int64_t e = (int64_t)(hkv * p.group + g0 + g) * hd + d;
-        p.out[e] = v;
-        if (p.xq) {   // lanes hold 32 consecutive elements of one head: one quantizer block
-            float mx = fabsf(v);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const double dq = (double)mx / 127.0;
-            const double id = dq == 0.0 ? 0.0 : 1.0 / dq;
-            int q = attn_round_half_up((double)v * id);
-            q = max(-127, min(127, q));
-            int sm = q;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
-            uint32_t word = (uint32_t)(q & 0xFF) << (8 * (lane & 3));
-            word |= __shfl_xor_sync(0xffffffffu, word, 1);
-            word |= __shfl_xor_sync(0xffffffffu, word, 2);
-            const int64_t blk = e >> 5;
-            if ((lane & 3) == 0) reinterpret_cast<uint32_t*>(p.xq)[blk * 8 + (lane >> 2)] = word;
-            if (lane == 0) {
-                p.xs[blk] = (float)dq;
-                if (p.xsum) p.xsum[blk] = sm;
-            }
-        }
+        attn_store(p, (int64_t)(hkv * p.group + g0 + g) * hd + d, O * (1.0f / s_L[g]), lane);
     }
 }
 
@@ -551,7 +561,6 @@ static int32_t attention_impl(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf*
                      RSTQ_E_INVALID, "invalid, unaligned or too small quantizer buffer");
         RSTQ_REQUIRE(xq->dev == q->dev && xs->dev == q->dev && (!xsum || xsum->dev == q->dev), RSTQ_E_DEVICE,
                      "buffers live on different devices");
-        if (S < 2) S = 2;   // the quantizer rides the merge of the slices
     }
     const int64_t part_bytes = n_kv * gz * S * gs * row * 4;
     const bool fresh = ds.attn_scratch_bytes < kAttnCounters * 4 + part_bytes;
