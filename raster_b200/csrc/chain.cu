@@ -75,7 +75,7 @@ rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t r = blockIdx.x;
     const float* xr = RES ? sum + r * features : x + r * features;   // where the row is read back from
-    float keep[kRowKeep];
+    float keep[kRowKeep], gain[kRowKeep];
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < kRowKeep; ++k) {
@@ -90,6 +90,7 @@ rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
             }
         }
         keep[k] = v;
+        gain[k] = i < features ? gain_offset + w[i] : 0.f;   // fetched now: its latency hides under the reduction
         ss = fmaf(v, v, ss);
     }
     for (int64_t i = threadIdx.x + (int64_t)kRowKeep * kRowThreads; i < features; i += kRowThreads) {
@@ -112,7 +113,7 @@ rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float*
     for (int k = 0; k < kRowKeep; ++k) {
         const int64_t i = threadIdx.x + (int64_t)k * kRowThreads;
         if (i < features) {
-            const float v = keep[k] * inv * (gain_offset + w[i]);
+            const float v = keep[k] * inv * gain[k];
             if (QUANT) quant_block_store(v, lane, r * nb + (i >> 5), xq, xs, xsum);
             else out[r * features + i] = v;
         }
