@@ -280,3 +280,82 @@ def _builtin():
 
 
 _builtin()
+
+
+# ---- op chains as one resident graph (chain-program! / run-chain!, src/raster/gpu/core.clj:711-767) ----
+VALID_CHAIN_ROLES = ("constant", "state", "input", "output", "scratch")
+
+
+class Chain:
+    def __init__(self, arena, buffers, roles, bounds, graph):
+        self.arena, self.buffers, self.roles, self.bounds, self.graph = arena, buffers, roles, bounds, graph
+
+
+def chain_program(buffers: dict, steps: list, weights: dict | None = None) -> Chain:
+    """Bind a hand-authored op chain as one resident CUDA graph.
+      buffers: {key: (dtype, size, init array or None, role)}, role one of VALID_CHAIN_ROLES
+               (default "scratch");
+      steps:   [{"op": registered kernel name, "bind": [buffer key | weight key | None, ...] in the
+                 kernel's array order, "scalars": [...], "n": work items}];
+      weights: {key: QWeight} for the matmul steps (bound by the caller: binding is load-time work).
+    Allocates the buffers in an arena of its own (uploading init arrays), runs every step once
+    (scratch is sized outside a capture), then records the sequence.  run_chain replays it."""
+    weights = weights or {}
+    roles = {}
+    for k, spec in buffers.items():
+        role = spec[3] if len(spec) > 3 and spec[3] is not None else "scratch"
+        if role not in VALID_CHAIN_ROLES:
+            raise ValueError(f"chain buffer {k!r} has unknown role {role!r} -- must be one of {VALID_CHAIN_ROLES}")
+        roles[k] = role
+    arena = make_kernel_arena()
+    recs = {}
+    try:
+        with with_arena(arena):
+            for k, spec in buffers.items():
+                dtype, size, init = spec[0], spec[1], spec[2] if len(spec) > 2 else None
+                recs[k] = make_buffer(size, dtype)
+                if init is not None:
+                    a = np.ascontiguousarray(init)
+                    if a.nbytes > recs[k]["byte_size"]:
+                        raise ValueError(f"chain buffer {k!r}: init array larger than the buffer")
+                    recs[k]["segment"].upload(a)
+
+        def resolve(key):
+            if key is None:
+                return None
+            if key in recs:
+                return recs[key]
+            if key in weights:
+                return weights[key]
+            raise KeyError(f"chain step binds {key!r}, which is neither a buffer nor a weight of this chain")
+
+        bounds = [bind_registered_map_void_kernel(st["op"], [resolve(b) for b in st["bind"]], st.get("scalars", []),
+                                                  st.get("n"), async_=True) for st in steps]
+        for b in bounds:
+            launch_registered_bound(b)
+        synchronize_async()
+        graph = record_graph(bounds)
+    except Exception:
+        close_kernel_arena(arena)
+        raise
+    return Chain(arena, recs, roles, bounds, graph)
+
+
+def run_chain(chain: Chain, inputs: dict) -> dict:
+    """Refresh the given "input" buffers (addresses stay), replay the graph, download the "output"
+    buffers: {key: array}.  "constant" / "state" / "scratch" buffers never move."""
+    for k, arr in inputs.items():
+        if chain.roles.get(k) != "input":
+            raise KeyError(f"{k!r} is not an input buffer of this chain")
+        chain.buffers[k]["segment"].upload(np.ascontiguousarray(arr))
+    replay_graph(chain.graph)
+    return {k: buffer_to_array(chain.buffers[k]) for k, r in chain.roles.items() if r == "output"}
+
+
+def destroy_chain(chain: Chain) -> None:
+    if chain.graph is not None:
+        destroy_graph(chain.graph)
+        chain.graph = None
+    for b in chain.bounds:
+        destroy_prepared(b)
+    close_kernel_arena(chain.arena)

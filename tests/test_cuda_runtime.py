@@ -129,3 +129,52 @@ def test_attention_steps_through_the_table():
         rt.close_kernel_arena(arena)
     finally:
         rt.shutdown()
+
+
+def test_chain_roles_are_checked():
+    with pytest.raises(ValueError):
+        rt.chain_program({"x": ("float", 8, None, "input"), "y": ("float", 8, None, "bogus")}, [])
+
+
+@pytest.mark.gpu
+def test_chain_program_replays_a_decode_mlp():
+    """rms-norm -> quantize -> gate|up matmul -> SwiGLU, bound once (chain-program!), replayed per
+    input (run-chain!), against the oracle."""
+    rt.init(("cuda:0",))
+    try:
+        H, F = 256, 512
+        Wg, Wu = synth.normal(3, F * H, 0.05), synth.normal(4, F * H, 0.05)
+        gq, gs = orc.quantize_weight(Wg, 4)
+        uq, us = orc.quantize_weight(Wu, 4)
+        gain = synth.normal(5, H, 0.1) + np.float32(1.0)
+        ctx = rt._ctx()
+        wts = {"wg": ctx.bind_weight(gq, gs, F, H, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR),
+               "wu": ctx.bind_weight(uq, us, F, H, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)}
+        buffers = {"x": ("float", H, None, "input"), "gain": ("float", H, gain, "constant"),
+                   "xn": ("float", H, None, "scratch"), "xq": ("byte", H, None), "xs": ("float", H // 32, None),
+                   "xsum": ("int", H // 32, None), "g": ("float", F, None), "u": ("float", F, None),
+                   "act": ("float", F, None, "output")}
+        steps = [{"op": "rms-norm!", "bind": ["x", "gain", "xn"], "scalars": [1, H, 1e-6, 0.0], "n": H},
+                 {"op": "quantize-act-i8", "bind": ["xn", "xq", "xs", "xsum"], "scalars": [1, H], "n": H // 32},
+                 {"op": "qmatmul-q4-x8!", "bind": ["xq", "xs", "xsum", "wg", "g"], "scalars": [1], "n": F},
+                 {"op": "qmatmul-q4-x8!", "bind": ["xq", "xs", "xsum", "wu", "u"], "scalars": [1], "n": F},
+                 {"op": "silu-mul!", "bind": ["g", "u", "act"], "scalars": [F], "n": F}]
+        chain = rt.chain_program(buffers, steps, wts)
+        for seed in (6, 7):
+            x = synth.normal(seed, H)
+            got = rt.run_chain(chain, {"x": x})
+            assert set(got) == {"act"}
+            xn = orc.rms_norm(x, gain, 1, H, 1e-6, 0.0)
+            xq, xs, xsum = orc.quantize_act_i8(xn, 1, H)
+            g = orc.matmul_a8_f64(gq, gs, 0, xq, xs, xsum, 1, H, F).ravel().astype(np.float32)
+            u = orc.matmul_a8_f64(uq, us, 0, xq, xs, xsum, 1, H, F).ravel().astype(np.float32)
+            assert relerr(got["act"], orc.silu_mul(g, u)) <= 1e-5
+        with pytest.raises(KeyError):
+            rt.run_chain(chain, {"gain": gain})             # a constant is not an input
+        rt.destroy_chain(chain)
+        with pytest.raises(KeyError):
+            rt.chain_program({"x": ("float", 8, None, "input")}, [{"op": "silu-mul!", "bind": ["x", "nope", "x"], "scalars": [8]}])
+        for w in wts.values():
+            w.free()
+    finally:
+        rt.shutdown()
