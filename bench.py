@@ -953,6 +953,109 @@ def run_attn(args):
     ctx.close()
 
 
+def run_decoder_tp(args, world, rank, local_rank):
+    """--case decoder:<bits>:<cache_len> under torchrun: the same layer sharded the Megatron way over the
+    ranks -- heads split for q|k|v and attention (no exchange), o split by rows (all-reduce fused into the
+    decode kernel), gate|up split by columns (no exchange), down by rows (all-reduce): two exchanges per
+    layer.  Strong scaling: the layer is fixed, each rank holds 1/N of every matrix and of the caches."""
+    import torch
+    import torch.distributed as dist
+    from raster_b200 import Context
+    from raster_b200 import _lib as L
+    from raster_b200 import synth
+    parts = args.case.split(":")
+    bits = int(parts[1]) if len(parts) > 1 else 4
+    clen = int(parts[2]) if len(parts) > 2 else 1024
+    H, F, NQ, NKV, HD = 4096, 11008, 32, 32, 128
+    P = world
+    nq, nkv, Fl = NQ // P, NKV // P, F // P
+    Hl, kvrow, maxpos = nq * HD, nkv * HD, clen
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = Context((f"cuda:{local_rank}",))
+    fmt = L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0
+    rng = np.random.default_rng(1 + rank)
+    shapes = {"qkv": (Hl + 2 * kvrow, H), "o": (H, Hl), "gate_up": (2 * Fl, H), "down": (H, Fl)}
+    per_layer_w = sum(stream_bytes(o, i, bits) for o, i in shapes.values()) * P
+    per_layer_kv = 2 * clen * NKV * HD * 4
+    layers = max(2, -(-3 * ctx.device_info()["l2_bytes"] // ((per_layer_w + per_layer_kv) // P)))
+    tp, region, ptrs = tp_group(ctx, dist, world, rank, 4 * H)
+    f32 = np.float32
+    stack = []
+    for _ in range(layers):
+        lay = {}
+        for name, (o, i) in shapes.items():
+            codes = rng.integers(0, 256, o * i * bits // 8, dtype=np.uint8)
+            scales = (rng.standard_normal(o * (i // 32)) * 0.01).astype(np.float32)
+            lay[name] = ctx.bind_weight(codes, scales, o, i, fmt, L.LAYOUT_ROWMAJOR)
+        lay["kc"] = ctx.array_to_buffer(synth.normal(7, maxpos * kvrow))
+        lay["vc"] = ctx.array_to_buffer(synth.normal(8, maxpos * kvrow))
+        lay["n1"] = ctx.array_to_buffer(np.ones(H, f32))
+        lay["n2"] = ctx.array_to_buffer(np.ones(H, f32))
+        stack.append(lay)
+    x = ctx.array_to_buffer(synth.normal(5, H))
+    h, o_, att, down = (ctx.make_buffer(n, f32) for n in (H, H, Hl, H))
+    act = ctx.make_buffer(Fl, f32)
+    xq, xs, xsum = ctx.make_buffer(H, np.int8), ctx.make_buffer(H // 32, f32), ctx.make_buffer(H // 32, np.int32)
+    bpos = ctx.array_to_buffer(np.array([clen - 1], np.int64))
+    blen = ctx.array_to_buffer(np.array([clen], np.int64))
+    scale = 1.0 / float(np.sqrt(HD))
+    qkv = ctx.make_buffer(Hl + 2 * kvrow, f32)
+    q_s, k_s, v_s = (ctx.wrap_buffer(qkv.device_ptr + 4 * off, n, f32) for off, n in ((0, Hl), (Hl, kvrow), (Hl + kvrow, kvrow)))
+    gu = ctx.make_buffer(2 * Fl, f32)
+    g_s, u_s = ctx.wrap_buffer(gu.device_ptr, Fl, f32), ctx.wrap_buffer(gu.device_ptr + 4 * Fl, Fl, f32)
+    down.fill_bytes(0)
+
+    def one_pass():
+        for lay in stack:
+            ctx.residual_rms_norm_quant_act(x, down, h, lay["n1"], xq, xs, xsum, 1, H)
+            ctx.qmatmul_prequant(lay["qkv"], xq, xs, xsum, qkv, 1)                      # this rank's heads
+            ctx.rope_append(q_s, k_s, v_s, lay["kc"], lay["vc"], nq, nkv, HD, 10000.0, maxpos=maxpos, posbuf=bpos)
+            ctx.gqa_decode_attention(q_s, lay["kc"], lay["vc"], att, 0, nq, nq // nkv, nkv, HD, maxpos, scale, clenbuf=blen)
+            tp.qmatmul(lay["o"], att, o_, 1, L.F32, L.MODE_A8, L.SPLIT_ROW)             # all-reduce
+            ctx.residual_rms_norm_quant_act(h, o_, x, lay["n2"], xq, xs, xsum, 1, H)
+            ctx.qmatmul_prequant(lay["gate_up"], xq, xs, xsum, gu, 1)                   # this rank's columns
+            ctx.silu_mul(g_s, u_s, act, Fl)
+            tp.qmatmul(lay["down"], act, down, 1, L.F32, L.MODE_A8, L.SPLIT_ROW)        # all-reduce
+
+    n0 = ctx.launch_count()
+    one_pass()
+    ctx.sync()
+    kernels = (ctx.launch_count() - n0) // layers
+    dist.barrier()
+    ctx.graph_begin()
+    one_pass()
+    g = ctx.graph_end()
+    for _ in range(3):
+        g.replay()
+    ctx.sync()
+    dist.barrier()
+    e0, e1 = ctx.event(), ctx.event()
+    n = max(3, args.steps)
+    e0.record()
+    for _ in range(n):
+        g.replay()
+    e1.record()
+    ctx.sync()
+    t = torch.tensor([e0.elapsed_ms(e1) / n], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    if rank == 0:
+        us_layer = float(t.item()) * 1e3 / layers
+        print(json.dumps({"case": args.case, "n_gpus": world, "layers_per_step": layers, "kernels_per_layer": kernels,
+                          "cache_len": clen, "us_per_layer": round(us_layer, 2), "exchanges_per_layer": 2,
+                          "weight_bytes_per_layer": per_layer_w, "kv_bytes_per_layer": per_layer_kv,
+                          "tokens_per_s_32_layers": round(1e6 / (32 * us_layer), 1), "scaling": "strong"}))
+    g.destroy()
+    tp.free()
+    for r in range(world):
+        if r != rank:
+            ctx.ipc_close(ptrs[r])
+    dist.barrier()
+    dist.destroy_process_group()
+    ctx.close()
+
+
 def run_decoder(args):
     """--case decoder:<bits>:<cache_len>: one token through whole Llama-7B-style decoder layers on one GPU --
     the reference's decode chain (test/raster/dl/decoder_layer_gpu_test.clj:59-77): rms-norm + quantize,
@@ -1132,6 +1235,9 @@ def main():
     ap.add_argument("--plan", type=int, default=0, help="with --case: decode work split (rstq_tune key 4)")
     args = ap.parse_args()
     if args.case and args.case.startswith("decoder"):
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world > 1:
+            return run_decoder_tp(args, world, int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")))
         return run_decoder(args)
     if args.case and args.case.startswith("layer"):
         return run_layer(args)
