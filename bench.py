@@ -661,6 +661,16 @@ def run_ours(args):
         except Exception as e:  # a detail point must not take the headline down
             detail["gemm_error"] = repr(e)[:200]
 
+        # ---- the caller of the path: one token through a whole decoder layer (own context, freed after) ----
+        try:
+            import types
+            dl = run_decoder(types.SimpleNamespace(case="decoder:4:1024", steps=5), emit=False)
+            detail["decoder_layer_q4_len1024_us"] = dl["us_per_layer"]
+            detail["decoder_layer_kernels"] = dl["kernels_per_layer"]
+            detail["decoder_tokens_per_s_32_layers"] = dl["tokens_per_s_32_layers"]
+        except Exception as e:
+            detail["decoder_error"] = repr(e)[:200]
+
         # ---- e2e: host arrays through the operator entry point ----------------
         host_copies = []
         for w in weights:
@@ -1056,7 +1066,7 @@ def run_decoder_tp(args, world, rank, local_rank):
     ctx.close()
 
 
-def run_decoder(args):
+def run_decoder(args, emit=True):
     """--case decoder:<bits>:<cache_len>: one token through whole Llama-7B-style decoder layers on one GPU --
     the reference's decode chain (test/raster/dl/decoder_layer_gpu_test.clj:59-77): rms-norm + quantize,
     q / k / v, rope, cache append, GQA attention over f32 caches, o, residual, rms-norm + quantize,
@@ -1170,12 +1180,16 @@ def run_decoder(args):
     e1.record()
     ctx.sync()
     us_layer = e0.elapsed_ms(e1) * 1e3 / n / layers
-    print(json.dumps({"case": args.case, "layers_per_step": layers, "kernels_per_layer": kernels,
-                      "cache_len": clen, "us_per_layer": round(us_layer, 2),
-                      "weight_bytes_per_layer": per_layer_w, "kv_bytes_per_layer": per_layer_kv,
-                      "GBs": round((per_layer_w + per_layer_kv) / us_layer / 1e3, 1),
-                      "tokens_per_s_32_layers": round(1e6 / (32 * us_layer), 1)}))
+    res = {"case": args.case, "layers_per_step": layers, "kernels_per_layer": kernels,
+           "cache_len": clen, "us_per_layer": round(us_layer, 2),
+           "weight_bytes_per_layer": per_layer_w, "kv_bytes_per_layer": per_layer_kv,
+           "GBs": round((per_layer_w + per_layer_kv) / us_layer / 1e3, 1),
+           "tokens_per_s_32_layers": round(1e6 / (32 * us_layer), 1)}
+    g.destroy()
     ctx.close()
+    if emit:
+        print(json.dumps(res))
+    return res
 
 
 def run_case(args):
