@@ -324,7 +324,7 @@ gqa_decode_kernel(const AttnParams p) {
 // registers, and with one head per CTA three CTAs fit an SM instead of two.
 constexpr int kFastGroup = 4;
 template <int VEC, int GC>
-__global__ void __launch_bounds__(kAttnWarps * 32)
+__global__ void __launch_bounds__(kAttnWarps * 32, GC == 1 ? 4 : 2)
 gqa_decode_fast_kernel(const AttnParams p) {
     extern __shared__ __align__(16) float s_part[];   // [kAttnWarps][gc][hd + 4], then q [gc][hd]
     __shared__ int s_last;
@@ -357,12 +357,41 @@ gqa_decode_fast_kernel(const AttnParams p) {
 #pragma unroll
         for (int u = 0; u < VEC; ++u) acc[g][u] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    // the rows of the next position are requested before the current one is worked on: a CTA has only
+    // a few positions per lane group, so an exposed load latency per step is most of the kernel
+    // (not with one head per CTA, where four CTAs per SM hide the latency already, and not with four
+    // heads of 128: the second set of rows would spill accumulators -- both measured)
+    constexpr bool PF = GC > 1 && !(GC == 4 && VEC == 4);
+    float4 kk[VEC], vv[VEC], kn[VEC], vn[VEC];
+    {
+        const int64_t jf = j0 + warp * 4 + grp;
+        if (PF && jf < j1) {
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) kn[u] = __ldg(kb + jf * kv4 + 8 * u);
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) vn[u] = __ldg(vb + jf * kv4 + 8 * u);
+        }
+    }
     for (int64_t j = j0 + warp * 4 + grp; j < j1; j += kAttnWarps * 4) {
-        float4 kk[VEC], vv[VEC];
+        if (PF) {
 #pragma unroll
-        for (int u = 0; u < VEC; ++u) kk[u] = __ldg(kb + j * kv4 + 8 * u);
+            for (int u = 0; u < VEC; ++u) {
+                kk[u] = kn[u];
+                vv[u] = vn[u];
+            }
+        }
+        const int64_t jn = j + kAttnWarps * 4;
+        if (!PF) {   // fetch this position's rows now
 #pragma unroll
-        for (int u = 0; u < VEC; ++u) vv[u] = __ldg(vb + j * kv4 + 8 * u);
+            for (int u = 0; u < VEC; ++u) kk[u] = __ldg(kb + j * kv4 + 8 * u);
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) vv[u] = __ldg(vb + j * kv4 + 8 * u);
+        } else if (jn < j1) {
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) kn[u] = __ldg(kb + jn * kv4 + 8 * u);
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) vn[u] = __ldg(vb + jn * kv4 + 8 * u);
+        }
 #pragma unroll
         for (int g = 0; g < GC; ++g) {
             if (g < gc) {
