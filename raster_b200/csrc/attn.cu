@@ -359,9 +359,8 @@ gqa_decode_fast_kernel(const AttnParams p) {
     }
     // the rows of the next position are requested before the current one is worked on: a CTA has only
     // a few positions per lane group, so an exposed load latency per step is most of the kernel
-    // (not with one head per CTA, where four CTAs per SM hide the latency already, and not with four
-    // heads of 128: the second set of rows would spill accumulators -- both measured)
-    constexpr bool PF = GC > 1 && !(GC == 4 && VEC == 4);
+    // (not with one head per CTA, where four CTAs per SM hide the latency already: measured)
+    constexpr bool PF = GC > 1;
     float4 kk[VEC], vv[VEC], kn[VEC], vn[VEC];
     {
         const int64_t jf = j0 + warp * 4 + grp;
@@ -568,7 +567,9 @@ static int32_t attention_impl(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf*
     int32_t rc = use_dev(ctx, q->dev);
     if (rc != RSTQ_OK) return rc;
     const bool fast = head_dim == 64 || head_dim == 128;
-    const int64_t fg = group >= kFastGroup ? kFastGroup : (group >= 2 ? 2 : 1);   // heads per CTA of the fast kernel
+    // heads per CTA of the fast kernel: at most two of 128 (four would leave no registers for the rows
+    // fetched ahead: 23.2 against 16.2 us at 32 q / 8 kv x 4096 although K / V then pass through L2 twice)
+    const int64_t fg = group >= kFastGroup && head_dim == 64 ? kFastGroup : (group >= 2 ? 2 : 1);
     const int64_t gs = fast ? fg : kAttnGroup;                         // query heads per CTA
     const int64_t gz = (group + gs - 1) / gs;
     RSTQ_REQUIRE(n_kv * gz <= kAttnCounters, RSTQ_E_LIMIT, "n_kv x ceil(group / %d) = %lld exceeds %d", (int)gs,
@@ -625,8 +626,7 @@ static int32_t attention_impl(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf*
                           : launch_attn(gqa_decode_fast_kernel<2, 4>, grid, block, smem, ds, p);
         else
             e = fg == 1 ? launch_attn(gqa_decode_fast_kernel<4, 1>, grid, block, smem, ds, p)
-                : fg == 2 ? launch_attn(gqa_decode_fast_kernel<4, 2>, grid, block, smem, ds, p)
-                          : launch_attn(gqa_decode_fast_kernel<4, 4>, grid, block, smem, ds, p);
+                        : launch_attn(gqa_decode_fast_kernel<4, 2>, grid, block, smem, ds, p);
         RSTQ_CUDA(e);
     } else {
         const size_t smem = (size_t)(kAttnWarps * gc * row * 4);
