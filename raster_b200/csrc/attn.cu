@@ -320,9 +320,9 @@ gqa_decode_kernel(const AttnParams p) {
 // head_dim = 32 * VEC (64, 128): eight lanes share a cache position, so a warp works on four
 // positions at once and a dot needs three shuffles; a lane owns float4 columns sub, sub + 8, ... of
 // the head.  Query heads (pre-scaled) sit in shared memory; a CTA serves up to kFastGroup of them.
-// GC = query heads a CTA serves at most (1, 2 or 4): the accumulators of unused heads would only cost
-// registers, and with one head per CTA three CTAs fit an SM instead of two.
-constexpr int kFastGroup = 4;
+// GC = query heads a CTA serves at most (1 or 2): the accumulators of unused heads would only cost
+// registers, and with one head per CTA four CTAs fit an SM instead of two.
+constexpr int kFastGroup = 2;
 template <int VEC, int GC>
 __global__ void __launch_bounds__(kAttnWarps * 32, GC == 1 ? 4 : 2)
 gqa_decode_fast_kernel(const AttnParams p) {
@@ -567,9 +567,10 @@ static int32_t attention_impl(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf*
     int32_t rc = use_dev(ctx, q->dev);
     if (rc != RSTQ_OK) return rc;
     const bool fast = head_dim == 64 || head_dim == 128;
-    // heads per CTA of the fast kernel: at most two of 128 (four would leave no registers for the rows
-    // fetched ahead: 23.2 against 16.2 us at 32 q / 8 kv x 4096 although K / V then pass through L2 twice)
-    const int64_t fg = group >= kFastGroup && head_dim == 64 ? kFastGroup : (group >= 2 ? 2 : 1);
+    // heads per CTA of the fast kernel: two (one when the group is one).  Four leave no registers for the
+    // rows fetched ahead at head_dim 128 (23.2 against 16.2 us at 32 q / 8 kv x 4096, although K / V then pass
+    // through L2 twice) and lose at head_dim 64 too (14.8 against 13.3 us).
+    const int64_t fg = group >= 2 ? 2 : 1;
     const int64_t gs = fast ? fg : kAttnGroup;                         // query heads per CTA
     const int64_t gz = (group + gs - 1) / gs;
     RSTQ_REQUIRE(n_kv * gz <= kAttnCounters, RSTQ_E_LIMIT, "n_kv x ceil(group / %d) = %lld exceeds %d", (int)gs,
@@ -622,8 +623,7 @@ static int32_t attention_impl(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf*
         cudaError_t e;
         if (head_dim == 64)
             e = fg == 1 ? launch_attn(gqa_decode_fast_kernel<2, 1>, grid, block, smem, ds, p)
-                : fg == 2 ? launch_attn(gqa_decode_fast_kernel<2, 2>, grid, block, smem, ds, p)
-                          : launch_attn(gqa_decode_fast_kernel<2, 4>, grid, block, smem, ds, p);
+                        : launch_attn(gqa_decode_fast_kernel<2, 2>, grid, block, smem, ds, p);
         else
             e = fg == 1 ? launch_attn(gqa_decode_fast_kernel<4, 1>, grid, block, smem, ds, p)
                         : launch_attn(gqa_decode_fast_kernel<4, 2>, grid, block, smem, ds, p);
