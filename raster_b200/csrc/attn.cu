@@ -7,9 +7,10 @@
 // The position / cache length is a host scalar or, when a one-element int64 device buffer is given,
 // read inside the kernel (the reference's -buf variants), so a captured graph serves every token.
 //
-// Attention is one kernel where the reference has three phases: a CTA owns one KV head and a slice
-// of the cache positions and serves every query head of the group from the K / V rows it reads
-// once (the reference reads them once per query head); warps walk the positions with an online
+// Attention is one kernel where the reference has three phases: a CTA owns one KV head, a slice of
+// the cache positions and up to two query heads of the group (eight in the general kernel), which
+// it serves from the K / V rows it reads once; the group's other heads find the rows in L2 (the
+// reference reads them once per query head); warps walk the positions with an online
 // softmax (running max, sum and weighted V in registers), the warps of a CTA are merged through
 // shared memory and the slices through a small scratch in device memory, where the last CTA to
 // arrive for a KV head writes out = sum_j p_j v_j.  The reference's score scratch `sc` is not used.
