@@ -1,4 +1,4 @@
-"""Regenerates tests/golden/qmatmul_small.npz from the CPU oracle.
+"""Regenerates tests/golden/qmatmul_small.npz and tests/golden/kquant_small.npz from the CPU oracle.
 
 The reference cannot run on this machine (no JVM), so these vectors come from
 the oracle *after* it has been pinned to the reference's own tests
@@ -45,7 +45,34 @@ def make():
     return g
 
 
+def make_k():
+    """K-quant vectors (kquant_small.npz): Q4_K / Q6_K codecs, q8_K activations, both GEMVs."""
+    g = {}
+    out, in_, m = 24, 512, 2
+    w = synth.normal(111, out * in_, 0.02) + np.float32(0.005)
+    x = synth.normal(112, m * in_)
+    g["w"], g["x"], g["shape"] = w, x, np.array([out, in_, m])
+    e4, e6 = orc.quantize_weight_q4k(w), orc.quantize_weight_q6k(w)
+    for k, v in e4.items():
+        g[f"q4k_{k}"] = v
+    for k, v in e6.items():
+        g[f"q6k_{k}"] = v
+    g["q4k_dequant"], g["q6k_dequant"] = orc.dequant_q4k(e4), orc.dequant_q6k(e6)
+    y4, y4d, y6, y6d = [], [], [], []
+    for r in range(m):
+        xq, xs, b32 = orc.quantize_act_q8k(x[r * in_:(r + 1) * in_], in_, 32)
+        _, _, b16 = orc.quantize_act_q8k(x[r * in_:(r + 1) * in_], in_, 16)
+        g[f"xq_{r}"], g[f"xs_{r}"], g[f"bsums32_{r}"], g[f"bsums16_{r}"] = xq, xs, b32, b16
+        a, ad = orc.qmatmul_q4k(xq, xs, b32, e4, in_, out)
+        b, bd = orc.qmatmul_q6k(xq, xs, b16, e6, in_, out)
+        y4.append(a), y4d.append(ad), y6.append(b), y6d.append(bd)
+    g["y_q4k"], g["y_q4k_f64"] = np.stack(y4), np.stack(y4d)
+    g["y_q6k"], g["y_q6k_f64"] = np.stack(y6), np.stack(y6d)
+    return g
+
+
 if __name__ == "__main__":
-    path = os.path.join(HERE, "qmatmul_small.npz")
-    np.savez_compressed(path, **make())
-    print(path, os.path.getsize(path), "bytes")
+    for name, fn in (("qmatmul_small.npz", make), ("kquant_small.npz", make_k)):
+        path = os.path.join(HERE, name)
+        np.savez_compressed(path, **fn())
+        print(path, os.path.getsize(path), "bytes")

@@ -7,6 +7,7 @@ from oracle import oracle as orc
 from raster_b200.quant import cpu_quant as cq, pack, train
 
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "qmatmul_small.npz"))
+GK = np.load(os.path.join(os.path.dirname(__file__), "golden", "kquant_small.npz"))
 
 
 def test_oracle_reproduces_golden():
@@ -15,10 +16,10 @@ def test_oracle_reproduces_golden():
         "make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
-    fresh = mod.make()
-    assert set(fresh) == set(G.files)
-    for k in G.files:
-        assert np.array_equal(fresh[k], G[k]), k
+    for fresh, gold in ((mod.make(), G), (mod.make_k(), GK)):
+        assert set(fresh) == set(gold.files)
+        for k in gold.files:
+            assert np.array_equal(fresh[k], gold[k]), k
 
 
 def test_host_codecs_reproduce_golden():
@@ -37,3 +38,13 @@ def test_host_codecs_reproduce_golden():
     assert np.array_equal(p["wp"], G["wp"])
     assert np.array_equal(train.dequant_q8_dense(t["codes"], t["scales"], in_, out),
                           orc.dequant_q8_dense(G["codes"], G["scales"], in_, out))
+
+
+def test_k_quant_host_codecs_reproduce_golden():
+    a4, a6 = cq.quantize_weight_q4k(GK["w"]), cq.quantize_weight_q6k(GK["w"])
+    for k in ("wq", "da", "db", "aq", "bq"):
+        assert np.array_equal(np.asarray(a4[k]).view(np.uint8), GK[f"q4k_{k}"].view(np.uint8)), k
+    for k in ("wq", "sc", "ds"):
+        assert np.array_equal(np.asarray(a6[k]).view(np.uint8), GK[f"q6k_{k}"].view(np.uint8)), k
+    assert np.array_equal(cq.dequant_q4k(a4), GK["q4k_dequant"])
+    assert np.array_equal(cq.dequant_q6k(a6), GK["q6k_dequant"])

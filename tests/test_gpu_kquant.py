@@ -175,3 +175,33 @@ def test_q6k_reference_case_and_registry(ctx):
     assert not np.array_equal(y, y4)                    # core_test.clj:39-46: different code paths
     assert {"q4_0", "q8_0", "q4_K", "q6_K"} <= set(qcore.registered_formats())
     qm.data["bound"].free()
+
+
+def test_operators_reproduce_k_quant_golden_vectors(ctx):
+    """The committed K-quant vectors (tests/golden/kquant_small.npz): quantizer bit for bit, both
+    operators within 1e-5 of the unrounded sums."""
+    import os
+    G = np.load(os.path.join(os.path.dirname(__file__), "golden", "kquant_small.npz"))
+    out, in_, m = (int(v) for v in G["shape"])
+    x = G["x"]
+    bx = ctx.array_to_buffer(x)
+    for sub in (32, 16):
+        bq, bs, bb = (ctx.make_buffer(m * in_, np.int8), ctx.make_buffer(m * in_ // 256, np.float32),
+                      ctx.make_buffer(m * in_ // sub, np.int32))
+        ctx.quant_act_q8k(bx, bq, bs, bb, m, in_, sub)
+        ctx.sync()
+        for r in range(m):
+            assert np.array_equal(bq.download()[r * in_:(r + 1) * in_], G[f"xq_{r}"])
+            assert np.array_equal(bs.download()[r * (in_ // 256):(r + 1) * (in_ // 256)], G[f"xs_{r}"])
+            assert np.array_equal(bb.download()[r * (in_ // sub):(r + 1) * (in_ // sub)], G[f"bsums{sub}_{r}"])
+        for o in (bq, bs, bb):
+            o.free()
+    w4 = ctx.bind_weight_q4k({k: G[f"q4k_{k}"] for k in ("wq", "da", "db", "aq", "bq")}, out, in_)
+    w6 = ctx.bind_weight_q6k({k: G[f"q6k_{k}"] for k in ("wq", "sc", "ds")}, out, in_)
+    by = ctx.make_buffer(m * out, np.float32)
+    for w, key in ((w4, "y_q4k_f64"), (w6, "y_q6k_f64")):
+        ctx.qmatmul(w, bx, by, m, L.F32, L.F32, L.MODE_A8)
+        ctx.sync()
+        assert relerr(by.download(), G[key]) <= 1e-5
+    for o in (w4, w6, bx, by):
+        o.free()
