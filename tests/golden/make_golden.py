@@ -1,4 +1,4 @@
-"""Regenerates tests/golden/qmatmul_small.npz and tests/golden/kquant_small.npz from the CPU oracle.
+"""Regenerates tests/golden/qmatmul_small.npz, kquant_small.npz and chain_small.npz from the CPU oracle.
 
 The reference cannot run on this machine (no JVM), so these vectors come from
 the oracle *after* it has been pinned to the reference's own tests
@@ -71,8 +71,28 @@ def make_k():
     return g
 
 
+def make_chain():
+    """Decode-chain neighbours (chain_small.npz): rms-norm, gated activations, rope, cache append, attention."""
+    import math
+    g = {}
+    rows, feat = 2, 96
+    x, w = synth.normal(121, rows * feat), synth.normal(122, feat, 0.1) + np.float32(1.0)
+    g["x"], g["gain"] = x, w
+    g["rms_norm"] = orc.rms_norm(x, w, rows, feat, 1e-6, 0.0)
+    g["rms_norm_gemma"] = orc.rms_norm(x, w, rows, feat, 1e-6, 1.0)
+    a, b = synth.normal(123, 200) * np.float32(3.0), synth.normal(124, 200)
+    g["a"], g["b"] = a, b
+    g["silu_mul"], g["gelu_mul"], g["residual_add"] = orc.silu_mul(a, b), orc.gelu_mul(a, b), orc.residual_add(a, b)
+    n_q, n_kv, hd, clen, pos = 4, 2, 16, 9, 8
+    q, k, v = synth.normal(125, n_q * hd), synth.normal(126, clen * n_kv * hd), synth.normal(127, clen * n_kv * hd)
+    g["q"], g["k"], g["v"], g["attn_shape"] = q, k, v, np.array([n_q, n_kv, hd, clen, pos])
+    g["rope_q"] = orc.rope_pos(q, n_q, hd, 10000.0, pos)
+    g["attention"] = orc.gqa_decode_attention(g["rope_q"], k, v, clen, n_q, n_q // n_kv, n_kv, hd, 1.0 / math.sqrt(hd))
+    return g
+
+
 if __name__ == "__main__":
-    for name, fn in (("qmatmul_small.npz", make), ("kquant_small.npz", make_k)):
+    for name, fn in (("qmatmul_small.npz", make), ("kquant_small.npz", make_k), ("chain_small.npz", make_chain)):
         path = os.path.join(HERE, name)
         np.savez_compressed(path, **fn())
         print(path, os.path.getsize(path), "bytes")
