@@ -94,6 +94,13 @@ typedef struct rstq_event rstq_event;
 #define RSTQ_TUNE_GEMV_PLAN 4     /* decode kernel work split: 0 (default) = choose per shape, 1 = equal
                                      unit ranges (32-row groups may be shared by neighbouring thread
                                      blocks), 2 = whole 32-row groups per thread block */
+#define RSTQ_TUNE_GEMV_PREFETCH 7  /* decode kernels: KB of a thread block's weight range requested into L2
+                                     ahead of its shared-memory ring (0 = none) */
+#define RSTQ_TUNE_PROBE 8         /* timing probes of the decode kernel, RESULTS ARE INVALID while set: 1 = the
+                                     weight stream is not copied (consumer rate alone), 2 = the arithmetic is
+                                     skipped (copy rate alone); 0 (default) = off */
+#define RSTQ_TUNE_FUSE_QUANT 6    /* 1 (default) = rstq_qmatmul in MODE_A8 at M = 1 quantizes the
+                                     activations inside the decode kernel; 0 = separate quantizer launch */
 
 /* ---- library / errors -------------------------------------------------- */
 RSTQ_API int32_t rstq_version(void);

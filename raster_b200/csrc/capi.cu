@@ -49,14 +49,25 @@ int32_t dev_reserve(DeviceState& ds, void** p, int64_t* have, int64_t need) {
                  "scratch must grow (%lld bytes) during graph capture; run the call once before "
                  "capturing", (long long)need);
     if (*p) {
-        RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
-        RSTQ_CUDA(cudaFree(*p));
+        int32_t rc = dev_release_scratch(ds, *p);
+        if (rc != RSTQ_OK) return rc;
         *p = nullptr;
         *have = 0;
     }
     need = (need + 0xFFFFF) & ~0xFFFFFll;
     RSTQ_CUDA(cudaMalloc(p, (size_t)need));
     *have = need;
+    return RSTQ_OK;
+}
+
+int32_t dev_release_scratch(DeviceState& ds, void* p) {
+    if (!p) return RSTQ_OK;
+    if (ds.live_graphs > 0) {   // a recorded launch may still name this block
+        ds.retired.push_back(p);
+        return RSTQ_OK;
+    }
+    RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
+    RSTQ_CUDA(cudaFree(p));
     return RSTQ_OK;
 }
 
@@ -207,6 +218,12 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
     if (mode == RSTQ_MODE_A8) {
         RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "unknown activation type");
         RSTQ_REQUIRE(out_dtype == RSTQ_F32 || tc, RSTQ_E_INVALID, "MODE_A8 decode writes f32");
+        if (M == 1 && !tc && ds.fuse_quant && w->in <= kFusedQuantMaxIn) {
+            // one token: every CTA of the decode kernel quantizes x (16 - 112 KB, in L2) while it
+            // stages it, bit for bit as the quantizer kernel would -- one launch, no scratch
+            GemvA8Args a{w->data, nullptr, nullptr, nullptr, (float*)y, 1, w->in, w->out, w->bits, w->zp, tp, x, act_dtype};
+            return launch_gemv_a8(ctx, ds, a);
+        }
         ActScratch s;
         int32_t rc = act_scratch(ds, M, w->in, &s);
         if (rc != RSTQ_OK) return rc;
@@ -436,6 +453,8 @@ int32_t rstq_shutdown(rstq_ctx* ctx) {
         if (ds.ordinal < 0) continue;
         cudaSetDevice(ds.ordinal);
         if (ds.stream) cudaStreamSynchronize(ds.stream);
+        for (void* r : ds.retired) cudaFree(r);
+        ds.retired.clear();
         if (ds.act_scratch) cudaFree(ds.act_scratch);
         if (ds.gemm_scratch) cudaFree(ds.gemm_scratch);
         if (ds.attn_scratch) cudaFree(ds.attn_scratch);
@@ -467,6 +486,8 @@ int32_t rstq_sync(rstq_ctx* ctx, int32_t dev) {
     if (st != 0) {
         // the flag is sticky until read: clear it so the context stays usable
         RSTQ_CUDA(cudaMemsetAsync(ds.status, 0, 4, ds.stream));
+        // a launch that gave up may have left hand-over flags set: the next launch must not take them
+        RSTQ_CUDA(cudaMemsetAsync(ds.counters, 0, (size_t)ds.counters_len * 4, ds.stream));
         RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
         set_error("a time-bounded wait inside a kernel ran out (status %d); results since the "
                   "last rstq_sync are invalid", st);
@@ -491,6 +512,17 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
         case RSTQ_TUNE_GEMV_PLAN:
             RSTQ_REQUIRE(value >= 0 && value <= 2, RSTQ_E_INVALID, "decode plan selector 0..2");
             for (auto& ds : ctx->devs) ds.gemv_plan = (int)value;
+            return RSTQ_OK;
+        case RSTQ_TUNE_GEMV_PREFETCH:
+            RSTQ_REQUIRE(value >= 0 && value <= (1 << 20), RSTQ_E_INVALID, "prefetch distance 0..2^20 KB");
+            for (auto& ds : ctx->devs) ds.gemv_prefetch_kb = value;
+            return RSTQ_OK;
+        case RSTQ_TUNE_PROBE:
+            RSTQ_REQUIRE(value >= 0 && value <= 3, RSTQ_E_INVALID, "probe selector 0..3");
+            for (auto& ds : ctx->devs) ds.gemv_probe = (int)value;
+            return RSTQ_OK;
+        case RSTQ_TUNE_FUSE_QUANT:
+            for (auto& ds : ctx->devs) ds.fuse_quant = value != 0;
             return RSTQ_OK;
         case RSTQ_TUNE_GEMM_MIN_M:
             RSTQ_REQUIRE(value >= 1, RSTQ_E_INVALID, "threshold must be >= 1");
@@ -1198,6 +1230,7 @@ int32_t rstq_graph_end(rstq_ctx* ctx, rstq_graph** graph, int32_t dev) {
         set_error("out of host memory");
         return RSTQ_E_OOM;
     }
+    ds.live_graphs++;
     *graph = gr;
     return RSTQ_OK;
 }
@@ -1220,6 +1253,11 @@ int32_t rstq_graph_destroy(rstq_graph* graph) {
     cudaStreamSynchronize(ds.stream);
     cudaGraphExecDestroy(graph->exec);
     cudaGraphDestroy(graph->graph);
+    if (--ds.live_graphs <= 0) {   // nothing recorded names the outgrown scratch any more
+        ds.live_graphs = 0;
+        for (void* r : ds.retired) cudaFree(r);
+        ds.retired.clear();
+    }
     cudaGetLastError();
     graph->magic = 0;
     delete graph;

@@ -23,11 +23,13 @@
 //    the int8 tile, so the fold is one FADD + one FMUL + one FFMA per value.
 //  * Chunks never straddle a 32-row group, so all consumer warps reach a group
 //    boundary together: they reduce across warps and store y directly when the
-//    CTA covered the whole K range of the group; otherwise (at most the first
-//    and the last group of a CTA) the partial goes to scratch and the last CTA
-//    to arrive for that group adds the partials in CTA order.  Nothing spins on
-//    another CTA; every mbarrier wait is time-bounded and reports through a
-//    status word instead of hanging.
+//    CTA covered the whole K range of the group; otherwise the group is cut
+//    between neighbouring CTAs: the one holding its head finishes it (its last
+//    segment), the ones behind hand their partial sums over as soon as their
+//    first segment is done (see hand_over in the kernel).  All CTAs of a launch
+//    are resident together (one per SM, G <= #SM); every wait -- mbarrier or
+//    hand-over flag -- is time-bounded and reports through a status word
+//    instead of hanging.
 #include "internal.h"
 #include "mma_helpers.cuh"
 #include "sync_helpers.cuh"
@@ -41,6 +43,11 @@ constexpr int kStreamThreads = kConsumers + 32;  // + producer warp
 __host__ __device__ constexpr int upw_of(int bits) { return bits == 4 ? 4 : 2; }
 __host__ __device__ constexpr int chunk_units_of(int bits) { return upw_of(bits) * kCW; }
 constexpr int kMaxDynSmem = 232448 - 1024;       // 227 KB opt-in limit less the static part
+// the in-kernel quantizer holds all of a thread's activations in registers: in <= 3 * 512 * 8
+constexpr int kQuantPasses = 3;
+constexpr int kQuantMaxIn = kQuantPasses * kConsumers * 8;
+static_assert(kGemvMaxM * 32 <= kConsumers, "one output per consumer thread in the hand-over");
+static_assert(kQuantMaxIn == kFusedQuantMaxIn, "the host routes by kFusedQuantMaxIn");
 constexpr int kMagicInt = 0x4B400000;            // bits of 12582912.0f = 2^23 + 2^22
 constexpr float kMagicFlt = 12582912.0f;
 
@@ -53,14 +60,16 @@ struct StreamParams {
     const int32_t* xsum;
     const void* x;        // F
     void* y;
-    float* partials;      // [G][2][M*32]
-    int* counters;        // [groups], zero between launches
+    float* partials;      // [G][M*32]: slot c = what CTA c hands over (the partial sums of its first segment)
+    int* flags;           // [G]: 1 while slot c holds a partial nobody has taken yet; zero between launches
     int* status;          // device status word (0 = ok)
     unsigned long long* dbg;  // optional per-CTA phase timestamps (8 per CTA), or null
     int64_t in, out;
     int64_t uq, ur;       // units per CTA: CTA c owns uq (+1 if c < ur) units
     int64_t U;            // all units (the last CTA's range is clipped to it)
     int M, nb, G, zp, NS, T, act_dtype, out_dtype;
+    int64_t pf_ahead;     // bytes of the CTA's range requested into L2 ahead of the ring (0: none)
+    int probe;            // timing probes (results invalid): 1 = the producer signals without copying, 2 = the consumers skip the arithmetic
     uint32_t act_off, act2_off, red_off, bar_off;  // byte offsets into dynamic smem (ring at 0)
     TpFuse tp;            // tp.nranks == 0: no exchange, results go to y
 };
@@ -180,6 +189,99 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
         for (int j = 0; j < U; ++j) {
             const int o = o0 + j * kConsumers;
             if (o < tot2) sxz[o] = v[j];
+        }
+    }
+}
+
+// A8, M == 1, the activation quantizer inside the staging pass (quantize-act-blocks!,
+// src/raster/compiler/backend/cpu/quant.clj:282-305): per 32-element block d = max|x| / 127 in double,
+// id = 1 / d, q = clamp(round_half_up((double)x * id), -127, 127), xs = (float)d, xsum = sum q.
+// Thread (b, tig) holds the eight elements its record needs; the four threads of a block are
+// neighbouring lanes (two shuffles for the maximum, two for the sum).  The codes come from f32
+// arithmetic whenever that provably gives the double result: t = x * fl32(127 / max) is within
+// 127 * 2^-22 of the double product, so a t further than 1e-3 from every k + 0.5 rounds the same way;
+// anything closer, and blocks whose maximum is zero, tiny, huge or not finite, take the double path.
+// xs: fl32(max / 127) equals (float)((double)max / 127.0) for every f32 max -- the quotient of a
+// 24-bit integer by 127 cannot sit on a 25-bit midpoint, so rounding through double changes nothing.
+__device__ __forceinline__ int quant_exact(float x, double id) {
+    const double v = (double)x * id, f = floor(v);
+    const int q = (int)f + ((v - f) >= 0.5 ? 1 : 0);
+    return max(-127, min(127, q));
+}
+template <int BITS>
+__device__ __forceinline__ void stage_a8_quant(const StreamParams& p, uint8_t* smem, int tid) {
+    uint4* srec = reinterpret_cast<uint4*>(smem + p.act_off);
+    const int items = p.nb * 4;   // a multiple of 4: the lanes of a block are active together
+    const bool bf = p.act_dtype == RSTQ_BF16;
+    // every load of the thread is issued before the first use (one trip to L2, not one per pass):
+    // kQuantPasses passes of kConsumers items cover in <= kQuantMaxIn
+    uint4 raw[kQuantPasses][2];
+#pragma unroll
+    for (int it = 0; it < kQuantPasses; ++it) {
+        const int i = it * kConsumers + tid;
+        raw[it][0] = raw[it][1] = make_uint4(0, 0, 0, 0);
+        if (i < items) {
+            const int b = i >> 2, tg = i & 3;
+            if (bf) {
+                const uint16_t* xb = reinterpret_cast<const uint16_t*>(p.x) + b * 32 + tg * 4;
+                const uint2 lo = *reinterpret_cast<const uint2*>(xb), hi = *reinterpret_cast<const uint2*>(xb + 16);
+                raw[it][0] = make_uint4(lo.x << 16, lo.x & 0xFFFF0000u, lo.y << 16, lo.y & 0xFFFF0000u);
+                raw[it][1] = make_uint4(hi.x << 16, hi.x & 0xFFFF0000u, hi.y << 16, hi.y & 0xFFFF0000u);
+            } else {
+                const uint4* xf = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.x) + b * 32 + tg * 4);
+                raw[it][0] = xf[0];
+                raw[it][1] = xf[4];
+            }
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < kQuantPasses; ++it) {
+        const int i = it * kConsumers + tid;
+        if (it * kConsumers + (tid & ~31) >= items) break;   // warp-uniform: the shuffles below need whole warps
+        const bool act = i < items;
+        const float f[8] = {__uint_as_float(raw[it][0].x), __uint_as_float(raw[it][0].y), __uint_as_float(raw[it][0].z),
+                            __uint_as_float(raw[it][0].w), __uint_as_float(raw[it][1].x), __uint_as_float(raw[it][1].y),
+                            __uint_as_float(raw[it][1].z), __uint_as_float(raw[it][1].w)};
+        float mx = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mx = fmaxf(mx, fabsf(f[k]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        int q[8];
+        float xs = 0.f;
+        bool exact = !(mx >= 1e-30f && mx <= 1e37f);
+        if (!exact) {
+            const float idf = __fdiv_rn(127.f, mx);
+            xs = __fdiv_rn(mx, 127.f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float t = f[k] * idf, fl = floorf(t);
+                exact = exact || fabsf(t - fl - 0.5f) < 1e-3f;
+                q[k] = (int)floorf(t + 0.5f);
+            }
+        }
+        if (exact) {
+            const double d = (double)mx / 127.0;
+            const double id = d == 0.0 ? 0.0 : 1.0 / d;
+            xs = (float)d;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) q[k] = quant_exact(f[k], id);
+        }
+        int sum = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sum += q[k];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (act) {
+            const bool hi = BITS == 4 && (i & 1);
+            uint4 r;
+            r.x = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) |
+                  ((uint32_t)(q[3] & 0xFF) << 24);
+            r.y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) |
+                  ((uint32_t)(q[7] & 0xFF) << 24);
+            r.z = __float_as_uint(hi ? xs * 0.0625f : xs);
+            r.w = (uint32_t)(kMagicInt - (p.zp * sum) * (hi ? 16 : 1));
+            srec[i] = r;
         }
     }
 }
@@ -398,7 +500,8 @@ __device__ __forceinline__ float stream_reduce_rc(const float* red, int row, int
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-template <int BITS, int NT, int MODE, bool ONECOL, bool TP>
+// QF: M == 1 only, the kernel quantizes the raw activations p.x itself while staging.
+template <int BITS, int NT, int MODE, bool ONECOL, bool TP, bool QF = false>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
     constexpr int UNIT = BITS == 4 ? kUnitBytesQ4 : kUnitBytesQ8;
     constexpr int kUPW = upw_of(BITS), kChunkUnits = chunk_units_of(BITS);
@@ -406,7 +509,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     constexpr int NV = NT * 8;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_abort;
-    __shared__ int s_last[2], s_cf[2], s_cn[2], s_slot0[2];
+    __shared__ int s_cn;
     __shared__ long long s_g0;
     __shared__ int s_bstart, s_total;
     __shared__ int s_tp_ok;
@@ -414,7 +517,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const int gid = lane >> 2, tig = lane & 3;
     const int NS = p.NS, nb = p.nb;
     unsigned long long* dbg = p.dbg ? p.dbg + (size_t)blockIdx.x * 8 : nullptr;
-    if (dbg && tid == 0) dbg[0] = gtime_ns();
+    if (dbg && tid == 0) {
+        dbg[0] = gtime_ns();
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        dbg[6] = smid;
+    }
     const uint32_t full0 = smem_u32(smem + p.bar_off), empty0 = full0 + NS * 8;
     if (tid < NS) mbar_init(full0 + 8 * tid, 1);
     else if (tid < 2 * NS) mbar_init(empty0 + 8 * (tid - NS), kCW);
@@ -448,14 +556,33 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             int b = b_start, left = total, s = 0, issued = 0;
             uint32_t ph = 0;
             bool ok = true;
+            // HBM requests beyond what the ring holds: the range is requested into L2 up to `pf_ahead`
+            // bytes ahead of the copy position, so the bytes in flight from HBM are not bounded by
+            // shared memory and the ring only has to cover the L2 round trip.
+            const uint8_t* const end = src + (int64_t)total * UNIT;
+            const uint8_t* pf = src;
+            const int64_t pf_ahead = p.pf_ahead;
             while (left > 0) {
+                if (pf_ahead > 0) {
+                    const uint8_t* lim = src + pf_ahead < end ? src + pf_ahead : end;
+                    while (pf < lim) {
+                        const int64_t rest = end - pf;
+                        const uint32_t nbytes = (uint32_t)(rest < 32768 ? rest : 32768);
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf), "r"(nbytes) : "memory");
+                        pf += nbytes;
+                    }
+                }
                 int n = nb - b < left ? nb - b : left;
                 n = n < kChunkUnits ? n : kChunkUnits;
                 ok = mbar_try(empty0 + 8 * s, ph ^ 1u) || mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
                 const uint32_t bytes = (uint32_t)(n * UNIT);
-                mbar_expect_tx(full0 + 8 * s, bytes);
-                bulk_copy_g2s_hint(smem_u32(smem) + (uint32_t)s * CHUNK_BYTES, src, bytes, full0 + 8 * s, pol);
+                if (p.probe & 1) {
+                    mbar_arrive(full0 + 8 * s);
+                } else {
+                    mbar_expect_tx(full0 + 8 * s, bytes);
+                    bulk_copy_g2s_hint(smem_u32(smem) + (uint32_t)s * CHUNK_BYTES, src, bytes, full0 + 8 * s, pol);
+                }
                 src += bytes;
                 b += n;
                 if (b == nb) b = 0;
@@ -510,7 +637,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                                  : "memory");
         }
     };
-    if (MODE == MODE_A8) stage_a8<ONECOL, BITS>(p, smem, tid);
+    if (QF) stage_a8_quant<BITS>(p, smem, tid);
+    else if (MODE == MODE_A8) stage_a8<ONECOL, BITS>(p, smem, tid);
     else stage_f(p, smem, tid);
     consumer_bar();
     if (dbg && tid == 0) dbg[2] = gtime_ns();
@@ -518,8 +646,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     float acc[NT][4][2];
     float* red = reinterpret_cast<float*>(smem + p.red_off);
     const int M = p.M, T = p.T;
-    int64_t part_g[2] = {0, 0};
-    int npart = 0;
 
     auto zero_acc = [&]() {
 #pragma unroll
@@ -527,13 +653,58 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[nt][i][0] = acc[nt][i][1] = 0.f;
     };
-    // Cross-warp reduction of the segment [b_from, b_to) of group g, then store.  Two
+    // A group whose K range is cut between CTAs (the equal-range split) is finished by the CTA that
+    // holds its head, for which it is the LAST segment; every CTA behind it holds a later part as its
+    // FIRST segment (or only one) and hands the partial sums over through its slot as soon as that
+    // segment is done -- early in its loop, so the finisher normally finds them waiting and the
+    // hand-over costs one read from L2 at the end instead of a chain of dependent trips.  Sums are
+    // added in CTA order.  The wait for a slot is time-bounded; the finisher clears the flags it took.
+    auto hand_over = [&](int64_t g, float sum, int64_t o, bool owner) {
+        // called by all consumer threads; `owner` threads hold `sum` for output index o of group g
+        const int c = blockIdx.x;
+        if (tid == 0) {
+            const int cl = cta_of_unit((g + 1) * nb - 1, p.uq, p.ur);
+            int cn = cl - c;
+            const unsigned long long t0 = gtime_ns();
+            for (int k = 1; k <= cn; ++k) {
+                const volatile int* f = p.flags + c + k;
+                uint32_t spins = 0;
+                while (*f == 0) {
+                    if ((++spins & 255u) == 0 && (*abort_flag || gtime_ns() - t0 > kWaitLimitNs)) {
+                        *abort_flag = 1;   // a contributor never delivered: report, do not hang
+                        cn = 0;
+                        break;
+                    }
+                }
+            }
+            __threadfence();
+            s_cn = cn;
+        }
+        consumer_bar();
+        const int cn = s_cn;
+        if (owner && cn > 0) {
+            const int64_t row = o & 31, m = o >> 5;
+            for (int k = 1; k <= cn; ++k) sum += __ldcg(p.partials + (int64_t)(c + k) * M * 32 + o);
+            if (g * 32 + row < p.out) emit(m * p.out + g * 32 + row, sum);
+        }
+        consumer_bar();   // every slot has been read
+        if (tid == 0)
+            for (int k = 1; k <= cn; ++k) p.flags[c + k] = 0;
+    };
+    auto publish = [&]() {   // after every partial store of this CTA's slot
+        consumer_bar();
+        if (tid == 0) {
+            __threadfence();
+            *reinterpret_cast<volatile int*>(p.flags + blockIdx.x) = 1;
+        }
+    };
+    // Cross-warp reduction of the segment [b_from, b_to) of group g, then store / hand over.  Two
     // reduction buffers alternate, so one barrier per flush is enough.
     int flush_no = 0;
     auto flush = [&](int64_t g, int b_from, int b_to) {
-        const bool whole = (b_from == 0) && (b_to == nb);
+        const bool head = b_from == 0, whole = head && (b_to == nb);
         const int64_t row0 = g * 32;
-        float* part = p.partials + ((int64_t)blockIdx.x * 2 + (g == g0 ? 0 : 1)) * M * 32;
+        float* part = p.partials + (int64_t)blockIdx.x * M * 32;
         float* rbuf = red + (flush_no & 1) * (ONECOL ? kCW * 32 : kCW * NV * 32);
         ++flush_no;
         if (ONECOL) {
@@ -544,9 +715,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             float sum = rbuf[(tid & 15) * 32 + (row & 7) * 4 + (row >> 3)];
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if ((tid & 15) == 0) {
-                if (!whole) part[row] = sum;
-                else if (row0 + row < p.out) emit(row0 + row, sum);
+            const bool owner = (tid & 15) == 0;
+            if (whole) {
+                if (owner && row0 + row < p.out) emit(row0 + row, sum);
+            } else if (!head) {
+                if (owner) part[row] = sum;
+                publish();
+            } else {
+                hand_over(g, sum, row, owner);
             }
         } else {
 #pragma unroll
@@ -557,16 +733,21 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     for (int c = 0; c < 2; ++c)
                         rbuf[(warp * NV + (nt * 4 + i) * 2 + c) * 32 + lane] = acc[nt][i][c];
             consumer_bar();
-            for (int o = tid; o < M * 32; o += kConsumers) {
-                const int m = o >> 5, row = o & 31;
-                float sum = 0.f;
+            const int o = tid;   // M <= 16: at most one output per consumer thread
+            const bool owner = o < M * 32;
+            const int m = o >> 5, row = o & 31;
+            float sum = 0.f;
+            if (owner)
                 for (int t = 0; t < T; ++t) sum += stream_reduce_rc<NT>(rbuf, row, m * T + t);
-                if (!whole) part[o] = sum;
-                else if (row0 + row < p.out)
-                    emit((int64_t)m * p.out + row0 + row, sum);
+            if (whole) {
+                if (owner && row0 + row < p.out) emit((int64_t)m * p.out + row0 + row, sum);
+            } else if (!head) {
+                if (owner) part[o] = sum;
+                publish();
+            } else {
+                hand_over(g, sum, o, owner);
             }
         }
-        if (!whole) part_g[npart++] = g;
     };
 
     {
@@ -588,7 +769,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             int n = nb - b < left ? nb - b : left;
             n = n < kChunkUnits ? n : kChunkUnits;
             if (alive && !mbar_try(full0 + 8 * s, ph)) alive = mbar_wait(full0 + 8 * s, ph, abort_flag);
-            if (alive) {
+            if (alive && !(p.probe & 2)) {
                 if (ONECOL) {
                     float v = acc[0][0][0];
                     if (n == kChunkUnits) {
@@ -639,44 +820,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     }
 
     if (dbg && tid == 0) dbg[4] = gtime_ns();
-    // Groups this CTA shares with its neighbours: count in (one fence, both counters at
-    // once); the last CTA to arrive adds the partials up in CTA order.  Thread 0 works out
-    // who shares the group and which of their two partial slots holds it.
-    if (npart > 0) {
-        consumer_bar();  // every partial store of this CTA is done
-        if (tid == 0) {
-            __threadfence();  // ... and ordered before the counter updates
-            int prev[2] = {0, 0};
-            for (int i = 0; i < npart; ++i) prev[i] = atomicAdd(&p.counters[part_g[i]], 1);
-            for (int i = 0; i < npart; ++i) {
-                const int64_t g = part_g[i];
-                const int cf = cta_of_unit(g * nb, p.uq, p.ur);
-                const int cl = cta_of_unit((g + 1) * nb - 1, p.uq, p.ur);
-                s_last[i] = (prev[i] == cl - cf);
-                s_cf[i] = cf;
-                s_cn[i] = cl - cf + 1;
-                // CTA cf holds the group as its last segment unless the group starts its range;
-                // every later sharer holds it as its first segment
-                s_slot0[i] = (range_begin(cf, p.uq, p.ur) >= g * nb) ? 0 : 1;
-            }
-        }
-        consumer_bar();
-        for (int i = 0; i < npart; ++i) {
-            if (!s_last[i]) continue;
-            const int64_t g = part_g[i];
-            const int cf = s_cf[i], cn = s_cn[i];
-            const int64_t row0 = g * 32;
-            for (int o = tid; o < M * 32; o += kConsumers) {
-                const int m = o >> 5, row = o & 31;
-                // partials are read from L2 (ld.cg): the writers fenced before counting in
-                float sum = __ldcg(p.partials + ((int64_t)cf * 2 + s_slot0[i]) * M * 32 + o);
-                for (int k = 1; k < cn; ++k)
-                    sum += __ldcg(p.partials + ((int64_t)(cf + k) * 2) * M * 32 + o);
-                if (row0 + row < p.out) emit((int64_t)m * p.out + row0 + row, sum);
-            }
-            if (tid == 0) p.counters[g] = 0;
-        }
-    }
     if (tid == 0 && s_abort) atomicExch(p.status, 1);
     if (dbg && tid == 0) dbg[5] = gtime_ns();
 
@@ -754,11 +897,12 @@ static bool whole_groups_pay(int64_t groups, int64_t nb, int64_t k, int64_t Gw, 
 }
 
 static StreamPlan plan_stream(const DeviceState& ds, int bits, int NT, int64_t groups, int64_t nb,
-                              int64_t act_bytes, int64_t act2_bytes) {
+                              int64_t act_bytes, int64_t act2_bytes, bool onecol = false) {
     StreamPlan pl{};
     const int kChunkUnits = chunk_units_of(bits);
     const int chunk = kChunkUnits * unit_bytes(bits);
-    const int64_t red = 2 * (int64_t)kCW * NT * 8 * 32 * 4;  // two alternating reduction buffers
+    // two alternating reduction buffers ([warp][lane] at M = 1, [warp][value][lane] otherwise)
+    const int64_t red = onecol ? 2 * (int64_t)kCW * 32 * 4 : 2 * (int64_t)kCW * NT * 8 * 32 * 4;
     const int64_t a1 = (act_bytes + 127) & ~127ll, a2 = (act2_bytes + 127) & ~127ll;
     const int64_t room = kMaxDynSmem - (a1 + a2 + red + 512);
     int64_t ns = room / chunk;
@@ -828,21 +972,29 @@ int32_t gemv_configure(DeviceState& ds) {
     CFG(8, 4, MODE_F, false, false);
     CFG(8, 4, MODE_F, false, true);
 #undef CFG
+    // the M = 1 kernel with the activation quantizer inside
+    if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, true, false, true>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, true, true, true>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<8, 1, MODE_A8, true, false, true>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<8, 1, MODE_A8, true, true, true>)) != RSTQ_OK) return rc;
     return RSTQ_OK;
 }
 
 static int32_t stream_scratch_ok(const DeviceState& ds, int64_t groups, int G, int64_t M) {
-    RSTQ_REQUIRE(groups <= ds.counters_len, RSTQ_E_LIMIT, "out = %lld rows exceeds the %lld-group limit",
-                 (long long)groups * 32, (long long)ds.counters_len);
-    RSTQ_REQUIRE((int64_t)G * 2 * M * 32 * 4 <= ds.partials_bytes, RSTQ_E_LIMIT, "partials scratch too small");
+    (void)groups;
+    RSTQ_REQUIRE(G <= ds.counters_len, RSTQ_E_LIMIT, "%d thread blocks exceed the %lld hand-over flags", G,
+                 (long long)ds.counters_len);
+    RSTQ_REQUIRE((int64_t)G * M * 32 * 4 <= ds.partials_bytes, RSTQ_E_LIMIT, "partials scratch too small");
     return RSTQ_OK;
 }
 
 static void fill_common(StreamParams& p, const DeviceState& ds, const StreamPlan& pl, int64_t in,
                         int64_t out, int M, int64_t nb, int zp) {
-    p.partials = ds.partials; p.counters = ds.counters; p.status = ds.status; p.dbg = ds.dbg;
+    p.partials = ds.partials; p.flags = ds.counters; p.status = ds.status; p.dbg = ds.dbg;
     p.in = in; p.out = out; p.uq = pl.uq; p.ur = pl.ur; p.U = ((out + 31) / 32) * nb;
     p.M = M; p.nb = (int)nb; p.G = pl.G; p.zp = zp; p.NS = pl.NS;
+    p.pf_ahead = ds.gemv_prefetch_kb << 10;
+    p.probe = ds.gemv_probe;
     p.act_off = pl.act_off; p.act2_off = pl.act2_off; p.red_off = pl.red_off; p.bar_off = pl.bar_off;
 }
 
@@ -865,12 +1017,12 @@ static cudaError_t launch_stream(K kernel, const DeviceState& ds, const StreamPl
 // Largest token count <= want whose staged activations fit next to a ring of >= 2 chunks.
 template <typename BytesFn>
 static int fit_tokens(const DeviceState& ds, int bits, int64_t groups, int64_t nb, int want, BytesFn f,
-                      StreamPlan* out) {
+                      StreamPlan* out, bool a8 = false) {
     for (int m = want; m >= 1; --m) {
         int NT;
         int64_t a1, a2;
         f(m, &NT, &a1, &a2);
-        StreamPlan pl = plan_stream(ds, bits, NT, groups, nb, a1, a2);
+        StreamPlan pl = plan_stream(ds, bits, NT, groups, nb, a1, a2, a8 && m == 1);
         if (pl.fits) {
             *out = pl;
             return m;
@@ -891,35 +1043,50 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
     for (int64_t m0 = 0; m0 < a.M;) {
         const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
         StreamPlan pl;
-        const int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
+        int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl, true);
         RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
                      (long long)a.in);
         if (a.tp && (M < a.M || a.out % 4 != 0)) return kNotFused;  // the exchange fuses into ONE launch
+        const bool qf = a.x != nullptr;
+        RSTQ_REQUIRE(!qf || (a.M == 1 && a.in <= kQuantMaxIn), RSTQ_E_INVALID,
+                     "the in-kernel quantizer serves M = 1 and in <= %d", kQuantMaxIn);
         int32_t rc = stream_scratch_ok(ds, groups, pl.G, M);
         if (rc != RSTQ_OK) return rc;
         const int NT = M <= 8 ? 1 : 2;
         StreamParams p{};
         fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp);
         p.w = a.w;
-        p.xq = a.xq + m0 * a.in;
-        p.xs = a.xs + m0 * nb;
-        p.xsum = a.xsum + m0 * nb;
+        if (qf) {
+            p.x = a.x;
+        } else {
+            p.xq = a.xq + m0 * a.in;
+            p.xs = a.xs + m0 * nb;
+            p.xsum = a.xsum + m0 * nb;
+        }
         p.y = a.y + m0 * a.out;
-        p.T = 1; p.act_dtype = RSTQ_F32; p.out_dtype = RSTQ_F32;
+        p.T = 1; p.act_dtype = qf ? a.act_dtype : RSTQ_F32; p.out_dtype = RSTQ_F32;
         if (a.tp) p.tp = *a.tp;
         cudaError_t le = cudaSuccess;
 #define LAUNCH(...)                                                                  \
     le = a.tp ? launch_stream(gemv_stream_kernel<__VA_ARGS__, true>, ds, pl, p)      \
               : launch_stream(gemv_stream_kernel<__VA_ARGS__, false>, ds, pl, p)
+#define LAUNCH1(B)                                                                                       \
+    do {                                                                                                 \
+        if (a.tp) le = qf ? launch_stream(gemv_stream_kernel<B, 1, MODE_A8, true, true, true>, ds, pl, p)  \
+                          : launch_stream(gemv_stream_kernel<B, 1, MODE_A8, true, true, false>, ds, pl, p);\
+        else le = qf ? launch_stream(gemv_stream_kernel<B, 1, MODE_A8, true, false, true>, ds, pl, p)      \
+                     : launch_stream(gemv_stream_kernel<B, 1, MODE_A8, true, false, false>, ds, pl, p);    \
+    } while (0)
         if (a.bits == 4) {
             if (NT == 2) LAUNCH(4, 2, MODE_A8, false);
-            else if (M == 1) LAUNCH(4, 1, MODE_A8, true);
+            else if (M == 1) LAUNCH1(4);
             else LAUNCH(4, 1, MODE_A8, false);
         } else {
             if (NT == 2) LAUNCH(8, 2, MODE_A8, false);
-            else if (M == 1) LAUNCH(8, 1, MODE_A8, true);
+            else if (M == 1) LAUNCH1(8);
             else LAUNCH(8, 1, MODE_A8, false);
         }
+#undef LAUNCH1
         ctx->launches++;
         RSTQ_CUDA(le);
         RSTQ_CUDA(cudaGetLastError());

@@ -67,12 +67,15 @@ struct DeviceState {
     bool capturing = false;
     bool pdl = true;               // launch the hot kernels with programmatic stream serialization
     int gemv_plan = 0;             // decode work split: 0 = per shape, 1 = equal unit ranges, 2 = whole groups
+    int64_t gemv_prefetch_kb = 0;  // decode kernels: KB of a CTA's weight range requested into L2 ahead of its ring
+    int gemv_probe = 0;            // timing probes of the decode kernel (RSTQ_TUNE_PROBE); results are invalid while set
+    bool fuse_quant = true;        // M = 1 operator: quantize the activations inside the decode kernel
     // scratch owned by the context
     void* act_scratch = nullptr;   // quantized / converted activations
     int64_t act_scratch_bytes = 0;
-    float* partials = nullptr;     // split-K partial sums
+    float* partials = nullptr;     // decode kernel: partial sums handed between CTAs that share a 32-row group
     int64_t partials_bytes = 0;
-    int* counters = nullptr;       // split-K arrival counters (zero between calls)
+    int* counters = nullptr;       // decode kernel: one hand-over flag per CTA (zero between calls)
     int64_t counters_len = 0;
     void* gemm_scratch = nullptr;  // fp16 activations + row exponents of the GEMM path
     int64_t gemm_scratch_bytes = 0;
@@ -85,6 +88,11 @@ struct DeviceState {
     void* io_dev = nullptr;        // device staging for the host-array entry points
     int64_t io_dev_bytes = 0;
     int* status = nullptr;         // device status word: nonzero after a bounded wait ran out
+    // Instantiated graphs hold the scratch addresses of the launches they recorded.  While any is
+    // alive, scratch that has to grow is parked here instead of freed, so a replay never touches
+    // memory that went back to the allocator; the blocks are released when the last graph is gone.
+    int live_graphs = 0;
+    std::vector<void*> retired;
     unsigned long long* dbg = nullptr;      // phase timestamps of the last streaming launch, when enabled
     unsigned long long* dbg_store = nullptr;
 };
@@ -208,6 +216,8 @@ struct GemvA8Args {
     int64_t M, in, out;   // y is [M, out] f32
     int bits, zp;
     const TpFuse* tp = nullptr;
+    const void* x = nullptr;     // M == 1 only: raw activations (f32 or bf16), quantized by the kernel
+    int act_dtype = RSTQ_F32;    // itself while staging; xq / xs / xsum are then not read
 };
 struct GemvFArgs {
     const uint8_t* w;
@@ -234,8 +244,11 @@ int32_t launch_qlinear_q8_dx(rstq_ctx* ctx, DeviceState& ds, const float* dy, co
 int32_t use_dev(rstq_ctx* ctx, int dev);
 int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M, int act_dtype,
                       int out_dtype, int mode, const TpFuse* tp = nullptr);
-// capi.cu: grow-only device scratch (refuses to grow during graph capture)
+// capi.cu: grow-only device scratch (refuses to grow during graph capture; the outgrown block is
+// freed at once, or parked until the last live graph of the device is destroyed)
 int32_t dev_reserve(DeviceState& ds, void** p, int64_t* have, int64_t need);
+int32_t dev_release_scratch(DeviceState& ds, void* p);
 constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels
+constexpr int64_t kFusedQuantMaxIn = 12288; // longest row the decode kernel quantizes itself (3 passes of 512 threads x 8)
 
 }  // namespace rstq

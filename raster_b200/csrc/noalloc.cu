@@ -5,8 +5,9 @@
 // arena at session start and forbids later growth, a caller in the middle of a
 // stream capture (allocation is illegal there), or a real-time decode loop that
 // must never reach the driver's allocator.  The regular entry points draw their
-// split-group scratch (partial sums, arrival counters, status word) from
-// buffers the context allocated; this one keeps the same scratch in fixed
+// split-group scratch (the partial sums thread blocks hand to one another and
+// one hand-over flag per block) from buffers the context allocated; this one
+// keeps the same scratch in fixed
 // arrays that live in the library's device image, so every GPU that loads the
 // library carries them (about 1.3 MB) until the process exits.
 //
@@ -15,10 +16,15 @@
 // M is cut into launches of <= 16, as everywhere else).
 //
 // The arrays are shared by every call on the device.  They keep the last call's
-// contents; the only part that must start at zero -- the arrival counters -- is
-// cleared once at set-up and restored to zero by each launch before it ends.
+// contents; the only part that must start at zero -- the hand-over flags -- is
+// cleared once at set-up and put back to zero by each launch before it ends.
 // Two calls that overlap on the GPU (different streams, no dependency) would
 // race on the arrays: serialise them.
+//
+// A time-bounded wait that runs out inside such a launch is reported like
+// everywhere else: the kernel sets the context's own status word (allocated
+// when the context was made, so nothing is allocated here) and the next
+// rstq_sync returns RSTQ_E_WAIT.
 #include "internal.h"
 
 namespace rstq {
@@ -30,27 +36,23 @@ constexpr int kNaMaxM = 16;
 // Scratch of the allocation-free entry point (device image, not the heap).
 static __device__ __align__(256) float g_na_partials[kNaMaxCtas * 2 * kNaMaxM * 32];
 static __device__ __align__(256) int g_na_counters[kNaMaxGroups];
-static __device__ __align__(256) int g_na_status[64];
 
 struct NaDevice {
     bool ready = false;
     float* partials = nullptr;
     int* counters = nullptr;
-    int* status = nullptr;
 };
 static NaDevice g_na_dev[64];
 
 // Once per device, with that device current: turn the host-side stand-ins of
 // the arrays into device addresses (a kernel must never be handed the symbol
-// itself) and clear the counters.
+// itself) and clear the flags.
 static int32_t na_setup(int ordinal, cudaStream_t stream) {
     NaDevice& d = g_na_dev[ordinal];
     if (d.ready) return RSTQ_OK;
     RSTQ_CUDA(cudaGetSymbolAddress((void**)&d.partials, g_na_partials));
     RSTQ_CUDA(cudaGetSymbolAddress((void**)&d.counters, g_na_counters));
-    RSTQ_CUDA(cudaGetSymbolAddress((void**)&d.status, g_na_status));
     RSTQ_CUDA(cudaMemsetAsync(d.counters, 0, sizeof(int) * kNaMaxGroups, stream));
-    RSTQ_CUDA(cudaMemsetAsync(d.status, 0, sizeof(int) * 64, stream));
     d.ready = true;
     return RSTQ_OK;
 }
@@ -88,7 +90,6 @@ extern "C" int32_t rstq_qmatmul_prequant_noalloc(rstq_weight* w, const void* xq,
     ds.partials_bytes = (int64_t)sizeof(float) * kNaMaxCtas * 2 * kNaMaxM * 32;
     ds.counters = d.counters;
     ds.counters_len = kNaMaxGroups;
-    ds.status = d.status;
     ds.dbg = nullptr;
     ds.stream = st;
     GemvA8Args a{w->data, (const int8_t*)xq, (const float*)xs, (const int32_t*)xsum, (float*)y,

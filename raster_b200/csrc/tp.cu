@@ -270,15 +270,30 @@ int32_t rstq_tp_create_local(rstq_ctx* ctx, int32_t nranks, const int32_t* devs,
         }
     }
     void* regions[kTpMaxRanks] = {};
+    for (int r = 0; r < nranks; ++r) tps[r] = nullptr;
+    auto undo = [&]() {   // a failure half-way: give back what was made so far
+        for (int r = 0; r < nranks; ++r) {
+            if (tps[r]) { tps[r]->magic = 0; delete tps[r]; tps[r] = nullptr; }
+            if (regions[r]) { cudaSetDevice(ctx->devs[devs[r]].ordinal); cudaFree(regions[r]); }
+        }
+        cudaGetLastError();
+    };
     for (int r = 0; r < nranks; ++r) {
-        RSTQ_CUDA(cudaSetDevice(ctx->devs[devs[r]].ordinal));
-        RSTQ_CUDA(cudaMalloc(&regions[r], (size_t)bytes));
-        RSTQ_CUDA(cudaMemset(regions[r], 0, (size_t)bytes));
-        RSTQ_CUDA(cudaDeviceSynchronize());
+        cudaError_t e = cudaSetDevice(ctx->devs[devs[r]].ordinal);
+        if (e == cudaSuccess) e = cudaMalloc(&regions[r], (size_t)bytes);
+        if (e == cudaSuccess) e = cudaMemset(regions[r], 0, (size_t)bytes);
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) {
+            undo();
+            return cuda_fail(e, "region allocation", __FILE__, __LINE__);
+        }
     }
     for (int r = 0; r < nranks; ++r) {
         const int32_t rc = rstq_tp_attach(ctx, devs[r], r, nranks, regions, bytes, &tps[r]);
-        if (rc != RSTQ_OK) return rc;
+        if (rc != RSTQ_OK) {
+            undo();
+            return rc;
+        }
         tps[r]->owns_region = true;
     }
     return RSTQ_OK;
@@ -325,7 +340,7 @@ int32_t rstq_tp_qmatmul(rstq_tp* tp, rstq_weight* w, rstq_buf* x, rstq_buf* y, i
     const int64_t need = M * w->out * 4;
     if (need > tp->tmp_bytes) {
         RSTQ_REQUIRE(!ds.capturing, RSTQ_E_INVALID, "first call of this size must happen outside graph capture");
-        if (tp->tmp) RSTQ_CUDA(cudaFree(tp->tmp));
+        if ((rc = dev_release_scratch(ds, tp->tmp)) != RSTQ_OK) return rc;  // parked while a graph may name it
         tp->tmp = nullptr;
         tp->tmp_bytes = 0;
         RSTQ_CUDA(cudaMalloc(&tp->tmp, (size_t)need));
@@ -392,6 +407,15 @@ int32_t rstq_tp_free(rstq_tp* tp) {
     RSTQ_REQUIRE(ok_tp(tp), RSTQ_E_INVALID, "invalid endpoint handle");
     int32_t rc = use_dev(tp->ctx, tp->dev);
     if (rc != RSTQ_OK) return rc;
+    // peers store into this rank's region: when this process drives them too (one process, several
+    // devices), their streams must be idle before the region goes away
+    if (tp->owns_region)
+        for (auto& other : tp->ctx->devs) {
+            if (other.ordinal < 0 || !other.stream) continue;
+            cudaSetDevice(other.ordinal);
+            cudaStreamSynchronize(other.stream);
+        }
+    if ((rc = use_dev(tp->ctx, tp->dev)) != RSTQ_OK) return rc;
     RSTQ_CUDA(cudaStreamSynchronize(tp->ctx->devs[tp->dev].stream));
     if (tp->tmp) cudaFree(tp->tmp);
     if (tp->owns_region) cudaFree(tp->region[tp->rank]);

@@ -73,6 +73,111 @@ def test_quant_act_rounding_ties_go_up(ctx):
     assert list(q[:7]) == [127, 1, 2, 3, 0, -1, -2] and xs[0] == 1.0
 
 
+# ------------------------------------------- one token: the quantizer inside the decode kernel
+def _hard_activations(in_, seed):
+    """N(0,1) with the blocks that stress the quantizer: all zero, tiny, huge, exact rounding ties,
+    and values a hair either side of a tie (the f32 shortcut must hand those to the double path)."""
+    x = synth.normal(seed, in_)
+    x[:32] = 0.0
+    x[32:64] = np.float32(1e-30)
+    x[64] = np.float32(1e30)
+    x[70] = np.float32(-1e30)
+    x[96:128] = 0.0
+    x[96] = 127.0                                   # d = 1: codes are round_half_up(x)
+    x[97:103] = [0.5, 1.5, 2.5, -0.5, -1.5, -2.5]
+    x[103:109] = np.nextafter(np.float32([0.5, 1.5, 2.5, -0.5, -1.5, -2.5]), np.float32(10))
+    x[109:115] = np.nextafter(np.float32([0.5, 1.5, 2.5, -0.5, -1.5, -2.5]), np.float32(-10))
+    x[128:160] = 0.0
+    x[128] = np.float32(3.1)                        # a maximum 127 / max is not exact for
+    x[129:160] = (np.arange(31, dtype=np.float32) + 0.5) * np.float32(3.1) / np.float32(127)
+    return x
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("plan", [0, 1])
+@pytest.mark.parametrize("act", ["f32", "bf16"])
+@pytest.mark.parametrize("out,in_", [(264, 1024), (4096, 4096), (1000, 11008), (96, 160), (512, 12288)])
+def test_fused_quantizer_is_bit_identical_to_the_quantizer_kernel(ctx, bits, plan, act, out, in_):
+    """rstq_qmatmul at M = 1 quantizes inside the decode kernel; with RSTQ_TUNE_FUSE_QUANT = 0 the
+    quantizer kernel runs first.  Same codes, scales and sums -> the same y, bit for bit, and both
+    equal the oracle's qlinear-i8 arithmetic."""
+    fmt_desc, fmt, ofmt = FMT[bits]
+    _, wq, ws = make_weight(out, in_, bits, seed=out + in_)
+    x = _hard_activations(in_, out + 3 * in_)
+    if act == "bf16":
+        xb = synth.to_bf16_bits(x)
+        x = synth.from_bf16_bits(xb)
+        bx, adt = ctx.array_to_buffer(xb), L.BF16
+    else:
+        bx, adt = ctx.array_to_buffer(x), L.F32
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    by = ctx.make_buffer(out, np.float32)
+    ys = {}
+    try:
+        ctx.tune(L.TUNE_GEMV_PLAN, plan)
+        for fuse in (1, 0):
+            ctx.tune(L.TUNE_FUSE_QUANT, fuse)
+            by.fill_bytes(0xFF)
+            ctx.qmatmul(w, bx, by, 1, adt, L.F32, L.MODE_A8)
+            ctx.sync()
+            ys[fuse] = by.download()
+    finally:
+        ctx.tune(L.TUNE_FUSE_QUANT, 1)
+        ctx.tune(L.TUNE_GEMV_PLAN, 0)
+    assert np.array_equal(ys[1].view(np.uint32), ys[0].view(np.uint32))
+    xq, xs, xsum = orc.quantize_act_i8(x, 1, in_)
+    ref = orc.matmul_a8_f64(wq, ws, ofmt, xq, xs, xsum, 1, in_, out)
+    assert relerr(ys[1], ref) <= TOL_A8
+    for b in (bx, by):
+        b.free()
+    w.free()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+@pytest.mark.parametrize("out,in_", [(11008, 4096), (4096, 11008), (28672, 8192), (64, 28672), (200, 96)])
+def test_equal_range_split_hands_partial_sums_over_correctly(ctx, bits, M, out, in_):
+    """Work split 1 cuts the weight into equal unit ranges over all SMs: 32-row groups are shared by two or
+    three neighbouring thread blocks, which hand their partial sums to the block that holds the group's
+    head.  Against work split 2 (whole groups, nothing shared) and, on a sample of rows, the oracle; three
+    launches back to back, so the hand-over flags of one launch are found cleared by the next."""
+    if M * in_ > 8 * 11008 and M > 8:
+        pytest.skip("M is cut into several launches at this length; covered by the token-splitting test")
+    fmt_desc, fmt, ofmt = FMT[bits]
+    rng = np.random.default_rng(out + in_ + M)
+    codes = rng.integers(0, 256, out * in_ * bits // 8, dtype=np.uint8)
+    scales = (rng.standard_normal(out * (in_ // 32)) * 0.01).astype(np.float32)
+    x = synth.normal(5, M * in_)
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    w = ctx.bind_weight(codes, scales, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    bq, bs, bsum = ctx.array_to_buffer(xq), ctx.array_to_buffer(xs), ctx.array_to_buffer(xsum)
+    ys = [ctx.make_buffer(M * out, np.float32) for _ in range(3)]
+    got = {}
+    try:
+        for plan in (2, 1):
+            ctx.tune(L.TUNE_GEMV_PLAN, plan)
+            for y in ys:
+                y.fill_bytes(0xFF)
+            for y in ys:
+                ctx.qmatmul_prequant(w, bq, bs, bsum, y, M)
+            ctx.sync()
+            got[plan] = [y.download() for y in ys]
+    finally:
+        ctx.tune(L.TUNE_GEMV_PLAN, 0)
+    full = float(np.abs(got[2][0]).max())
+    for k in range(3):
+        assert np.array_equal(got[1][k].view(np.uint32), got[1][0].view(np.uint32))    # run to run: bit-identical
+        assert np.abs(got[1][k] - got[2][k]).max() <= TOL_A8 * full                   # another summation order
+    rows = np.sort(rng.choice(out, size=min(out, 64), replace=False))     # the oracle on a sample of rows
+    c = np.ascontiguousarray(codes.reshape(out, in_ * bits // 8)[rows]).ravel()
+    sc = np.ascontiguousarray(scales.reshape(out, in_ // 32)[rows]).ravel()
+    ref = orc.matmul_a8_f64(c, sc, ofmt, xq, xs, xsum, M, in_, rows.size).reshape(M, rows.size)
+    assert np.abs(got[1][0].reshape(M, out)[:, rows] - ref).max() <= TOL_A8 * full
+    for b in (bq, bs, bsum, *ys):
+        b.free()
+    w.free()
+
+
 # ---------------------------------------------------------------- decode kernels, A8
 @pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("out,in_,M", [
@@ -380,7 +485,7 @@ def test_graph_replay_is_idempotent_and_clone_is_equal(ctx):
     g.replay()
     ctx.sync()
     first = by.download()
-    assert ctx.launch_count() - n0 == 4           # 2 x (quantize + gemv)
+    assert ctx.launch_count() - n0 == 2           # one token: the quantizer runs inside the decode kernel
     assert np.array_equal(first, by2.download())
     g.replay(), g.replay()
     ctx.sync()
@@ -392,6 +497,40 @@ def test_graph_replay_is_idempotent_and_clone_is_equal(ctx):
     for b in (bx, by, by2):
         b.free()
     w.free(), w2.free()
+
+
+def test_scratch_that_grows_after_a_capture_does_not_break_the_graph(ctx):
+    """A captured launch has the scratch addresses of its day recorded.  A later, larger call makes the
+    scratch grow; the outgrown block must stay valid until the graph is destroyed, so a replay still
+    computes the right thing (and touches no freed memory)."""
+    out, in_ = 256, 4096
+    _, wq, ws = make_weight(out, in_, 4, seed=77)
+    w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    x = synth.normal(78, 2 * in_)
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(2 * out, np.float32)
+    ctx.qmatmul(w, bx, by, 2)                      # M = 2: quantizer -> scratch -> decode kernel
+    ctx.graph_begin()
+    ctx.qmatmul(w, bx, by, 2)
+    g = ctx.graph_end()
+    g.replay()
+    ctx.sync()
+    first = by.download()
+    xq, xs, xsum = orc.quantize_act_i8(x, 2, in_)
+    assert relerr(first, orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, 2, in_, out)) <= TOL_A8
+    big = 640                                     # 640 x 4096 codes: several MB, the scratch must grow
+    xb = synth.normal(79, big * in_)
+    ybig = ctx.qmatmul_host(w, xb, big, L.F32, L.MODE_A8)
+    assert np.isfinite(ybig).all()
+    other = ctx.make_buffer(4 << 20, np.uint8)    # whatever the allocator hands out next gets scribbled
+    other.fill_bytes(0x7F)
+    by.fill_bytes(0xFF)
+    g.replay()
+    ctx.sync()
+    assert np.array_equal(first.view(np.uint32), by.download().view(np.uint32))
+    g.destroy()
+    for b in (bx, by, other):
+        b.free()
+    w.free()
 
 
 # ---------------------------------------------------------------- token splitting

@@ -17,8 +17,6 @@ definition; the last test shows the departure and bounds where it can occur.
 CPU only.  Skipped when neither the reference checkout nor a prebuilt oracle/_ref is there.
 """
 import ctypes as C
-import os
-import sys
 
 import numpy as np
 import pytest
@@ -26,8 +24,7 @@ import pytest
 from javarandom import JavaRandom
 from oracle import oracle as orc
 
-sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
-import build_ref  # noqa: E402
+from oracle import build_ref  # noqa: E402
 
 if build_ref.reference_present():
     build_ref.build()

@@ -19,9 +19,15 @@ from raster_b200 import synth
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("plan", [1, 0])
 @pytest.mark.parametrize("bits,fmt", [(4, L.FMT_Q4_0), (8, L.FMT_Q8_0)])
-@pytest.mark.parametrize("out,in_,M", [(4096, 11008, 1), (1000, 2048, 3), (11008, 4096, 8)])
-def test_noalloc_matches_regular_entry_twice(ctx, bits, fmt, out, in_, M):
+@pytest.mark.parametrize("out,in_,M", [(4096, 11008, 1), (1000, 2048, 3), (11008, 4096, 8), (1000, 4096, 16)])
+def test_noalloc_matches_regular_entry_twice(ctx, plan, bits, fmt, out, in_, M):
+    """plan 1 cuts the weight into equal ranges, so neighbouring thread blocks share 32-row groups and
+    hand their partial sums over through the fixed arrays (partials + arrival counters): that is the
+    scratch this entry point exists for.  plan 0 is the default split (whole groups at these shapes,
+    the arrays stay untouched).  Two calls in a row: the second one finds the counters the first one
+    must have put back to zero."""
     w = synth.normal(out + in_, out * in_, 0.02)
     wq, ws = orc.quantize_weight(w, bits)
     x = synth.normal(out + in_ + 1, M * in_)
@@ -29,21 +35,25 @@ def test_noalloc_matches_regular_entry_twice(ctx, bits, fmt, out, in_, M):
     bw = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
     bq, bs, bsum = ctx.array_to_buffer(xq), ctx.array_to_buffer(xs), ctx.array_to_buffer(xsum)
     y_ref, y_na = ctx.make_buffer(M * out, np.float32), ctx.make_buffer(M * out, np.float32)
-    ctx.qmatmul_prequant(bw, bq, bs, bsum, y_ref, M)
-    ctx.sync()
-    ref = y_ref.download()
     oracle = orc.matmul_a8_f64(wq, ws, 0 if bits == 4 else 1, xq, xs, xsum, M, in_, out).ravel()
     scale = np.abs(oracle).max()
-    assert np.abs(ref - oracle).max() <= 2e-6 * scale
-    for call in range(2):
-        y_na.fill_bytes(0xFF)
-        L.check(ctx.lib.rstq_qmatmul_prequant_noalloc(
-            bw.handle, C.c_void_p(bq.device_ptr), C.c_void_p(bs.device_ptr),
-            C.c_void_p(bsum.device_ptr), C.c_void_p(y_na.device_ptr), None, M))
+    try:
+        ctx.tune(L.TUNE_GEMV_PLAN, plan)
+        ctx.qmatmul_prequant(bw, bq, bs, bsum, y_ref, M)
         ctx.sync()
-        got = y_na.download()
-        assert np.abs(got - ref).max() <= 2e-6 * scale, f"call {call}"
-        assert np.abs(got - oracle).max() <= 2e-6 * scale, f"call {call}"
+        ref = y_ref.download()
+        assert np.abs(ref - oracle).max() <= 2e-6 * scale
+        for call in range(2):
+            y_na.fill_bytes(0xFF)
+            L.check(ctx.lib.rstq_qmatmul_prequant_noalloc(
+                bw.handle, C.c_void_p(bq.device_ptr), C.c_void_p(bs.device_ptr),
+                C.c_void_p(bsum.device_ptr), C.c_void_p(y_na.device_ptr), None, M))
+            ctx.sync()          # raises if a bounded wait inside the launch ran out (status word)
+            got = y_na.download()
+            assert np.abs(got - ref).max() <= 2e-6 * scale, f"call {call}"
+            assert np.abs(got - oracle).max() <= 2e-6 * scale, f"call {call}"
+    finally:
+        ctx.tune(L.TUNE_GEMV_PLAN, 0)
     for b in (bq, bs, bsum, y_ref, y_na):
         b.free()
     bw.free()
