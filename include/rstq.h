@@ -96,9 +96,17 @@ typedef struct rstq_event rstq_event;
                                      blocks), 2 = whole 32-row groups per thread block */
 #define RSTQ_TUNE_GEMV_PREFETCH 7  /* decode kernels: KB of a thread block's weight range requested into L2
                                      ahead of its shared-memory ring (0 = none) */
-#define RSTQ_TUNE_PROBE 8         /* timing probes of the decode kernel, RESULTS ARE INVALID while set: 1 = the
-                                     weight stream is not copied (consumer rate alone), 2 = the arithmetic is
-                                     skipped (copy rate alone); 0 (default) = off */
+#define RSTQ_TUNE_PROBE 8         /* only in a library built with -DRSTQ_PROBES=1 (otherwise any value but 0 is
+                                     refused): timing probes of the decode kernel, RESULTS ARE INVALID while
+                                     set: 1 = the weight stream is not copied (consumer rate alone), 2 = the
+                                     arithmetic is skipped (copy rate alone) */
+#define RSTQ_TUNE_PREFETCH_NEXT 9  /* 1 (default) = a decode launch asks for the head of the weight that followed
+                                     it last time on this device to be brought into L2 (up to 48 MB) while its own
+                                     consumers drain: a decode loop walks its matrices in the same order for
+                                     every token, so consecutive launches overlap at the memory system.  A hint
+                                     only: results never depend on it.  A launch recorded in a graph keeps
+                                     naming that weight: destroy graphs before freeing weights they ran beside.
+                                     0 = off */
 #define RSTQ_TUNE_FUSE_QUANT 6    /* 1 (default) = rstq_qmatmul in MODE_A8 at M = 1 quantizes the
                                      activations inside the decode kernel; 0 = separate quantizer launch */
 
@@ -117,9 +125,11 @@ RSTQ_API int32_t rstq_sync(rstq_ctx* ctx, int32_t dev);
 RSTQ_API int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value);
 /* out[0] = SM count, out[1] = L2 bytes, out[2] = total device memory, out[3] = cc major*10+minor */
 RSTQ_API int32_t rstq_device_info(rstq_ctx* ctx, int32_t dev, int64_t* out4);
-/* Phase timestamps (ns, device global timer) of the last streaming decode launch, 8 per CTA:
- * [0] entry, [1] consumers start, [2] activations staged, [3] first weights landed,
- * [4] main loop done, [5] exit.  Filled only while RSTQ_TUNE_TIMELINE is 1. */
+/* Phase timestamps (ns, device global timer) of the streaming decode launches made since
+ * RSTQ_TUNE_TIMELINE was set to 1: six slots of 160 rows used in turn (launch k writes slot k % 6),
+ * a row of 8 values per CTA: [0] entry, [1] consumers start (the preceding kernel has finished),
+ * [2] activations staged, [3] first weights landed, [4] main loop done, [5] exit, [6] SM id.
+ * Rows of CTAs a launch did not have read as zero. */
 RSTQ_API int32_t rstq_timeline_read(rstq_ctx* ctx, int32_t dev, int64_t* out, int64_t n);
 
 /* ---- device buffers: make-buffer / array->buffer! / buffer->array /

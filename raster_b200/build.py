@@ -2,7 +2,8 @@
 
 sm_100a only.  ``python -m raster_b200.build`` rebuilds when a source is newer
 than the library; ``--force`` always rebuilds; ``--verbose`` prints ptxas
-register / spill / shared-memory figures.
+register / spill / shared-memory figures; ``--probes`` builds the variant with
+the decode kernel's timing probes compiled in (experiments only).
 """
 from __future__ import annotations
 
@@ -49,7 +50,10 @@ def needs_build() -> bool:
     return any(os.path.getmtime(p) > t for p in sources() + _deps() + [os.path.abspath(__file__)])
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, probes: bool = False) -> str:
+    """``probes`` compiles the timing probes and per-chunk stamps of the decode kernel in
+    (-DRSTQ_PROBES=1): for experiments only, always a full rebuild."""
+    force = force or probes
     if not force and not needs_build():
         return LIB
     os.makedirs(OBJDIR, exist_ok=True)
@@ -61,7 +65,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if (not force and os.path.exists(obj) and os.path.getmtime(obj) > os.path.getmtime(src)
                 and os.path.getmtime(obj) > hdr_time):
             return obj, ""
-        cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DRSTQ_PROBES=1"] if probes else []), "-c", src, "-o", obj]
         if verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -87,5 +91,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, probes="--probes" in sys.argv)
     print(path)

@@ -134,16 +134,35 @@ static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* o
     return RSTQ_OK;
 }
 
+// A decode launch of w is about to be made: remember the order of the weights on this device (the
+// previous one learns that w follows it) and return what followed w last time, if it still exists.
+static NextWeight note_decode_launch(rstq_ctx* ctx, DeviceState& ds, rstq_weight* w) {
+    if (ds.last_decode_w && ds.last_decode_w != w && ctx->live_weights.count(ds.last_decode_w))
+        ds.last_decode_w->next_hint = w;
+    ds.last_decode_w = w;
+    NextWeight n;
+    rstq_weight* h = w->next_hint;
+    if (ds.prefetch_next && h && h != w && ctx->live_weights.count(h) && h->dev == w->dev) {
+        n.data = h->data;
+        n.groups = h->outp / 32;
+        n.nb = h->nb;
+        n.bits = h->bits;
+    }
+    return n;
+}
+
 // One matmul over device pointers, M split into decode-kernel chunks.
 static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs,
                       const int32_t* xsum, float* y, int64_t M, const TpFuse* tp = nullptr) {
     GemvA8Args a{w->data, xq, xs, xsum, y, M, w->in, w->out, w->bits, w->zp, tp};
+    a.next = note_decode_launch(ctx, ctx->devs[w->dev], w);
     return launch_gemv_a8(ctx, ctx->devs[w->dev], a);
 }
 
 static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
                      int act_dtype, int out_dtype, const TpFuse* tp = nullptr) {
     GemvFArgs a{w->data, x, y, M, w->in, w->out, w->bits, w->zp, act_dtype, out_dtype, tp};
+    a.next = note_decode_launch(ctx, ctx->devs[w->dev], w);
     return launch_gemv_f(ctx, ctx->devs[w->dev], a);
 }
 
@@ -222,6 +241,7 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
             // one token: every CTA of the decode kernel quantizes x (16 - 112 KB, in L2) while it
             // stages it, bit for bit as the quantizer kernel would -- one launch, no scratch
             GemvA8Args a{w->data, nullptr, nullptr, nullptr, (float*)y, 1, w->in, w->out, w->bits, w->zp, tp, x, act_dtype};
+            a.next = note_decode_launch(ctx, ds, w);
             return launch_gemv_a8(ctx, ds, a);
         }
         ActScratch s;
@@ -342,6 +362,7 @@ static int32_t bind_impl(rstq_ctx* ctx, rstq_weight** wout, const void* codes,
         if (e != cudaSuccess) return cuda_fail(e, "weight bind", __FILE__, __LINE__);
         return rc;
     }
+    ctx->live_weights.insert(w);
     *wout = w;
     return RSTQ_OK;
 }
@@ -507,7 +528,14 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
             for (auto& ds : ctx->devs) ds.pdl = value != 0;
             return RSTQ_OK;
         case RSTQ_TUNE_TIMELINE:
-            for (auto& ds : ctx->devs) ds.dbg = value ? ds.dbg_store : nullptr;
+            for (auto& ds : ctx->devs) {
+                ds.dbg = value ? ds.dbg_store : nullptr;
+                ds.dbg_launch = 0;
+                if (value && ds.ordinal >= 0 && !ds.capturing) {   // a fresh record: unused rows read as zero
+                    RSTQ_CUDA(cudaSetDevice(ds.ordinal));
+                    RSTQ_CUDA(cudaMemsetAsync(ds.dbg_store, 0, 1024 * 8 * 8, ds.stream));
+                }
+            }
             return RSTQ_OK;
         case RSTQ_TUNE_GEMV_PLAN:
             RSTQ_REQUIRE(value >= 0 && value <= 2, RSTQ_E_INVALID, "decode plan selector 0..2");
@@ -518,8 +546,16 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
             for (auto& ds : ctx->devs) ds.gemv_prefetch_kb = value;
             return RSTQ_OK;
         case RSTQ_TUNE_PROBE:
+#if defined(RSTQ_PROBES) && RSTQ_PROBES
             RSTQ_REQUIRE(value >= 0 && value <= 3, RSTQ_E_INVALID, "probe selector 0..3");
             for (auto& ds : ctx->devs) ds.gemv_probe = (int)value;
+            return RSTQ_OK;
+#else
+            RSTQ_REQUIRE(value == 0, RSTQ_E_INVALID, "this library was built without timing probes");
+            return RSTQ_OK;
+#endif
+        case RSTQ_TUNE_PREFETCH_NEXT:
+            for (auto& ds : ctx->devs) ds.prefetch_next = value != 0;
             return RSTQ_OK;
         case RSTQ_TUNE_FUSE_QUANT:
             for (auto& ds : ctx->devs) ds.fuse_quant = value != 0;
@@ -782,6 +818,8 @@ int32_t rstq_weight_clone(rstq_weight* src, rstq_weight** wout) {
         delete w;
         return cuda_fail(e, "weight clone", __FILE__, __LINE__);
     }
+    w->next_hint = nullptr;
+    ctx->live_weights.insert(w);
     *wout = w;
     return RSTQ_OK;
 }
@@ -790,6 +828,8 @@ int32_t rstq_weight_free(rstq_weight* w) {
     if (!w) return RSTQ_OK;
     RSTQ_REQUIRE(ok_w(w), RSTQ_E_INVALID, "invalid weight handle");
     DeviceState& ds = w->ctx->devs[w->dev];
+    w->ctx->live_weights.erase(w);
+    if (ds.last_decode_w == w) ds.last_decode_w = nullptr;
     cudaSetDevice(ds.ordinal);
     if (!ds.capturing) cudaStreamSynchronize(ds.stream);
     cudaFree(w->data);

@@ -34,13 +34,30 @@
 #include "mma_helpers.cuh"
 #include "sync_helpers.cuh"
 
+// Timing probes and the per-chunk stamps of CTA 0 exist only in builds made with -DRSTQ_PROBES=1
+// (python -m raster_b200.build --probes); the shipped library carries neither.
+#ifndef RSTQ_PROBES
+#define RSTQ_PROBES 0
+#endif
+#if RSTQ_PROBES
+#define PROBE(bit) (p.probe & (bit))
+#else
+#define PROBE(bit) false
+#endif
+
 namespace rstq {
 
 constexpr int kCW = 16;                          // consumer warps
 constexpr int kConsumers = kCW * 32;
 constexpr int kStreamThreads = kConsumers + 32;  // + producer warp
 // units per consumer warp per chunk: 4 (40 KB chunks) for 4-bit, 2 (36 KB chunks) for 8-bit
-__host__ __device__ constexpr int upw_of(int bits) { return bits == 4 ? 4 : 2; }
+#ifndef RSTQ_UPW4
+#define RSTQ_UPW4 4
+#endif
+#ifndef RSTQ_NSMAX
+#define RSTQ_NSMAX 6
+#endif
+__host__ __device__ constexpr int upw_of(int bits) { return bits == 4 ? RSTQ_UPW4 : 2; }
 __host__ __device__ constexpr int chunk_units_of(int bits) { return upw_of(bits) * kCW; }
 constexpr int kMaxDynSmem = 232448 - 1024;       // 227 KB opt-in limit less the static part
 // the in-kernel quantizer holds all of a thread's activations in registers: in <= 3 * 512 * 8
@@ -48,6 +65,10 @@ constexpr int kQuantPasses = 3;
 constexpr int kQuantMaxIn = kQuantPasses * kConsumers * 8;
 static_assert(kGemvMaxM * 32 <= kConsumers, "one output per consumer thread in the hand-over");
 static_assert(kQuantMaxIn == kFusedQuantMaxIn, "the host routes by kFusedQuantMaxIn");
+// M = 1: the per-warp partial sums of whole groups are parked in shared memory (kParkStride floats per
+// group: [warp][33]) and reduced across warps once per kParkGroups groups, not once per group
+constexpr int kParkGroups = 8;
+constexpr int kParkStride = kCW * 33;
 constexpr int kMagicInt = 0x4B400000;            // bits of 12582912.0f = 2^23 + 2^22
 constexpr float kMagicFlt = 12582912.0f;
 
@@ -64,11 +85,17 @@ struct StreamParams {
     int* flags;           // [G]: 1 while slot c holds a partial nobody has taken yet; zero between launches
     int* status;          // device status word (0 = ok)
     unsigned long long* dbg;  // optional per-CTA phase timestamps (8 per CTA), or null
+    unsigned long long* dbg_fine;  // with dbg: 512 values behind the slots, CTA 0's stamp per wait / chunk / flush
     int64_t in, out;
     int64_t uq, ur;       // units per CTA: CTA c owns uq (+1 if c < ur) units
     int64_t U;            // all units (the last CTA's range is clipped to it)
     int M, nb, G, zp, NS, T, act_dtype, out_dtype;
     int64_t pf_ahead;     // bytes of the CTA's range requested into L2 ahead of the ring (0: none)
+    // the weight expected to be streamed by the NEXT launch of this stream (null: unknown): its
+    // thread block j will own units [range_begin(j), range_begin(j + 1)) of nx_U, of nx_unit bytes each
+    const uint8_t* nx_w;
+    int64_t nx_uq, nx_ur, nx_U, nx_pf_units;
+    int nx_G, nx_unit;
     int probe;            // timing probes (results invalid): 1 = the producer signals without copying, 2 = the consumers skip the arithmetic
     uint32_t act_off, act2_off, red_off, bar_off;  // byte offsets into dynamic smem (ring at 0)
     TpFuse tp;            // tp.nranks == 0: no exchange, results go to y
@@ -102,7 +129,8 @@ __device__ __forceinline__ void imma_acc(int (&d)[4], const uint32_t (&a)[4], ui
 // A8, M == 1: srec [nb][4 tig] uint4 {xq word tig, xq word 4+tig, xs_t bits, c_t}: lane tig
 //            folds row gid + 8*tig only (all eight tile columns are the same token), so the
 //            record carries that row's constants: for 4-bit codes the rows of odd tig sit in
-//            the high nibbles (tile value x16): xs_t = xs/16 and c_t = bias - 16*zp*xsum;
+//            the high nibbles (tile value x16, taken as a difference of two tile rows: see row_fold):
+//            xs_t = xs/16 and c_t = bias - 16*zp*xsum + 1;
 //            otherwise xs_t = xs and c_t = bias - zp*xsum (bias = bits of 2^23 + 2^22).
 // A8, M > 1 : sB [nb][M][4 tig] uint2 {xq word tig, xq word 4+tig};
 //             sxz [nb][Mz] int2 {xs bits, zp*xsum}, Mz = M rounded up to even.
@@ -136,7 +164,7 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
                     r.x = wa[j];
                     r.y = wb[j];
                     r.z = __float_as_uint(hi ? xs[j] * 0.0625f : xs[j]);
-                    r.w = (uint32_t)(kMagicInt - (p.zp * zs[j]) * (hi ? 16 : 1));
+                    r.w = (uint32_t)(kMagicInt - (p.zp * zs[j]) * (hi ? 16 : 1) + (hi ? 1 : 0));
                     srec[i] = r;
                 }
             }
@@ -280,7 +308,7 @@ __device__ __forceinline__ void stage_a8_quant(const StreamParams& p, uint8_t* s
             r.y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) |
                   ((uint32_t)(q[7] & 0xFF) << 24);
             r.z = __float_as_uint(hi ? xs * 0.0625f : xs);
-            r.w = (uint32_t)(kMagicInt - (p.zp * sum) * (hi ? 16 : 1));
+            r.w = (uint32_t)(kMagicInt - (p.zp * sum) * (hi ? 16 : 1) + (hi ? 1 : 0));
             srec[i] = r;
         }
     }
@@ -360,25 +388,58 @@ __device__ __forceinline__ void a_frags(const SUnit<BITS>& u, uint32_t (&a)[2][4
     }
 }
 
-// M == 1: lane (gid, tig) owns output row gid + 8*tig of the group.  `codes` points at the
-// lane's 16-byte slot, `scale` at the f32 scale of its row, `rec` at its staged record.
+// ---- M == 1 -------------------------------------------------------------------------------
+// Lane (gid, tig) owns output row gid + 8*tig of the group.  Everything is addressed by 32-bit
+// shared-memory addresses: `codes` = the lane's 16-byte slot of a unit, `scale` = the f32 scale of
+// its row, `rec` = its staged record {xq word tig, xq word 4 + tig, xs_t, c_t}.
+//
+// 4-bit codes: the low-nibble rows (gid, gid + 16) take the masked word, the high-nibble rows
+// (gid + 8, gid + 24) take the word AS IT IS: as unsigned bytes 16*h + l, so their tile row holds
+// 16*dot(h) + dot(l), and dot(l) is the tile row of the low-nibble partner.  A lane of a high-nibble row
+// (odd tig) therefore folds d_hi - d_lo = 16*dot(h), written (d_hi & m) + (d_lo ^ m) + c with m = ~0 and the
+// "+ 1" of the two's complement inside its staged constant c; an even lane (m = 0) folds d_lo + c.
+// One mask per word instead of two.
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds32f(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
 template <int BITS>
-__device__ __forceinline__ float unit_a8_row(const uint8_t* codes, const float* scale,
-                                             const uint4* rec, bool odd, bool upper, float acc) {
-    SUnit<BITS> u;
-    u.c0 = *reinterpret_cast<const uint4*>(codes);
-    if (BITS == 8) u.c1 = *reinterpret_cast<const uint4*>(codes + 512);
-    const float sc = *scale;
-    const uint4 r = *rec;
+struct RowUnit {
+    uint4 c0, c1, r;
+    float sc;
+};
+template <int BITS>
+__device__ __forceinline__ void row_load(RowUnit<BITS>& u, uint32_t codes, uint32_t scale, uint32_t rec) {
+    u.c0 = lds128(codes);
+    if (BITS == 8) u.c1 = lds128(codes + 512);
+    u.sc = lds32f(scale);
+    u.r = lds128(rec);
+}
+template <int BITS>
+__device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bool upper, float acc) {
     uint32_t a[2][4];
-    a_frags<BITS>(u, a);
+    if (BITS == 4) {
+        const uint32_t lo = 0x0F0F0F0Fu;
+        a[0][0] = u.c0.x & lo; a[0][1] = u.c0.x; a[0][2] = u.c0.y & lo; a[0][3] = u.c0.y;
+        a[1][0] = u.c0.z & lo; a[1][1] = u.c0.z; a[1][2] = u.c0.w & lo; a[1][3] = u.c0.w;
+    } else {
+        a[0][0] = u.c0.x; a[0][1] = u.c0.y; a[0][2] = u.c1.x; a[0][3] = u.c1.y;
+        a[1][0] = u.c0.z; a[1][1] = u.c0.w; a[1][2] = u.c1.z; a[1][3] = u.c1.w;
+    }
     int d0[4], d1[4];
-    imma_u8s8(d0, a[0], r.x, r.y);
-    imma_u8s8(d1, a[1], r.x, r.y);
+    imma_u8s8(d0, a[0], u.r.x, u.r.y);
+    imma_u8s8(d1, a[1], u.r.x, u.r.y);
     // tig 0 -> d0[0] (row gid), 1 -> d0[2] (gid+8), 2 -> d1[0] (gid+16), 3 -> d1[2] (gid+24)
-    const int lo = upper ? d1[0] : d0[0], hi = upper ? d1[2] : d0[2];
-    const float f = __int_as_float((odd ? hi : lo) + (int)r.w) - kMagicFlt;
-    return fmaf(sc * __uint_as_float(r.z), f, acc);
+    const uint32_t lo = (uint32_t)(upper ? d1[0] : d0[0]), hi = (uint32_t)(upper ? d1[2] : d0[2]);
+    const uint32_t iv = BITS == 4 ? (hi & m) + (lo ^ m) + u.r.w : (m ? hi : lo) + u.r.w;
+    const float f = __uint_as_float(iv) - kMagicFlt;
+    return fmaf(u.sc * __uint_as_float(u.r.z), f, acc);
 }
 
 template <int BITS, int NT>
@@ -559,8 +620,31 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             // HBM requests beyond what the ring holds: the range is requested into L2 up to `pf_ahead`
             // bytes ahead of the copy position, so the bytes in flight from HBM are not bounded by
             // shared memory and the ring only has to cover the L2 round trip.
+            // Once this CTA's own range is requested in full, ask for the head of the next launch's weights to be
+            // brought into L2: by the time this launch's consumers have drained their rings -- HBM would
+            // idle meanwhile, the next launch's CTAs cannot be resident before these leave -- the next
+            // launch finds its first chunks in L2 and fills its rings at L2 speed.
+            auto prefetch_next = [&]() {
+                if (!p.nx_w) return;
+                for (int j = blockIdx.x; j < p.nx_G; j += gridDim.x) {
+                    const int64_t u0 = range_begin(j, p.nx_uq, p.nx_ur);
+                    int64_t u1 = range_begin(j + 1, p.nx_uq, p.nx_ur);
+                    u1 = u1 < p.nx_U ? u1 : p.nx_U;
+                    int64_t n = u1 - u0 < p.nx_pf_units ? u1 - u0 : p.nx_pf_units;
+                    const uint8_t* q = p.nx_w + u0 * p.nx_unit;
+                    for (int64_t rest = n * p.nx_unit; rest > 0; rest -= 32768, q += 32768) {
+                        const uint32_t nbytes = (uint32_t)(rest < 32768 ? rest : 32768);
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(q), "r"(nbytes) : "memory");
+                    }
+                }
+            };
+            bool nx_done = false;
             const uint8_t* const end = src + (int64_t)total * UNIT;
             const uint8_t* pf = src;
+#if RSTQ_PROBES
+            unsigned long long* pfine = (p.dbg && blockIdx.x == 0) ? p.dbg_fine + 256 : nullptr;  // producer stamps
+            int npf = 0;
+#endif
             const int64_t pf_ahead = p.pf_ahead;
             while (left > 0) {
                 if (pf_ahead > 0) {
@@ -576,20 +660,33 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 n = n < kChunkUnits ? n : kChunkUnits;
                 ok = mbar_try(empty0 + 8 * s, ph ^ 1u) || mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
+#if RSTQ_PROBES
+                if (pfine && npf < 250) pfine[1 + npf++] = gtime_ns();
+#endif
                 const uint32_t bytes = (uint32_t)(n * UNIT);
-                if (p.probe & 1) {
+                if (PROBE(1)) {
                     mbar_arrive(full0 + 8 * s);
                 } else {
                     mbar_expect_tx(full0 + 8 * s, bytes);
                     bulk_copy_g2s_hint(smem_u32(smem) + (uint32_t)s * CHUNK_BYTES, src, bytes, full0 + 8 * s, pol);
                 }
+#if RSTQ_PROBES
+                if (pfine && npf < 250) pfine[1 + npf++] = gtime_ns();
+#endif
                 src += bytes;
                 b += n;
                 if (b == nb) b = 0;
                 left -= n;
                 ++issued;
                 if (++s == NS) { s = 0; ph ^= 1u; }
+                if (!nx_done && left == 0) {   // behind the last request of this launch's own stream
+                    prefetch_next();
+                    nx_done = true;
+                }
             }
+#if RSTQ_PROBES
+            if (pfine) pfine[0] = (unsigned long long)npf;
+#endif
             if (!ok) {
                 // gave up: still wait (bounded) for the copies already issued to land,
                 // so no copy is in flight into this CTA's shared memory when it exits
@@ -646,6 +743,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     float acc[NT][4][2];
     float* red = reinterpret_cast<float*>(smem + p.red_off);
     const int M = p.M, T = p.T;
+    // fine record of CTA 0 (thread 0): a stamp after every wait, chunk and flush step, behind the slots
+#if RSTQ_PROBES
+    unsigned long long* fine = (p.dbg && blockIdx.x == 0 && tid == 0) ? p.dbg_fine : nullptr;
+    int nfine = 0;
+#endif
+    auto stamp = [&]() {
+#if RSTQ_PROBES
+        if (fine && nfine < 250) fine[1 + nfine++] = gtime_ns();
+#endif
+    };
 
     auto zero_acc = [&]() {
 #pragma unroll
@@ -705,14 +812,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         const bool head = b_from == 0, whole = head && (b_to == nb);
         const int64_t row0 = g * 32;
         float* part = p.partials + (int64_t)blockIdx.x * M * 32;
-        float* rbuf = red + (flush_no & 1) * (ONECOL ? kCW * 32 : kCW * NV * 32);
+        float* rbuf = ONECOL ? red + kParkGroups * kParkStride : red + (flush_no & 1) * (kCW * NV * 32);
         ++flush_no;
         if (ONECOL) {
-            rbuf[warp * 32 + lane] = acc[0][0][0];  // row gid + 8*tig of this lane
+            // (whole groups are parked by the loop and reduced in batches; this serves the cut ones)
+            rbuf[warp * 33 + lane] = acc[0][0][0];  // row gid + 8*tig of this lane (33: the 16 readers of a row hit 16 banks)
             consumer_bar();
             // thread t: row t >> 4, warp t & 15; 16 neighbouring lanes add up one row
             const int row = tid >> 4;
-            float sum = rbuf[(tid & 15) * 32 + (row & 7) * 4 + (row >> 3)];
+            float sum = rbuf[(tid & 15) * 33 + (row & 7) * 4 + (row >> 3)];
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             const bool owner = (tid & 15) == 0;
@@ -750,16 +858,115 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         }
     };
 
-    {
+    // M = 1: reduce the parked groups [g_first, g_first + count) across the warps and store them
+    auto flush_parked = [&](int64_t g_first, int count, bool more) {
+        consumer_bar();
+        const int row = tid >> 4;
+        const int src = (tid & 15) * 33 + (row & 7) * 4 + (row >> 3);
+        for (int i = 0; i < count; ++i) {
+            float sum = red[i * kParkStride + src];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const int64_t r = (g_first + i) * 32 + row;
+            if ((tid & 15) == 0 && r < p.out) emit(r, sum);
+        }
+        if (more) consumer_bar();   // the slots are written again
+    };
+
+    if (ONECOL) {
+        // ---- M == 1: the loop is bound by instruction issue, so it is kept lean: 32-bit shared-memory
+        // addresses that run along, segments cut into full chunks (four units per warp, fully unrolled,
+        // every load issued before the first tensor-core tile) and one ragged chunk, whole groups
+        // parked without a barrier.
         constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
+        constexpr uint32_t USTEP = kCW * UNIT, RSTEP = kCW * 64;   // next unit / record of this warp in a chunk
+        const uint32_t ring = smem_u32(smem), act = smem_u32(smem + p.act_off);
+        const uint32_t m = (tig & 1) ? 0xFFFFFFFFu : 0u;
+        const bool upper = tig & 2;
+        uint32_t codes = ring + warp * UNIT + lane * 16;            // this lane's slot of the warp's first unit
+        uint32_t scale = ring + warp * UNIT + CODES + lane * 4;
+        uint32_t rec = act + ((b_start + warp) * 4 + tig) * 16;
+        int s = 0, left = total, b = b_start;
+        uint32_t ph = 0;
+        bool alive = true;
+        int64_t g = g0, g_parked = g0;
+        int parked = 0;
+        if (dbg) {  // timestamp of the first weights; the loop's own wait then passes at once
+            if (!mbar_try(full0, 0)) alive = mbar_wait(full0, 0, abort_flag);
+            if (tid == 0) dbg[3] = gtime_ns();
+        }
+        // the answer of a barrier test takes a while: the test of the next chunk is issued before
+        // the arithmetic of this one
+        bool ready = mbar_test(full0, 0);
+        while (left > 0) {
+            const int seg = nb - b < left ? nb - b : left;   // this segment: blocks [b, b + seg) of group g
+            float v = 0.f;
+            for (int done = 0; done < seg;) {
+                const int n = seg - done < kChunkUnits ? seg - done : kChunkUnits;
+                const uint32_t bar = full0 + 8 * s;
+                if (alive && !ready && !mbar_try(bar, ph)) alive = mbar_wait(bar, ph, abort_flag);
+                stamp();
+                const int sn = s + 1 == NS ? 0 : s + 1;
+                ready = mbar_test(full0 + 8 * sn, sn ? ph : ph ^ 1u);
+                if (alive && !PROBE(2)) {
+                    if (n == kChunkUnits) {
+                        RowUnit<BITS> u[kUPW];
+#pragma unroll
+                        for (int j = 0; j < kUPW; ++j) row_load<BITS>(u[j], codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
+#pragma unroll
+                        for (int j = 0; j < kUPW; ++j) v = row_fold<BITS>(u[j], m, upper, v);
+                    } else {
+                        for (int j = 0; warp + j * kCW < n; ++j) {
+                            RowUnit<BITS> u;
+                            row_load<BITS>(u, codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
+                            v = row_fold<BITS>(u, m, upper, v);
+                        }
+                    }
+                }
+                __syncwarp();
+                stamp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);  // also when not alive: never block the producer
+                stamp();
+                done += n;
+                rec += n * 64;
+                if (sn) {
+                    codes += CHUNK_BYTES;
+                    scale += CHUNK_BYTES;
+                } else {
+                    codes -= (NS - 1) * CHUNK_BYTES;
+                    scale -= (NS - 1) * CHUNK_BYTES;
+                    ph ^= 1u;
+                }
+                s = sn;
+            }
+            left -= seg;
+            if (b == 0 && seg == nb) {
+                // a whole group: park this warp's sums, no barrier
+                if (parked == 0) g_parked = g;
+                red[parked * kParkStride + warp * 33 + lane] = v;
+                if (++parked == kParkGroups || left == 0) {
+                    flush_parked(g_parked, parked, left > 0);
+                    parked = 0;
+                }
+            } else {
+                acc[0][0][0] = v;
+                flush(g, b, b + seg);
+                if (left == 0 && parked > 0) {
+                    flush_parked(g_parked, parked, false);
+                    parked = 0;
+                }
+            }
+            stamp();
+            rec -= (b + seg) * 64;   // back to block 0 of the next group
+            b = 0;
+            ++g;
+        }
+    } else {
         int64_t g = g0;
         int b = b_start, seg_from = b_start, left = total, s = 0;
         uint32_t ph = 0;
         bool alive = true;
-        // running pointers: this warp's first unit in ring slot s, and (M == 1) its record
-        const uint8_t* unit0 = smem + warp * UNIT;
-        const uint4* rec = reinterpret_cast<const uint4*>(smem + p.act_off) + (b_start + warp) * 4 + tig;
-        const bool odd = tig & 1, upper = tig & 2;
+        const uint8_t* unit0 = smem + warp * UNIT;   // this warp's first unit in ring slot s
         zero_acc();
         if (dbg) {  // timestamp of the first weights; the loop's own wait then passes at once
             if (!mbar_try(full0, 0)) alive = mbar_wait(full0, 0, abort_flag);
@@ -768,40 +975,21 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         while (left > 0) {
             int n = nb - b < left ? nb - b : left;
             n = n < kChunkUnits ? n : kChunkUnits;
-            if (alive && !mbar_try(full0 + 8 * s, ph)) alive = mbar_wait(full0 + 8 * s, ph, abort_flag);
-            if (alive && !(p.probe & 2)) {
-                if (ONECOL) {
-                    float v = acc[0][0][0];
-                    if (n == kChunkUnits) {
-#pragma unroll
-                        for (int j = 0; j < kUPW; ++j) {
-                            const uint8_t* un = unit0 + j * kCW * UNIT;
-                            v = unit_a8_row<BITS>(un + lane * 16, reinterpret_cast<const float*>(un + CODES) + lane,
-                                                  rec + j * kCW * 4, odd, upper, v);
-                        }
-                    } else {
-                        for (int j = 0; warp + j * kCW < n; ++j) {
-                            const uint8_t* un = unit0 + j * kCW * UNIT;
-                            v = unit_a8_row<BITS>(un + lane * 16, reinterpret_cast<const float*>(un + CODES) + lane,
-                                                  rec + j * kCW * 4, odd, upper, v);
-                        }
-                    }
-                    acc[0][0][0] = v;
-                } else {
-                    for (int j = 0; warp + j * kCW < n; ++j) {
-                        SUnit<BITS> un;
-                        lds_unit<BITS>(un, unit0 + j * kCW * UNIT, lane);
-                        const int blk = b + warp + j * kCW;
-                        if (MODE == MODE_A8) unit_a8<BITS, NT>(un, smem, p, blk, gid, tig, acc);
-                        else unit_f<BITS, NT>(un, smem, p, blk, gid, tig, acc);
-                    }
+            if (alive && !mbar_test(full0 + 8 * s, ph) && !mbar_try(full0 + 8 * s, ph))
+                alive = mbar_wait(full0 + 8 * s, ph, abort_flag);
+            if (alive && !PROBE(2)) {
+                for (int j = 0; warp + j * kCW < n; ++j) {
+                    SUnit<BITS> un;
+                    lds_unit<BITS>(un, unit0 + j * kCW * UNIT, lane);
+                    const int blk = b + warp + j * kCW;
+                    if (MODE == MODE_A8) unit_a8<BITS, NT>(un, smem, p, blk, gid, tig, acc);
+                    else unit_f<BITS, NT>(un, smem, p, blk, gid, tig, acc);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);  // also when not alive: never block the producer
             b += n;
             left -= n;
-            rec += n * 4;
             unit0 += CHUNK_BYTES;
             if (++s == NS) {
                 s = 0;
@@ -811,13 +999,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (b == nb || left == 0) {
                 flush(g, seg_from, b);
                 ++g;
-                rec -= b * 4;  // back to block 0 of the next group
                 b = 0;
                 seg_from = 0;
                 zero_acc();
             }
         }
     }
+#if RSTQ_PROBES
+    if (fine) fine[0] = (unsigned long long)nfine;
+#endif
 
     if (dbg && tid == 0) dbg[4] = gtime_ns();
     if (tid == 0 && s_abort) atomicExch(p.status, 1);
@@ -896,38 +1086,44 @@ static bool whole_groups_pay(int64_t groups, int64_t nb, int64_t k, int64_t Gw, 
     return !(Gw * 2 < sm_count && bytes_per_cta > (4ll << 20));
 }
 
-static StreamPlan plan_stream(const DeviceState& ds, int bits, int NT, int64_t groups, int64_t nb,
-                              int64_t act_bytes, int64_t act2_bytes, bool onecol = false) {
-    StreamPlan pl{};
+// How the units of a weight are cut over the CTAs of a launch: G ranges, CTA c owns uq (+1 if c < ur).
+static void split_units(const DeviceState& ds, int bits, int64_t groups, int64_t nb, int* Gout, int64_t* uq,
+                        int64_t* ur) {
     const int kChunkUnits = chunk_units_of(bits);
-    const int chunk = kChunkUnits * unit_bytes(bits);
-    // two alternating reduction buffers ([warp][lane] at M = 1, [warp][value][lane] otherwise)
-    const int64_t red = onecol ? 2 * (int64_t)kCW * 32 * 4 : 2 * (int64_t)kCW * NT * 8 * 32 * 4;
-    const int64_t a1 = (act_bytes + 127) & ~127ll, a2 = (act2_bytes + 127) & ~127ll;
-    const int64_t room = kMaxDynSmem - (a1 + a2 + red + 512);
-    int64_t ns = room / chunk;
-    if (ns > 6) ns = 6;
-    pl.fits = ns >= 2;
-    if (!pl.fits) return pl;
     const int64_t U = groups * nb;
     int64_t G = (U + kChunkUnits - 1) / kChunkUnits;  // at least one chunk of work per CTA
     if (G > ds.sm_count) G = ds.sm_count;
     if (G < 1) G = 1;
-    pl.G = (int)G;
-    pl.uq = U / G;
-    pl.ur = U % G;
-    // Whole 32-row groups per CTA: no group is shared, so the partial-sum hand-over between
-    // neighbouring CTAs (three dependent trips to L2 at the end of the kernel) disappears.  Fewer
+    *Gout = (int)G;
+    *uq = U / G;
+    *ur = U % G;
+    // Whole 32-row groups per CTA: no group is shared, nothing is handed over between CTAs.  Fewer
     // CTAs then stream more each; HBM stays the limit as long as enough SMs pull.
     const int64_t k = (groups + ds.sm_count - 1) / ds.sm_count;   // groups per CTA
     const int64_t Gw = (groups + k - 1) / k;
     bool whole = ds.gemv_plan == 2;
     if (ds.gemv_plan == 0) whole = whole_groups_pay(groups, nb, k, Gw, ds.sm_count, unit_bytes(bits));
     if (whole && groups >= 1) {
-        pl.G = (int)Gw;
-        pl.uq = k * nb;
-        pl.ur = 0;
+        *Gout = (int)Gw;
+        *uq = k * nb;
+        *ur = 0;
     }
+}
+
+static StreamPlan plan_stream(const DeviceState& ds, int bits, int NT, int64_t groups, int64_t nb,
+                              int64_t act_bytes, int64_t act2_bytes, bool onecol = false) {
+    StreamPlan pl{};
+    const int kChunkUnits = chunk_units_of(bits);
+    const int chunk = kChunkUnits * unit_bytes(bits);
+    // two alternating reduction buffers ([warp][lane] at M = 1, [warp][value][lane] otherwise)
+    const int64_t red = onecol ? (int64_t)(kParkGroups + 1) * kParkStride * 4 : 2 * (int64_t)kCW * NT * 8 * 32 * 4;
+    const int64_t a1 = (act_bytes + 127) & ~127ll, a2 = (act2_bytes + 127) & ~127ll;
+    const int64_t room = kMaxDynSmem - (a1 + a2 + red + 512);
+    int64_t ns = room / chunk;
+    if (ns > RSTQ_NSMAX) ns = RSTQ_NSMAX;
+    pl.fits = ns >= 2;
+    if (!pl.fits) return pl;
+    split_units(ds, bits, groups, nb, &pl.G, &pl.uq, &pl.ur);
     pl.NS = (int)ns;
     pl.act_off = (uint32_t)(ns * chunk);
     pl.act2_off = pl.act_off + (uint32_t)a1;
@@ -990,12 +1186,30 @@ static int32_t stream_scratch_ok(const DeviceState& ds, int64_t groups, int G, i
 
 static void fill_common(StreamParams& p, const DeviceState& ds, const StreamPlan& pl, int64_t in,
                         int64_t out, int M, int64_t nb, int zp) {
-    p.partials = ds.partials; p.flags = ds.counters; p.status = ds.status; p.dbg = ds.dbg;
+    p.partials = ds.partials; p.flags = ds.counters; p.status = ds.status;
+    // timeline: six launch slots of 160 CTA rows each, used in turn
+    p.dbg = ds.dbg ? ds.dbg + (size_t)(ds.dbg_launch++ % 6) * 160 * 8 : nullptr;
+    p.dbg_fine = ds.dbg ? ds.dbg + 6 * 160 * 8 : nullptr;
     p.in = in; p.out = out; p.uq = pl.uq; p.ur = pl.ur; p.U = ((out + 31) / 32) * nb;
     p.M = M; p.nb = (int)nb; p.G = pl.G; p.zp = zp; p.NS = pl.NS;
     p.pf_ahead = ds.gemv_prefetch_kb << 10;
     p.probe = ds.gemv_probe;
     p.act_off = pl.act_off; p.act2_off = pl.act2_off; p.red_off = pl.red_off; p.bar_off = pl.bar_off;
+}
+
+// At most this much of the next launch's weight is requested into L2 ahead of time (the head of
+// every thread block's range); larger matrices are HBM-bound anyway and must not flood the L2.
+constexpr int64_t kNextPrefetchBytes = 48ll << 20;
+
+static void fill_next(StreamParams& p, const DeviceState& ds, const NextWeight& n) {
+    p.nx_w = nullptr;
+    if (!n.data || n.groups < 1 || n.nb < 1) return;
+    p.nx_w = n.data;
+    p.nx_unit = unit_bytes(n.bits);
+    p.nx_U = n.groups * n.nb;
+    split_units(ds, n.bits, n.groups, n.nb, &p.nx_G, &p.nx_uq, &p.nx_ur);
+    const int64_t per_cta = kNextPrefetchBytes / p.nx_G / p.nx_unit;
+    p.nx_pf_units = per_cta < 1 ? 1 : per_cta;
 }
 
 template <typename K>
@@ -1066,6 +1280,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         p.y = a.y + m0 * a.out;
         p.T = 1; p.act_dtype = qf ? a.act_dtype : RSTQ_F32; p.out_dtype = RSTQ_F32;
         if (a.tp) p.tp = *a.tp;
+        if (m0 + M >= a.M) fill_next(p, ds, a.next);   // the last piece of this call: what comes next is another weight
         cudaError_t le = cudaSuccess;
 #define LAUNCH(...)                                                                  \
     le = a.tp ? launch_stream(gemv_stream_kernel<__VA_ARGS__, true>, ds, pl, p)      \
@@ -1134,6 +1349,7 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
         p.y = (char*)a.y + m0 * a.out * ye;
         p.T = T; p.act_dtype = a.act_dtype; p.out_dtype = a.out_dtype;
         if (a.tp) p.tp = *a.tp;
+        if (m0 + M >= a.M) fill_next(p, ds, a.next);   // the last piece of this call: what comes next is another weight
         cudaError_t le = cudaSuccess;
         if (a.bits == 4) {
             if (NT == 1) LAUNCH(4, 1, MODE_F, false);

@@ -5,6 +5,7 @@
 
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 #include "../../include/rstq.h"
@@ -69,6 +70,8 @@ struct DeviceState {
     int gemv_plan = 0;             // decode work split: 0 = per shape, 1 = equal unit ranges, 2 = whole groups
     int64_t gemv_prefetch_kb = 0;  // decode kernels: KB of a CTA's weight range requested into L2 ahead of its ring
     int gemv_probe = 0;            // timing probes of the decode kernel (RSTQ_TUNE_PROBE); results are invalid while set
+    bool prefetch_next = true;     // decode launches request the weight that followed this one last time into L2
+    rstq_weight* last_decode_w = nullptr;   // the weight of the most recent decode launch on this device
     bool fuse_quant = true;        // M = 1 operator: quantize the activations inside the decode kernel
     // scratch owned by the context
     void* act_scratch = nullptr;   // quantized / converted activations
@@ -95,6 +98,7 @@ struct DeviceState {
     std::vector<void*> retired;
     unsigned long long* dbg = nullptr;      // phase timestamps of the last streaming launch, when enabled
     unsigned long long* dbg_store = nullptr;
+    mutable uint64_t dbg_launch = 0;        // decode launches recorded so far (picks the timeline slot)
 };
 
 }  // namespace rstq
@@ -122,6 +126,7 @@ struct rstq_ctx {
         }
     };
     std::unordered_map<CacheKey, rstq_weight*, CacheHash> wcache;
+    std::unordered_set<const rstq_weight*> live_weights;   // handles that may be named as a prefetch target
 };
 
 struct rstq_buf {
@@ -148,6 +153,11 @@ struct rstq_weight {
     uint64_t host_fp = 0;          // fingerprint of the host arrays (host-array operators' cache)
     int8_t* raw_codes = nullptr;   // row-major signed codes / scales as the reference holds them:
     float* raw_scales = nullptr;   // made on first use by the backward-data operator
+    // The weight a decode launch of THIS one was followed by last time on the same device.  A decode
+    // loop walks its matrices in the same order for every token, so the next launch of this weight
+    // asks for that one's first bytes to be brought into L2 while its own consumers still work
+    // (a hint: a wrong guess costs bandwidth, not correctness).  Checked against live_weights.
+    rstq_weight* next_hint = nullptr;
     float* mins = nullptr;         // Q4_K only: per-sub-block minima db*bq, [out, nb]; zp is 0 then
     int64_t pair_out = 0;          // Q6_K only: logical rows; `out` = 2 * pair_out twin rows, y[o] = t[2o] + t[2o+1]
 };
@@ -207,6 +217,11 @@ struct TpFuse {
 constexpr int32_t kNotFused = 1;  // a launcher declined the fused exchange before launching anything
 
 // gemv.cu
+struct NextWeight {      // what a decode launch may prefetch for the launch expected after it
+    const uint8_t* data = nullptr;
+    int64_t groups = 0, nb = 0;
+    int bits = 0;
+};
 struct GemvA8Args {
     const uint8_t* w;
     const int8_t* xq;
@@ -218,6 +233,7 @@ struct GemvA8Args {
     const TpFuse* tp = nullptr;
     const void* x = nullptr;     // M == 1 only: raw activations (f32 or bf16), quantized by the kernel
     int act_dtype = RSTQ_F32;    // itself while staging; xq / xs / xsum are then not read
+    NextWeight next;
 };
 struct GemvFArgs {
     const uint8_t* w;
@@ -227,6 +243,7 @@ struct GemvFArgs {
     int bits, zp;
     int act_dtype, out_dtype;
     const TpFuse* tp = nullptr;
+    NextWeight next;
 };
 // gemv_stream.cu.  Any M >= 1: the launchers cut M into pieces the kernel takes.
 int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a);
