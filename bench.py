@@ -180,28 +180,16 @@ def tp_group(ctx, dist, world, rank, payload_bytes):
     return tp, region, ptrs
 
 
-def run_layer(args):
-    """--case layer70:<bits>: the three MLP projections at the 70B-class shapes (8192 <-> 28672).
-    --case layer:<bits>: the seven projections of a Llama-7B-style decoder layer at M = 1 (q, k, v,
-    o 4096x4096; gate, up 11008x4096; down 4096x11008), tensor-parallel over the ranks of the launch:
-    q, k, v, gate, up split by columns, o and down by rows (strong scaling: the layer is fixed).
-    Prints one JSON line with microseconds per layer and weight-stream GB/s."""
-    from raster_b200 import Context
+def layer_case(ctx, dist, world, rank, tp, which, bits, steps):
+    """Strong scaling: one FIXED layer sharded over the ranks of the launch.  which = "layer70": the three MLP
+    projections at the 70B-class shapes of BASELINE configs[4] (8192 <-> 28672); "layer": the seven projections
+    of a Llama-7B-style decoder layer, configs[3] (q, k, v, o 4096x4096; gate, up 11008x4096; down 4096x11008).
+    q, k, v, gate, up split by columns (outputs all-gathered), o and down by rows (partial products summed);
+    M = 1, int8-activation arithmetic.  Returns microseconds per layer (max over ranks) and GB/s."""
     from raster_b200 import _lib as L
     from raster_b200 import synth
-    bits = int(args.case.split(":")[1]) if ":" in args.case else 4
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    ctx = Context((f"cuda:{local_rank}",))
     fmt = L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0
-    if args.case.startswith("layer70"):     # the 70B-class MLP shapes of BASELINE configs[4]
+    if which == "layer70":
         H, F = 8192, 28672
         projs = [("gate", F, H, "column"), ("up", F, H, "column"), ("down", H, F, "row")]
     else:
@@ -212,9 +200,6 @@ def run_layer(args):
     L2 = ctx.device_info()["l2_bytes"]
     per_layer = sum(stream_bytes(o, i, bits) for _, o, i, _ in projs)
     layers = max(2, -(-4 * L2 // (per_layer // world)))      # distinct layers so weights come from HBM
-    tp = None
-    if world > 1:
-        tp, region, ptrs = tp_group(ctx, dist, world, rank, 4 * F)
     stack = []
     for _ in range(layers):
         lay = []
@@ -227,7 +212,7 @@ def run_layer(args):
     xs = {si: ctx.array_to_buffer(synth.normal(5, si)) for si in {p[3] for p in stack[0]}}
     ys = {out: ctx.make_buffer(out, np.float32) for out in {p[2] for p in stack[0]}}
 
-    def one_pass(_):
+    def one_pass():
         for lay in stack:
             for w, split, out, si in lay:
                 if tp is None:
@@ -235,12 +220,13 @@ def run_layer(args):
                 else:
                     tp.qmatmul(w, xs[si], ys[out], 1, L.F32, L.MODE_A8,
                                L.SPLIT_COLUMN if split == "column" else L.SPLIT_ROW)
-    one_pass(False)
+    one_pass()
+    one_pass()          # the second pass knows the order of the weights (next-weight prefetch)
     ctx.sync()
     if dist is not None:
         dist.barrier()
     ctx.graph_begin()
-    one_pass(True)
+    one_pass()
     g = ctx.graph_end()
     for _ in range(3):
         g.replay()
@@ -248,27 +234,54 @@ def run_layer(args):
     if dist is not None:
         dist.barrier()
     e0, e1 = ctx.event(), ctx.event()
-    n = max(3, args.steps)
+    n = max(3, steps)
     e0.record()
     for _ in range(n):
         g.replay()
     e1.record()
     ctx.sync()
     ms = e0.elapsed_ms(e1) / n
+    e0.destroy(), e1.destroy()
     if dist is not None:
         import torch
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
         dist.barrier()
-    if rank == 0:
-        us_layer = ms * 1e3 / layers
-        print(json.dumps({"case": args.case, "n_gpus": world, "layers_per_step": layers,
-                          "us_per_layer": round(us_layer, 2),
-                          "GBs_total": round(per_layer / us_layer / 1e3, 1),
-                          "GBs_per_gpu": round(per_layer / world / us_layer / 1e3, 1),
-                          "weight_bytes_per_layer": per_layer, "scaling": "strong"}))
     g.destroy()
+    for lay in stack:
+        for w, *_ in lay:
+            w.free()
+    for b in list(xs.values()) + list(ys.values()):
+        b.free()
+    us_layer = ms * 1e3 / layers
+    return {"n_gpus": world, "layers_per_step": layers, "us_per_layer": round(us_layer, 2),
+            "GBs_total": round(per_layer / us_layer / 1e3, 1),
+            "GBs_per_gpu": round(per_layer / world / us_layer / 1e3, 1),
+            "weight_bytes_per_layer": per_layer, "scaling": "strong"}
+
+
+def run_layer(args):
+    """--case layer70:<bits> / layer:<bits>: see layer_case; prints one JSON line."""
+    from raster_b200 import Context
+    bits = int(args.case.split(":")[1]) if ":" in args.case else 4
+    which = "layer70" if args.case.startswith("layer70") else "layer"
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = Context((f"cuda:{local_rank}",))
+    tp = None
+    if world > 1:
+        tp, region, ptrs = tp_group(ctx, dist, world, rank, 4 * 28672)
+    res = layer_case(ctx, dist, world, rank, tp, which, bits, args.steps)
+    if rank == 0:
+        print(json.dumps({"case": args.case, **res}))
     if tp is not None:
         tp.free()
         for r in range(world):
@@ -300,7 +313,7 @@ def run_tp(args, world, rank, local_rank):
         first = ctx.bind_weight(w["wqi"], w["wsi"], w["out"], w["in"], L.FMT_Q4_0, L.LAYOUT_STREAM8)
         bound.append([first] + [first.clone() for _ in range(R - 1)])
 
-    tp, region, ptrs = tp_group(ctx, dist, world, rank, 4 * max(up["out"], down["out"]))
+    tp, region, ptrs = tp_group(ctx, dist, world, rank, 4 * 28672)   # wide enough for the 70B-class layer below
 
     x_up = ctx.array_to_buffer(up["x"][: up["in"]])                 # replicated activation
     y_up = ctx.make_buffer(world * up["out"], np.float32)           # gathered columns
@@ -340,8 +353,48 @@ def run_tp(args, world, rank, local_rank):
         e0.destroy(), e1.destroy()
         return float(t.item())
 
+    # ---- correctness of the sharded operator, before anything is timed: every rank computes its own
+    # shard with the CPU oracle (column split: its rows; row split: its K-slice partial products), the
+    # per-rank results are gathered / summed over torch.distributed and compared with what the fused
+    # kernels left in y on this rank.  A checker only: nothing timed below touches it. ----
+    def tp_check():
+        from oracle import oracle as orc
+        tp.qmatmul(bound[0][R - 1], x_up, y_up, 1, L.F32, L.MODE_A8, L.SPLIT_COLUMN)
+        tp.qmatmul(bound[1][R - 1], x_dn, y_dn, 1, L.F32, L.MODE_A8, L.SPLIT_ROW)
+        barrier()
+        mine = orc.qlinear_i8(np.ascontiguousarray(up["x"][: up["in"]]), up["wqi"], up["wsi"], up["in"], up["out"], 4)
+        t = torch.from_numpy(np.asarray(mine, np.float32)).cuda()
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        ref_up = torch.cat(parts).cpu().numpy().astype(np.float64)
+        err_up = float(np.abs(y_up.download() - ref_up).max() / np.abs(ref_up).max())
+        mine = orc.qlinear_i8(np.ascontiguousarray(down["x"][: down["in"]]), down["wqi"], down["wsi"], down["in"],
+                              down["out"], 4)
+        t = torch.from_numpy(np.asarray(mine, np.float64)).cuda()
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ref_dn = t.cpu().numpy()
+        err_dn = float(np.abs(y_dn.download() - ref_dn).max() / np.abs(ref_dn).max())
+        worst = torch.tensor([max(err_up, err_dn)], device="cuda")
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        return float(worst.item()), err_up, err_dn
+
+    tp_pass(False)
+    tp_err, tp_err_up, tp_err_dn = tp_check()
+    if tp_err > 4e-6:
+        if rank == 0:
+            print(json.dumps({"error": "sharded result differs from the per-shard oracle", "n_gpus": world,
+                              "tp_check_max_rel_err": tp_err, "gather_err_rank0": tp_err_up,
+                              "reduce_err_rank0": tp_err_dn}))
+        dist.barrier()
+        dist.destroy_process_group()
+        ctx.close()
+        sys.exit(3)
+
+    n0 = ctx.launch_count()
+    tp_pass(False)
+    ctx.sync()
+    kernels_per_step = ctx.launch_count() - n0      # counted: one fused kernel (quantizer, GEMV, exchange) per matmul
     g_tp = capture(tp_pass)
-    kernels_per_step = 6 * R            # quantizer, GEMV, exchange for each of the 2 R matmuls
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -424,6 +477,17 @@ def run_tp(args, world, rank, local_rank):
         ctx.set_stream(None)
     barrier()
 
+    # ---- strong scaling (configs[3] and configs[4]): one fixed layer cut over the N ranks ----
+    strong = {}
+    for which, key in (("layer70", "strong_layer70"), ("layer", "strong_layer7b")):
+        try:
+            r = layer_case(ctx, dist, world, rank, tp, which, 4, max(3, args.steps // 4))
+            strong[key + "_us"] = r["us_per_layer"]
+            strong[key + "_GBs"] = r["GBs_total"]
+        except Exception as e:          # reported, not fatal
+            strong[key + "_error"] = repr(e)[:160]
+        barrier()
+
     # ---- e2e: x from pinned host memory every step, y back to the host ----
     hx_up = torch.from_numpy(np.ascontiguousarray(up["x"][: up["in"]])).pin_memory()
     hx_dn = torch.from_numpy(np.ascontiguousarray(down["x"][: down["in"]])).pin_memory()
@@ -500,9 +564,12 @@ def run_tp(args, world, rank, local_rank):
                        "frac_of_nominal_8TBs": round(value / world / 8000.0, 4)},
             "roofline": roofline, "e2e": e2e, "cpu_baseline": None,
             "gpu_launches": kernels_per_step * args.steps, "clocks": clocks,
-            "detail": {"no_exchange_ms_per_step": round(ms_loc, 5),
+            "detail": {"tp_check_max_rel_err": tp_err, "tp_check": "all-gathered and all-reduced y of every rank against "
+                       "the per-shard CPU oracle, before timing (bound 4e-6)",
+                       "no_exchange_ms_per_step": round(ms_loc, 5),
                        "no_exchange_GBs": round(per_pass * R * world / (ms_loc * 1e-3) / 1e9, 1),
-                       "exchange_us_per_matmul": round((ms_per_step - ms_loc) * 1e3 / (2 * R), 3), **nccl},
+                       "exchange_us_per_matmul": round((ms_per_step - ms_loc) * 1e3 / (2 * R), 3),
+                       **strong, **nccl},
         }))
     g_tp.destroy()
     tp.free()
@@ -560,8 +627,14 @@ def run_ours(args):
         return f
 
     # ---- headline: the operator (quantize + GEMV), M = 1, f32 x ------------
+    op_pass(1)(False)
+    op_pass(1)(False)                  # (the second pass knows the order of the weights: next-weight prefetch)
+    ctx.sync()
+    n0 = ctx.launch_count()
+    op_pass(1)(False)
+    ctx.sync()
+    kernels_per_step = ctx.launch_count() - n0      # counted: one kernel per call (quantizer inside the decode kernel)
     g_op = capture(op_pass(1))
-    kernels_per_step = 2 * R * len(weights)
 
     def barrier():
         if dist is not None:
@@ -660,6 +733,12 @@ def run_ours(args):
             detail.update(gemm_detail(ctx, info))
         except Exception as e:  # a detail point must not take the headline down
             detail["gemm_error"] = repr(e)[:200]
+
+        # ---- configs[4]: the 70B-class shapes, M ladder across the decode / tensor-core routing ----
+        try:
+            detail.update(c5_detail(ctx, info))
+        except Exception as e:
+            detail["c5_error"] = repr(e)[:200]
 
         # ---- the caller of the path: one token through a whole decoder layer (own context, freed after) ----
         try:
@@ -760,6 +839,46 @@ def gemm_detail(ctx, info, M=512, K=4096, N=4096):
     out = {"gemm_int8_M512_K4096_N4096_bf16_us": round(us, 2), "gemm_int8_M512_K4096_N4096_bf16_TFLOPs": round(tf, 1)}
     if peak:
         out["gemm_frac_of_measured_bf16_peak"] = round(tf / peak, 4)
+    return out
+
+
+def c5_detail(ctx, info, steps=3):
+    """BASELINE configs[4] on one GPU: int4 W 8192x28672 and 28672x8192 (random codes, scales of the
+    N(0, 0.015) magnitude), bf16 activations N(0, 1), M in {1, 16, 64, 256}; f32 output for M <= 16, bf16
+    above (the prefill path).  Distinct weight copies, more than L2 in total, replayed from one graph."""
+    from raster_b200 import _lib as L
+    from raster_b200 import synth
+    out = {}
+    rng = np.random.default_rng(5)
+    for name, N, K in (("8192to28672", 28672, 8192), ("28672to8192", 8192, 28672)):
+        codes = rng.integers(0, 256, N * K // 2, dtype=np.uint8)
+        scales = (np.abs(rng.standard_normal(N * (K // 32))) * 0.006 + 1e-4).astype(np.float32)
+        first = ctx.bind_weight(codes, scales, N, K, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+        R = max(2, -(-int(1.2 * info["l2_bytes"]) // first.stream_bytes))
+        ws = [first] + [first.clone() for _ in range(R - 1)]
+        for M in (1, 16, 64, 256):
+            x = ctx.array_to_buffer(synth.to_bf16_bits(synth.normal(90 + M, M * K)))
+            odt = L.F32 if M <= 16 else L.BF16
+            y = ctx.make_buffer(M * N, np.float32 if M <= 16 else np.uint16)
+
+            def fn():
+                for w in ws:
+                    ctx.qmatmul(w, x, y, M, L.BF16, odt, L.MODE_F)
+            fn()
+            fn()
+            ctx.sync()
+            ctx.graph_begin()
+            fn()
+            g = ctx.graph_end()
+            us = time_graph(ctx, g, steps, 2) * 1e3 / steps / R
+            g.destroy()
+            out[f"c5_{name}_M{M}_us"] = round(us, 2)
+            out[f"c5_{name}_M{M}_GBs"] = round(first.stream_bytes / us / 1e3, 1)
+            if M >= 64:
+                out[f"c5_{name}_M{M}_TFLOPs"] = round(2.0 * M * N * K / us / 1e6, 1)
+            x.free(), y.free()
+        for w in ws:
+            w.free()
     return out
 
 

@@ -224,12 +224,15 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
     // quantized-activation arithmetic get it bit-faithfully at decode and small-batch sizes.
     bool tc = M >= (mode == RSTQ_MODE_A8 ? (ctx->tune_gemm_min_m > 64 ? ctx->tune_gemm_min_m : 64)
                                           : ctx->tune_gemm_min_m);
-    // MODE_F, 9 .. 16 tokens of long rows: the decode kernel keeps every token's activations in
-    // shared memory and would have to cut M into several launches, each streaming all the
-    // weights again (3 - 5 x slower than the tensor-core path, measured at K = 8192 and 28672).
-    if (mode == RSTQ_MODE_F && !tc && M >= 9 && ctx->tune_gemm_min_m == 17 &&
-        w->in * 2 * M * (act_dtype == RSTQ_F32 ? 2 : 1) > 96 * 1024)
-        tc = true;
+    // MODE_F below the threshold: the decode kernel keeps every token's activations (for f32, two or
+    // three bf16 terms each) in shared memory beside the weight ring; what does not fit is cut into
+    // several launches, each streaming all the weights again.  Measured at the Llama-7B shapes, M = 1 .. 16:
+    // two launches of f32 (three of bf16) activations already cost more than the tensor-core path.
+    // (Matrices of a few MB stay on the decode kernel and keep its f32-grade result.)
+    if (mode == RSTQ_MODE_F && !tc && M >= 2 && ctx->tune_gemm_min_m == 17 && w->data_bytes >= (4ll << 20)) {
+        const int pieces = gemv_f_pieces(ds, w->bits, w->out, w->in, M, act_dtype);
+        if (pieces >= (act_dtype == RSTQ_F32 ? 2 : 3)) tc = true;
+    }
     // The same for MODE_A8 when not even 8 tokens of codes fit (K > 16 K): the codes and scales the
     // quantizer produced feed the tensor-core path instead (<= 1e-3, no longer the exact integer dots).
     if (mode == RSTQ_MODE_A8 && !tc && M >= 9 && ctx->tune_gemm_min_m == 17 && w->in * 8 > 128 * 1024) tc = true;
@@ -237,7 +240,7 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
     if (mode == RSTQ_MODE_A8) {
         RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "unknown activation type");
         RSTQ_REQUIRE(out_dtype == RSTQ_F32 || tc, RSTQ_E_INVALID, "MODE_A8 decode writes f32");
-        if (M == 1 && !tc && ds.fuse_quant && w->in <= kFusedQuantMaxIn) {
+        if (M == 1 && !tc && ds.fuse_quant && !ds.x_on_host && w->in <= kFusedQuantMaxIn) {
             // one token: every CTA of the decode kernel quantizes x (16 - 112 KB, in L2) while it
             // stages it, bit for bit as the quantizer kernel would -- one launch, no scratch
             GemvA8Args a{w->data, nullptr, nullptr, nullptr, (float*)y, 1, w->in, w->out, w->bits, w->zp, tp, x, act_dtype};
@@ -1018,7 +1021,7 @@ static int32_t cached_weight(rstq_ctx* ctx, const void* codes, const float* scal
 extern "C++" {
 template <typename Body>
 int32_t host_roundtrip(rstq_ctx* ctx, int dev, const void* x, int64_t x_bytes, void* y,
-                              int64_t y_bytes, Body body, bool y_write_only = false) {
+                              int64_t y_bytes, Body body, bool y_write_only = false, bool x_read_once = false) {
     DeviceState& ds = ctx->devs[dev];
     RSTQ_REQUIRE(!ds.capturing, RSTQ_E_STATE, "host-array operators cannot be captured");
     int32_t rc = use_dev(ctx, dev);
@@ -1030,13 +1033,18 @@ int32_t host_roundtrip(rstq_ctx* ctx, int dev, const void* x, int64_t x_bytes, v
     char* dp = (char*)ds.io_dev;
     memcpy(hp, x, (size_t)x_bytes);
     // Small activations are read by the first kernel straight from the pinned host copy (unified
-    // addressing makes it device-visible): one PCIe round trip instead of a copy engine launch.
-    const bool direct = x_bytes <= 256 * 1024;
+    // addressing makes it device-visible): one PCIe round trip instead of a copy engine launch.  Only
+    // where that kernel reads x once (the activation quantizer): the decode kernels stage x in every
+    // thread block, which would cross PCIe a hundred times over.
+    const bool direct = x_read_once && x_bytes <= 256 * 1024;
+    ds.x_on_host = direct;
     if (!direct) RSTQ_CUDA(cudaMemcpyAsync(dp, hp, (size_t)x_bytes, cudaMemcpyHostToDevice, ds.stream));
     // A small result the kernels only write goes straight to the pinned host copy too (posted
     // PCIe writes during the kernel instead of a copy-engine launch after it).
     const bool y_direct = y_write_only && y_bytes <= 64 * 1024;
-    if ((rc = body(direct ? (void*)hp : (void*)dp, y_direct ? (void*)(hp + xa) : (void*)(dp + xa))) != RSTQ_OK) return rc;
+    rc = body(direct ? (void*)hp : (void*)dp, y_direct ? (void*)(hp + xa) : (void*)(dp + xa));
+    ds.x_on_host = false;
+    if (rc != RSTQ_OK) return rc;
     if (!y_direct)
         RSTQ_CUDA(cudaMemcpyAsync(hp + xa, dp + xa, (size_t)y_bytes, cudaMemcpyDeviceToHost, ds.stream));
     RSTQ_CUDA(cudaStreamSynchronize(ds.stream));
@@ -1057,7 +1065,7 @@ static int32_t qlinear_i8_impl(rstq_ctx* ctx, const float* x, const void* wqi, c
     if (rc != RSTQ_OK) return rc;
     return host_roundtrip(ctx, w->dev, x, in * 4, y, out * 4, [&](void* dx, void* dy) {
         return matmul_device(ctx, w, dx, dy, 1, RSTQ_F32, RSTQ_F32, RSTQ_MODE_A8);
-    }, true);  // M = 1: the decode kernel stores each result once and never reads y
+    }, true, true);  // M = 1: the decode kernel stores each result once and never reads y; the quantizer reads x once
 }
 
 int32_t rstq_qlinear_i8(rstq_ctx* ctx, const float* x, const void* wqi, const float* wsi, float* y,

@@ -47,7 +47,11 @@
 
 namespace rstq {
 
-constexpr int kCW = 16;                          // consumer warps
+#ifndef RSTQ_CW
+#define RSTQ_CW 16
+#endif
+constexpr int kCW = RSTQ_CW;                     // consumer warps (16, 24 or 32: the cross-warp sums fold warps 16.. onto 0..15)
+static_assert(kCW >= 16 && kCW <= 32, "the M = 1 reduction reads two partial sums per thread");
 constexpr int kConsumers = kCW * 32;
 constexpr int kStreamThreads = kConsumers + 32;  // + producer warp
 // units per consumer warp per chunk: 4 (40 KB chunks) for 4-bit, 2 (36 KB chunks) for 8-bit
@@ -64,7 +68,7 @@ constexpr int kMaxDynSmem = 232448 - 1024;       // 227 KB opt-in limit less the
 constexpr int kQuantPasses = 3;
 constexpr int kQuantMaxIn = kQuantPasses * kConsumers * 8;
 static_assert(kGemvMaxM * 32 <= kConsumers, "one output per consumer thread in the hand-over");
-static_assert(kQuantMaxIn == kFusedQuantMaxIn, "the host routes by kFusedQuantMaxIn");
+static_assert(kQuantMaxIn >= kFusedQuantMaxIn, "the host routes by kFusedQuantMaxIn");
 // M = 1: the per-warp partial sums of whole groups are parked in shared memory (kParkStride floats per
 // group: [warp][33]) and reduced across warps once per kParkGroups groups, not once per group
 constexpr int kParkGroups = 8;
@@ -275,38 +279,50 @@ __device__ __forceinline__ void stage_a8_quant(const StreamParams& p, uint8_t* s
         for (int k = 0; k < 8; ++k) mx = fmaxf(mx, fabsf(f[k]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        int q[8];
+        // f32 shortcut: u = fma(x, 127 / max, 1.5 * 2^23) holds round-to-nearest(x * 127 / max) in its low
+        // mantissa bits (two's complement in the low byte); the quotient is 2 ulp accurate, so the
+        // product is within 4e-5 of the double one and every element whose remainder is further than
+        // 2e-4 from a tie rounds exactly as round_half_up of the double product does.
+        uint32_t wa, wb;
+        int sum;
         float xs = 0.f;
         bool exact = !(mx >= 1e-30f && mx <= 1e37f);
         if (!exact) {
-            const float idf = __fdiv_rn(127.f, mx);
+            const float idf = __fdividef(127.f, mx);
             xs = __fdiv_rn(mx, 127.f);
+            uint32_t ub[8];
+            float amb = 0.f;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                const float t = f[k] * idf, fl = floorf(t);
-                exact = exact || fabsf(t - fl - 0.5f) < 1e-3f;
-                q[k] = (int)floorf(t + 0.5f);
+                const float u = fmaf(f[k], idf, kMagicFlt);
+                const float frac = fmaf(f[k], idf, kMagicFlt - u);   // x * idf - n, n = u - magic exactly
+                amb = fmaxf(amb, fabsf(frac));
+                ub[k] = __float_as_uint(u);
             }
+            exact = amb > 0.5f - 2e-4f;
+            wa = __byte_perm(__byte_perm(ub[0], ub[1], 0x0040), __byte_perm(ub[2], ub[3], 0x0040), 0x5410);
+            wb = __byte_perm(__byte_perm(ub[4], ub[5], 0x0040), __byte_perm(ub[6], ub[7], 0x0040), 0x5410);
         }
         if (exact) {
             const double d = (double)mx / 127.0;
             const double id = d == 0.0 ? 0.0 : 1.0 / d;
             xs = (float)d;
+            int q[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) q[k] = quant_exact(f[k], id);
+            wa = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) |
+                 ((uint32_t)(q[3] & 0xFF) << 24);
+            wb = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) |
+                 ((uint32_t)(q[7] & 0xFF) << 24);
         }
-        int sum = 0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) sum += q[k];
+        sum = __dp4a((int)wa, 0x01010101, __dp4a((int)wb, 0x01010101, 0));
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         if (act) {
             const bool hi = BITS == 4 && (i & 1);
             uint4 r;
-            r.x = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) |
-                  ((uint32_t)(q[3] & 0xFF) << 24);
-            r.y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) |
-                  ((uint32_t)(q[7] & 0xFF) << 24);
+            r.x = wa;
+            r.y = wb;
             r.z = __float_as_uint(hi ? xs * 0.0625f : xs);
             r.w = (uint32_t)(kMagicInt - (p.zp * sum) * (hi ? 16 : 1) + (hi ? 1 : 0));
             srec[i] = r;
@@ -818,12 +834,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             // (whole groups are parked by the loop and reduced in batches; this serves the cut ones)
             rbuf[warp * 33 + lane] = acc[0][0][0];  // row gid + 8*tig of this lane (33: the 16 readers of a row hit 16 banks)
             consumer_bar();
-            // thread t: row t >> 4, warp t & 15; 16 neighbouring lanes add up one row
-            const int row = tid >> 4;
-            float sum = rbuf[(tid & 15) * 33 + (row & 7) * 4 + (row >> 3)];
+            // thread t < 512: row t >> 4, warps t & 15 (and 16 + that); 16 neighbouring lanes add up one row
+            const int row = (tid >> 4) & 31, wsrc = tid & 15;
+            float sum = rbuf[wsrc * 33 + (row & 7) * 4 + (row >> 3)];
+            if (wsrc + 16 < kCW) sum += rbuf[(wsrc + 16) * 33 + (row & 7) * 4 + (row >> 3)];
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            const bool owner = (tid & 15) == 0;
+            const bool owner = (tid & 15) == 0 && tid < 512;
             if (whole) {
                 if (owner && row0 + row < p.out) emit(row0 + row, sum);
             } else if (!head) {
@@ -861,14 +878,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     // M = 1: reduce the parked groups [g_first, g_first + count) across the warps and store them
     auto flush_parked = [&](int64_t g_first, int count, bool more) {
         consumer_bar();
-        const int row = tid >> 4;
-        const int src = (tid & 15) * 33 + (row & 7) * 4 + (row >> 3);
+        const int row = (tid >> 4) & 31, wsrc = tid & 15;
+        const int src = wsrc * 33 + (row & 7) * 4 + (row >> 3);
         for (int i = 0; i < count; ++i) {
             float sum = red[i * kParkStride + src];
+            if (wsrc + 16 < kCW) sum += red[i * kParkStride + src + 16 * 33];
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             const int64_t r = (g_first + i) * 32 + row;
-            if ((tid & 15) == 0 && r < p.out) emit(r, sum);
+            if ((tid & 15) == 0 && tid < 512 && r < p.out) emit(r, sum);
         }
         if (more) consumer_bar();   // the slots are written again
     };
@@ -891,6 +909,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         bool alive = true;
         int64_t g = g0, g_parked = g0;
         int parked = 0;
+#if RSTQ_PROBES
+        long long waited = 0, ck[5] = {0, 0, 0, 0, 0}, ckt = 0;
+        const long long loop0 = clock64();
+#define CK_START() ckt = clock64()
+#define CK_ADD(i) do { const long long t__ = clock64(); ck[i] += t__ - ckt; ckt = t__; } while (0)
+#else
+#define CK_START()
+#define CK_ADD(i)
+#endif
         if (dbg) {  // timestamp of the first weights; the loop's own wait then passes at once
             if (!mbar_try(full0, 0)) alive = mbar_wait(full0, 0, abort_flag);
             if (tid == 0) dbg[3] = gtime_ns();
@@ -904,10 +931,18 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             for (int done = 0; done < seg;) {
                 const int n = seg - done < kChunkUnits ? seg - done : kChunkUnits;
                 const uint32_t bar = full0 + 8 * s;
+#if RSTQ_PROBES
+                const long long w0 = clock64();
+#endif
                 if (alive && !ready && !mbar_try(bar, ph)) alive = mbar_wait(bar, ph, abort_flag);
+#if RSTQ_PROBES
+                waited += clock64() - w0;
+#endif
                 stamp();
+                CK_START();
                 const int sn = s + 1 == NS ? 0 : s + 1;
                 ready = mbar_test(full0 + 8 * sn, sn ? ph : ph ^ 1u);
+                CK_ADD(0);
                 if (alive && !PROBE(2)) {
                     if (n == kChunkUnits) {
                         RowUnit<BITS> u[kUPW];
@@ -923,10 +958,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                         }
                     }
                 }
+                CK_ADD(1);
                 __syncwarp();
                 stamp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);  // also when not alive: never block the producer
                 stamp();
+                CK_ADD(2);
                 done += n;
                 rec += n * 64;
                 if (sn) {
@@ -938,8 +975,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     ph ^= 1u;
                 }
                 s = sn;
+                CK_ADD(3);
             }
             left -= seg;
+            CK_START();
             if (b == 0 && seg == nb) {
                 // a whole group: park this warp's sums, no barrier
                 if (parked == 0) g_parked = g;
@@ -957,10 +996,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 }
             }
             stamp();
+            CK_ADD(4);
             rec -= (b + seg) * 64;   // back to block 0 of the next group
             b = 0;
             ++g;
         }
+#if RSTQ_PROBES
+        if (dbg && tid == 0) dbg[7] = ((unsigned long long)(clock64() - loop0) << 32) | (unsigned long long)(waited & 0xFFFFFFFF);
+        if (p.dbg && blockIdx.x == 0 && tid == 0)
+            for (int i = 0; i < 5; ++i) p.dbg_fine[300 + i] = (unsigned long long)ck[i];
+#endif
     } else {
         int64_t g = g0;
         int b = b_start, seg_from = b_start, left = total, s = 0;
@@ -1308,6 +1353,33 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         m0 += M;
     }
     return RSTQ_OK;
+}
+
+// How many launches launch_gemv_f would make for M tokens (each streams all the weights again).
+int gemv_f_pieces(const DeviceState& ds, int bits, int64_t out, int64_t in, int64_t M, int act_dtype) {
+    const int64_t nb = in / 32, groups = (out + 31) / 32;
+    int max_terms = 3;
+    auto terms = [&](int m) { return act_dtype == RSTQ_F32 ? ((3 * m <= 8 && max_terms == 3) ? 3 : 2) : 1; };
+    auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
+        const int C = m * terms(m);
+        *NT = C <= 8 ? 1 : (C <= 16 ? 2 : 4);
+        *a1 = nb * 2 * C * 32;
+        *a2 = 0;
+    };
+    int pieces = 0;
+    for (int64_t m0 = 0; m0 < M;) {
+        const int want = (int)(M - m0 < kGemvMaxM ? M - m0 : kGemvMaxM);
+        StreamPlan pl;
+        int m = fit_tokens(ds, bits, groups, nb, want, bytes, &pl);
+        if (m < 1 && max_terms == 3) {
+            max_terms = 2;
+            m = fit_tokens(ds, bits, groups, nb, want, bytes, &pl);
+        }
+        if (m < 1) return 1 << 20;
+        m0 += m;
+        ++pieces;
+    }
+    return pieces;
 }
 
 int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {

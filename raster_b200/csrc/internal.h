@@ -72,6 +72,7 @@ struct DeviceState {
     int gemv_probe = 0;            // timing probes of the decode kernel (RSTQ_TUNE_PROBE); results are invalid while set
     bool prefetch_next = true;     // decode launches request the weight that followed this one last time into L2
     rstq_weight* last_decode_w = nullptr;   // the weight of the most recent decode launch on this device
+    bool x_on_host = false;        // the current host-array call lets its first kernel read x from pinned host memory
     bool fuse_quant = true;        // M = 1 operator: quantize the activations inside the decode kernel
     // scratch owned by the context
     void* act_scratch = nullptr;   // quantized / converted activations
@@ -248,6 +249,7 @@ struct GemvFArgs {
 // gemv_stream.cu.  Any M >= 1: the launchers cut M into pieces the kernel takes.
 int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a);
 int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a);
+int gemv_f_pieces(const DeviceState& ds, int bits, int64_t out, int64_t in, int64_t M, int act_dtype);
 int32_t gemv_configure(DeviceState& ds);  // shared-memory attributes, once per device
 // gemm_tc.cu
 int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const void* x, const float* xs,
