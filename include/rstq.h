@@ -119,18 +119,18 @@ RSTQ_API int32_t rstq_device_count(int32_t* count);
  *      src/raster/gpu/core.clj:243-293 and src/raster/gpu/ocl_runtime.clj:205-215.
  * `devices` lists CUDA ordinals; later calls name a device by its index in
  * that list (device index 0 = devices[0]). ------------------------------- */
-RSTQ_API int32_t rstq_init(const int32_t* devices, int32_t ndev, rstq_ctx** ctx);
+RSTQ_API int32_t rstq_init(const int32_t* devices, rstq_ctx** ctx, int32_t ndev);
 RSTQ_API int32_t rstq_shutdown(rstq_ctx* ctx);
 RSTQ_API int32_t rstq_sync(rstq_ctx* ctx, int32_t dev);
 RSTQ_API int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value);
 /* out[0] = SM count, out[1] = L2 bytes, out[2] = total device memory, out[3] = cc major*10+minor */
-RSTQ_API int32_t rstq_device_info(rstq_ctx* ctx, int32_t dev, int64_t* out4);
+RSTQ_API int32_t rstq_device_info(rstq_ctx* ctx, int64_t* out4, int32_t dev);
 /* Phase timestamps (ns, device global timer) of the streaming decode launches made since
  * RSTQ_TUNE_TIMELINE was set to 1: six slots of 160 rows used in turn (launch k writes slot k % 6),
  * a row of 8 values per CTA: [0] entry, [1] consumers start (the preceding kernel has finished),
  * [2] activations staged, [3] first weights landed, [4] main loop done, [5] exit, [6] SM id.
  * Rows of CTAs a launch did not have read as zero. */
-RSTQ_API int32_t rstq_timeline_read(rstq_ctx* ctx, int32_t dev, int64_t* out, int64_t n);
+RSTQ_API int32_t rstq_timeline_read(rstq_ctx* ctx, int64_t* out, int32_t dev, int64_t n);
 
 /* ---- device buffers: make-buffer / array->buffer! / buffer->array /
  *      free-buffer! of src/raster/gpu/ocl_runtime.clj:405-499. ----------- */
@@ -143,13 +143,12 @@ RSTQ_API int32_t rstq_buf_ptr(rstq_buf* buf, void** device_ptr, int64_t* bytes);
 /* A buffer handle over device memory the caller allocated (a runtime's own arena, a tensor of
  * another library); rstq_free releases the handle only.  The reference's counterpart is
  * buffer-of-array (src/raster/gpu/ocl_runtime.clj:452-499), which wraps an existing segment. */
-RSTQ_API int32_t rstq_buf_wrap(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, void* device_ptr,
-                               int64_t bytes);
+RSTQ_API int32_t rstq_buf_wrap(rstq_ctx* ctx, rstq_buf** buf, void* device_ptr, int32_t dev, int64_t bytes);
 /* Launch on a CUDA stream of the caller (cudaStream_t) instead of the context's own, so that the
  * operators order with the caller's other work without events; NULL returns to the own stream.
  * Plays the part of *current-arena* (src/raster/gpu/ocl_runtime.clj:222-224): the queue every
  * launch of the session goes to. */
-RSTQ_API int32_t rstq_stream_set(rstq_ctx* ctx, int32_t dev, void* stream);
+RSTQ_API int32_t rstq_stream_set(rstq_ctx* ctx, void* stream, int32_t dev);
 
 /* ---- weights: the one-time host->device bind.  Replaces repack-stream
  *      (src/raster/compiler/backend/cpu/quant.clj:317-326) as the load-time
@@ -318,10 +317,10 @@ RSTQ_API int32_t rstq_residual_add(rstq_ctx* ctx, rstq_buf* a, rstq_buf* b, rstq
  * posbuf / clenbuf: NULL, or a device buffer holding one int64 that the kernel reads (the -buf
  * variants: a captured graph then serves every token; call once before capturing).  The
  * reference's score scratch `sc` has no counterpart (scores stay in registers).  All f32. */
-RSTQ_API int32_t rstq_rope_pos(rstq_ctx* ctx, rstq_buf* x, rstq_buf* out, int64_t heads, int64_t head_dim,
-                               double theta, int64_t pos, rstq_buf* posbuf);
-RSTQ_API int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, int64_t kvrow, int64_t pos,
-                                int64_t maxpos, rstq_buf* posbuf);
+RSTQ_API int32_t rstq_rope_pos(rstq_ctx* ctx, rstq_buf* x, rstq_buf* out, rstq_buf* posbuf, int64_t heads,
+                               int64_t head_dim, double theta, int64_t pos);
+RSTQ_API int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, rstq_buf* posbuf, int64_t kvrow,
+                                int64_t pos, int64_t maxpos);
 /* Fusions the chain invites (no counterpart in the reference; each equals its steps run one by one,
  * bit for bit):
  *   rstq_rope_append                  rope of q and k in place + append of the turned k and of v to
@@ -335,12 +334,12 @@ RSTQ_API int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, i
  * rstq_qmatmul_prequant.  head_dim 64 or 128; xsum may be NULL. */
 RSTQ_API int32_t rstq_gqa_decode_attention_quant_act(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v,
                                                      rstq_buf* out, rstq_buf* xq, rstq_buf* xs, rstq_buf* xsum,
-                                                     int64_t cache_len, rstq_buf* clenbuf, int64_t n_q,
-                                                     int64_t group, int64_t n_kv, int64_t head_dim, int64_t maxpos,
-                                                     double scale);
+                                                     rstq_buf* clenbuf, int64_t cache_len, int64_t n_q,
+                                                     int64_t group, int64_t n_kv, int64_t head_dim,
+                                                     int64_t maxpos, double scale);
 RSTQ_API int32_t rstq_rope_append(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* kcache,
-                                  rstq_buf* vcache, int64_t n_q, int64_t n_kv, int64_t head_dim, double theta,
-                                  int64_t pos, int64_t maxpos, rstq_buf* posbuf);
+                                  rstq_buf* vcache, rstq_buf* posbuf, int64_t n_q, int64_t n_kv,
+                                  int64_t head_dim, double theta, int64_t pos, int64_t maxpos);
 RSTQ_API int32_t rstq_residual_rms_norm_quant_act(rstq_ctx* ctx, rstq_buf* a, rstq_buf* b, rstq_buf* sum,
                                                   rstq_buf* weight, rstq_buf* xq, rstq_buf* xs, rstq_buf* xsum,
                                                   int64_t rows, int64_t features, double eps, double gain_offset);
@@ -349,7 +348,7 @@ RSTQ_API int32_t rstq_silu_mul_quant_act(rstq_ctx* ctx, rstq_buf* gate, rstq_buf
 RSTQ_API int32_t rstq_gelu_mul_quant_act(rstq_ctx* ctx, rstq_buf* gate, rstq_buf* up, rstq_buf* xq, rstq_buf* xs,
                                          rstq_buf* xsum, int64_t n);
 RSTQ_API int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
-                                           int64_t cache_len, rstq_buf* clenbuf, int64_t n_q, int64_t group,
+                                           rstq_buf* clenbuf, int64_t cache_len, int64_t n_q, int64_t group,
                                            int64_t n_kv, int64_t head_dim, int64_t maxpos, double scale);
 
 /* ---- tensor-parallel exchange of the sharded operator.  No counterpart in the reference: it
@@ -364,11 +363,11 @@ RSTQ_API int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf*
 typedef struct rstq_tp rstq_tp;
 #define RSTQ_TP_MAX_RANKS 8
 RSTQ_API int64_t rstq_tp_region_bytes(int32_t nranks, int64_t max_payload_bytes); /* 0 = bad arguments */
-RSTQ_API int32_t rstq_tp_attach(rstq_ctx* ctx, int32_t dev, int32_t rank, int32_t nranks,
-                                void* const* regions, int64_t region_bytes, rstq_tp** tp);
+RSTQ_API int32_t rstq_tp_attach(rstq_ctx* ctx, void* const* regions, rstq_tp** tp, int32_t dev, int32_t rank,
+                                int32_t nranks, int64_t region_bytes);
 /* one process, nranks devices of ctx (devs = device indexes of the context): tps[nranks] */
-RSTQ_API int32_t rstq_tp_create_local(rstq_ctx* ctx, int32_t nranks, const int32_t* devs,
-                                      int64_t max_payload_bytes, rstq_tp** tps);
+RSTQ_API int32_t rstq_tp_create_local(rstq_ctx* ctx, const int32_t* devs, rstq_tp** tps, int32_t nranks,
+                                      int64_t max_payload_bytes);
 /* dst[row][rank][row_bytes] = src of rank `rank` [row][row_bytes]; row_bytes % 16 == 0 */
 RSTQ_API int32_t rstq_tp_allgather(rstq_tp* tp, rstq_buf* src, rstq_buf* dst, int64_t rows,
                                    int64_t row_bytes);
@@ -384,8 +383,8 @@ RSTQ_API int32_t rstq_tp_free(rstq_tp* tp);
  * to the other processes of the box by any channel, and map theirs.  The mapped address goes
  * into the `regions` array of rstq_tp_attach. */
 RSTQ_API int32_t rstq_ipc_export(rstq_buf* buf, void* handle64);
-RSTQ_API int32_t rstq_ipc_open(rstq_ctx* ctx, int32_t dev, const void* handle64, void** device_ptr);
-RSTQ_API int32_t rstq_ipc_close(rstq_ctx* ctx, int32_t dev, void* device_ptr);
+RSTQ_API int32_t rstq_ipc_open(rstq_ctx* ctx, const void* handle64, void** device_ptr, int32_t dev);
+RSTQ_API int32_t rstq_ipc_close(rstq_ctx* ctx, void* device_ptr, int32_t dev);
 
 #ifdef __cplusplus
 }

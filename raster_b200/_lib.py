@@ -18,20 +18,20 @@ SIGNATURES = {
     "rstq_version": [],
     "rstq_last_error": [],
     "rstq_device_count": [C.POINTER(i32)],
-    "rstq_init": [C.POINTER(i32), i32, pp],
+    "rstq_init": [C.POINTER(i32), pp, i32],
     "rstq_shutdown": [vp],
     "rstq_sync": [vp, i32],
     "rstq_tune": [vp, i32, i64],
-    "rstq_device_info": [vp, i32, C.POINTER(i64)],
-    "rstq_timeline_read": [vp, i32, C.POINTER(i64), i64],
+    "rstq_device_info": [vp, C.POINTER(i64), i32],
+    "rstq_timeline_read": [vp, C.POINTER(i64), i32, i64],
     "rstq_alloc": [vp, pp, i32, i64],
     "rstq_free": [vp],
     "rstq_upload": [vp, vp, i64, i64],
     "rstq_download": [vp, vp, i64, i64],
     "rstq_memset": [vp, i32, i64, i64],
     "rstq_buf_ptr": [vp, pp, C.POINTER(i64)],
-    "rstq_buf_wrap": [vp, pp, i32, vp, i64],
-    "rstq_stream_set": [vp, i32, vp],
+    "rstq_buf_wrap": [vp, pp, vp, i32, i64],
+    "rstq_stream_set": [vp, vp, i32],
     "rstq_weight_bind": [vp, pp, vp, vp, i32, i64, i64, i32, i32],
     "rstq_weight_bind_shard": [vp, pp, vp, vp, i32, i64, i64, i32, i32, i32, i32, i32],
     "rstq_weight_bind_q4k": [vp, pp, vp, vp, vp, vp, vp, i32, i64, i64],
@@ -67,24 +67,24 @@ SIGNATURES = {
     "rstq_silu_mul": [vp, vp, vp, vp, i64],
     "rstq_gelu_mul": [vp, vp, vp, vp, i64],
     "rstq_residual_add": [vp, vp, vp, vp, i64],
-    "rstq_rope_pos": [vp, vp, vp, i64, i64, C.c_double, i64, vp],
-    "rstq_gqa_decode_attention_quant_act": [vp, vp, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, C.c_double],
-    "rstq_rope_append": [vp, vp, vp, vp, vp, vp, i64, i64, i64, C.c_double, i64, i64, vp],
+    "rstq_rope_pos": [vp, vp, vp, vp, i64, i64, C.c_double, i64],
+    "rstq_gqa_decode_attention_quant_act": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, C.c_double],
+    "rstq_rope_append": [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, C.c_double, i64, i64],
     "rstq_residual_rms_norm_quant_act": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, C.c_double, C.c_double],
     "rstq_silu_mul_quant_act": [vp, vp, vp, vp, vp, vp, i64],
     "rstq_gelu_mul_quant_act": [vp, vp, vp, vp, vp, vp, i64],
-    "rstq_kv_append": [vp, vp, vp, i64, i64, i64, vp],
-    "rstq_gqa_decode_attention": [vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, C.c_double],
+    "rstq_kv_append": [vp, vp, vp, vp, i64, i64, i64],
+    "rstq_gqa_decode_attention": [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, C.c_double],
     "rstq_tp_region_bytes": [i32, i64],
-    "rstq_tp_attach": [vp, i32, i32, i32, pp, i64, pp],
-    "rstq_tp_create_local": [vp, i32, C.POINTER(i32), i64, pp],
+    "rstq_tp_attach": [vp, pp, pp, i32, i32, i32, i64],
+    "rstq_tp_create_local": [vp, C.POINTER(i32), pp, i32, i64],
     "rstq_tp_allgather": [vp, vp, vp, i64, i64],
     "rstq_tp_allreduce_f32": [vp, vp, vp, i64],
     "rstq_tp_qmatmul": [vp, vp, vp, vp, i64, i32, i32, i32],
     "rstq_tp_free": [vp],
     "rstq_ipc_export": [vp, vp],
-    "rstq_ipc_open": [vp, i32, vp, pp],
-    "rstq_ipc_close": [vp, i32, vp],
+    "rstq_ipc_open": [vp, vp, pp, i32],
+    "rstq_ipc_close": [vp, vp, i32],
 }
 _RESTYPE = {"rstq_last_error": C.c_char_p, "rstq_tp_region_bytes": i64}
 

@@ -477,8 +477,8 @@ static bool attn_buf(const rstq_buf* b, const rstq_ctx* ctx, int64_t bytes) {
 
 extern "C" {
 
-int32_t rstq_rope_pos(rstq_ctx* ctx, rstq_buf* x, rstq_buf* out, int64_t heads, int64_t head_dim, double theta,
-                      int64_t pos, rstq_buf* posbuf) {
+int32_t rstq_rope_pos(rstq_ctx* ctx, rstq_buf* x, rstq_buf* out, rstq_buf* posbuf, int64_t heads,
+                      int64_t head_dim, double theta, int64_t pos) {
     RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
     RSTQ_REQUIRE(heads >= 1 && head_dim >= 2 && head_dim % 2 == 0 && theta > 0.0 && (posbuf || pos >= 0), RSTQ_E_SHAPE,
                  "heads = %lld, head_dim = %lld (even), theta = %g, pos = %lld", (long long)heads,
@@ -499,8 +499,8 @@ int32_t rstq_rope_pos(rstq_ctx* ctx, rstq_buf* x, rstq_buf* out, int64_t heads, 
     return RSTQ_OK;
 }
 
-int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, int64_t kvrow, int64_t pos, int64_t maxpos,
-                       rstq_buf* posbuf) {
+int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, rstq_buf* posbuf, int64_t kvrow,
+                       int64_t pos, int64_t maxpos) {
     RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
     RSTQ_REQUIRE(kvrow >= 1 && maxpos >= 1 && (posbuf || (pos >= 0 && pos < maxpos)), RSTQ_E_SHAPE,
                  "kvrow = %lld, pos = %lld of %lld", (long long)kvrow, (long long)pos, (long long)maxpos);
@@ -520,9 +520,9 @@ int32_t rstq_kv_append(rstq_ctx* ctx, rstq_buf* src, rstq_buf* cache, int64_t kv
     return RSTQ_OK;
 }
 
-int32_t rstq_rope_append(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* kcache, rstq_buf* vcache,
-                         int64_t n_q, int64_t n_kv, int64_t head_dim, double theta, int64_t pos, int64_t maxpos,
-                         rstq_buf* posbuf) {
+int32_t rstq_rope_append(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* kcache,
+                         rstq_buf* vcache, rstq_buf* posbuf, int64_t n_q, int64_t n_kv, int64_t head_dim,
+                         double theta, int64_t pos, int64_t maxpos) {
     RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
     RSTQ_REQUIRE(n_q >= 1 && n_kv >= 1 && head_dim >= 2 && head_dim % 2 == 0 && theta > 0.0 && maxpos >= 1 &&
                      (posbuf || (pos >= 0 && pos < maxpos)),
@@ -640,15 +640,15 @@ static int32_t attention_impl(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf*
 }
 
 int32_t rstq_gqa_decode_attention(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
-                                  int64_t cache_len, rstq_buf* clenbuf, int64_t n_q, int64_t group, int64_t n_kv,
-                                  int64_t head_dim, int64_t maxpos, double scale) {
+                                  rstq_buf* clenbuf, int64_t cache_len, int64_t n_q, int64_t group,
+                                  int64_t n_kv, int64_t head_dim, int64_t maxpos, double scale) {
     return attention_impl(ctx, q, k, v, out, cache_len, clenbuf, n_q, group, n_kv, head_dim, maxpos, scale, nullptr,
                           nullptr, nullptr);
 }
 
 int32_t rstq_gqa_decode_attention_quant_act(rstq_ctx* ctx, rstq_buf* q, rstq_buf* k, rstq_buf* v, rstq_buf* out,
-                                            rstq_buf* xq, rstq_buf* xs, rstq_buf* xsum, int64_t cache_len,
-                                            rstq_buf* clenbuf, int64_t n_q, int64_t group, int64_t n_kv,
+                                            rstq_buf* xq, rstq_buf* xs, rstq_buf* xsum, rstq_buf* clenbuf,
+                                            int64_t cache_len, int64_t n_q, int64_t group, int64_t n_kv,
                                             int64_t head_dim, int64_t maxpos, double scale) {
     RSTQ_REQUIRE(xq && xs, RSTQ_E_INVALID, "null quantizer buffer");
     return attention_impl(ctx, q, k, v, out, cache_len, clenbuf, n_q, group, n_kv, head_dim, maxpos, scale, xq, xs, xsum);

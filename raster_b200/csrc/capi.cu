@@ -394,7 +394,7 @@ int32_t rstq_device_count(int32_t* count) {
     return RSTQ_OK;
 }
 
-int32_t rstq_init(const int32_t* devices, int32_t ndev, rstq_ctx** ctxp) {
+int32_t rstq_init(const int32_t* devices, rstq_ctx** ctxp, int32_t ndev) {
     RSTQ_REQUIRE(ctxp, RSTQ_E_INVALID, "null argument");
     *ctxp = nullptr;
     RSTQ_REQUIRE(devices && ndev >= 1 && ndev <= 64, RSTQ_E_INVALID, "need 1..64 devices");
@@ -573,7 +573,7 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
     }
 }
 
-int32_t rstq_timeline_read(rstq_ctx* ctx, int32_t dev, int64_t* out, int64_t n) {
+int32_t rstq_timeline_read(rstq_ctx* ctx, int64_t* out, int32_t dev, int64_t n) {
     CHECK_CTX(ctx);
     CHECK_DEV(ctx, dev);
     RSTQ_REQUIRE(out && n >= 0 && n <= 1024 * 8, RSTQ_E_INVALID, "need 0 <= n <= 8192");
@@ -585,7 +585,7 @@ int32_t rstq_timeline_read(rstq_ctx* ctx, int32_t dev, int64_t* out, int64_t n) 
     return RSTQ_OK;
 }
 
-int32_t rstq_device_info(rstq_ctx* ctx, int32_t dev, int64_t* out4) {
+int32_t rstq_device_info(rstq_ctx* ctx, int64_t* out4, int32_t dev) {
     CHECK_CTX(ctx);
     CHECK_DEV(ctx, dev);
     RSTQ_REQUIRE(out4, RSTQ_E_INVALID, "null argument");
@@ -619,7 +619,7 @@ int32_t rstq_alloc(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, int64_t bytes) {
     return RSTQ_OK;
 }
 
-int32_t rstq_buf_wrap(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, void* device_ptr, int64_t bytes) {
+int32_t rstq_buf_wrap(rstq_ctx* ctx, rstq_buf** buf, void* device_ptr, int32_t dev, int64_t bytes) {
     CHECK_CTX(ctx);
     RSTQ_REQUIRE(buf, RSTQ_E_INVALID, "null argument");
     *buf = nullptr;
@@ -632,7 +632,7 @@ int32_t rstq_buf_wrap(rstq_ctx* ctx, rstq_buf** buf, int32_t dev, void* device_p
     return RSTQ_OK;
 }
 
-int32_t rstq_stream_set(rstq_ctx* ctx, int32_t dev, void* stream) {
+int32_t rstq_stream_set(rstq_ctx* ctx, void* stream, int32_t dev) {
     CHECK_CTX(ctx);
     CHECK_DEV(ctx, dev);
     DeviceState& ds = ctx->devs[dev];

@@ -880,13 +880,35 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         consumer_bar();
         const int row = (tid >> 4) & 31, wsrc = tid & 15;
         const int src = wsrc * 33 + (row & 7) * 4 + (row >> 3);
+        float* sres = red + kParkGroups * kParkStride;   // (TP) the finished sums, [group][32 rows]
         for (int i = 0; i < count; ++i) {
             float sum = red[i * kParkStride + src];
             if (wsrc + 16 < kCW) sum += red[i * kParkStride + src + 16 * 33];
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             const int64_t r = (g_first + i) * 32 + row;
-            if ((tid & 15) == 0 && tid < 512 && r < p.out) emit(r, sum);
+            if ((tid & 15) == 0 && tid < 512) {
+                if (TP) sres[i * 32 + row] = sum;
+                else if (r < p.out) store_out(p.y, p.out_dtype, r, sum);
+            }
+        }
+        if (TP) {
+            // Fused exchange: the 32 (value, epoch) pairs of a group are neighbours in every rank's
+            // stage, so one warp writes them to one peer as one 256-byte row (two full NVLink
+            // packets) instead of 32 separate 8-byte stores from 32 threads.
+            consumer_bar();
+            for (int job = warp; job < count * tpn; job += kCW) {
+                const int i = job / tpn, peer = job - i * tpn;
+                const int64_t r = (g_first + i) * 32 + lane;
+                uint8_t* dst = nullptr;
+#pragma unroll
+                for (int q = 0; q < kTpMaxRanks; ++q)   // static indices keep the pointer table in the parameter bank
+                    if (q == peer) dst = p.tp.region[q];
+                if (r < p.out)
+                    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + tp_slot + r * 8),
+                                 "r"(__float_as_uint(sres[i * 32 + lane])), "r"(tp_e)
+                                 : "memory");
+            }
         }
         if (more) consumer_bar();   // the slots are written again
     };

@@ -213,8 +213,8 @@ int64_t rstq_tp_region_bytes(int32_t nranks, int64_t max_payload_bytes) {
     return kTpHeader + 6 * (int64_t)nranks * slot;
 }
 
-int32_t rstq_tp_attach(rstq_ctx* ctx, int32_t dev, int32_t rank, int32_t nranks, void* const* regions,
-                       int64_t region_bytes, rstq_tp** out) {
+int32_t rstq_tp_attach(rstq_ctx* ctx, void* const* regions, rstq_tp** out, int32_t dev, int32_t rank,
+                       int32_t nranks, int64_t region_bytes) {
     RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
     RSTQ_REQUIRE(dev >= 0 && dev < (int)ctx->devs.size(), RSTQ_E_INVALID, "device index %d out of range", dev);
     RSTQ_REQUIRE(out && regions, RSTQ_E_INVALID, "null argument");
@@ -241,8 +241,8 @@ int32_t rstq_tp_attach(rstq_ctx* ctx, int32_t dev, int32_t rank, int32_t nranks,
     return RSTQ_OK;
 }
 
-int32_t rstq_tp_create_local(rstq_ctx* ctx, int32_t nranks, const int32_t* devs, int64_t max_payload_bytes,
-                             rstq_tp** tps) {
+int32_t rstq_tp_create_local(rstq_ctx* ctx, const int32_t* devs, rstq_tp** tps, int32_t nranks,
+                             int64_t max_payload_bytes) {
     RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
     RSTQ_REQUIRE(devs && tps, RSTQ_E_INVALID, "null argument");
     const int64_t bytes = rstq_tp_region_bytes(nranks, max_payload_bytes);
@@ -289,7 +289,7 @@ int32_t rstq_tp_create_local(rstq_ctx* ctx, int32_t nranks, const int32_t* devs,
         }
     }
     for (int r = 0; r < nranks; ++r) {
-        const int32_t rc = rstq_tp_attach(ctx, devs[r], r, nranks, regions, bytes, &tps[r]);
+        const int32_t rc = rstq_tp_attach(ctx, regions, &tps[r], devs[r], r, nranks, bytes);
         if (rc != RSTQ_OK) {
             undo();
             return rc;
@@ -380,7 +380,7 @@ int32_t rstq_ipc_export(rstq_buf* buf, void* handle64) {
     return RSTQ_OK;
 }
 
-int32_t rstq_ipc_open(rstq_ctx* ctx, int32_t dev, const void* handle64, void** device_ptr) {
+int32_t rstq_ipc_open(rstq_ctx* ctx, const void* handle64, void** device_ptr, int32_t dev) {
     RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
     RSTQ_REQUIRE(dev >= 0 && dev < (int)ctx->devs.size(), RSTQ_E_NODEV, "device index %d out of range", dev);
     RSTQ_REQUIRE(handle64 && device_ptr, RSTQ_E_INVALID, "null argument");
@@ -392,7 +392,7 @@ int32_t rstq_ipc_open(rstq_ctx* ctx, int32_t dev, const void* handle64, void** d
     return RSTQ_OK;
 }
 
-int32_t rstq_ipc_close(rstq_ctx* ctx, int32_t dev, void* device_ptr) {
+int32_t rstq_ipc_close(rstq_ctx* ctx, void* device_ptr, int32_t dev) {
     RSTQ_REQUIRE(ctx && ctx->magic == kCtxMagic, RSTQ_E_INVALID, "invalid context handle");
     RSTQ_REQUIRE(dev >= 0 && dev < (int)ctx->devs.size(), RSTQ_E_NODEV, "device index %d out of range", dev);
     RSTQ_REQUIRE(device_ptr, RSTQ_E_INVALID, "null argument");

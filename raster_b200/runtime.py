@@ -61,7 +61,7 @@ class DeviceBuffer:
         if wrap_ptr is None:
             L.check(ctx.lib.rstq_alloc(ctx.handle, C.byref(h), dev, max(self.byte_size, 1)))
         else:   # buffer-of-array: memory somebody else owns
-            L.check(ctx.lib.rstq_buf_wrap(ctx.handle, C.byref(h), dev, C.c_void_p(int(wrap_ptr)),
+            L.check(ctx.lib.rstq_buf_wrap(ctx.handle, C.byref(h), C.c_void_p(int(wrap_ptr)), dev,
                                           self.byte_size))
         self.handle = h
 
@@ -181,7 +181,7 @@ class Context:
         ords = [parse_device(d) for d in devices]
         arr = (C.c_int32 * len(ords))(*ords)
         h = C.c_void_p()
-        L.check(self.lib.rstq_init(arr, len(ords), C.byref(h)))
+        L.check(self.lib.rstq_init(arr, C.byref(h), len(ords)))
         self.handle = h
         self.devices = ords
 
@@ -198,7 +198,7 @@ class Context:
 
     def set_stream(self, cuda_stream: int | None, dev=0) -> None:
         """Launch on the caller's cudaStream_t (an integer handle); None = the context's own."""
-        L.check(self.lib.rstq_stream_set(self.handle, dev, C.c_void_p(cuda_stream or 0)))
+        L.check(self.lib.rstq_stream_set(self.handle, C.c_void_p(cuda_stream or 0), dev))
 
     # -- tensor-parallel groups ------------------------------------------------
     def tp_region_bytes(self, nranks: int, max_payload_bytes: int) -> int:
@@ -209,7 +209,7 @@ class Context:
         n = len(devs)
         arr = (C.c_int32 * n)(*devs)
         hs = (C.c_void_p * n)()
-        L.check(self.lib.rstq_tp_create_local(self.handle, n, arr, max_payload_bytes, hs))
+        L.check(self.lib.rstq_tp_create_local(self.handle, arr, hs, n, max_payload_bytes))
         return [TpEndpoint(self, C.c_void_p(hs[r]), r, n, devs[r]) for r in range(n)]
 
     def tp_attach(self, rank: int, nranks: int, region_ptrs, region_bytes: int, dev=0) -> TpEndpoint:
@@ -217,7 +217,7 @@ class Context:
         addresses it (symmetric memory or an IPC mapping)."""
         arr = (C.c_void_p * nranks)(*[int(p) for p in region_ptrs])
         h = C.c_void_p()
-        L.check(self.lib.rstq_tp_attach(self.handle, dev, rank, nranks, arr, region_bytes, C.byref(h)))
+        L.check(self.lib.rstq_tp_attach(self.handle, arr, C.byref(h), dev, rank, nranks, region_bytes))
         return TpEndpoint(self, h, rank, nranks, dev)
 
     def ipc_export(self, buf: DeviceBuffer) -> bytes:
@@ -227,11 +227,11 @@ class Context:
 
     def ipc_open(self, handle: bytes, dev=0) -> int:
         p = C.c_void_p()
-        L.check(self.lib.rstq_ipc_open(self.handle, dev, C.c_char_p(bytes(handle)), C.byref(p)))
+        L.check(self.lib.rstq_ipc_open(self.handle, C.c_char_p(bytes(handle)), C.byref(p), dev))
         return int(p.value)
 
     def ipc_close(self, device_ptr: int, dev=0) -> None:
-        L.check(self.lib.rstq_ipc_close(self.handle, dev, C.c_void_p(device_ptr)))
+        L.check(self.lib.rstq_ipc_close(self.handle, C.c_void_p(device_ptr), dev))
 
     # -- weights ---------------------------------------------------------
     def bind_weight(self, codes, scales, out, in_, fmt, layout, dev=0, split=L.SPLIT_NONE,
@@ -328,24 +328,24 @@ class Context:
 
     # -- attention steps of the decode chain (raster.dl.attention) -----------------
     def rope_pos(self, x, out, heads, head_dim, theta, pos=0, posbuf=None) -> None:
-        L.check(self.lib.rstq_rope_pos(self.handle, x.handle, out.handle, heads, head_dim, theta, pos,
-                                       posbuf.handle if posbuf is not None else None))
+        L.check(self.lib.rstq_rope_pos(self.handle, x.handle, out.handle,
+                                       posbuf.handle if posbuf is not None else None, heads, head_dim, theta, pos))
 
     def kv_append(self, src, cache, kvrow, pos=0, maxpos=1, posbuf=None) -> None:
-        L.check(self.lib.rstq_kv_append(self.handle, src.handle, cache.handle, kvrow, pos, maxpos,
-                                        posbuf.handle if posbuf is not None else None))
+        L.check(self.lib.rstq_kv_append(self.handle, src.handle, cache.handle,
+                                        posbuf.handle if posbuf is not None else None, kvrow, pos, maxpos))
 
     def gqa_decode_attention_quant_act(self, q, k, v, out, xq, xs, xsum, cache_len, n_q, group, n_kv, head_dim,
                                        maxpos, scale, clenbuf=None) -> None:
         L.check(self.lib.rstq_gqa_decode_attention_quant_act(
             self.handle, q.handle, k.handle, v.handle, out.handle, xq.handle, xs.handle,
-            xsum.handle if xsum is not None else None, cache_len,
-            clenbuf.handle if clenbuf is not None else None, n_q, group, n_kv, head_dim, maxpos, scale))
+            xsum.handle if xsum is not None else None, clenbuf.handle if clenbuf is not None else None,
+            cache_len, n_q, group, n_kv, head_dim, maxpos, scale))
 
     def rope_append(self, q, k, v, kcache, vcache, n_q, n_kv, head_dim, theta, pos=0, maxpos=1, posbuf=None) -> None:
         L.check(self.lib.rstq_rope_append(self.handle, q.handle, k.handle, v.handle, kcache.handle, vcache.handle,
-                                          n_q, n_kv, head_dim, theta, pos, maxpos,
-                                          posbuf.handle if posbuf is not None else None))
+                                          posbuf.handle if posbuf is not None else None,
+                                          n_q, n_kv, head_dim, theta, pos, maxpos))
 
     def residual_rms_norm_quant_act(self, a, b, total, weight, xq, xs, xsum, rows, features, eps=1e-6,
                                     gain_offset=0.0) -> None:
@@ -364,9 +364,9 @@ class Context:
 
     def gqa_decode_attention(self, q, k, v, out, cache_len, n_q, group, n_kv, head_dim, maxpos, scale,
                              clenbuf=None) -> None:
-        L.check(self.lib.rstq_gqa_decode_attention(self.handle, q.handle, k.handle, v.handle, out.handle, cache_len,
-                                                   clenbuf.handle if clenbuf is not None else None, n_q, group,
-                                                   n_kv, head_dim, maxpos, scale))
+        L.check(self.lib.rstq_gqa_decode_attention(self.handle, q.handle, k.handle, v.handle, out.handle,
+                                                   clenbuf.handle if clenbuf is not None else None, cache_len,
+                                                   n_q, group, n_kv, head_dim, maxpos, scale))
 
     # -- graphs / events / misc ------------------------------------------------
     def graph_begin(self, dev=0) -> None:
@@ -388,7 +388,7 @@ class Context:
 
     def device_info(self, dev=0) -> dict:
         v = (C.c_int64 * 4)()
-        L.check(self.lib.rstq_device_info(self.handle, dev, v))
+        L.check(self.lib.rstq_device_info(self.handle, v, dev))
         return {"sm_count": v[0], "l2_bytes": v[1], "total_mem": v[2], "cc": v[3]}
 
     def launch_count(self) -> int:

@@ -42,9 +42,9 @@ def test_null_and_bad_handles_are_status_codes_not_crashes():
     assert lib.rstq_graph_destroy(None) == L.OK
     assert lib.rstq_event_destroy(None) == L.OK
     assert lib.rstq_sync(None, 0) == L.E_INVALID
-    assert lib.rstq_init(None, 1, None) == L.E_INVALID
+    assert lib.rstq_init(None, None, 1) == L.E_INVALID
     h = C.c_void_p()
-    assert lib.rstq_init(None, 0, C.byref(h)) == L.E_INVALID
+    assert lib.rstq_init(None, C.byref(h), 0) == L.E_INVALID
     assert lib.rstq_alloc(None, C.byref(h), 0, 16) == L.E_INVALID
     assert b"context" in lib.rstq_last_error()
 
@@ -54,7 +54,7 @@ def test_init_without_gpu_fails_loudly():
     lib = L.load()
     devs = (C.c_int32 * 1)(0)
     h = C.c_void_p()
-    assert lib.rstq_init(devs, 1, C.byref(h)) == L.E_NODEV
+    assert lib.rstq_init(devs, C.byref(h), 1) == L.E_NODEV
     assert not h.value
     assert b"no CPU path" in lib.rstq_last_error()
     from raster_b200 import Context
