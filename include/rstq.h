@@ -209,10 +209,19 @@ RSTQ_API int32_t rstq_quant_act_q8k(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rs
 /* ---- the matmul on device-resident data.
  * rstq_qmatmul: y[M, out] = W . x[M, in]; x is act_dtype, y is out_dtype.
  *   MODE_A8 quantizes x inside the call -- the arithmetic of qlinear-i8! / qlinear-i8-q8!
- *   (src/raster/quant/op.clj:43-51, :81-90) for any M; bf16 activations are widened exactly
- *   first, so they give the result of the same values passed as f32.
+ *   (src/raster/quant/op.clj:43-51, :81-90); bf16 activations are widened exactly first, so they
+ *   give the result of the same values passed as f32.  At M = 1 (in <= 12288) the quantizer runs
+ *   inside the decode kernel (same codes, scales and sums, bit for bit).  Up to M = 63 the block dots
+ *   are exact integers and the result agrees with the reference formula to <= 2e-6 of max|y|; from
+ *   M = 64 -- and from M = 9 when in > 16384, where eight tokens of codes no longer fit beside the
+ *   weight ring -- the exact codes and scales feed the fp16 tensor-core path instead: <= 1e-3 of
+ *   max|y| (measured ~4e-5), no longer the exact integer dots.  RSTQ_TUNE_GEMM_MIN_M raised above
+ *   M keeps the exact path at any size.
  *   MODE_F multiplies the float activations directly -- qlinear-q8
- *   (src/raster/quant/train.clj:77-108) and the prefill GEMM.
+ *   (src/raster/quant/train.clj:77-108) and the prefill GEMM: decode kernel (f32-grade, <= 2e-5)
+ *   up to M = 16, tensor-core path (<= 1e-3) from M = 17, and already from M = 2 when the matrix is
+ *   larger than 4 MB and the decode kernel would have to stream it twice or more because M tokens
+ *   of activations do not fit in shared memory.
  * rstq_qmatmul_prequant: the kernel-level call of the reference,
  *   (xq xs xsum wqi wsi y in out ...) of qmatmul-q4-x8! / qmatmul-q8-x8!
  *   (src/raster/quant/kernels.clj:216-247, :308-333), and with xsum == NULL and a

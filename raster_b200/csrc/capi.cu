@@ -929,8 +929,29 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
     CHECK_CTX(ctx);
     RSTQ_REQUIRE(ok_w(w) && w->ctx == ctx, RSTQ_E_INVALID, "invalid weight handle");
     RSTQ_REQUIRE(M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)M);
-    RSTQ_REQUIRE(!w->pair_out, RSTQ_E_INVALID, "Q6_K weights go through rstq_qmatmul");
     int32_t rc;
+    if (w->pair_out) {
+        // qmatmul-q6k-dp4a! (src/raster/quant/kernels_k.clj:270-300): q8_K activations, xs per super-block,
+        // bsums per 16-element sub-block (rstq_quant_act_q8k with sub = 16 produces exactly these)
+        RSTQ_REQUIRE(xsum, RSTQ_E_INVALID, "a Q6_K weight needs the sub-block sums");
+        const int64_t nsb = w->in / 256;
+        if ((rc = need_bytes(xq, M * w->in, "xq")) != RSTQ_OK) return rc;
+        if ((rc = need_bytes(xs, M * nsb * 4, "xs")) != RSTQ_OK) return rc;
+        if ((rc = need_bytes(xsum, M * (w->in / 16) * 4, "bsums")) != RSTQ_OK) return rc;
+        if ((rc = need_bytes(y, M * w->pair_out * 4, "y")) != RSTQ_OK) return rc;
+        RSTQ_REQUIRE(xq->dev == w->dev && xs->dev == w->dev && y->dev == w->dev && xsum->dev == w->dev,
+                     RSTQ_E_DEVICE, "weight and buffers live on different devices");
+        if ((rc = use_dev(ctx, w->dev)) != RSTQ_OK) return rc;
+        DeviceState& dsk = ctx->devs[w->dev];
+        ActScratch s;
+        if ((rc = act_scratch(dsk, M, w->in, &s)) != RSTQ_OK) return rc;
+        if ((rc = dev_reserve(dsk, &dsk.kq_scratch, &dsk.kq_scratch_bytes, M * w->out * 4)) != RSTQ_OK) return rc;
+        if ((rc = launch_q6k_prep(ctx, dsk, (const float*)xs->ptr, (const int32_t*)xsum->ptr, s.xs, s.xsum,
+                                  M * w->nb)) != RSTQ_OK)
+            return rc;
+        if ((rc = run_a8(ctx, w, (const int8_t*)xq->ptr, s.xs, s.xsum, (float*)dsk.kq_scratch, M)) != RSTQ_OK) return rc;
+        return launch_pair_sum(ctx, dsk, (const float*)dsk.kq_scratch, (float*)y->ptr, M, w->pair_out);
+    }
     if (w->mins) {
         // qmatmul-q4k-dp4a! (src/raster/quant/kernels_k.clj:195-237): q8_K activations, xs per
         // super-block, bsums per 32-element sub-block

@@ -196,6 +196,8 @@ int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
 int32_t launch_quant_act_q8k(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs, float* xs32,
                              int32_t* bsums, int64_t rows, int64_t in, int sub);
 int32_t launch_expand_scales(rstq_ctx* ctx, DeviceState& ds, const float* xs, float* xs32, int64_t n32);
+int32_t launch_q6k_prep(rstq_ctx* ctx, DeviceState& ds, const float* xs, const int32_t* bsums16, float* xs32,
+                        int32_t* bsum32, int64_t n32);
 int32_t launch_pair_sum(rstq_ctx* ctx, DeviceState& ds, const float* t, float* y, int64_t M, int64_t out);
 int32_t launch_q4k_min(rstq_ctx* ctx, DeviceState& ds, const float* mins, const float* xs32, const int32_t* bsums,
                        float* y, int64_t M, int64_t nb, int64_t out);

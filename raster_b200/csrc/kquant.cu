@@ -83,6 +83,20 @@ expand_scales_kernel(const float* __restrict__ xs, float* __restrict__ xs32, int
         xs32[i] = xs[i >> 3];
 }
 
+// Q6_K kernel-level call (qmatmul-q6k-dp4a!, src/raster/quant/kernels_k.clj:270-300): the caller holds the
+// q8_K activation scale per super-block and the code sums per 16-element sub-block; the twin-row units want
+// a scale and a sum per 32-element block: xs32[i] = xs[i / 8], bsum32[i] = bsums16[2 i] + bsums16[2 i + 1].
+__global__ void __launch_bounds__(256)
+q6k_prep_kernel(const float* __restrict__ xs, const int32_t* __restrict__ bsums16, float* __restrict__ xs32,
+                int32_t* __restrict__ bsum32, int64_t n32) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n32; i += (int64_t)gridDim.x * blockDim.x) {
+        xs32[i] = xs[i >> 3];
+        bsum32[i] = bsums16[2 * i] + bsums16[2 * i + 1];
+    }
+}
+
 // y[m, o] += sum over b of mins[o, b] * (xs32[m, b] * bsums[m, b]).  The products t[m, b] of up to
 // TT tokens are staged in shared memory once per CTA; a warp owns an output row at a time and reads
 // it with 16-byte loads (nb % 8 == 0), so mins crosses the memory system once per TT tokens.
@@ -172,6 +186,15 @@ int32_t launch_expand_scales(rstq_ctx* ctx, DeviceState& ds, const float* xs, fl
     int64_t ctas = (n32 + 255) / 256;
     if (ctas > (int64_t)ds.sm_count * 4) ctas = (int64_t)ds.sm_count * 4;
     RSTQ_CUDA(launch_pdl(expand_scales_kernel, dim3((unsigned)ctas), ds, xs, xs32, n32));
+    ctx->launches++;
+    return RSTQ_OK;
+}
+
+int32_t launch_q6k_prep(rstq_ctx* ctx, DeviceState& ds, const float* xs, const int32_t* bsums16, float* xs32,
+                        int32_t* bsum32, int64_t n32) {
+    int64_t ctas = (n32 + 255) / 256;
+    if (ctas > (int64_t)ds.sm_count * 4) ctas = (int64_t)ds.sm_count * 4;
+    RSTQ_CUDA(launch_pdl(q6k_prep_kernel, dim3((unsigned)ctas), ds, xs, bsums16, xs32, bsum32, n32));
     ctx->launches++;
     return RSTQ_OK;
 }

@@ -359,3 +359,149 @@ def destroy_chain(chain: Chain) -> None:
     for b in chain.bounds:
         destroy_prepared(b)
     close_kernel_arena(chain.arena)
+
+
+# ---- resident programs: bind-program! / run-program! / profile-program! ---------------------------
+# src/raster/gpu/core.clj:889-1249 (bind), :1272 (run), :1343-1388 (profile).  A program descriptor is
+# data: {"all_params": [sym ...] (call order), "array_params": [sym ...], "writes": {sym ...} (array
+# params some step writes), "intermediates": {sym: (dtype, n)}, "steps": [{"op", "bind", "scalars",
+# "n", "phase"}]} -- the step list the compiler emits for the resident path, reduced to what this
+# library runs: registered operators (a `^:no-inline` qlinear call becomes a step the way an opaque BLAS
+# call becomes a :gemm step, src/raster/compiler/pipeline.clj:1186-1201).
+_PROGRAMS = {}
+
+
+def bind_program(descriptor: dict, args, roles=None, key="program", profile=False, weights=None) -> dict:
+    """Allocates resident buffers for the array params and the intermediates, binds every step once and
+    records the sequence as one graph.  args: values in descriptor["all_params"] order (arrays for
+    array params, numbers for scalars).  roles: {sym: "constant"|"state"|"input"|"output"} overriding the
+    derived defaults (read-only -> input, written -> output).  Binding a key twice raises; a program bound
+    with profile=True also answers profile_program."""
+    if key in _PROGRAMS:
+        raise KeyError(f"program {key!r} is already bound -- destroy it first or bind under another key")
+    all_params, array_params = list(descriptor["all_params"]), list(descriptor["array_params"])
+    if len(args) != len(all_params):
+        raise ValueError(f"bind_program: {len(all_params)} parameters, {len(args)} arguments")
+    argmap = dict(zip(all_params, args))
+    writes = set(descriptor.get("writes", ()))
+    roles = dict(roles or {})
+    for r in roles.values():
+        if r not in VALID_CHAIN_ROLES:
+            raise ValueError(f"unknown role {r!r} -- must be one of {VALID_CHAIN_ROLES}")
+    buffers = {}
+    for p in array_params:
+        a = np.ascontiguousarray(argmap[p])
+        role = roles.get(p, "output" if p in writes else "input")
+        buffers[p] = (_np_dtype_name(a), a.size, a, role)
+    for sym, (dtype, n) in descriptor.get("intermediates", {}).items():
+        if sym in buffers:
+            raise KeyError(f"intermediate {sym!r} collides with a parameter of the program")
+        buffers[sym] = (dtype, n, None, "scratch")
+    scalars = {p: argmap[p] for p in all_params if p not in array_params}
+    steps = []
+    for st in descriptor["steps"]:
+        steps.append({"op": st["op"], "bind": st["bind"], "n": st.get("n"),
+                      "scalars": [scalars[s] if isinstance(s, str) and s in scalars else s for s in st.get("scalars", [])]})
+    chain = chain_program(buffers, steps, weights)
+    handle = {"program-key": key, "descriptor": descriptor, "chain": chain, "profile?": bool(profile),
+              "phases": [st.get("phase", "main") for st in descriptor["steps"]]}
+    _PROGRAMS[key] = handle
+    return handle
+
+
+def _resolve_program(prog_or_key) -> dict:
+    h = prog_or_key if isinstance(prog_or_key, dict) else _PROGRAMS.get(prog_or_key)
+    if h is None or h.get("program-key") not in _PROGRAMS:
+        raise KeyError(f"no bound program {prog_or_key!r}")
+    return h
+
+
+def _upload_inputs(h, args):
+    d = h["descriptor"]
+    argmap = dict(zip(d["all_params"], args))
+    chain = h["chain"]
+    for p in d["array_params"]:
+        if chain.roles[p] == "input":
+            chain.buffers[p]["segment"].upload(np.ascontiguousarray(argmap[p]))
+
+
+def run_program(prog_or_key, args) -> dict:
+    """Uploads the "input" params, replays the graph, downloads the "output" params: {sym: array}."""
+    h = _resolve_program(prog_or_key)
+    _upload_inputs(h, args)
+    chain = h["chain"]
+    replay_graph(chain.graph)
+    return {k: buffer_to_array(chain.buffers[k]) for k, r in chain.roles.items() if r == "output"}
+
+
+def profile_program(prog_or_key, args) -> dict:
+    """The profiling twin of run_program: the same steps, launched one by one between device events.
+    {"result", "profile": [{"kernel-name", "phase", "ms"}] in execution order, "kernel-total-ms",
+    "device-wall-ms" (first start to last end, gaps included), "host-wall-ms"}."""
+    import time
+    h = _resolve_program(prog_or_key)
+    if not h["profile?"]:
+        raise RuntimeError("profile_program: program was not bound with profile=True -- rebind it")
+    _upload_inputs(h, args)
+    ctx, chain = _ctx(), h["chain"]
+    evs = [ctx.event() for _ in range(len(chain.bounds) + 1)]
+    t0 = time.perf_counter()
+    evs[0].record()
+    for b, e in zip(chain.bounds, evs[1:]):
+        launch_registered_bound(b)
+        e.record()
+    synchronize_async()
+    t1 = time.perf_counter()
+    prof = [{"kernel-name": b["kernel_name"], "phase": ph, "ms": evs[i].elapsed_ms(evs[i + 1])}
+            for i, (b, ph) in enumerate(zip(chain.bounds, h["phases"]))]
+    wall = evs[0].elapsed_ms(evs[-1])
+    for e in evs:
+        e.destroy()
+    result = {k: buffer_to_array(chain.buffers[k]) for k, r in chain.roles.items() if r == "output"}
+    return {"result": result, "profile": prof, "kernel-total-ms": float(sum(p["ms"] for p in prof)),
+            "device-wall-ms": wall, "host-wall-ms": (t1 - t0) * 1e3}
+
+
+def destroy_program(prog_or_key) -> None:
+    h = _resolve_program(prog_or_key)
+    destroy_chain(h["chain"])
+    _PROGRAMS.pop(h["program-key"], None)
+
+
+# ---- device catalogue row (src/raster/runtime/hardware_catalogue.clj:13-130) -----------------------
+# The same capability map the reference merges into detected device info, for the part this library
+# targets.  Bandwidth and tensor throughput are the figures MEASURED on the deployment pool (a copy
+# kernel and a cuBLAS bf16 GEMM), not the data-sheet ones.
+GPU_CATALOGUE = {
+    "NVIDIA B200": {
+        "compute-capability": [10, 0],
+        "sm-count": 148,
+        "warp-size": 32,
+        "max-threads-per-block": 1024,
+        "shared-memory-per-block": 232448,        # opt-in dynamic limit (227 KB)
+        "registers-per-block": 65536,
+        "tensor-memory-bytes-per-sm": 262144,
+        "l2-bytes": 132120576,                    # 126 MB
+        "global-memory-bytes": 192265846784,      # 183 359 MiB as the driver reports it
+        "memory-bandwidth-gb-s": 6552.6,          # measured copy; 7700 nominal
+        "peak-flops-dp": 40.0e12,
+        "peak-flops-sp": 80.0e12,
+        "peak-flops-bf16-dense": 1619.0e12,       # measured cuBLAS burst; 2250e12 nominal
+        "nvlink-gb-s-per-direction": 900.0,
+    },
+}
+
+
+def detect_devices() -> list:
+    """The devices of the live context, each as its catalogue row with the values the driver reports
+    laid over it -- what detect-gpus does for the other back ends (src/raster/runtime/hardware.clj:218-228
+    returns [] for CUDA today)."""
+    ctx = _ctx()
+    out = []
+    for i, dev in enumerate(_state["devices"]):
+        info = ctx.device_info(i)
+        row = dict(GPU_CATALOGUE["NVIDIA B200"]) if info["cc"] == 100 else {}
+        row.update({"id": dev, "sm-count": info["sm_count"], "l2-bytes": info["l2_bytes"],
+                    "global-memory-bytes": info["total_mem"]})
+        out.append(row)
+    return out

@@ -91,3 +91,27 @@ def qmatmul_q4k_dp4a(xp, xs, bsums, wp, da, db, aq, bq, y, in_, out, ctx=None):
         for b in (bq_, bs, bb, by):
             b.free()
         w.free()
+
+
+def qmatmul_q6k_dp4a(xp, xs, bsums, wp, sc, ds, y, in_, out, ctx=None):
+    """`qmatmul-q6k-dp4a!` (src/raster/quant/kernels_k.clj:270-300), the reference's argument order:
+    y[o] = sum_sb ds[o, sb] * xs[sb] * sum_{j<16} sc_j * (dot_j - 32 * bsums_j); xp / wp are the int8
+    activation codes / the one-byte 6-bit weight codes read as little-endian int32 words, bsums the
+    code sums per 16-element sub-block (quant_act_q8k_gpu(..., sub=16)).  Overwrites and returns y."""
+    ctx = ctx or default_context()
+    enc = {"wq": np.ascontiguousarray(wp, dtype=np.int32).view(np.uint8), "sc": sc, "ds": ds}
+    if y.dtype != np.float32 or y.size < out:
+        raise ValueError("y must be float32 with out elements")
+    w = ctx.bind_weight_q6k(enc, out, in_)
+    bq_ = ctx.array_to_buffer(np.ascontiguousarray(xp, dtype=np.int32).view(np.int8))
+    bs = ctx.array_to_buffer(np.ascontiguousarray(xs, dtype=np.float32))
+    bb = ctx.array_to_buffer(np.ascontiguousarray(bsums, dtype=np.int32))
+    by = ctx.make_buffer(out, np.float32)
+    try:
+        ctx.qmatmul_prequant(w, bq_, bs, bb, by, 1)
+        y[:out] = by.download()
+        return y
+    finally:
+        for b in (bq_, bs, bb, by):
+            b.free()
+        w.free()

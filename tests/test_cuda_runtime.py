@@ -178,3 +178,64 @@ def test_chain_program_replays_a_decode_mlp():
             w.free()
     finally:
         rt.shutdown()
+
+
+def test_b200_catalogue_row_has_the_keys_of_the_reference_catalogue():
+    """src/raster/runtime/hardware_catalogue.clj:17-30: every row carries these capability keys."""
+    row = rt.GPU_CATALOGUE["NVIDIA B200"]
+    for k in ("compute-capability", "sm-count", "warp-size", "max-threads-per-block", "shared-memory-per-block",
+              "registers-per-block", "global-memory-bytes", "memory-bandwidth-gb-s", "peak-flops-dp", "peak-flops-sp"):
+        assert k in row
+    assert row["sm-count"] == 148 and row["compute-capability"] == [10, 0]
+
+
+@pytest.mark.gpu
+def test_bind_run_and_profile_program():
+    """bind-program! / run-program! / profile-program! (src/raster/gpu/core.clj:889-1388) on the decode MLP:
+    params in call order, roles derived (read-only -> input, written -> output) with the weights' gain
+    overridden to constant, one graph per program, per-kernel device times from the profiling twin."""
+    rt.init(("cuda:0",))
+    try:
+        H, F = 256, 512
+        Wg = synth.normal(3, F * H, 0.05)
+        gq, gs = orc.quantize_weight(Wg, 4)
+        gain = synth.normal(5, H, 0.1) + np.float32(1.0)
+        ctx = rt._ctx()
+        wts = {"wg": ctx.bind_weight(gq, gs, F, H, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)}
+        desc = {"all_params": ["x", "gain", "g", "rows", "eps"], "array_params": ["x", "gain", "g"], "writes": {"g"},
+                "intermediates": {"xn": ("float", H), "xq": ("byte", H), "xs": ("float", H // 32), "xsum": ("int", H // 32)},
+                "steps": [{"op": "rms-norm!", "bind": ["x", "gain", "xn"], "scalars": ["rows", H, "eps", 0.0], "n": H},
+                          {"op": "quantize-act-i8", "bind": ["xn", "xq", "xs", "xsum"], "scalars": [1, H], "n": H // 32},
+                          {"op": "qmatmul-q4-x8!", "bind": ["xq", "xs", "xsum", "wg", "g"], "scalars": [1], "n": F,
+                           "phase": "matmul"}]}
+        x0 = synth.normal(6, H)
+        args = [x0, gain, np.zeros(F, np.float32), 1, 1e-6]
+        prog = rt.bind_program(desc, args, roles={"gain": "constant"}, key="mlp", profile=True, weights=wts)
+        with pytest.raises(KeyError):
+            rt.bind_program(desc, args, key="mlp", weights=wts)          # a key binds once
+
+        def ref(x):
+            xn = orc.rms_norm(x, gain, 1, H, 1e-6, 0.0)
+            xq, xs, xsum = orc.quantize_act_i8(xn, 1, H)
+            return orc.matmul_a8_f64(gq, gs, 0, xq, xs, xsum, 1, H, F).ravel()
+        for seed in (6, 7):
+            x = synth.normal(seed, H)
+            got = rt.run_program("mlp", [x, gain, None, 1, 1e-6])
+            assert set(got) == {"g"}                                      # only the written param comes back
+            assert relerr(got["g"], ref(x)) <= 1e-5
+        p = rt.profile_program(prog, [x0, gain, None, 1, 1e-6])
+        assert [k["kernel-name"] for k in p["profile"]] == ["rms-norm!", "quantize-act-i8", "qmatmul-q4-x8!"]
+        assert [k["phase"] for k in p["profile"]] == ["main", "main", "matmul"]
+        assert all(k["ms"] > 0 for k in p["profile"])
+        assert abs(p["kernel-total-ms"] - sum(k["ms"] for k in p["profile"])) < 1e-9
+        assert p["device-wall-ms"] >= 0.999 * p["kernel-total-ms"] and p["host-wall-ms"] > 0
+        assert relerr(p["result"]["g"], ref(x0)) <= 1e-5
+        rt.destroy_program("mlp")
+        with pytest.raises(KeyError):
+            rt.run_program("mlp", args)
+        rows = rt.detect_devices()
+        assert rows[0]["sm-count"] == 148 and rows[0]["memory-bandwidth-gb-s"] > 6000
+        for w in wts.values():
+            w.free()
+    finally:
+        rt.shutdown()

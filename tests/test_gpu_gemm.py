@@ -95,6 +95,32 @@ def test_gemm_quantized_activation_mode(ctx):
     bw.free()
 
 
+def test_quantized_activation_mode_changes_path_at_64_tokens(ctx):
+    """M = 63 runs the exact integer block dots on the decode kernel (2e-6), M = 64 the fp16 tensor-core
+    product of the same codes (1e-3); RSTQ_TUNE_GEMM_MIN_M above M keeps the exact path."""
+    out, in_ = 256, 512
+    w = synth.normal(31, out * in_, 0.02)
+    wq, ws = orc.quantize_weight(w, 4)
+    bw = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
+    x = synth.normal(32, 64 * in_)
+    xq, xs, xsum = orc.quantize_act_i8(x, 64, in_)
+    ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, 64, in_, out).reshape(64, out)
+    n0 = ctx.launch_count()
+    y63 = ctx.qmatmul_host(bw, x[: 63 * in_], 63, L.F32, L.MODE_A8)
+    exact_launches = ctx.launch_count() - n0
+    assert relerr(y63, ref[:63]) <= 2e-6
+    y64 = ctx.qmatmul_host(bw, x, 64, L.F32, L.MODE_A8)
+    assert relerr(y64, ref) <= 1e-3
+    try:
+        ctx.tune(L.TUNE_GEMM_MIN_M, 1000)
+        y64x = ctx.qmatmul_host(bw, x, 64, L.F32, L.MODE_A8)
+    finally:
+        ctx.tune(L.TUNE_GEMM_MIN_M, 17)
+    assert relerr(y64x, ref) <= 2e-6 and exact_launches >= 2
+    assert np.array_equal(y64x[:63].view(np.uint32), y63.view(np.uint32))   # the same kernel, the same sums
+    bw.free()
+
+
 def test_gemm_extreme_magnitudes_stay_finite(ctx):
     out, in_, M = 128, 256, 32
     w = synth.normal(5, out * in_, 1e-6)             # tiny weights: scales far below fp16 range

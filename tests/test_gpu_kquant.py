@@ -177,6 +177,22 @@ def test_q6k_reference_case_and_registry(ctx):
     qm.data["bound"].free()
 
 
+@pytest.mark.parametrize("out,in_", [(8, 256), (72, 1024), (1000, 4096)])
+def test_q6k_kernel_level_call(ctx, out, in_):
+    """qmatmul-q6k-dp4a! through rstq_qmatmul_prequant: q8_K activations with sums per 16 elements (the device
+    quantizer with sub = 16 gives the oracle's arrays bit for bit), against the oracle's unrounded sums."""
+    from raster_b200.quant import kernels_k as qk
+    W, x = gen_centered(out * in_, 3), gen_centered(in_, 4)
+    e = orc.quantize_weight_q6k(W)
+    xp, xs, bsums = qk.quant_act_q8k_gpu(x, in_ // 256, sub=16)
+    oq, os_, ob = orc.quantize_act_q8k(x, in_, 16)
+    assert np.array_equal(xp.view(np.int8), oq) and np.array_equal(xs, os_) and np.array_equal(bsums, ob)
+    y = qk.qmatmul_q6k_dp4a(xp, xs, bsums, e["wq"].view(np.int32), e["sc"], e["ds"], np.zeros(out, np.float32),
+                            in_, out)
+    ycpu, y64 = orc.qmatmul_q6k(oq, os_, ob, e, in_, out)
+    assert relerr(y, y64) <= 1e-5 and np.abs(y - ycpu).max() < 1e-3
+
+
 def test_operators_reproduce_k_quant_golden_vectors(ctx):
     """The committed K-quant vectors (tests/golden/kquant_small.npz): quantizer bit for bit, both
     operators within 1e-5 of the unrounded sums."""
