@@ -95,7 +95,8 @@ typedef struct rstq_event rstq_event;
                                      unit ranges (32-row groups may be shared by neighbouring thread
                                      blocks), 2 = whole 32-row groups per thread block */
 #define RSTQ_TUNE_GEMV_PREFETCH 7  /* decode kernels: KB of a thread block's weight range requested into L2
-                                     ahead of its shared-memory ring (0 = none) */
+                                     ahead of its shared-memory ring; -1 (default) = 64 KB for matrices of
+                                     16 .. 64 MB, none otherwise; 0 = none */
 #define RSTQ_TUNE_PROBE 8         /* only in a library built with -DRSTQ_PROBES=1 (otherwise any value but 0 is
                                      refused): timing probes of the decode kernel, RESULTS ARE INVALID while
                                      set: 1 = the weight stream is not copied (consumer rate alone), 2 = the

@@ -545,7 +545,7 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
             for (auto& ds : ctx->devs) ds.gemv_plan = (int)value;
             return RSTQ_OK;
         case RSTQ_TUNE_GEMV_PREFETCH:
-            RSTQ_REQUIRE(value >= 0 && value <= (1 << 20), RSTQ_E_INVALID, "prefetch distance 0..2^20 KB");
+            RSTQ_REQUIRE(value >= -1 && value <= (1 << 20), RSTQ_E_INVALID, "prefetch distance -1 (by size), 0..2^20 KB");
             for (auto& ds : ctx->devs) ds.gemv_prefetch_kb = value;
             return RSTQ_OK;
         case RSTQ_TUNE_PROBE:

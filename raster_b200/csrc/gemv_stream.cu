@@ -1252,14 +1252,19 @@ static int32_t stream_scratch_ok(const DeviceState& ds, int64_t groups, int G, i
 }
 
 static void fill_common(StreamParams& p, const DeviceState& ds, const StreamPlan& pl, int64_t in,
-                        int64_t out, int M, int64_t nb, int zp) {
+                        int64_t out, int M, int64_t nb, int zp, int bits_of_unit) {
     p.partials = ds.partials; p.flags = ds.counters; p.status = ds.status;
     // timeline: six launch slots of 160 CTA rows each, used in turn
     p.dbg = ds.dbg ? ds.dbg + (size_t)(ds.dbg_launch++ % 6) * 160 * 8 : nullptr;
     p.dbg_fine = ds.dbg ? ds.dbg + 6 * 160 * 8 : nullptr;
     p.in = in; p.out = out; p.uq = pl.uq; p.ur = pl.ur; p.U = ((out + 31) / 32) * nb;
     p.M = M; p.nb = (int)nb; p.G = pl.G; p.zp = zp; p.NS = pl.NS;
-    p.pf_ahead = ds.gemv_prefetch_kb << 10;
+    // L2 requests ahead of the ring: by default 64 KB for matrices of 16 .. 64 MB (a CTA's range is then a
+    // little longer than its ring: the chunks behind the ring would otherwise be requested only when the
+    // consumers free slots); measured: smaller and much larger matrices lose a little with any distance
+    const int64_t wbytes = p.U * unit_bytes(bits_of_unit);
+    p.pf_ahead = ds.gemv_prefetch_kb >= 0 ? ds.gemv_prefetch_kb << 10
+                                          : (wbytes >= (16ll << 20) && wbytes <= (64ll << 20) ? 64ll << 10 : 0);
     p.probe = ds.gemv_probe;
     p.act_off = pl.act_off; p.act2_off = pl.act2_off; p.red_off = pl.red_off; p.bar_off = pl.bar_off;
 }
@@ -1335,7 +1340,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         if (rc != RSTQ_OK) return rc;
         const int NT = M <= 8 ? 1 : 2;
         StreamParams p{};
-        fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp);
+        fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp, a.bits);
         p.w = a.w;
         if (qf) {
             p.x = a.x;
@@ -1437,7 +1442,7 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
         const int T = terms(M), C = M * T;
         const int NT = C <= 8 ? 1 : (C <= 16 ? 2 : 4);
         StreamParams p{};
-        fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp);
+        fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp, a.bits);
         p.w = a.w;
         p.x = (const char*)a.x + m0 * a.in * xe;
         p.y = (char*)a.y + m0 * a.out * ye;

@@ -68,7 +68,7 @@ struct DeviceState {
     bool capturing = false;
     bool pdl = true;               // launch the hot kernels with programmatic stream serialization
     int gemv_plan = 0;             // decode work split: 0 = per shape, 1 = equal unit ranges, 2 = whole groups
-    int64_t gemv_prefetch_kb = 0;  // decode kernels: KB of a CTA's weight range requested into L2 ahead of its ring
+    int64_t gemv_prefetch_kb = -1; // decode kernels: KB of a CTA's weight range requested into L2 ahead of its ring (-1: by size)
     int gemv_probe = 0;            // timing probes of the decode kernel (RSTQ_TUNE_PROBE); results are invalid while set
     bool prefetch_next = true;     // decode launches request the weight that followed this one last time into L2
     rstq_weight* last_decode_w = nullptr;   // the weight of the most recent decode launch on this device
