@@ -1347,6 +1347,77 @@ def run_decoder(args, emit=True):
     return res
 
 
+def run_m1(args):
+    """--case m1:<bits>:<out>:<in>[:<M>] [--tune k=v,k=v ...]: the decode launch (pre-quantized activations) and
+    the operator (MODE_A8, quantizer included) over rotated weight copies (4 x L2 in total), each replayed from
+    one CUDA graph and timed with CUDA events, under the given rstq_tune settings (include/rstq.h: 4 = work
+    split, 6 = quantizer inside the kernel, 7 = own-range L2 distance in KB, 9 = next-weight prefetch, 8 =
+    timing probes of a library built with `python -m raster_b200.build --probes`).
+    --case timeline:<bits>:<out>:<in>: per-CTA phase stamps (rstq_timeline_read) of the last six of 18
+    back-to-back launches, min / median / max over the CTAs, ns after the launch before ended."""
+    import ctypes as C
+    from raster_b200 import Context
+    from raster_b200 import _lib as L
+    from raster_b200 import synth
+    from raster_b200.quant import cpu_quant as cq
+    parts = args.case.split(":")
+    kind, bits, out, in_ = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
+    M = int(parts[4]) if len(parts) > 4 else 1
+    ctx = Context(("cuda:0",))
+    for kv in (args.tune.split(",") if args.tune else []):
+        k, v = kv.split("=")
+        ctx.tune(int(k), int(v))
+    rng = np.random.default_rng(0)
+    codes = rng.integers(0, 256, out * in_ * bits // 8, dtype=np.uint8)
+    scales = (rng.standard_normal(out * (in_ // 32)) * 0.01).astype(np.float32)
+    w0 = ctx.bind_weight(codes, scales, out, in_, L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0, L.LAYOUT_ROWMAJOR)
+    R = 18 if kind == "timeline" else max(3, -(-4 * ctx.device_info()["l2_bytes"] // w0.stream_bytes))
+    ws = [w0] + [w0.clone() for _ in range(R - 1)]
+    x = synth.normal(3, M * in_)
+    a = cq.quantize_act_i8(x, M, in_)
+    bq, bs, bsum = ctx.array_to_buffer(a["xq"]), ctx.array_to_buffer(a["xs"]), ctx.array_to_buffer(a["xsum"])
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    gemv = lambda: [ctx.qmatmul_prequant(w, bq, bs, bsum, by, M) for w in ws]
+    op = lambda: [ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8) for w in ws]
+
+    def graph_of(fn):
+        fn(), fn()                      # the second pass knows the order of the weights
+        ctx.sync()
+        ctx.graph_begin()
+        fn()
+        return ctx.graph_end()
+    if kind == "timeline":
+        gemv(), gemv()
+        ctx.sync()
+        ctx.tune(L.TUNE_TIMELINE, 1)
+        ctx.graph_begin()
+        gemv()
+        g = ctx.graph_end()
+        g.replay()
+        ctx.sync()
+        buf = (C.c_int64 * (6 * 160 * 8))()
+        L.check(ctx.lib.rstq_timeline_read(ctx.handle, buf, 0, 6 * 160 * 8))
+        t = np.array(buf[:]).reshape(6, 160, 8)
+        t0 = None
+        for k in range(6):
+            rows = t[k][t[k][:, 0] > 0]
+            t0 = rows[:, 1].min() if t0 is None else t0
+            r = rows[:, :6] - t0
+            f = lambda c: "%d/%d/%d" % (r[:, c].min(), np.median(r[:, c]), r[:, c].max())
+            print(json.dumps({"launch": 12 + k, "ctas": len(rows), "entry": f(0), "predecessor_done": f(1),
+                              "staged": f(2), "first_weights": f(3), "loop_done": f(4), "exit": f(5)}))
+    else:
+        res = {"case": args.case, "tune": args.tune, "copies": R}
+        for name, fn in (("gemv", gemv), ("op", op)):
+            g = graph_of(fn)
+            us = time_graph(ctx, g, max(3, args.steps // 2), 3) * 1e3 / max(3, args.steps // 2) / R
+            g.destroy()
+            res[name + "_us"] = round(us, 2)
+            res[name + "_GBs"] = round(w0.stream_bytes / us / 1e3, 1)
+        print(json.dumps(res))
+    ctx.close()
+
+
 def run_case(args):
     """One small named case for profiler captures: a few launches of one decode kernel on
     distinct weight copies (more than L2 in total), nothing else.
@@ -1359,6 +1430,9 @@ def run_case(args):
     rng = np.random.default_rng(0)
     ctx = Context(("cuda:0",))
     ctx.tune(L.TUNE_GEMV_PLAN, args.plan)
+    if args.no_prefetch:
+        ctx.tune(L.TUNE_PREFETCH_NEXT, 0)
+        ctx.tune(L.TUNE_GEMV_PREFETCH, 0)
     nb = in_ // 32
     codes = rng.integers(0, 256, out * in_ * bits // 8, dtype=np.uint8)
     scales = (rng.standard_normal(out * nb) * 0.01).astype(np.float32)
@@ -1402,6 +1476,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, help="small single-kernel case for profiler captures")
     ap.add_argument("--plan", type=int, default=0, help="with --case: decode work split (rstq_tune key 4)")
+    ap.add_argument("--tune", default="", help="with --case m1 / timeline: rstq_tune settings, key=value[,key=value ...]")
+    ap.add_argument("--no-prefetch", action="store_true",
+                    help="with --case gemv: no L2 requests ahead (neither the next weight nor the own range)")
     args = ap.parse_args()
     if args.case and args.case.startswith("decoder"):
         world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -1416,6 +1493,8 @@ def main():
         return run_q4k(args)
     if args.case and args.case.startswith("attn"):
         return run_attn(args)
+    if args.case and args.case.startswith(("m1:", "timeline:")):
+        return run_m1(args)
     if args.case:
         return run_case(args)
     args.warmup = max(args.warmup, 3)
