@@ -133,8 +133,7 @@ __device__ __forceinline__ void imma_acc(int (&d)[4], const uint32_t (&a)[4], ui
 // A8, M == 1: srec [nb][4 tig] uint4 {xq word tig, xq word 4+tig, xs_t bits, c_t}: lane tig
 //            folds row gid + 8*tig only (all eight tile columns are the same token), so the
 //            record carries that row's constants: for 4-bit codes the rows of odd tig sit in
-//            the high nibbles (tile value x16, taken as a difference of two tile rows: see row_fold):
-//            xs_t = xs/16 and c_t = bias - 16*zp*xsum + 1;
+//            the high nibbles (tile value x16): xs_t = xs/16 and c_t = bias - 16*zp*xsum;
 //            otherwise xs_t = xs and c_t = bias - zp*xsum (bias = bits of 2^23 + 2^22).
 // A8, M > 1 : sB [nb][M][4 tig] uint2 {xq word tig, xq word 4+tig};
 //             sxz [nb][Mz] int2 {xs bits, zp*xsum}, Mz = M rounded up to even.
@@ -168,7 +167,7 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
                     r.x = wa[j];
                     r.y = wb[j];
                     r.z = __float_as_uint(hi ? xs[j] * 0.0625f : xs[j]);
-                    r.w = (uint32_t)(kMagicInt - (p.zp * zs[j]) * (hi ? 16 : 1) + (hi ? 1 : 0));
+                    r.w = (uint32_t)(kMagicInt - (p.zp * zs[j]) * (hi ? 16 : 1));
                     srec[i] = r;
                 }
             }
@@ -324,7 +323,7 @@ __device__ __forceinline__ void stage_a8_quant(const StreamParams& p, uint8_t* s
             r.x = wa;
             r.y = wb;
             r.z = __float_as_uint(hi ? xs * 0.0625f : xs);
-            r.w = (uint32_t)(kMagicInt - (p.zp * sum) * (hi ? 16 : 1) + (hi ? 1 : 0));
+            r.w = (uint32_t)(kMagicInt - (p.zp * sum) * (hi ? 16 : 1));
             srec[i] = r;
         }
     }
@@ -409,12 +408,8 @@ __device__ __forceinline__ void a_frags(const SUnit<BITS>& u, uint32_t (&a)[2][4
 // shared-memory addresses: `codes` = the lane's 16-byte slot of a unit, `scale` = the f32 scale of
 // its row, `rec` = its staged record {xq word tig, xq word 4 + tig, xs_t, c_t}.
 //
-// 4-bit codes: the low-nibble rows (gid, gid + 16) take the masked word, the high-nibble rows
-// (gid + 8, gid + 24) take the word AS IT IS: as unsigned bytes 16*h + l, so their tile row holds
-// 16*dot(h) + dot(l), and dot(l) is the tile row of the low-nibble partner.  A lane of a high-nibble row
-// (odd tig) therefore folds d_hi - d_lo = 16*dot(h), written (d_hi & m) + (d_lo ^ m) + c with m = ~0 and the
-// "+ 1" of the two's complement inside its staged constant c; an even lane (m = 0) folds d_lo + c.
-// One mask per word instead of two.
+// 4-bit codes: two masks per word give the low-nibble rows (gid, gid + 16) and the high-nibble rows
+// (gid + 8, gid + 24), the latter multiplied by 16 (undone in the staged scale and constant).
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
@@ -441,9 +436,9 @@ template <int BITS>
 __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bool upper, float acc) {
     uint32_t a[2][4];
     if (BITS == 4) {
-        const uint32_t lo = 0x0F0F0F0Fu;
-        a[0][0] = u.c0.x & lo; a[0][1] = u.c0.x; a[0][2] = u.c0.y & lo; a[0][3] = u.c0.y;
-        a[1][0] = u.c0.z & lo; a[1][1] = u.c0.z; a[1][2] = u.c0.w & lo; a[1][3] = u.c0.w;
+        const uint32_t lo = 0x0F0F0F0Fu, hi = 0xF0F0F0F0u;
+        a[0][0] = u.c0.x & lo; a[0][1] = u.c0.x & hi; a[0][2] = u.c0.y & lo; a[0][3] = u.c0.y & hi;
+        a[1][0] = u.c0.z & lo; a[1][1] = u.c0.z & hi; a[1][2] = u.c0.w & lo; a[1][3] = u.c0.w & hi;
     } else {
         a[0][0] = u.c0.x; a[0][1] = u.c0.y; a[0][2] = u.c1.x; a[0][3] = u.c1.y;
         a[1][0] = u.c0.z; a[1][1] = u.c0.w; a[1][2] = u.c1.z; a[1][3] = u.c1.w;
@@ -453,7 +448,7 @@ __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bo
     imma_u8s8(d1, a[1], u.r.x, u.r.y);
     // tig 0 -> d0[0] (row gid), 1 -> d0[2] (gid+8), 2 -> d1[0] (gid+16), 3 -> d1[2] (gid+24)
     const uint32_t lo = (uint32_t)(upper ? d1[0] : d0[0]), hi = (uint32_t)(upper ? d1[2] : d0[2]);
-    const uint32_t iv = BITS == 4 ? (hi & m) + (lo ^ m) + u.r.w : (m ? hi : lo) + u.r.w;
+    const uint32_t iv = (m ? hi : lo) + u.r.w;
     const float f = __uint_as_float(iv) - kMagicFlt;
     return fmaf(u.sc * __uint_as_float(u.r.z), f, acc);
 }
