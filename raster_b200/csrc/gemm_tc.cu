@@ -256,6 +256,32 @@ __device__ __forceinline__ uint32_t scale_h2(float s) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// The conversion of gemm_tmem_kernel: one fused multiply-add per pair of weights.  A byte b placed
+// in the low byte of a half (0x00bb) IS the fp16 subnormal b * 2^-24, so
+//     fma(0x00bb, s, -zero * 2^-24 * s) = (b - zero) * s * 2^-24, rounded once:
+// the product is exact inside the fma and the addend, a power of two times the already rounded
+// scale s, is exact as well, which makes the result the same bits as subtracting the zero point
+// first (exact integers) and multiplying by s afterwards, in half the instructions.  The caller
+// folds the 2^-24 into the scale.
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+// bytes 0..3 of `bytes` (other bits of each byte pair must be zero) -> four halves v * scale + add
+__device__ __forceinline__ uint2 bytes_fma_h4(uint32_t bytes, uint32_t scale2, uint32_t add2) {
+    uint2 r;
+    r.x = hfma2_u32(__byte_perm(bytes, 0u, 0x4140), scale2, add2);
+    r.y = hfma2_u32(__byte_perm(bytes, 0u, 0x4342), scale2, add2);
+    return r;
+}
+constexpr int kSubnormalShift = 8;  // block scales carry 2^8 more: code * 2^-24 * (s * 2^8) stays in fp16 range
+
 template <int BITS, int NTOK>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
@@ -504,6 +530,7 @@ constexpr int kGemmThreadsT = (3 + kDqWarps) * 32;  // TMA warp, MMA warp (even 
 // accumulators, at most 6
 __host__ __device__ constexpr int gemm_stages(int ntok) { return (512 - 2 * ntok) / 64 > 6 ? 6 : (512 - 2 * ntok) / 64; }
 constexpr int kAColsPerStage = kKStep / 2;
+constexpr int kWeightPfSteps = 8;  // K-steps of packed weights requested into L2 ahead of the loads
 
 __device__ __forceinline__ void tmem_st_16x256b_x2(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr),
@@ -627,8 +654,25 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     volatile int* abort_flag = &s_abort;
     const int ksteps = min(p.ksteps, p.ksteps_total - ks_begin);
 
+    // four-stage ring and whole K-steps: the dequant warps work as two sets of eight on alternate
+    // K-steps (see there), so a stage collects eight arrivals instead of sixteen
+    const bool paired = kNSTT == 4 && (p.nb & 3) == 0;
+    if (tid == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
+    if (paired && warp >= 2 && warp < 2 + kDqWarps) {
+        // the first weights this warp will load: ask for them now, so that the HBM round trip
+        // runs while the CTA sets itself up (barriers, tensor memory, the CTA-wide sync)
+        const int t = (warp - 2) >> 2, pset = t & 1, blk0 = 2 * (t >> 1);
+        int64_t g = (int64_t)ft * 4 + (warp & 3);
+        g = g < p.ngroups ? g : (int64_t)p.ngroups - 1;
+        const uint8_t* q = p.w + (g * p.nb + 4 * (ks_begin + pset) + blk0) * UNIT + lane * 128;
+        if (lane * 128 < 2 * UNIT) {
+#pragma unroll
+            for (int d = 0; d < 2; ++d)
+                if (pset + 2 * d < ksteps) asm volatile("prefetch.global.L2 [%0];" ::"l"(q + (size_t)d * 8 * UNIT));
+        }
+    }
     if (tid < kNSTT) {
-        mbar_init(full + 8 * tid, kDqWarps + 1);
+        mbar_init(full + 8 * tid, (paired ? kDqWarps / 2 : kDqWarps) + 1);
         mbar_init(empty + 8 * tid, 1);
     } else if (tid == kNSTT) {
         mbar_init(acc_full, ksteps >= 2 ? 2 : 1);  // one arrival per MMA issuer that has steps
@@ -650,11 +694,37 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     if (warp == 0) {
         // ---------------- TMA producer of the activation tiles ----------------
         if (lane == 0) {
+            // The dequant warps read the packed weights with plain loads a few K-steps ahead, which
+            // covers an L2 round trip but not one to HBM.  This thread therefore asks for the
+            // weights to be brought into L2 kPfSteps K-steps ahead of those loads, four K-steps (16
+            // units, one contiguous run per row group) per request.
+            constexpr int kPfSteps = kWeightPfSteps;
+            const int nb_end = min(p.nb, 4 * (ks_begin + ksteps));
+            auto request = [&](int ks) {  // K-steps ks .. ks + 3 of this CTA's range
+                const int b0 = 4 * (ks_begin + ks);
+                const int nblk = min(16, nb_end - b0);
+                if (nblk <= 0) return;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int64_t gg = (int64_t)ft * 4 + g;
+                    if (gg < p.ngroups) {
+                        const uint8_t* q = p.w + (gg * p.nb + b0) * UNIT;
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(q), "r"((uint32_t)(nblk * UNIT))
+                                     : "memory");
+                    }
+                }
+            };
             asm volatile("griddepcontrol.wait;" ::: "memory");  // activations come from the pre-pass
             int s = 0, issued = 0;
             uint32_t ph = 0;
             bool ok = true;
             for (int ks = 0; ks < ksteps; ++ks) {
+                // weight requests: none before the wait above (they would compete for HBM with the
+                // pre-pass this kernel waits for) nor before the first activation tiles are on their
+                // way; the dequant warps load K-steps 0 .. 3 themselves
+                if (kPfSteps > 0 && ks == kNSTT)
+                    for (int k2 = 4; k2 < 8 + kPfSteps; k2 += 4) request(k2);
+                if (kPfSteps > 0 && (ks & 3) == 0 && ks >= 4) request(ks + 4 + kPfSteps);
                 ok = mbar_block(empty + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
                 const uint32_t dst = sbase + s * BSTAGE;
@@ -707,7 +777,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                 umma_commit_if(empty + 8 * s, leader);  // the stage is free once these MMAs have read it
                 any = true;
                 if (ks + 2 < ksteps && !n2) ok = mbar_spin(full + 8 * s2, ph2, abort_flag);
-                s = s2;
+                    s = s2;
                 ph = ph2;
             }
             if (dbg && lane == 0) dbg[307 + 2 * m] = (unsigned long long)clock64();
@@ -748,20 +818,23 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
         const float wmul = p.wmul;
         // this warp's rows are tensor-memory lanes 32*grp .. 32*grp + 31; its block is 16 columns wide
         const uint32_t t_lane = (uint32_t)(grp * 32) << 16;
-        auto convert_store = [&](const RawT<BITS>& r, uint32_t a_stage) {
-            const uint32_t dst = a_stage + t_lane + sub * 16;
+        auto convert_store = [&](const RawT<BITS>& r, uint32_t a_stage, int blk) {
+            const uint32_t dst = a_stage + t_lane + blk * 16;
             const float sc[4] = {r.s.x, r.s.y, r.s.z, r.s.w};
             if constexpr (BITS == 4) {
-                const uint32_t off = 0x64086408u;  // 1024 + zero point 8
+                constexpr uint32_t kZero = 0x80088008u;   // -8 * 2^-24 twice
+                constexpr uint32_t kSixteenth = 0x2C002C00u;
                 const uint32_t w[4] = {r.c.x, r.c.y, r.c.z, r.c.w};
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {  // rows gid + 16q (low nibbles) and gid + 16q + 8 (high)
                     const uint32_t s_lo = scale_h2(sc[2 * q] * wmul), s_hi = scale_h2(sc[2 * q + 1] * wmul);
+                    const uint32_t z_lo = hmul2_u32(s_lo, kZero), z_hi = hmul2_u32(s_hi, kZero);
+                    const uint32_t s_hi16 = hmul2_u32(s_hi, kSixteenth);  // high nibbles stay where they are: 16 n
                     uint32_t v[8];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {  // columns 8h .. 8h + 7: elements 16h + 4tig ..
-                        const uint2 lo = bytes_to_h4(w[2 * q + h] & 0x0F0F0F0Fu, off, s_lo);
-                        const uint2 hi = bytes_to_h4((w[2 * q + h] >> 4) & 0x0F0F0F0Fu, off, s_hi);
+                        const uint2 lo = bytes_fma_h4(w[2 * q + h] & 0x0F0F0F0Fu, s_lo, z_lo);
+                        const uint2 hi = bytes_fma_h4(w[2 * q + h] & 0xF0F0F0F0u, s_hi16, z_hi);
                         v[4 * h + 0] = lo.x;
                         v[4 * h + 1] = lo.y;
                         v[4 * h + 2] = hi.x;
@@ -770,48 +843,120 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                     tmem_st_16x256b_x2(dst + ((uint32_t)(16 * q) << 16), v);
                 }
             } else {
-                const uint32_t off = 0x64806480u;  // 1024 + zero point 128
+                constexpr uint32_t kZero = 0x80808080u;  // -128 * 2^-24 twice
                 const uint32_t w0[4] = {r.c0.x, r.c0.y, r.c0.z, r.c0.w}, w1[4] = {r.c1.x, r.c1.y, r.c1.z, r.c1.w};
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {  // rows gid + 16q (i = 2q) and gid + 16q + 8 (i = 2q + 1)
                     const uint32_t s_a = scale_h2(sc[2 * q] * wmul), s_b = scale_h2(sc[2 * q + 1] * wmul);
+                    const uint32_t z_a = hmul2_u32(s_a, kZero), z_b = hmul2_u32(s_b, kZero);
                     uint32_t v[8];
-                    const uint2 a0 = bytes_to_h4(w0[2 * q], off, s_a), b0 = bytes_to_h4(w0[2 * q + 1], off, s_b);
-                    const uint2 a1 = bytes_to_h4(w1[2 * q], off, s_a), b1 = bytes_to_h4(w1[2 * q + 1], off, s_b);
+                    const uint2 a0 = bytes_fma_h4(w0[2 * q], s_a, z_a), b0 = bytes_fma_h4(w0[2 * q + 1], s_b, z_b);
+                    const uint2 a1 = bytes_fma_h4(w1[2 * q], s_a, z_a), b1 = bytes_fma_h4(w1[2 * q + 1], s_b, z_b);
                     v[0] = a0.x; v[1] = a0.y; v[2] = b0.x; v[3] = b0.y;   // plane 0: columns 0..7
                     v[4] = a1.x; v[5] = a1.y; v[6] = b1.x; v[7] = b1.y;   // plane 1: columns 8..15
                     tmem_st_16x256b_x2(dst + ((uint32_t)(16 * q) << 16), v);
                 }
             }
         };
+        // one K-step of this warp: wait for the stage, convert, store, hand over
+        auto step = [&](const RawT<BITS>& r, int st, uint32_t parity) -> bool {
+            if (!__all_sync(0xffffffffu, mbar_block(empty + 8 * st, parity, abort_flag))) return false;
+            tc_fence_after();
+            convert_store(r, tmem + A_COL0 + st * kAColsPerStage, sub);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full + 8 * st);
+            return true;
+        };
 
-        RawT<BITS> raw[kPrefetch];
-#pragma unroll
-        for (int j = 0; j < kPrefetch; ++j) load(raw[j]);
-        int s = 0;
-        uint32_t ph = 0;
         bool ok = true;
-        for (int ks0 = 0; ks0 < ksteps && ok; ks0 += kPrefetch) {
+        if (paired) {
+            // Two sets of eight warps take alternate K-steps, a warp converting two adjacent
+            // blocks of its row group per step: while one set converts, the other waits for its
+            // stage or stores, so the issue slots do not idle between bursts, and the fixed cost
+            // of a step (barrier test, store wait, arrival) is paid once per two units.
+            // Own step i of set `pset` is K-step pset + 2i, stage pset + 2 (i & 1), ring pass i / 2.
+            const int t = dq >> 2, pset = t & 1, blk0 = 2 * (t >> 1);
+            const int n_own = (ksteps - pset + 1) >> 1;
+            const int64_t g_ld = g_valid ? g_glob : (int64_t)p.ngroups - 1;
+            const uint8_t* wl = p.w + (g_ld * p.nb + 4 * (ks_begin + pset) + blk0) * UNIT + lane * 16;
+            const uint32_t s_delta = (uint32_t)(CODES + gid * 16 - lane * 16);
+            auto fetch2 = [&](RawT<BITS> (&r)[2], int own_off) {
+                const uint8_t* q = wl + (size_t)own_off * (8 * UNIT);
 #pragma unroll
-            for (int j = 0; j < kPrefetch; ++j) {
-                const int ks = ks0 + j;
-                if (ks < ksteps && ok) {
-                    ok = __all_sync(0xffffffffu, mbar_block(empty + 8 * s, ph ^ 1u, abort_flag));
-                    if (ok) {
-                        tc_fence_after();
-                        convert_store(raw[j], tmem + A_COL0 + s * kAColsPerStage);
-                        tmem_st_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(full + 8 * s);
-                        load(raw[j]);
-                        if (++s == kNSTT) { s = 0; ph ^= 1u; }
+                for (int u = 0; u < 2; ++u, q += UNIT) {
+                    if constexpr (BITS == 4) {
+                        r[u].c = __ldg(reinterpret_cast<const uint4*>(q));
+                    } else {
+                        r[u].c0 = __ldg(reinterpret_cast<const uint4*>(q));
+                        r[u].c1 = __ldg(reinterpret_cast<const uint4*>(q + 512));
+                    }
+                    r[u].s = __ldg(reinterpret_cast<const float4*>(q + s_delta));
+                }
+            };
+            auto step2 = [&](const RawT<BITS> (&r)[2], int st, uint32_t parity) -> bool {
+                if (!__all_sync(0xffffffffu, mbar_block(empty + 8 * st, parity, abort_flag))) return false;
+                tc_fence_after();
+                    const uint32_t a_stage = tmem + A_COL0 + st * kAColsPerStage;
+                convert_store(r[0], a_stage, blk0);
+                convert_store(r[1], a_stage, blk0 + 1);
+                    tmem_st_wait();
+                    tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full + 8 * st);
+                    return true;
+            };
+            RawT<BITS> raw[2][2];
+#pragma unroll
+            for (int d = 0; d < 2; ++d) {
+                raw[d][0] = RawT<BITS>{};
+                raw[d][1] = RawT<BITS>{};
+                if (d < n_own) fetch2(raw[d], d);
+            }
+            uint32_t par = 1;  // parity of "stage free": the first pass through the ring finds every stage free
+            int i = 0;
+            for (; i + 2 <= n_own && ok; i += 2) {
+                ok = step2(raw[0], pset, par);
+                if (i + 2 < n_own) fetch2(raw[0], 2);
+                if (ok) {
+                    ok = step2(raw[1], pset + 2, par);
+                    if (i + 3 < n_own) fetch2(raw[1], 3);
+                }
+                wl += (size_t)16 * UNIT;
+                par ^= 1u;
+            }
+            if (ok && i < n_own) ok = step2(raw[0], pset, par);
+        } else {
+            RawT<BITS> raw[kPrefetch];
+#pragma unroll
+            for (int j = 0; j < kPrefetch; ++j) load(raw[j]);
+            int s = 0;
+            uint32_t ph = 0;
+            for (int ks0 = 0; ks0 < ksteps && ok; ks0 += kPrefetch) {
+#pragma unroll
+                for (int j = 0; j < kPrefetch; ++j) {
+                    const int ks = ks0 + j;
+                    if (ks < ksteps && ok) {
+                        ok = step(raw[j], s, ph ^ 1u);
+                        if (ok) {
+                            load(raw[j]);
+                            if (++s == kNSTT) { s = 0; ph ^= 1u; }
+                        }
                     }
                 }
             }
         }
 
         // ---------------- epilogue: tensor memory -> y ----------------
+        // this warp's token scales, one per lane, fetched while the last MMAs run
+        // (the pre-pass that wrote them completed before any activation tile was loaded)
+        float rs_lane = 0.f;
+        if (ok) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            const int tl = tok0 + (dq >> 2) * (NTOK / 4) + lane;
+            if (lane < NTOK / 4 && tl < p.M) rs_lane = __ldg(p.rowscale + tl);
+        }
         if (ok) {
             const bool got = mbar_block(acc_full, 0, abort_flag);
             ok = __all_sync(0xffffffffu, got);
@@ -857,8 +1002,8 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
 #pragma unroll
                 for (int t0 = 0; t0 < CPW; t0 += 8) {
                     const int t = t0 + (lane >> 2), tok = tokb + t;
+                    const float sc = wdiv * __shfl_sync(0xffffffffu, rs_lane, t);
                     if (tok < p.M && f0 < p.out) {
-                        const float sc = wdiv * __ldg(p.rowscale + tok);
                         const float4 a = *reinterpret_cast<const float4*>(tile + t * LD + fg);
                         const float4 c = *reinterpret_cast<const float4*>(tile + t * LD + fg + 4);
                         if (p.out_dtype == RSTQ_BF16) {
@@ -875,28 +1020,18 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                         }
                     }
                 }
-            } else if (f < p.out && p.ksplit > 1) {
-                // two K ranges add their halves into a zeroed f32 array: a + b in either order
-                float* y = p.acc32 + f;
+            } else {
+                // one element per store (a lane owns one feature); with two K ranges the halves
+                // are added into a zeroed f32 array: a + b in either order
+                const bool f_ok = f < p.out;
 #pragma unroll
-                for (int j = 0; j < CPW; ++j)
-                    if (tokb + j < p.M)
-                        atomicAdd(y + (int64_t)(tokb + j) * p.out,
-                                  __uint_as_float(v[j]) * wdiv * __ldg(p.rowscale + tokb + j));
-            } else if (f < p.out) {
-                if (p.out_dtype == RSTQ_BF16) {
-                    __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) + f;
-#pragma unroll
-                    for (int j = 0; j < CPW; ++j)
-                        if (tokb + j < p.M)
-                            y[(int64_t)(tokb + j) * p.out] =
-                                __float2bfloat16_rn(__uint_as_float(v[j]) * wdiv * __ldg(p.rowscale + tokb + j));
-                } else {
-                    float* y = reinterpret_cast<float*>(p.y) + f;
-#pragma unroll
-                    for (int j = 0; j < CPW; ++j)
-                        if (tokb + j < p.M)
-                            y[(int64_t)(tokb + j) * p.out] = __uint_as_float(v[j]) * wdiv * __ldg(p.rowscale + tokb + j);
+                for (int j = 0; j < CPW; ++j) {
+                    const float val = __uint_as_float(v[j]) * wdiv * __shfl_sync(0xffffffffu, rs_lane, j);
+                    if (f_ok && tokb + j < p.M) {
+                        const int64_t at = (int64_t)(tokb + j) * p.out + f;
+                        if (p.ksplit > 1) atomicAdd(p.acc32 + at, val);
+                        else store_out(p.y, p.out_dtype, at, val);
+                    }
                 }
             }
         }
@@ -963,6 +1098,22 @@ static cudaError_t launch_pdl(K kernel, dim3 grid, dim3 block, size_t smem, cons
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// x (src 0 = f32, 1 = bf16, 2 = int8 codes with per-block scales xs) -> fp16 rows x16 and 2^e per row
+static int32_t launch_act_to_f16(rstq_ctx* ctx, DeviceState& ds, const void* x, const float* xs, int src, void* x16,
+                                 float* rowscale, int64_t M, int64_t in) {
+    cudaError_t le;
+    const dim3 grid((unsigned)M), block(256);
+    if (src == 0)
+        le = launch_pdl(act_to_f16_kernel<0>, grid, block, 0, ds, x, xs, (__half*)x16, rowscale, in);
+    else if (src == 1)
+        le = launch_pdl(act_to_f16_kernel<1>, grid, block, 0, ds, x, xs, (__half*)x16, rowscale, in);
+    else
+        le = launch_pdl(act_to_f16_kernel<2>, grid, block, 0, ds, x, xs, (__half*)x16, rowscale, in);
+    ctx->launches++;
+    RSTQ_CUDA(le);
+    return RSTQ_OK;
+}
+
 // y[M, out] = x[M, in] . dequant(W)^T on the tensor cores.  src: 0 = f32 x, 1 = bf16 x,
 // 2 = int8 codes x with per-block scales xs.  x16 / rowscale are caller-provided scratch
 // (M*in fp16, M floats).
@@ -981,23 +1132,15 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
                  "activation scratch must be 16-byte aligned");
     EncodeTiledFn enc = encode_tiled_fn();
     RSTQ_REQUIRE(enc, RSTQ_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    // pre-pass: activations -> fp16 with one exponent per token row (kind::f16 wants A and B of
-    // one type, and fp16 keeps three more mantissa bits of the weights than bf16 would)
+    // pre-pass: activations -> fp16 with one exponent per token row.  kind::f16 wants A and B of
+    // one type (fp16 weights against bf16 activations raise "illegal instruction"), and fp16 on
+    // both sides keeps three more mantissa bits of the weights than bf16 would.
     const bool a_in_tmem = ctx->tune_gemm_kernel != 1;
-    cudaError_t le;
-    if (src == 0)
-        le = launch_pdl(act_to_f16_kernel<0>, dim3((unsigned)M), dim3(256), 0, ds, x, xs, (__half*)x16,
-                        rowscale, w->in);
-    else if (src == 1)
-        le = launch_pdl(act_to_f16_kernel<1>, dim3((unsigned)M), dim3(256), 0, ds, x, xs, (__half*)x16,
-                        rowscale, w->in);
-    else
-        le = launch_pdl(act_to_f16_kernel<2>, dim3((unsigned)M), dim3(256), 0, ds, x, xs, (__half*)x16,
-                        rowscale, w->in);
-    ctx->launches++;
-    RSTQ_CUDA(le);
-
     const int ntok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    int32_t rc = launch_act_to_f16(ctx, ds, x, xs, src, x16, rowscale, M, w->in);
+    if (rc != RSTQ_OK) return rc;
+    cudaError_t le;
+
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {(cuuint64_t)w->in, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)w->in * 2};
@@ -1019,8 +1162,10 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     p.M = (int)M;
     p.ksteps_total = (int)((w->nb + 3) / 4);
     p.ttiles = (int)((M + ntok - 1) / ntok);
-    p.wmul = ldexpf(1.0f, w->gemm_exp);
-    p.wdiv = ldexpf(1.0f, -w->gemm_exp);
+    // gemm_tmem_kernel converts codes as fp16 subnormals (code * 2^-24): its block scales carry
+    // 2^kSubnormalShift more and the result the remaining 2^(24 - kSubnormalShift)
+    p.wmul = ldexpf(1.0f, w->gemm_exp + (a_in_tmem ? kSubnormalShift : 0));
+    p.wdiv = ldexpf(1.0f, -w->gemm_exp + (a_in_tmem ? 24 - kSubnormalShift : 0));
     p.out_dtype = out_dtype;
     p.dbg = ds.dbg;
     const int64_t ftiles = (w->out + 127) / 128;
