@@ -996,7 +996,7 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
 }
 
 // ---- host-array operators -----------------------------------------------------
-// A fingerprint of the host arrays (64 samples of 8 bytes spread over the codes, 64 over the
+// A fingerprint of the host arrays (8 samples of 8 bytes spread over the codes, 8 over the
 // scales): the cache is keyed by address, and a caller may free a matrix and get the same address
 // back for another one of the same shape.  A hit whose fingerprint differs is bound again.
 static uint64_t host_fingerprint(const void* codes, int64_t code_bytes, const float* scales, int64_t nscales) {
@@ -1004,14 +1004,16 @@ static uint64_t host_fingerprint(const void* codes, int64_t code_bytes, const fl
     auto mix = [&](uint64_t v) { h = (h ^ v) * 0xBF58476D1CE4E5B9ull; h ^= h >> 29; };
     const uint8_t* c = (const uint8_t*)codes;
     const int64_t cw = code_bytes / 8;
-    for (int i = 0; i < 64 && cw > 0; ++i) {
+    // eight samples of each: every sample is a cache miss on a matrix that was not touched since
+    // the last call (about 40 ns apiece), and this runs on every host-array call
+    for (int i = 0; i < 8 && cw > 0; ++i) {
         uint64_t v;
-        memcpy(&v, c + (cw - 1) * i / 63 * 8, 8);
+        memcpy(&v, c + (cw - 1) * i / 7 * 8, 8);
         mix(v);
     }
-    for (int i = 0; i < 64 && nscales > 0; ++i) {
+    for (int i = 0; i < 8 && nscales > 0; ++i) {
         uint32_t v;
-        memcpy(&v, scales + (nscales - 1) * i / 63, 4);
+        memcpy(&v, scales + (nscales - 1) * i / 7, 4);
         mix(v);
     }
     return h;
