@@ -108,6 +108,11 @@ typedef struct rstq_event rstq_event;
                                      only: results never depend on it.  A launch recorded in a graph keeps
                                      naming that weight: destroy graphs before freeing weights they ran beside.
                                      0 = off */
+#define RSTQ_TUNE_ACT_IMAGE 10    /* 1 (default) = rstq_qmatmul in MODE_A8 at 2 <= M <= 16: the activation quantizer
+                                     also writes the codes, scales and sums in the order the decode kernel
+                                     keeps them in shared memory, and that kernel's copy thread brings them
+                                     in with bulk copies beside the weight stream; 0 = the kernel's warps
+                                     gather them from the quantizer's row-major output first */
 #define RSTQ_TUNE_FUSE_QUANT 6    /* 1 (default) = rstq_qmatmul in MODE_A8 at M = 1 quantizes the
                                      activations inside the decode kernel; 0 = separate quantizer launch */
 

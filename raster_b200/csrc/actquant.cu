@@ -23,7 +23,7 @@ __device__ __forceinline__ int round_half_up(double v) {
 template <bool BF16IN>
 __global__ void __launch_bounds__(256)
 quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float* __restrict__ xs,
-                    int32_t* __restrict__ xsum, int64_t nblocks) {
+                    int32_t* __restrict__ xsum, int64_t nblocks, uint8_t* __restrict__ img, int M, int nb, int zp) {
     // programmatic dependent launch: let the consumer kernel start its weight stream now;
     // x may come from the kernel before this one, so wait for it
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -54,11 +54,24 @@ quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float*
             xs[blk] = (float)d;
             if (xsum) xsum[blk] = s;
         }
+        if (img) {
+            // The decode kernel's staged form of the same data, for M > 1 (block-major, the eight
+            // code words of a (block, token) as four (word tg, word 4 + tg) pairs; then per (block,
+            // token) the scale and zero-point x code sum), so that it can take it with a bulk copy.
+            const int c = (int)(blk / nb), b = (int)(blk - (int64_t)c * nb);   // token, block
+            const int j = lane >> 2;                                            // word held by lanes 0, 4, .. 28
+            if ((lane & 3) == 0)
+                reinterpret_cast<uint32_t*>(img)[((int64_t)(b * M + c) * 4 + (j & 3)) * 2 + (j >> 2)] = w;
+            const int Mz = (M + 1) & ~1;
+            int2* z = reinterpret_cast<int2*>(img + (((int64_t)nb * M * 32 + 127) & ~127ll));
+            if (lane == 0) z[(int64_t)b * Mz + c] = make_int2(__float_as_int((float)d), zp * s);
+            if (lane == 1 && c == M - 1 && Mz > M) z[(int64_t)b * Mz + M] = make_int2(0, 0);
+        }
     }
 }
 
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
-                            int32_t* xsum, int64_t M, int64_t in, int act_dtype) {
+                            int32_t* xsum, int64_t M, int64_t in, int act_dtype, uint8_t* img, int zp) {
     const int64_t nblocks = M * (in / 32);
     int64_t ctas = (nblocks + 7) / 8;  // 8 warps per CTA
     const int64_t cap = (int64_t)ds.sm_count * 8;
@@ -74,9 +87,11 @@ int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_
     cfg.attrs = attr;
     cfg.numAttrs = ds.pdl ? 1 : 0;
     if (act_dtype == RSTQ_BF16)
-        RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel<true>, x, xq, xs, xsum, nblocks));
+        RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel<true>, x, xq, xs, xsum, nblocks, img, (int)M,
+                                     (int)(in / 32), zp));
     else
-        RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel<false>, x, xq, xs, xsum, nblocks));
+        RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel<false>, x, xq, xs, xsum, nblocks, img, (int)M,
+                                     (int)(in / 32), zp));
     ctx->launches++;
     RSTQ_CUDA(cudaGetLastError());
     return RSTQ_OK;

@@ -120,17 +120,21 @@ struct ActScratch {
     int8_t* xq;
     float* xs;
     int32_t* xsum;
+    uint8_t* img;   // the decode kernel's staged form of the three (2 <= M <= 16), see quant_act_i8_kernel
 };
 static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* out) {
     const int64_t nb = in / 32;
     const int64_t xq_bytes = (M * in + 255) & ~255ll;
     const int64_t sb = (M * nb * 4 + 255) & ~255ll;
-    int32_t rc = dev_reserve(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 2 * sb);
+    const bool image = M >= 2 && M <= 16;
+    const int64_t img_bytes = image ? ((nb * M * 32 + 127) & ~127ll) + ((nb * ((M + 1) & ~1ll) * 8 + 255) & ~255ll) : 0;
+    int32_t rc = dev_reserve(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 2 * sb + img_bytes);
     if (rc != RSTQ_OK) return rc;
     char* base = (char*)ds.act_scratch;
     out->xq = (int8_t*)base;
     out->xs = (float*)(base + xq_bytes);
     out->xsum = (int32_t*)(base + xq_bytes + sb);
+    out->img = image ? (uint8_t*)(base + xq_bytes + 2 * sb) : nullptr;
     return RSTQ_OK;
 }
 
@@ -153,8 +157,10 @@ static NextWeight note_decode_launch(rstq_ctx* ctx, DeviceState& ds, rstq_weight
 
 // One matmul over device pointers, M split into decode-kernel chunks.
 static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs,
-                      const int32_t* xsum, float* y, int64_t M, const TpFuse* tp = nullptr) {
+                      const int32_t* xsum, float* y, int64_t M, const TpFuse* tp = nullptr,
+                      const uint8_t* img = nullptr) {
     GemvA8Args a{w->data, xq, xs, xsum, y, M, w->in, w->out, w->bits, w->zp, tp};
+    a.img = img;
     a.next = note_decode_launch(ctx, ctx->devs[w->dev], w);
     return launch_gemv_a8(ctx, ctx->devs[w->dev], a);
 }
@@ -250,9 +256,10 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
         ActScratch s;
         int32_t rc = act_scratch(ds, M, w->in, &s);
         if (rc != RSTQ_OK) return rc;
-        rc = launch_quant_act_i8(ctx, ds, x, s.xq, s.xs, s.xsum, M, w->in, act_dtype);
+        uint8_t* img = (!tc && ds.act_image) ? s.img : nullptr;
+        rc = launch_quant_act_i8(ctx, ds, x, s.xq, s.xs, s.xsum, M, w->in, act_dtype, img, w->zp);
         if (rc != RSTQ_OK) return rc;
-        if (!tc) return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M, tp);
+        if (!tc) return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M, tp, img);
         void* x16;
         float* rowscale;
         float* acc;
@@ -559,6 +566,9 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
 #endif
         case RSTQ_TUNE_PREFETCH_NEXT:
             for (auto& ds : ctx->devs) ds.prefetch_next = value != 0;
+            return RSTQ_OK;
+        case RSTQ_TUNE_ACT_IMAGE:
+            for (auto& ds : ctx->devs) ds.act_image = value != 0;
             return RSTQ_OK;
         case RSTQ_TUNE_FUSE_QUANT:
             for (auto& ds : ctx->devs) ds.fuse_quant = value != 0;

@@ -102,6 +102,11 @@ struct StreamParams {
     int nx_G, nx_unit;
     int probe;            // timing probes (results invalid): 1 = the producer signals without copying, 2 = the consumers skip the arithmetic
     uint32_t act_off, act2_off, red_off, bar_off;  // byte offsets into dynamic smem (ring at 0)
+    // MODE_A8, M > 1: the staged activations as the quantizer wrote them out, an image of what
+    // stage_a8 would build (fragments at act_off, scale / sum records at act2_off); the producer
+    // thread copies it in with two bulk copies under a barrier of its own.  Null: stage in the kernel.
+    const uint8_t* img;
+    uint32_t img_b_bytes, img_z_bytes, img_z_off;
     TpFuse tp;            // tp.nranks == 0: no exchange, results go to y
 };
 
@@ -596,8 +601,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         dbg[6] = smid;
     }
     const uint32_t full0 = smem_u32(smem + p.bar_off), empty0 = full0 + NS * 8;
+    const uint32_t act_bar = empty0 + NS * 8;
     if (tid < NS) mbar_init(full0 + 8 * tid, 1);
     else if (tid < 2 * NS) mbar_init(empty0 + 8 * (tid - NS), kCW);
+    else if (tid == 2 * NS + 1) mbar_init(act_bar, 1);
     if (tid == 2 * NS) {
         // this CTA's unit range, as (first group, first block in it, unit count)
         const int64_t u0 = range_begin(blockIdx.x, p.uq, p.ur);
@@ -608,7 +615,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         s_total = (int)((u1 < p.U ? u1 : p.U) - u0);
         s_abort = 0;
     }
-    if (tid < 2 * NS) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (tid < 2 * NS || tid == 2 * NS + 1) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     // Programmatic dependent launch: the next kernel in the stream may be scheduled onto
     // SMs as this grid's CTAs retire (a no-op for a plain launch).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -657,7 +664,23 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             int npf = 0;
 #endif
             const int64_t pf_ahead = p.pf_ahead;
+            // The activation image is the quantizer's output: it is copied once the ring has its first
+            // NS chunks on the way (the weights do not depend on the kernel before this one, the image
+            // does), as bulk copies that run beside the weight stream instead of 16 warps of loads
+            // and stores in front of it.
+            bool img_done = p.img == nullptr;
+            auto copy_image = [&]() {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                mbar_expect_tx(act_bar, p.img_b_bytes + p.img_z_bytes);
+                for (uint32_t o = 0; o < p.img_b_bytes; o += 32768) {
+                    const uint32_t n = p.img_b_bytes - o < 32768 ? p.img_b_bytes - o : 32768;
+                    bulk_copy_g2s(smem_u32(smem + p.act_off) + o, p.img + o, n, act_bar);
+                }
+                bulk_copy_g2s(smem_u32(smem + p.act2_off), p.img + p.img_z_off, p.img_z_bytes, act_bar);
+                img_done = true;
+            };
             while (left > 0) {
+                if (!img_done && issued >= NS) copy_image();
                 if (pf_ahead > 0) {
                     const uint8_t* lim = src + pf_ahead < end ? src + pf_ahead : end;
                     while (pf < lim) {
@@ -698,6 +721,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 #if RSTQ_PROBES
             if (pfine) pfine[0] = (unsigned long long)npf;
 #endif
+            if (!img_done && ok) copy_image();
+            if (!ok && p.img && img_done) {  // gave up with the image copy in flight: let it land (bounded)
+                const unsigned long long t0 = gtime_ns();
+                while (!mbar_try(act_bar, 0) && gtime_ns() - t0 < kWaitLimitNs) {
+                }
+            }
             if (!ok) {
                 // gave up: still wait (bounded) for the copies already issued to land,
                 // so no copy is in flight into this CTA's shared memory when it exits
@@ -745,9 +774,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                                  : "memory");
         }
     };
-    if (QF) stage_a8_quant<BITS>(p, smem, tid);
-    else if (MODE == MODE_A8) stage_a8<ONECOL, BITS>(p, smem, tid);
-    else stage_f(p, smem, tid);
+    if (QF) {
+        stage_a8_quant<BITS>(p, smem, tid);
+    } else if (MODE == MODE_A8) {
+        if (!ONECOL && p.img) {
+            int got = 1;
+            if (lane == 0) got = mbar_spin(act_bar, 0, abort_flag);   // on expiry the abort flag ends the loops below
+            (void)__shfl_sync(0xffffffffu, got, 0);
+        } else {
+            stage_a8<ONECOL, BITS>(p, smem, tid);
+        }
+    } else {
+        stage_f(p, smem, tid);
+    }
     consumer_bar();
     if (dbg && tid == 0) dbg[2] = gtime_ns();
 
@@ -1191,7 +1230,7 @@ static StreamPlan plan_stream(const DeviceState& ds, int bits, int NT, int64_t g
     pl.act2_off = pl.act_off + (uint32_t)a1;
     pl.red_off = pl.act2_off + (uint32_t)a2;
     pl.bar_off = pl.red_off + (uint32_t)red;
-    pl.smem = pl.bar_off + 2 * ns * 8;
+    pl.smem = pl.bar_off + 2 * ns * 8 + 16;  // ring barriers + the activation image's
     return pl;
 }
 
@@ -1346,6 +1385,12 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         }
         p.y = a.y + m0 * a.out;
         p.T = 1; p.act_dtype = qf ? a.act_dtype : RSTQ_F32; p.out_dtype = RSTQ_F32;
+        if (a.img && M > 1 && M == a.M) {   // the image was laid out for the whole call: one piece only
+            p.img = a.img;
+            p.img_b_bytes = (uint32_t)(nb * M * 32);
+            p.img_z_bytes = (uint32_t)(nb * ((M + 1) & ~1) * 8);
+            p.img_z_off = (p.img_b_bytes + 127u) & ~127u;
+        }
         if (a.tp) p.tp = *a.tp;
         if (m0 + M >= a.M) fill_next(p, ds, a.next);   // the last piece of this call: what comes next is another weight
         cudaError_t le = cudaSuccess;

@@ -72,6 +72,7 @@ struct DeviceState {
     int gemv_probe = 0;            // timing probes of the decode kernel (RSTQ_TUNE_PROBE); results are invalid while set
     bool prefetch_next = true;     // decode launches request the weight that followed this one last time into L2
     rstq_weight* last_decode_w = nullptr;   // the weight of the most recent decode launch on this device
+    bool act_image = true;         // MODE_A8, 2 <= M <= 16: the quantizer also writes the decode kernel's staged form, taken by bulk copy
     bool x_on_host = false;        // the current host-array call lets its first kernel read x from pinned host memory
     bool fuse_quant = true;        // M = 1 operator: quantize the activations inside the decode kernel
     // scratch owned by the context
@@ -203,7 +204,7 @@ int32_t launch_q4k_min(rstq_ctx* ctx, DeviceState& ds, const float* mins, const 
                        float* y, int64_t M, int64_t nb, int64_t out);
 // actquant.cu
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
-                            int32_t* xsum, int64_t M, int64_t in, int act_dtype = RSTQ_F32);
+                            int32_t* xsum, int64_t M, int64_t in, int act_dtype = RSTQ_F32, uint8_t* img = nullptr, int zp = 0);
 // Exchange fused into the tail of the decode kernel (layout of a region: see tp.cu).  The
 // kernel writes its results into slot `rank` of every rank's stage instead of y, signals, waits
 // (time-bounded) for the other ranks and lays the slots side by side (sum = 0) or adds them in
@@ -237,6 +238,7 @@ struct GemvA8Args {
     const void* x = nullptr;     // M == 1 only: raw activations (f32 or bf16), quantized by the kernel
     int act_dtype = RSTQ_F32;    // itself while staging; xq / xs / xsum are then not read
     NextWeight next;
+    const uint8_t* img = nullptr;  // M > 1: the quantizer's image of the staged activations (see StreamParams::img)
 };
 struct GemvFArgs {
     const uint8_t* w;
