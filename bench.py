@@ -1348,7 +1348,7 @@ def run_decoder(args, emit=True):
 
 
 def run_m1(args):
-    """--case m1:<bits>:<out>:<in>[:<M>] [--tune k=v,k=v ...]: the decode launch (pre-quantized activations) and
+    """--case m1:<bits>:<out>:<in>[:<M>[:ff|fb]] [--tune k=v,k=v ...]: the decode launch (pre-quantized activations) and
     the operator (MODE_A8, quantizer included) over rotated weight copies (4 x L2 in total), each replayed from
     one CUDA graph and timed with CUDA events, under the given rstq_tune settings (include/rstq.h: 4 = work
     split, 6 = quantizer inside the kernel, 7 = own-range L2 distance in KB, 9 = next-weight prefetch, 8 =
@@ -1379,6 +1379,10 @@ def run_m1(args):
     bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
     gemv = lambda: [ctx.qmatmul_prequant(w, bq, bs, bsum, by, M) for w in ws]
     op = lambda: [ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8) for w in ws]
+    if len(parts) > 5:      # ":ff" / ":fb": MODE_F with f32 / bf16 activations; both columns are the operator then
+        bxb = ctx.array_to_buffer(synth.to_bf16_bits(x))
+        src, act = (bxb, L.BF16) if parts[5] == "fb" else (bx, L.F32)
+        gemv = op = lambda: [ctx.qmatmul(w, src, by, M, act, L.F32, L.MODE_F) for w in ws]
 
     def graph_of(fn):
         fn(), fn()                      # the second pass knows the order of the weights
