@@ -1136,33 +1136,43 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         const unsigned long long t0 = gtime_ns();
         bool ok = true;
         for (int64_t q = q0 + tid; q < q1 && ok; q += kConsumers) {
-            float2 acc = make_float2(0.f, 0.f);
             const int64_t row = q / row_pairs, col = q - row * row_pairs;
-            for (int r = 0; r < tpn && ok; ++r) {
-                const uint8_t* src = stage + (int64_t)r * p.tp.slot_bytes + q * 16;
-                uint32_t a0, e0, a1, e1;
-                for (uint32_t spins = 1;; ++spins) {
-                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(a0), "=r"(e0), "=r"(a1), "=r"(e1)
-                                 : "l"(src)
-                                 : "memory");
-                    if (e0 == tp_e && e1 == tp_e) break;
-                    if ((spins & 63u) == 0 && (s_tp_ok == 0 || gtime_ns() - t0 > kWaitLimitNs)) {
-                        ok = false;  // a rank never delivered: report, do not hang
-                        s_tp_ok = 0;
-                        atomicExch(p.status, 2);
-                        break;
-                    }
-                }
-                if (!ok) break;
-                if (p.tp.sum) {
-                    if (r == 0) acc = make_float2(__uint_as_float(a0), __uint_as_float(a1));
-                    else { acc.x += __uint_as_float(a0); acc.y += __uint_as_float(a1); }
-                } else {
-                    dst[(row * tpn + r) * row_pairs + col] = make_float2(__uint_as_float(a0), __uint_as_float(a1));
+            // All ranks' slots of this pair are read at once and only those that do not carry this
+            // exchange's epoch yet are read again: one L2 round trip when everything has arrived,
+            // instead of one per rank in a row.
+            uint32_t v[kTpMaxRanks][4];
+            uint32_t pend = (1u << tpn) - 1u;
+            for (uint32_t spins = 1; pend; ++spins) {
+#pragma unroll
+                for (int r = 0; r < kTpMaxRanks; ++r)
+                    if ((pend >> r) & 1u)
+                        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(v[r][0]), "=r"(v[r][1]), "=r"(v[r][2]), "=r"(v[r][3])
+                                     : "l"(stage + (int64_t)r * p.tp.slot_bytes + q * 16)
+                                     : "memory");
+#pragma unroll
+                for (int r = 0; r < kTpMaxRanks; ++r)
+                    if (((pend >> r) & 1u) && v[r][1] == tp_e && v[r][3] == tp_e) pend &= ~(1u << r);
+                if (pend && (spins & 63u) == 0 && (s_tp_ok == 0 || gtime_ns() - t0 > kWaitLimitNs)) {
+                    ok = false;  // a rank never delivered: report, do not hang
+                    s_tp_ok = 0;
+                    atomicExch(p.status, 2);
+                    break;
                 }
             }
-            if (ok && p.tp.sum) dst[q] = acc;
+            if (!ok) break;
+            if (p.tp.sum) {
+                float2 acc = make_float2(__uint_as_float(v[0][0]), __uint_as_float(v[0][2]));
+#pragma unroll
+                for (int r = 1; r < kTpMaxRanks; ++r)   // rank order: the same sum on every rank
+                    if (r < tpn) { acc.x += __uint_as_float(v[r][0]); acc.y += __uint_as_float(v[r][2]); }
+                dst[q] = acc;
+            } else {
+#pragma unroll
+                for (int r = 0; r < kTpMaxRanks; ++r)
+                    if (r < tpn)
+                        dst[(row * tpn + r) * row_pairs + col] = make_float2(__uint_as_float(v[r][0]), __uint_as_float(v[r][2]));
+            }
         }
         if (dbg && tid == 0) dbg[7] = gtime_ns();
     }
