@@ -1039,8 +1039,8 @@ def run_dx(args):
 
 
 def run_q4k(args):
-    """--case q4k:<out>:<in>:<M> / q6k:<out>:<in>:<M>: the Q4_K operator (q8_K quantizer + decode kernel +
-    min-term GEMV) or the Q6_K operator (q8_K quantizer + decode kernel over twin rows + pair sum) on
+    """--case q4k:<out>:<in>:<M> / q6k:<out>:<in>:<M> [--tune 11=0]: the Q4_K operator (q8_K quantizer + decode
+    kernel over units with the minima inside; with --tune 11=0: + min-term GEMV) or the Q6_K operator (q8_K quantizer + decode kernel over twin rows + pair sum) on
     distinct weight copies (more than L2 in total), timed with CUDA events per call."""
     from raster_b200 import Context
     from raster_b200 import _lib as L
@@ -1048,6 +1048,9 @@ def run_q4k(args):
     out, in_, M = int(out), int(in_), int(M)
     rng = np.random.default_rng(0)
     ctx = Context(("cuda:0",))
+    for kv in (args.tune.split(",") if args.tune else []):     # e.g. 11=0: Q4_K minima outside the units
+        k, v = kv.split("=")
+        ctx.tune(int(k), int(v))
     enc6 = {"wq": rng.integers(0, 64, out * in_, dtype=np.uint8), "sc": rng.integers(0, 128, out * in_ // 16, dtype=np.int8),
             "ds": (np.abs(rng.standard_normal(out * in_ // 256)) * 1e-4).astype(np.float32)} if kind == "q6k" else None
     enc = {"wq": rng.integers(0, 256, out * in_ // 2, dtype=np.uint8),

@@ -150,7 +150,7 @@ static NextWeight note_decode_launch(rstq_ctx* ctx, DeviceState& ds, rstq_weight
         n.data = h->data;
         n.groups = h->outp / 32;
         n.nb = h->nb;
-        n.bits = h->bits;
+        n.bits = h->kq ? 5 : h->bits;   // the unit kind
     }
     return n;
 }
@@ -161,6 +161,7 @@ static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const flo
                       const uint8_t* img = nullptr) {
     GemvA8Args a{w->data, xq, xs, xsum, y, M, w->in, w->out, w->bits, w->zp, tp};
     a.img = img;
+    a.kq = w->kq;
     a.next = note_decode_launch(ctx, ctx->devs[w->dev], w);
     return launch_gemv_a8(ctx, ctx->devs[w->dev], a);
 }
@@ -176,7 +177,7 @@ static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int6
 static int32_t run_q4k(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs32, const int32_t* bsums,
                        float* y, int64_t M) {
     int32_t rc = run_a8(ctx, w, xq, xs32, bsums, y, M);
-    if (rc != RSTQ_OK) return rc;
+    if (rc != RSTQ_OK || w->kq) return rc;   // Q4_K units: the decode kernel added the min term itself
     return launch_q4k_min(ctx, ctx->devs[w->dev], w->mins, xs32, bsums, y, M, w->nb, w->out);
 }
 
@@ -567,6 +568,9 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
         case RSTQ_TUNE_PREFETCH_NEXT:
             for (auto& ds : ctx->devs) ds.prefetch_next = value != 0;
             return RSTQ_OK;
+        case RSTQ_TUNE_Q4K_UNITS:
+            ctx->tune_q4k_units = value != 0;
+            return RSTQ_OK;
         case RSTQ_TUNE_ACT_IMAGE:
             for (auto& ds : ctx->devs) ds.act_image = value != 0;
             return RSTQ_OK;
@@ -762,6 +766,25 @@ int32_t rstq_weight_bind_q4k(rstq_ctx* ctx, rstq_weight** wout, const void* wq, 
         rstq_weight_free(w);
         return cuda_fail(e, "Q4_K bind", __FILE__, __LINE__);
     }
+    if (ctx->tune_q4k_units) {
+        // the minima move into the units (768 B): the decode kernel folds them, no third kernel
+        const int64_t kbytes = (w->outp / 32) * w->nb * kUnitBytesQ4K;
+        uint8_t* kdata = nullptr;
+        e = cudaMalloc((void**)&kdata, (size_t)kbytes);
+        if (e == cudaSuccess) {
+            rc = launch_q4k_units(ctx, ds, w->data, w->mins, kdata, w->out, w->nb);
+            if (rc == RSTQ_OK) e = cudaStreamSynchronize(ds.stream);
+        }
+        if (e != cudaSuccess || rc != RSTQ_OK) {
+            if (kdata) cudaFree(kdata);
+            rstq_weight_free(w);
+            return rc != RSTQ_OK ? rc : cuda_fail(e, "Q4_K units", __FILE__, __LINE__);
+        }
+        cudaFree(w->data);
+        w->data = kdata;
+        w->data_bytes = kbytes;
+        w->kq = true;
+    }
     *wout = w;
     return RSTQ_OK;
 }
@@ -861,7 +884,7 @@ int32_t rstq_weight_info(rstq_weight* w, int64_t* out6) {
     out6[0] = w->pair_out ? w->pair_out : w->out;
     out6[1] = w->in;
     out6[2] = w->pair_out ? 6 : w->bits;
-    out6[3] = w->data_bytes + (w->mins ? w->out * w->nb * 4 : 0);
+    out6[3] = w->data_bytes + (w->mins && !w->kq ? w->out * w->nb * 4 : 0);
     // Q4_K as the reference stores it: nibbles, da + db per super-block, aq + bq per sub-block
     out6[4] = w->mins ? w->out * w->in / 2 + w->out * (w->in / 256) * 8 + w->out * w->nb * 2
                       : w->out * w->in * w->bits / 8 + w->out * w->nb * 4;

@@ -61,7 +61,8 @@ constexpr int kStreamThreads = kConsumers + 32;  // + producer warp
 #ifndef RSTQ_NSMAX
 #define RSTQ_NSMAX 6
 #endif
-__host__ __device__ constexpr int upw_of(int bits) { return bits == 4 ? RSTQ_UPW4 : 2; }
+// `bits` of the host-side helpers is the unit kind: 4, 8, or 5 = 4-bit codes with the 32 Q4_K minima behind the scales
+__host__ __device__ constexpr int upw_of(int bits) { return bits == 8 ? 2 : RSTQ_UPW4; }
 __host__ __device__ constexpr int chunk_units_of(int bits) { return upw_of(bits) * kCW; }
 constexpr int kMaxDynSmem = 232448 - 1024;       // 227 KB opt-in limit less the static part
 // the in-kernel quantizer holds all of a thread's activations in registers: in <= 3 * 512 * 8
@@ -107,6 +108,7 @@ struct StreamParams {
     // thread copies it in with two bulk copies under a barrier of its own.  Null: stage in the kernel.
     const uint8_t* img;
     uint32_t img_b_bytes, img_z_bytes, img_z_off;
+    int kq;   // Q4_K units (zero point 0): the staged constant of a block is t = xs * code sum, which the minima multiply
     TpFuse tp;            // tp.nranks == 0: no exchange, results go to y
 };
 
@@ -172,7 +174,7 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
                     r.x = wa[j];
                     r.y = wb[j];
                     r.z = __float_as_uint(hi ? xs[j] * 0.0625f : xs[j]);
-                    r.w = (uint32_t)(kMagicInt - (p.zp * zs[j]) * (hi ? 16 : 1));
+                    r.w = p.kq ? __float_as_uint(xs[j] * (float)zs[j]) : (uint32_t)(kMagicInt - (p.zp * zs[j]) * (hi ? 16 : 1));
                     srec[i] = r;
                 }
             }
@@ -217,7 +219,8 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
                 const int b = o / Mz, c = o - b * Mz;
                 if (c < M) {
                     v[j].x = __float_as_int(p.xs[(int64_t)c * nb + b]);
-                    v[j].y = p.zp * p.xsum[(int64_t)c * nb + b];
+                    const int cs = p.xsum[(int64_t)c * nb + b];
+                    v[j].y = p.kq ? __float_as_int(__int_as_float(v[j].x) * (float)cs) : p.zp * cs;
                 }
             }
         }
@@ -372,14 +375,15 @@ __device__ __forceinline__ void stage_f(const StreamParams& p, uint8_t* smem, in
 template <int BITS>
 struct SUnit {
     uint4 c0, c1;
-    float4 sc;
+    float4 sc, mn;
 };
-template <int BITS>
+template <int BITS, bool KQ = false>
 __device__ __forceinline__ void lds_unit(SUnit<BITS>& u, const uint8_t* unit, int lane) {
     constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
     u.c0 = *reinterpret_cast<const uint4*>(unit + lane * 16);
     if (BITS == 8) u.c1 = *reinterpret_cast<const uint4*>(unit + 512 + lane * 16);
     u.sc = *reinterpret_cast<const float4*>(unit + CODES + (lane >> 2) * 16);
+    if (KQ) u.mn = *reinterpret_cast<const float4*>(unit + CODES + 128 + (lane >> 2) * 16);
 }
 
 // A-fragment registers of the two 16-row tiles (q = 0: rows gid, gid+8; q = 1: rows
@@ -428,16 +432,17 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
 template <int BITS>
 struct RowUnit {
     uint4 c0, c1, r;
-    float sc;
+    float sc, mn;
 };
-template <int BITS>
+template <int BITS, bool KQ = false>
 __device__ __forceinline__ void row_load(RowUnit<BITS>& u, uint32_t codes, uint32_t scale, uint32_t rec) {
     u.c0 = lds128(codes);
     if (BITS == 8) u.c1 = lds128(codes + 512);
     u.sc = lds32f(scale);
+    if (KQ) u.mn = lds32f(scale + 128);   // the row's minimum db * bq: 32 floats behind the 32 scales
     u.r = lds128(rec);
 }
-template <int BITS>
+template <int BITS, bool KQ = false>
 __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bool upper, float acc) {
     uint32_t a[2][4];
     if (BITS == 4) {
@@ -453,18 +458,24 @@ __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bo
     imma_u8s8(d1, a[1], u.r.x, u.r.y);
     // tig 0 -> d0[0] (row gid), 1 -> d0[2] (gid+8), 2 -> d1[0] (gid+16), 3 -> d1[2] (gid+24)
     const uint32_t lo = (uint32_t)(upper ? d1[0] : d0[0]), hi = (uint32_t)(upper ? d1[2] : d0[2]);
+    if (KQ) {   // zero point 0: the record's last word is t = xs * code sum of the block, for the minimum term
+        const uint32_t iv = (m ? hi : lo) + (uint32_t)kMagicInt;
+        const float f = __uint_as_float(iv) - kMagicFlt;
+        return fmaf(u.mn, __uint_as_float(u.r.w), fmaf(u.sc * __uint_as_float(u.r.z), f, acc));
+    }
     const uint32_t iv = (m ? hi : lo) + u.r.w;
     const float f = __uint_as_float(iv) - kMagicFlt;
     return fmaf(u.sc * __uint_as_float(u.r.z), f, acc);
 }
 
-template <int BITS, int NT>
+template <int BITS, int NT, bool KQ = false>
 __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* smem,
                                         const StreamParams& p, int b, int gid, int tig,
                                         float (&acc)[NT][4][2]) {
     uint32_t a[2][4];
     a_frags<BITS>(u, a);
     const float sc[4] = {u.sc.x, u.sc.y, u.sc.z, u.sc.w};
+    const float mn[4] = {u.mn.x, u.mn.y, u.mn.z, u.mn.w};
     // value of the high-nibble rows is 16x: scale by xs/16 and shift their zero-point term
     constexpr float HI = BITS == 4 ? 0.0625f : 1.0f;
     constexpr int ZSH = BITS == 4 ? 4 : 0;
@@ -482,8 +493,10 @@ __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* sme
         const int4 z = *reinterpret_cast<const int4*>(xz + c0);
         const float xs0 = __int_as_float(z.x), xs1 = __int_as_float(z.z);
         const float xs0h = xs0 * HI, xs1h = xs1 * HI;
-        const int ca0 = kMagicInt - z.y, ca1 = kMagicInt - z.w;
-        const int cb0 = kMagicInt - (z.y << ZSH), cb1 = kMagicInt - (z.w << ZSH);
+        // Q4_K (zero point 0): the second word of a record is t = xs * code sum, which the minima multiply
+        const int ca0 = KQ ? kMagicInt : kMagicInt - z.y, ca1 = KQ ? kMagicInt : kMagicInt - z.w;
+        const int cb0 = KQ ? kMagicInt : kMagicInt - (z.y << ZSH), cb1 = KQ ? kMagicInt : kMagicInt - (z.w << ZSH);
+        const float t0 = __int_as_float(z.y), t1 = __int_as_float(z.w);
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             int d[4];
@@ -495,6 +508,12 @@ __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* sme
                 fmaf(s1 * xs0h, __int_as_float(d[2]) - kMagicFlt, acc[nt][2 * q + 1][0]);
             acc[nt][2 * q + 1][1] =
                 fmaf(s1 * xs1h, __int_as_float(d[3]) - kMagicFlt, acc[nt][2 * q + 1][1]);
+            if (KQ) {
+                acc[nt][2 * q][0] = fmaf(mn[2 * q], t0, acc[nt][2 * q][0]);
+                acc[nt][2 * q][1] = fmaf(mn[2 * q], t1, acc[nt][2 * q][1]);
+                acc[nt][2 * q + 1][0] = fmaf(mn[2 * q + 1], t0, acc[nt][2 * q + 1][0]);
+                acc[nt][2 * q + 1][1] = fmaf(mn[2 * q + 1], t1, acc[nt][2 * q + 1][1]);
+            }
         }
     }
 }
@@ -578,9 +597,9 @@ __device__ __forceinline__ float stream_reduce_rc(const float* red, int row, int
 
 // ---- the kernel ---------------------------------------------------------------------
 // QF: M == 1 only, the kernel quantizes the raw activations p.x itself while staging.
-template <int BITS, int NT, int MODE, bool ONECOL, bool TP, bool QF = false>
+template <int BITS, int NT, int MODE, bool ONECOL, bool TP, bool QF = false, bool KQ = false>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
-    constexpr int UNIT = BITS == 4 ? kUnitBytesQ4 : kUnitBytesQ8;
+    constexpr int UNIT = BITS == 4 ? (KQ ? kUnitBytesQ4K : kUnitBytesQ4) : kUnitBytesQ8;
     constexpr int kUPW = upw_of(BITS), kChunkUnits = chunk_units_of(BITS);
     constexpr int CHUNK_BYTES = kChunkUnits * UNIT;
     constexpr int NV = NT * 8;
@@ -1003,14 +1022,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     if (n == kChunkUnits) {
                         RowUnit<BITS> u[kUPW];
 #pragma unroll
-                        for (int j = 0; j < kUPW; ++j) row_load<BITS>(u[j], codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
+                        for (int j = 0; j < kUPW; ++j) row_load<BITS, KQ>(u[j], codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
 #pragma unroll
-                        for (int j = 0; j < kUPW; ++j) v = row_fold<BITS>(u[j], m, upper, v);
+                        for (int j = 0; j < kUPW; ++j) v = row_fold<BITS, KQ>(u[j], m, upper, v);
                     } else {
                         for (int j = 0; warp + j * kCW < n; ++j) {
                             RowUnit<BITS> u;
-                            row_load<BITS>(u, codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
-                            v = row_fold<BITS>(u, m, upper, v);
+                            row_load<BITS, KQ>(u, codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
+                            v = row_fold<BITS, KQ>(u, m, upper, v);
                         }
                     }
                 }
@@ -1081,9 +1100,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (alive && !PROBE(2)) {
                 for (int j = 0; warp + j * kCW < n; ++j) {
                     SUnit<BITS> un;
-                    lds_unit<BITS>(un, unit0 + j * kCW * UNIT, lane);
+                    lds_unit<BITS, KQ>(un, unit0 + j * kCW * UNIT, lane);
                     const int blk = b + warp + j * kCW;
-                    if (MODE == MODE_A8) unit_a8<BITS, NT>(un, smem, p, blk, gid, tig, acc);
+                    if (MODE == MODE_A8) unit_a8<BITS, NT, KQ>(un, smem, p, blk, gid, tig, acc);
                     else unit_f<BITS, NT>(un, smem, p, blk, gid, tig, acc);
                 }
             }
@@ -1284,6 +1303,10 @@ int32_t gemv_configure(DeviceState& ds) {
     if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, true, true, true>)) != RSTQ_OK) return rc;
     if ((rc = set_stream_attr(gemv_stream_kernel<8, 1, MODE_A8, true, false, true>)) != RSTQ_OK) return rc;
     if ((rc = set_stream_attr(gemv_stream_kernel<8, 1, MODE_A8, true, true, true>)) != RSTQ_OK) return rc;
+    // Q4_K units (minima inside)
+    if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, true, false, false, true>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, false, false, false, true>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<4, 2, MODE_A8, false, false, false, true>)) != RSTQ_OK) return rc;
     return RSTQ_OK;
 }
 
@@ -1370,10 +1393,12 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         if (m == 1) { *a1 = nb * 64; *a2 = 0; }
         else { *a1 = nb * m * 32; *a2 = nb * ((m + 1) & ~1) * 8; }
     };
+    const int ukind = a.kq ? 5 : a.bits;   // unit kind for the size helpers: Q4_K units carry 128 more bytes
+    RSTQ_REQUIRE(!a.kq || (a.bits == 4 && !a.tp && !a.x), RSTQ_E_INVALID, "Q4_K units: 4-bit, one device, pre-quantized activations");
     for (int64_t m0 = 0; m0 < a.M;) {
         const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
         StreamPlan pl;
-        int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl, true);
+        int M = fit_tokens(ds, ukind, groups, nb, want, bytes, &pl, true);
         RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
                      (long long)a.in);
         if (a.tp && (M < a.M || a.out % 4 != 0)) return kNotFused;  // the exchange fuses into ONE launch
@@ -1384,8 +1409,9 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         if (rc != RSTQ_OK) return rc;
         const int NT = M <= 8 ? 1 : 2;
         StreamParams p{};
-        fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp, a.bits);
+        fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp, ukind);
         p.w = a.w;
+        p.kq = a.kq ? 1 : 0;
         if (qf) {
             p.x = a.x;
         } else {
@@ -1414,7 +1440,11 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         else le = qf ? launch_stream(gemv_stream_kernel<B, 1, MODE_A8, true, false, true>, ds, pl, p)      \
                      : launch_stream(gemv_stream_kernel<B, 1, MODE_A8, true, false, false>, ds, pl, p);    \
     } while (0)
-        if (a.bits == 4) {
+        if (a.kq) {
+            if (NT == 2) le = launch_stream(gemv_stream_kernel<4, 2, MODE_A8, false, false, false, true>, ds, pl, p);
+            else if (M == 1) le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, true, false, false, true>, ds, pl, p);
+            else le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, false, false, false, true>, ds, pl, p);
+        } else if (a.bits == 4) {
             if (NT == 2) LAUNCH(4, 2, MODE_A8, false);
             else if (M == 1) LAUNCH1(4);
             else LAUNCH(4, 1, MODE_A8, false);

@@ -122,4 +122,37 @@ int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
     return RSTQ_OK;
 }
 
+// One thread per destination word: 160 words of codes and scales as they are, then the 32 minima.
+__global__ void q4k_units_kernel(const uint8_t* __restrict__ src, const float* __restrict__ mins,
+                                 uint8_t* __restrict__ dst, int64_t out, int64_t nb, int64_t groups) {
+    constexpr int SW = kUnitBytesQ4 / 4, DW = kUnitBytesQ4K / 4;
+    const int64_t total = groups * nb * DW;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t unit = idx / DW;
+        const int wi = (int)(idx % DW);
+        uint32_t v;
+        if (wi < SW) {
+            v = reinterpret_cast<const uint32_t*>(src + unit * kUnitBytesQ4)[wi];
+        } else {
+            const int si = wi - SW;
+            const int64_t g = unit / nb, b = unit % nb;
+            const int64_t row = g * 32 + (si >> 2) + 8 * (si & 3);
+            v = __float_as_uint(row < out ? mins[row * nb + b] : 0.0f);
+        }
+        reinterpret_cast<uint32_t*>(dst + unit * kUnitBytesQ4K)[wi] = v;
+    }
+}
+
+int32_t launch_q4k_units(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src, const float* mins, uint8_t* dst,
+                         int64_t out, int64_t nb) {
+    const int64_t groups = (out + 31) / 32, total = groups * nb * (kUnitBytesQ4K / 4);
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (blocks < 1) blocks = 1;
+    q4k_units_kernel<<<blocks, 256, 0, ds.stream>>>(src, mins, dst, out, nb, groups);
+    ctx->launches++;
+    RSTQ_CUDA(cudaGetLastError());
+    return RSTQ_OK;
+}
+
 }  // namespace rstq
