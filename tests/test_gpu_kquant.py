@@ -91,6 +91,33 @@ def test_q4k_matmul_matches_the_oracle(ctx, out, in_, M):
         o.free()
 
 
+@pytest.mark.parametrize("M", [1, 3])
+def test_q4k_minima_outside_the_units_matches_too(ctx, M):
+    """RSTQ_TUNE_Q4K_UNITS = 0: 640-byte units and the min term as a third kernel (the first layout)."""
+    out, in_ = 200, 1024
+    W = synth.normal(41, out * in_, 0.02) + np.float32(0.01)
+    x = synth.normal(42, M * in_)
+    e = orc.quantize_weight_q4k(W)
+    ref = oracle_rows(e, x, M, in_, out)
+    ys = []
+    try:
+        for units in (0, 1):
+            ctx.tune(L.TUNE_Q4K_UNITS, units)
+            w = ctx.bind_weight_q4k(e, out, in_)
+            bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+            n0 = ctx.launch_count()
+            ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+            ctx.sync()
+            assert ctx.launch_count() - n0 == (2 if units else 3)
+            ys.append(by.download())
+            assert relerr(ys[-1], ref) <= 1e-5
+            for o in (w, bx, by):
+                o.free()
+    finally:
+        ctx.tune(L.TUNE_Q4K_UNITS, 1)
+    assert relerr(ys[0], ys[1].reshape(ys[0].shape)) <= 2e-6
+
+
 def test_kernel_level_call_and_registry(ctx):
     from raster_b200.quant import core as qcore
     from raster_b200.quant import kernels_k as qk

@@ -134,6 +134,41 @@ def test_fused_quantizer_is_bit_identical_to_the_quantizer_kernel(ctx, bits, pla
 
 
 @pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("plan", [0, 1])
+@pytest.mark.parametrize("M,out,in_", [(2, 264, 1024), (3, 96, 160), (4, 4096, 4096), (8, 1000, 11008), (8, 11008, 4096),
+                                       (9, 520, 2048), (16, 512, 4096), (7, 64, 28672)])
+def test_activation_image_is_bit_identical_to_the_in_kernel_gather(ctx, bits, plan, M, out, in_):
+    """rstq_qmatmul in MODE_A8 at 2 <= M <= 16: the quantizer also writes the decode kernel's staged form of
+    the activations and the kernel takes it by bulk copy; with RSTQ_TUNE_ACT_IMAGE = 0 the kernel's warps gather
+    it from the quantizer's row-major output.  Same bytes in shared memory -> the same y, bit for bit (also when
+    the call is cut into several launches and falls back to the gather), and both match the oracle."""
+    fmt_desc, fmt, ofmt = FMT[bits]
+    _, wq, ws = make_weight(out, in_, bits, seed=out + in_ + M)
+    x = synth.normal(out + 7 * in_ + M, M * in_)
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    ys = {}
+    try:
+        ctx.tune(L.TUNE_GEMV_PLAN, plan)
+        for image in (1, 0):
+            ctx.tune(L.TUNE_ACT_IMAGE, image)
+            by.fill_bytes(0xFF)
+            ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+            ctx.sync()
+            ys[image] = by.download()
+    finally:
+        ctx.tune(L.TUNE_ACT_IMAGE, 1)
+        ctx.tune(L.TUNE_GEMV_PLAN, 0)
+    assert np.array_equal(ys[1].view(np.uint32), ys[0].view(np.uint32))
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    ref = orc.matmul_a8_f64(wq, ws, ofmt, xq, xs, xsum, M, in_, out)
+    assert relerr(ys[1], ref) <= TOL_A8
+    for b in (bx, by):
+        b.free()
+    w.free()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("M", [1, 3, 8, 16])
 @pytest.mark.parametrize("out,in_", [(11008, 4096), (4096, 11008), (28672, 8192), (64, 28672), (200, 96)])
 def test_equal_range_split_hands_partial_sums_over_correctly(ctx, bits, M, out, in_):
