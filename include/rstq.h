@@ -111,6 +111,10 @@ typedef struct rstq_event rstq_event;
 #define RSTQ_TUNE_Q4K_UNITS 11   /* 1 (default) = Q4_K weights bound from now on are stored as 768-byte units with the
                                      sub-block minima behind the scales and the decode kernel adds the min term
                                      itself (quantizer + one kernel); 0 = 640-byte units and a third kernel for it */
+#define RSTQ_TUNE_Q6K_UNITS 12   /* 1 (default) = Q6_K weights bound from now on are stored as 1280-byte units (8-bit
+                                     codes, one scale per row and 16 elements: the reference's code bytes) and
+                                     take quantizer + one decode launch; 0 = two twin rows of 8-bit units per
+                                     row (twice the code bytes) and a third kernel that adds the pairs */
 #define RSTQ_TUNE_ACT_IMAGE 10    /* 1 (default) = rstq_qmatmul in MODE_A8 at 2 <= M <= 16: the activation quantizer
                                      also writes the codes, scales and sums in the order the decode kernel
                                      keeps them in shared memory, and that kernel's copy thread brings them

@@ -128,13 +128,14 @@ static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* o
     const int64_t sb = (M * nb * 4 + 255) & ~255ll;
     const bool image = M >= 2 && M <= 16;
     const int64_t img_bytes = image ? ((nb * M * 32 + 127) & ~127ll) + ((nb * ((M + 1) & ~1ll) * 8 + 255) & ~255ll) : 0;
-    int32_t rc = dev_reserve(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 2 * sb + img_bytes);
+    // xsum has room for sums per 16 elements (Q6_K units): two per block
+    int32_t rc = dev_reserve(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 3 * sb + img_bytes);
     if (rc != RSTQ_OK) return rc;
     char* base = (char*)ds.act_scratch;
     out->xq = (int8_t*)base;
     out->xs = (float*)(base + xq_bytes);
     out->xsum = (int32_t*)(base + xq_bytes + sb);
-    out->img = image ? (uint8_t*)(base + xq_bytes + 2 * sb) : nullptr;
+    out->img = image ? (uint8_t*)(base + xq_bytes + 3 * sb) : nullptr;
     return RSTQ_OK;
 }
 
@@ -150,7 +151,7 @@ static NextWeight note_decode_launch(rstq_ctx* ctx, DeviceState& ds, rstq_weight
         n.data = h->data;
         n.groups = h->outp / 32;
         n.nb = h->nb;
-        n.bits = h->kq ? 5 : h->bits;   // the unit kind
+        n.bits = h->kq ? 5 : (h->k6 ? 6 : h->bits);   // the unit kind
     }
     return n;
 }
@@ -161,7 +162,7 @@ static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const flo
                       const uint8_t* img = nullptr) {
     GemvA8Args a{w->data, xq, xs, xsum, y, M, w->in, w->out, w->bits, w->zp, tp};
     a.img = img;
-    a.kq = w->kq;
+    a.uk = w->kq ? 1 : (w->k6 ? 2 : 0);
     a.next = note_decode_launch(ctx, ctx->devs[w->dev], w);
     return launch_gemv_a8(ctx, ctx->devs[w->dev], a);
 }
@@ -207,6 +208,12 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
         ActScratch s;
         int32_t rc = act_scratch(ds, M, w->in, &s);
         if (rc != RSTQ_OK) return rc;
+        if (w->k6) {
+            // units with a scale per 16 elements: code sums per 16, one decode launch, y as it is
+            rc = launch_quant_act_q8k(ctx, ds, (const float*)x, s.xq, nullptr, s.xs, s.xsum, M, w->in, 16);
+            if (rc != RSTQ_OK) return rc;
+            return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M);
+        }
         if ((rc = dev_reserve(ds, &ds.kq_scratch, &ds.kq_scratch_bytes, M * w->out * 4)) != RSTQ_OK) return rc;
         rc = launch_quant_act_q8k(ctx, ds, (const float*)x, s.xq, nullptr, s.xs, s.xsum, M, w->in, 32);
         if (rc != RSTQ_OK) return rc;
@@ -571,6 +578,9 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
         case RSTQ_TUNE_Q4K_UNITS:
             ctx->tune_q4k_units = value != 0;
             return RSTQ_OK;
+        case RSTQ_TUNE_Q6K_UNITS:
+            ctx->tune_q6k_units = value != 0;
+            return RSTQ_OK;
         case RSTQ_TUNE_ACT_IMAGE:
             for (auto& ds : ctx->devs) ds.act_image = value != 0;
             return RSTQ_OK;
@@ -798,6 +808,45 @@ int32_t rstq_weight_bind_q6k(rstq_ctx* ctx, rstq_weight** wout, const void* wq, 
                  "in = %lld must be a positive multiple of 256 and out = %lld >= 1", (long long)in, (long long)out);
     const int64_t nb = in / 32, nsb = in / 256;
     const uint8_t* q = (const uint8_t*)wq;
+    if (ctx->tune_q6k_units) {
+        // Units with a scale per 16 elements (1280 B): the reference's code bytes, one launch.  The codes
+        // go through the 8-bit repack as they are (with scales that are then dropped), the 2 * nb scales
+        // per row ds * sc (the product the reference forms in double, rounded to f32 once) behind them.
+        const int64_t n16 = out * (in / 16);
+        std::vector<float> s16((size_t)n16), s32((size_t)(out * nb), 0.0f);
+        for (int64_t o = 0; o < out; ++o)
+            for (int64_t j = 0; j < in / 16; ++j)
+                s16[(size_t)(o * (in / 16) + j)] = (float)((double)dsup[o * nsb + j / 16] * (double)sc[o * (in / 16) + j]);
+        rstq_weight* w = nullptr;
+        int32_t rc = bind_impl(ctx, &w, q, s32.data(), dev, out, in, RSTQ_FMT_Q8_0, RSTQ_LAYOUT_ROWMAJOR,
+                               RSTQ_SPLIT_NONE, 0, 1);
+        if (rc != RSTQ_OK) return rc;
+        DeviceState& ds = ctx->devs[dev];
+        const int64_t kbytes = (w->outp / 32) * w->nb * kUnitBytesQ6K;
+        uint8_t* kdata = nullptr;
+        float* d16 = nullptr;
+        cudaError_t e = cudaMalloc((void**)&kdata, (size_t)kbytes);
+        if (e == cudaSuccess) e = cudaMalloc((void**)&d16, (size_t)n16 * 4);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d16, s16.data(), (size_t)n16 * 4, cudaMemcpyHostToDevice, ds.stream);
+        if (e == cudaSuccess) {
+            rc = launch_q6k_units(ctx, ds, w->data, d16, kdata, out, w->nb);
+            if (rc == RSTQ_OK) e = cudaStreamSynchronize(ds.stream);
+        }
+        if (d16) cudaFree(d16);
+        if (e != cudaSuccess || rc != RSTQ_OK) {
+            if (kdata) cudaFree(kdata);
+            rstq_weight_free(w);
+            return rc != RSTQ_OK ? rc : cuda_fail(e, "Q6_K units", __FILE__, __LINE__);
+        }
+        cudaFree(w->data);
+        w->data = kdata;
+        w->data_bytes = kbytes;
+        w->zp = 32;
+        w->pair_out = out;   // marks the format; `out` stays the logical row count
+        w->k6 = true;
+        *wout = w;
+        return RSTQ_OK;
+    }
     std::vector<uint8_t> codes((size_t)(2 * out * in));
     std::vector<float> scales((size_t)(2 * out * nb));
     for (int64_t o = 0; o < out; ++o) {
@@ -978,6 +1027,10 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
         DeviceState& dsk = ctx->devs[w->dev];
         ActScratch s;
         if ((rc = act_scratch(dsk, M, w->in, &s)) != RSTQ_OK) return rc;
+        if (w->k6) {   // the sums per 16 go to the kernel as they are; the scales per super-block are spread over the blocks
+            if ((rc = launch_expand_scales(ctx, dsk, (const float*)xs->ptr, s.xs, M * w->nb)) != RSTQ_OK) return rc;
+            return run_a8(ctx, w, (const int8_t*)xq->ptr, s.xs, (const int32_t*)xsum->ptr, (float*)y->ptr, M);
+        }
         if ((rc = dev_reserve(dsk, &dsk.kq_scratch, &dsk.kq_scratch_bytes, M * w->out * 4)) != RSTQ_OK) return rc;
         if ((rc = launch_q6k_prep(ctx, dsk, (const float*)xs->ptr, (const int32_t*)xsum->ptr, s.xs, s.xsum,
                                   M * w->nb)) != RSTQ_OK)

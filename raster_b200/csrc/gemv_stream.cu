@@ -62,7 +62,8 @@ constexpr int kStreamThreads = kConsumers + 32;  // + producer warp
 #define RSTQ_NSMAX 6
 #endif
 // `bits` of the host-side helpers is the unit kind: 4, 8, or 5 = 4-bit codes with the 32 Q4_K minima behind the scales
-__host__ __device__ constexpr int upw_of(int bits) { return bits == 8 ? 2 : RSTQ_UPW4; }
+//   and 6 = 8-bit codes with a scale per 16 elements (Q6_K: 64 scales behind the codes)
+__host__ __device__ constexpr int upw_of(int bits) { return (bits == 8 || bits == 6) ? 2 : RSTQ_UPW4; }
 __host__ __device__ constexpr int chunk_units_of(int bits) { return upw_of(bits) * kCW; }
 constexpr int kMaxDynSmem = 232448 - 1024;       // 227 KB opt-in limit less the static part
 // the in-kernel quantizer holds all of a thread's activations in registers: in <= 3 * 512 * 8
@@ -109,6 +110,7 @@ struct StreamParams {
     const uint8_t* img;
     uint32_t img_b_bytes, img_z_bytes, img_z_off;
     int kq;   // Q4_K units (zero point 0): the staged constant of a block is t = xs * code sum, which the minima multiply
+    int k6;   // Q6_K units: xsum holds the code sums per 16 elements (2 per block), a record two constants
     TpFuse tp;            // tp.nranks == 0: no exchange, results go to y
 };
 
@@ -153,7 +155,7 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
         for (int i0 = tid; i0 < nb * 4; i0 += 4 * kConsumers) {
             uint32_t wa[4], wb[4];
             float xs[4];
-            int zs[4];
+            int zs[4], zs2[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int i = i0 + j * kConsumers;
@@ -162,7 +164,8 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
                     wa[j] = xqw[b * 8 + tg];
                     wb[j] = xqw[b * 8 + 4 + tg];
                     xs[j] = p.xs[b];
-                    zs[j] = p.xsum[b];
+                    zs[j] = p.k6 ? p.xsum[2 * b] : p.xsum[b];
+                    zs2[j] = p.k6 ? p.xsum[2 * b + 1] : 0;
                 }
             }
 #pragma unroll
@@ -175,7 +178,12 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
                     r.y = wb[j];
                     r.z = __float_as_uint(hi ? xs[j] * 0.0625f : xs[j]);
                     r.w = p.kq ? __float_as_uint(xs[j] * (float)zs[j]) : (uint32_t)(kMagicInt - (p.zp * zs[j]) * (hi ? 16 : 1));
-                    srec[i] = r;
+                    if (p.k6) {   // 32-byte records: the second half's constant behind the first 16 bytes
+                        srec[2 * i] = r;
+                        srec[2 * i + 1] = make_uint4((uint32_t)(kMagicInt - p.zp * zs2[j]), 0u, 0u, 0u);
+                    } else {
+                        srec[i] = r;
+                    }
                 }
             }
         }
@@ -209,6 +217,20 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
             if (dst[j] >= 0) sB[dst[j]] = make_uint2(wa[j], wb[j]);
     }
     const int tot2 = nb * Mz;
+    if (p.k6) {   // Q6_K: {xs bits, zp * code sum of elements 0..15, of 16..31, 0} per (block, token)
+        int4* sxz4 = reinterpret_cast<int4*>(smem + p.act2_off);
+        for (int o = tid; o < tot2; o += kConsumers) {
+            const int b = o / Mz, c = o - b * Mz;
+            int4 v = make_int4(0, 0, 0, 0);
+            if (c < M) {
+                v.x = __float_as_int(p.xs[(int64_t)c * nb + b]);
+                v.y = p.zp * p.xsum[((int64_t)c * nb + b) * 2];
+                v.z = p.zp * p.xsum[((int64_t)c * nb + b) * 2 + 1];
+            }
+            sxz4[o] = v;
+        }
+        return;
+    }
     for (int o0 = tid; o0 < tot2; o0 += U * kConsumers) {
         int2 v[U];
 #pragma unroll
@@ -372,18 +394,25 @@ __device__ __forceinline__ void stage_f(const StreamParams& p, uint8_t* smem, in
 }
 
 // ---- one unit (32 rows x one 32-element block) from the ring ------------------------
+// UK: unit kind beyond the plain one: 1 = Q4_K (32 minima behind the scales), 2 = Q6_K (8-bit codes, 64
+// scales: for row gid + 8i of the group the scales of elements 0..15 and 16..31 at floats (gid*4 + i)*2 + h)
 template <int BITS>
 struct SUnit {
     uint4 c0, c1;
-    float4 sc, mn;
+    float4 sc, mn;   // Q6_K: sc = {row i=0 h=0, i=0 h=1, i=1 h=0, i=1 h=1}, mn = the same of i = 2, 3
 };
-template <int BITS, bool KQ = false>
+template <int BITS, int UK = 0>
 __device__ __forceinline__ void lds_unit(SUnit<BITS>& u, const uint8_t* unit, int lane) {
     constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
     u.c0 = *reinterpret_cast<const uint4*>(unit + lane * 16);
     if (BITS == 8) u.c1 = *reinterpret_cast<const uint4*>(unit + 512 + lane * 16);
+    if (UK == 2) {
+        u.sc = *reinterpret_cast<const float4*>(unit + CODES + (lane >> 2) * 32);
+        u.mn = *reinterpret_cast<const float4*>(unit + CODES + (lane >> 2) * 32 + 16);
+        return;
+    }
     u.sc = *reinterpret_cast<const float4*>(unit + CODES + (lane >> 2) * 16);
-    if (KQ) u.mn = *reinterpret_cast<const float4*>(unit + CODES + 128 + (lane >> 2) * 16);
+    if (UK == 1) u.mn = *reinterpret_cast<const float4*>(unit + CODES + 128 + (lane >> 2) * 16);
 }
 
 // A-fragment registers of the two 16-row tiles (q = 0: rows gid, gid+8; q = 1: rows
@@ -432,18 +461,23 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
 template <int BITS>
 struct RowUnit {
     uint4 c0, c1, r;
-    float sc, mn;
+    float sc, mn;    // Q6_K: the row's scales of elements 0..15 and 16..31
+    uint32_t c2;     // Q6_K: the constant of the second half (the first half's is r.w)
 };
-template <int BITS, bool KQ = false>
+// `scale` = address of the lane's first scale: unit + CODES + lane * 4 (Q6_K: + lane * 8)
+template <int BITS, int UK = 0>
 __device__ __forceinline__ void row_load(RowUnit<BITS>& u, uint32_t codes, uint32_t scale, uint32_t rec) {
     u.c0 = lds128(codes);
     if (BITS == 8) u.c1 = lds128(codes + 512);
     u.sc = lds32f(scale);
-    if (KQ) u.mn = lds32f(scale + 128);   // the row's minimum db * bq: 32 floats behind the 32 scales
+    if (UK == 1) u.mn = lds32f(scale + 128);   // the row's minimum db * bq: 32 floats behind the 32 scales
+    if (UK == 2) u.mn = lds32f(scale + 4);
     u.r = lds128(rec);
+    if (UK == 2) u.c2 = __float_as_uint(lds32f(rec + 16));
 }
-template <int BITS, bool KQ = false>
+template <int BITS, int UK = 0>
 __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bool upper, float acc) {
+    constexpr bool KQ = UK == 1;
     uint32_t a[2][4];
     if (BITS == 4) {
         const uint32_t lo = 0x0F0F0F0Fu, hi = 0xF0F0F0F0u;
@@ -452,6 +486,21 @@ __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bo
     } else {
         a[0][0] = u.c0.x; a[0][1] = u.c0.y; a[0][2] = u.c1.x; a[0][3] = u.c1.y;
         a[1][0] = u.c0.z; a[1][1] = u.c0.w; a[1][2] = u.c1.z; a[1][3] = u.c1.w;
+    }
+    if (UK == 2) {
+        // Q6_K: a scale per 16 elements, so the two halves of the block are two tiles each: the
+        // same A registers against {b0, 0} and {0, b1}
+        int e0[4], e1[4], f0[4], f1[4];
+        imma_u8s8(e0, a[0], u.r.x, 0u);
+        imma_u8s8(f0, a[0], 0u, u.r.y);
+        imma_u8s8(e1, a[1], u.r.x, 0u);
+        imma_u8s8(f1, a[1], 0u, u.r.y);
+        const uint32_t lo_e = (uint32_t)(upper ? e1[0] : e0[0]), hi_e = (uint32_t)(upper ? e1[2] : e0[2]);
+        const uint32_t lo_f = (uint32_t)(upper ? f1[0] : f0[0]), hi_f = (uint32_t)(upper ? f1[2] : f0[2]);
+        const float ve = __uint_as_float((m ? hi_e : lo_e) + u.r.w) - kMagicFlt;
+        const float vf = __uint_as_float((m ? hi_f : lo_f) + u.c2) - kMagicFlt;
+        const float xs = __uint_as_float(u.r.z);
+        return fmaf(u.mn * xs, vf, fmaf(u.sc * xs, ve, acc));
     }
     int d0[4], d1[4];
     imma_u8s8(d0, a[0], u.r.x, u.r.y);
@@ -468,12 +517,46 @@ __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bo
     return fmaf(u.sc * __uint_as_float(u.r.z), f, acc);
 }
 
-template <int BITS, int NT, bool KQ = false>
+template <int BITS, int NT, int UK = 0>
 __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* smem,
                                         const StreamParams& p, int b, int gid, int tig,
                                         float (&acc)[NT][4][2]) {
+    constexpr bool KQ = UK == 1;
     uint32_t a[2][4];
     a_frags<BITS>(u, a);
+    if (UK == 2) {
+        // Q6_K: per (block, token) {xs, zp * sum of 0..15, zp * sum of 16..31}; two tiles per 16 rows
+        const int M = p.M, Mz = (M + 1) & ~1;
+        const uint2* xB = reinterpret_cast<const uint2*>(smem + p.act_off) + b * M * 4;
+        const int4* xz = reinterpret_cast<const int4*>(smem + p.act2_off) + b * Mz;
+        const float se[4] = {u.sc.x, u.sc.z, u.mn.x, u.mn.z};   // rows gid + 8i, elements 0..15
+        const float sf[4] = {u.sc.y, u.sc.w, u.mn.y, u.mn.w};   // elements 16..31
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            int col = nt * 8 + gid;
+            col = col < M ? col : M - 1;
+            const uint2 bb = xB[col * 4 + tig];
+            int c0 = nt * 8 + 2 * tig;
+            c0 = c0 < Mz ? c0 : 0;
+            const int4 z0 = xz[c0], z1 = xz[c0 + 1];
+            const float xs0 = __int_as_float(z0.x), xs1 = __int_as_float(z1.x);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                int de[4], df[4];
+                imma_acc(de, a[q], bb.x, 0u, kMagicInt - z0.y, kMagicInt - z1.y, kMagicInt - z0.y, kMagicInt - z1.y);
+                imma_acc(df, a[q], 0u, bb.y, kMagicInt - z0.z, kMagicInt - z1.z, kMagicInt - z0.z, kMagicInt - z1.z);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {   // row gid + 8 (2q + i)
+                    const float s_e = se[2 * q + i], s_f = sf[2 * q + i];
+                    acc[nt][2 * q + i][0] = fmaf(s_f * xs0, __int_as_float(df[2 * i]) - kMagicFlt,
+                                                 fmaf(s_e * xs0, __int_as_float(de[2 * i]) - kMagicFlt, acc[nt][2 * q + i][0]));
+                    acc[nt][2 * q + i][1] = fmaf(s_f * xs1, __int_as_float(df[2 * i + 1]) - kMagicFlt,
+                                                 fmaf(s_e * xs1, __int_as_float(de[2 * i + 1]) - kMagicFlt, acc[nt][2 * q + i][1]));
+                }
+            }
+        }
+        return;
+    }
     const float sc[4] = {u.sc.x, u.sc.y, u.sc.z, u.sc.w};
     const float mn[4] = {u.mn.x, u.mn.y, u.mn.z, u.mn.w};
     // value of the high-nibble rows is 16x: scale by xs/16 and shift their zero-point term
@@ -597,9 +680,10 @@ __device__ __forceinline__ float stream_reduce_rc(const float* red, int row, int
 
 // ---- the kernel ---------------------------------------------------------------------
 // QF: M == 1 only, the kernel quantizes the raw activations p.x itself while staging.
-template <int BITS, int NT, int MODE, bool ONECOL, bool TP, bool QF = false, bool KQ = false>
+template <int BITS, int NT, int MODE, bool ONECOL, bool TP, bool QF = false, int UK = 0>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
-    constexpr int UNIT = BITS == 4 ? (KQ ? kUnitBytesQ4K : kUnitBytesQ4) : kUnitBytesQ8;
+    constexpr int UNIT = BITS == 4 ? (UK == 1 ? kUnitBytesQ4K : kUnitBytesQ4) : (UK == 2 ? kUnitBytesQ6K : kUnitBytesQ8);
+    constexpr int REC = UK == 2 ? 32 : 16;   // bytes of a staged (block, tig) record at M = 1
     constexpr int kUPW = upw_of(BITS), kChunkUnits = chunk_units_of(BITS);
     constexpr int CHUNK_BYTES = kChunkUnits * UNIT;
     constexpr int NV = NT * 8;
@@ -972,13 +1056,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         // every load issued before the first tensor-core tile) and one ragged chunk, whole groups
         // parked without a barrier.
         constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
-        constexpr uint32_t USTEP = kCW * UNIT, RSTEP = kCW * 64;   // next unit / record of this warp in a chunk
+        constexpr uint32_t USTEP = kCW * UNIT, RSTEP = kCW * 4 * REC;   // next unit / record of this warp in a chunk
         const uint32_t ring = smem_u32(smem), act = smem_u32(smem + p.act_off);
         const uint32_t m = (tig & 1) ? 0xFFFFFFFFu : 0u;
         const bool upper = tig & 2;
         uint32_t codes = ring + warp * UNIT + lane * 16;            // this lane's slot of the warp's first unit
-        uint32_t scale = ring + warp * UNIT + CODES + lane * 4;
-        uint32_t rec = act + ((b_start + warp) * 4 + tig) * 16;
+        uint32_t scale = ring + warp * UNIT + CODES + lane * (UK == 2 ? 8 : 4);
+        uint32_t rec = act + ((b_start + warp) * 4 + tig) * REC;
         int s = 0, left = total, b = b_start;
         uint32_t ph = 0;
         bool alive = true;
@@ -1022,14 +1106,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     if (n == kChunkUnits) {
                         RowUnit<BITS> u[kUPW];
 #pragma unroll
-                        for (int j = 0; j < kUPW; ++j) row_load<BITS, KQ>(u[j], codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
+                        for (int j = 0; j < kUPW; ++j) row_load<BITS, UK>(u[j], codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
 #pragma unroll
-                        for (int j = 0; j < kUPW; ++j) v = row_fold<BITS, KQ>(u[j], m, upper, v);
+                        for (int j = 0; j < kUPW; ++j) v = row_fold<BITS, UK>(u[j], m, upper, v);
                     } else {
                         for (int j = 0; warp + j * kCW < n; ++j) {
                             RowUnit<BITS> u;
-                            row_load<BITS, KQ>(u, codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
-                            v = row_fold<BITS, KQ>(u, m, upper, v);
+                            row_load<BITS, UK>(u, codes + j * USTEP, scale + j * USTEP, rec + j * RSTEP);
+                            v = row_fold<BITS, UK>(u, m, upper, v);
                         }
                     }
                 }
@@ -1040,7 +1124,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 stamp();
                 CK_ADD(2);
                 done += n;
-                rec += n * 64;
+                rec += n * 4 * REC;
                 if (sn) {
                     codes += CHUNK_BYTES;
                     scale += CHUNK_BYTES;
@@ -1072,7 +1156,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             }
             stamp();
             CK_ADD(4);
-            rec -= (b + seg) * 64;   // back to block 0 of the next group
+            rec -= (b + seg) * 4 * REC;   // back to block 0 of the next group
             b = 0;
             ++g;
         }
@@ -1100,9 +1184,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (alive && !PROBE(2)) {
                 for (int j = 0; warp + j * kCW < n; ++j) {
                     SUnit<BITS> un;
-                    lds_unit<BITS, KQ>(un, unit0 + j * kCW * UNIT, lane);
+                    lds_unit<BITS, UK>(un, unit0 + j * kCW * UNIT, lane);
                     const int blk = b + warp + j * kCW;
-                    if (MODE == MODE_A8) unit_a8<BITS, NT, KQ>(un, smem, p, blk, gid, tig, acc);
+                    if (MODE == MODE_A8) unit_a8<BITS, NT, UK>(un, smem, p, blk, gid, tig, acc);
                     else unit_f<BITS, NT>(un, smem, p, blk, gid, tig, acc);
                 }
             }
@@ -1304,9 +1388,13 @@ int32_t gemv_configure(DeviceState& ds) {
     if ((rc = set_stream_attr(gemv_stream_kernel<8, 1, MODE_A8, true, false, true>)) != RSTQ_OK) return rc;
     if ((rc = set_stream_attr(gemv_stream_kernel<8, 1, MODE_A8, true, true, true>)) != RSTQ_OK) return rc;
     // Q4_K units (minima inside)
-    if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, true, false, false, true>)) != RSTQ_OK) return rc;
-    if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, false, false, false, true>)) != RSTQ_OK) return rc;
-    if ((rc = set_stream_attr(gemv_stream_kernel<4, 2, MODE_A8, false, false, false, true>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, true, false, false, 1>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<4, 1, MODE_A8, false, false, false, 1>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<4, 2, MODE_A8, false, false, false, 1>)) != RSTQ_OK) return rc;
+    // Q6_K units (8-bit codes, a scale per 16 elements)
+    if ((rc = set_stream_attr(gemv_stream_kernel<8, 1, MODE_A8, true, false, false, 2>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<8, 1, MODE_A8, false, false, false, 2>)) != RSTQ_OK) return rc;
+    if ((rc = set_stream_attr(gemv_stream_kernel<8, 2, MODE_A8, false, false, false, 2>)) != RSTQ_OK) return rc;
     return RSTQ_OK;
 }
 
@@ -1388,13 +1476,16 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
     RSTQ_REQUIRE(a.M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)a.M);
     const int64_t nb = a.in / 32, groups = (a.out + 31) / 32;
     RSTQ_REQUIRE(nb < (1 << 24) && groups * nb < (1ll << 40), RSTQ_E_LIMIT, "matrix too large");
+    const bool k6 = a.uk == 2;
     auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
         *NT = m <= 8 ? 1 : 2;
-        if (m == 1) { *a1 = nb * 64; *a2 = 0; }
-        else { *a1 = nb * m * 32; *a2 = nb * ((m + 1) & ~1) * 8; }
+        if (m == 1) { *a1 = nb * (k6 ? 128 : 64); *a2 = 0; }
+        else { *a1 = nb * m * 32; *a2 = nb * ((m + 1) & ~1) * (k6 ? 16 : 8); }
     };
-    const int ukind = a.kq ? 5 : a.bits;   // unit kind for the size helpers: Q4_K units carry 128 more bytes
-    RSTQ_REQUIRE(!a.kq || (a.bits == 4 && !a.tp && !a.x), RSTQ_E_INVALID, "Q4_K units: 4-bit, one device, pre-quantized activations");
+    // unit kind for the size helpers: Q4_K units carry 128 more bytes than 4-bit ones, Q6_K units 128 more than 8-bit ones
+    const int ukind = a.uk == 1 ? 5 : (k6 ? 6 : a.bits);
+    RSTQ_REQUIRE(a.uk == 0 || (a.bits == (k6 ? 8 : 4) && !a.tp && !a.x), RSTQ_E_INVALID,
+                 "K-quant units: one device, pre-quantized activations");
     for (int64_t m0 = 0; m0 < a.M;) {
         const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
         StreamPlan pl;
@@ -1411,17 +1502,18 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         StreamParams p{};
         fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp, ukind);
         p.w = a.w;
-        p.kq = a.kq ? 1 : 0;
+        p.kq = a.uk == 1;
+        p.k6 = k6;
         if (qf) {
             p.x = a.x;
         } else {
             p.xq = a.xq + m0 * a.in;
             p.xs = a.xs + m0 * nb;
-            p.xsum = a.xsum + m0 * nb;
+            p.xsum = a.xsum + m0 * nb * (k6 ? 2 : 1);   // Q6_K: sums per 16 elements
         }
         p.y = a.y + m0 * a.out;
         p.T = 1; p.act_dtype = qf ? a.act_dtype : RSTQ_F32; p.out_dtype = RSTQ_F32;
-        if (a.img && M > 1 && M == a.M) {   // the image was laid out for the whole call: one piece only
+        if (a.img && M > 1 && M == a.M && a.uk == 0) {   // the image was laid out for the whole call: one piece only
             p.img = a.img;
             p.img_b_bytes = (uint32_t)(nb * M * 32);
             p.img_z_bytes = (uint32_t)(nb * ((M + 1) & ~1) * 8);
@@ -1440,10 +1532,14 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         else le = qf ? launch_stream(gemv_stream_kernel<B, 1, MODE_A8, true, false, true>, ds, pl, p)      \
                      : launch_stream(gemv_stream_kernel<B, 1, MODE_A8, true, false, false>, ds, pl, p);    \
     } while (0)
-        if (a.kq) {
-            if (NT == 2) le = launch_stream(gemv_stream_kernel<4, 2, MODE_A8, false, false, false, true>, ds, pl, p);
-            else if (M == 1) le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, true, false, false, true>, ds, pl, p);
-            else le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, false, false, false, true>, ds, pl, p);
+        if (k6) {
+            if (NT == 2) le = launch_stream(gemv_stream_kernel<8, 2, MODE_A8, false, false, false, 2>, ds, pl, p);
+            else if (M == 1) le = launch_stream(gemv_stream_kernel<8, 1, MODE_A8, true, false, false, 2>, ds, pl, p);
+            else le = launch_stream(gemv_stream_kernel<8, 1, MODE_A8, false, false, false, 2>, ds, pl, p);
+        } else if (a.uk == 1) {
+            if (NT == 2) le = launch_stream(gemv_stream_kernel<4, 2, MODE_A8, false, false, false, 1>, ds, pl, p);
+            else if (M == 1) le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, true, false, false, 1>, ds, pl, p);
+            else le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, false, false, false, 1>, ds, pl, p);
         } else if (a.bits == 4) {
             if (NT == 2) LAUNCH(4, 2, MODE_A8, false);
             else if (M == 1) LAUNCH1(4);

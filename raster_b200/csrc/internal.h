@@ -52,12 +52,15 @@ int32_t cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 // One 16-byte load per lane thus feeds two 16-row tensor-core tiles with no
 // data movement between lanes.
 constexpr int kUnitBytesQ4 = 640;
+constexpr int kUnitBytesQ6K = 1280;  // 1024 bytes of 8-bit codes as in the 8-bit unit, then 64 scales (one per row and 16 elements)
 constexpr int kUnitBytesQ4K = 768;  // a 4-bit unit with the 32 Q4_K minima (db * bq, added as they are) behind the 32 scales
 constexpr int kUnitBytesQ8 = 1152;
 constexpr int kUnitCodesQ4 = 512;
 constexpr int kUnitCodesQ8 = 1024;
 // `bits` here is the unit kind: 4, 8, or 5 = the Q4_K unit
-inline int unit_bytes(int bits) { return bits == 4 ? kUnitBytesQ4 : (bits == 5 ? kUnitBytesQ4K : kUnitBytesQ8); }
+inline int unit_bytes(int bits) {
+    return bits == 4 ? kUnitBytesQ4 : (bits == 5 ? kUnitBytesQ4K : (bits == 6 ? kUnitBytesQ6K : kUnitBytesQ8));
+}
 
 struct DeviceState {
     int ordinal = -1;
@@ -112,6 +115,7 @@ struct rstq_ctx {
     std::vector<rstq::DeviceState> devs;
     int64_t tune_gemm_min_m = 17;
     bool tune_q4k_units = true;     // Q4_K weights bound from now on keep their minima inside the units
+    bool tune_q6k_units = true;     // Q6_K weights bound from now on are 1280-byte units (a scale per 16 elements), not twin rows
     int64_t tune_gemm_kernel = 0;   // 0 = weights in tensor memory, 1 = weights through shared memory
     int64_t launches = 0;
     struct CacheKey {
@@ -165,6 +169,8 @@ struct rstq_weight {
     rstq_weight* next_hint = nullptr;
     float* mins = nullptr;         // Q4_K only: per-sub-block minima db*bq, [out, nb]; zp is 0 then
     bool kq = false;               // Q4_K only: `data` holds 768-byte units with the minima inside (default)
+    bool k6 = false;               // Q6_K only: `data` holds 1280-byte units with a scale per 16 elements (default);
+                                   // `out` is then the logical row count (= pair_out), not twice it
     int64_t pair_out = 0;          // Q6_K only: logical rows; `out` = 2 * pair_out twin rows, y[o] = t[2o] + t[2o+1]
 };
 
@@ -200,6 +206,9 @@ int32_t launch_repack(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src_codes,
 // 640-byte 4-bit units + row-major minima [out, nb] -> 768-byte Q4_K units (the minimum db * bq of
 // row gid + 8i of the group at float gid*4 + i behind the scales, the order the scales have)
 int32_t launch_q4k_units(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src, const float* mins, uint8_t* dst,
+                         int64_t out, int64_t nb);
+// 1152-byte 8-bit units + row-major scales per 16 elements [out, in/16] -> 1280-byte Q6_K units
+int32_t launch_q6k_units(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src, const float* scales16, uint8_t* dst,
                          int64_t out, int64_t nb);
 // kquant.cu (Q4_K: q8_K activation quantizer, scale expansion, the min-term GEMV)
 int32_t launch_quant_act_q8k(rstq_ctx* ctx, DeviceState& ds, const float* x, int8_t* xq, float* xs, float* xs32,
@@ -247,7 +256,9 @@ struct GemvA8Args {
     int act_dtype = RSTQ_F32;    // itself while staging; xq / xs / xsum are then not read
     NextWeight next;
     const uint8_t* img = nullptr;  // M > 1: the quantizer's image of the staged activations (see StreamParams::img)
-    bool kq = false;               // w holds Q4_K units (768 B, minima inside): xs / xsum are the q8_K scales and sums
+    int uk = 0;                    // unit kind of w: 0 = plain, 1 = Q4_K units (768 B, minima inside; xs / xsum are the
+                                   // q8_K scales per block and sums per 32), 2 = Q6_K units (1280 B, a scale per 16
+                                   // elements; xsum holds the sums per 16, two per block)
 };
 struct GemvFArgs {
     const uint8_t* w;

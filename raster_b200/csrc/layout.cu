@@ -144,6 +144,41 @@ __global__ void q4k_units_kernel(const uint8_t* __restrict__ src, const float* _
     }
 }
 
+// 1152-byte 8-bit units (their 32 scales are dropped) + row-major scales per 16 elements
+// [out, in/16] -> 1280-byte Q6_K units: one thread per destination word, 256 words of codes as they
+// are, then 64 scales: float (gid*4 + i)*2 + h = row gid + 8i of the group, elements 16h .. 16h + 15.
+__global__ void q6k_units_kernel(const uint8_t* __restrict__ src, const float* __restrict__ scales16,
+                                 uint8_t* __restrict__ dst, int64_t out, int64_t nb, int64_t groups) {
+    constexpr int CW = kUnitCodesQ8 / 4, DW = kUnitBytesQ6K / 4;
+    const int64_t total = groups * nb * DW;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t unit = idx / DW;
+        const int wi = (int)(idx % DW);
+        uint32_t v;
+        if (wi < CW) {
+            v = reinterpret_cast<const uint32_t*>(src + unit * kUnitBytesQ8)[wi];
+        } else {
+            const int si = wi - CW, h = si & 1, slot = si >> 1;
+            const int64_t g = unit / nb, b = unit % nb;
+            const int64_t row = g * 32 + (slot >> 2) + 8 * (slot & 3);
+            v = __float_as_uint(row < out ? scales16[row * (nb * 2) + b * 2 + h] : 0.0f);
+        }
+        reinterpret_cast<uint32_t*>(dst + unit * kUnitBytesQ6K)[wi] = v;
+    }
+}
+
+int32_t launch_q6k_units(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src, const float* scales16, uint8_t* dst,
+                         int64_t out, int64_t nb) {
+    const int64_t groups = (out + 31) / 32, total = groups * nb * (kUnitBytesQ6K / 4);
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (blocks < 1) blocks = 1;
+    q6k_units_kernel<<<blocks, 256, 0, ds.stream>>>(src, scales16, dst, out, nb, groups);
+    ctx->launches++;
+    RSTQ_CUDA(cudaGetLastError());
+    return RSTQ_OK;
+}
+
 int32_t launch_q4k_units(rstq_ctx* ctx, DeviceState& ds, const uint8_t* src, const float* mins, uint8_t* dst,
                          int64_t out, int64_t nb) {
     const int64_t groups = (out + 31) / 32, total = groups * nb * (kUnitBytesQ4K / 4);

@@ -188,6 +188,36 @@ def test_q6k_matmul_matches_the_oracle(ctx, out, in_, M):
         o.free()
 
 
+@pytest.mark.parametrize("M,out,in_", [(1, 200, 1024), (3, 96, 512), (9, 72, 2048)])
+def test_q6k_twin_rows_layout_matches_too(ctx, M, out, in_):
+    """RSTQ_TUNE_Q6K_UNITS = 0: two twin rows of 8-bit units per row and a kernel that adds the pairs (the first
+    layout); 1 (default): units with a scale per 16 elements.  Both against the oracle and against each other."""
+    W = synth.normal(51 + out, out * in_, 0.02)
+    x = synth.normal(52 + in_, M * in_)
+    e = orc.quantize_weight_q6k(W)
+    ref = oracle_rows_q6k(e, x, M, in_, out)
+    ys, dev_bytes = [], []
+    try:
+        for units in (0, 1):
+            ctx.tune(L.TUNE_Q6K_UNITS, units)
+            w = ctx.bind_weight_q6k(e, out, in_)
+            assert (w.out, w.in_) == (out, in_)
+            dev_bytes.append(w.device_bytes)
+            bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+            n0 = ctx.launch_count()
+            ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+            ctx.sync()
+            assert ctx.launch_count() - n0 == (2 if units else 3)
+            ys.append(by.download())
+            assert relerr(ys[-1], ref) <= 1e-5
+            for o in (w, bx, by):
+                o.free()
+    finally:
+        ctx.tune(L.TUNE_Q6K_UNITS, 1)
+    assert relerr(ys[0], ys[1].reshape(ys[0].shape)) <= 2e-6
+    assert dev_bytes[1] <= 0.7 * dev_bytes[0]        # 1280 against 2 x 1152 bytes per 32 x 32 weights (rows padded to 32)
+
+
 def test_q6k_reference_case_and_registry(ctx):
     from raster_b200.quant import core as qcore
     out, in_ = 8, 256                                   # kernels_k_test.clj:52-66, seeds 3 and 4
