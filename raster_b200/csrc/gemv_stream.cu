@@ -1182,14 +1182,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (alive && !mbar_test(full0 + 8 * s, ph) && !mbar_try(full0 + 8 * s, ph))
                 alive = mbar_wait(full0 + 8 * s, ph, abort_flag);
             if (alive && !PROBE(2)) {
-                if (n == kChunkUnits && MODE == MODE_A8 && NT == 1) {
+                if (n == kChunkUnits && NT == 1) {
                     // a full chunk: this warp's units are all loaded before the first tile, so that
                     // the shared-memory round trips of one unit run under the arithmetic of another
                     SUnit<BITS> un[kUPW];
 #pragma unroll
                     for (int j = 0; j < kUPW; ++j) lds_unit<BITS, UK>(un[j], unit0 + j * kCW * UNIT, lane);
 #pragma unroll
-                    for (int j = 0; j < kUPW; ++j) unit_a8<BITS, NT, UK>(un[j], smem, p, b + warp + j * kCW, gid, tig, acc);
+                    for (int j = 0; j < kUPW; ++j) {
+                        if (MODE == MODE_A8) unit_a8<BITS, NT, UK>(un[j], smem, p, b + warp + j * kCW, gid, tig, acc);
+                        else unit_f<BITS, NT>(un[j], smem, p, b + warp + j * kCW, gid, tig, acc);
+                    }
                 } else {
                     for (int j = 0; warp + j * kCW < n; ++j) {
                         SUnit<BITS> un;
