@@ -527,8 +527,10 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
 // tensor-memory sub-partition), (warp - 2) >> 2 = block of the K-step.
 constexpr int kGemmThreadsT = (3 + kDqWarps) * 32;  // TMA warp, MMA warp (even K-steps), 16 dequant / epilogue warps, MMA warp (odd K-steps)
 // pipeline stages (B in shared memory, A in tensor memory): what is left of the 512 columns after two
-// accumulators, at most 6
-__host__ __device__ constexpr int gemm_stages(int ntok) { return (512 - 2 * ntok) / 64 > 6 ? 6 : (512 - 2 * ntok) / 64; }
+// accumulators, at most 4: with exactly four the dequant warps run their two-set schedule, which
+// measured faster than six stages on the one-set schedule where six would fit (M <= 64: 76 -> 68 us
+// at M = 16 on 28672 x 8192)
+__host__ __device__ constexpr int gemm_stages(int ntok) { return (512 - 2 * ntok) / 64 > 4 ? 4 : (512 - 2 * ntok) / 64; }
 constexpr int kAColsPerStage = kKStep / 2;
 constexpr int kWeightPfSteps = 8;  // K-steps of packed weights requested into L2 ahead of the loads
 
