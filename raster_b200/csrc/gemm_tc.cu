@@ -10,17 +10,19 @@
 //
 //  * A is produced on the fly: 16 warps read the packed 4/8-bit codes and f32
 //    block scales of the mma32 layout straight from global memory (register
-//    prefetch three K-steps ahead), convert code -> fp16 with the 0x6400 magic
-//    (exact integers), multiply by the block scale and store 16-byte rows into
-//    shared memory in the K-major 128-byte-swizzled layout the tensor core
-//    reads.  fp16 (11-bit significand) rather than bf16 keeps the result within
-//    1e-3 of the f32 reference; a per-matrix power of two keeps scaled weights
-//    in fp16 range.
+//    prefetch four K-steps ahead, behind requests into L2 eight more ahead),
+//    turn code and block scale into fp16 (exact integers times the rounded
+//    scale) and hand them to the tensor core: gemm_tmem_kernel, the default,
+//    stores them into a ring in tensor memory; gemm_tc_kernel stores 16-byte
+//    rows into shared memory in the K-major 128-byte-swizzled layout.  fp16
+//    (11-bit significand) rather than bf16 keeps the result within 1e-3 of the
+//    f32 reference; a per-matrix power of two keeps scaled weights in fp16 range.
 //  * B comes from a small pre-pass that rewrites the activations as fp16 with
 //    one power-of-two exponent per token row (exact for bf16 inputs), loaded by
 //    TMA (cp.async.bulk.tensor, 128-byte swizzle) by one producer thread.
-//  * One thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = NTOK,
-//    K = 16 per instruction); tcgen05.commit releases a stage to the producers.
+//  * One thread (gemm_tmem_kernel: one of two, on alternate K-steps) issues
+//    tcgen05.mma (cta_group::1, kind::f16, M = 128, N = NTOK, K = 16 per
+//    instruction); tcgen05.commit releases a stage to the producers.
 //  * The 16 dequant warps then read the accumulator with tcgen05.ld, undo the two
 //    exponents and store y (f32 or bf16) row-major [token, feature].
 // Every mbarrier wait is time-bounded; on expiry the CTA reports through the
@@ -523,8 +525,10 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
 // slot, so every lane converts its slot in registers and stores it to the A ring in tensor
 // memory (64 columns per 128-element K-step); tcgen05.mma reads A from tensor memory and only B
 // from shared memory, which halves the shared-memory traffic of the K loop.
-// Warp roles: 0 = TMA (activations), 1 = MMA, 2..17 = dequant: warp & 3 = 32-row group (= its
-// tensor-memory sub-partition), (warp - 2) >> 2 = block of the K-step.
+// Warp roles: 0 = TMA (activations) and the L2 requests for the weights, 1 and 18 = MMA (even / odd
+// K-steps), 2..17 = dequant, then epilogue: warp & 3 = 32-row group (= its tensor-memory
+// sub-partition); t = (warp - 2) >> 2 picks, on whole K-steps, the set (t & 1: even / odd K-steps) and
+// the pair of blocks (2 (t >> 1), + 1) of a K-step, otherwise the one block t of every K-step.
 constexpr int kGemmThreadsT = (3 + kDqWarps) * 32;  // TMA warp, MMA warp (even K-steps), 16 dequant / epilogue warps, MMA warp (odd K-steps)
 // pipeline stages (B in shared memory, A in tensor memory): what is left of the 512 columns after two
 // accumulators, at most 4: with exactly four the dequant warps run their two-set schedule, which
