@@ -146,6 +146,12 @@ __device__ __forceinline__ void imma_acc(int (&d)[4], const uint32_t (&a)[4], ui
 //            otherwise xs_t = xs and c_t = bias - zp*xsum (bias = bits of 2^23 + 2^22).
 // A8, M > 1 : sB [nb][M][4 tig] uint2 {xq word tig, xq word 4+tig};
 //             sxz [nb][Mz] int2 {xs bits, zp*xsum}, Mz = M rounded up to even.
+//             (For 2 <= M <= 16 the activation quantizer can write both arrays in this order itself:
+//             StreamParams::img, copied in by the producer thread instead of staged here.)
+// K-quant units: Q4_K (zero point 0): the constant of a record is t = xs * code sum, which the unit's
+//             minima multiply (c_t at M = 1, the second word of sxz otherwise).  Q6_K: xsum holds the
+//             code sums per 16 elements; M = 1 records are 32 bytes {.., c of elements 0..15 | c of
+//             16..31, 0, 0, 0}, sxz entries int4 {xs bits, zp*sum of 0..15, zp*sum of 16..31, 0}.
 template <bool ONECOL, int BITS>
 __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, int tid) {
     const int nb = p.nb, M = p.M;
