@@ -845,7 +845,8 @@ def gemm_detail(ctx, info, M=512, K=4096, N=4096):
 def c5_detail(ctx, info, steps=3):
     """BASELINE configs[4] on one GPU: int4 W 8192x28672 and 28672x8192 (random codes, scales of the
     N(0, 0.015) magnitude), bf16 activations N(0, 1), M in {1, 16, 64, 256}; f32 output for M <= 16, bf16
-    above (the prefill path).  Distinct weight copies, more than L2 in total, replayed from one graph."""
+    above (the prefill path): MODE_F, and for M <= 16 MODE_A8 as well (`_a8_`).  Distinct weight copies, more than
+    L2 in total, replayed from one graph."""
     from raster_b200 import _lib as L
     from raster_b200 import synth
     out = {}
@@ -876,6 +877,22 @@ def c5_detail(ctx, info, steps=3):
             out[f"c5_{name}_M{M}_GBs"] = round(first.stream_bytes / us / 1e3, 1)
             if M >= 64:
                 out[f"c5_{name}_M{M}_TFLOPs"] = round(2.0 * M * N * K / us / 1e6, 1)
+            if M <= 16:
+                # the same call in the reference's own int4 arithmetic (qlinear-i8: activations quantized to
+                # int8 per 32-block, exact integer dots), which the decode kernel streams at the int8 tile rate
+                def fa():
+                    for w in ws:
+                        ctx.qmatmul(w, x, y, M, L.BF16, L.F32, L.MODE_A8)
+                fa()
+                fa()
+                ctx.sync()
+                ctx.graph_begin()
+                fa()
+                g = ctx.graph_end()
+                us = time_graph(ctx, g, steps, 2) * 1e3 / steps / R
+                g.destroy()
+                out[f"c5_{name}_M{M}_a8_us"] = round(us, 2)
+                out[f"c5_{name}_M{M}_a8_GBs"] = round(first.stream_bytes / us / 1e3, 1)
             x.free(), y.free()
         for w in ws:
             w.free()
