@@ -581,6 +581,10 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
         case RSTQ_TUNE_Q6K_UNITS:
             ctx->tune_q6k_units = value != 0;
             return RSTQ_OK;
+        case RSTQ_TUNE_GEMM_WIDE:
+            RSTQ_REQUIRE(value >= 0 && value <= 2, RSTQ_E_INVALID, "256-token tile selector 0..2");
+            ctx->tune_gemm_wide = value;
+            return RSTQ_OK;
         case RSTQ_TUNE_ACT_IMAGE:
             for (auto& ds : ctx->devs) ds.act_image = value != 0;
             return RSTQ_OK;

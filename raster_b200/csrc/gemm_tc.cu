@@ -534,7 +534,10 @@ constexpr int kGemmThreadsT = (3 + kDqWarps) * 32;  // TMA warp, MMA warp (even 
 // accumulators, at most 4: with exactly four the dequant warps run their two-set schedule, which
 // measured faster than six stages on the one-set schedule where six would fit (M <= 64: 76 -> 68 us
 // at M = 16 on 28672 x 8192)
-__host__ __device__ constexpr int gemm_stages(int ntok) { return (512 - 2 * ntok) / 64 > 4 ? 4 : (512 - 2 * ntok) / 64; }
+__host__ __device__ constexpr int gemm_stages(int ntok) { return ntok > 128 ? 3 : ((512 - 2 * ntok) / 64 > 4 ? 4 : (512 - 2 * ntok) / 64); }
+// A 256-token tile has one accumulator (256 columns) and one issuing thread: an MMA then takes the
+// tensor core 128 cycles, more than its issue costs; its activation stage is 64 KB, so three stages.
+__host__ __device__ constexpr int gemm_issuers(int ntok) { return ntok > 128 ? 1 : 2; }
 constexpr int kAColsPerStage = kKStep / 2;
 constexpr int kWeightPfSteps = 8;  // K-steps of packed weights requested into L2 ahead of the loads
 
@@ -637,10 +640,11 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
     constexpr int CODES = BITS == 4 ? kUnitCodesQ4 : kUnitCodesQ8;
     constexpr int BSTAGE = NTOK * kKStep * 2;
     constexpr int kNSTT = gemm_stages(NTOK);
-    constexpr uint32_t TMEM_COLS = 512;                       // two accumulators (2 x NTOK) + A ring, power of two
-    constexpr uint32_t A_COL0 = 2 * NTOK;                     // A ring starts after the accumulators
-    static_assert(2 * NTOK + kNSTT * kAColsPerStage <= 512 && kNSTT >= 2 && kNSTT % 2 == 0,
-                  "tensor memory holds both accumulators and the A ring");
+    constexpr int ISS = gemm_issuers(NTOK);
+    constexpr uint32_t TMEM_COLS = 512;                       // ISS accumulators (NTOK columns each) + A ring, power of two
+    constexpr uint32_t A_COL0 = ISS * NTOK;                   // A ring starts after the accumulators
+    static_assert(ISS * NTOK + kNSTT * kAColsPerStage <= 512 && kNSTT >= 3,
+                  "tensor memory holds the accumulators and the A ring");
     extern __shared__ uint8_t smem_raw[];
     if (p.dbg && blockIdx.x == 0 && threadIdx.x == 64) { p.dbg[300] = (unsigned long long)clock64(); p.dbg[304] = gtime_ns(); }
     __shared__ int s_abort;
@@ -662,7 +666,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
 
     // four-stage ring and whole K-steps: the dequant warps work as two sets of eight on alternate
     // K-steps (see there), so a stage collects eight arrivals instead of sixteen
-    const bool paired = kNSTT == 4 && (p.nb & 3) == 0;
+    const bool paired = (p.nb & 3) == 0;
     if (tid == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
     if (paired && warp >= 2 && warp < 2 + kDqWarps) {
         // the first weights this warp will load: ask for them now, so that the HBM round trip
@@ -681,7 +685,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
         mbar_init(full + 8 * tid, (paired ? kDqWarps / 2 : kDqWarps) + 1);
         mbar_init(empty + 8 * tid, 1);
     } else if (tid == kNSTT) {
-        mbar_init(acc_full, ksteps >= 2 ? 2 : 1);  // one arrival per MMA issuer that has steps
+        mbar_init(acc_full, (ISS == 2 && ksteps >= 2) ? 2 : 1);  // one arrival per MMA issuer that has steps
         s_abort = 0;
     }
     if (tid <= kNSTT) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -749,7 +753,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                 }
             }
         }
-    } else if (warp == 1 || warp == 2 + kDqWarps) {
+    } else if (warp == 1 || (ISS == 2 && warp == 2 + kDqWarps)) {
         // ---------------- MMA issuers ----------------
         // Issuing is what limits the tensor core here: a tcgen05 instruction costs the issuing
         // thread 50 - 60 cycles (measured: an MMA, a commit and a barrier test alike, whatever N
@@ -772,8 +776,8 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             bool any = false;
             bool ok = mbar_spin(full + 8 * s, 0, abort_flag);
             if (dbg && lane == 0) dbg[306 + 2 * m] = (unsigned long long)clock64();
-            for (int ks = m; ks < ksteps && ok; ks += 2) {
-                int s2 = s + 2;
+            for (int ks = m; ks < ksteps && ok; ks += ISS) {
+                int s2 = s + ISS;
                 uint32_t ph2 = ph;
                 if (s2 >= kNSTT) { s2 -= kNSTT; ph2 ^= 1u; }
                 const uint32_t a0 = tmem + A_COL0 + s * kAColsPerStage, b_lo = d_lo + (uint32_t)s * (BSTAGE >> 4);
@@ -782,7 +786,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                                                                full + 8 * s2, ph2);
                 umma_commit_if(empty + 8 * s, leader);  // the stage is free once these MMAs have read it
                 any = true;
-                if (ks + 2 < ksteps && !n2) ok = mbar_spin(full + 8 * s2, ph2, abort_flag);
+                if (ks + ISS < ksteps && !n2) ok = mbar_spin(full + 8 * s2, ph2, abort_flag);
                     s = s2;
                 ph = ph2;
             }
@@ -796,6 +800,8 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                 }
             }
         }
+    } else if (warp == 2 + kDqWarps) {
+        // the second issuer warp of the two-accumulator tiles: nothing to do on a 256-token tile
     } else {
         // ---------------- dequant warps ----------------
         const int dq = warp - 2, grp = warp & 3, sub = dq >> 2;
@@ -920,19 +926,22 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                 raw[d][1] = RawT<BITS>{};
                 if (d < n_own) fetch2(raw[d], d);
             }
-            uint32_t par = 1;  // parity of "stage free": the first pass through the ring finds every stage free
+            // stage and "stage free" parity of K-step ks: ring position ks % stages, pass ks / stages
+            // (the first pass finds every stage free: parity 1)
+            auto stage_of = [&](int ks) { return ks % kNSTT; };
+            auto parity_of = [&](int ks) { return (uint32_t)(((ks / kNSTT) & 1) ^ 1); };
             int i = 0;
             for (; i + 2 <= n_own && ok; i += 2) {
-                ok = step2(raw[0], pset, par);
+                const int ks = pset + 2 * i;
+                ok = step2(raw[0], stage_of(ks), parity_of(ks));
                 if (i + 2 < n_own) fetch2(raw[0], 2);
                 if (ok) {
-                    ok = step2(raw[1], pset + 2, par);
+                    ok = step2(raw[1], stage_of(ks + 2), parity_of(ks + 2));
                     if (i + 3 < n_own) fetch2(raw[1], 3);
                 }
                 wl += (size_t)16 * UNIT;
-                par ^= 1u;
             }
-            if (ok && i < n_own) ok = step2(raw[0], pset, par);
+            if (ok && i < n_own) ok = step2(raw[0], stage_of(pset + 2 * i), parity_of(pset + 2 * i));
         } else {
             RawT<BITS> raw[kPrefetch];
 #pragma unroll
@@ -955,13 +964,23 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
         }
 
         // ---------------- epilogue: tensor memory -> y ----------------
-        // this warp's token scales, one per lane, fetched while the last MMAs run
-        // (the pre-pass that wrote them completed before any activation tile was loaded)
-        float rs_lane = 0.f;
+        // A warp owns 32 features (its tensor-memory lanes) x CPW tokens, handled CH <= 32 tokens at a
+        // time.  Its token scales, one per lane and chunk, are fetched while the last MMAs run (the
+        // pre-pass that wrote them completed before any activation tile was loaded).
+        constexpr int CPW = NTOK / 4;                 // columns per warp
+        constexpr int CH = CPW < 32 ? CPW : 32;       // columns per chunk
+        constexpr int NCH = CPW / CH;
+        const int cq = dq >> 2;                       // column quarter
+        float rs_lane[NCH];
+#pragma unroll
+        for (int h = 0; h < NCH; ++h) rs_lane[h] = 0.f;
         if (ok) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            const int tl = tok0 + (dq >> 2) * (NTOK / 4) + lane;
-            if (lane < NTOK / 4 && tl < p.M) rs_lane = __ldg(p.rowscale + tl);
+#pragma unroll
+            for (int h = 0; h < NCH; ++h) {
+                const int tl = tok0 + cq * CPW + h * CH + lane;
+                if (lane < CH && tl < p.M) rs_lane[h] = __ldg(p.rowscale + tl);
+            }
         }
         if (ok) {
             const bool got = mbar_block(acc_full, 0, abort_flag);
@@ -969,74 +988,74 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
         }
         if (dbg && tid == 64) dbg[302] = (unsigned long long)clock64();
         if (ok) {
-            asm volatile("griddepcontrol.wait;" ::: "memory");  // y may still be read by the grid before us
             tc_fence_after();
             const int sp = warp & 3;          // tensor-memory lanes 32*sp .. 32*sp + 31
-            const int cq = dq >> 2;           // column quarter
             const int64_t f = (int64_t)ft * 128 + sp * 32 + lane;
-            constexpr int CPW = NTOK / 4;     // columns per warp
-            // all loads of this warp's columns first, one wait, then the stores with the output
-            // type decided once (a lane owns one feature: consecutive lanes write consecutive
-            // elements of a token's row)
-            uint32_t v[CPW];
-            const uint32_t t0 = tmem + ((uint32_t)(sp * 32) << 16) + (uint32_t)(cq * CPW);
-#pragma unroll
-            for (int c0 = 0; c0 < CPW; c0 += 8) tmem_ld8(t0 + c0, *reinterpret_cast<uint32_t(*)[8]>(&v[c0]));
-            tmem_ld_wait();
-            if (ksteps >= 2) {  // the odd K-steps went into the second accumulator
-                uint32_t v2[CPW];
-#pragma unroll
-                for (int c0 = 0; c0 < CPW; c0 += 8) tmem_ld8(t0 + NTOK + c0, *reinterpret_cast<uint32_t(*)[8]>(&v2[c0]));
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < CPW; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
-            }
             const float wdiv = p.wdiv;
-            const int tokb = tok0 + cq * CPW;
-            if (p.ksplit == 1 && (p.out & 7) == 0) {
-                // Fast path: transpose the warp's 32-feature x CPW-token tile through shared memory
-                // (the B ring is idle: every MMA has completed) so that a lane stores eight
-                // consecutive features of one token with one 16-byte (bf16) or two (f32) stores,
-                // instead of one element per store.
-                constexpr int LD = 36;  // floats per token row of the staging tile (16-byte aligned rows)
-                float* tile = reinterpret_cast<float*>(smem) + dq * (CPW * LD);
+            constexpr int LD = 36;  // floats per token row of the staging tile (16-byte aligned rows)
+            float* tile = reinterpret_cast<float*>(smem) + dq * (CH * LD);
 #pragma unroll
-                for (int j = 0; j < CPW; ++j) tile[j * LD + lane] = __uint_as_float(v[j]);
-                __syncwarp();
-                const int fg = (lane & 3) * 8;
-                const int64_t f0 = (int64_t)ft * 128 + sp * 32 + fg;
+            for (int h = 0; h < NCH; ++h) {
+                // all loads of the chunk first, one wait, then the stores with the output type decided
+                // once (a lane owns one feature: consecutive lanes write consecutive elements of a row)
+                uint32_t v[CH];
+                const uint32_t t0 = tmem + ((uint32_t)(sp * 32) << 16) + (uint32_t)(cq * CPW + h * CH);
 #pragma unroll
-                for (int t0 = 0; t0 < CPW; t0 += 8) {
-                    const int t = t0 + (lane >> 2), tok = tokb + t;
-                    const float sc = wdiv * __shfl_sync(0xffffffffu, rs_lane, t);
-                    if (tok < p.M && f0 < p.out) {
-                        const float4 a = *reinterpret_cast<const float4*>(tile + t * LD + fg);
-                        const float4 c = *reinterpret_cast<const float4*>(tile + t * LD + fg + 4);
-                        if (p.out_dtype == RSTQ_BF16) {
-                            uint4 o;
-                            o.x = pack_bf16x2(a.y * sc, a.x * sc);
-                            o.y = pack_bf16x2(a.w * sc, a.z * sc);
-                            o.z = pack_bf16x2(c.y * sc, c.x * sc);
-                            o.w = pack_bf16x2(c.w * sc, c.z * sc);
-                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)tok * p.out + f0) = o;
-                        } else {
-                            float* y = reinterpret_cast<float*>(p.y) + (int64_t)tok * p.out + f0;
-                            *reinterpret_cast<float4*>(y) = make_float4(a.x * sc, a.y * sc, a.z * sc, a.w * sc);
-                            *reinterpret_cast<float4*>(y + 4) = make_float4(c.x * sc, c.y * sc, c.z * sc, c.w * sc);
+                for (int c0 = 0; c0 < CH; c0 += 8) tmem_ld8(t0 + c0, *reinterpret_cast<uint32_t(*)[8]>(&v[c0]));
+                tmem_ld_wait();
+                if (ISS == 2 && ksteps >= 2) {  // the odd K-steps went into the second accumulator
+                    uint32_t v2[CH];
+#pragma unroll
+                    for (int c0 = 0; c0 < CH; c0 += 8) tmem_ld8(t0 + NTOK + c0, *reinterpret_cast<uint32_t(*)[8]>(&v2[c0]));
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+                }
+                const int tokb = tok0 + cq * CPW + h * CH;
+                if (p.ksplit == 1 && (p.out & 7) == 0) {
+                    // Fast path: transpose the warp's 32-feature x CH-token tile through shared memory
+                    // (the B ring is idle: every MMA has completed) so that a lane stores eight
+                    // consecutive features of one token with one 16-byte (bf16) or two (f32) stores,
+                    // instead of one element per store.
+                    if (h) __syncwarp();   // the tile of the previous chunk has been read
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) tile[j * LD + lane] = __uint_as_float(v[j]);
+                    __syncwarp();
+                    const int fg = (lane & 3) * 8;
+                    const int64_t f0 = (int64_t)ft * 128 + sp * 32 + fg;
+#pragma unroll
+                    for (int t0c = 0; t0c < CH; t0c += 8) {
+                        const int t = t0c + (lane >> 2), tok = tokb + t;
+                        const float sc = wdiv * __shfl_sync(0xffffffffu, rs_lane[h], t);
+                        if (tok < p.M && f0 < p.out) {
+                            const float4 a = *reinterpret_cast<const float4*>(tile + t * LD + fg);
+                            const float4 c = *reinterpret_cast<const float4*>(tile + t * LD + fg + 4);
+                            if (p.out_dtype == RSTQ_BF16) {
+                                uint4 o;
+                                o.x = pack_bf16x2(a.y * sc, a.x * sc);
+                                o.y = pack_bf16x2(a.w * sc, a.z * sc);
+                                o.z = pack_bf16x2(c.y * sc, c.x * sc);
+                                o.w = pack_bf16x2(c.w * sc, c.z * sc);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)tok * p.out + f0) = o;
+                            } else {
+                                float* y = reinterpret_cast<float*>(p.y) + (int64_t)tok * p.out + f0;
+                                *reinterpret_cast<float4*>(y) = make_float4(a.x * sc, a.y * sc, a.z * sc, a.w * sc);
+                                *reinterpret_cast<float4*>(y + 4) = make_float4(c.x * sc, c.y * sc, c.z * sc, c.w * sc);
+                            }
                         }
                     }
-                }
-            } else {
-                // one element per store (a lane owns one feature); with two K ranges the halves
-                // are added into a zeroed f32 array: a + b in either order
-                const bool f_ok = f < p.out;
+                } else {
+                    // one element per store (a lane owns one feature); with two K ranges the halves
+                    // are added into a zeroed f32 array: a + b in either order
+                    const bool f_ok = f < p.out;
 #pragma unroll
-                for (int j = 0; j < CPW; ++j) {
-                    const float val = __uint_as_float(v[j]) * wdiv * __shfl_sync(0xffffffffu, rs_lane, j);
-                    if (f_ok && tokb + j < p.M) {
-                        const int64_t at = (int64_t)(tokb + j) * p.out + f;
-                        if (p.ksplit > 1) atomicAdd(p.acc32 + at, val);
-                        else store_out(p.y, p.out_dtype, at, val);
+                    for (int j = 0; j < CH; ++j) {
+                        const float val = __uint_as_float(v[j]) * wdiv * __shfl_sync(0xffffffffu, rs_lane[h], j);
+                        if (f_ok && tokb + j < p.M) {
+                            const int64_t at = (int64_t)(tokb + j) * p.out + f;
+                            if (p.ksplit > 1) atomicAdd(p.acc32 + at, val);
+                            else store_out(p.y, p.out_dtype, at, val);
+                        }
                     }
                 }
             }
@@ -1069,8 +1088,9 @@ static EncodeTiledFn encode_tiled_fn() {
 
 template <int BITS, int NTOK>
 static int32_t gemm_attr() {
-    RSTQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BITS, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kNST * (kAStage + NTOK * kKStep * 2) + 1024));
+    if constexpr (NTOK <= 128)
+        RSTQ_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BITS, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kNST * (kAStage + NTOK * kKStep * 2) + 1024));
     RSTQ_CUDA(cudaFuncSetAttribute(gemm_tmem_kernel<BITS, NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    gemm_stages(NTOK) * (NTOK * kKStep * 2) + 1024));
     return RSTQ_OK;
@@ -1085,6 +1105,8 @@ int32_t gemm_configure(DeviceState& ds) {
     if ((rc = gemm_attr<8, 32>()) != RSTQ_OK) return rc;
     if ((rc = gemm_attr<8, 64>()) != RSTQ_OK) return rc;
     if ((rc = gemm_attr<8, 128>()) != RSTQ_OK) return rc;
+    if ((rc = gemm_attr<4, 256>()) != RSTQ_OK) return rc;
+    if ((rc = gemm_attr<8, 256>()) != RSTQ_OK) return rc;
     return RSTQ_OK;
 }
 
@@ -1142,7 +1164,18 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     // one type (fp16 weights against bf16 activations raise "illegal instruction"), and fp16 on
     // both sides keeps three more mantissa bits of the weights than bf16 would.
     const bool a_in_tmem = ctx->tune_gemm_kernel != 1;
-    const int ntok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    // Token-tile width.  Above 128 tokens a tile may be 256 wide (gemm_tmem_kernel only): the K loop is
+    // bound by the issue of the tensor-core instructions, and an instruction of twice the width does
+    // twice the work -- a K-step of a 256-wide tile takes 1140 cycles against 690 of a 128-wide one
+    // (measured) -- but halves the number of tiles.  Whichever needs fewer cycles over the waves
+    // of CTAs the grid makes on this device is taken (M = 512 on 4096 features: 128 wide, one wave of
+    // 128 tiles; M = 768: 256 wide, one wave of 96 instead of two of 192).
+    int ntok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    if (M > 128 && a_in_tmem && ctx->tune_gemm_wide != 1) {
+        const int64_t ft = (w->out + 127) / 128, sm = ds.sm_count > 0 ? ds.sm_count : 1;
+        const int64_t waves128 = (ft * ((M + 127) / 128) + sm - 1) / sm, waves256 = (ft * ((M + 255) / 256) + sm - 1) / sm;
+        if (ctx->tune_gemm_wide == 2 || waves256 * 1140 < waves128 * 690) ntok = 256;
+    }
     int32_t rc = launch_act_to_f16(ctx, ds, x, xs, src, x16, rowscale, M, w->in);
     if (rc != RSTQ_OK) return rc;
     cudaError_t le;
@@ -1197,11 +1230,13 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     if (w->bits == 4) {
         if (ntok == 32) GL(4, 32);
         else if (ntok == 64) GL(4, 64);
-        else GL(4, 128);
+        else if (ntok == 128) GL(4, 128);
+        else le = launch_pdl(gemm_tmem_kernel<4, 256>, grid, dim3(kGemmThreadsT), smem, ds, p, tmap);
     } else {
         if (ntok == 32) GL(8, 32);
         else if (ntok == 64) GL(8, 64);
-        else GL(8, 128);
+        else if (ntok == 128) GL(8, 128);
+        else le = launch_pdl(gemm_tmem_kernel<8, 256>, grid, dim3(kGemmThreadsT), smem, ds, p, tmap);
     }
 #undef GL
     ctx->launches++;

@@ -116,6 +116,7 @@ struct rstq_ctx {
     int64_t tune_gemm_min_m = 17;
     bool tune_q4k_units = true;     // Q4_K weights bound from now on keep their minima inside the units
     bool tune_q6k_units = true;     // Q6_K weights bound from now on are 1280-byte units (a scale per 16 elements), not twin rows
+    int64_t tune_gemm_wide = 0;        // 256-token tiles of the prefill GEMM above 128 tokens: 0 = where they need fewer cycles, 1 = never, 2 = always
     int64_t tune_gemm_kernel = 0;   // 0 = weights in tensor memory, 1 = weights through shared memory
     int64_t launches = 0;
     struct CacheKey {

@@ -152,3 +152,46 @@ def test_gemm_shared_memory_variant_still_agrees(ctx):
     y0 = ctx.qmatmul_host(bw, x, M, L.F32, L.MODE_F)
     assert relerr(y1, ref) <= 1e-3 and relerr(y0, ref) <= 1e-3
     bw.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M,out,in_", [(1024, 512, 1024), (1100, 384, 2048), (300, 256, 1024)])
+def test_wide_token_tiles_match_the_narrow_ones(ctx, bits, M, out, in_):
+    """Above 128 tokens the prefill GEMM may use 256-token tiles (RSTQ_TUNE_GEMM_WIDE: 2 = always, 1 = never):
+    one accumulator, one issuing thread, three stages.  Same products, same f32 sums in another order: equal
+    to the 128-token tiles within 1e-5 of max|y|, and to the f64 reference within 1e-3."""
+    fmt = L.FMT_Q4_0 if bits == 4 else L.FMT_Q8_0
+    rng = np.random.default_rng(bits * 1000 + M)
+    codes = rng.integers(0, 256, out * in_ * bits // 8, dtype=np.uint8)
+    scales = (rng.standard_normal(out * (in_ // 32)) * 0.01).astype(np.float32)
+    w = ctx.bind_weight(codes, scales, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    x = synth.from_bf16_bits(synth.to_bf16_bits(synth.normal(M + out, M * in_)))
+    bx, by = ctx.array_to_buffer(synth.to_bf16_bits(x)), ctx.make_buffer(M * out, np.float32)
+    ys = {}
+    try:
+        for wide in (2, 1):
+            ctx.tune(L.TUNE_GEMM_WIDE, wide)
+            by.fill_bytes(0xFF)
+            ctx.qmatmul(w, bx, by, M, L.BF16, L.F32, L.MODE_F)
+            ctx.sync()
+            ys[wide] = by.download().astype(np.float64)
+    finally:
+        ctx.tune(L.TUNE_GEMM_WIDE, 0)
+    scale = np.abs(ys[1]).max()
+    assert np.abs(ys[2] - ys[1]).max() <= 1e-5 * scale
+    # against the dequantized weights in f64 on sampled rows
+    zp = 8 if bits == 4 else 128
+    rows = rng.choice(out, 16, replace=False)
+    nb = in_ // 32
+    for r in rows:
+        if bits == 4:
+            b = codes[r * in_ // 2:(r + 1) * in_ // 2].reshape(nb, 16)
+            q = np.concatenate([b & 15, b >> 4], axis=1).astype(np.float64)
+        else:
+            q = codes[r * in_:(r + 1) * in_].reshape(nb, 32).astype(np.float64)
+        wrow = ((q - zp) * scales[r * nb:(r + 1) * nb, None].astype(np.float64)).ravel()
+        ref = x.reshape(M, in_).astype(np.float64) @ wrow
+        assert np.abs(ys[2].reshape(M, out)[:, r] - ref).max() <= 1e-3 * max(np.abs(ref).max(), 1e-30)
+    for o in (w, bx, by):
+        o.free()
