@@ -117,7 +117,8 @@ typedef struct rstq_event rstq_event;
                                      row (twice the code bytes) and a third kernel that adds the pairs */
 #define RSTQ_TUNE_GEMM_WIDE 13    /* prefill GEMM above 128 tokens, 256-token tiles (one accumulator, one issuing
                                      thread) instead of 128-token ones: 0 (default) = where the grid then needs
-                                     fewer cycles over its waves of thread blocks, 1 = never, 2 = always */
+                                     fewer cycles over its waves of thread blocks, 1 = never, 2 = always,
+                                     3 = as 0 but never two thread blocks per tile (each half of K) */
 #define RSTQ_TUNE_ACT_IMAGE 10    /* 1 (default) = rstq_qmatmul in MODE_A8 at 2 <= M <= 16: the activation quantizer
                                      also writes the codes, scales and sums in the order the decode kernel
                                      keeps them in shared memory, and that kernel's copy thread brings them

@@ -187,7 +187,8 @@ static int32_t run_q4k(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const fl
 static int32_t gemm_scratch(DeviceState& ds, int64_t M, int64_t in, int64_t out, void** x16, float** rowscale,
                             float** acc) {
     const int64_t xb = (M * in * 2 + 255) & ~255ll, rb = (M * 4 + 255) & ~255ll;
-    const int64_t ab = M <= 256 ? M * out * 4 : 0;
+    // the partial tiles of a GEMM split along K (launch_gemm; gemm_tc_kernel's f32 array for M <= 256 fits too)
+    const int64_t ab = M <= 256 && M * out * 4 > kPairScratchBytes ? M * out * 4 : kPairScratchBytes;
     int32_t rc = dev_reserve(ds, &ds.gemm_scratch, &ds.gemm_scratch_bytes, xb + rb + ab);
     if (rc != RSTQ_OK) return rc;
     *x16 = ds.gemm_scratch;
@@ -582,7 +583,7 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
             ctx->tune_q6k_units = value != 0;
             return RSTQ_OK;
         case RSTQ_TUNE_GEMM_WIDE:
-            RSTQ_REQUIRE(value >= 0 && value <= 2, RSTQ_E_INVALID, "256-token tile selector 0..2");
+            RSTQ_REQUIRE(value >= 0 && value <= 3, RSTQ_E_INVALID, "256-token tile selector 0..3");
             ctx->tune_gemm_wide = value;
             return RSTQ_OK;
         case RSTQ_TUNE_ACT_IMAGE:

@@ -221,7 +221,10 @@ struct GemmParams {
     int M, ksteps, ttiles;
     int tiles, ksplit;      // feature x token tiles; K is cut into ksplit ranges of ksteps steps (last may be shorter)
     int ksteps_total;
-    float* acc32;           // ksplit > 1: partial results are added into this zeroed [M, out] f32 array
+    float* acc32;           // ksplit > 1 (gemm_tc_kernel): partial results are added into this zeroed [M, out] f32 array
+    float* part;            // ksplit > 1 (gemm_tmem_kernel): the K range 1 CTA of a tile leaves its f32 accumulator
+                            // here ([tile][warp][column][lane]), the K range 0 CTA adds it to its own and stores y
+    int* pair_flags;        // one word per tile, zero between launches: set when `part` of the tile is complete
     float wmul, wdiv;       // 2^ew applied to the block scales, 2^-ew applied to the result
     int out_dtype;
     unsigned long long* dbg;  // optional timeline of CTA 0 (see RSTQ_TUNE_TIMELINE), or null
@@ -987,13 +990,36 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
             ok = __all_sync(0xffffffffu, got);
         }
         if (dbg && tid == 64) dbg[302] = (unsigned long long)clock64();
+        // Two CTAs on one tile (each half of K): the K range 1 CTA hands its accumulator over through
+        // L2, the K range 0 CTA adds it to its own (always a + b in this order) and writes y.
+        const bool pair = p.ksplit > 1 && p.part != nullptr;
+        const bool giver = pair && kz == 1, taker = pair && kz == 0;
+        float* part = pair ? p.part + ((size_t)tile * kDqWarps + dq) * (CPW * 32) : nullptr;
+        if (ok && taker) {
+            int got = 1;
+            if (lane == 0) {
+                const unsigned long long t0 = gtime_ns();
+                for (;;) {
+                    int v;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.pair_flags + tile) : "memory");
+                    if (v != 0) break;
+                    if (*abort_flag || gtime_ns() - t0 > kWaitLimitNs) {
+                        *abort_flag = 1;
+                        got = 0;
+                        break;
+                    }
+                    __nanosleep(64);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, got, 0) != 0;
+        }
         if (ok) {
             tc_fence_after();
             const int sp = warp & 3;          // tensor-memory lanes 32*sp .. 32*sp + 31
             const int64_t f = (int64_t)ft * 128 + sp * 32 + lane;
             const float wdiv = p.wdiv;
             constexpr int LD = 36;  // floats per token row of the staging tile (16-byte aligned rows)
-            float* tile = reinterpret_cast<float*>(smem) + dq * (CH * LD);
+            float* tile_s = reinterpret_cast<float*>(smem) + dq * (CH * LD);
 #pragma unroll
             for (int h = 0; h < NCH; ++h) {
                 // all loads of the chunk first, one wait, then the stores with the output type decided
@@ -1012,14 +1038,24 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                     for (int j = 0; j < CH; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
                 }
                 const int tokb = tok0 + cq * CPW + h * CH;
-                if (p.ksplit == 1 && (p.out & 7) == 0) {
+                if (giver) {   // raw sums, 128 bytes per column and warp
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) part[(h * CH + j) * 32 + lane] = __uint_as_float(v[j]);
+                    continue;
+                }
+                if (taker) {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j)
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(part + (h * CH + j) * 32 + lane));
+                }
+                if ((p.ksplit == 1 || pair) && (p.out & 7) == 0) {
                     // Fast path: transpose the warp's 32-feature x CH-token tile through shared memory
                     // (the B ring is idle: every MMA has completed) so that a lane stores eight
                     // consecutive features of one token with one 16-byte (bf16) or two (f32) stores,
                     // instead of one element per store.
                     if (h) __syncwarp();   // the tile of the previous chunk has been read
 #pragma unroll
-                    for (int j = 0; j < CH; ++j) tile[j * LD + lane] = __uint_as_float(v[j]);
+                    for (int j = 0; j < CH; ++j) tile_s[j * LD + lane] = __uint_as_float(v[j]);
                     __syncwarp();
                     const int fg = (lane & 3) * 8;
                     const int64_t f0 = (int64_t)ft * 128 + sp * 32 + fg;
@@ -1028,8 +1064,8 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                         const int t = t0c + (lane >> 2), tok = tokb + t;
                         const float sc = wdiv * __shfl_sync(0xffffffffu, rs_lane[h], t);
                         if (tok < p.M && f0 < p.out) {
-                            const float4 a = *reinterpret_cast<const float4*>(tile + t * LD + fg);
-                            const float4 c = *reinterpret_cast<const float4*>(tile + t * LD + fg + 4);
+                            const float4 a = *reinterpret_cast<const float4*>(tile_s + t * LD + fg);
+                            const float4 c = *reinterpret_cast<const float4*>(tile_s + t * LD + fg + 4);
                             if (p.out_dtype == RSTQ_BF16) {
                                 uint4 o;
                                 o.x = pack_bf16x2(a.y * sc, a.x * sc);
@@ -1053,11 +1089,22 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                         const float val = __uint_as_float(v[j]) * wdiv * __shfl_sync(0xffffffffu, rs_lane[h], j);
                         if (f_ok && tokb + j < p.M) {
                             const int64_t at = (int64_t)(tokb + j) * p.out + f;
-                            if (p.ksplit > 1) atomicAdd(p.acc32 + at, val);
+                            if (p.ksplit > 1 && !pair) atomicAdd(p.acc32 + at, val);
                             else store_out(p.y, p.out_dtype, at, val);
                         }
                     }
                 }
+            }
+        }
+        if (pair) {
+            // giver: every warp's part is out before the flag goes up; taker: every warp has read its
+            // part before the flag goes down again (the next launch's giver writes only after this
+            // grid has completed).  All sixteen warps meet here whether or not a wait ran out.
+            if (giver && ok) __threadfence();
+            asm volatile("bar.sync 6, %0;" ::"r"(kDqWarps * 32) : "memory");
+            if (dq == 0 && lane == 0) {
+                if (taker) p.pair_flags[tile] = 0;
+                else if (ok) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.pair_flags + tile), "r"(1) : "memory");
             }
         }
     }
@@ -1160,22 +1207,43 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
                  "activation scratch must be 16-byte aligned");
     EncodeTiledFn enc = encode_tiled_fn();
     RSTQ_REQUIRE(enc, RSTQ_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const bool a_in_tmem = ctx->tune_gemm_kernel != 1;
+    // Token-tile width and the split along K.  Above 128 tokens a tile may be 256 wide (gemm_tmem_kernel
+    // only): the K loop is bound by the issue of the tensor-core instructions, and an instruction of
+    // twice the width does twice the work -- a K-step of a 256-wide tile takes 1140 cycles against
+    // 690 of a 128-wide one (measured) -- but halves the number of tiles.  When a grid would fill at
+    // most half the SMs and K is long, two CTAs share a tile, each taking half of K; the second hands
+    // its accumulator to the first through L2 (about 1500 cycles).  Whichever combination needs the
+    // fewest cycles over the waves of CTAs it makes on this device is taken (4096 features: M <= 256: 128
+    // wide, split; M = 512: 128 wide, one wave of 128 tiles; M = 768: 256 wide, one wave of 96 tiles
+    // instead of two of 192; M >= 1024: 256 wide).
+    const int64_t ftiles = (w->out + 127) / 128, sm = ds.sm_count > 0 ? ds.sm_count : 1;
+    const int64_t ksteps_total = (w->nb + 3) / 4;
+    // (measured: a 128-wide K-step 690 cycles; a 256-wide one 1140 with 64 CTAs running, 1240 with 96,
+    // 1400 with all 148 -- their activation tiles are twice as large and all come from L2; set-up, first
+    // loads and epilogue of a CTA about 8000 resp. 9000 cycles)
+    auto cycles = [&](int nt, bool* split) {
+        const int64_t tiles = ftiles * ((M + nt - 1) / nt);
+        *split = a_in_tmem && acc32 && tiles * 2 <= sm && tiles <= kPairTiles && ksteps_total >= 16 && ctx->tune_gemm_wide != 3;
+        const int64_t ctas = *split ? tiles * 2 : tiles, active = ctas < sm ? ctas : sm;
+        const int64_t c = nt == 256 ? 1140 + (active > 64 ? (active - 64) * 31 / 10 : 0) : 690;
+        const int64_t fixed = nt == 256 ? 9000 : 8000;
+        return *split ? (ksteps_total + 1) / 2 * c + 1500 + fixed : (tiles + sm - 1) / sm * (ksteps_total * c + fixed);
+    };
+    int ntok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    bool split = false;
+    const int64_t c_narrow = cycles(ntok, &split);
+    if (M > 128 && a_in_tmem && ctx->tune_gemm_wide != 1) {
+        bool split_w = false;
+        const int64_t c_wide = cycles(256, &split_w);
+        if (ctx->tune_gemm_wide == 2 || c_wide < c_narrow) {
+            ntok = 256;
+            split = split_w;
+        }
+    }
     // pre-pass: activations -> fp16 with one exponent per token row.  kind::f16 wants A and B of
     // one type (fp16 weights against bf16 activations raise "illegal instruction"), and fp16 on
     // both sides keeps three more mantissa bits of the weights than bf16 would.
-    const bool a_in_tmem = ctx->tune_gemm_kernel != 1;
-    // Token-tile width.  Above 128 tokens a tile may be 256 wide (gemm_tmem_kernel only): the K loop is
-    // bound by the issue of the tensor-core instructions, and an instruction of twice the width does
-    // twice the work -- a K-step of a 256-wide tile takes 1140 cycles against 690 of a 128-wide one
-    // (measured) -- but halves the number of tiles.  Whichever needs fewer cycles over the waves
-    // of CTAs the grid makes on this device is taken (M = 512 on 4096 features: 128 wide, one wave of
-    // 128 tiles; M = 768: 256 wide, one wave of 96 instead of two of 192).
-    int ntok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
-    if (M > 128 && a_in_tmem && ctx->tune_gemm_wide != 1) {
-        const int64_t ft = (w->out + 127) / 128, sm = ds.sm_count > 0 ? ds.sm_count : 1;
-        const int64_t waves128 = (ft * ((M + 127) / 128) + sm - 1) / sm, waves256 = (ft * ((M + 255) / 256) + sm - 1) / sm;
-        if (ctx->tune_gemm_wide == 2 || waves256 * 1140 < waves128 * 690) ntok = 256;
-    }
     int32_t rc = launch_act_to_f16(ctx, ds, x, xs, src, x16, rowscale, M, w->in);
     if (rc != RSTQ_OK) return rc;
     cudaError_t le;
@@ -1207,20 +1275,13 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     p.wdiv = ldexpf(1.0f, -w->gemm_exp + (a_in_tmem ? 24 - kSubnormalShift : 0));
     p.out_dtype = out_dtype;
     p.dbg = ds.dbg;
-    const int64_t ftiles = (w->out + 127) / 128;
     RSTQ_REQUIRE(ftiles * p.ttiles < (1ll << 30), RSTQ_E_LIMIT, "grid too large");
     p.tiles = (int)(ftiles * p.ttiles);
-    // Few output tiles and a long K (small M, short matrices): two CTAs share a tile, each takes half
-    // of K, so twice as many SMs stream weights.  The halves meet in a zeroed f32 array (a + b is the
-    // same in either order, so the result stays reproducible); a bf16 result is converted afterwards.
-    const bool a_tmem = ctx->tune_gemm_kernel != 1;
-    p.ksplit = (a_tmem && acc32 && p.tiles * 2 <= ds.sm_count && p.ksteps_total >= 16) ? 2 : 1;
+    p.ksplit = split ? 2 : 1;
     p.ksteps = (p.ksteps_total + p.ksplit - 1) / p.ksplit;
     p.acc32 = nullptr;
-    if (p.ksplit > 1) {
-        p.acc32 = out_dtype == RSTQ_F32 ? (float*)y : acc32;
-        RSTQ_CUDA(cudaMemsetAsync(p.acc32, 0, (size_t)M * w->out * 4, ds.stream));
-    }
+    p.part = split ? acc32 : nullptr;   // [tile][16 warps][columns per warp][32 lanes] f32: tiles * 128 * ntok floats
+    p.pair_flags = ds.counters + ds.counters_len - kPairTiles;
     const dim3 grid((unsigned)(p.tiles * p.ksplit));
     const size_t smem = a_in_tmem ? gemm_stages(ntok) * ((size_t)ntok * kKStep * 2) + 1024
                                   : kNST * (kAStage + (size_t)ntok * kKStep * 2) + 1024;
@@ -1242,14 +1303,6 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     ctx->launches++;
     RSTQ_CUDA(le);
     RSTQ_CUDA(cudaGetLastError());
-    if (p.ksplit > 1 && out_dtype != RSTQ_F32) {
-        const int64_t n = M * w->out;
-        int64_t ctas = (n + 255) / 256;
-        if (ctas > (int64_t)ds.sm_count * 8) ctas = (int64_t)ds.sm_count * 8;
-        RSTQ_CUDA(launch_pdl(gemm_finish_kernel, dim3((unsigned)ctas), dim3(256), 0, ds, (const float*)p.acc32, y,
-                             out_dtype, n));
-        ctx->launches++;
-    }
     return RSTQ_OK;
 }
 

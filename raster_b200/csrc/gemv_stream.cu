@@ -1419,7 +1419,7 @@ int32_t gemv_configure(DeviceState& ds) {
 
 static int32_t stream_scratch_ok(const DeviceState& ds, int64_t groups, int G, int64_t M) {
     (void)groups;
-    RSTQ_REQUIRE(G <= ds.counters_len, RSTQ_E_LIMIT, "%d thread blocks exceed the %lld hand-over flags", G,
+    RSTQ_REQUIRE(G <= ds.counters_len - kPairTiles, RSTQ_E_LIMIT, "%d thread blocks exceed the %lld hand-over flags", G,
                  (long long)ds.counters_len);
     RSTQ_REQUIRE((int64_t)G * M * 32 * 4 <= ds.partials_bytes, RSTQ_E_LIMIT, "partials scratch too small");
     return RSTQ_OK;

@@ -52,6 +52,10 @@ int32_t cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 // One 16-byte load per lane thus feeds two 16-row tensor-core tiles with no
 // data movement between lanes.
 constexpr int kUnitBytesQ4 = 640;
+// prefill GEMM, two CTAs per tile: at most this many tiles (their flags are the last words of
+// DeviceState::counters, their partial tiles of up to 128 x 256 floats live in the GEMM scratch)
+constexpr int kPairTiles = 128;
+constexpr int64_t kPairScratchBytes = (int64_t)kPairTiles * 128 * 256 * 4;
 constexpr int kUnitBytesQ6K = 1280;  // 1024 bytes of 8-bit codes as in the 8-bit unit, then 64 scales (one per row and 16 elements)
 constexpr int kUnitBytesQ4K = 768;  // a 4-bit unit with the 32 Q4_K minima (db * bq, added as they are) behind the 32 scales
 constexpr int kUnitBytesQ8 = 1152;
@@ -116,7 +120,7 @@ struct rstq_ctx {
     int64_t tune_gemm_min_m = 17;
     bool tune_q4k_units = true;     // Q4_K weights bound from now on keep their minima inside the units
     bool tune_q6k_units = true;     // Q6_K weights bound from now on are 1280-byte units (a scale per 16 elements), not twin rows
-    int64_t tune_gemm_wide = 0;        // 256-token tiles of the prefill GEMM above 128 tokens: 0 = where they need fewer cycles, 1 = never, 2 = always
+    int64_t tune_gemm_wide = 0;        // 256-token tiles of the prefill GEMM above 128 tokens: 0 = where they need fewer cycles, 1 = never, 2 = always, 3 = as 0 but no split along K
     int64_t tune_gemm_kernel = 0;   // 0 = weights in tensor memory, 1 = weights through shared memory
     int64_t launches = 0;
     struct CacheKey {
