@@ -221,7 +221,6 @@ struct GemmParams {
     int M, ksteps, ttiles;
     int tiles, ksplit;      // feature x token tiles; K is cut into ksplit ranges of ksteps steps (last may be shorter)
     int ksteps_total;
-    float* acc32;           // ksplit > 1 (gemm_tc_kernel): partial results are added into this zeroed [M, out] f32 array
     float* part;            // ksplit > 1 (gemm_tmem_kernel): the K range 1 CTA of a tile leaves its f32 accumulator
                             // here ([tile][warp][column][lane]), the K range 0 CTA adds it to its own and stores y
     int* pair_flags;        // one word per tile, zero between launches: set when `part` of the tile is complete
@@ -992,7 +991,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
         if (dbg && tid == 64) dbg[302] = (unsigned long long)clock64();
         // Two CTAs on one tile (each half of K): the K range 1 CTA hands its accumulator over through
         // L2, the K range 0 CTA adds it to its own (always a + b in this order) and writes y.
-        const bool pair = p.ksplit > 1 && p.part != nullptr;
+        const bool pair = p.ksplit > 1;
         const bool giver = pair && kz == 1, taker = pair && kz == 0;
         float* part = pair ? p.part + ((size_t)tile * kDqWarps + dq) * (CPW * 32) : nullptr;
         if (ok && taker) {
@@ -1048,7 +1047,7 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                     for (int j = 0; j < CH; ++j)
                         v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(part + (h * CH + j) * 32 + lane));
                 }
-                if ((p.ksplit == 1 || pair) && (p.out & 7) == 0) {
+                if ((p.out & 7) == 0) {
                     // Fast path: transpose the warp's 32-feature x CH-token tile through shared memory
                     // (the B ring is idle: every MMA has completed) so that a lane stores eight
                     // consecutive features of one token with one 16-byte (bf16) or two (f32) stores,
@@ -1081,16 +1080,13 @@ gemm_tmem_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap) {
                         }
                     }
                 } else {
-                    // one element per store (a lane owns one feature); with two K ranges the halves
-                    // are added into a zeroed f32 array: a + b in either order
+                    // one element per store (a lane owns one feature)
                     const bool f_ok = f < p.out;
 #pragma unroll
                     for (int j = 0; j < CH; ++j) {
                         const float val = __uint_as_float(v[j]) * wdiv * __shfl_sync(0xffffffffu, rs_lane[h], j);
                         if (f_ok && tokb + j < p.M) {
-                            const int64_t at = (int64_t)(tokb + j) * p.out + f;
-                            if (p.ksplit > 1 && !pair) atomicAdd(p.acc32 + at, val);
-                            else store_out(p.y, p.out_dtype, at, val);
+                            store_out(p.y, p.out_dtype, (int64_t)(tokb + j) * p.out + f, val);
                         }
                     }
                 }
@@ -1192,14 +1188,6 @@ static int32_t launch_act_to_f16(rstq_ctx* ctx, DeviceState& ds, const void* x, 
 // y[M, out] = x[M, in] . dequant(W)^T on the tensor cores.  src: 0 = f32 x, 1 = bf16 x,
 // 2 = int8 codes x with per-block scales xs.  x16 / rowscale are caller-provided scratch
 // (M*in fp16, M floats).
-// f32 -> output type after a split-K accumulation
-__global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restrict__ acc, void* __restrict__ y,
-                                                          int out_dtype, int64_t n) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) store_out(y, out_dtype, i, acc[i]);
-}
-
 int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const void* x, const float* xs,
                     int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale, float* acc32) {
     RSTQ_REQUIRE(M >= 1 && M < (1ll << 30), RSTQ_E_SHAPE, "M = %lld", (long long)M);
@@ -1279,7 +1267,6 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     p.tiles = (int)(ftiles * p.ttiles);
     p.ksplit = split ? 2 : 1;
     p.ksteps = (p.ksteps_total + p.ksplit - 1) / p.ksplit;
-    p.acc32 = nullptr;
     p.part = split ? acc32 : nullptr;   // [tile][16 warps][columns per warp][32 lanes] f32: tiles * 128 * ntok floats
     p.pair_flags = ds.counters + ds.counters_len - kPairTiles;
     const dim3 grid((unsigned)(p.tiles * p.ksplit));
