@@ -138,6 +138,11 @@ RSTQ_API int32_t rstq_device_count(int32_t* count);
  * that list (device index 0 = devices[0]). ------------------------------- */
 RSTQ_API int32_t rstq_init(const int32_t* devices, rstq_ctx** ctx, int32_t ndev);
 RSTQ_API int32_t rstq_shutdown(rstq_ctx* ctx);
+/* How the prefill GEMM (M above the decode kernel's range) would tile a call on a device of sm_count SMs
+ * at the default settings: plan2[0] = tokens per tile (32, 64, 128 or 256), plan2[1] = thread blocks per
+ * tile (2 = each takes half of K; the second hands its sums to the first).  Pure host arithmetic: no
+ * device, no context.  No counterpart in the reference (its GEMM is one work-item per output). */
+RSTQ_API int32_t rstq_gemm_plan(int32_t* plan2, int64_t out, int64_t in, int64_t m, int32_t sm_count);
 RSTQ_API int32_t rstq_sync(rstq_ctx* ctx, int32_t dev);
 RSTQ_API int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value);
 /* out[0] = SM count, out[1] = L2 bytes, out[2] = total device memory, out[3] = cc major*10+minor */

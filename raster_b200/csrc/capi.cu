@@ -513,6 +513,18 @@ int32_t rstq_shutdown(rstq_ctx* ctx) {
     return RSTQ_OK;
 }
 
+int32_t rstq_gemm_plan(int32_t* plan2, int64_t out, int64_t in, int64_t m, int32_t sm_count) {
+    RSTQ_REQUIRE(plan2, RSTQ_E_INVALID, "null argument");
+    RSTQ_REQUIRE(out >= 1 && in >= 32 && in % 32 == 0 && m >= 1 && sm_count >= 1, RSTQ_E_SHAPE,
+                 "out = %lld, in = %lld, m = %lld, sm_count = %d", (long long)out, (long long)in, (long long)m, sm_count);
+    int ntok = 0;
+    bool split = false;
+    gemm_plan(out, in, m, sm_count, true, 0, &ntok, &split);
+    plan2[0] = ntok;
+    plan2[1] = split ? 2 : 1;
+    return RSTQ_OK;
+}
+
 int32_t rstq_sync(rstq_ctx* ctx, int32_t dev) {
     CHECK_CTX(ctx);
     CHECK_DEV(ctx, dev);

@@ -1185,6 +1185,40 @@ static int32_t launch_act_to_f16(rstq_ctx* ctx, DeviceState& ds, const void* x, 
     return RSTQ_OK;
 }
 
+// Token-tile width and split along K of a prefill GEMM on a device of `sm_count` SMs: whichever of
+// 128- / 256-wide tiles, one or two CTAs per tile, needs the fewest cycles over the waves of CTAs
+// the grid makes.  `tmem_kernel`: the call runs gemm_tmem_kernel with a pair scratch (wide tiles and
+// the split exist only there); `wide`: RSTQ_TUNE_GEMM_WIDE.
+// (measured: a 128-wide K-step 690 cycles; a 256-wide one 1140 with 64 CTAs running, 1240 with 96,
+// 1400 with all 148 -- their activation tiles are twice as large and all come from L2; set-up, first
+// loads and epilogue of a CTA about 8000 resp. 9000 cycles; the hand-over of a pair about 1500)
+void gemm_plan(int64_t out, int64_t in, int64_t M, int sm_count, bool tmem_kernel, int wide, int* ntok_out,
+               bool* split_out) {
+    const int64_t ftiles = (out + 127) / 128, sm = sm_count > 0 ? sm_count : 1;
+    const int64_t ksteps_total = (in / 32 + 3) / 4;
+    auto cycles = [&](int nt, bool* split) {
+        const int64_t tiles = ftiles * ((M + nt - 1) / nt);
+        *split = tmem_kernel && tiles * 2 <= sm && tiles <= kPairTiles && ksteps_total >= 16 && wide != 3;
+        const int64_t ctas = *split ? tiles * 2 : tiles, active = ctas < sm ? ctas : sm;
+        const int64_t c = nt == 256 ? 1140 + (active > 64 ? (active - 64) * 31 / 10 : 0) : 690;
+        const int64_t fixed = nt == 256 ? 9000 : 8000;
+        return *split ? (ksteps_total + 1) / 2 * c + 1500 + fixed : (tiles + sm - 1) / sm * (ksteps_total * c + fixed);
+    };
+    int ntok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    bool split = false;
+    const int64_t c_narrow = cycles(ntok, &split);
+    if (M > 128 && tmem_kernel && wide != 1) {
+        bool split_w = false;
+        const int64_t c_wide = cycles(256, &split_w);
+        if (wide == 2 || c_wide < c_narrow) {
+            ntok = 256;
+            split = split_w;
+        }
+    }
+    *ntok_out = ntok;
+    *split_out = split;
+}
+
 // y[M, out] = x[M, in] . dequant(W)^T on the tensor cores.  src: 0 = f32 x, 1 = bf16 x,
 // 2 = int8 codes x with per-block scales xs.  x16 / rowscale are caller-provided scratch
 // (M*in fp16, M floats).
@@ -1205,30 +1239,10 @@ int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const 
     // fewest cycles over the waves of CTAs it makes on this device is taken (4096 features: M <= 256: 128
     // wide, split; M = 512: 128 wide, one wave of 128 tiles; M = 768: 256 wide, one wave of 96 tiles
     // instead of two of 192; M >= 1024: 256 wide).
-    const int64_t ftiles = (w->out + 127) / 128, sm = ds.sm_count > 0 ? ds.sm_count : 1;
-    const int64_t ksteps_total = (w->nb + 3) / 4;
-    // (measured: a 128-wide K-step 690 cycles; a 256-wide one 1140 with 64 CTAs running, 1240 with 96,
-    // 1400 with all 148 -- their activation tiles are twice as large and all come from L2; set-up, first
-    // loads and epilogue of a CTA about 8000 resp. 9000 cycles)
-    auto cycles = [&](int nt, bool* split) {
-        const int64_t tiles = ftiles * ((M + nt - 1) / nt);
-        *split = a_in_tmem && acc32 && tiles * 2 <= sm && tiles <= kPairTiles && ksteps_total >= 16 && ctx->tune_gemm_wide != 3;
-        const int64_t ctas = *split ? tiles * 2 : tiles, active = ctas < sm ? ctas : sm;
-        const int64_t c = nt == 256 ? 1140 + (active > 64 ? (active - 64) * 31 / 10 : 0) : 690;
-        const int64_t fixed = nt == 256 ? 9000 : 8000;
-        return *split ? (ksteps_total + 1) / 2 * c + 1500 + fixed : (tiles + sm - 1) / sm * (ksteps_total * c + fixed);
-    };
-    int ntok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    const int64_t ftiles = (w->out + 127) / 128;
+    int ntok = 128;
     bool split = false;
-    const int64_t c_narrow = cycles(ntok, &split);
-    if (M > 128 && a_in_tmem && ctx->tune_gemm_wide != 1) {
-        bool split_w = false;
-        const int64_t c_wide = cycles(256, &split_w);
-        if (ctx->tune_gemm_wide == 2 || c_wide < c_narrow) {
-            ntok = 256;
-            split = split_w;
-        }
-    }
+    gemm_plan(w->out, w->in, M, ds.sm_count, a_in_tmem && acc32 != nullptr, (int)ctx->tune_gemm_wide, &ntok, &split);
     // pre-pass: activations -> fp16 with one exponent per token row.  kind::f16 wants A and B of
     // one type (fp16 weights against bf16 activations raise "illegal instruction"), and fp16 on
     // both sides keeps three more mantissa bits of the weights than bf16 would.

@@ -281,6 +281,9 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a);
 int gemv_f_pieces(const DeviceState& ds, int bits, int64_t out, int64_t in, int64_t M, int act_dtype);
 int32_t gemv_configure(DeviceState& ds);  // shared-memory attributes, once per device
 // gemm_tc.cu
+// gemm_tc.cu: token-tile width (32 / 64 / 128 / 256) and whether two CTAs share a tile, for a device of sm_count SMs
+void gemm_plan(int64_t out, int64_t in, int64_t M, int sm_count, bool tmem_kernel, int wide, int* ntok_out,
+               bool* split_out);
 int32_t launch_gemm(rstq_ctx* ctx, DeviceState& ds, const rstq_weight* w, const void* x, const float* xs,
                     int src, void* y, int out_dtype, int64_t M, void* x16, float* rowscale,
                     float* acc32 = nullptr);

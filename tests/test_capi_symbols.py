@@ -60,3 +60,30 @@ def test_init_without_gpu_fails_loudly():
     from raster_b200 import Context
     with pytest.raises(L.RstqError):
         Context()
+
+
+def test_gemm_plan_is_host_arithmetic_and_follows_the_wave_model():
+    """rstq_gemm_plan needs no device: tile width and thread blocks per tile of the prefill GEMM on a
+    148-SM part.  4096 features: up to 256 tokens the grid fills at most half the SMs and K = 4096 is
+    long enough, so two thread blocks share a tile; 512 tokens are one wave of 128 tiles of 128; from
+    768 on the tiles are 256 wide (one wave of 96 instead of two of 192)."""
+    import ctypes as C
+    from raster_b200 import _lib as L
+    lib = L.load()
+    plan = (C.c_int32 * 2)()
+
+    def of(out, in_, m, sm=148):
+        L.check(lib.rstq_gemm_plan(plan, out, in_, m, sm))
+        return plan[0], plan[1]
+    assert of(4096, 4096, 17) == (32, 2)
+    assert of(4096, 4096, 64) == (64, 2)
+    assert of(4096, 4096, 256) == (128, 2)
+    assert of(4096, 4096, 512) == (128, 1)
+    assert of(4096, 4096, 768) == (256, 1)
+    assert of(4096, 4096, 2048) == (256, 1)
+    assert of(28672, 8192, 256) == (256, 1)          # 224 wide tiles: two waves instead of four
+    assert of(28672, 8192, 16) == (32, 1)            # 224 tiles: more than half the SMs, no split
+    assert of(4096, 256, 64) == (64, 1)              # K too short to cut
+    assert of(4096, 4096, 512, sm=296) == (128, 2)   # a part twice as wide would split
+    assert lib.rstq_gemm_plan(plan, 4096, 100, 64, 148) == L.E_SHAPE
+    assert lib.rstq_gemm_plan(None, 4096, 4096, 64, 148) == L.E_INVALID
