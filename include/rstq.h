@@ -188,11 +188,14 @@ RSTQ_API int32_t rstq_weight_bind_shard(rstq_ctx* ctx, rstq_weight** w, const vo
  * makes (src/raster/compiler/backend/cpu/quant.clj:85-150): wq nibbles [out, in/2] (element k low,
  * k+16 high per 32-element sub-block), da / db f32 [out, in/256], aq (0..63) / bq (-32..31) int8
  * [out, in/32]; in % 256 == 0.  On the device the sub-block scales da*aq ride the 4-bit units of
- * the decode kernel and the minima db*bq are a separate f32 [out, in/32] array.  Such a weight is
+ * the decode kernel, and so do the minima db*bq (768-byte units; RSTQ_TUNE_Q4K_UNITS = 0 keeps them
+ * as a separate f32 [out, in/32] array folded by a second kernel).  Such a weight is
  * used with rstq_qmatmul (f32 activations, MODE_A8: q8_K quantizer + qmatmul-q4k, the `:apply` of
  * the registered :q4_K format, src/raster/quant/core.clj:57-66) and rstq_qmatmul_prequant (xs per
  * super-block [M, in/256], xsum = bsums [M, in/32]: qmatmul-q4k-dp4a!,
- * src/raster/quant/kernels_k.clj:195-237).  Not sharded, no tensor-core route, no MODE_F. */
+ * src/raster/quant/kernels_k.clj:195-237).  Sharded by binding a rank's rows (column split) or its
+ * super-blocks of K (row split) and calling rstq_tp_qmatmul, which then runs the exchange as a launch
+ * of its own.  No tensor-core route, no MODE_F. */
 RSTQ_API int32_t rstq_weight_bind_q4k(rstq_ctx* ctx, rstq_weight** w, const void* wq, const float* da,
                                       const float* db, const int8_t* aq, const int8_t* bq, int32_t dev,
                                       int64_t out, int64_t in);

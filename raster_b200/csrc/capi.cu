@@ -205,7 +205,7 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
         // rows through the decode kernel, then the pairs added (src/raster/quant/core.clj:68-75).
         RSTQ_REQUIRE(mode == RSTQ_MODE_A8 && act_dtype == RSTQ_F32 && out_dtype == RSTQ_F32, RSTQ_E_INVALID,
                      "a Q6_K weight takes f32 activations in MODE_A8 and writes f32");
-        RSTQ_REQUIRE(!tp, RSTQ_E_INVALID, "Q6_K weights are not sharded");
+        if (tp) return kNotFused;   // the exchange is fused into the per-32-block kernels only
         ActScratch s;
         int32_t rc = act_scratch(ds, M, w->in, &s);
         if (rc != RSTQ_OK) return rc;
@@ -226,7 +226,7 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
         // dots, scale / min fold (src/raster/quant/core.clj:57-66) -- at any M, on the decode kernel.
         RSTQ_REQUIRE(mode == RSTQ_MODE_A8 && act_dtype == RSTQ_F32 && out_dtype == RSTQ_F32, RSTQ_E_INVALID,
                      "a Q4_K weight takes f32 activations in MODE_A8 and writes f32");
-        RSTQ_REQUIRE(!tp, RSTQ_E_INVALID, "Q4_K weights are not sharded");
+        if (tp) return kNotFused;
         ActScratch s;
         int32_t rc = act_scratch(ds, M, w->in, &s);
         if (rc != RSTQ_OK) return rc;

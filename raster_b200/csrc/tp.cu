@@ -326,7 +326,10 @@ int32_t rstq_tp_qmatmul(rstq_tp* tp, rstq_weight* w, rstq_buf* x, rstq_buf* y, i
     RSTQ_REQUIRE(x && y && x->magic == kBufMagic && y->magic == kBufMagic && x->dev == tp->dev && y->dev == tp->dev,
                  RSTQ_E_INVALID, "invalid buffer");
     RSTQ_REQUIRE(split == RSTQ_SPLIT_COLUMN || split == RSTQ_SPLIT_ROW, RSTQ_E_INVALID, "split must be column or row");
-    RSTQ_REQUIRE(!w->mins && !w->pair_out, RSTQ_E_INVALID, "K-quant weights are not sharded");
+    // K-quant shards (the rows, or the K range in whole super-blocks, of the arrays a rank bound) take the
+    // unfused route: quantizer, decode kernel, exchange kernel
+    RSTQ_REQUIRE((!w->mins || w->kq) && (!w->pair_out || w->k6), RSTQ_E_INVALID,
+                 "K-quant weights are sharded in their unit layouts only (RSTQ_TUNE_Q4K_UNITS / _Q6K_UNITS = 1)");
     RSTQ_REQUIRE(M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)M);
     RSTQ_REQUIRE(w->out % 4 == 0, RSTQ_E_SHAPE, "out of a shard must be a multiple of 4 (16-byte rows), got %lld",
                  (long long)w->out);

@@ -102,6 +102,27 @@ def shard_rowmajor(plan: ShardPlan, rank: int, codes, scales, out: int, in_: int
             np.ascontiguousarray(s[r0:r1, k0 // BLOCK:k1 // BLOCK]).reshape(-1))
 
 
+def shard_kquant(plan: ShardPlan, rank: int, enc: dict, out: int, in_: int) -> dict:
+    """One rank's arrays of a Q4_K (keys wq, da, db, aq, bq) or Q6_K (wq, sc, ds) matrix, row-major [out, in].
+
+    Every array holds a fixed number of entries per row and super-block of 256 elements (Q4_K: 128 code
+    bytes, one da and db, eight aq and bq; Q6_K: 256 code bytes, sixteen sc, one ds), so a column split is a
+    slice of rows and a row split a slice of whole super-blocks in every row; the activation quantizer
+    q8_K works per super-block, so each rank quantizes its own slice of x exactly as the whole would be."""
+    check(plan, out, in_)
+    if in_ % 256 or (plan.split == "row" and (in_ // 256) % plan.ranks):
+        raise ValueError(f"K-quant shards are cut at super-blocks of 256: in = {in_}, ranks = {plan.ranks}")
+    r0, r1 = row_range(plan, rank, out)
+    k0, k1 = k_range(plan, rank, in_)
+    per_sb = ({"wq": 128, "da": 1, "db": 1, "aq": 8, "bq": 8} if "da" in enc else {"wq": 256, "sc": 16, "ds": 1})
+    nsb = in_ // 256
+    part = {}
+    for key, n in per_sb.items():
+        a = np.ascontiguousarray(enc[key]).reshape(out, nsb, n)
+        part[key] = np.ascontiguousarray(a[r0:r1, k0 // 256:k1 // 256]).reshape(-1)
+    return part
+
+
 def slice_activations(plan: ShardPlan, rank: int, x, M: int, in_: int):
     """x [M, in] -> the columns this rank multiplies (all of them for a column split)."""
     xa = np.ascontiguousarray(x).reshape(M, in_)

@@ -239,3 +239,41 @@ def test_decoder_layer_projections_sharded(group):
             assert np.array_equal(got[r].view(np.uint32), got[0].view(np.uint32)), (name, r)
         for o in sh + bx + by:
             o.free()
+
+
+@pytest.mark.parametrize("fmt", ["q4k", "q6k"])
+@pytest.mark.parametrize("split,M", [("column", 1), ("column", 5), ("row", 1), ("row", 3)])
+def test_kquant_shards(group, fmt, split, M):
+    """Q4_K / Q6_K matrices sharded by rows (column split: gathered) or by whole super-blocks of K (row
+    split: summed): every rank binds its slice of the format's arrays, quantizes its slice of x to q8_K and
+    runs quantizer + decode kernel + exchange kernel.  Against the unsharded f64 oracle."""
+    ctx, tps, P = group
+    out, in_ = (256 * P, 1024) if split == "column" else (384, 512 * P)
+    W = synth.normal(61, out * in_, 0.02) + np.float32(0.01)
+    x = synth.normal(62 + M, M * in_)
+    plan = shard.ShardPlan(split, P)
+    if fmt == "q4k":
+        e = orc.quantize_weight_q4k(W)
+        bind, mm = ctx.bind_weight_q4k, orc.qmatmul_q4k
+    else:
+        e = orc.quantize_weight_q6k(W)
+        bind, mm = ctx.bind_weight_q6k, orc.qmatmul_q6k
+    ref = []
+    for m in range(M):
+        xq, xs, bsums = orc.quantize_act_q8k(x[m * in_:(m + 1) * in_], in_, 32 if fmt == "q4k" else 16)
+        ref.append(mm(xq, xs, bsums, e, in_, out)[1])
+    ref = np.concatenate([np.asarray(r).ravel() for r in ref])
+    so, si = shard.shard_shape(plan, out, in_)
+    shards = [bind(shard.shard_kquant(plan, r, e, out, in_), so, si, dev=r) for r in range(P)]
+    bx = [ctx.array_to_buffer(shard.slice_activations(plan, r, x, M, in_), dev=r) for r in range(P)]
+    by = [ctx.make_buffer(M * out, np.float32, dev=r) for r in range(P)]
+    for rep in range(2):
+        for r in range(P):
+            tps[r].qmatmul(shards[r], bx[r], by[r], M, L.F32, L.MODE_A8, plan.split_code)
+    _sync_all(ctx, P)
+    got = [b.download() for b in by]
+    for r in range(1, P):
+        assert np.array_equal(got[r].view(np.uint32), got[0].view(np.uint32)), "ranks disagree"
+    assert relerr(got[0], ref) <= 1e-5
+    for o in shards + bx + by:
+        o.free()

@@ -148,3 +148,33 @@ def test_two_gloo_ranks_reproduce_the_unsharded_oracle():
     for rank, col_exact, row_err in got:
         assert col_exact, f"rank {rank}: gathered columns differ"
         assert row_err <= 1e-6, f"rank {rank}: row-split sum off by {row_err}"
+
+
+@pytest.mark.parametrize("fmt", ["q4k", "q6k"])
+@pytest.mark.parametrize("split,P", [("column", 2), ("column", 4), ("row", 2), ("row", 4)])
+def test_kquant_shards_reproduce_the_unsharded_oracle(fmt, split, P):
+    """shard_kquant cuts the K-quant arrays by rows or by whole super-blocks; the q8_K quantizer works per
+    super-block, so each rank's slice of x quantizes as the whole does: gathered rows are the unsharded rows
+    bit for bit (f64 oracle), summed partials agree to rounding."""
+    out, in_ = 32, 1024
+    rng = np.random.default_rng(7)
+    W = (rng.standard_normal(out * in_) * 0.02 + 0.01).astype(np.float32)
+    x = rng.standard_normal(in_).astype(np.float32)
+    plan = shard.ShardPlan(split, P)
+    if fmt == "q4k":
+        e, mm, sub = orc.quantize_weight_q4k(W), orc.qmatmul_q4k, 32
+    else:
+        e, mm, sub = orc.quantize_weight_q6k(W), orc.qmatmul_q6k, 16
+    xq, xs, bs = orc.quantize_act_q8k(x, in_, sub)
+    full = np.asarray(mm(xq, xs, bs, e, in_, out)[1], np.float64).ravel()
+    so, si = shard.shard_shape(plan, out, in_)
+    parts = []
+    for r in range(P):
+        er = shard.shard_kquant(plan, r, e, out, in_)
+        xr = shard.slice_activations(plan, r, x, 1, in_)
+        q, s, b = orc.quantize_act_q8k(xr, si, sub)
+        parts.append(np.asarray(mm(q, s, b, er, si, so)[1], np.float64).ravel())
+    if split == "column":
+        assert np.array_equal(np.concatenate(parts), full)
+    else:
+        assert relerr(sum(parts), full) <= 1e-12
