@@ -119,6 +119,14 @@ typedef struct rstq_event rstq_event;
                                      thread) instead of 128-token ones: 0 (default) = where the grid then needs
                                      fewer cycles over its waves of thread blocks, 1 = never, 2 = always,
                                      3 = as 0 but never two thread blocks per tile (each half of K) */
+#define RSTQ_TUNE_ACT_RING 14     /* MODE_A8 decode at 2 <= M <= 16, how the activations share shared memory with the
+                                     weight ring: 0 (default) = the plan that keeps most weight bytes on their way,
+                                     all tokens in one launch; 1 = all of K resident beside 64-unit chunks (tokens
+                                     that do not fit go to further launches, each streaming the weights again);
+                                     2 / 3 = every ring stage carries its own slice of the activation image
+                                     (64- / 32-unit chunks), so shared memory does not grow with K and the
+                                     image is read from L2 once per 32-row group; 4 = resident, 32-unit chunks.
+                                     Results are bit-identical in every setting */
 #define RSTQ_TUNE_ACT_IMAGE 10    /* 1 (default) = rstq_qmatmul in MODE_A8 at 2 <= M <= 16: the activation quantizer
                                      also writes the codes, scales and sums in the order the decode kernel
                                      keeps them in shared memory, and that kernel's copy thread brings them

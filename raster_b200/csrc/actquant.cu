@@ -58,16 +58,63 @@ quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float*
             // The decode kernel's staged form of the same data, for M > 1 (block-major, the eight
             // code words of a (block, token) as four (word tg, word 4 + tg) pairs; then per (block,
             // token) the scale and zero-point x code sum), so that it can take it with a bulk copy.
-            const int c = (int)(blk / nb), b = (int)(blk - (int64_t)c * nb);   // token, block
+            // More than kGemvMaxM tokens: one image per decode launch of kGemvMaxM tokens, act_image_stride apart.
+            const int ct = (int)(blk / nb), b = (int)(blk - (int64_t)ct * nb);   // token, block
+            const int piece = ct / kGemvMaxM, c = ct - piece * kGemvMaxM;        // token inside its launch
+            const int Mp = min(kGemvMaxM, M - piece * kGemvMaxM);                // tokens of that launch
+            uint8_t* im = img + piece * act_image_stride(nb);
             const int j = lane >> 2;                                            // word held by lanes 0, 4, .. 28
             if ((lane & 3) == 0)
-                reinterpret_cast<uint32_t*>(img)[((int64_t)(b * M + c) * 4 + (j & 3)) * 2 + (j >> 2)] = w;
-            const int Mz = (M + 1) & ~1;
-            int2* z = reinterpret_cast<int2*>(img + (((int64_t)nb * M * 32 + 127) & ~127ll));
+                reinterpret_cast<uint32_t*>(im)[((int64_t)(b * Mp + c) * 4 + (j & 3)) * 2 + (j >> 2)] = w;
+            const int Mz = (Mp + 1) & ~1;
+            int2* z = reinterpret_cast<int2*>(im + (((int64_t)nb * Mp * 32 + 127) & ~127ll));
             if (lane == 0) z[(int64_t)b * Mz + c] = make_int2(__float_as_int((float)d), zp * s);
-            if (lane == 1 && c == M - 1 && Mz > M) z[(int64_t)b * Mz + M] = make_int2(0, 0);
+            if (lane == 1 && c == Mp - 1 && Mz > Mp) z[(int64_t)b * Mz + Mp] = make_int2(0, 0);
         }
     }
+}
+
+// The same image from activations that arrive quantized (rstq_qmatmul_prequant): codes [M][in], scales and
+// code sums [M][nb].  Eight lanes per (token, block), one code word each.
+__global__ void __launch_bounds__(256)
+act_image_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs, const int32_t* __restrict__ xsum,
+                 int64_t nblocks, uint8_t* __restrict__ img, int M, int nb, int zp) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int Mz = (M + 1) & ~1;
+    int2* z = reinterpret_cast<int2*>(img + (((int64_t)nb * M * 32 + 127) & ~127ll));
+    const int64_t n = nblocks * 8, step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += step) {
+        const int64_t blk = i >> 3;
+        const int j = (int)(i & 7);
+        const int c = (int)(blk / nb), b = (int)(blk - (int64_t)c * nb);
+        reinterpret_cast<uint32_t*>(img)[((int64_t)(b * M + c) * 4 + (j & 3)) * 2 + (j >> 2)] =
+            reinterpret_cast<const uint32_t*>(xq)[i];
+        if (j == 0) z[(int64_t)b * Mz + c] = make_int2(__float_as_int(xs[blk]), zp * xsum[blk]);
+        if (j == 1 && c == M - 1 && Mz > M) z[(int64_t)b * Mz + M] = make_int2(0, 0);
+    }
+}
+
+int32_t launch_act_image(rstq_ctx* ctx, DeviceState& ds, const int8_t* xq, const float* xs, const int32_t* xsum,
+                         int64_t M, int64_t in, uint8_t* img, int zp) {
+    const int64_t nblocks = M * (in / 32);
+    int64_t ctas = (nblocks * 8 + 255) / 256;
+    const int64_t cap = (int64_t)ds.sm_count * 8;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ds.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ds.pdl ? 1 : 0;
+    RSTQ_CUDA(cudaLaunchKernelEx(&cfg, act_image_kernel, xq, xs, xsum, nblocks, img, (int)M, (int)(in / 32), zp));
+    ctx->launches++;
+    RSTQ_CUDA(cudaGetLastError());
+    return RSTQ_OK;
 }
 
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,

@@ -120,14 +120,14 @@ struct ActScratch {
     int8_t* xq;
     float* xs;
     int32_t* xsum;
-    uint8_t* img;   // the decode kernel's staged form of the three (2 <= M <= 16), see quant_act_i8_kernel
+    uint8_t* img;   // the decode kernel's staged form of the three (2 <= M < 64), see quant_act_i8_kernel
 };
 static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* out) {
     const int64_t nb = in / 32;
     const int64_t xq_bytes = (M * in + 255) & ~255ll;
     const int64_t sb = (M * nb * 4 + 255) & ~255ll;
-    const bool image = M >= 2 && M <= 16;
-    const int64_t img_bytes = image ? ((nb * M * 32 + 127) & ~127ll) + ((nb * ((M + 1) & ~1ll) * 8 + 255) & ~255ll) : 0;
+    const bool image = M >= 2 && M < 64;   // what the decode kernels serve in MODE_A8: one image per launch of kGemvMaxM tokens
+    const int64_t img_bytes = image ? ((M + kGemvMaxM - 1) / kGemvMaxM) * act_image_stride(nb) : 0;
     // xsum has room for sums per 16 elements (Q6_K units): two per block
     int32_t rc = dev_reserve(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 3 * sb + img_bytes);
     if (rc != RSTQ_OK) return rc;
@@ -159,9 +159,10 @@ static NextWeight note_decode_launch(rstq_ctx* ctx, DeviceState& ds, rstq_weight
 // One matmul over device pointers, M split into decode-kernel chunks.
 static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs,
                       const int32_t* xsum, float* y, int64_t M, const TpFuse* tp = nullptr,
-                      const uint8_t* img = nullptr) {
+                      const uint8_t* img = nullptr, uint8_t* img_scratch = nullptr) {
     GemvA8Args a{w->data, xq, xs, xsum, y, M, w->in, w->out, w->bits, w->zp, tp};
     a.img = img;
+    a.img_scratch = img_scratch;
     a.uk = w->kq ? 1 : (w->k6 ? 2 : 0);
     a.next = note_decode_launch(ctx, ctx->devs[w->dev], w);
     return launch_gemv_a8(ctx, ctx->devs[w->dev], a);
@@ -250,7 +251,9 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
     }
     // The same for MODE_A8 when not even 8 tokens of codes fit (K > 16 K): the codes and scales the
     // quantizer produced feed the tensor-core path instead (<= 1e-3, no longer the exact integer dots).
-    if (mode == RSTQ_MODE_A8 && !tc && M >= 9 && ctx->tune_gemm_min_m == 17 && w->in * 8 > 128 * 1024) tc = true;
+    // Up to 16 tokens this does not arise: their activations ride the weight ring, whatever K is.
+    const bool rides = M <= 16 && ds.act_image && ds.act_ring != 1 && ds.act_ring != 4;
+    if (mode == RSTQ_MODE_A8 && !tc && M >= 9 && !rides && ctx->tune_gemm_min_m == 17 && w->in * 8 > 128 * 1024) tc = true;
     if (tp && (tc || out_dtype != RSTQ_F32)) return kNotFused;  // only the decode kernel fuses the exchange
     if (mode == RSTQ_MODE_A8) {
         RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "unknown activation type");
@@ -600,6 +603,10 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
             return RSTQ_OK;
         case RSTQ_TUNE_ACT_IMAGE:
             for (auto& ds : ctx->devs) ds.act_image = value != 0;
+            return RSTQ_OK;
+        case RSTQ_TUNE_ACT_RING:
+            RSTQ_REQUIRE(value >= 0 && value <= 4, RSTQ_E_INVALID, "activation ring selector 0..4");
+            for (auto& ds : ctx->devs) ds.act_ring = value;
             return RSTQ_OK;
         case RSTQ_TUNE_FUSE_QUANT:
             for (auto& ds : ctx->devs) ds.fuse_quant = value != 0;
@@ -1083,11 +1090,15 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
     if ((rc = use_dev(ctx, w->dev)) != RSTQ_OK) return rc;
     DeviceState& ds = ctx->devs[w->dev];
     const int32_t* sums = xsum ? (const int32_t*)xsum->ptr : nullptr;
+    ActScratch s{};
+    if (!sums) {
+        if ((rc = act_scratch(ds, M, w->in, &s)) != RSTQ_OK) return rc;
+    } else if (M >= 2 && M <= 16 && ds.act_image) {
+        if (act_scratch(ds, M, w->in, &s) != RSTQ_OK) s = ActScratch{};   // no room to be had now (a capture in progress): without the image
+    }
     if (!sums) {
         // the stored codes carry a zero point, so the block sums are needed even
         // when the caller's arithmetic (signed x signed) has none
-        ActScratch s;
-        if ((rc = act_scratch(ds, M, w->in, &s)) != RSTQ_OK) return rc;
         const int64_t nblocks = M * w->nb;
         block_sum_kernel<<<(unsigned)((nblocks + 127) / 128), 128, 0, ds.stream>>>(
             (const int8_t*)xq->ptr, s.xsum, nblocks);
@@ -1095,7 +1106,10 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
         RSTQ_CUDA(cudaGetLastError());
         sums = s.xsum;
     }
-    return run_a8(ctx, w, (const int8_t*)xq->ptr, (const float*)xs->ptr, sums, (float*)y->ptr, M);
+    // (2 <= M <= 16: with room for the decode kernel's image of the activations, built when shared memory
+    // cannot hold them for all of K beside a ring deep enough)
+    return run_a8(ctx, w, (const int8_t*)xq->ptr, (const float*)xs->ptr, sums, (float*)y->ptr, M, nullptr, nullptr,
+                  ds.act_image ? s.img : nullptr);
 }
 
 // ---- host-array operators -----------------------------------------------------

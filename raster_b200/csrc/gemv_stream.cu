@@ -109,6 +109,13 @@ struct StreamParams {
     // thread copies it in with two bulk copies under a barrier of its own.  Null: stage in the kernel.
     const uint8_t* img;
     uint32_t img_b_bytes, img_z_bytes, img_z_off;
+    // MODE_A8, M > 1, `ring` set: nothing of the image is kept for the whole launch; every ring stage holds,
+    // behind its weight chunk, the image's slice for the chunk's K blocks (fragments at act_off, records at
+    // act2_off, both counted from the stage), copied by the producer with the chunk.  Shared memory then
+    // does not grow with K, at the price of reading the image (from L2) once per 32-row group.
+    int ring;
+    int cu;                 // units per chunk (M > 1: a multiple of the consumer warps, <= chunk_units_of)
+    uint32_t stage_bytes;   // distance between ring stages
     int kq;   // Q4_K units (zero point 0): the staged constant of a block is t = xs * code sum, which the minima multiply
     int k6;   // Q6_K units: xsum holds the code sums per 16 elements (2 per block), a record two constants
     TpFuse tp;            // tp.nranks == 0: no exchange, results go to y
@@ -524,7 +531,7 @@ __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bo
 }
 
 template <int BITS, int NT, int UK = 0>
-__device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* smem,
+__device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* actB, const uint8_t* actZ,
                                         const StreamParams& p, int b, int gid, int tig,
                                         float (&acc)[NT][4][2]) {
     constexpr bool KQ = UK == 1;
@@ -533,8 +540,8 @@ __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* sme
     if (UK == 2) {
         // Q6_K: per (block, token) {xs, zp * sum of 0..15, zp * sum of 16..31}; two tiles per 16 rows
         const int M = p.M, Mz = (M + 1) & ~1;
-        const uint2* xB = reinterpret_cast<const uint2*>(smem + p.act_off) + b * M * 4;
-        const int4* xz = reinterpret_cast<const int4*>(smem + p.act2_off) + b * Mz;
+        const uint2* xB = reinterpret_cast<const uint2*>(actB) + b * M * 4;
+        const int4* xz = reinterpret_cast<const int4*>(actZ) + b * Mz;
         const float se[4] = {u.sc.x, u.sc.z, u.mn.x, u.mn.z};   // rows gid + 8i, elements 0..15
         const float sf[4] = {u.sc.y, u.sc.w, u.mn.y, u.mn.w};   // elements 16..31
 #pragma unroll
@@ -569,8 +576,8 @@ __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* sme
     constexpr float HI = BITS == 4 ? 0.0625f : 1.0f;
     constexpr int ZSH = BITS == 4 ? 4 : 0;
     const int M = p.M, Mz = (M + 1) & ~1;
-    const uint2* xB = reinterpret_cast<const uint2*>(smem + p.act_off) + b * M * 4;
-    const int2* xz = reinterpret_cast<const int2*>(smem + p.act2_off) + b * Mz;
+    const uint2* xB = reinterpret_cast<const uint2*>(actB) + b * M * 4;
+    const int2* xz = reinterpret_cast<const int2*>(actZ) + b * Mz;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         // columns beyond M are never stored, so any valid address will do for them
@@ -788,8 +795,32 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 bulk_copy_g2s(smem_u32(smem + p.act2_off), p.img + p.img_z_off, p.img_z_bytes, act_bar);
                 img_done = true;
             };
+            // Ring of activations: a stage's slice of the image depends on the kernel before this one, its
+            // weights do not.  The first NS chunks of weights leave at once, registered on their barriers
+            // without an arrival; their slices follow after the wait, with the arrival.
+            const bool ring = MODE == MODE_A8 && !ONECOL && p.ring;
+            const int Mz8 = ((p.M + 1) & ~1) * 8, M32 = p.M * 32;
+            const int cu = ONECOL ? kChunkUnits : p.cu;
+            const uint32_t stage_bytes = ONECOL ? (uint32_t)CHUNK_BYTES : p.stage_bytes;
+            int pend_b[RSTQ_NSMAX], pend_n[RSTQ_NSMAX], npend = 0;
+            bool dep_waited = !ring;
+            if (ring) img_done = true;   // nothing is copied for the whole launch
+            auto copy_slice = [&](int slot, int bb, int nn, uint32_t more) {
+                const uint32_t nb1 = (uint32_t)(nn * M32), nb2 = (uint32_t)(nn * Mz8);
+                const uint32_t dst = smem_u32(smem) + (uint32_t)slot * stage_bytes;
+                mbar_expect_tx(full0 + 8 * slot, more + nb1 + nb2);
+                bulk_copy_g2s(dst + p.act_off, p.img + (int64_t)bb * M32, nb1, full0 + 8 * slot);
+                bulk_copy_g2s(dst + p.act2_off, p.img + p.img_z_off + (int64_t)bb * Mz8, nb2, full0 + 8 * slot);
+            };
+            auto slices_of_first = [&]() {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                for (int k = 0; k < npend; ++k) copy_slice(k, pend_b[k], pend_n[k], 0u);
+                npend = 0;
+                dep_waited = true;
+            };
             while (left > 0) {
                 if (!img_done && issued >= NS) copy_image();
+                if (!dep_waited && issued >= NS) slices_of_first();
                 if (pf_ahead > 0) {
                     const uint8_t* lim = src + pf_ahead < end ? src + pf_ahead : end;
                     while (pf < lim) {
@@ -800,7 +831,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     }
                 }
                 int n = nb - b < left ? nb - b : left;
-                n = n < kChunkUnits ? n : kChunkUnits;
+                n = n < cu ? n : cu;
                 ok = mbar_try(empty0 + 8 * s, ph ^ 1u) || mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
 #if RSTQ_PROBES
@@ -809,9 +840,18 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 const uint32_t bytes = (uint32_t)(n * UNIT);
                 if (PROBE(1)) {
                     mbar_arrive(full0 + 8 * s);
+                } else if (ring) {
+                    if (dep_waited) {
+                        copy_slice(s, b, n, bytes);
+                    } else {
+                        mbar_expect_only(full0 + 8 * s, bytes);
+                        pend_b[npend] = b;
+                        pend_n[npend++] = n;
+                    }
+                    bulk_copy_g2s_hint(smem_u32(smem) + (uint32_t)s * stage_bytes, src, bytes, full0 + 8 * s, pol);
                 } else {
                     mbar_expect_tx(full0 + 8 * s, bytes);
-                    bulk_copy_g2s_hint(smem_u32(smem) + (uint32_t)s * CHUNK_BYTES, src, bytes, full0 + 8 * s, pol);
+                    bulk_copy_g2s_hint(smem_u32(smem) + (uint32_t)s * stage_bytes, src, bytes, full0 + 8 * s, pol);
                 }
 #if RSTQ_PROBES
                 if (pfine && npf < 250) pfine[1 + npf++] = gtime_ns();
@@ -831,6 +871,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (pfine) pfine[0] = (unsigned long long)npf;
 #endif
             if (!img_done && ok) copy_image();
+            if (!dep_waited && ok) slices_of_first();
             if (!ok && p.img && img_done) {  // gave up with the image copy in flight: let it land (bounded)
                 const unsigned long long t0 = gtime_ns();
                 while (!mbar_try(act_bar, 0) && gtime_ns() - t0 < kWaitLimitNs) {
@@ -886,7 +927,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     if (QF) {
         stage_a8_quant<BITS>(p, smem, tid);
     } else if (MODE == MODE_A8) {
-        if (!ONECOL && p.img) {
+        if (!ONECOL && p.ring) {
+            // the slices arrive with the weight chunks
+        } else if (!ONECOL && p.img) {
             int got = 1;
             if (lane == 0) got = mbar_spin(act_bar, 0, abort_flag);   // on expiry the abort flag ends the loops below
             (void)__shfl_sync(0xffffffffu, got, 0);
@@ -964,14 +1007,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             *reinterpret_cast<volatile int*>(p.flags + blockIdx.x) = 1;
         }
     };
-    // Cross-warp reduction of the segment [b_from, b_to) of group g, then store / hand over.  Two
-    // reduction buffers alternate, so one barrier per flush is enough.
+    // Cross-warp reduction of the segment [b_from, b_to) of group g, then store / hand over.  With one
+    // tile of tokens two reduction buffers alternate, so one barrier per flush is enough.
     int flush_no = 0;
     auto flush = [&](int64_t g, int b_from, int b_to) {
         const bool head = b_from == 0, whole = head && (b_to == nb);
         const int64_t row0 = g * 32;
         float* part = p.partials + (int64_t)blockIdx.x * M * 32;
-        float* rbuf = ONECOL ? red + kParkGroups * kParkStride : red + (flush_no & 1) * (kCW * NV * 32);
+        // (two tiles of tokens and more: one buffer and a barrier before it is written again -- the second
+        // buffer would take 32 KB and more from the ring)
+        float* rbuf = ONECOL ? red + kParkGroups * kParkStride : red + (NT == 1 ? (flush_no & 1) * (kCW * NV * 32) : 0);
+        if (!ONECOL && NT > 1 && flush_no > 0) consumer_bar();
         ++flush_no;
         if (ONECOL) {
             // (whole groups are parked by the loop and reduced in batches; this serves the cut ones)
@@ -1177,6 +1223,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         uint32_t ph = 0;
         bool alive = true;
         const uint8_t* unit0 = smem + warp * UNIT;   // this warp's first unit in ring slot s
+        const int cu = p.cu;
+        const uint32_t stage_bytes = p.stage_bytes;
+        // activations: staged for all of K (block index = the block in the group), or the stage's own slice
+        // (block index = the unit's place in the chunk)
+        const bool ring = MODE == MODE_A8 && p.ring;
+        const uint8_t* actB = smem + p.act_off;
+        const uint8_t* actZ = smem + p.act2_off;
         zero_acc();
         if (dbg) {  // timestamp of the first weights; the loop's own wait then passes at once
             if (!mbar_try(full0, 0)) alive = mbar_wait(full0, 0, abort_flag);
@@ -1184,10 +1237,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         }
         while (left > 0) {
             int n = nb - b < left ? nb - b : left;
-            n = n < kChunkUnits ? n : kChunkUnits;
+            n = n < cu ? n : cu;
             if (alive && !mbar_test(full0 + 8 * s, ph) && !mbar_try(full0 + 8 * s, ph))
                 alive = mbar_wait(full0 + 8 * s, ph, abort_flag);
             if (alive && !PROBE(2)) {
+                const int b0 = ring ? warp : b + warp;   // block index of this warp's first unit
                 if (n == kChunkUnits && NT == 1) {
                     // a full chunk: this warp's units are all loaded before the first tile, so that
                     // the shared-memory round trips of one unit run under the arithmetic of another
@@ -1196,16 +1250,21 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     for (int j = 0; j < kUPW; ++j) lds_unit<BITS, UK>(un[j], unit0 + j * kCW * UNIT, lane);
 #pragma unroll
                     for (int j = 0; j < kUPW; ++j) {
-                        if (MODE == MODE_A8) unit_a8<BITS, NT, UK>(un[j], smem, p, b + warp + j * kCW, gid, tig, acc);
+                        if (MODE == MODE_A8) unit_a8<BITS, NT, UK>(un[j], actB, actZ, p, b0 + j * kCW, gid, tig, acc);
                         else unit_f<BITS, NT>(un[j], smem, p, b + warp + j * kCW, gid, tig, acc);
                     }
+                } else if (kUPW == 4 && n == kChunkUnits / 2 && NT == 1 && MODE == MODE_A8) {
+                    SUnit<BITS> un[2];   // a full chunk of the half-size ring
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) lds_unit<BITS, UK>(un[j], unit0 + j * kCW * UNIT, lane);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) unit_a8<BITS, NT, UK>(un[j], actB, actZ, p, b0 + j * kCW, gid, tig, acc);
                 } else {
                     for (int j = 0; warp + j * kCW < n; ++j) {
                         SUnit<BITS> un;
                         lds_unit<BITS, UK>(un, unit0 + j * kCW * UNIT, lane);
-                        const int blk = b + warp + j * kCW;
-                        if (MODE == MODE_A8) unit_a8<BITS, NT, UK>(un, smem, p, blk, gid, tig, acc);
-                        else unit_f<BITS, NT>(un, smem, p, blk, gid, tig, acc);
+                        if (MODE == MODE_A8) unit_a8<BITS, NT, UK>(un, actB, actZ, p, b0 + j * kCW, gid, tig, acc);
+                        else unit_f<BITS, NT>(un, smem, p, b + warp + j * kCW, gid, tig, acc);
                     }
                 }
             }
@@ -1213,11 +1272,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (lane == 0) mbar_arrive(empty0 + 8 * s);  // also when not alive: never block the producer
             b += n;
             left -= n;
-            unit0 += CHUNK_BYTES;
+            unit0 += stage_bytes;
+            if (ring) { actB += stage_bytes; actZ += stage_bytes; }
             if (++s == NS) {
                 s = 0;
                 ph ^= 1u;
-                unit0 -= (size_t)NS * CHUNK_BYTES;
+                unit0 -= (size_t)NS * stage_bytes;
+                if (ring) { actB -= (size_t)NS * stage_bytes; actZ -= (size_t)NS * stage_bytes; }
             }
             if (b == nb || left == 0) {
                 flush(g, seg_from, b);
@@ -1307,6 +1368,9 @@ struct StreamPlan {
     int64_t uq, ur;
     uint32_t act_off, act2_off, red_off, bar_off;
     size_t smem;
+    int cu, ring;           // units per chunk; the activations travel with the chunks (StreamParams::ring)
+    uint32_t stage_bytes;
+    int64_t in_flight() const { return (int64_t)(NS - 1) * cu; }   // units on their way while one chunk is consumed
 };
 
 // Measured on B200 at 14 shapes from 512x4096 to 28672x8192 (int4 and int8, M = 1..8): whole
@@ -1343,24 +1407,44 @@ static void split_units(const DeviceState& ds, int bits, int64_t groups, int64_t
     }
 }
 
+// cu: units per chunk (0: the full chunk of the unit kind).  ring: act_bytes / act2_bytes are the bytes PER UNIT
+// of a chunk's slice of the activation image, which rides in the ring stage behind the weights.
 static StreamPlan plan_stream(const DeviceState& ds, int bits, int NT, int64_t groups, int64_t nb,
-                              int64_t act_bytes, int64_t act2_bytes, bool onecol = false) {
+                              int64_t act_bytes, int64_t act2_bytes, bool onecol = false, int cu = 0,
+                              bool ring = false) {
     StreamPlan pl{};
-    const int kChunkUnits = chunk_units_of(bits);
-    const int chunk = kChunkUnits * unit_bytes(bits);
-    // two alternating reduction buffers ([warp][lane] at M = 1, [warp][value][lane] otherwise)
-    const int64_t red = onecol ? (int64_t)(kParkGroups + 1) * kParkStride * 4 : 2 * (int64_t)kCW * NT * 8 * 32 * 4;
-    const int64_t a1 = (act_bytes + 127) & ~127ll, a2 = (act2_bytes + 127) & ~127ll;
-    const int64_t room = kMaxDynSmem - (a1 + a2 + red + 512);
-    int64_t ns = room / chunk;
+    if (cu <= 0) cu = chunk_units_of(bits);
+    const int chunk = cu * unit_bytes(bits);
+    // reduction buffers ([warp][lane] at M = 1; [warp][value][lane] otherwise, two that alternate for one tile of tokens)
+    const int64_t red = onecol ? (int64_t)(kParkGroups + 1) * kParkStride * 4 : (NT == 1 ? 2 : 1) * (int64_t)kCW * NT * 8 * 32 * 4;
+    int64_t a1 = (act_bytes + 127) & ~127ll, a2 = (act2_bytes + 127) & ~127ll;
+    int64_t stage = chunk, room;
+    if (ring) {
+        a1 = (act_bytes * cu + 127) & ~127ll;
+        a2 = (act2_bytes * cu + 127) & ~127ll;
+        stage = chunk + a1 + a2;
+        room = kMaxDynSmem - (red + 512);
+    } else {
+        room = kMaxDynSmem - (a1 + a2 + red + 512);
+    }
+    int64_t ns = room / stage;
     if (ns > RSTQ_NSMAX) ns = RSTQ_NSMAX;
     pl.fits = ns >= 2;
     if (!pl.fits) return pl;
     split_units(ds, bits, groups, nb, &pl.G, &pl.uq, &pl.ur);
     pl.NS = (int)ns;
-    pl.act_off = (uint32_t)(ns * chunk);
-    pl.act2_off = pl.act_off + (uint32_t)a1;
-    pl.red_off = pl.act2_off + (uint32_t)a2;
+    pl.cu = cu;
+    pl.ring = ring;
+    pl.stage_bytes = (uint32_t)stage;
+    if (ring) {
+        pl.act_off = (uint32_t)chunk;            // inside every stage
+        pl.act2_off = (uint32_t)(chunk + a1);
+        pl.red_off = (uint32_t)(ns * stage);
+    } else {
+        pl.act_off = (uint32_t)(ns * chunk);
+        pl.act2_off = pl.act_off + (uint32_t)a1;
+        pl.red_off = pl.act2_off + (uint32_t)a2;
+    }
     pl.bar_off = pl.red_off + (uint32_t)red;
     pl.smem = pl.bar_off + 2 * ns * 8 + 16;  // ring barriers + the activation image's
     return pl;
@@ -1441,6 +1525,7 @@ static void fill_common(StreamParams& p, const DeviceState& ds, const StreamPlan
                                           : (wbytes >= (16ll << 20) && wbytes <= (64ll << 20) ? 64ll << 10 : 0);
     p.probe = ds.gemv_probe;
     p.act_off = pl.act_off; p.act2_off = pl.act2_off; p.red_off = pl.red_off; p.bar_off = pl.bar_off;
+    p.cu = pl.cu; p.ring = pl.ring; p.stage_bytes = pl.stage_bytes;
 }
 
 // At most this much of the next launch's weight is requested into L2 ahead of time (the head of
@@ -1509,6 +1594,46 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
         StreamPlan pl;
         int M = fit_tokens(ds, ukind, groups, nb, want, bytes, &pl, true);
+        // With the quantizer's image of the whole call at hand, the activations can travel with the weight
+        // chunks instead of staying in shared memory for all of K (StreamParams::ring); smaller chunks give
+        // a ring of the same bytes more stages.  Chosen by the weight bytes on their way while one chunk is
+        // consumed, which is what bounds the stream.
+        // the quantizer's image of this launch's tokens: laid out per kGemvMaxM tokens, so it serves a launch
+        // that starts at such a boundary and takes all that is left up to the next
+        const bool at_piece = a.img && a.uk == 0 && want > 1 && m0 % kGemvMaxM == 0;
+        const uint8_t* img = at_piece ? a.img + (m0 / kGemvMaxM) * act_image_stride(nb) : nullptr;
+        if (want > 1 && a.uk == 0) {
+            // (measured on B200, int4, 4096 <= K <= 28672: with the image at hand the ring is as fast as
+            // resident activations where those fit at the same depth and up to 3x faster where they do not;
+            // 32-unit chunks lose 10 - 30 % in either form and 48-unit ones 3 - 6 %, whatever depth they buy:
+            // above one token the loop is bound by the consumers' instructions, not by the bytes in flight)
+            const bool have_img = img != nullptr;
+            const bool can_make = !have_img && a.img_scratch && want == a.M;   // pre-quantized: one more small kernel
+            const int full = chunk_units_of(ukind), half = full / 2, NTw = want <= 8 ? 1 : 2;
+            const int64_t b1 = (int64_t)want * 32, b2 = (int64_t)((want + 1) & ~1) * 8;
+            const bool imgs = have_img || can_make;
+            const StreamPlan res_h = plan_stream(ds, ukind, NTw, groups, nb, nb * b1, nb * b2, false, half);
+            const StreamPlan ring_f = imgs ? plan_stream(ds, ukind, NTw, groups, nb, b1, b2, false, full, true) : StreamPlan{};
+            const StreamPlan ring_h = imgs ? plan_stream(ds, ukind, NTw, groups, nb, b1, b2, false, half, true) : StreamPlan{};
+            const StreamPlan* pick = nullptr;
+            switch (ds.act_ring) {
+                case 1: break;
+                case 2: if (ring_f.fits) pick = &ring_f; break;
+                case 3: if (ring_h.fits) pick = &ring_h; break;
+                case 4: if (res_h.fits) pick = &res_h; break;
+                default:
+                    if (ring_f.fits && (have_img || M < want || ring_f.NS > pl.NS)) pick = &ring_f;
+            }
+            if (pick) {
+                pl = *pick;
+                M = want;
+                if (pl.ring && !have_img) {
+                    int32_t rc = launch_act_image(ctx, ds, a.xq, a.xs, a.xsum, a.M, a.in, a.img_scratch, a.zp);
+                    if (rc != RSTQ_OK) return rc;
+                    img = a.img_scratch;
+                }
+            }
+        }
         RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
                      (long long)a.in);
         if (a.tp && (M < a.M || a.out % 4 != 0)) return kNotFused;  // the exchange fuses into ONE launch
@@ -1532,8 +1657,10 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         }
         p.y = a.y + m0 * a.out;
         p.T = 1; p.act_dtype = qf ? a.act_dtype : RSTQ_F32; p.out_dtype = RSTQ_F32;
-        if (a.img && M > 1 && M == a.M && a.uk == 0) {   // the image was laid out for the whole call: one piece only
-            p.img = a.img;
+        if (M != want) img = nullptr;   // fewer tokens than the image was laid out for
+        RSTQ_REQUIRE(!pl.ring || img, RSTQ_E_STATE, "a ring of activations without their image");
+        if (img) {
+            p.img = img;
             p.img_b_bytes = (uint32_t)(nb * M * 32);
             p.img_z_bytes = (uint32_t)(nb * ((M + 1) & ~1) * 8);
             p.img_z_off = (p.img_b_bytes + 127u) & ~127u;

@@ -81,6 +81,7 @@ struct DeviceState {
     int gemv_probe = 0;            // timing probes of the decode kernel (RSTQ_TUNE_PROBE); results are invalid while set
     bool prefetch_next = true;     // decode launches request the weight that followed this one last time into L2
     rstq_weight* last_decode_w = nullptr;   // the weight of the most recent decode launch on this device
+    int act_ring = 0;              // MODE_A8, M > 1: 0 = the plan with most weight bytes in flight, 1 = activations resident + full chunks, 2 / 3 = activations ride the ring (full / half chunks), 4 = resident + half chunks
     bool act_image = true;         // MODE_A8, 2 <= M <= 16: the quantizer also writes the decode kernel's staged form, taken by bulk copy
     bool x_on_host = false;        // the current host-array call lets its first kernel read x from pinned host memory
     bool fuse_quant = true;        // M = 1 operator: quantize the activations inside the decode kernel
@@ -225,6 +226,13 @@ int32_t launch_pair_sum(rstq_ctx* ctx, DeviceState& ds, const float* t, float* y
 int32_t launch_q4k_min(rstq_ctx* ctx, DeviceState& ds, const float* mins, const float* xs32, const int32_t* bsums,
                        float* y, int64_t M, int64_t nb, int64_t out);
 // actquant.cu
+constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels
+// bytes of the decode kernel's image of kGemvMaxM tokens' quantized activations (fragments, then scale / sum records)
+__host__ __device__ constexpr int64_t act_image_stride(int64_t nb) {
+    return ((nb * kGemvMaxM * 32 + 127) & ~127ll) + ((nb * kGemvMaxM * 8 + 255) & ~255ll);
+}
+int32_t launch_act_image(rstq_ctx* ctx, DeviceState& ds, const int8_t* xq, const float* xs, const int32_t* xsum,
+                         int64_t M, int64_t in, uint8_t* img, int zp);
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
                             int32_t* xsum, int64_t M, int64_t in, int act_dtype = RSTQ_F32, uint8_t* img = nullptr, int zp = 0);
 // Exchange fused into the tail of the decode kernel (layout of a region: see tp.cu).  The
@@ -261,6 +269,7 @@ struct GemvA8Args {
     int act_dtype = RSTQ_F32;    // itself while staging; xq / xs / xsum are then not read
     NextWeight next;
     const uint8_t* img = nullptr;  // M > 1: the quantizer's image of the staged activations (see StreamParams::img)
+    uint8_t* img_scratch = nullptr;  // pre-quantized activations, 2 <= M <= 16: room for that image, built by a kernel of its own when the ring of activations pays
     int uk = 0;                    // unit kind of w: 0 = plain, 1 = Q4_K units (768 B, minima inside; xs / xsum are the
                                    // q8_K scales per block and sums per 32), 2 = Q6_K units (1280 B, a scale per 16
                                    // elements; xsum holds the sums per 16, two per block)
@@ -299,7 +308,6 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
 // freed at once, or parked until the last live graph of the device is destroyed)
 int32_t dev_reserve(DeviceState& ds, void** p, int64_t* have, int64_t need);
 int32_t dev_release_scratch(DeviceState& ds, void* p);
-constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels
 constexpr int64_t kFusedQuantMaxIn = 12288; // longest row the decode kernel quantizes itself (3 passes of 512 threads x 8)
 
 }  // namespace rstq

@@ -21,6 +21,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
                  "r"(bytes)
                  : "memory");
 }
+// Raise the phase's expected byte count without arriving: for copies that complete on a barrier whose
+// (single) arrival comes later, with the rest of the bytes.
+__device__ __forceinline__ void mbar_expect_only(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

@@ -140,8 +140,10 @@ def test_fused_quantizer_is_bit_identical_to_the_quantizer_kernel(ctx, bits, pla
 def test_activation_image_is_bit_identical_to_the_in_kernel_gather(ctx, bits, plan, M, out, in_):
     """rstq_qmatmul in MODE_A8 at 2 <= M <= 16: the quantizer also writes the decode kernel's staged form of
     the activations and the kernel takes it by bulk copy; with RSTQ_TUNE_ACT_IMAGE = 0 the kernel's warps gather
-    it from the quantizer's row-major output.  Same bytes in shared memory -> the same y, bit for bit (also when
-    the call is cut into several launches and falls back to the gather), and both match the oracle."""
+    it from the quantizer's row-major output.  Same bytes in shared memory -> the same y, bit for bit, and both
+    match the oracle.  (Where shared memory cannot hold all of K for every token, the gather cuts the call into
+    several launches while the image rides the weight ring in one; a last launch of ONE token runs the M = 1
+    kernel, which adds a row's blocks up in another order, so the last token is compared with the oracle only.)"""
     fmt_desc, fmt, ofmt = FMT[bits]
     _, wq, ws = make_weight(out, in_, bits, seed=out + in_ + M)
     x = synth.normal(out + 7 * in_ + M, M * in_)
@@ -159,10 +161,62 @@ def test_activation_image_is_bit_identical_to_the_in_kernel_gather(ctx, bits, pl
     finally:
         ctx.tune(L.TUNE_ACT_IMAGE, 1)
         ctx.tune(L.TUNE_GEMV_PLAN, 0)
-    assert np.array_equal(ys[1].view(np.uint32), ys[0].view(np.uint32))
+    head = (M - 1) * out
+    assert np.array_equal(ys[1][:head].view(np.uint32), ys[0][:head].view(np.uint32))
     xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
     ref = orc.matmul_a8_f64(wq, ws, ofmt, xq, xs, xsum, M, in_, out)
-    assert relerr(ys[1], ref) <= TOL_A8
+    assert relerr(ys[1], ref) <= TOL_A8 and relerr(ys[0], ref) <= TOL_A8
+    for b in (bx, by):
+        b.free()
+    w.free()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("plan", [0, 1])
+@pytest.mark.parametrize("M,out,in_", [(2, 264, 1024), (3, 96, 160), (4, 4096, 4096), (8, 1000, 11008), (5, 11008, 4096),
+                                       (9, 520, 2048), (16, 512, 4096), (16, 300, 8192), (7, 64, 28672), (16, 96, 28672),
+                                       (12, 2048, 11008), (20, 200, 11008), (33, 96, 4096), (40, 64, 8192), (63, 40, 2048)])
+def test_activations_riding_the_ring_give_the_same_bits(ctx, bits, plan, M, out, in_):
+    """RSTQ_TUNE_ACT_RING: the activations of a MODE_A8 decode launch (up to 16 tokens; more tokens take several
+    launches, the quantizer lays out one image for each) either stay in shared memory for
+    all of K (1, 4: further launches for the tokens that do not fit) or every ring stage carries the slice of the
+    quantizer's image for its own K blocks (2, 3), in chunks of 64 or 32 units (16 for 8-bit codes).  The same
+    integer dots are folded in the same order, so y is the same bit for bit in every setting, the default's
+    choice included, with whole groups per thread block and with groups cut between neighbours (ragged chunks
+    at every cut), and it matches the oracle."""
+    # (bit for bit: a block goes to the same warp whatever the chunk size, since chunks start a multiple of 16
+    # blocks after the segment's first)
+    fmt_desc, fmt, ofmt = FMT[bits]
+    _, wq, ws = make_weight(out, in_, bits, seed=out + in_ + M + 1)
+    x = synth.normal(out + 5 * in_ + M, M * in_)
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    ys = {}
+    try:
+        ctx.tune(L.TUNE_GEMV_PLAN, plan)
+        ctx.tune(L.TUNE_GEMM_MIN_M, 64)      # keep M >= 9 at long K on the decode kernel
+        for ring in (1, 2, 3, 4, 0):
+            ctx.tune(L.TUNE_ACT_RING, ring)
+            for rep in range(2):             # twice: the ring's barriers and the hand-over flags start clean again
+                by.fill_bytes(0xFF)
+                ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+                ctx.sync()
+            ys[ring] = by.download()
+    finally:
+        ctx.tune(L.TUNE_ACT_RING, 0)
+        ctx.tune(L.TUNE_GEMM_MIN_M, 17)
+        ctx.tune(L.TUNE_GEMV_PLAN, 0)
+    for ring in (3, 0):
+        assert np.array_equal(ys[ring].view(np.uint32), ys[2].view(np.uint32)), ring
+    # resident activations: tokens that do not fit go to further launches; a last launch of ONE token runs the
+    # M = 1 kernel, which adds a row's blocks up in another order -- every other token is the same bit for bit
+    head = (M - 1) * out
+    for ring in (1, 4):
+        assert np.array_equal(ys[ring][:head].view(np.uint32), ys[2][:head].view(np.uint32)), ring
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    ref = orc.matmul_a8_f64(wq, ws, ofmt, xq, xs, xsum, M, in_, out)
+    for ring in (0, 1, 2, 3, 4):
+        assert relerr(ys[ring], ref) <= TOL_A8, ring
     for b in (bx, by):
         b.free()
     w.free()
@@ -584,12 +638,20 @@ def test_tokens_are_split_when_activations_exceed_shared_memory(ctx):
     w = ctx.bind_weight(wq, ws, out, in_, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
     xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
     ref = orc.matmul_a8_f64(wq, ws, 0, xq, xs, xsum, M, in_, out).reshape(M, out)
-    y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)      # 16 tokens of rows this long: tensor-core path
-    assert relerr(y, ref) <= TOL_GEMM
     n0 = ctx.launch_count()
-    y = ctx.qmatmul_host(w, x[: 8 * in_], 8, L.F32, L.MODE_A8)   # 8 tokens: decode kernel, M cut in pieces
-    assert ctx.launch_count() - n0 >= 3      # quantizer + at least two decode launches
-    assert relerr(y, ref[:8]) <= TOL_A8
+    y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)      # up to 16 tokens ride the weight ring: one exact decode launch
+    assert ctx.launch_count() - n0 <= 2      # quantizer + decode
+    assert relerr(y, ref) <= TOL_A8
+    try:
+        ctx.tune(L.TUNE_ACT_RING, 1)         # activations resident for all of K
+        y = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_A8)          # 16 tokens of rows this long: tensor-core path
+        assert relerr(y, ref) <= TOL_GEMM
+        n0 = ctx.launch_count()
+        y = ctx.qmatmul_host(w, x[: 8 * in_], 8, L.F32, L.MODE_A8)   # 8 tokens: decode kernel, M cut in pieces
+        assert ctx.launch_count() - n0 >= 3      # quantizer + at least two decode launches
+        assert relerr(y, ref[:8]) <= TOL_A8
+    finally:
+        ctx.tune(L.TUNE_ACT_RING, 0)
     yf = ctx.qmatmul_host(w, x, M, L.F32, L.MODE_F)      # long rows, M >= 9: the tensor-core path
     assert relerr(yf, orc.matmul_dq_f64(wq, ws, 0, x, M, in_, out)) <= TOL_GEMM
     ref8 = orc.matmul_dq_f64(wq, ws, 0, x[: 8 * in_], 8, in_, out)
