@@ -23,7 +23,8 @@ __device__ __forceinline__ int round_half_up(double v) {
 template <bool BF16IN>
 __global__ void __launch_bounds__(256)
 quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float* __restrict__ xs,
-                    int32_t* __restrict__ xsum, int64_t nblocks, uint8_t* __restrict__ img, int M, int nb, int zp) {
+                    int32_t* __restrict__ xsum, int64_t nblocks, uint8_t* __restrict__ img, int M, int nb, int zp,
+                    int four_bit) {
     // programmatic dependent launch: let the consumer kernel start its weight stream now;
     // x may come from the kernel before this one, so wait for it
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -56,8 +57,8 @@ quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float*
         }
         if (img) {
             // The decode kernel's staged form of the same data, for M > 1 (block-major, the eight
-            // code words of a (block, token) as four (word tg, word 4 + tg) pairs; then per (block,
-            // token) the scale and zero-point x code sum), so that it can take it with a bulk copy.
+            // code words of a (block, token) as four (word tg, word 4 + tg) pairs; then the records of
+            // put_act_record), so that it can take it with a bulk copy.
             // More than kGemvMaxM tokens: one image per decode launch of kGemvMaxM tokens, act_image_stride apart.
             const int ct = (int)(blk / nb), b = (int)(blk - (int64_t)ct * nb);   // token, block
             const int piece = ct / kGemvMaxM, c = ct - piece * kGemvMaxM;        // token inside its launch
@@ -67,9 +68,9 @@ quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float*
             if ((lane & 3) == 0)
                 reinterpret_cast<uint32_t*>(im)[((int64_t)(b * Mp + c) * 4 + (j & 3)) * 2 + (j >> 2)] = w;
             const int Mz = (Mp + 1) & ~1;
-            int2* z = reinterpret_cast<int2*>(im + (((int64_t)nb * Mp * 32 + 127) & ~127ll));
-            if (lane == 0) z[(int64_t)b * Mz + c] = make_int2(__float_as_int((float)d), zp * s);
-            if (lane == 1 && c == Mp - 1 && Mz > Mp) z[(int64_t)b * Mz + Mp] = make_int2(0, 0);
+            uint8_t* recs = im + (((int64_t)nb * Mp * 32 + 127) & ~127ll);
+            if (lane == 0) put_act_record(recs, b, Mz, c, (float)d, zp * s, four_bit);
+            if (lane == 1 && c == Mp - 1 && Mz > Mp) put_act_record(recs, b, Mz, Mp, 0.f, 0, four_bit);
         }
     }
 }
@@ -78,11 +79,11 @@ quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float*
 // code sums [M][nb].  Eight lanes per (token, block), one code word each.
 __global__ void __launch_bounds__(256)
 act_image_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs, const int32_t* __restrict__ xsum,
-                 int64_t nblocks, uint8_t* __restrict__ img, int M, int nb, int zp) {
+                 int64_t nblocks, uint8_t* __restrict__ img, int M, int nb, int zp, int four_bit) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int Mz = (M + 1) & ~1;
-    int2* z = reinterpret_cast<int2*>(img + (((int64_t)nb * M * 32 + 127) & ~127ll));
+    uint8_t* recs = img + (((int64_t)nb * M * 32 + 127) & ~127ll);
     const int64_t n = nblocks * 8, step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += step) {
         const int64_t blk = i >> 3;
@@ -90,13 +91,13 @@ act_image_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs, co
         const int c = (int)(blk / nb), b = (int)(blk - (int64_t)c * nb);
         reinterpret_cast<uint32_t*>(img)[((int64_t)(b * M + c) * 4 + (j & 3)) * 2 + (j >> 2)] =
             reinterpret_cast<const uint32_t*>(xq)[i];
-        if (j == 0) z[(int64_t)b * Mz + c] = make_int2(__float_as_int(xs[blk]), zp * xsum[blk]);
-        if (j == 1 && c == M - 1 && Mz > M) z[(int64_t)b * Mz + M] = make_int2(0, 0);
+        if (j == 0) put_act_record(recs, b, Mz, c, xs[blk], zp * xsum[blk], four_bit);
+        if (j == 1 && c == M - 1 && Mz > M) put_act_record(recs, b, Mz, M, 0.f, 0, four_bit);
     }
 }
 
 int32_t launch_act_image(rstq_ctx* ctx, DeviceState& ds, const int8_t* xq, const float* xs, const int32_t* xsum,
-                         int64_t M, int64_t in, uint8_t* img, int zp) {
+                         int64_t M, int64_t in, uint8_t* img, int zp, int bits) {
     const int64_t nblocks = M * (in / 32);
     int64_t ctas = (nblocks * 8 + 255) / 256;
     const int64_t cap = (int64_t)ds.sm_count * 8;
@@ -111,14 +112,15 @@ int32_t launch_act_image(rstq_ctx* ctx, DeviceState& ds, const int8_t* xq, const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ds.pdl ? 1 : 0;
-    RSTQ_CUDA(cudaLaunchKernelEx(&cfg, act_image_kernel, xq, xs, xsum, nblocks, img, (int)M, (int)(in / 32), zp));
+    RSTQ_CUDA(cudaLaunchKernelEx(&cfg, act_image_kernel, xq, xs, xsum, nblocks, img, (int)M, (int)(in / 32), zp,
+                                 (int)(bits == 4)));
     ctx->launches++;
     RSTQ_CUDA(cudaGetLastError());
     return RSTQ_OK;
 }
 
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
-                            int32_t* xsum, int64_t M, int64_t in, int act_dtype, uint8_t* img, int zp) {
+                            int32_t* xsum, int64_t M, int64_t in, int act_dtype, uint8_t* img, int zp, int bits) {
     const int64_t nblocks = M * (in / 32);
     int64_t ctas = (nblocks + 7) / 8;  // 8 warps per CTA
     const int64_t cap = (int64_t)ds.sm_count * 8;
@@ -135,10 +137,10 @@ int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_
     cfg.numAttrs = ds.pdl ? 1 : 0;
     if (act_dtype == RSTQ_BF16)
         RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel<true>, x, xq, xs, xsum, nblocks, img, (int)M,
-                                     (int)(in / 32), zp));
+                                     (int)(in / 32), zp, (int)(bits == 4)));
     else
         RSTQ_CUDA(cudaLaunchKernelEx(&cfg, quant_act_i8_kernel<false>, x, xq, xs, xsum, nblocks, img, (int)M,
-                                     (int)(in / 32), zp));
+                                     (int)(in / 32), zp, (int)(bits == 4)));
     ctx->launches++;
     RSTQ_CUDA(cudaGetLastError());
     return RSTQ_OK;

@@ -269,7 +269,7 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
         int32_t rc = act_scratch(ds, M, w->in, &s);
         if (rc != RSTQ_OK) return rc;
         uint8_t* img = (!tc && ds.act_image) ? s.img : nullptr;
-        rc = launch_quant_act_i8(ctx, ds, x, s.xq, s.xs, s.xsum, M, w->in, act_dtype, img, w->zp);
+        rc = launch_quant_act_i8(ctx, ds, x, s.xq, s.xs, s.xsum, M, w->in, act_dtype, img, w->zp, w->bits);
         if (rc != RSTQ_OK) return rc;
         if (!tc) return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M, tp, img);
         void* x16;

@@ -75,7 +75,7 @@ static_assert(kQuantMaxIn >= kFusedQuantMaxIn, "the host routes by kFusedQuantMa
 // group: [warp][33]) and reduced across warps once per kParkGroups groups, not once per group
 constexpr int kParkGroups = 8;
 constexpr int kParkStride = kCW * 33;
-constexpr int kMagicInt = 0x4B400000;            // bits of 12582912.0f = 2^23 + 2^22
+constexpr int kMagicInt = kActMagicInt;          // bits of 12582912.0f = 2^23 + 2^22
 constexpr float kMagicFlt = 12582912.0f;
 
 enum { MODE_F = 0, MODE_A8 = 1 };
@@ -152,7 +152,8 @@ __device__ __forceinline__ void imma_acc(int (&d)[4], const uint32_t (&a)[4], ui
 //            the high nibbles (tile value x16): xs_t = xs/16 and c_t = bias - 16*zp*xsum;
 //            otherwise xs_t = xs and c_t = bias - zp*xsum (bias = bits of 2^23 + 2^22).
 // A8, M > 1 : sB [nb][M][4 tig] uint2 {xq word tig, xq word 4+tig};
-//             sxz [nb][Mz] int2 {xs bits, zp*xsum}, Mz = M rounded up to even.
+//             plain units: [nb][Mz / 2] records of a token pair (put_act_record), Mz = M rounded up to even;
+//             Q4_K units: sxz [nb][Mz] int2 {xs bits, bits of xs * code sum}.
 //             (For 2 <= M <= 16 the activation quantizer can write both arrays in this order itself:
 //             StreamParams::img, copied in by the producer thread instead of staged here.)
 // K-quant units: Q4_K (zero point 0): the constant of a record is t = xs * code sum, which the unit's
@@ -244,6 +245,20 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
         }
         return;
     }
+    if (!p.kq) {   // plain units: the pair records
+        uint8_t* recs = smem + p.act2_off;
+        for (int o = tid; o < tot2; o += kConsumers) {
+            const int b = o / Mz, c = o - b * Mz;
+            float xs = 0.f;
+            int zs = 0;
+            if (c < M) {
+                xs = p.xs[(int64_t)c * nb + b];
+                zs = p.zp * p.xsum[(int64_t)c * nb + b];
+            }
+            put_act_record(recs, b, Mz, c, xs, zs, BITS == 4);
+        }
+        return;
+    }
     for (int o0 = tid; o0 < tot2; o0 += U * kConsumers) {
         int2 v[U];
 #pragma unroll
@@ -255,7 +270,7 @@ __device__ __forceinline__ void stage_a8(const StreamParams& p, uint8_t* smem, i
                 if (c < M) {
                     v[j].x = __float_as_int(p.xs[(int64_t)c * nb + b]);
                     const int cs = p.xsum[(int64_t)c * nb + b];
-                    v[j].y = p.kq ? __float_as_int(__int_as_float(v[j].x) * (float)cs) : p.zp * cs;
+                    v[j].y = __float_as_int(__int_as_float(v[j].x) * (float)cs);
                 }
             }
         }
@@ -530,6 +545,36 @@ __device__ __forceinline__ float row_fold(const RowUnit<BITS>& u, uint32_t m, bo
     return fmaf(u.sc * __uint_as_float(u.r.z), f, acc);
 }
 
+// Two f32 in one 64-bit register (element 0 in the low half) and the packed arithmetic of sm_100 on them.
+__device__ __forceinline__ uint64_t pack_b32x2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    return pack_b32x2(__float_as_uint(lo), __float_as_uint(hi));
+}
+__device__ __forceinline__ float lo_f32x2(uint64_t v) {
+    uint32_t lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+    return __uint_as_float(lo);
+}
+__device__ __forceinline__ float hi_f32x2(uint64_t v) {
+    uint32_t lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+    return __uint_as_float(hi);
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 template <int BITS, int NT, int UK = 0>
 __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* actB, const uint8_t* actZ,
                                         const StreamParams& p, int b, int gid, int tig,
@@ -566,6 +611,40 @@ __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* act
                     acc[nt][2 * q + i][1] = fmaf(s_f * xs1, __int_as_float(df[2 * i + 1]) - kMagicFlt,
                                                  fmaf(s_e * xs1, __int_as_float(de[2 * i + 1]) - kMagicFlt, acc[nt][2 * q + i][1]));
                 }
+            }
+        }
+        return;
+    }
+    if (UK == 0) {
+        // Plain units: everything that depends on the (block, token) alone comes ready-made in the pair record
+        // (put_act_record); the fold of a row's two values is two packed f32 operations and two fmas:
+        // t = (float(d) - bias) * xs for both tokens at once, acc += s * t each.
+        const float sc[4] = {u.sc.x, u.sc.y, u.sc.z, u.sc.w};
+        const int M = p.M, Mh = (M + 1) >> 1;
+        const uint2* xB = reinterpret_cast<const uint2*>(actB) + b * M * 4;
+        const ulonglong2* rec = reinterpret_cast<const ulonglong2*>(actZ) + b * Mh * 2;
+        const uint64_t nbias = pack_f32x2(-kMagicFlt, -kMagicFlt);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            // columns beyond M are never stored, so any valid address will do for them
+            int col = nt * 8 + gid;
+            col = col < M ? col : M - 1;
+            const uint2 bb = xB[col * 4 + tig];
+            int pr = nt * 4 + tig;
+            pr = pr < Mh ? pr : 0;
+            const ulonglong2 xv = rec[pr * 2];                                      // {xs_a, xs_b}, {xs_a h, xs_b h}
+            const int4 cv = *reinterpret_cast<const int4*>(rec + pr * 2 + 1);       // ca_a, ca_b, cb_a, cb_b
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                int d[4];
+                imma_acc(d, a[q], bb.x, bb.y, cv.x, cv.y, cv.z, cv.w);
+                const uint64_t tl = mul_f32x2(add_f32x2(pack_b32x2((uint32_t)d[0], (uint32_t)d[1]), nbias), xv.x);
+                const uint64_t th = mul_f32x2(add_f32x2(pack_b32x2((uint32_t)d[2], (uint32_t)d[3]), nbias), xv.y);
+                const float s0 = sc[2 * q], s1 = sc[2 * q + 1];
+                acc[nt][2 * q][0] = fmaf(s0, lo_f32x2(tl), acc[nt][2 * q][0]);
+                acc[nt][2 * q][1] = fmaf(s0, hi_f32x2(tl), acc[nt][2 * q][1]);
+                acc[nt][2 * q + 1][0] = fmaf(s1, lo_f32x2(th), acc[nt][2 * q + 1][0]);
+                acc[nt][2 * q + 1][1] = fmaf(s1, hi_f32x2(th), acc[nt][2 * q + 1][1]);
             }
         }
         return;
@@ -799,7 +878,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             // weights do not.  The first NS chunks of weights leave at once, registered on their barriers
             // without an arrival; their slices follow after the wait, with the arrival.
             const bool ring = MODE == MODE_A8 && !ONECOL && p.ring;
-            const int Mz8 = ((p.M + 1) & ~1) * 8, M32 = p.M * 32;
+            const int Mz8 = ((p.M + 1) & ~1) * kActRecBytes, M32 = p.M * 32;   // bytes of a block's records / fragments
             const int cu = ONECOL ? kChunkUnits : p.cu;
             const uint32_t stage_bytes = ONECOL ? (uint32_t)CHUNK_BYTES : p.stage_bytes;
             int pend_b[RSTQ_NSMAX], pend_n[RSTQ_NSMAX], npend = 0;
@@ -1584,7 +1663,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
     auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
         *NT = m <= 8 ? 1 : 2;
         if (m == 1) { *a1 = nb * (k6 ? 128 : 64); *a2 = 0; }
-        else { *a1 = nb * m * 32; *a2 = nb * ((m + 1) & ~1) * (k6 ? 16 : 8); }
+        else { *a1 = nb * m * 32; *a2 = nb * ((m + 1) & ~1) * (k6 ? 16 : (a.uk == 0 ? kActRecBytes : 8)); }
     };
     // unit kind for the size helpers: Q4_K units carry 128 more bytes than 4-bit ones, Q6_K units 128 more than 8-bit ones
     const int ukind = a.uk == 1 ? 5 : (k6 ? 6 : a.bits);
@@ -1610,7 +1689,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
             const bool have_img = img != nullptr;
             const bool can_make = !have_img && a.img_scratch && want == a.M;   // pre-quantized: one more small kernel
             const int full = chunk_units_of(ukind), half = full / 2, NTw = want <= 8 ? 1 : 2;
-            const int64_t b1 = (int64_t)want * 32, b2 = (int64_t)((want + 1) & ~1) * 8;
+            const int64_t b1 = (int64_t)want * 32, b2 = (int64_t)((want + 1) & ~1) * kActRecBytes;
             const bool imgs = have_img || can_make;
             const StreamPlan res_h = plan_stream(ds, ukind, NTw, groups, nb, nb * b1, nb * b2, false, half);
             const StreamPlan ring_f = imgs ? plan_stream(ds, ukind, NTw, groups, nb, b1, b2, false, full, true) : StreamPlan{};
@@ -1628,7 +1707,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
                 pl = *pick;
                 M = want;
                 if (pl.ring && !have_img) {
-                    int32_t rc = launch_act_image(ctx, ds, a.xq, a.xs, a.xsum, a.M, a.in, a.img_scratch, a.zp);
+                    int32_t rc = launch_act_image(ctx, ds, a.xq, a.xs, a.xsum, a.M, a.in, a.img_scratch, a.zp, a.bits);
                     if (rc != RSTQ_OK) return rc;
                     img = a.img_scratch;
                 }
@@ -1662,7 +1741,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         if (img) {
             p.img = img;
             p.img_b_bytes = (uint32_t)(nb * M * 32);
-            p.img_z_bytes = (uint32_t)(nb * ((M + 1) & ~1) * 8);
+            p.img_z_bytes = (uint32_t)(nb * ((M + 1) & ~1) * kActRecBytes);
             p.img_z_off = (p.img_b_bytes + 127u) & ~127u;
         }
         if (a.tp) p.tp = *a.tp;

@@ -227,14 +227,34 @@ int32_t launch_q4k_min(rstq_ctx* ctx, DeviceState& ds, const float* mins, const 
                        float* y, int64_t M, int64_t nb, int64_t out);
 // actquant.cu
 constexpr int kGemvMaxM = 16;             // widest token tile of the decode kernels
-// bytes of the decode kernel's image of kGemvMaxM tokens' quantized activations (fragments, then scale / sum records)
+// bytes of the decode kernel's image of kGemvMaxM tokens' quantized activations (fragments, then the records)
+constexpr int kActRecBytes = 16;   // per (block, token), plain units
 __host__ __device__ constexpr int64_t act_image_stride(int64_t nb) {
-    return ((nb * kGemvMaxM * 32 + 127) & ~127ll) + ((nb * kGemvMaxM * 8 + 255) & ~255ll);
+    return ((nb * kGemvMaxM * 32 + 127) & ~127ll) + ((nb * kGemvMaxM * kActRecBytes + 255) & ~255ll);
 }
+constexpr int kActMagicInt = 0x4B400000;   // bits of 12582912.0f = 2^23 + 2^22: int -> float through the tile's accumulator input
+#ifdef __CUDACC__
+// The record of a (block, token) for the decode kernel above one token, plain units: the tokens of a block go
+// in pairs (a, b) of 32 bytes {xs_a, xs_b, xs_a*h, xs_b*h | ca_a, ca_b, cb_a, cb_b}: the scale as the rows in
+// the low nibbles want it and as those in the high nibbles do (their tile values are 16 times the codes:
+// h = 1/16 for 4-bit units, else 1), and the accumulator inputs of the two kinds of rows (the int -> float
+// bias less the zero-point term zs = zp * code sum, times 16 for the high-nibble rows).  A lane holds two
+// neighbouring tokens' results, so it reads one pair: two 16-byte loads, nothing to compute.  (Measured:
+// records of half the size, the high-nibble variants derived in the loop, were 2 - 8 % slower: the loop is
+// bound by instruction issue before shared-memory bandwidth.)
+__device__ __forceinline__ void put_act_record(uint8_t* recs, int64_t b, int Mz, int c, float xs, int zs, bool four_bit) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(recs + (b * (Mz >> 1) + (c >> 1)) * 32) + (c & 1);
+    r[0] = __float_as_uint(xs);
+    r[2] = __float_as_uint(four_bit ? xs * 0.0625f : xs);
+    r[4] = (uint32_t)(kActMagicInt - zs);
+    r[6] = (uint32_t)(kActMagicInt - (four_bit ? zs * 16 : zs));
+}
+#endif
 int32_t launch_act_image(rstq_ctx* ctx, DeviceState& ds, const int8_t* xq, const float* xs, const int32_t* xsum,
-                         int64_t M, int64_t in, uint8_t* img, int zp);
+                         int64_t M, int64_t in, uint8_t* img, int zp, int bits);
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
-                            int32_t* xsum, int64_t M, int64_t in, int act_dtype = RSTQ_F32, uint8_t* img = nullptr, int zp = 0);
+                            int32_t* xsum, int64_t M, int64_t in, int act_dtype = RSTQ_F32, uint8_t* img = nullptr, int zp = 0,
+                            int bits = 8);
 // Exchange fused into the tail of the decode kernel (layout of a region: see tp.cu).  The
 // kernel writes its results into slot `rank` of every rank's stage instead of y, signals, waits
 // (time-bounded) for the other ranks and lays the slots side by side (sum = 0) or adds them in
