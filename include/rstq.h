@@ -119,15 +119,19 @@ typedef struct rstq_event rstq_event;
                                      thread) instead of 128-token ones: 0 (default) = where the grid then needs
                                      fewer cycles over its waves of thread blocks, 1 = never, 2 = always,
                                      3 = as 0 but never two thread blocks per tile (each half of K) */
-#define RSTQ_TUNE_ACT_RING 14     /* MODE_A8 decode at 2 <= M <= 16, how the activations share shared memory with the
-                                     weight ring: 0 (default) = the plan that keeps most weight bytes on their way,
-                                     all tokens in one launch; 1 = all of K resident beside 64-unit chunks (tokens
-                                     that do not fit go to further launches, each streaming the weights again);
-                                     2 / 3 = every ring stage carries its own slice of the activation image
-                                     (64- / 32-unit chunks), so shared memory does not grow with K and the
-                                     image is read from L2 once per 32-row group; 4 = resident, 32-unit chunks.
-                                     Results are bit-identical in every setting */
-#define RSTQ_TUNE_ACT_IMAGE 10    /* 1 (default) = rstq_qmatmul in MODE_A8 at 2 <= M <= 16: the activation quantizer
+#define RSTQ_TUNE_ACT_RING 14     /* MODE_A8 decode launches of 2 .. 16 tokens, how the activations share shared memory
+                                     with the weight ring: 0 (default) = every ring stage carries its own slice of
+                                     the activation image wherever that image exists (always in rstq_qmatmul; in
+                                     rstq_qmatmul_prequant it is built when the resident form would need more
+                                     launches or leave a shallower ring), so shared memory does not grow with K and
+                                     the image is read from L2 once per 32-row group; 1 = all of K resident beside
+                                     the ring (tokens that do not fit go to further launches, each streaming the
+                                     weights again); 2 = as 0, also where the resident form fits; 3 = the slices
+                                     ride 32-unit chunks; 4 = resident, 32-unit chunks (3, 4: measured slower).
+                                     Every token's result is the same bit for bit in every setting, except that a
+                                     last launch of ONE token (setting 1 or 4) adds a row's blocks up in the M = 1
+                                     kernel's order */
+#define RSTQ_TUNE_ACT_IMAGE 10    /* 1 (default) = rstq_qmatmul in MODE_A8 at 2 <= M < 64: the activation quantizer
                                      also writes the codes, scales and sums in the order the decode kernel
                                      keeps them in shared memory, and that kernel's copy thread brings them
                                      in with bulk copies beside the weight stream; 0 = the kernel's warps
@@ -246,8 +250,8 @@ RSTQ_API int32_t rstq_quant_act_q8k(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rs
  *   give the result of the same values passed as f32.  At M = 1 (in <= 12288) the quantizer runs
  *   inside the decode kernel (same codes, scales and sums, bit for bit).  Up to M = 63 the block dots
  *   are exact integers and the result agrees with the reference formula to <= 2e-6 of max|y|; from
- *   M = 64 -- and from M = 9 when in > 16384, where eight tokens of codes no longer fit beside the
- *   weight ring -- the exact codes and scales feed the fp16 tensor-core path instead: <= 1e-3 of
+ *   M = 64 -- and from M = 17 when in > 16384, where the decode kernel would need a launch per 16
+ *   tokens of rows that long -- the exact codes and scales feed the fp16 tensor-core path instead: <= 1e-3 of
  *   max|y| (measured ~4e-5), no longer the exact integer dots.  RSTQ_TUNE_GEMM_MIN_M raised above
  *   M keeps the exact path at any size.
  *   MODE_F multiplies the float activations directly -- qlinear-q8
