@@ -846,7 +846,7 @@ def gemm_detail(ctx, info, M=512, K=4096, N=4096):
 
 def c5_detail(ctx, info, steps=3):
     """BASELINE configs[4] on one GPU: int4 W 8192x28672 and 28672x8192 (random codes, scales of the
-    N(0, 0.015) magnitude), bf16 activations N(0, 1), M in {1, 16, 64, 256}; f32 output for M <= 16, bf16
+    N(0, 0.015) magnitude), bf16 activations N(0, 1), M in {1, 4, 8, 16, 64, 256}; f32 output for M <= 16, bf16
     above (the prefill path): MODE_F, and for M <= 16 MODE_A8 as well (`_a8_`).  Distinct weight copies, more than
     L2 in total, replayed from one graph."""
     from raster_b200 import _lib as L
@@ -859,7 +859,7 @@ def c5_detail(ctx, info, steps=3):
         first = ctx.bind_weight(codes, scales, N, K, L.FMT_Q4_0, L.LAYOUT_ROWMAJOR)
         R = max(2, -(-int(1.2 * info["l2_bytes"]) // first.stream_bytes))
         ws = [first] + [first.clone() for _ in range(R - 1)]
-        for M in (1, 16, 64, 256):
+        for M in (1, 4, 8, 16, 64, 256):
             x = ctx.array_to_buffer(synth.to_bf16_bits(synth.normal(90 + M, M * K)))
             odt = L.F32 if M <= 16 else L.BF16
             y = ctx.make_buffer(M * N, np.float32 if M <= 16 else np.uint16)
