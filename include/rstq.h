@@ -256,9 +256,10 @@ RSTQ_API int32_t rstq_quant_act_q8k(rstq_ctx* ctx, rstq_buf* x, rstq_buf* xq, rs
  *   M keeps the exact path at any size.
  *   MODE_F multiplies the float activations directly -- qlinear-q8
  *   (src/raster/quant/train.clj:77-108) and the prefill GEMM: decode kernel (f32-grade, <= 2e-5)
- *   up to M = 16, tensor-core path (<= 1e-3) from M = 17, and already from M = 2 when the matrix is
- *   larger than 4 MB and the decode kernel would have to stream it twice or more because M tokens
- *   of activations do not fit in shared memory.
+ *   up to M = 16, tensor-core path (<= 1e-3) from M = 17, and already from M = 9 (f32 activations;
+ *   from M = 2 with RSTQ_TUNE_ACT_RING = 1) when the matrix is larger than 4 MB and the decode kernel
+ *   would have to stream it twice or more: activations that do not fit in shared memory for all of K
+ *   ride the weight ring, up to 16 columns (bf16 tokens, or two exact bf16 terms per f32 token).
  * rstq_qmatmul_prequant: the kernel-level call of the reference,
  *   (xq xs xsum wqi wsi y in out ...) of qmatmul-q4-x8! / qmatmul-q8-x8!
  *   (src/raster/quant/kernels.clj:216-247, :308-333), and with xsum == NULL and a

@@ -171,6 +171,12 @@ static int32_t run_a8(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const flo
 static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int64_t M,
                      int act_dtype, int out_dtype, const TpFuse* tp = nullptr) {
     GemvFArgs a{w->data, x, y, M, w->in, w->out, w->bits, w->zp, act_dtype, out_dtype, tp};
+    DeviceState& ds = ctx->devs[w->dev];
+    if (M > 1 || act_dtype == RSTQ_F32) {   // room for the staged activations to ride the weight ring; without it: fewer tokens per launch
+        const int64_t need = gemv_f_image_bytes(w->in);
+        if (ds.f_image_bytes >= need || dev_reserve(ds, &ds.f_image, &ds.f_image_bytes, need) == RSTQ_OK)
+            a.img_scratch = (uint8_t*)ds.f_image;
+    }
     a.next = note_decode_launch(ctx, ctx->devs[w->dev], w);
     return launch_gemv_f(ctx, ctx->devs[w->dev], a);
 }
@@ -502,6 +508,7 @@ int32_t rstq_shutdown(rstq_ctx* ctx) {
         if (ds.gemm_scratch) cudaFree(ds.gemm_scratch);
         if (ds.attn_scratch) cudaFree(ds.attn_scratch);
         if (ds.kq_scratch) cudaFree(ds.kq_scratch);
+        if (ds.f_image) cudaFree(ds.f_image);
         if (ds.partials) cudaFree(ds.partials);
         if (ds.counters) cudaFree(ds.counters);
         if (ds.status) cudaFree(ds.status);

@@ -109,11 +109,12 @@ struct StreamParams {
     // thread copies it in with two bulk copies under a barrier of its own.  Null: stage in the kernel.
     const uint8_t* img;
     uint32_t img_b_bytes, img_z_bytes, img_z_off;
-    // MODE_A8, M > 1, `ring` set: nothing of the image is kept for the whole launch; every ring stage holds,
+    // M > 1 (in mode F also one token of f32), `ring` set: nothing of the image is kept for the whole launch; every ring stage holds,
     // behind its weight chunk, the image's slice for the chunk's K blocks (fragments at act_off, records at
     // act2_off, both counted from the stage), copied by the producer with the chunk.  Shared memory then
     // does not grow with K, at the price of reading the image (from L2) once per 32-row group.
     int ring;
+    uint32_t slice1, slice2;   // ring: bytes per K block of the image's two arrays (mode F: one array)
     int cu;                 // units per chunk (M > 1: a multiple of the consumer warps, <= chunk_units_of)
     uint32_t stage_bytes;   // distance between ring stages
     int kq;   // Q4_K units (zero point 0): the staged constant of a block is t = xs * code sum, which the minima multiply
@@ -389,6 +390,27 @@ __device__ __forceinline__ void stage_a8_quant(const StreamParams& p, uint8_t* s
 
 // F: sx [nb][2 halves][C][4 tig] entries of 8 bytes = bf16 (e0, e2, e1, e3) of the four
 // elements 16h + 4tig + 0..3 of column c = m*T + t (term t of token m), C = M*T.
+// the entry of elements e .. e + 3 of x (f32 or bf16), term t
+__device__ __forceinline__ uint2 f_entry(const void* x, int act_dtype, int64_t e, int t) {
+    __nv_bfloat16 q[4];
+    if (act_dtype == RSTQ_BF16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(x) + e);
+        q[0] = __ushort_as_bfloat16((unsigned short)(raw.x & 0xFFFF));
+        q[1] = __ushort_as_bfloat16((unsigned short)(raw.x >> 16));
+        q[2] = __ushort_as_bfloat16((unsigned short)(raw.y & 0xFFFF));
+        q[3] = __ushort_as_bfloat16((unsigned short)(raw.y >> 16));
+    } else {
+        const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + e);
+        q[0] = bf16_term(f.x, t);
+        q[1] = bf16_term(f.y, t);
+        q[2] = bf16_term(f.z, t);
+        q[3] = bf16_term(f.w, t);
+    }
+    uint2 v;
+    v.x = (uint32_t)__bfloat16_as_ushort(q[0]) | ((uint32_t)__bfloat16_as_ushort(q[2]) << 16);
+    v.y = (uint32_t)__bfloat16_as_ushort(q[1]) | ((uint32_t)__bfloat16_as_ushort(q[3]) << 16);
+    return v;
+}
 __device__ __forceinline__ void stage_f(const StreamParams& p, uint8_t* smem, int tid) {
     uint2* sx = reinterpret_cast<uint2*>(smem + p.act_off);
     const int C = p.M * p.T, nb = p.nb;
@@ -397,27 +419,28 @@ __device__ __forceinline__ void stage_f(const StreamParams& p, uint8_t* smem, in
         for (int i = tid; i < nb * 8; i += kConsumers) {
             const int tg = i & 3, h = (i >> 2) & 1, b = i >> 3;
             const int64_t e = (int64_t)m * p.in + b * 32 + h * 16 + tg * 4;
-            __nv_bfloat16 q[4];
-            if (p.act_dtype == RSTQ_BF16) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(
-                    reinterpret_cast<const __nv_bfloat16*>(p.x) + e);
-                q[0] = __ushort_as_bfloat16((unsigned short)(raw.x & 0xFFFF));
-                q[1] = __ushort_as_bfloat16((unsigned short)(raw.x >> 16));
-                q[2] = __ushort_as_bfloat16((unsigned short)(raw.y & 0xFFFF));
-                q[3] = __ushort_as_bfloat16((unsigned short)(raw.y >> 16));
-            } else {
-                const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + e);
-                q[0] = bf16_term(f.x, t);
-                q[1] = bf16_term(f.y, t);
-                q[2] = bf16_term(f.z, t);
-                q[3] = bf16_term(f.w, t);
-            }
-            uint2 v;
-            v.x = (uint32_t)__bfloat16_as_ushort(q[0]) | ((uint32_t)__bfloat16_as_ushort(q[2]) << 16);
-            v.y = (uint32_t)__bfloat16_as_ushort(q[1]) | ((uint32_t)__bfloat16_as_ushort(q[3]) << 16);
-            sx[((b * 2 + h) * C + c) * 4 + tg] = v;
+            sx[((b * 2 + h) * C + c) * 4 + tg] = f_entry(p.x, p.act_dtype, e, t);
         }
         if (++t == p.T) { t = 0; ++m; }
+    }
+}
+// The same array in global memory, for launches whose activations ride the weight ring (StreamParams::ring):
+// block-major, so the entries of a chunk's K blocks are one contiguous slice.
+__global__ void __launch_bounds__(256)
+act_image_f_kernel(const void* __restrict__ x, uint2* __restrict__ img, int M, int T, int nb, int64_t in, int act_dtype) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int C = M * T;
+    const int64_t n = (int64_t)nb * 8 * C, step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < n; o += step) {
+        const int tg = (int)(o & 3);
+        const int64_t r = o >> 2;                 // (b * 2 + h) * C + c
+        const int c = (int)(r % C);
+        const int64_t bh = r / C;
+        const int h = (int)(bh & 1);
+        const int64_t b = bh >> 1;
+        const int m = c / T, t = c - m * T;
+        img[o] = f_entry(x, act_dtype, (int64_t)m * in + b * 32 + h * 16 + tg * 4, t);
     }
 }
 
@@ -694,7 +717,7 @@ __device__ __forceinline__ void unit_a8(const SUnit<BITS>& u, const uint8_t* act
 }
 
 template <int BITS, int NT>
-__device__ __forceinline__ void unit_f(const SUnit<BITS>& u, const uint8_t* smem,
+__device__ __forceinline__ void unit_f(const SUnit<BITS>& u, const uint8_t* actB,
                                        const StreamParams& p, int b, int gid, int tig,
                                        float (&acc)[NT][4][2]) {
     // fr[h][i][j]: half h, row gid + 8i, j = 0 -> elements (+0, +2), j = 1 -> (+1, +3)
@@ -733,7 +756,7 @@ __device__ __forceinline__ void unit_f(const SUnit<BITS>& u, const uint8_t* smem
     }
     const float sc[4] = {u.sc.x, u.sc.y, u.sc.z, u.sc.w};
     const int C = p.M * p.T;
-    const uint2* xb = reinterpret_cast<const uint2*>(smem + p.act_off) + b * 2 * C * 4;
+    const uint2* xb = reinterpret_cast<const uint2*>(actB) + b * 2 * C * 4;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         int col = nt * 8 + gid;
@@ -877,8 +900,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             // Ring of activations: a stage's slice of the image depends on the kernel before this one, its
             // weights do not.  The first NS chunks of weights leave at once, registered on their barriers
             // without an arrival; their slices follow after the wait, with the arrival.
-            const bool ring = MODE == MODE_A8 && !ONECOL && p.ring;
-            const int Mz8 = ((p.M + 1) & ~1) * kActRecBytes, M32 = p.M * 32;   // bytes of a block's records / fragments
+            const bool ring = !ONECOL && p.ring;
+            const int Mz8 = (int)p.slice2, M32 = (int)p.slice1;   // bytes of a block's records / fragments (entries in mode F, no records)
             const int cu = ONECOL ? kChunkUnits : p.cu;
             const uint32_t stage_bytes = ONECOL ? (uint32_t)CHUNK_BYTES : p.stage_bytes;
             int pend_b[RSTQ_NSMAX], pend_n[RSTQ_NSMAX], npend = 0;
@@ -889,7 +912,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 const uint32_t dst = smem_u32(smem) + (uint32_t)slot * stage_bytes;
                 mbar_expect_tx(full0 + 8 * slot, more + nb1 + nb2);
                 bulk_copy_g2s(dst + p.act_off, p.img + (int64_t)bb * M32, nb1, full0 + 8 * slot);
-                bulk_copy_g2s(dst + p.act2_off, p.img + p.img_z_off + (int64_t)bb * Mz8, nb2, full0 + 8 * slot);
+                if (nb2) bulk_copy_g2s(dst + p.act2_off, p.img + p.img_z_off + (int64_t)bb * Mz8, nb2, full0 + 8 * slot);
             };
             auto slices_of_first = [&]() {
                 asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -1015,7 +1038,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         } else {
             stage_a8<ONECOL, BITS>(p, smem, tid);
         }
-    } else {
+    } else if (!p.ring) {
         stage_f(p, smem, tid);
     }
     consumer_bar();
@@ -1306,7 +1329,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         const uint32_t stage_bytes = p.stage_bytes;
         // activations: staged for all of K (block index = the block in the group), or the stage's own slice
         // (block index = the unit's place in the chunk)
-        const bool ring = MODE == MODE_A8 && p.ring;
+        const bool ring = p.ring;
         const uint8_t* actB = smem + p.act_off;
         const uint8_t* actZ = smem + p.act2_off;
         zero_acc();
@@ -1330,7 +1353,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 #pragma unroll
                     for (int j = 0; j < kUPW; ++j) {
                         if (MODE == MODE_A8) unit_a8<BITS, NT, UK>(un[j], actB, actZ, p, b0 + j * kCW, gid, tig, acc);
-                        else unit_f<BITS, NT>(un[j], smem, p, b + warp + j * kCW, gid, tig, acc);
+                        else unit_f<BITS, NT>(un[j], actB, p, b0 + j * kCW, gid, tig, acc);
                     }
                 } else if (kUPW == 4 && n == kChunkUnits / 2 && NT == 1 && MODE == MODE_A8) {
                     SUnit<BITS> un[2];   // a full chunk of the half-size ring
@@ -1343,7 +1366,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                         SUnit<BITS> un;
                         lds_unit<BITS, UK>(un, unit0 + j * kCW * UNIT, lane);
                         if (MODE == MODE_A8) unit_a8<BITS, NT, UK>(un, actB, actZ, p, b0 + j * kCW, gid, tig, acc);
-                        else unit_f<BITS, NT>(un, smem, p, b + warp + j * kCW, gid, tig, acc);
+                        else unit_f<BITS, NT>(un, actB, p, b0 + j * kCW, gid, tig, acc);
                     }
                 }
             }
@@ -1739,6 +1762,8 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         if (M != want) img = nullptr;   // fewer tokens than the image was laid out for
         RSTQ_REQUIRE(!pl.ring || img, RSTQ_E_STATE, "a ring of activations without their image");
         if (img) {
+            p.slice1 = (uint32_t)M * 32u;
+            p.slice2 = (uint32_t)((M + 1) & ~1) * kActRecBytes;
             p.img = img;
             p.img_b_bytes = (uint32_t)(nb * M * 32);
             p.img_z_bytes = (uint32_t)(nb * ((M + 1) & ~1) * kActRecBytes);
@@ -1783,26 +1808,49 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
     return RSTQ_OK;
 }
 
-// How many launches launch_gemv_f would make for M tokens (each streams all the weights again).
-int gemv_f_pieces(const DeviceState& ds, int bits, int64_t out, int64_t in, int64_t M, int act_dtype) {
-    const int64_t nb = in / 32, groups = (out + 31) / 32;
-    int max_terms = 3;
-    auto terms = [&](int m) { return act_dtype == RSTQ_F32 ? ((3 * m <= 8 && max_terms == 3) ? 3 : 2) : 1; };
+// Mode F, one launch: how many of `want` tokens it takes and with which plan.  f32 activations are expanded
+// into exact bf16 terms: three while they fit one 8-column tile, else two (16 significant bits); a very long
+// row may force two.  When shared memory cannot keep all of K for `want` tokens beside the ring, the staged
+// array is built in global memory by a kernel of its own and rides the ring in slices (up to two column
+// tiles: the slice of a chunk grows with the columns); `ring` off: fewer tokens per launch instead.
+static int plan_f_piece(const DeviceState& ds, int bits, int64_t groups, int64_t nb, int want, int act_dtype,
+                        int* max_terms, bool ring_ok, StreamPlan* pl) {
+    auto terms = [&](int m) { return act_dtype == RSTQ_F32 ? ((3 * m <= 8 && *max_terms == 3) ? 3 : 2) : 1; };
     auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
         const int C = m * terms(m);
         *NT = C <= 8 ? 1 : (C <= 16 ? 2 : 4);
         *a1 = nb * 2 * C * 32;
         *a2 = 0;
     };
+    int m = fit_tokens(ds, bits, groups, nb, want, bytes, pl);
+    if (m < 1 && *max_terms == 3) {
+        *max_terms = 2;  // a very long row: two bf16 terms (16 significant bits) per element
+        m = fit_tokens(ds, bits, groups, nb, want, bytes, pl);
+    }
+    if (m < want && ring_ok && ds.act_ring != 1 && ds.act_ring != 4) {
+        const int C = want * terms(want);
+        if (C <= 16) {
+            const int NT = C <= 8 ? 1 : 2, full = chunk_units_of(bits);
+            StreamPlan r = plan_stream(ds, bits, NT, groups, nb, 2 * C * 32, 0, false, full, true);
+            if (!r.fits || ds.act_ring == 3) r = plan_stream(ds, bits, NT, groups, nb, 2 * C * 32, 0, false, full / 2, true);
+            if (r.fits) {
+                *pl = r;
+                m = want;
+            }
+        }
+    }
+    return m;
+}
+
+// How many launches launch_gemv_f would make for M tokens (each streams all the weights again).
+int gemv_f_pieces(const DeviceState& ds, int bits, int64_t out, int64_t in, int64_t M, int act_dtype) {
+    const int64_t nb = in / 32, groups = (out + 31) / 32;
+    int max_terms = 3;
     int pieces = 0;
     for (int64_t m0 = 0; m0 < M;) {
         const int want = (int)(M - m0 < kGemvMaxM ? M - m0 : kGemvMaxM);
         StreamPlan pl;
-        int m = fit_tokens(ds, bits, groups, nb, want, bytes, &pl);
-        if (m < 1 && max_terms == 3) {
-            max_terms = 2;
-            m = fit_tokens(ds, bits, groups, nb, want, bytes, &pl);
-        }
+        const int m = plan_f_piece(ds, bits, groups, nb, want, act_dtype, &max_terms, true, &pl);
         if (m < 1) return 1 << 20;
         m0 += m;
         ++pieces;
@@ -1810,37 +1858,25 @@ int gemv_f_pieces(const DeviceState& ds, int bits, int64_t out, int64_t in, int6
     return pieces;
 }
 
+// bytes of the staged array of mode F for one launch of up to kGemvMaxM tokens riding the ring (two column tiles)
+int64_t gemv_f_image_bytes(int64_t in) { return (in / 32) * 2 * 16 * 32; }
+
 int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
     RSTQ_REQUIRE(a.M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)a.M);
     const int64_t nb = a.in / 32, groups = (a.out + 31) / 32;
     RSTQ_REQUIRE(nb < (1 << 24) && groups * nb < (1ll << 40), RSTQ_E_LIMIT, "matrix too large");
-    // f32 activations are expanded into exact bf16 terms: three while they fit one
-    // 8-column tile, else two (16 significant bits).
     int max_terms = 3;
-    auto terms = [&](int m) {
-        return a.act_dtype == RSTQ_F32 ? ((3 * m <= 8 && max_terms == 3) ? 3 : 2) : 1;
-    };
-    auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
-        const int C = m * terms(m);
-        *NT = C <= 8 ? 1 : (C <= 16 ? 2 : 4);
-        *a1 = nb * 2 * C * 32;
-        *a2 = 0;
-    };
     const int64_t xe = a.act_dtype == RSTQ_F32 ? 4 : 2, ye = a.out_dtype == RSTQ_F32 ? 4 : 2;
     for (int64_t m0 = 0; m0 < a.M;) {
         const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
         StreamPlan pl;
-        int M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
-        if (M < 1 && max_terms == 3) {
-            max_terms = 2;  // a very long row: two bf16 terms (16 significant bits) per element
-            M = fit_tokens(ds, a.bits, groups, nb, want, bytes, &pl);
-        }
+        const int M = plan_f_piece(ds, a.bits, groups, nb, want, a.act_dtype, &max_terms, a.img_scratch != nullptr, &pl);
         RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
                      (long long)a.in);
         if (a.tp && (M < a.M || a.out % 4 != 0 || a.out_dtype != RSTQ_F32)) return kNotFused;
         int32_t rc = stream_scratch_ok(ds, groups, pl.G, M);
         if (rc != RSTQ_OK) return rc;
-        const int T = terms(M), C = M * T;
+        const int T = a.act_dtype == RSTQ_F32 ? ((3 * M <= 8 && max_terms == 3) ? 3 : 2) : 1, C = M * T;
         const int NT = C <= 8 ? 1 : (C <= 16 ? 2 : 4);
         StreamParams p{};
         fill_common(p, ds, pl, a.in, a.out, M, nb, a.zp, a.bits);
@@ -1848,6 +1884,28 @@ int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a) {
         p.x = (const char*)a.x + m0 * a.in * xe;
         p.y = (char*)a.y + m0 * a.out * ye;
         p.T = T; p.act_dtype = a.act_dtype; p.out_dtype = a.out_dtype;
+        if (pl.ring) {
+            // the staged array of this launch's tokens, built by a kernel of its own; the decode kernel's copy
+            // thread waits for that grid before the first slice, as it does for the quantizer in mode A8
+            const int64_t n = nb * 8 * C;
+            int64_t ctas = (n + 255) / 256;
+            if (ctas > (int64_t)ds.sm_count * 8) ctas = (int64_t)ds.sm_count * 8;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)ctas);
+            cfg.blockDim = dim3(256);
+            cfg.stream = ds.stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = ds.pdl ? 1 : 0;
+            RSTQ_CUDA(cudaLaunchKernelEx(&cfg, act_image_f_kernel, p.x, reinterpret_cast<uint2*>(a.img_scratch), M, T,
+                                         (int)nb, a.in, a.act_dtype));
+            ctx->launches++;
+            p.img = a.img_scratch;
+            p.slice1 = (uint32_t)(2 * C * 32);
+            p.slice2 = 0;
+        }
         if (a.tp) p.tp = *a.tp;
         if (m0 + M >= a.M) fill_next(p, ds, a.next);   // the last piece of this call: what comes next is another weight
         cudaError_t le = cudaSuccess;

@@ -96,6 +96,8 @@ struct DeviceState {
     int64_t gemm_scratch_bytes = 0;
     void* kq_scratch = nullptr;    // Q6_K: the twin-row results before they are added in pairs
     int64_t kq_scratch_bytes = 0;
+    void* f_image = nullptr;       // mode F: the staged activations of a decode launch that ride the weight ring
+    int64_t f_image_bytes = 0;
     void* attn_scratch = nullptr;  // decode attention: arrival counters + per-slice softmax states
     int64_t attn_scratch_bytes = 0;
     void* pinned = nullptr;        // host staging for the host-array entry points
@@ -303,11 +305,14 @@ struct GemvFArgs {
     int act_dtype, out_dtype;
     const TpFuse* tp = nullptr;
     NextWeight next;
+    uint8_t* img_scratch = nullptr;   // gemv_f_image_bytes(in) of room for the staged activations of a launch whose
+                                      // tokens do not fit in shared memory for all of K (they then ride the weight ring)
 };
 // gemv_stream.cu.  Any M >= 1: the launchers cut M into pieces the kernel takes.
 int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a);
 int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a);
 int gemv_f_pieces(const DeviceState& ds, int bits, int64_t out, int64_t in, int64_t M, int act_dtype);
+int64_t gemv_f_image_bytes(int64_t in);
 int32_t gemv_configure(DeviceState& ds);  // shared-memory attributes, once per device
 // gemm_tc.cu
 // gemm_tc.cu: token-tile width (32 / 64 / 128 / 256) and whether two CTAs share a tile, for a device of sm_count SMs

@@ -223,6 +223,56 @@ def test_activations_riding_the_ring_give_the_same_bits(ctx, bits, plan, M, out,
 
 
 @pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("act", ["f32", "bf16"])
+@pytest.mark.parametrize("M,out,in_", [(4, 300, 11008), (8, 200, 11008), (3, 64, 28672), (16, 64, 8192), (2, 96, 28672),
+                                       (8, 4096, 4096), (5, 520, 2048)])
+def test_mode_f_activations_ride_the_ring_when_they_do_not_fit(ctx, bits, act, M, out, in_):
+    """MODE_F on the decode kernel (qlinear-q8: y = dequant(W) . x): tokens whose staged activations (for f32 two
+    or three exact bf16 terms each) do not fit in shared memory for all of K are staged in global memory by a
+    kernel of its own and ride the weight ring in slices, one launch for all of them; with RSTQ_TUNE_ACT_RING = 1
+    they go to further launches instead.  bf16 activations: the same products in the same order, bit for bit.
+    f32: a launch of more tokens may use two terms where a launch of one uses three, so both are held to the
+    oracle's bound."""
+    fmt_desc, fmt, ofmt = FMT[bits]
+    _, wq, ws = make_weight(out, in_, bits, seed=out + in_ + M + 2)
+    x = synth.normal(out + 3 * in_ + M, M * in_)
+    if act == "bf16":
+        xb = synth.to_bf16_bits(x)
+        x = synth.from_bf16_bits(xb)
+        bx, adt = ctx.array_to_buffer(xb), L.BF16
+    else:
+        bx, adt = ctx.array_to_buffer(x), L.F32
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    by = ctx.make_buffer(M * out, np.float32)
+    ys, launches = {}, {}
+    try:
+        ctx.tune(L.TUNE_GEMM_MIN_M, 64)
+        for ring in (1, 0):
+            ctx.tune(L.TUNE_ACT_RING, ring)
+            for rep in range(2):
+                by.fill_bytes(0xFF)
+                n0 = ctx.launch_count()
+                ctx.qmatmul(w, bx, by, M, adt, L.F32, L.MODE_F)
+                ctx.sync()
+                launches[ring] = ctx.launch_count() - n0
+            ys[ring] = by.download()
+    finally:
+        ctx.tune(L.TUNE_ACT_RING, 0)
+        ctx.tune(L.TUNE_GEMM_MIN_M, 17)
+    ref = orc.matmul_dq_f64(wq, ws, ofmt, x, M, in_, out)
+    tol = TOL_A8 if act == "bf16" else TOL_F
+    assert relerr(ys[0], ref) <= tol and relerr(ys[1], ref) <= tol
+    assert launches[0] <= launches[1]
+    if act == "bf16" or M <= 8:      # up to two column tiles ride the ring (16 f32 tokens are 32 columns of terms)
+        assert launches[0] <= 2, launches
+    if act == "bf16":
+        assert np.array_equal(ys[0].view(np.uint32), ys[1].view(np.uint32))
+    for b in (bx, by):
+        b.free()
+    w.free()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("M", [1, 3, 8, 16])
 @pytest.mark.parametrize("out,in_", [(11008, 4096), (4096, 11008), (28672, 8192), (64, 28672), (200, 96)])
 def test_equal_range_split_hands_partial_sums_over_correctly(ctx, bits, M, out, in_):
