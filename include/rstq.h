@@ -130,7 +130,10 @@ typedef struct rstq_event rstq_event;
                                      ride 32-unit chunks; 4 = resident, 32-unit chunks (3, 4: measured slower).
                                      Every token's result is the same bit for bit in every setting, except that a
                                      last launch of ONE token (setting 1 or 4) adds a row's blocks up in the M = 1
-                                     kernel's order */
+                                     kernel's order.  MODE_F decode launches follow the same key: 0 = staged
+                                     activations that do not fit in shared memory for all of K ride the ring (up
+                                     to 16 columns: bf16 tokens, or two bf16 terms per f32 token), 1 / 4 = further
+                                     launches (or the tensor-core route) instead */
 #define RSTQ_TUNE_ACT_IMAGE 10    /* 1 (default) = rstq_qmatmul in MODE_A8 at 2 <= M < 64: the activation quantizer
                                      also writes the codes, scales and sums in the order the decode kernel
                                      keeps them in shared memory, and that kernel's copy thread brings them
