@@ -1621,10 +1621,11 @@ static void fill_common(StreamParams& p, const DeviceState& ds, const StreamPlan
     p.M = M; p.nb = (int)nb; p.G = pl.G; p.zp = zp; p.NS = pl.NS;
     // L2 requests ahead of the ring: by default 64 KB for matrices of 16 .. 64 MB (a CTA's range is then a
     // little longer than its ring: the chunks behind the ring would otherwise be requested only when the
-    // consumers free slots); measured: smaller and much larger matrices lose a little with any distance
+    // consumers free slots); measured: smaller and, at one token, much larger matrices lose a little with any
+    // distance; above one token (a shallower ring beside the activations) 64 KB gains 1 - 5 % at 147 MB too
     const int64_t wbytes = p.U * unit_bytes(bits_of_unit);
     p.pf_ahead = ds.gemv_prefetch_kb >= 0 ? ds.gemv_prefetch_kb << 10
-                                          : (wbytes >= (16ll << 20) && wbytes <= (64ll << 20) ? 64ll << 10 : 0);
+                                          : (wbytes >= (16ll << 20) && (M > 1 || wbytes <= (64ll << 20)) ? 64ll << 10 : 0);
     p.probe = ds.gemv_probe;
     p.act_off = pl.act_off; p.act2_off = pl.act2_off; p.red_off = pl.red_off; p.bar_off = pl.bar_off;
     p.cu = pl.cu; p.ring = pl.ring; p.stage_bytes = pl.stage_bytes;
