@@ -122,8 +122,8 @@ typedef struct rstq_event rstq_event;
 #define RSTQ_TUNE_ACT_RING 14     /* MODE_A8 decode launches of 2 .. 16 tokens, how the activations share shared memory
                                      with the weight ring: 0 (default) = every ring stage carries its own slice of
                                      the activation image wherever that image exists (always in rstq_qmatmul; in
-                                     rstq_qmatmul_prequant it is built when the resident form would need more
-                                     launches or leave a shallower ring), so shared memory does not grow with K and
+                                     rstq_qmatmul_prequant and for Q4_K / Q6_K weights it is built when the
+                                     resident form would need more launches or leave a shallower ring), so shared memory does not grow with K and
                                      the image is read from L2 once per 32-row group; 1 = all of K resident beside
                                      the ring (tokens that do not fit go to further launches, each streaming the
                                      weights again); 2 = as 0, also where the resident form fits; 3 = the slices

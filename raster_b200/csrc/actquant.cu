@@ -79,11 +79,15 @@ quant_act_i8_kernel(const void* __restrict__ xv, int8_t* __restrict__ xq, float*
 // code sums [M][nb].  Eight lanes per (token, block), one code word each.
 __global__ void __launch_bounds__(256)
 act_image_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs, const int32_t* __restrict__ xsum,
-                 int64_t nblocks, uint8_t* __restrict__ img, int M, int nb, int zp, int four_bit) {
+                 int64_t nblocks, uint8_t* __restrict__ img, int M, int nb, int zp, int four_bit, int uk) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int Mz = (M + 1) & ~1;
     uint8_t* recs = img + (((int64_t)nb * M * 32 + 127) & ~127ll);
+    // K-quant units keep their own records: Q4_K (uk 1) {xs, xs * code sum} per (block, token), Q6_K (uk 2)
+    // {xs, zp * sum of elements 0..15, zp * sum of 16..31, 0} with the sums per 16 elements in xsum
+    int2* z2 = reinterpret_cast<int2*>(recs);
+    int4* z4 = reinterpret_cast<int4*>(recs);
     const int64_t n = nblocks * 8, step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += step) {
         const int64_t blk = i >> 3;
@@ -91,13 +95,21 @@ act_image_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs, co
         const int c = (int)(blk / nb), b = (int)(blk - (int64_t)c * nb);
         reinterpret_cast<uint32_t*>(img)[((int64_t)(b * M + c) * 4 + (j & 3)) * 2 + (j >> 2)] =
             reinterpret_cast<const uint32_t*>(xq)[i];
-        if (j == 0) put_act_record(recs, b, Mz, c, xs[blk], zp * xsum[blk], four_bit);
-        if (j == 1 && c == M - 1 && Mz > M) put_act_record(recs, b, Mz, M, 0.f, 0, four_bit);
+        if (uk == 1) {
+            if (j == 0) z2[(int64_t)b * Mz + c] = make_int2(__float_as_int(xs[blk]), __float_as_int(xs[blk] * (float)xsum[blk]));
+            if (j == 1 && c == M - 1 && Mz > M) z2[(int64_t)b * Mz + M] = make_int2(0, 0);
+        } else if (uk == 2) {
+            if (j == 0) z4[(int64_t)b * Mz + c] = make_int4(__float_as_int(xs[blk]), zp * xsum[2 * blk], zp * xsum[2 * blk + 1], 0);
+            if (j == 1 && c == M - 1 && Mz > M) z4[(int64_t)b * Mz + M] = make_int4(0, 0, 0, 0);
+        } else {
+            if (j == 0) put_act_record(recs, b, Mz, c, xs[blk], zp * xsum[blk], four_bit);
+            if (j == 1 && c == M - 1 && Mz > M) put_act_record(recs, b, Mz, M, 0.f, 0, four_bit);
+        }
     }
 }
 
 int32_t launch_act_image(rstq_ctx* ctx, DeviceState& ds, const int8_t* xq, const float* xs, const int32_t* xsum,
-                         int64_t M, int64_t in, uint8_t* img, int zp, int bits) {
+                         int64_t M, int64_t in, uint8_t* img, int zp, int bits, int uk) {
     const int64_t nblocks = M * (in / 32);
     int64_t ctas = (nblocks * 8 + 255) / 256;
     const int64_t cap = (int64_t)ds.sm_count * 8;
@@ -113,7 +125,7 @@ int32_t launch_act_image(rstq_ctx* ctx, DeviceState& ds, const int8_t* xq, const
     cfg.attrs = attr;
     cfg.numAttrs = ds.pdl ? 1 : 0;
     RSTQ_CUDA(cudaLaunchKernelEx(&cfg, act_image_kernel, xq, xs, xsum, nblocks, img, (int)M, (int)(in / 32), zp,
-                                 (int)(bits == 4)));
+                                 (int)(bits == 4), uk));
     ctx->launches++;
     RSTQ_CUDA(cudaGetLastError());
     return RSTQ_OK;

@@ -183,8 +183,8 @@ static int32_t run_f(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int6
 
 // Q4_K: decode kernel over the sub-block scales (zero point 0), then the min term added to y.
 static int32_t run_q4k(rstq_ctx* ctx, rstq_weight* w, const int8_t* xq, const float* xs32, const int32_t* bsums,
-                       float* y, int64_t M) {
-    int32_t rc = run_a8(ctx, w, xq, xs32, bsums, y, M);
+                       float* y, int64_t M, uint8_t* img_scratch = nullptr) {
+    int32_t rc = run_a8(ctx, w, xq, xs32, bsums, y, M, nullptr, nullptr, w->kq ? img_scratch : nullptr);
     if (rc != RSTQ_OK || w->kq) return rc;   // Q4_K units: the decode kernel added the min term itself
     return launch_q4k_min(ctx, ctx->devs[w->dev], w->mins, xs32, bsums, y, M, w->nb, w->out);
 }
@@ -220,7 +220,7 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
             // units with a scale per 16 elements: code sums per 16, one decode launch, y as it is
             rc = launch_quant_act_q8k(ctx, ds, (const float*)x, s.xq, nullptr, s.xs, s.xsum, M, w->in, 16);
             if (rc != RSTQ_OK) return rc;
-            return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M);
+            return run_a8(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M, nullptr, nullptr, ds.act_image ? s.img : nullptr);
         }
         if ((rc = dev_reserve(ds, &ds.kq_scratch, &ds.kq_scratch_bytes, M * w->out * 4)) != RSTQ_OK) return rc;
         rc = launch_quant_act_q8k(ctx, ds, (const float*)x, s.xq, nullptr, s.xs, s.xsum, M, w->in, 32);
@@ -239,7 +239,7 @@ int32_t matmul_device(rstq_ctx* ctx, rstq_weight* w, const void* x, void* y, int
         if (rc != RSTQ_OK) return rc;
         rc = launch_quant_act_q8k(ctx, ds, (const float*)x, s.xq, nullptr, s.xs, s.xsum, M, w->in, 32);
         if (rc != RSTQ_OK) return rc;
-        return run_q4k(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M);
+        return run_q4k(ctx, w, s.xq, s.xs, s.xsum, (float*)y, M, ds.act_image ? s.img : nullptr);
     }
     // Prefill shapes go to the tensor-core GEMM (fp16 operands, results within 1e-3 of the
     // reference).  A8 keeps its exact integer path up to M = 63: callers that chose the
@@ -1060,7 +1060,8 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
         if ((rc = act_scratch(dsk, M, w->in, &s)) != RSTQ_OK) return rc;
         if (w->k6) {   // the sums per 16 go to the kernel as they are; the scales per super-block are spread over the blocks
             if ((rc = launch_expand_scales(ctx, dsk, (const float*)xs->ptr, s.xs, M * w->nb)) != RSTQ_OK) return rc;
-            return run_a8(ctx, w, (const int8_t*)xq->ptr, s.xs, (const int32_t*)xsum->ptr, (float*)y->ptr, M);
+            return run_a8(ctx, w, (const int8_t*)xq->ptr, s.xs, (const int32_t*)xsum->ptr, (float*)y->ptr, M, nullptr, nullptr,
+                          dsk.act_image ? s.img : nullptr);
         }
         if ((rc = dev_reserve(dsk, &dsk.kq_scratch, &dsk.kq_scratch_bytes, M * w->out * 4)) != RSTQ_OK) return rc;
         if ((rc = launch_q6k_prep(ctx, dsk, (const float*)xs->ptr, (const int32_t*)xsum->ptr, s.xs, s.xsum,
@@ -1085,7 +1086,8 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
         ActScratch s;
         if ((rc = act_scratch(dsk, M, w->in, &s)) != RSTQ_OK) return rc;
         if ((rc = launch_expand_scales(ctx, dsk, (const float*)xs->ptr, s.xs, M * w->nb)) != RSTQ_OK) return rc;
-        return run_q4k(ctx, w, (const int8_t*)xq->ptr, s.xs, (const int32_t*)xsum->ptr, (float*)y->ptr, M);
+        return run_q4k(ctx, w, (const int8_t*)xq->ptr, s.xs, (const int32_t*)xsum->ptr, (float*)y->ptr, M,
+                       dsk.act_image ? s.img : nullptr);
     }
     if ((rc = need_bytes(xq, M * w->in, "xq")) != RSTQ_OK) return rc;
     if ((rc = need_bytes(xs, M * w->nb * 4, "xs")) != RSTQ_OK) return rc;

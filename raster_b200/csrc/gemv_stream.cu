@@ -1705,7 +1705,8 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         // that starts at such a boundary and takes all that is left up to the next
         const bool at_piece = a.img && a.uk == 0 && want > 1 && m0 % kGemvMaxM == 0;
         const uint8_t* img = at_piece ? a.img + (m0 / kGemvMaxM) * act_image_stride(nb) : nullptr;
-        if (want > 1 && a.uk == 0) {
+        const int rec_bytes = a.uk == 1 ? 8 : kActRecBytes;   // of a (block, token) record: Q4_K units keep {xs, xs * code sum}
+        if (want > 1) {
             // (measured on B200, int4, 4096 <= K <= 28672: with the image at hand the ring is as fast as
             // resident activations where those fit at the same depth and up to 3x faster where they do not;
             // 32-unit chunks lose 10 - 30 % in either form and 48-unit ones 3 - 6 %, whatever depth they buy:
@@ -1713,7 +1714,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
             const bool have_img = img != nullptr;
             const bool can_make = !have_img && a.img_scratch && want == a.M;   // pre-quantized: one more small kernel
             const int full = chunk_units_of(ukind), half = full / 2, NTw = want <= 8 ? 1 : 2;
-            const int64_t b1 = (int64_t)want * 32, b2 = (int64_t)((want + 1) & ~1) * kActRecBytes;
+            const int64_t b1 = (int64_t)want * 32, b2 = (int64_t)((want + 1) & ~1) * rec_bytes;
             const bool imgs = have_img || can_make;
             const StreamPlan res_h = plan_stream(ds, ukind, NTw, groups, nb, nb * b1, nb * b2, false, half);
             const StreamPlan ring_f = imgs ? plan_stream(ds, ukind, NTw, groups, nb, b1, b2, false, full, true) : StreamPlan{};
@@ -1731,7 +1732,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
                 pl = *pick;
                 M = want;
                 if (pl.ring && !have_img) {
-                    int32_t rc = launch_act_image(ctx, ds, a.xq, a.xs, a.xsum, a.M, a.in, a.img_scratch, a.zp, a.bits);
+                    int32_t rc = launch_act_image(ctx, ds, a.xq, a.xs, a.xsum, a.M, a.in, a.img_scratch, a.zp, a.bits, a.uk);
                     if (rc != RSTQ_OK) return rc;
                     img = a.img_scratch;
                 }
@@ -1764,10 +1765,10 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         RSTQ_REQUIRE(!pl.ring || img, RSTQ_E_STATE, "a ring of activations without their image");
         if (img) {
             p.slice1 = (uint32_t)M * 32u;
-            p.slice2 = (uint32_t)((M + 1) & ~1) * kActRecBytes;
+            p.slice2 = (uint32_t)((M + 1) & ~1) * rec_bytes;
             p.img = img;
             p.img_b_bytes = (uint32_t)(nb * M * 32);
-            p.img_z_bytes = (uint32_t)(nb * ((M + 1) & ~1) * kActRecBytes);
+            p.img_z_bytes = (uint32_t)(nb * ((M + 1) & ~1) * rec_bytes);
             p.img_z_off = (p.img_b_bytes + 127u) & ~127u;
         }
         if (a.tp) p.tp = *a.tp;

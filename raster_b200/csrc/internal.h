@@ -253,7 +253,7 @@ __device__ __forceinline__ void put_act_record(uint8_t* recs, int64_t b, int Mz,
 }
 #endif
 int32_t launch_act_image(rstq_ctx* ctx, DeviceState& ds, const int8_t* xq, const float* xs, const int32_t* xsum,
-                         int64_t M, int64_t in, uint8_t* img, int zp, int bits);
+                         int64_t M, int64_t in, uint8_t* img, int zp, int bits, int uk);
 int32_t launch_quant_act_i8(rstq_ctx* ctx, DeviceState& ds, const void* x, int8_t* xq, float* xs,
                             int32_t* xsum, int64_t M, int64_t in, int act_dtype = RSTQ_F32, uint8_t* img = nullptr, int zp = 0,
                             int bits = 8);

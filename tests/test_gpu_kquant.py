@@ -169,6 +169,44 @@ def oracle_rows_q6k(e, x, M, in_, out):
     return np.stack(ys)
 
 
+@pytest.mark.parametrize("fmt", ["q4k", "q6k"])
+@pytest.mark.parametrize("out,in_,M", [(64, 28672, 6), (96, 8192, 16), (72, 11008 // 256 * 256, 12), (40, 16384, 9)])
+def test_kquant_activations_ride_the_ring_when_k_is_long(ctx, fmt, out, in_, M):
+    """Several tokens of a long K do not fit in shared memory beside the weight ring: by default a small kernel
+    lays the q8_K codes, scales and sums out in the decode kernel's order and each ring stage carries the slice for
+    its K-blocks (one decode launch); with RSTQ_TUNE_ACT_RING = 1 the tokens that do not fit go to further launches.
+    The same sums in the same order: bit-identical (up to a last launch of one token, which runs the M = 1 kernel),
+    and within the oracle's bound."""
+    W = synth.normal(25 + out, out * in_, 0.02) + np.float32(0.01)
+    x = synth.normal(26 + in_, M * in_)
+    if fmt == "q4k":
+        e = orc.quantize_weight_q4k(W)
+        w, ref = ctx.bind_weight_q4k(e, out, in_), oracle_rows(e, x, M, in_, out)
+    else:
+        e = orc.quantize_weight_q6k(W)
+        w, ref = ctx.bind_weight_q6k(e, out, in_), oracle_rows_q6k(e, x, M, in_, out)
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    ys, launches = {}, {}
+    try:
+        for ring in (1, 0):
+            ctx.tune(L.TUNE_ACT_RING, ring)
+            for rep in range(2):
+                by.fill_bytes(0xFF)
+                n0 = ctx.launch_count()
+                ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+                ctx.sync()
+                launches[ring] = ctx.launch_count() - n0
+            ys[ring] = by.download()
+    finally:
+        ctx.tune(L.TUNE_ACT_RING, 0)
+    assert relerr(ys[0], ref) <= 1e-5 and relerr(ys[1], ref) <= 1e-5
+    head = (M - 1) * out
+    assert np.array_equal(ys[0][:head].view(np.uint32), ys[1][:head].view(np.uint32))
+    assert launches[0] <= 3 and launches[0] <= launches[1]      # quantizer, image, one decode launch
+    for o in (w, bx, by):
+        o.free()
+
+
 @pytest.mark.parametrize("out,in_,M", [(8, 256, 1), (100, 512, 3), (4096, 4096, 1), (1024, 2048, 8), (512, 1024, 20)])
 def test_q6k_matmul_matches_the_oracle(ctx, out, in_, M):
     W = synth.normal(15 + out, out * in_, 0.02)
