@@ -50,6 +50,7 @@
 (defrstq shutdown*           "rstq_shutdown"       I [P])
 (defrstq sync*               "rstq_sync"           I [P I])          ; ctx dev
 (defrstq gemm-plan*          "rstq_gemm_plan"      I [P L L L I])    ; plan2 out in m sm-count
+(defrstq decode-plan*        "rstq_decode_plan"    I [P I I L L L I I])  ; plan6 mode bits out in m act-dtype sm-count
 (defrstq tune*               "rstq_tune"           I [P I L])        ; ctx key value
 (defrstq device-info*        "rstq_device_info"    I [P P I])        ; ctx out4 dev
 (defrstq timeline-read*      "rstq_timeline_read"  I [P P I L])      ; ctx out dev n

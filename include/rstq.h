@@ -158,6 +158,13 @@ RSTQ_API int32_t rstq_shutdown(rstq_ctx* ctx);
  * tile (2 = each takes half of K; the second hands its sums to the first).  Pure host arithmetic: no
  * device, no context.  No counterpart in the reference (its GEMM is one work-item per output). */
 RSTQ_API int32_t rstq_gemm_plan(int32_t* plan2, int64_t out, int64_t in, int64_t m, int32_t sm_count);
+/* What the FIRST decode launch of rstq_qmatmul (mode, bits 4 / 8, act_dtype) on an out x in weight with m tokens
+ * would be at the default settings on a device of sm_count SMs: plan6[0] = tokens it takes (up to 16; 0 = a
+ * row of activations does not fit at all), [1] = ring stages, [2] = units per chunk, [3] = 1 when the
+ * activations ride the ring (RSTQ_TUNE_ACT_RING), [4] = dynamic shared memory in bytes (<= 231424),
+ * [5] = thread blocks.  Pure host arithmetic: no device, no context.  No counterpart in the reference. */
+RSTQ_API int32_t rstq_decode_plan(int32_t* plan6, int32_t mode, int32_t bits, int64_t out, int64_t in, int64_t m,
+                                  int32_t act_dtype, int32_t sm_count);
 RSTQ_API int32_t rstq_sync(rstq_ctx* ctx, int32_t dev);
 RSTQ_API int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value);
 /* out[0] = SM count, out[1] = L2 bytes, out[2] = total device memory, out[3] = cc major*10+minor */

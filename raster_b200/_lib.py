@@ -22,6 +22,7 @@ SIGNATURES = {
     "rstq_shutdown": [vp],
     "rstq_sync": [vp, i32],
     "rstq_gemm_plan": [C.POINTER(i32), i64, i64, i64, i32],
+    "rstq_decode_plan": [C.POINTER(i32), i32, i32, i64, i64, i64, i32, i32],
     "rstq_tune": [vp, i32, i64],
     "rstq_device_info": [vp, C.POINTER(i64), i32],
     "rstq_timeline_read": [vp, C.POINTER(i64), i32, i64],

@@ -126,7 +126,7 @@ static int32_t act_scratch(DeviceState& ds, int64_t M, int64_t in, ActScratch* o
     const int64_t nb = in / 32;
     const int64_t xq_bytes = (M * in + 255) & ~255ll;
     const int64_t sb = (M * nb * 4 + 255) & ~255ll;
-    const bool image = M >= 2 && M < 64;   // what the decode kernels serve in MODE_A8: one image per launch of kGemvMaxM tokens
+    const bool image = M >= 1 && M < 64;   // what the decode kernels serve in MODE_A8: one image per launch of kGemvMaxM tokens
     const int64_t img_bytes = image ? ((M + kGemvMaxM - 1) / kGemvMaxM) * act_image_stride(nb) : 0;
     // xsum has room for sums per 16 elements (Q6_K units): two per block
     int32_t rc = dev_reserve(ds, &ds.act_scratch, &ds.act_scratch_bytes, xq_bytes + 3 * sb + img_bytes);
@@ -533,6 +533,17 @@ int32_t rstq_gemm_plan(int32_t* plan2, int64_t out, int64_t in, int64_t m, int32
     plan2[0] = ntok;
     plan2[1] = split ? 2 : 1;
     return RSTQ_OK;
+}
+
+int32_t rstq_decode_plan(int32_t* plan6, int32_t mode, int32_t bits, int64_t out, int64_t in, int64_t m, int32_t act_dtype,
+                         int32_t sm_count) {
+    RSTQ_REQUIRE(plan6, RSTQ_E_INVALID, "null argument");
+    RSTQ_REQUIRE(mode == RSTQ_MODE_A8 || mode == RSTQ_MODE_F, RSTQ_E_INVALID, "unknown mode %d", mode);
+    RSTQ_REQUIRE(bits == 4 || bits == 8, RSTQ_E_INVALID, "bits = %d", bits);
+    RSTQ_REQUIRE(act_dtype == RSTQ_F32 || act_dtype == RSTQ_BF16, RSTQ_E_INVALID, "unknown activation type");
+    RSTQ_REQUIRE(out >= 1 && in >= 32 && in % 32 == 0 && m >= 1 && sm_count >= 1, RSTQ_E_SHAPE,
+                 "out = %lld, in = %lld, m = %lld, sm_count = %d", (long long)out, (long long)in, (long long)m, sm_count);
+    return decode_plan(mode == RSTQ_MODE_A8 ? 1 : 0, bits, out, in, m, act_dtype, sm_count, plan6);
 }
 
 int32_t rstq_sync(rstq_ctx* ctx, int32_t dev) {
@@ -1102,7 +1113,7 @@ int32_t rstq_qmatmul_prequant(rstq_ctx* ctx, rstq_weight* w, rstq_buf* xq, rstq_
     ActScratch s{};
     if (!sums) {
         if ((rc = act_scratch(ds, M, w->in, &s)) != RSTQ_OK) return rc;
-    } else if (M >= 2 && M <= 16 && ds.act_image) {
+    } else if (M >= 1 && M <= 16 && ds.act_image) {
         if (act_scratch(ds, M, w->in, &s) != RSTQ_OK) s = ActScratch{};   // no room to be had now (a capture in progress): without the image
     }
     if (!sums) {

@@ -1679,16 +1679,96 @@ static int fit_tokens(const DeviceState& ds, int bits, int64_t groups, int64_t n
     return 0;
 }
 
+// Mode A8, one launch: how many of `want` tokens it takes and with which plan.  uk = unit kind of the weight
+// (GemvA8Args::uk); have_img: the quantizer's image of exactly these tokens exists; can_make: it can be built by
+// act_image_kernel (one more small launch).  *make: the chosen plan needs that kernel.
+// With the image at hand, the activations can travel with the weight chunks instead of staying in shared
+// memory for all of K (StreamParams::ring).  Measured on B200, int4, 4096 <= K <= 28672: the ring is as fast as
+// resident activations where those fit at the same depth and up to 3x faster where they do not; 32-unit chunks
+// lose 10 - 30 % in either form and 48-unit ones 3 - 6 %, whatever depth they buy: above one token the loop is
+// bound by the consumers, not by the bytes in flight.
+static int plan_a8_piece(const DeviceState& ds, int uk, int bits, int64_t groups, int64_t nb, int want, bool have_img,
+                         bool can_make, StreamPlan* pl, bool* make) {
+    const bool k6 = uk == 2;
+    const int ukind = uk == 1 ? 5 : (k6 ? 6 : bits);
+    const int rec_bytes = uk == 1 ? 8 : kActRecBytes;   // of a (block, token) record: Q4_K units keep {xs, xs * code sum}
+    auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
+        *NT = m <= 8 ? 1 : 2;
+        if (m == 1) { *a1 = nb * (k6 ? 128 : 64); *a2 = 0; }
+        else { *a1 = nb * m * 32; *a2 = nb * ((m + 1) & ~1) * rec_bytes; }
+    };
+    *make = false;
+    int M = fit_tokens(ds, ukind, groups, nb, want, bytes, pl, true);
+    if (want <= 1) {
+        // one token of a row so long that its staged record leaves no room for two ring stages (4-bit units:
+        // K > ~57 K): the general kernel with the image riding the ring serves it
+        if (M < 1 && (have_img || can_make) && ds.act_ring != 1 && ds.act_ring != 4) {
+            const StreamPlan r = plan_stream(ds, ukind, 1, groups, nb, 32, 2 * rec_bytes, false, chunk_units_of(ukind), true);
+            if (r.fits) {
+                *pl = r;
+                M = 1;
+                *make = !have_img;
+            }
+        }
+        return M;
+    }
+    const int full = chunk_units_of(ukind), half = full / 2, NTw = want <= 8 ? 1 : 2;
+    const int64_t b1 = (int64_t)want * 32, b2 = (int64_t)((want + 1) & ~1) * rec_bytes;
+    const bool imgs = have_img || can_make;
+    const StreamPlan res_h = plan_stream(ds, ukind, NTw, groups, nb, nb * b1, nb * b2, false, half);
+    const StreamPlan ring_f = imgs ? plan_stream(ds, ukind, NTw, groups, nb, b1, b2, false, full, true) : StreamPlan{};
+    const StreamPlan ring_h = imgs ? plan_stream(ds, ukind, NTw, groups, nb, b1, b2, false, half, true) : StreamPlan{};
+    const StreamPlan* pick = nullptr;
+    switch (ds.act_ring) {
+        case 1: break;
+        case 2: if (ring_f.fits) pick = &ring_f; break;
+        case 3: if (ring_h.fits) pick = &ring_h; break;
+        case 4: if (res_h.fits) pick = &res_h; break;
+        default:
+            if (ring_f.fits && (have_img || M < want || ring_f.NS > pl->NS)) pick = &ring_f;
+    }
+    if (pick) {
+        *pl = *pick;
+        M = want;
+        *make = pl->ring && !have_img;
+    }
+    return M;
+}
+
+static int plan_f_piece(const DeviceState& ds, int bits, int64_t groups, int64_t nb, int want, int act_dtype,
+                        int* max_terms, bool ring_ok, StreamPlan* pl);
+
+// What the decode kernel's launcher would do with the first launch of a call, as host arithmetic (rstq_decode_plan).
+int32_t decode_plan(int mode, int bits, int64_t out, int64_t in, int64_t M, int act_dtype, int sm_count, int32_t* res) {
+    DeviceState ds;
+    ds.sm_count = sm_count;
+    const int64_t nb = in / 32, groups = (out + 31) / 32;
+    const int want = (int)(M < kGemvMaxM ? M : kGemvMaxM);
+    StreamPlan pl{};
+    int m;
+    if (mode == MODE_A8) {
+        bool make = false;
+        // (the operator's quantizer lays the image out whenever it runs as a kernel of its own: above one token,
+        // and at one token of a row longer than the in-kernel quantizer takes)
+        m = plan_a8_piece(ds, 0, bits, groups, nb, want, want > 1 || in > kFusedQuantMaxIn, false, &pl, &make);
+    } else {
+        int max_terms = 3;
+        m = plan_f_piece(ds, bits, groups, nb, want, act_dtype, &max_terms, true, &pl);
+    }
+    res[0] = m;
+    res[1] = m >= 1 ? pl.NS : 0;
+    res[2] = m >= 1 ? pl.cu : 0;
+    res[3] = m >= 1 ? pl.ring : 0;
+    res[4] = m >= 1 ? (int32_t)pl.smem : 0;
+    res[5] = m >= 1 ? pl.G : 0;
+    return RSTQ_OK;
+}
+
 int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
     RSTQ_REQUIRE(a.M >= 1, RSTQ_E_SHAPE, "M = %lld", (long long)a.M);
     const int64_t nb = a.in / 32, groups = (a.out + 31) / 32;
     RSTQ_REQUIRE(nb < (1 << 24) && groups * nb < (1ll << 40), RSTQ_E_LIMIT, "matrix too large");
     const bool k6 = a.uk == 2;
-    auto bytes = [&](int m, int* NT, int64_t* a1, int64_t* a2) {
-        *NT = m <= 8 ? 1 : 2;
-        if (m == 1) { *a1 = nb * (k6 ? 128 : 64); *a2 = 0; }
-        else { *a1 = nb * m * 32; *a2 = nb * ((m + 1) & ~1) * (k6 ? 16 : (a.uk == 0 ? kActRecBytes : 8)); }
-    };
     // unit kind for the size helpers: Q4_K units carry 128 more bytes than 4-bit ones, Q6_K units 128 more than 8-bit ones
     const int ukind = a.uk == 1 ? 5 : (k6 ? 6 : a.bits);
     RSTQ_REQUIRE(a.uk == 0 || (a.bits == (k6 ? 8 : 4) && !a.tp && !a.x), RSTQ_E_INVALID,
@@ -1696,47 +1776,18 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
     for (int64_t m0 = 0; m0 < a.M;) {
         const int want = (int)(a.M - m0 < kGemvMaxM ? a.M - m0 : kGemvMaxM);
         StreamPlan pl;
-        int M = fit_tokens(ds, ukind, groups, nb, want, bytes, &pl, true);
-        // With the quantizer's image of the whole call at hand, the activations can travel with the weight
-        // chunks instead of staying in shared memory for all of K (StreamParams::ring); smaller chunks give
-        // a ring of the same bytes more stages.  Chosen by the weight bytes on their way while one chunk is
-        // consumed, which is what bounds the stream.
         // the quantizer's image of this launch's tokens: laid out per kGemvMaxM tokens, so it serves a launch
         // that starts at such a boundary and takes all that is left up to the next
-        const bool at_piece = a.img && a.uk == 0 && want > 1 && m0 % kGemvMaxM == 0;
+        const bool at_piece = a.img && a.uk == 0 && m0 % kGemvMaxM == 0 && (want > 1 || a.M == 1);
         const uint8_t* img = at_piece ? a.img + (m0 / kGemvMaxM) * act_image_stride(nb) : nullptr;
-        const int rec_bytes = a.uk == 1 ? 8 : kActRecBytes;   // of a (block, token) record: Q4_K units keep {xs, xs * code sum}
-        if (want > 1) {
-            // (measured on B200, int4, 4096 <= K <= 28672: with the image at hand the ring is as fast as
-            // resident activations where those fit at the same depth and up to 3x faster where they do not;
-            // 32-unit chunks lose 10 - 30 % in either form and 48-unit ones 3 - 6 %, whatever depth they buy:
-            // above one token the loop is bound by the consumers' instructions, not by the bytes in flight)
-            const bool have_img = img != nullptr;
-            const bool can_make = !have_img && a.img_scratch && want == a.M;   // pre-quantized: one more small kernel
-            const int full = chunk_units_of(ukind), half = full / 2, NTw = want <= 8 ? 1 : 2;
-            const int64_t b1 = (int64_t)want * 32, b2 = (int64_t)((want + 1) & ~1) * rec_bytes;
-            const bool imgs = have_img || can_make;
-            const StreamPlan res_h = plan_stream(ds, ukind, NTw, groups, nb, nb * b1, nb * b2, false, half);
-            const StreamPlan ring_f = imgs ? plan_stream(ds, ukind, NTw, groups, nb, b1, b2, false, full, true) : StreamPlan{};
-            const StreamPlan ring_h = imgs ? plan_stream(ds, ukind, NTw, groups, nb, b1, b2, false, half, true) : StreamPlan{};
-            const StreamPlan* pick = nullptr;
-            switch (ds.act_ring) {
-                case 1: break;
-                case 2: if (ring_f.fits) pick = &ring_f; break;
-                case 3: if (ring_h.fits) pick = &ring_h; break;
-                case 4: if (res_h.fits) pick = &res_h; break;
-                default:
-                    if (ring_f.fits && (have_img || M < want || ring_f.NS > pl.NS)) pick = &ring_f;
-            }
-            if (pick) {
-                pl = *pick;
-                M = want;
-                if (pl.ring && !have_img) {
-                    int32_t rc = launch_act_image(ctx, ds, a.xq, a.xs, a.xsum, a.M, a.in, a.img_scratch, a.zp, a.bits, a.uk);
-                    if (rc != RSTQ_OK) return rc;
-                    img = a.img_scratch;
-                }
-            }
+        const int rec_bytes = a.uk == 1 ? 8 : kActRecBytes;
+        bool make = false;
+        const bool can_make = !img && a.img_scratch && want == a.M;   // pre-quantized: one more small kernel
+        int M = plan_a8_piece(ds, a.uk, a.bits, groups, nb, want, img != nullptr, can_make, &pl, &make);
+        if (make) {
+            int32_t rc = launch_act_image(ctx, ds, a.xq, a.xs, a.xsum, a.M, a.in, a.img_scratch, a.zp, a.bits, a.uk);
+            if (rc != RSTQ_OK) return rc;
+            img = a.img_scratch;
         }
         RSTQ_REQUIRE(M >= 1, RSTQ_E_LIMIT, "in = %lld: one row of activations exceeds shared memory",
                      (long long)a.in);
@@ -1761,7 +1812,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
         }
         p.y = a.y + m0 * a.out;
         p.T = 1; p.act_dtype = qf ? a.act_dtype : RSTQ_F32; p.out_dtype = RSTQ_F32;
-        if (M != want) img = nullptr;   // fewer tokens than the image was laid out for
+        if (M != want || (M == 1 && !pl.ring)) img = nullptr;   // fewer tokens than the image was laid out for; one token keeps its own record
         RSTQ_REQUIRE(!pl.ring || img, RSTQ_E_STATE, "a ring of activations without their image");
         if (img) {
             p.slice1 = (uint32_t)M * 32u;
@@ -1786,19 +1837,19 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a) {
     } while (0)
         if (k6) {
             if (NT == 2) le = launch_stream(gemv_stream_kernel<8, 2, MODE_A8, false, false, false, 2>, ds, pl, p);
-            else if (M == 1) le = launch_stream(gemv_stream_kernel<8, 1, MODE_A8, true, false, false, 2>, ds, pl, p);
+            else if (M == 1 && !pl.ring) le = launch_stream(gemv_stream_kernel<8, 1, MODE_A8, true, false, false, 2>, ds, pl, p);
             else le = launch_stream(gemv_stream_kernel<8, 1, MODE_A8, false, false, false, 2>, ds, pl, p);
         } else if (a.uk == 1) {
             if (NT == 2) le = launch_stream(gemv_stream_kernel<4, 2, MODE_A8, false, false, false, 1>, ds, pl, p);
-            else if (M == 1) le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, true, false, false, 1>, ds, pl, p);
+            else if (M == 1 && !pl.ring) le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, true, false, false, 1>, ds, pl, p);
             else le = launch_stream(gemv_stream_kernel<4, 1, MODE_A8, false, false, false, 1>, ds, pl, p);
         } else if (a.bits == 4) {
             if (NT == 2) LAUNCH(4, 2, MODE_A8, false);
-            else if (M == 1) LAUNCH1(4);
+            else if (M == 1 && !pl.ring) LAUNCH1(4);
             else LAUNCH(4, 1, MODE_A8, false);
         } else {
             if (NT == 2) LAUNCH(8, 2, MODE_A8, false);
-            else if (M == 1) LAUNCH1(8);
+            else if (M == 1 && !pl.ring) LAUNCH1(8);
             else LAUNCH(8, 1, MODE_A8, false);
         }
 #undef LAUNCH1
@@ -1830,14 +1881,16 @@ static int plan_f_piece(const DeviceState& ds, int bits, int64_t groups, int64_t
         m = fit_tokens(ds, bits, groups, nb, want, bytes, pl);
     }
     if (m < want && ring_ok && ds.act_ring != 1 && ds.act_ring != 4) {
-        const int C = want * terms(want);
-        if (C <= 16) {
+        for (int mm = want; mm > m; --mm) {   // the most tokens whose columns of terms ride the ring
+            const int C = mm * terms(mm);
+            if (C > 16) continue;
             const int NT = C <= 8 ? 1 : 2, full = chunk_units_of(bits);
             StreamPlan r = plan_stream(ds, bits, NT, groups, nb, 2 * C * 32, 0, false, full, true);
             if (!r.fits || ds.act_ring == 3) r = plan_stream(ds, bits, NT, groups, nb, 2 * C * 32, 0, false, full / 2, true);
             if (r.fits) {
                 *pl = r;
-                m = want;
+                m = mm;
+                break;
             }
         }
     }

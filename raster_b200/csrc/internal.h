@@ -313,6 +313,7 @@ int32_t launch_gemv_a8(rstq_ctx* ctx, DeviceState& ds, const GemvA8Args& a);
 int32_t launch_gemv_f(rstq_ctx* ctx, DeviceState& ds, const GemvFArgs& a);
 int gemv_f_pieces(const DeviceState& ds, int bits, int64_t out, int64_t in, int64_t M, int act_dtype);
 int64_t gemv_f_image_bytes(int64_t in);
+int32_t decode_plan(int mode, int bits, int64_t out, int64_t in, int64_t M, int act_dtype, int sm_count, int32_t* res);
 int32_t gemv_configure(DeviceState& ds);  // shared-memory attributes, once per device
 // gemm_tc.cu
 // gemm_tc.cu: token-tile width (32 / 64 / 128 / 256) and whether two CTAs share a tile, for a device of sm_count SMs

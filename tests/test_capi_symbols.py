@@ -87,3 +87,52 @@ def test_gemm_plan_is_host_arithmetic_and_follows_the_wave_model():
     assert of(4096, 4096, 512, sm=296) == (128, 2)   # a part twice as wide would split
     assert lib.rstq_gemm_plan(plan, 4096, 100, 64, 148) == L.E_SHAPE
     assert lib.rstq_gemm_plan(None, 4096, 4096, 64, 148) == L.E_INVALID
+
+
+def test_decode_plan_is_host_arithmetic_and_always_fits_shared_memory():
+    """rstq_decode_plan needs no device: what the first decode launch of a call would be.  One token keeps its
+    activations resident; several tokens of MODE_A8 ride the weight ring in one launch whatever K is (three
+    stages up to 8 tokens, two at 9 .. 16); MODE_F rides the ring where the staged terms do not fit (up to 16
+    columns of terms), else takes fewer tokens.  Over a sweep of shapes and token counts the plan never asks
+    for more than the 227 KB of dynamic shared memory a thread block can have, nor for fewer than two stages."""
+    import ctypes as C
+    from raster_b200 import _lib as L
+    lib = L.load()
+    plan = (C.c_int32 * 6)()
+
+    def of(mode, bits, out, in_, m, act=L.F32, sm=148):
+        L.check(lib.rstq_decode_plan(plan, mode, bits, out, in_, m, act, sm))
+        return {"tokens": plan[0], "stages": plan[1], "chunk": plan[2], "ring": plan[3], "smem": plan[4], "blocks": plan[5]}
+    p = of(L.MODE_A8, 4, 11008, 4096, 1)
+    assert (p["tokens"], p["ring"], p["chunk"], p["blocks"]) == (1, 0, 64, 115) and p["stages"] >= 4
+    p = of(L.MODE_A8, 4, 8192, 28672, 8)
+    assert (p["tokens"], p["ring"], p["stages"], p["chunk"], p["blocks"]) == (8, 1, 3, 64, 128)
+    p = of(L.MODE_A8, 4, 28672, 8192, 16)
+    assert (p["tokens"], p["ring"], p["stages"]) == (16, 1, 2)
+    p = of(L.MODE_A8, 8, 4096, 4096, 4)
+    assert (p["tokens"], p["ring"], p["chunk"]) == (4, 1, 32)
+    p = of(L.MODE_F, 4, 4096, 11008, 4, L.F32)          # 4 f32 tokens = 8 columns of terms: one launch on the ring
+    assert (p["tokens"], p["ring"]) == (4, 1)
+    p = of(L.MODE_F, 4, 4096, 11008, 8, L.BF16)
+    assert (p["tokens"], p["ring"]) == (8, 1)
+    p = of(L.MODE_F, 4, 4096, 4096, 4, L.BF16)          # fits beside the ring: resident
+    assert (p["tokens"], p["ring"]) == (4, 0)
+    p = of(L.MODE_F, 4, 4096, 11008, 16, L.F32)         # 32 columns of terms: the 8 tokens (16 columns) that ride the ring
+    assert (p["tokens"], p["ring"], p["chunk"]) == (8, 1, 32)
+    p = of(L.MODE_A8, 4, 4096, 65536, 1)                # one token of a row too long to stay resident: the ring serves it
+    assert (p["tokens"], p["ring"]) == (1, 1)
+    for mode in (L.MODE_A8, L.MODE_F):
+        for bits in (4, 8):
+            for in_ in (32, 256, 4096, 8192, 11008, 16384, 28672, 65536):
+                for m in (1, 2, 3, 5, 8, 9, 12, 16, 40):
+                    for act in (L.F32, L.BF16):
+                        p = of(mode, bits, 4096, in_, m, act)
+                        assert 1 <= p["tokens"] <= min(m, 16)
+                        assert p["stages"] >= 2 and 16 <= p["chunk"] <= 64
+                        assert 0 < p["smem"] <= 231424, (mode, bits, in_, m, act, p)
+                        assert 1 <= p["blocks"] <= 148
+                        if mode == L.MODE_A8 and m > 1:
+                            assert p["ring"] == 1 and p["tokens"] == min(m, 16)
+    assert lib.rstq_decode_plan(plan, L.MODE_A8, 4, 4096, 100, 1, L.F32, 148) == L.E_SHAPE
+    assert lib.rstq_decode_plan(plan, 7, 4, 4096, 4096, 1, L.F32, 148) == L.E_INVALID
+    assert lib.rstq_decode_plan(None, L.MODE_A8, 4, 4096, 4096, 1, L.F32, 148) == L.E_INVALID

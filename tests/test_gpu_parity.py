@@ -222,6 +222,39 @@ def test_activations_riding_the_ring_give_the_same_bits(ctx, bits, plan, M, out,
     w.free()
 
 
+@pytest.mark.parametrize("M", [1, 3])
+@pytest.mark.parametrize("bits", [4, 8])
+def test_rows_too_long_to_stay_resident_ride_the_ring(ctx, bits, M):
+    """K = 65536: the staged record of even one token (64 B per block for 4-bit units) leaves no room for two
+    ring stages beside it, so the call runs on the general kernel with the quantizer's image riding the ring --
+    through the operator and through the pre-quantized entry (image built by a kernel of its own).  MODE_F too."""
+    out, in_ = 40, 65536
+    fmt_desc, fmt, ofmt = FMT[bits]
+    _, wq, ws = make_weight(out, in_, bits, seed=77 + M)
+    x = synth.normal(78 + M, M * in_)
+    w = ctx.bind_weight(wq, ws, out, in_, fmt, L.LAYOUT_ROWMAJOR)
+    bx, by = ctx.array_to_buffer(x), ctx.make_buffer(M * out, np.float32)
+    xq, xs, xsum = orc.quantize_act_i8(x, M, in_)
+    ref = orc.matmul_a8_f64(wq, ws, ofmt, xq, xs, xsum, M, in_, out)
+    by.fill_bytes(0xFF)
+    ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_A8)
+    ctx.sync()
+    y_op = by.download()
+    assert relerr(y_op, ref) <= TOL_A8
+    bq, bs, bsum = ctx.array_to_buffer(xq), ctx.array_to_buffer(xs), ctx.array_to_buffer(xsum)
+    by.fill_bytes(0xFF)
+    ctx.qmatmul_prequant(w, bq, bs, bsum, by, M)
+    ctx.sync()
+    assert np.array_equal(by.download().view(np.uint32), y_op.view(np.uint32))
+    by.fill_bytes(0xFF)
+    ctx.qmatmul(w, bx, by, M, L.F32, L.F32, L.MODE_F)
+    ctx.sync()
+    assert relerr(by.download(), orc.matmul_dq_f64(wq, ws, ofmt, x, M, in_, out)) <= TOL_F
+    for b in (bx, by, bq, bs, bsum):
+        b.free()
+    w.free()
+
+
 @pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("act", ["f32", "bf16"])
 @pytest.mark.parametrize("M,out,in_", [(4, 300, 11008), (8, 200, 11008), (3, 64, 28672), (16, 64, 8192), (2, 96, 28672),
