@@ -1479,15 +1479,19 @@ struct StreamPlan {
 // groups were faster every time, by 3 % (64 groups) to 37 % (Llama-7B shapes), even with only 32 of
 // 148 SMs holding a CTA.  The equal-range split is kept for matrices so flat that a handful of
 // CTAs would each have to stream many megabytes.
-static bool whole_groups_pay(int64_t groups, int64_t nb, int64_t k, int64_t Gw, int sm_count, int unit) {
+// Two token tiles (9 .. 16 tokens): the loop is bound by the consumers, so SMs left without a thread block cost
+// their share: 70B-class matrices (7 groups per block, 128 of 148 SMs busy) gain 3 - 6 % from the equal-range
+// split, the 7B shapes (3 groups per block) still lose 7 - 15 % to its hand-overs.
+static bool whole_groups_pay(int64_t groups, int64_t nb, int64_t k, int64_t Gw, int sm_count, int unit, int nt) {
     (void)groups;
     const int64_t bytes_per_cta = k * nb * unit;
+    if (nt >= 2 && Gw * 8 < sm_count * 7 && bytes_per_cta >= (1ll << 20)) return false;
     return !(Gw * 2 < sm_count && bytes_per_cta > (4ll << 20));
 }
 
 // How the units of a weight are cut over the CTAs of a launch: G ranges, CTA c owns uq (+1 if c < ur).
 static void split_units(const DeviceState& ds, int bits, int64_t groups, int64_t nb, int* Gout, int64_t* uq,
-                        int64_t* ur) {
+                        int64_t* ur, int nt = 1) {
     const int kChunkUnits = chunk_units_of(bits);
     const int64_t U = groups * nb;
     int64_t G = (U + kChunkUnits - 1) / kChunkUnits;  // at least one chunk of work per CTA
@@ -1501,7 +1505,7 @@ static void split_units(const DeviceState& ds, int bits, int64_t groups, int64_t
     const int64_t k = (groups + ds.sm_count - 1) / ds.sm_count;   // groups per CTA
     const int64_t Gw = (groups + k - 1) / k;
     bool whole = ds.gemv_plan == 2;
-    if (ds.gemv_plan == 0) whole = whole_groups_pay(groups, nb, k, Gw, ds.sm_count, unit_bytes(bits));
+    if (ds.gemv_plan == 0) whole = whole_groups_pay(groups, nb, k, Gw, ds.sm_count, unit_bytes(bits), nt);
     if (whole && groups >= 1) {
         *Gout = (int)Gw;
         *uq = k * nb;
@@ -1533,7 +1537,7 @@ static StreamPlan plan_stream(const DeviceState& ds, int bits, int NT, int64_t g
     if (ns > RSTQ_NSMAX) ns = RSTQ_NSMAX;
     pl.fits = ns >= 2;
     if (!pl.fits) return pl;
-    split_units(ds, bits, groups, nb, &pl.G, &pl.uq, &pl.ur);
+    split_units(ds, bits, groups, nb, &pl.G, &pl.uq, &pl.ur, onecol ? 1 : NT);
     pl.NS = (int)ns;
     pl.cu = cu;
     pl.ring = ring;
@@ -1641,7 +1645,8 @@ static void fill_next(StreamParams& p, const DeviceState& ds, const NextWeight& 
     p.nx_w = n.data;
     p.nx_unit = unit_bytes(n.bits);
     p.nx_U = n.groups * n.nb;
-    split_units(ds, n.bits, n.groups, n.nb, &p.nx_G, &p.nx_uq, &p.nx_ur);
+    // (the next launch is taken to have this one's token tiles: a decode loop runs its matrices with one M)
+    split_units(ds, n.bits, n.groups, n.nb, &p.nx_G, &p.nx_uq, &p.nx_ur, p.M * (p.T > 0 ? p.T : 1) <= 8 ? 1 : 2);
     const int64_t per_cta = kNextPrefetchBytes / p.nx_G / p.nx_unit;
     p.nx_pf_units = per_cta < 1 ? 1 : per_cta;
 }
