@@ -303,6 +303,9 @@ def run_tp(args, world, rank, local_rank):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     hbm_peak, peak_src = measured_peaks()
     ctx = Context((f"cuda:{local_rank}",))
+    for kv in (args.tune.split(",") if args.tune else []):     # e.g. 15=0: every thread block stays for the exchange's tail
+        k, v = kv.split("=")
+        ctx.tune(int(k), int(v))
     info = ctx.device_info()
     weights = make_weights(rank)          # this rank's slab of the N-times larger matrices
     up, down = weights
@@ -1502,7 +1505,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, help="small single-kernel case for profiler captures")
     ap.add_argument("--plan", type=int, default=0, help="with --case: decode work split (rstq_tune key 4)")
-    ap.add_argument("--tune", default="", help="with --case m1 / timeline: rstq_tune settings, key=value[,key=value ...]")
+    ap.add_argument("--tune", default="", help="with --case m1 / timeline, or --gpus N: rstq_tune settings, key=value[,key=value ...]")
     ap.add_argument("--no-prefetch", action="store_true",
                     help="with --case gemv: no L2 requests ahead (neither the next weight nor the own range)")
     args = ap.parse_args()

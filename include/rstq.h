@@ -119,6 +119,10 @@ typedef struct rstq_event rstq_event;
                                      thread) instead of 128-token ones: 0 (default) = where the grid then needs
                                      fewer cycles over its waves of thread blocks, 1 = never, 2 = always,
                                      3 = as 0 but never two thread blocks per tile (each half of K) */
+#define RSTQ_TUNE_TP_TAIL 15      /* fused decode + exchange (rstq_tp_qmatmul): how many thread blocks of the decode kernel
+                                     stay for the exchange's tail (wait for the peers' results, write y); the others
+                                     leave their SMs to the next launch, which fills its weight rings meanwhile.
+                                     0 = all of them; default 32, and never fewer than one thread per pair of results */
 #define RSTQ_TUNE_ACT_RING 14     /* MODE_A8 decode launches of 2 .. 16 tokens, how the activations share shared memory
                                      with the weight ring: 0 (default) = every ring stage carries its own slice of
                                      the activation image wherever that image exists (always in rstq_qmatmul; in

@@ -103,6 +103,7 @@ SPLIT_NONE, SPLIT_COLUMN, SPLIT_ROW = 0, 1, 2
 TUNE_GEMM_KERNEL, TUNE_GEMM_MIN_M, TUNE_PDL, TUNE_TIMELINE, TUNE_GEMV_PLAN = 0, 1, 2, 3, 4
 TUNE_FUSE_QUANT, TUNE_GEMV_PREFETCH, TUNE_PROBE, TUNE_PREFETCH_NEXT, TUNE_ACT_IMAGE, TUNE_Q4K_UNITS, TUNE_Q6K_UNITS, TUNE_GEMM_WIDE = 6, 7, 8, 9, 10, 11, 12, 13
 TUNE_ACT_RING = 14
+TUNE_TP_TAIL = 15
 
 
 class RstqError(RuntimeError):

@@ -622,6 +622,10 @@ int32_t rstq_tune(rstq_ctx* ctx, int32_t key, int64_t value) {
         case RSTQ_TUNE_ACT_IMAGE:
             for (auto& ds : ctx->devs) ds.act_image = value != 0;
             return RSTQ_OK;
+        case RSTQ_TUNE_TP_TAIL:
+            RSTQ_REQUIRE(value >= 0 && value <= 1024, RSTQ_E_INVALID, "thread blocks for the exchange's tail: 0 (all) .. 1024");
+            for (auto& ds : ctx->devs) ds.tp_tail_ctas = (int)value;
+            return RSTQ_OK;
         case RSTQ_TUNE_ACT_RING:
             RSTQ_REQUIRE(value >= 0 && value <= 4, RSTQ_E_INVALID, "activation ring selector 0..4");
             for (auto& ds : ctx->devs) ds.act_ring = value;

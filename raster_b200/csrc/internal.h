@@ -81,6 +81,7 @@ struct DeviceState {
     int gemv_probe = 0;            // timing probes of the decode kernel (RSTQ_TUNE_PROBE); results are invalid while set
     bool prefetch_next = true;     // decode launches request the weight that followed this one last time into L2
     rstq_weight* last_decode_w = nullptr;   // the weight of the most recent decode launch on this device
+    int tp_tail_ctas = 32;         // fused exchange: fewest thread blocks of the decode kernel that stay for the exchange's tail (0 = all)
     int act_ring = 0;              // MODE_A8, M > 1: 0 = the plan with most weight bytes in flight, 1 = activations resident + full chunks, 2 / 3 = activations ride the ring (full / half chunks), 4 = resident + half chunks
     bool act_image = true;         // MODE_A8, 2 <= M <= 16: the quantizer also writes the decode kernel's staged form, taken by bulk copy
     bool x_on_host = false;        // the current host-array call lets its first kernel read x from pinned host memory
