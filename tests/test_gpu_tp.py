@@ -74,7 +74,7 @@ def test_allgather_and_allreduce_primitives(group):
 
 
 @pytest.mark.parametrize("bits,fmt", [(4, L.FMT_Q4_0), (8, L.FMT_Q8_0)])
-@pytest.mark.parametrize("M,mode", [(1, L.MODE_A8), (4, L.MODE_F)])
+@pytest.mark.parametrize("M,mode", [(1, L.MODE_A8), (4, L.MODE_F), (4, L.MODE_A8), (12, L.MODE_A8)])   # M > 1 in MODE_A8: the activations ride the ring of the fused kernel too
 def test_column_split_gathers_every_ranks_columns(group, bits, fmt, M, mode):
     ctx, tps, P = group
     out, in_ = 512 * P, 1024
@@ -106,7 +106,7 @@ def test_column_split_gathers_every_ranks_columns(group, bits, fmt, M, mode):
 
 
 @pytest.mark.parametrize("bits,fmt", [(4, L.FMT_Q4_0), (8, L.FMT_Q8_0)])
-@pytest.mark.parametrize("M,mode", [(1, L.MODE_A8), (3, L.MODE_F)])
+@pytest.mark.parametrize("M,mode", [(1, L.MODE_A8), (3, L.MODE_F), (5, L.MODE_A8)])
 def test_row_split_sums_to_the_oracle(group, bits, fmt, M, mode):
     ctx, tps, P = group
     out, in_ = 768, 1024 * P
