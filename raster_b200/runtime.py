@@ -21,6 +21,24 @@ from . import _lib as L
 _ptr_cache: dict = {}   # id(array) -> (weak reference to it, its address): hot callers pass the same arrays
 
 
+def gemm_plan(out: int, in_: int, m: int, sm_count: int = 148) -> dict:
+    """How the prefill GEMM would tile a call on a device of sm_count SMs (rstq_gemm_plan: host arithmetic, no
+    device): tokens per tile and thread blocks per tile."""
+    plan = (C.c_int32 * 2)()
+    L.check(L.load().rstq_gemm_plan(plan, out, in_, m, sm_count))
+    return {"tile_tokens": plan[0], "blocks_per_tile": plan[1]}
+
+
+def decode_plan(mode: int, bits: int, out: int, in_: int, m: int, act_dtype: int = L.F32, sm_count: int = 148) -> dict:
+    """What the first decode launch of a call would be (rstq_decode_plan: host arithmetic, no device): tokens it
+    takes, ring stages, units per chunk, whether the activations ride the weight ring, dynamic shared memory,
+    thread blocks."""
+    plan = (C.c_int32 * 6)()
+    L.check(L.load().rstq_decode_plan(plan, mode, bits, out, in_, m, act_dtype, sm_count))
+    return {"tokens": plan[0], "stages": plan[1], "chunk_units": plan[2], "ring": bool(plan[3]), "smem_bytes": plan[4],
+            "blocks": plan[5]}
+
+
 def _np_ptr(a: np.ndarray):
     """Address of a C-contiguous array as an int (c_void_p parameters take it).  `ndarray.ctypes` costs
     about a microsecond per use, a quarter of a small operator call with four arrays, so addresses of

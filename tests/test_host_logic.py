@@ -105,3 +105,15 @@ def test_synthetic_streams_are_counter_based():
     assert np.array_equal(a[:100], synth.normal(1, 100, 0.02))
     assert abs(float(a.std()) - 0.02) < 0.002 and abs(float(a.mean())) < 0.002
     assert not np.array_equal(a[:100], synth.normal(2, 100, 0.02))
+
+
+def test_plan_queries_need_no_device():
+    """runtime.gemm_plan / decode_plan wrap the two host-arithmetic entries of the library: they answer on a
+    machine without a GPU (no context is made)."""
+    from raster_b200 import _lib as L
+    from raster_b200 import runtime as R
+    assert R.gemm_plan(4096, 4096, 512) == {"tile_tokens": 128, "blocks_per_tile": 1}
+    p = R.decode_plan(L.MODE_A8, 4, 8192, 28672, 8)
+    assert p["tokens"] == 8 and p["ring"] and p["stages"] == 3 and p["smem_bytes"] <= 231424
+    p = R.decode_plan(L.MODE_F, 4, 4096, 4096, 1, L.BF16)
+    assert p["tokens"] == 1 and not p["ring"]
