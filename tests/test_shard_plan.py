@@ -126,7 +126,30 @@ def _gloo_rank(rank, world, port, q):
                 dist.all_reduce(t, op=dist.ReduceOp.SUM)
                 res[split] = t.numpy()
         full = np.asarray(orc.matmul_dq_f64(wq, ws, 0, x, M, in_, out), np.float32).reshape(M, out)
-        q.put((rank, bool(np.array_equal(res["column"], full)), relerr(res["row"], full)))
+        # the K-quant formats the same way: rows, or whole super-blocks of K, per rank (one token)
+        kq_ok = True
+        rng = np.random.default_rng(9)
+        Wk = (rng.standard_normal(32 * 512) * 0.02 + 0.01).astype(np.float32)
+        xk = rng.standard_normal(512).astype(np.float32)
+        for fmt, quant, mm, sub in (("q4k", orc.quantize_weight_q4k, orc.qmatmul_q4k, 32),
+                                    ("q6k", orc.quantize_weight_q6k, orc.qmatmul_q6k, 16)):
+            e = quant(Wk)
+            a, b, c = orc.quantize_act_q8k(xk, 512, sub)
+            fullk = np.asarray(mm(a, b, c, e, 512, 32)[1], np.float32).ravel()
+            for split in ("column", "row"):
+                plan = shard.ShardPlan(split, world)
+                so, si = shard.shard_shape(plan, 32, 512)
+                er = shard.shard_kquant(plan, rank, e, 32, 512)
+                a, b, c = orc.quantize_act_q8k(shard.slice_activations(plan, rank, xk, 1, 512), si, sub)
+                t = torch.from_numpy(np.asarray(mm(a, b, c, er, si, so)[1], np.float32).ravel().copy())
+                if split == "column":
+                    got = [torch.empty_like(t) for _ in range(world)]
+                    dist.all_gather(got, t)
+                    kq_ok = kq_ok and bool(np.array_equal(torch.cat(got).numpy(), fullk))
+                else:
+                    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+                    kq_ok = kq_ok and relerr(t.numpy(), fullk) <= 1e-6
+        q.put((rank, bool(np.array_equal(res["column"], full)) and kq_ok, relerr(res["row"], full)))
     finally:
         dist.destroy_process_group()
 
